@@ -1,0 +1,404 @@
+"""ctypes/numpy front end of the CPU oracle (``oxq_oracle.c``).
+
+TEST INFRASTRUCTURE ONLY.  Tests, the smoke run and the benchmark's CPU-baseline leg import this
+module as the checker; the product package never does.
+
+Function families (see the C file for the reference file:line each one follows):
+
+* ``ref_*``  -- literal restatements of the reference's CPU arithmetic.
+* ``spec_*`` -- the arithmetic of the benchmark configurations where the reference has none
+  (parity unpinned; the exact formulas are stated in the C source).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "liboxq_oracle.so")
+
+SYMMETRIC, ASYMMETRIC = 0, 1
+ROUND_HALF_EVEN, ROUND_HALF_AWAY = 0, 1
+
+ERR_NAMES = {
+    0: "Ok", 1: "EmptyInput", 2: "GroupSizeMismatch", 3: "InvalidScale", 4: "DimensionMismatch",
+    5: "NonFiniteFp8", 6: "InvalidBitWidth", 8: "InvalidArgument",
+}
+
+
+class OracleError(Exception):
+    def __init__(self, code):
+        super().__init__(ERR_NAMES.get(code, str(code)))
+        self.code = code
+        self.name = ERR_NAMES.get(code, str(code))
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle shared object with gcc if it is missing or stale."""
+    src = os.path.join(_HERE, "oxq_oracle.c")
+    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "-B", "liboxq_oracle.so"])
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        _lib = C.CDLL(_LIB_PATH)
+        _lib.orc_spec_absmax_f32.restype = C.c_float
+        _lib.orc_spec_absmax_bf16.restype = C.c_float
+        _lib.orc_spec_fp8_scale.restype = C.c_float
+        _lib.orc_spec_fp8_scale.argtypes = [C.c_float]
+        _lib.orc_spec_nvfp4_global_scale.restype = C.c_float
+        _lib.orc_spec_nvfp4_global_scale.argtypes = [C.c_float]
+        _lib.orc_e4m3_to_f32.restype = C.c_float
+        _lib.orc_e2m1_to_f32.restype = C.c_float
+        _lib.orc_f16_to_f32.restype = C.c_float
+        _lib.orc_bf16_to_f32.restype = C.c_float
+        _lib.orc_e4m3_rne_sat.argtypes = [C.c_float]
+        _lib.orc_e2m1_rne_sat.argtypes = [C.c_float]
+        _lib.orc_ref_e2m1_quantize_one.argtypes = [C.c_float]
+        _lib.orc_f32_to_f16.argtypes = [C.c_float]
+        _lib.orc_f32_to_bf16.argtypes = [C.c_float]
+    return _lib
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+def _sz(n):
+    return C.c_size_t(int(n))
+
+
+# --------------------------------------------------------------------------- inputs
+
+def gaussian(shape, sigma: float, seed: int) -> np.ndarray:
+    """Seeded synthetic tensor: Philox(seed) standard normal f32 times sigma (the benchmark inputs)."""
+    g = np.random.Generator(np.random.Philox(seed))
+    return (g.standard_normal(shape, dtype=np.float32) * np.float32(sigma)).astype(np.float32)
+
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even f32 -> bf16, returned as uint16 bit patterns."""
+    u = _c(x, np.float32).view(np.uint32)
+    nan = (u & 0x7F800000) == 0x7F800000
+    nan &= (u & 0x007FFFFF) != 0
+    r = ((u + (0x7FFF + ((u >> 16) & 1))) >> 16).astype(np.uint16)
+    r[nan] = ((u[nan] >> 16) | 0x40).astype(np.uint16)
+    return r
+
+
+def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    return (_c(b, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f16_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    return _c(b, np.uint16).view(np.float16).astype(np.float32)
+
+
+# --------------------------------------------------------------------------- MinMax (reference)
+
+def ref_minmax_calibrate(x, bits=8, scheme=SYMMETRIC, group=0):
+    x = _c(x, np.float32).ravel()
+    ng = 1 if group == 0 else max(x.size // max(group, 1), 1)
+    scales = np.zeros(ng, np.float32)
+    zps = np.zeros(ng, np.int32)
+    rc = lib().orc_ref_minmax_calibrate(_p(x), _sz(x.size), bits, scheme, _sz(group), _p(scales), _p(zps))
+    if rc:
+        raise OracleError(rc)
+    return scales, zps
+
+
+def ref_minmax_calibrate_2d(x, rows, cols, bits=8, scheme=SYMMETRIC):
+    x = _c(x, np.float32).ravel()
+    scales = np.zeros(max(rows, 1), np.float32)
+    zps = np.zeros(max(rows, 1), np.int32)
+    rc = lib().orc_ref_minmax_calibrate_2d(_p(x), _sz(rows), _sz(cols), bits, scheme, _p(scales), _p(zps))
+    if rc:
+        raise OracleError(rc)
+    return scales, zps
+
+
+def minmax_quantize_grouped(x, scales, zps, group, bits=8, scheme=SYMMETRIC, rounding=ROUND_HALF_AWAY,
+                            clamp_sym_lo127=False):
+    """``rounding=ROUND_HALF_AWAY, clamp_sym_lo127=False`` is the reference; the other setting is spec mode."""
+    x = _c(x, np.float32).ravel()
+    out = np.zeros(x.size, np.int32)
+    rc = lib().orc_minmax_quantize_grouped(_p(x), _sz(x.size), _p(_c(scales, np.float32)), _p(_c(zps, np.int32)),
+                                           _sz(group), bits, scheme, rounding, int(clamp_sym_lo127), _p(out))
+    if rc:
+        raise OracleError(rc)
+    return out
+
+
+def ref_minmax_dequantize_grouped(codes, scales, zps, group):
+    codes = _c(codes, np.int32).ravel()
+    out = np.zeros(codes.size, np.float32)
+    lib().orc_ref_minmax_dequantize_grouped(_p(codes), _sz(codes.size), _p(_c(scales, np.float32)),
+                                            _p(_c(zps, np.int32)), _sz(group), _p(out))
+    return out
+
+
+# --------------------------------------------------------------------------- FP8 codec
+
+def ref_fp8_encode(x, e5m2=False):
+    x = _c(x, np.float32).ravel()
+    out = np.zeros(x.size, np.uint8)
+    rc = lib().orc_ref_fp8_encode(_p(x), _sz(x.size), int(e5m2), _p(out))
+    if rc:
+        raise OracleError(rc)
+    return out
+
+
+def ref_fp8_decode(b, e5m2=False):
+    b = _c(b, np.uint8).ravel()
+    out = np.zeros(b.size, np.float32)
+    lib().orc_ref_fp8_decode(_p(b), _sz(b.size), int(e5m2), _p(out))
+    return out
+
+
+def e4m3_rne_sat(x):
+    x = _c(x, np.float32).ravel()
+    return np.array([lib().orc_e4m3_rne_sat(float(v)) & 0xFF for v in x], np.uint8)
+
+
+def e4m3_to_f32(b):
+    b = _c(b, np.uint8)
+    lut = np.array([lib().orc_e4m3_to_f32(C.c_uint8(i)) for i in range(256)], np.float32)
+    return lut[b]
+
+
+def e2m1_to_f32(nib):
+    lut = np.array([lib().orc_e2m1_to_f32(C.c_uint8(i)) for i in range(16)], np.float32)
+    return lut[_c(nib, np.uint8) & 0xF]
+
+
+def e2m1_rne_sat(x):
+    x = _c(x, np.float32).ravel()
+    return np.array([lib().orc_e2m1_rne_sat(float(v)) & 0xFF for v in x], np.uint8)
+
+
+def ref_e2m1_quantize_one(v: float) -> int:
+    return lib().orc_ref_e2m1_quantize_one(float(v)) & 0xFF
+
+
+# --------------------------------------------------------------------------- packing
+
+def ref_pack_int4(v):
+    v = _c(v, np.int8).ravel()
+    out = np.zeros(max(v.size // 8, 0), np.uint32)
+    rc = lib().orc_ref_pack_int4(_p(v), _sz(v.size), _p(out))
+    if rc:
+        raise OracleError(rc)
+    return out
+
+
+def ref_unpack_int4(words):
+    w = _c(words, np.uint32).ravel()
+    out = np.zeros(w.size * 8, np.int8)
+    lib().orc_ref_unpack_int4(_p(w), _sz(w.size), _p(out))
+    return out
+
+
+def pack_uint4(v):
+    v = _c(v, np.uint8).ravel()
+    out = np.zeros(v.size // 8, np.uint32)
+    lib().orc_pack_uint4(_p(v), _sz(v.size), _p(out))
+    return out
+
+
+def unpack_uint4(words):
+    w = _c(words, np.uint32).ravel()
+    out = np.zeros(w.size * 8, np.uint8)
+    lib().orc_unpack_uint4(_p(w), _sz(w.size), _p(out))
+    return out
+
+
+# --------------------------------------------------------------------------- micro-scaling (reference)
+
+def ref_microscale_fp4(x, block=32):
+    x = _c(x, np.float32).ravel()
+    packed = np.zeros((x.size + 1) // 2, np.uint8)
+    scales = np.zeros((x.size + block - 1) // block, np.float32)
+    rc = lib().orc_ref_microscale_fp4(_p(x), _sz(x.size), _sz(block), _p(packed), _p(scales))
+    if rc:
+        raise OracleError(rc)
+    return packed, scales
+
+
+def ref_microscale_fp4_dequant(packed, scales, n, block=32):
+    out = np.zeros(n, np.float32)
+    lib().orc_ref_microscale_fp4_dequant(_p(_c(packed, np.uint8)), _p(_c(scales, np.float32)), _sz(n), _sz(block),
+                                         _p(out))
+    return out
+
+
+# --------------------------------------------------------------------------- spec quantizers
+
+def spec_int8_quant_rows(x, rounding=ROUND_HALF_EVEN):
+    x = _c(x, np.float32)
+    rows, cols = x.shape
+    q = np.zeros((rows, cols), np.int8)
+    s = np.zeros(rows, np.float32)
+    lib().orc_spec_int8_quant_rows(_p(x), _sz(rows), _sz(cols), rounding, _p(q), _p(s))
+    return q, s
+
+
+def spec_int8_dequant_rows(q, scales):
+    q = _c(q, np.int8)
+    rows, cols = q.shape
+    y = np.zeros((rows, cols), np.float32)
+    lib().orc_spec_int8_dequant_rows(_p(q), _p(_c(scales, np.float32)), _sz(rows), _sz(cols), _p(y))
+    return y
+
+
+def spec_absmax(x) -> float:
+    if x.dtype == np.uint16:
+        x = _c(x, np.uint16)
+        return float(lib().orc_spec_absmax_bf16(_p(x), _sz(x.size)))
+    x = _c(x, np.float32)
+    return float(lib().orc_spec_absmax_f32(_p(x), _sz(x.size)))
+
+
+def spec_fp8_scale(absmax: float) -> np.float32:
+    return np.float32(lib().orc_spec_fp8_scale(C.c_float(absmax)))
+
+
+def spec_fp8_quant(x, scale):
+    """x: f32 array, or uint16 array holding bf16 bit patterns."""
+    out = np.zeros(x.shape, np.uint8)
+    if x.dtype == np.uint16:
+        x = _c(x, np.uint16)
+        lib().orc_spec_fp8_quant_bf16(_p(x), _sz(x.size), C.c_float(scale), _p(out))
+    else:
+        x = _c(x, np.float32)
+        lib().orc_spec_fp8_quant_f32(_p(x), _sz(x.size), C.c_float(scale), _p(out))
+    return out
+
+
+def spec_fp8_dequant(q, scale):
+    q = _c(q, np.uint8)
+    out = np.zeros(q.shape, np.float32)
+    lib().orc_spec_fp8_dequant(_p(q), _sz(q.size), C.c_float(scale), _p(out))
+    return out
+
+
+def spec_int4g_quant(x, group=128, rounding=ROUND_HALF_AWAY):
+    x = _c(x, np.float32)
+    rows, k = x.shape
+    ng = rows * (k // group)
+    codes = np.zeros((rows, k // 8), np.uint32)
+    scales = np.zeros((rows, k // group), np.uint16)
+    zeros = np.zeros((ng + 7) // 8, np.uint32)
+    lib().orc_spec_int4g_quant(_p(x), _sz(rows), _sz(k), _sz(group), rounding, _p(codes), _p(scales), _p(zeros))
+    return codes, scales, zeros
+
+
+def spec_int4g_dequant(codes, scales_f16, zeros, rows, k, group=128):
+    out = np.zeros((rows, k), np.float32)
+    lib().orc_spec_int4g_dequant(_p(_c(codes, np.uint32)), _p(_c(scales_f16, np.uint16)), _p(_c(zeros, np.uint32)),
+                                 _sz(rows), _sz(k), _sz(group), _p(out))
+    return out
+
+
+def spec_mxfp8_quant(x):
+    x = _c(x, np.float32)
+    rows, k = x.shape
+    codes = np.zeros((rows, k), np.uint8)
+    sf = np.zeros((rows, k // 32), np.uint8)
+    lib().orc_spec_mxfp8_quant(_p(x), _sz(rows), _sz(k), _p(codes), _p(sf))
+    return codes, sf
+
+
+def spec_mxfp8_dequant(codes, sf):
+    codes = _c(codes, np.uint8)
+    rows, k = codes.shape
+    out = np.zeros((rows, k), np.float32)
+    lib().orc_spec_mxfp8_dequant(_p(codes), _p(_c(sf, np.uint8)), _sz(rows), _sz(k), _p(out))
+    return out
+
+
+def spec_nvfp4_global_scale(absmax: float) -> np.float32:
+    return np.float32(lib().orc_spec_nvfp4_global_scale(C.c_float(absmax)))
+
+
+def spec_nvfp4_quant(x, g):
+    x = _c(x, np.float32)
+    rows, k = x.shape
+    packed = np.zeros((rows, k // 2), np.uint8)
+    sf = np.zeros((rows, k // 16), np.uint8)
+    lib().orc_spec_nvfp4_quant(_p(x), _sz(rows), _sz(k), C.c_float(g), _p(packed), _p(sf))
+    return packed, sf
+
+
+def spec_nvfp4_dequant(packed, sf, g, rows, k):
+    out = np.zeros((rows, k), np.float32)
+    lib().orc_spec_nvfp4_dequant(_p(_c(packed, np.uint8)), _p(_c(sf, np.uint8)), C.c_float(g), _sz(rows), _sz(k),
+                                 _p(out))
+    return out
+
+
+# --------------------------------------------------------------------------- GEMM / MLP
+
+def ref_linear_f32(x, w, bias=None, threads=1):
+    """Y = X W^T (+bias) with the reference's left-to-right f32 accumulation."""
+    x = _c(x, np.float32)
+    w = _c(w, np.float32)
+    batch, in_f = x.shape
+    out_f = w.shape[0]
+    y = np.zeros((batch, out_f), np.float32)
+    b = _p(_c(bias, np.float32)) if bias is not None else None
+    lib().orc_ref_linear_f32(_p(x), _p(w), b, _sz(batch), _sz(in_f), _sz(out_f), _p(y), int(threads))
+    return y
+
+
+def ref_silu_mul(gate, up):
+    gate = _c(gate, np.float32)
+    up = _c(up, np.float32)
+    h = np.zeros(gate.shape, np.float32)
+    lib().orc_ref_silu_mul(_p(gate), _p(up), _sz(gate.size), _p(h))
+    return h
+
+
+def ref_all_reduce_sum(partials):
+    p = _c(np.stack(partials), np.float32)
+    out = np.zeros(p.shape[1:], np.float32)
+    lib().orc_ref_all_reduce_sum(_p(p), _sz(p.shape[0]), _sz(out.size), _p(out))
+    return out
+
+
+def ref_swiglu_mlp(x, w_gate, w_up, w_down, threads=1):
+    """SwiGluFfn::forward (crates/oxicuda-lm/src/layer/ffn.rs:235-254)."""
+    gate = ref_linear_f32(x, w_gate, threads=threads)
+    up = ref_linear_f32(x, w_up, threads=threads)
+    return ref_linear_f32(ref_silu_mul(gate, up), w_down, threads=threads)
+
+
+def ref_tp_swiglu_mlp(x, w_gate, w_up, w_down, tp, threads=1):
+    """Column-parallel gate/up, row-parallel down, rank-order sum
+    (crates/oxicuda-dist-infer/src/tensor_parallel/{column,row}_parallel.rs)."""
+    inter = w_gate.shape[0]
+    sh = inter // tp
+    parts = []
+    for r in range(tp):
+        g = ref_linear_f32(x, w_gate[r * sh:(r + 1) * sh], threads=threads)
+        u = ref_linear_f32(x, w_up[r * sh:(r + 1) * sh], threads=threads)
+        parts.append(ref_linear_f32(ref_silu_mul(g, u), np.ascontiguousarray(w_down[:, r * sh:(r + 1) * sh]),
+                                    threads=threads))
+    return ref_all_reduce_sum(parts)
+
+
+def max_threads() -> int:
+    return int(lib().orc_max_threads())

@@ -1,0 +1,634 @@
+/*
+ * oxq_oracle.c -- CPU restatement of the OxiCUDA quantized-inference path.
+ *
+ * THIS IS TEST INFRASTRUCTURE, NOT PRODUCT CODE.  It is the checker that the
+ * parity tests, the smoke run and the CPU-baseline leg of the benchmark compare
+ * the CUDA library against.  Nothing in the shipped library or its host layer
+ * calls into this file.
+ *
+ * Two families of functions live here:
+ *
+ *   orc_ref_*   literal restatements of the reference's scalar CPU arithmetic
+ *               ("refcompat").  Each cites the reference file:line it follows.
+ *               They are pinned by the reference's own known-answer tests.
+ *
+ *   orc_spec_*  the arithmetic the benchmark configurations describe where the
+ *               reference has no implementation at all (per-tensor FP8 scaling
+ *               of bf16 tensors with RNE/satfinite conversion, uint4 g128 with
+ *               f16 scales, MXFP8 with E8M0 scales, NVFP4 with E4M3 block
+ *               scales and an f32 tensor scale).  PARITY UNPINNED: no reference
+ *               code or vector exists for them; they follow the public format
+ *               definitions (OCP Microscaling v1.0, the NVFP4 recipe) and the
+ *               exact formulas stated beside each function.
+ *
+ * Build: gcc -O2 -ffp-contract=off -fno-fast-math -fopenmp -shared -fPIC
+ * (see the Makefile in this directory).  -ffp-contract=off matters: a fused
+ * multiply-add would change x/scale+zp rounding.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stddef.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define ORC_OK 0
+#define ORC_ERR_EMPTY_INPUT 1
+#define ORC_ERR_GROUP_SIZE_MISMATCH 2
+#define ORC_ERR_INVALID_SCALE 3
+#define ORC_ERR_DIMENSION_MISMATCH 4
+#define ORC_ERR_NON_FINITE_FP8 5
+#define ORC_ERR_INVALID_BITS 6
+#define ORC_ERR_INVALID_ARGUMENT 8
+
+#define ORC_SYMMETRIC 0
+#define ORC_ASYMMETRIC 1
+#define ORC_ROUND_HALF_EVEN 0
+#define ORC_ROUND_HALF_AWAY 1
+
+static inline float bits_f32(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+static inline uint32_t f32_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+
+static inline float clampf(float v, float lo, float hi) {
+    /* Rust f32::clamp: NaN stays NaN */
+    if (v < lo) return lo;
+    if (v > hi) return hi;
+    return v;
+}
+
+static inline float round_mode(float v, int rounding) {
+    /* Rust f32::round == roundf (half away from zero); spec mode == rintf (half to even). */
+    return rounding == ORC_ROUND_HALF_AWAY ? roundf(v) : rintf(v);
+}
+
+/* Rust `as i32` on a float: NaN -> 0, saturating otherwise. */
+static inline int32_t f32_as_i32(float v) {
+    if (v != v) return 0;
+    if (v >= 2147483648.0f) return INT32_MAX;
+    if (v <= -2147483648.0f) return INT32_MIN;
+    return (int32_t)v;
+}
+
+/* ------------------------------------------------------------------------- */
+/* bf16 / f16 helpers                                                         */
+/* ------------------------------------------------------------------------- */
+
+uint16_t orc_f32_to_bf16(float f) {
+    uint32_t u = f32_bits(f);
+    if ((u & 0x7F800000u) == 0x7F800000u && (u & 0x007FFFFFu)) return (uint16_t)((u >> 16) | 0x0040u);
+    uint32_t lsb = (u >> 16) & 1u;
+    u += 0x7FFFu + lsb;
+    return (uint16_t)(u >> 16);
+}
+float orc_bf16_to_f32(uint16_t h) { return bits_f32(((uint32_t)h) << 16); }
+
+/* IEEE binary16 <- f32, round to nearest even, overflow to Inf. */
+uint16_t orc_f32_to_f16(float f) {
+    uint32_t x = f32_bits(f);
+    uint32_t sign = (x >> 16) & 0x8000u;
+    uint32_t ax = x & 0x7FFFFFFFu;
+    if (ax >= 0x7F800000u) return (uint16_t)(sign | (ax > 0x7F800000u ? 0x7E00u : 0x7C00u));
+    if (ax >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u);          /* rounds to >= 65520 -> Inf */
+    if (ax < 0x33000001u) return (uint16_t)sign;                        /* <= 2^-25 -> 0 (tie at 2^-25 to even = 0) */
+    int e = (int)(ax >> 23) - 127;
+    uint32_t man = (ax & 0x007FFFFFu) | 0x00800000u;
+    if (e < -14) {                                                      /* subnormal half */
+        int shift = 13 + (-14 - e);                                     /* drop bits */
+        uint32_t q = man >> shift;
+        uint32_t rem = man & ((1u << shift) - 1u);
+        uint32_t half = 1u << (shift - 1);
+        if (rem > half || (rem == half && (q & 1u))) q++;
+        return (uint16_t)(sign | q);
+    }
+    uint32_t q = ((uint32_t)(e + 15) << 10) | ((man >> 13) & 0x3FFu);
+    uint32_t rem = man & 0x1FFFu;
+    if (rem > 0x1000u || (rem == 0x1000u && (q & 1u))) q++;
+    return (uint16_t)(sign | q);
+}
+float orc_f16_to_f32(uint16_t h) {
+    uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+    uint32_t e = (h >> 10) & 0x1Fu, m = h & 0x3FFu;
+    if (e == 0) {
+        if (m == 0) return bits_f32(sign);
+        float v = (float)m * 5.9604644775390625e-08f; /* m * 2^-24 */
+        return sign ? -v : v;
+    }
+    if (e == 31) return bits_f32(sign | 0x7F800000u | (m << 13));
+    return bits_f32(sign | ((e + 112u) << 23) | (m << 13));
+}
+
+/* ------------------------------------------------------------------------- */
+/* A.1  MinMaxQuantizer  (crates/oxicuda-quant/src/scheme/minmax.rs)          */
+/* ------------------------------------------------------------------------- */
+
+/* calibrate_slice, minmax.rs:209-243 */
+int orc_ref_minmax_calibrate_slice(const float* x, size_t n, int bits, int scheme,
+                                   float* scale_out, int32_t* zp_out) {
+    if (bits < 1 || bits > 16) return ORC_ERR_INVALID_BITS;      /* new() panics, minmax.rs:99-100 */
+    float fmin = INFINITY, fmax = -INFINITY;
+    for (size_t i = 0; i < n; i++) {
+        float v = x[i];
+        if (v < fmin) fmin = v;
+        if (v > fmax) fmax = v;
+    }
+    float scale; int32_t zp;
+    if (scheme == ORC_SYMMETRIC) {
+        float q_max = (float)(1 << (bits - 1)) - 1.0f;
+        float abs_max = fmaxf(fmaxf(fabsf(fmin), fabsf(fmax)), 1e-8f);
+        scale = abs_max / q_max;
+        zp = 0;
+    } else {
+        float q_range = (float)((1 << bits) - 1);
+        float range = fmaxf(fmax - fmin, 1e-8f);
+        scale = range / q_range;
+        zp = f32_as_i32(clampf(roundf(-fmin / scale), 0.0f, q_range));
+    }
+    *scale_out = scale; *zp_out = zp;
+    if (!isfinite(scale) || scale <= 0.0f) return ORC_ERR_INVALID_SCALE;
+    return ORC_OK;
+}
+
+/* calibrate with PerGroup granularity, minmax.rs:134-172; group==0 means PerTensor. */
+int orc_ref_minmax_calibrate(const float* x, size_t n, int bits, int scheme, size_t group,
+                             float* scales, int32_t* zps) {
+    if (n == 0) return ORC_ERR_EMPTY_INPUT;
+    if (group == 0) return orc_ref_minmax_calibrate_slice(x, n, bits, scheme, scales, zps);
+    if (n % group != 0) return ORC_ERR_GROUP_SIZE_MISMATCH;
+    for (size_t g = 0; g < n / group; g++) {
+        int rc = orc_ref_minmax_calibrate_slice(x + g * group, group, bits, scheme, scales + g, zps + g);
+        if (rc) return rc;
+    }
+    return ORC_OK;
+}
+
+/* calibrate_2d, minmax.rs:179-207 */
+int orc_ref_minmax_calibrate_2d(const float* x, size_t rows, size_t cols, int bits, int scheme,
+                                float* scales, int32_t* zps) {
+    if (rows == 0) return ORC_ERR_EMPTY_INPUT;
+    if (cols == 0) return ORC_ERR_DIMENSION_MISMATCH;
+    for (size_t r = 0; r < rows; r++) {
+        int rc = orc_ref_minmax_calibrate_slice(x + r * cols, cols, bits, scheme, scales + r, zps + r);
+        if (rc) return rc;
+    }
+    return ORC_OK;
+}
+
+/* quantize_grouped, minmax.rs:275-299 (quantize :252-268 is the group == n case with one scale).
+ * `rounding` = HALF_AWAY and clamp_sym_lo127 = 0 reproduce the reference exactly;
+ * HALF_EVEN with clamp_sym_lo127 = 1 is the benchmark-configuration ("spec") variant. */
+int orc_minmax_quantize_grouped(const float* x, size_t n, const float* scales, const int32_t* zps,
+                                size_t group, int bits, int scheme, int rounding, int clamp_sym_lo127,
+                                int32_t* out) {
+    if (group == 0 || n % group != 0) return ORC_ERR_GROUP_SIZE_MISMATCH;
+    float q_max = scheme == ORC_SYMMETRIC ? (float)(1 << (bits - 1)) - 1.0f : (float)(1 << bits) - 1.0f;
+    float q_min = scheme == ORC_SYMMETRIC ? -(float)(1 << (bits - 1)) : 0.0f;
+    if (scheme == ORC_SYMMETRIC && clamp_sym_lo127) q_min = -q_max;
+    for (size_t g = 0; g < n / group; g++) {
+        float scale = scales[g];
+        float zp = (float)zps[g];
+        for (size_t i = 0; i < group; i++) {
+            float v = x[g * group + i] / scale + zp;
+            out[g * group + i] = f32_as_i32(clampf(round_mode(v, rounding), q_min, q_max));
+        }
+    }
+    return ORC_OK;
+}
+
+/* dequantize_grouped, minmax.rs:309-324 */
+void orc_ref_minmax_dequantize_grouped(const int32_t* codes, size_t n, const float* scales,
+                                       const int32_t* zps, size_t group, float* out) {
+    for (size_t g = 0; g < n / group; g++)
+        for (size_t i = 0; i < group; i++)
+            out[g * group + i] = (float)(codes[g * group + i] - zps[g]) * scales[g];
+}
+
+/* ------------------------------------------------------------------------- */
+/* A.2  Fp8Codec (crates/oxicuda-quant/src/scheme/fp8.rs)                      */
+/* ------------------------------------------------------------------------- */
+
+static void fp8_params(int e5m2, int* exp_bits, int* man_bits, int* bias, float* maxv) {
+    if (e5m2) { *exp_bits = 5; *man_bits = 2; *bias = 15; *maxv = 57344.0f; }
+    else      { *exp_bits = 4; *man_bits = 3; *bias = 7;  *maxv = 448.0f; }
+}
+
+/* fp32_to_fp8, fp8.rs:163-208 (truncating, with the reference's subnormal shift). */
+static uint8_t ref_fp32_to_fp8(float v, int e5m2) {
+    int exp_bits, man_bits, bias8; float maxv;
+    fp8_params(e5m2, &exp_bits, &man_bits, &bias8, &maxv);
+    uint32_t bits = f32_bits(v);
+    uint8_t sign = (uint8_t)(bits >> 31);
+    int exp32 = (int)((bits >> 23) & 0xFF);
+    uint32_t man32 = bits & 0x007FFFFFu;
+    if (v == 0.0f) return (uint8_t)(sign << 7);
+    int exp8_raw = exp32 - 127 + bias8;
+    int man_shift = 23 - man_bits;
+    if (exp8_raw <= 0) {
+        uint32_t full_man = (man32 | 0x00800000u) >> 1;
+        uint32_t shift = (uint32_t)(1 - exp8_raw) + (uint32_t)man_shift;
+        if (shift >= 24) return (uint8_t)(sign << 7);
+        uint8_t man8 = (uint8_t)(full_man >> shift) & (uint8_t)((1 << man_bits) - 1);
+        return (uint8_t)((sign << 7) | man8);
+    }
+    int max_exp = (1 << exp_bits) - 1;
+    if (exp8_raw >= max_exp) return (uint8_t)((sign << 7) | (e5m2 ? 0x7B : 0x7E));
+    uint8_t man8 = (uint8_t)(man32 >> man_shift) & (uint8_t)((1 << man_bits) - 1);
+    return (uint8_t)((sign << 7) | ((uint8_t)exp8_raw << man_bits) | man8);
+}
+
+/* encode_f32, fp8.rs:115-122 */
+int orc_ref_fp8_encode(const float* x, size_t n, int e5m2, uint8_t* out) {
+    int eb, mb, b; float maxv;
+    fp8_params(e5m2, &eb, &mb, &b, &maxv);
+    for (size_t i = 0; i < n; i++) {
+        if (!isfinite(x[i])) return ORC_ERR_NON_FINITE_FP8;
+        out[i] = ref_fp32_to_fp8(clampf(x[i], -maxv, maxv), e5m2);
+    }
+    return ORC_OK;
+}
+
+/* fp8_to_fp32, fp8.rs:210-261.  `leading` is always 0 there because leading_zeros()
+ * is taken on a 32-bit value, so subnormals decode as 2^(1-bias) * (1 + m/2^man_bits). */
+void orc_ref_fp8_decode(const uint8_t* in, size_t n, int e5m2, float* out) {
+    int exp_bits, man_bits, bias8; float maxv;
+    fp8_params(e5m2, &exp_bits, &man_bits, &bias8, &maxv);
+    for (size_t i = 0; i < n; i++) {
+        uint8_t b = in[i];
+        uint32_t sign = b >> 7;
+        uint32_t exp8 = (b >> man_bits) & ((1u << exp_bits) - 1u);
+        uint32_t man8 = b & ((1u << man_bits) - 1u);
+        uint32_t all_exp = (1u << exp_bits) - 1u;
+        if (!e5m2) {
+            if (exp8 == all_exp && man8 == (1u << man_bits) - 1u) { out[i] = NAN; continue; }
+        } else if (exp8 == all_exp) {
+            out[i] = man8 == 0 ? (sign ? -INFINITY : INFINITY) : NAN; continue;
+        }
+        int man_shift = 23 - man_bits;
+        if (exp8 == 0) {
+            if (man8 == 0) { out[i] = bits_f32(sign << 31); continue; }
+            uint32_t exp32 = (uint32_t)(127 + 1 - bias8);
+            uint32_t man32 = (man8 & ((1u << man_bits) - 1u)) << man_shift;
+            out[i] = bits_f32((sign << 31) | (exp32 << 23) | man32); continue;
+        }
+        uint32_t exp32 = (uint32_t)((int)exp8 - bias8 + 127);
+        out[i] = bits_f32((sign << 31) | (exp32 << 23) | (man8 << man_shift));
+    }
+}
+
+/* IEEE-style conversions (what the hardware cvt.rn.satfinite.e4m3x2.f32 does): round to nearest
+ * even, saturate finite overflow and +-Inf to +-448 (0x7E), NaN -> 0x7F.  Used by every orc_spec_*. */
+uint8_t orc_e4m3_rne_sat(float v) {
+    uint32_t u = f32_bits(v);
+    uint8_t sign = (uint8_t)((u >> 24) & 0x80u);
+    uint32_t au = u & 0x7FFFFFFFu;
+    if (au > 0x7F800000u) return 0x7F;                      /* NaN (sign dropped by the hardware conversion) */
+    float a = bits_f32(au);
+    if (a >= 464.0f) return (uint8_t)(sign | 0x7E);         /* > max + half ulp(=16)... ties at 464 go to even=512 -> sat */
+    if (a > 448.0f) return (uint8_t)(sign | 0x7E);
+    /* scale so that one E4M3 step == 1.0, then rintf (RNE).  Subnormal step is 2^-9. */
+    int e = (int)(au >> 23) - 127;
+    if (e < -6) e = -6;
+    float step = bits_f32((uint32_t)(e - 3 + 127) << 23);   /* 2^(e-3) */
+    float q = rintf(a / step);                              /* exact division by a power of two */
+    float r = q * step;
+    if (r > 448.0f) r = 448.0f;
+    if (r == 0.0f) return sign;
+    uint32_t ru = f32_bits(r);
+    int re = (int)(ru >> 23) - 127;
+    if (re < -6) {                                          /* subnormal: m * 2^-9 */
+        return (uint8_t)(sign | (uint8_t)(r * 512.0f));
+    }
+    return (uint8_t)(sign | ((uint32_t)(re + 7) << 3) | ((ru >> 20) & 7u));
+}
+float orc_e4m3_to_f32(uint8_t b) {
+    uint32_t sign = b >> 7, e = (b >> 3) & 0xF, m = b & 7;
+    float v;
+    if (e == 15 && m == 7) return NAN;
+    if (e == 0) v = (float)m * 0.001953125f;               /* m * 2^-9 */
+    else v = bits_f32(((e + 120u) << 23) | (m << 20));
+    return sign ? -v : v;
+}
+
+/* ------------------------------------------------------------------------- */
+/* A.3  nibble packing (crates/oxicuda-blas/src/precision/int_ops.rs:375-428)  */
+/* ------------------------------------------------------------------------- */
+
+int orc_ref_pack_int4(const int8_t* v, size_t n, uint32_t* out) {
+    if (n % 8 != 0) return ORC_ERR_INVALID_ARGUMENT;
+    for (size_t i = 0; i < n; i++) if (v[i] < -8 || v[i] > 7) return ORC_ERR_INVALID_ARGUMENT;
+    for (size_t w = 0; w < n / 8; w++) {
+        uint32_t p = 0;
+        for (int j = 0; j < 8; j++) p |= ((uint32_t)((uint8_t)v[w * 8 + j] & 0x0F)) << (j * 4);
+        out[w] = p;
+    }
+    return ORC_OK;
+}
+void orc_ref_unpack_int4(const uint32_t* in, size_t words, int8_t* out) {
+    for (size_t w = 0; w < words; w++)
+        for (int j = 0; j < 8; j++) {
+            uint8_t nib = (uint8_t)((in[w] >> (j * 4)) & 0x0F);
+            out[w * 8 + j] = (nib & 0x08) ? (int8_t)(0xF0u | nib) : (int8_t)nib;
+        }
+}
+/* Unsigned variant: same bit positions, no sign extension (GPTQ/AWQ u32 packing,
+ * crates/oxicuda-dnn/src/quantize/gptq_awq.rs:936-945). */
+void orc_pack_uint4(const uint8_t* v, size_t n, uint32_t* out) {
+    for (size_t w = 0; w < n / 8; w++) {
+        uint32_t p = 0;
+        for (int j = 0; j < 8; j++) p |= ((uint32_t)(v[w * 8 + j] & 0x0F)) << (j * 4);
+        out[w] = p;
+    }
+}
+void orc_unpack_uint4(const uint32_t* in, size_t words, uint8_t* out) {
+    for (size_t w = 0; w < words; w++)
+        for (int j = 0; j < 8; j++) out[w * 8 + j] = (uint8_t)((in[w] >> (j * 4)) & 0x0F);
+}
+
+/* ------------------------------------------------------------------------- */
+/* A.4  E2M1 + micro-scaling (crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs) */
+/* ------------------------------------------------------------------------- */
+
+/* Fp4Quantizer::quantize_one(E2M1), fp4_fp6_ops.rs:645-661 */
+uint8_t orc_ref_e2m1_quantize_one(float value) {
+    if (value == 0.0f) return 0;
+    uint8_t sign = value < 0.0f ? 1 : 0;
+    float a = fminf(fabsf(value), 6.0f);
+    float l2 = log2f(a);
+    int eu = (int)floorf(l2);
+    int eb = eu + 1; if (eb < 0) eb = 0; if (eb > 3) eb = 3;
+    int ea = eb - 1;
+    float sig = a / powf(2.0f, (float)ea);
+    uint8_t m = (sig - 1.0f) >= 0.5f ? 1 : 0;
+    return (uint8_t)((sign << 3) | ((uint8_t)eb << 1) | m);
+}
+/* Fp4Quantizer::dequantize_one(E2M1), fp4_fp6_ops.rs:678-697 (also the IEEE E2M1 value). */
+float orc_e2m1_to_f32(uint8_t raw) {
+    uint8_t sign = (raw >> 3) & 1, e = (raw >> 1) & 3, m = raw & 1;
+    float v;
+    if (e == 0) v = (float)m * 0.5f;
+    else v = (1.0f + (float)m * 0.5f) * (float)(1 << (e - 1));
+    return sign ? -v : v;
+}
+/* MicroScalingQuantizer::compute_scales + quantize_fp4, fp4_fp6_ops.rs:763-782, :849-876.
+ * PackedFp4::pack(v0, v1) = v0 | v1 << 4, :465-472.  block in {32,64,128} (:202-214). */
+int orc_ref_microscale_fp4(const float* x, size_t n, size_t block, uint8_t* packed, float* scales) {
+    if (!(block == 32 || block == 64 || block == 128)) return ORC_ERR_INVALID_ARGUMENT;
+    size_t nb = (n + block - 1) / block;
+    for (size_t b = 0; b < nb; b++) {
+        size_t s = b * block, e = s + block < n ? s + block : n;
+        float mx = 0.0f;
+        for (size_t i = s; i < e; i++) mx = fmaxf(mx, fabsf(x[i]));
+        scales[b] = mx == 0.0f ? 1.0f : mx / 6.0f;
+    }
+    size_t npad = n + (n & 1);
+    for (size_t i = 0; i < npad; i += 2) {
+        float v0 = x[i] / scales[i / block];
+        float v1 = (i + 1 < n) ? x[i + 1] / scales[(i + 1) / block] : 0.0f;
+        packed[i / 2] = (uint8_t)(orc_ref_e2m1_quantize_one(v0) | (orc_ref_e2m1_quantize_one(v1) << 4));
+    }
+    return ORC_OK;
+}
+void orc_ref_microscale_fp4_dequant(const uint8_t* packed, const float* scales, size_t n, size_t block, float* out) {
+    for (size_t i = 0; i < n; i++) {
+        uint8_t nib = (i & 1) ? (packed[i / 2] >> 4) : (packed[i / 2] & 0x0F);
+        out[i] = orc_e2m1_to_f32(nib) * scales[i / block];
+    }
+}
+
+/* Round-to-nearest-even onto the E2M1 grid {0,.5,1,1.5,2,3,4,6} with saturation
+ * (the hardware cvt.rn.satfinite.e2m1x2.f32).  Sign is kept, so small negatives give 0x8. */
+uint8_t orc_e2m1_rne_sat(float v) {
+    uint8_t sign = (uint8_t)((f32_bits(v) >> 28) & 0x8u);
+    float a = fabsf(v);
+    uint8_t c;
+    if (a != a) return 0x7;                       /* NaN -> +max, as the conversion instruction does */
+    if (a <= 0.25f) c = 0;                        /* tie 0.25 -> code 0 (even) */
+    else if (a < 0.75f) c = 1;
+    else if (a <= 1.25f) c = 2;                   /* ties 0.75, 1.25 -> code 2 */
+    else if (a < 1.75f) c = 3;
+    else if (a <= 2.5f) c = 4;                    /* ties 1.75, 2.5 -> code 4 */
+    else if (a < 3.5f) c = 5;
+    else if (a <= 5.0f) c = 6;                    /* ties 3.5, 5.0 -> code 6 */
+    else c = 7;
+    return (uint8_t)(sign | c);
+}
+
+/* ------------------------------------------------------------------------- */
+/* spec quantizers (PARITY UNPINNED: defined here, see file header)            */
+/* ------------------------------------------------------------------------- */
+
+/* INT8 symmetric per-row, benchmark configuration 1:
+ * scale = max(absmax_row, 1e-8)/127 (same scale as minmax.rs:221-225); code = clamp(round(x/scale), -127, 127). */
+void orc_spec_int8_quant_rows(const float* x, size_t rows, size_t cols, int rounding, int8_t* q, float* scales) {
+#pragma omp parallel for schedule(static)
+    for (size_t r = 0; r < rows; r++) {
+        const float* p = x + r * cols;
+        float fmin = INFINITY, fmax = -INFINITY;
+        for (size_t i = 0; i < cols; i++) { float v = p[i]; if (v < fmin) fmin = v; if (v > fmax) fmax = v; }
+        float s = fmaxf(fmaxf(fabsf(fmin), fabsf(fmax)), 1e-8f) / 127.0f;
+        scales[r] = s;
+        for (size_t i = 0; i < cols; i++)
+            q[r * cols + i] = (int8_t)f32_as_i32(clampf(round_mode(p[i] / s, rounding), -127.0f, 127.0f));
+    }
+}
+void orc_spec_int8_dequant_rows(const int8_t* q, const float* scales, size_t rows, size_t cols, float* y) {
+#pragma omp parallel for schedule(static)
+    for (size_t r = 0; r < rows; r++)
+        for (size_t i = 0; i < cols; i++) y[r * cols + i] = (float)q[r * cols + i] * scales[r];
+}
+
+/* absmax over a tensor; NaNs are skipped exactly as fmaxf skips them. */
+float orc_spec_absmax_f32(const float* x, size_t n) {
+    float m = 0.0f;
+#pragma omp parallel for reduction(max : m) schedule(static)
+    for (size_t i = 0; i < n; i++) { float a = fabsf(x[i]); if (a > m) m = a; }
+    return m;
+}
+float orc_spec_absmax_bf16(const uint16_t* x, size_t n) {
+    float m = 0.0f;
+#pragma omp parallel for reduction(max : m) schedule(static)
+    for (size_t i = 0; i < n; i++) { float a = fabsf(orc_bf16_to_f32(x[i])); if (a > m) m = a; }
+    return m;
+}
+/* FP8 E4M3 per-tensor, benchmark configuration 2: scale = absmax/448 (1.0 if the tensor is all zero);
+ * code = e4m3_rne_sat(x / scale) with a true IEEE f32 divide. */
+float orc_spec_fp8_scale(float absmax) { return absmax > 0.0f ? absmax / 448.0f : 1.0f; }
+void orc_spec_fp8_quant_f32(const float* x, size_t n, float scale, uint8_t* out) {
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; i++) out[i] = orc_e4m3_rne_sat(x[i] / scale);
+}
+void orc_spec_fp8_quant_bf16(const uint16_t* x, size_t n, float scale, uint8_t* out) {
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; i++) out[i] = orc_e4m3_rne_sat(orc_bf16_to_f32(x[i]) / scale);
+}
+void orc_spec_fp8_dequant(const uint8_t* q, size_t n, float scale, float* out) {
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; i++) out[i] = orc_e4m3_to_f32(q[i]) * scale;
+}
+
+/* uint4 group-wise asymmetric with f16 scales, benchmark configuration 3.  Per group of `group`
+ * consecutive K elements of a row:  s32 = max(max-min, 1e-8)/15 (minmax.rs:226-232);
+ * s = f16_rne(s32), bumped to the smallest f16 subnormal if it rounds to zero;
+ * zp = clamp(round_half_away(-min / f32(s)), 0, 15); q = clamp(round(x / f32(s) + zp), 0, 15).
+ * Codes and zero-points are packed 8 per u32, element j at bits [4j, 4j+4). */
+void orc_spec_int4g_quant(const float* x, size_t rows, size_t k, size_t group, int rounding,
+                          uint32_t* codes, uint16_t* scales_f16, uint32_t* zeros_packed) {
+    size_t gpr = k / group;
+    size_t ngroups = rows * gpr;
+    memset(zeros_packed, 0, ((ngroups + 7) / 8) * 4);
+#pragma omp parallel for schedule(static)
+    for (size_t r = 0; r < rows; r++) {
+        for (size_t g = 0; g < gpr; g++) {
+            const float* p = x + r * k + g * group;
+            float fmin = INFINITY, fmax = -INFINITY;
+            for (size_t i = 0; i < group; i++) { float v = p[i]; if (v < fmin) fmin = v; if (v > fmax) fmax = v; }
+            float s32 = fmaxf(fmax - fmin, 1e-8f) / 15.0f;
+            uint16_t sh = orc_f32_to_f16(s32);
+            if ((sh & 0x7FFFu) == 0) sh = 1;
+            float s = orc_f16_to_f32(sh);
+            int32_t zp = f32_as_i32(clampf(roundf(-fmin / s), 0.0f, 15.0f));
+            size_t gi = r * gpr + g;
+            scales_f16[gi] = sh;
+#pragma omp atomic
+            zeros_packed[gi / 8] |= ((uint32_t)zp) << ((gi % 8) * 4);
+            for (size_t w = 0; w < group / 8; w++) {
+                uint32_t pk = 0;
+                for (int j = 0; j < 8; j++) {
+                    float v = p[w * 8 + j] / s + (float)zp;
+                    uint32_t qv = (uint32_t)f32_as_i32(clampf(round_mode(v, rounding), 0.0f, 15.0f));
+                    pk |= qv << (4 * j);
+                }
+                codes[(r * k + g * group) / 8 + w] = pk;
+            }
+        }
+    }
+}
+void orc_spec_int4g_dequant(const uint32_t* codes, const uint16_t* scales_f16, const uint32_t* zeros_packed,
+                            size_t rows, size_t k, size_t group, float* out) {
+    size_t gpr = k / group;
+#pragma omp parallel for schedule(static)
+    for (size_t r = 0; r < rows; r++)
+        for (size_t c = 0; c < k; c++) {
+            size_t gi = r * gpr + c / group;
+            int32_t zp = (int32_t)((zeros_packed[gi / 8] >> ((gi % 8) * 4)) & 0xF);
+            int32_t q = (int32_t)((codes[(r * k + c) / 8] >> ((c % 8) * 4)) & 0xF);
+            out[r * k + c] = (float)(q - zp) * orc_f16_to_f32(scales_f16[gi]);
+        }
+}
+
+/* MXFP8 (OCP Microscaling v1.0): E4M3 elements, one E8M0 scale per 32 consecutive K elements.
+ * e = floor(log2(absmax_blk)) - 8; scale byte = clamp(e + 127, 0, 254); all-zero block -> byte 0
+ * and codes 0; otherwise code = e4m3_rne_sat(x * 2^-(byte-127)).  0xFF (NaN) is never written. */
+static inline float pow2_of(int e) { /* exact 2^e for e in [-127, 127] */
+    if (e >= -126) return bits_f32((uint32_t)(e + 127) << 23);
+    return bits_f32(0x00400000u);     /* 2^-127, an f32 subnormal */
+}
+void orc_spec_mxfp8_quant(const float* x, size_t rows, size_t k, uint8_t* codes, uint8_t* sf) {
+    size_t bpr = k / 32;
+#pragma omp parallel for schedule(static)
+    for (size_t r = 0; r < rows; r++)
+        for (size_t b = 0; b < bpr; b++) {
+            const float* p = x + r * k + b * 32;
+            float mx = 0.0f;
+            for (int i = 0; i < 32; i++) { float a = fabsf(p[i]); if (a > mx) mx = a; }
+            uint8_t* c = codes + r * k + b * 32;
+            if (mx == 0.0f) { sf[r * bpr + b] = 0; for (int i = 0; i < 32; i++) c[i] = (uint8_t)((f32_bits(p[i]) >> 24) & 0x80u); continue; }
+            int e = ilogbf(mx) - 8;
+            int byte = e + 127; if (byte < 0) byte = 0; if (byte > 254) byte = 254;
+            sf[r * bpr + b] = (uint8_t)byte;
+            float inv = pow2_of(-(byte - 127));
+            for (int i = 0; i < 32; i++) c[i] = orc_e4m3_rne_sat(p[i] * inv);
+        }
+}
+void orc_spec_mxfp8_dequant(const uint8_t* codes, const uint8_t* sf, size_t rows, size_t k, float* out) {
+    size_t bpr = k / 32;
+#pragma omp parallel for schedule(static)
+    for (size_t r = 0; r < rows; r++)
+        for (size_t c = 0; c < k; c++)
+            out[r * k + c] = orc_e4m3_to_f32(codes[r * k + c]) * pow2_of((int)sf[r * bpr + c / 32] - 127);
+}
+
+/* NVFP4: E2M1 elements, one unsigned E4M3 scale per 16 consecutive K elements, one f32 scale per tensor.
+ * g = absmax_tensor / (448*6) (1.0 if the tensor is all zero); SF = e4m3_rne_sat(absmax_blk / (6*g));
+ * code = e2m1_rne_sat(x / (g * f32(SF))), all codes of a block are (signed) zero when SF == 0.
+ * Two codes per byte, even element in the low nibble. */
+float orc_spec_nvfp4_global_scale(float absmax) { return absmax > 0.0f ? absmax / (448.0f * 6.0f) : 1.0f; }
+void orc_spec_nvfp4_quant(const float* x, size_t rows, size_t k, float g, uint8_t* packed, uint8_t* sf) {
+    size_t bpr = k / 16;
+    float six_g = 6.0f * g;
+#pragma omp parallel for schedule(static)
+    for (size_t r = 0; r < rows; r++)
+        for (size_t b = 0; b < bpr; b++) {
+            const float* p = x + r * k + b * 16;
+            float mx = 0.0f;
+            for (int i = 0; i < 16; i++) { float a = fabsf(p[i]); if (a > mx) mx = a; }
+            uint8_t s8 = orc_e4m3_rne_sat(mx / six_g);
+            sf[r * bpr + b] = s8;
+            float d = g * orc_e4m3_to_f32(s8);
+            uint8_t* o = packed + (r * k + b * 16) / 2;
+            for (int i = 0; i < 16; i += 2) {
+                uint8_t c0, c1;
+                if (s8 == 0) { c0 = (uint8_t)((f32_bits(p[i]) >> 28) & 8u); c1 = (uint8_t)((f32_bits(p[i + 1]) >> 28) & 8u); }
+                else { c0 = orc_e2m1_rne_sat(p[i] / d); c1 = orc_e2m1_rne_sat(p[i + 1] / d); }
+                o[i / 2] = (uint8_t)(c0 | (c1 << 4));
+            }
+        }
+}
+void orc_spec_nvfp4_dequant(const uint8_t* packed, const uint8_t* sf, float g, size_t rows, size_t k, float* out) {
+    size_t bpr = k / 16;
+#pragma omp parallel for schedule(static)
+    for (size_t r = 0; r < rows; r++)
+        for (size_t c = 0; c < k; c++) {
+            size_t idx = r * k + c;
+            uint8_t nib = (idx & 1) ? (packed[idx / 2] >> 4) : (packed[idx / 2] & 0xF);
+            out[idx] = orc_e2m1_to_f32(nib) * orc_e4m3_to_f32(sf[r * bpr + c / 16]) * g;
+        }
+}
+
+/* ------------------------------------------------------------------------- */
+/* A.5  f32 GEMM / SwiGLU / tensor-parallel helpers                            */
+/* ------------------------------------------------------------------------- */
+
+/* Y[b,o] = bias[o] + sum_i X[b,i] * W[o,i], accumulated left to right in f32
+ * (crates/oxicuda-dist-infer/src/tensor_parallel/column_parallel.rs:77-95;
+ *  crates/oxicuda-lm/src/layer/ffn.rs:72-110 is the bias-free form).  `threads` <= 1 runs the
+ * reference's single-threaded loop; otherwise rows of W are split over OpenMP threads (the
+ * per-output summation order is unchanged, so results are identical). */
+void orc_ref_linear_f32(const float* x, const float* w, const float* bias, size_t batch, size_t in_f, size_t out_f,
+                        float* y, int threads) {
+#ifdef _OPENMP
+    int nt = threads <= 1 ? 1 : threads;
+#pragma omp parallel for schedule(static) num_threads(nt)
+#endif
+    for (size_t o = 0; o < out_f; o++) {
+        const float* wr = w + o * in_f;
+        for (size_t b = 0; b < batch; b++) {
+            float acc = bias ? bias[o] : 0.0f;
+            const float* xr = x + b * in_f;
+            for (size_t i = 0; i < in_f; i++) acc += xr[i] * wr[i];
+            y[b * out_f + o] = acc;
+        }
+    }
+}
+
+/* silu(x) = x / (1 + exp(-x)), crates/oxicuda-lm/src/layer/ffn.rs:25-27;
+ * h = silu(gate) * up, ffn.rs:245-249 */
+void orc_ref_silu_mul(const float* gate, const float* up, size_t n, float* h) {
+    for (size_t i = 0; i < n; i++) h[i] = (gate[i] / (1.0f + expf(-gate[i]))) * up[i];
+}
+
+/* RowLinear::all_reduce, crates/oxicuda-dist-infer/src/tensor_parallel/row_parallel.rs:202-223:
+ * elementwise sum of the rank partials in rank order.  partials = [ranks][len] contiguous. */
+void orc_ref_all_reduce_sum(const float* partials, size_t ranks, size_t len, float* out) {
+    memcpy(out, partials, len * sizeof(float));
+    for (size_t r = 1; r < ranks; r++)
+        for (size_t i = 0; i < len; i++) out[i] += partials[r * len + i];
+}
+
+int orc_max_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}

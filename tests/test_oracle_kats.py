@@ -1,0 +1,215 @@
+"""Pins the CPU oracle against the known-answer tests the reference carries for this path.
+
+Every case cites the reference test it restates (paths relative to the reference workspace).
+"""
+import math
+
+import numpy as np
+import pytest
+
+
+# ---- crates/oxicuda-quant/src/scheme/minmax.rs tests -------------------------------------------
+
+def test_symmetric_calibrate_scale(orc):  # minmax.rs:341-349
+    s, z = orc.ref_minmax_calibrate([-2.0, -1.0, 0.5, 2.0], 8, orc.SYMMETRIC)
+    assert abs(s[0] - 2.0 / 127.0) < 1e-6 and z[0] == 0
+    assert s[0] == np.float32(2.0) / np.float32(127.0)
+
+
+def test_asymmetric_calibrate_scale_zp(orc):  # minmax.rs:351-360
+    s, z = orc.ref_minmax_calibrate([0.0, 1.0, 2.0, 3.0], 8, orc.ASYMMETRIC)
+    assert abs(s[0] - 3.0 / 255.0) < 1e-5 and z[0] == 0
+
+
+def test_per_group_calibrate(orc):  # minmax.rs:362-368 (int4_per_group(4) is 4-bit symmetric)
+    s, z = orc.ref_minmax_calibrate([-1.0, 0.0, 0.5, 1.0, -2.0, 0.0, 1.0, 2.0], 4, orc.SYMMETRIC, group=4)
+    assert len(s) == 2
+    assert s[0] == np.float32(1.0) / np.float32(7.0) and s[1] == np.float32(2.0) / np.float32(7.0)
+
+
+def test_symmetric_round_trip_low_error(orc):  # minmax.rs:370-385
+    t = np.array([(i / 127.0) * 2.0 - 1.0 for i in range(128)], np.float32)
+    s, z = orc.ref_minmax_calibrate(t, 8, orc.SYMMETRIC)
+    codes = orc.minmax_quantize_grouped(t, s, z, t.size, 8, orc.SYMMETRIC)
+    deq = orc.ref_minmax_dequantize_grouped(codes, s, z, t.size)
+    assert np.abs(t - deq).max() < 0.02
+
+
+def test_grouped_round_trip(orc):  # minmax.rs:387-402
+    t = np.array([i * 0.1 for i in range(64)], np.float32)
+    s, z = orc.ref_minmax_calibrate(t, 4, orc.SYMMETRIC, group=16)
+    codes = orc.minmax_quantize_grouped(t, s, z, 16, 4, orc.SYMMETRIC)
+    deq = orc.ref_minmax_dequantize_grouped(codes, s, z, 16)
+    assert np.abs(t - deq).max() < 0.5
+
+
+def test_empty_input_error(orc):  # minmax.rs:404-408
+    with pytest.raises(orc.OracleError) as e:
+        orc.ref_minmax_calibrate(np.zeros(0, np.float32))
+    assert e.value.name == "EmptyInput"
+
+
+def test_group_size_mismatch_error(orc):  # minmax.rs:410-418
+    with pytest.raises(orc.OracleError) as e:
+        orc.ref_minmax_calibrate(np.ones(10, np.float32), 4, orc.SYMMETRIC, group=3)
+    assert e.value.name == "GroupSizeMismatch"
+
+
+def test_q_range_int8(orc):  # minmax.rs:420-426: q_max 127, q_min -128 on the reference path
+    s = np.array([1.0], np.float32)
+    z = np.array([0], np.int32)
+    codes = orc.minmax_quantize_grouped([1e9, -1e9], s, z, 2, 8, orc.SYMMETRIC)
+    assert list(codes) == [127, -128]
+    codes = orc.minmax_quantize_grouped([1e9, -1e9], s, z, 2, 8, orc.SYMMETRIC, orc.ROUND_HALF_EVEN, True)
+    assert list(codes) == [127, -127]
+
+
+def test_calibrate_2d_per_row(orc):  # minmax.rs:428-439
+    t = [0.0, 1.0, -1.0, 0.5, 0.0, 2.0, -2.0, 1.5]
+    s, z = orc.ref_minmax_calibrate_2d(t, 2, 4)
+    assert len(s) == 2 and s[1] > s[0]
+    with pytest.raises(orc.OracleError):
+        orc.ref_minmax_calibrate_2d(t, 0, 4)
+    with pytest.raises(orc.OracleError) as e:
+        orc.ref_minmax_calibrate_2d(t, 2, 0)
+    assert e.value.name == "DimensionMismatch"
+
+
+def test_rounding_modes_and_nonfinite(orc):
+    s = np.array([1.0], np.float32)
+    z = np.array([0], np.int32)
+    x = [0.5, 1.5, 2.5, -0.5, -2.5, float("nan"), float("inf"), float("-inf")]
+    away = orc.minmax_quantize_grouped(x, s, z, len(x), 8, orc.SYMMETRIC, orc.ROUND_HALF_AWAY)
+    even = orc.minmax_quantize_grouped(x, s, z, len(x), 8, orc.SYMMETRIC, orc.ROUND_HALF_EVEN)
+    assert list(away) == [1, 2, 3, -1, -3, 0, 127, -128]    # Rust f32::round; NaN as i32 == 0
+    assert list(even) == [0, 2, 2, 0, -2, 0, 127, -128]
+    with pytest.raises(orc.OracleError) as e:                # Inf in calibration -> InvalidScale (minmax.rs:234-236)
+        orc.ref_minmax_calibrate([1.0, float("inf")])
+    assert e.value.name == "InvalidScale"
+    sc, zp = orc.ref_minmax_calibrate(np.zeros(8, np.float32))
+    assert sc[0] == np.float32(1e-8) / np.float32(127.0)
+
+
+# ---- crates/oxicuda-quant/src/scheme/fp8.rs tests ----------------------------------------------
+
+def test_e4m3_zero_encodes_to_zero(orc):  # fp8.rs:287-292
+    assert list(orc.ref_fp8_encode([0.0, -0.0])) == [0x00, 0x80]
+
+
+def test_e4m3_round_trip_basic(orc):  # fp8.rs:294-303
+    v = np.array([1.0, -1.0, 2.0, 0.5, 0.25, -0.25], np.float32)
+    dec = orc.ref_fp8_decode(orc.ref_fp8_encode(v))
+    assert (np.abs(v - dec) / np.abs(v) < 0.15).all()
+
+
+def test_e5m2_round_trip_basic(orc):  # fp8.rs:305-314
+    v = np.array([1.0, -1.0, 4.0, 16.0, -8.0], np.float32)
+    dec = orc.ref_fp8_decode(orc.ref_fp8_encode(v, e5m2=True), e5m2=True)
+    assert (np.abs(v - dec) / np.abs(v) < 0.25).all()
+
+
+def test_e4m3_saturates_large_values(orc):  # fp8.rs:316-324
+    dec = orc.ref_fp8_decode(orc.ref_fp8_encode([1000.0]))
+    assert 0.0 < dec[0] <= 449.0
+
+
+def test_nan_input_errors(orc):  # fp8.rs:326-340
+    for bad in (float("nan"), float("inf")):
+        with pytest.raises(orc.OracleError) as e:
+            orc.ref_fp8_encode([bad])
+        assert e.value.name == "NonFiniteFp8"
+
+
+def test_mse_within_tolerance(orc):  # fp8.rs:342-348
+    d = np.array([(i / 128.0) - 1.0 for i in range(256)], np.float32)
+    dec = orc.ref_fp8_decode(orc.ref_fp8_encode(d))
+    assert float(((d - dec) ** 2).sum() / d.size) < 0.01
+
+
+def test_ref_fp8_literal_quirks(orc):
+    """Behaviour of the literal restatement that the reference tests leave unpinned (fp8.rs:163-261):
+    truncation, |v| >= 256 -> 448, subnormal shift, subnormal decode."""
+    enc = orc.ref_fp8_encode([1.9375, 256.0, 2.0 ** -7, 1.0])
+    assert list(enc) == [0x3F, 0x7E, 0x02, 0x38]            # 0x38 = E4M3 one (blas types.rs:355-357)
+    assert orc.ref_fp8_decode([0x3F])[0] == 1.875
+    assert orc.ref_fp8_decode([0x02])[0] == np.float32(2.0 ** -6 * 1.25)
+    assert orc.ref_fp8_encode([1.0], e5m2=True)[0] == 0x3C  # E5M2 one (blas types.rs:383-385)
+    assert math.isnan(orc.ref_fp8_decode([0x7F])[0])
+
+
+# ---- crates/oxicuda-blas/src/precision/int_ops.rs tests ----------------------------------------
+
+def test_pack_unpack_int4_roundtrip(orc):  # int_ops.rs:1008-1017
+    v = [0, 1, -1, 7, -8, 3, -5, 2]
+    p = orc.ref_pack_int4(v)
+    assert p.size == 1 and list(orc.ref_unpack_int4(p)) == v
+
+
+def test_pack_int4_errors(orc):  # int_ops.rs:1019-1029
+    with pytest.raises(orc.OracleError):
+        orc.ref_pack_int4([0, 1, 2])
+    with pytest.raises(orc.OracleError):
+        orc.ref_pack_int4([0, 1, 2, 3, 4, 5, 6, 10])
+
+
+def test_unpack_int4_patterns(orc):  # int_ops.rs:1031-1052
+    assert list(orc.ref_unpack_int4([0x00000000])) == [0] * 8
+    assert list(orc.ref_unpack_int4([0xFFFFFFFF])) == [-1] * 8
+    assert list(orc.ref_unpack_int4([0x87878787])) == [7, -8] * 4
+    assert list(orc.unpack_uint4([0x87878787])) == [7, 8] * 4
+    v = np.arange(16, dtype=np.uint8)
+    assert list(orc.unpack_uint4(orc.pack_uint4(v))) == list(v)
+
+
+# ---- crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs tests ------------------------------------
+
+def test_fp4_e2m1_roundtrip_accuracy(orc):  # fp4_fp6_ops.rs:1681-1697
+    for v in [0.0, 1.0, -1.0, 2.0, -2.0, 4.0, -4.0, 6.0]:
+        rec = orc.e2m1_to_f32(np.array([orc.ref_e2m1_quantize_one(v)], np.uint8))[0]
+        assert abs(v - rec) <= abs(v) * 0.6 + 0.01
+
+
+def test_ref_e2m1_floor_map(orc):
+    """The reference encoder's value map (fp4_fp6_ops.rs:645-661), by interval."""
+    table = [(0.3, 0.0), (0.74, 0.0), (0.75, 0.5), (0.99, 0.5), (1.0, 1.0), (1.49, 1.0), (1.5, 1.5), (1.99, 1.5),
+             (2.0, 2.0), (2.99, 2.0), (3.0, 3.0), (3.99, 3.0), (4.0, 4.0), (5.99, 4.0), (6.0, 6.0), (100.0, 6.0)]
+    for v, want in table:
+        got = orc.e2m1_to_f32(np.array([orc.ref_e2m1_quantize_one(v)], np.uint8))[0]
+        assert got == want, (v, got, want)
+    assert orc.ref_e2m1_quantize_one(-0.1) == 0x8
+    assert orc.ref_e2m1_quantize_one(-0.0) == 0x0
+
+
+def test_micro_scaling_fp4_roundtrip(orc):  # fp4_fp6_ops.rs micro_scaling tests: block scale = absmax/6
+    x = np.array([i * 0.25 - 4.0 for i in range(64)], np.float32)
+    packed, scales = orc.ref_microscale_fp4(x, 32)
+    assert scales[0] == np.float32(np.abs(x[:32]).max()) / np.float32(6.0)
+    rec = orc.ref_microscale_fp4_dequant(packed, scales, x.size, 32)
+    assert np.abs(x - rec).max() <= np.abs(x).max() * 0.35
+    with pytest.raises(orc.OracleError):
+        orc.ref_microscale_fp4(x, 16)                      # block_size must be 32/64/128 (fp4_fp6_ops.rs:202-214)
+    _, s0 = orc.ref_microscale_fp4(np.zeros(32, np.float32), 32)
+    assert s0[0] == 1.0                                    # all-zero block -> scale 1.0 (:773-777)
+
+
+# ---- adjacent scale KATs -----------------------------------------------------------------------
+
+def test_int8_block_dequant_kat(orc):  # crates/oxicuda-dnn/src/quantize/int8_quantize.rs:619-639
+    y = orc.spec_int8_dequant_rows(np.array([[-128, 0, 127]], np.int8), np.array([0.1], np.float32))
+    assert np.allclose(y[0], [-12.8, 0.0, 12.7], atol=1e-5)
+
+
+# ---- tensor-parallel definition ----------------------------------------------------------------
+
+def test_tp_column_then_row_matches_unsharded(orc):  # crates/oxicuda-dist-infer/src/lib.rs:120 (tp=4 e2e)
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((3, 8)).astype(np.float32)
+    wg = rng.standard_normal((16, 8)).astype(np.float32)
+    wu = rng.standard_normal((16, 8)).astype(np.float32)
+    wd = rng.standard_normal((8, 16)).astype(np.float32)
+    full = orc.ref_swiglu_mlp(x, wg, wu, wd)
+    tp = orc.ref_tp_swiglu_mlp(x, wg, wu, wd, 4)
+    assert np.allclose(full, tp, rtol=1e-5, atol=1e-5)
+    want = (x @ wg.T)
+    want = want / (1 + np.exp(-want)) * (x @ wu.T)
+    assert np.allclose(full, want @ wd.T, rtol=1e-4, atol=1e-4)

@@ -135,7 +135,7 @@ def test_spec_mxfp8(orc):
     assert ((vals[am > 0] >= 256) & (vals[am > 0] <= 448)).all()
     deq = orc.spec_mxfp8_dequant(codes, sf)
     err = np.abs(deq - x).reshape(8, 8, 32).max(axis=2)
-    assert (err <= am / 16.0).all()
+    assert (err <= am / 8.0).all()          # values in (448, 512) * 2^e saturate to 448 * 2^e
 
 
 def test_spec_nvfp4(orc):

@@ -1,0 +1,353 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-inference hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras]
+
+Headline workload (BASELINE.json configs[1]): FP8 E4M3 GEMM M = N = K = 8192, bf16 operands
+N(0,1) quantised per tensor (scale = absmax/448), f32 accumulate, bf16 output = acc * sA * sB.
+
+  value     TFLOP/s of the GEMM kernel with the E4M3 operands already resident in HBM.
+  e2e       the same metric through the host-buffer path: pinned bf16 host operands -> H2D ->
+            absmax + quantize of both operands -> GEMM -> D2H of the bf16 result, every step.
+  roofline  the GEMM kernel against the tensor-core peak (2 x the measured bf16 figure of
+            MEASURED_PEAKS.json: FP8 issues at twice the bf16 rate; no FP8 figure is measured there).
+  extras    the memory-bound kernels of the path (quantizers, decode GEMMs) in GB/s of algorithmic
+            bytes against the measured HBM copy bandwidth, each on a ring of buffers larger than L2.
+  cpu_baseline / --impl reference
+            the CPU oracle (a C restatement of the reference's scalar loops; the reference itself is
+            a Rust workspace that cannot be built here) on a bounded sample of the same GEMM.
+
+One process per GPU; with --gpus N > 1 (under torchrun) every rank runs the same single-GPU GEMM on
+its own data (the GEMM does not shard without the tensor-parallel MLP around it; "weak" scaling of
+independent replicas) and the time is the max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M = N = K = 8192
+FLOP = 2.0 * M * N * K
+L2_BYTES = 126 * 1024 * 1024
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        top = sorted(sm)[len(sm) // 2:]                   # samples under load = upper half
+        return {"sm_mhz": statistics.median(top), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm
+
+def cpu_gemm_sample(sample_rows: int, threads: int):
+    """Times the oracle's FP8 path on `sample_rows` rows of X against the full 8192 x 8192 weight:
+    quantised codes -> dequantise -> f32 GEMM in the reference's accumulation order."""
+    from oracle import oracle as orc
+    rng = np.random.Generator(np.random.Philox(0))
+    xq = rng.integers(0, 0x7E, size=(sample_rows, K), dtype=np.uint8)
+    wq = rng.integers(0, 0x7E, size=(N, K), dtype=np.uint8)
+    t0 = time.perf_counter()
+    x = orc.spec_fp8_dequant(xq, 1.0)
+    w = orc.spec_fp8_dequant(wq, 1.0)
+    orc.ref_linear_f32(x, w, threads=threads)
+    dt = time.perf_counter() - t0
+    return 2.0 * sample_rows * N * K / dt / 1e12, dt
+
+
+def run_reference(args):
+    from oracle import oracle as orc
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = orc.max_threads()
+    rows = 64
+    for _ in range(args.warmup):
+        cpu_gemm_sample(8, threads)
+    vals, times = [], []
+    for _ in range(args.steps):
+        v, dt = cpu_gemm_sample(rows, threads)
+        vals.append(v)
+        times.append(dt)
+    val = float(np.mean(vals))
+    sample = f"{rows} of {M} rows of X against the full {N}x{K} weight per step (dequantise + f32 GEMM, reference summation order)"
+    line = {
+        "impl": "reference", "metric": "quant_gemm_tflops_prefill", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(np.mean(times)) * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "fp8_e4m3_gemm_8192x8192x8192", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+
+def time_region(torch, fn, steps, dist_on):
+    """Times `steps` calls of fn() with CUDA events on the current stream, barrier + sync on both sides."""
+    if dist_on:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if dist_on:
+        torch.distributed.barrier()
+    ms = e0.elapsed_time(e1)
+    if dist_on:
+        t = torch.tensor([ms], device="cuda")
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def ring_time(torch, make_call, ring, iters=40, warm=5):
+    """Average ms per call over a ring of distinct buffer sets (total > L2), CUDA events."""
+    for i in range(warm):
+        make_call(ring[i % len(ring)])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        make_call(ring[i % len(ring)])
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def extras(torch, ops, peaks):
+    """Memory-bound kernels of the path: GB/s of algorithmic bytes, fraction of the measured copy bandwidth."""
+    out = {}
+    hbm = peaks["hbm_gbs"]
+
+    def rec(name, nbytes, ms, launches=1):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": round(ms, 5), "GB/s": round(gbs, 1), "frac_of_hbm": round(gbs / hbm, 3), "bytes": int(nbytes),
+                     "launches_per_call": launches}
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    # config 1: INT8 per-row quantize / dequantize of 4096x4096 f32 (ring of 4 -> 256 MiB of inputs)
+    ring = [torch.randn((4096, 4096), generator=g, device="cuda") * 0.02 for _ in range(4)]
+    q8 = [ops.int8_quant_rows(r) for r in ring]
+    rec("int8_quant_rows_4096x4096", 67108864 + 16777216 + 16384, ring_time(torch, lambda r: ops.int8_quant_rows(r), ring))
+    rec("int8_dequant_rows_4096x4096", 16777216 + 16384 + 67108864, ring_time(torch, lambda r: ops.int8_dequant_rows(*r), q8))
+    x8 = torch.randn((8, 4096), generator=g, device="cuda")
+    rec("gemm_w8a32_m8_4096x4096", 16777216 + 16384 + 131072 + 131072, ring_time(torch, lambda r: ops.gemm_w8a32(x8, *r), q8))
+    del ring, q8
+    # config 2: bf16 -> E4M3 of 8192x8192 (ring of 3 -> 384 MiB)
+    ring = [torch.randn((8192, 8192), generator=g, device="cuda", dtype=torch.bfloat16) for _ in range(3)]
+    outq = torch.empty((8192, 8192), dtype=torch.uint8, device="cuda")
+    stats = torch.empty(2, device="cuda")
+    am = torch.empty(1, device="cuda")
+    rec("absmax_bf16_8192x8192", 134217728, ring_time(torch, lambda r: ops.absmax(r, out=am), ring))
+    one = torch.ones(1, device="cuda")
+    rec("fp8_quant_bf16_8192x8192", 201326592, ring_time(torch, lambda r: ops.fp8_quant(r, one, out=outq), ring))
+    rec("fp8_quant_dynamic_bf16_8192x8192", 335544320, ring_time(torch, lambda r: ops.fp8_quant_dynamic(r, out=outq, stats=stats), ring), 2)
+    # config 4 quantizers on the 4096x4096 activation shape (ring of 8 -> 256 MiB)
+    ring4 = [r[:4096, :4096].contiguous() for r in ring] + [r[4096:, 4096:].contiguous() for r in ring] + [ring[0][:4096, 4096:].contiguous(), ring[1][4096:, :4096].contiguous()]
+    rec("mxfp8_quant_bf16_4096x4096", 33554432 + 16777216 + 2 * 524288, ring_time(torch, lambda r: ops.mxfp8_quant(r), ring4))
+    rec("nvfp4_quant_bf16_4096x4096(absmax+encode)", 2 * 33554432 + 8388608 + 2 * 1048576, ring_time(torch, lambda r: ops.nvfp4_quant(r), ring4), 2)
+    del ring, ring4, outq
+    # config 3: W4A16 decode GEMMs; weights cycled through a ring > 4x L2
+    for (n, k) in ((6144, 4096), (4096, 4096), (14336, 4096), (4096, 14336)):
+        wbytes = n * k // 2 + n * k // 128 * 2 + n * k // 128 // 2
+        copies = max(4, int(4 * L2_BYTES // wbytes) + 1)
+        w = torch.randn((n, k), generator=g, device="cuda") * 0.02
+        c, s, z = ops.int4g_quant_pack(w, 128)
+        ring = [(c.clone(), s.clone(), z.clone()) for _ in range(copies)]
+        del w
+        for m in (1, 8, 32):
+            x = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+            ws = ops.gemm_w4a16_workspace(m, n, k, "cuda")
+            y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+            ms = ring_time(torch, lambda r: ops.gemm_w4a16(x, r[0], r[1], r[2], 128, workspace=ws, out=y), ring, iters=3 * copies)
+            rec(f"gemm_w4a16_m{m}_{n}x{k}", wbytes + m * k * 2 + m * n * 2, ms)
+        del ring
+    # the offline W4 quantize + pack kernel on the largest weight
+    ringw = [torch.randn((14336, 4096), generator=g, device="cuda") * 0.02 for _ in range(3)]
+    rec("int4g_quant_pack_f32_14336x4096", 14336 * 4096 * 4 + 14336 * 4096 // 2 + 458752 * 2 + 458752 // 2,
+        ring_time(torch, lambda r: ops.int4g_quant_pack(r, 128), ringw, iters=12))
+    return out
+
+
+def run_ours(args):
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
+    from oxicuda_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist_on = world > 1
+    torch.cuda.set_device(local_rank)
+    if dist_on:
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    peaks = load_peaks()
+
+    g = torch.Generator(device="cuda").manual_seed(rank)
+    a = torch.randn((M, K), generator=g, device="cuda").to(torch.bfloat16)
+    b = torch.randn((N, K), generator=g, device="cuda").to(torch.bfloat16)
+    qa, sa = ops.fp8_quant_dynamic(a)
+    qb, sb = ops.fp8_quant_dynamic(b)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    sa1, sb1 = sa[1:], sb[1:]
+
+    def step():
+        ops.gemm_fp8(qa, qb, sa1, sb1, out=y)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if ops.handle().device_status() != 0:
+        raise SystemExit("device-side wait expired during warm-up")
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = time_region(torch, step, args.steps, dist_on)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = ms / args.steps
+    value = world * FLOP / (ms_per_step * 1e-3) / 1e12
+    kernel_tflops = FLOP / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end through host buffers ------------------------------------------------------
+    a_h = a.cpu().pin_memory()
+    b_h = b.cpu().pin_memory()
+    y_h = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    a_d, b_d = torch.empty_like(a), torch.empty_like(b)
+    qa2, qb2 = torch.empty_like(qa), torch.empty_like(qb)
+    st_a, st_b = torch.empty(2, device="cuda"), torch.empty(2, device="cuda")
+
+    def e2e_step():
+        a_d.copy_(a_h, non_blocking=True)
+        b_d.copy_(b_h, non_blocking=True)
+        ops.fp8_quant_dynamic(a_d, out=qa2, stats=st_a)
+        ops.fp8_quant_dynamic(b_d, out=qb2, stats=st_b)
+        ops.gemm_fp8(qa2, qb2, st_a[1:], st_b[1:], out=y)
+        y_h.copy_(y, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    e2e_ms = time_region(torch, e2e_step, e2e_steps, dist_on) / e2e_steps
+    e2e_val = world * FLOP / (e2e_ms * 1e-3) / 1e12
+
+    extra = None
+    cpu = None
+    if rank == 0 and not args.no_extras:
+        extra = extras(torch, ops, peaks)
+    if rank == 0 and world == 1:
+        from oracle import oracle as orc
+        threads = orc.max_threads()
+        rows = 64
+        v, dt = cpu_gemm_sample(rows, threads)
+        cpu = {"value": v, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+               "sample": f"{rows} of {M} rows of X against the full {N}x{K} weight (dequantise + f32 GEMM, reference summation order), {dt:.1f} s"}
+
+    if dist_on:
+        torch.distributed.barrier()
+    if rank == 0:
+        fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+        line = {
+            "metric": "quant_gemm_tflops_prefill", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+            "config": {"workload": "fp8_e4m3_gemm_8192x8192x8192", "m": M, "n": N, "k": K, "accumulate": "f32", "out": "bf16",
+                       "l2": "operands + output = 256 MiB per step, larger than the 126 MB L2",
+                       "multi_gpu": "independent replicas, one GEMM per rank" if world > 1 else "single GPU"},
+            "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": fp8_peak, "unit": "TFLOP/s",
+                         "frac": kernel_tflops / fp8_peak, "traffic": None,
+                         "peak_note": f"2 x bf16_tflops_sustained ({peaks['source']}); nominal dense FP8 is 4500",
+                         "frac_of_nominal": kernel_tflops / 4500.0},
+            "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2, "d2h_bytes_per_step": M * N * 2,
+                    "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        if extra is not None:
+            line["extras"] = extra
+        print(json.dumps(line), flush=True)
+    if dist_on:
+        torch.distributed.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,170 @@
+/*
+ * oxq.h -- C ABI of liboxq_b200.so: hand-written sm_100a kernels for the OxiCUDA quantized-inference
+ * path (oxicuda-quant quantize/dequantize kernels and the oxicuda-blas low-precision GEMMs).
+ *
+ * The reference is a Rust workspace with no FFI boundary of its own on this path: its two public
+ * surfaces are ordinary Rust APIs.  Each entry point below names the reference interface it stands
+ * behind (paths relative to the reference workspace root).  A Rust shim binds these symbols with
+ * `extern "C"` declarations and keeps the reference's type names on top.
+ *
+ * Conventions
+ *   - Every pointer named *_dev or documented "device" is a device pointer owned by the caller
+ *     (reference: MatrixDesc borrows a CUdeviceptr, crates/oxicuda-blas/src/types.rs:443-455).
+ *   - Every call is asynchronous on the handle's stream and performs no host synchronisation
+ *     (reference: dispatch() launches and returns, crates/oxicuda-blas/src/level3/gemm/dispatch.rs:198-203).
+ *   - No call allocates device memory.  Kernels that need scratch take a caller-provided workspace.
+ *   - A handle is not thread-safe: one per host thread, exactly the BlasHandle rule
+ *     (crates/oxicuda-blas/src/handle.rs:37-40).
+ *   - There is no CPU fallback: on a machine without an sm_100 device every launch returns an error.
+ *   - Matrices are row-major.  GEMMs compute Y[M x N] = X[M x K] * W[N x K]^T with K contiguous in
+ *     both operands (the weight layout of ColumnLinearShard,
+ *     crates/oxicuda-dist-infer/src/tensor_parallel/column_parallel.rs:77-95).
+ *
+ * Status codes: 0 = OK; 1..9 mirror QuantError (crates/oxicuda-quant/src/error.rs:10-58);
+ * 10..19 mirror BlasError (crates/oxicuda-blas/src/error.rs:16-59); 100 = a bounded device-side
+ * wait expired; 1000 + n = cudaError_t n.
+ */
+#ifndef OXQ_H_
+#define OXQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define OXQ_API __attribute__((visibility("default")))
+#else
+#define OXQ_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct oxq_handle oxq_handle;
+
+enum {
+    OXQ_OK = 0,
+    /* QuantError */
+    OXQ_ERR_EMPTY_INPUT = 1,
+    OXQ_ERR_GROUP_SIZE_MISMATCH = 2,
+    OXQ_ERR_INVALID_SCALE = 3,
+    OXQ_ERR_QUANT_DIMENSION_MISMATCH = 4,
+    OXQ_ERR_NON_FINITE_FP8 = 5,
+    OXQ_ERR_INVALID_BIT_WIDTH = 6,
+    /* BlasError */
+    OXQ_ERR_INVALID_DIMENSION = 10,
+    OXQ_ERR_BUFFER_TOO_SMALL = 11,
+    OXQ_ERR_DIMENSION_MISMATCH = 12,
+    OXQ_ERR_UNSUPPORTED_OPERATION = 13,
+    OXQ_ERR_LAUNCH_FAILED = 14,
+    OXQ_ERR_INVALID_ARGUMENT = 15,
+    /* device side */
+    OXQ_ERR_DEVICE_TIMEOUT = 100,
+    OXQ_ERR_CUDA_BASE = 1000
+};
+
+/* element types of floating-point tensors handed to the quantizers */
+enum { OXQ_F32 = 0, OXQ_BF16 = 1, OXQ_F16 = 2 };
+/* integer rounding of x/scale: HALF_EVEN is cvt.rni (crates/oxicuda-quant/src/ptx_kernels.rs:166-172),
+ * HALF_AWAY is f32::round as used by MinMaxQuantizer (crates/oxicuda-quant/src/scheme/minmax.rs:263). */
+enum { OXQ_ROUND_HALF_EVEN = 0, OXQ_ROUND_HALF_AWAY = 1 };
+/* FP8 conversion: SPEC_RNE = round-to-nearest-even, saturating (cvt.rn.satfinite.e4m3x2.f32, the
+ * conversion the reference's PTX builder documents, crates/oxicuda-ptx/src/builder/body_builder/mod.rs:1309-1323);
+ * REFCOMPAT = the literal bit manipulation of Fp8Codec (crates/oxicuda-quant/src/scheme/fp8.rs:163-208). */
+enum { OXQ_FP8_SPEC_RNE = 0, OXQ_FP8_REFCOMPAT = 1 };
+
+/* ---- handle: stands in for BlasHandle (crates/oxicuda-blas/src/handle.rs:41-52) ---------------- */
+OXQ_API int32_t oxq_handle_create(int device, void* cuda_stream, oxq_handle** out);
+OXQ_API int32_t oxq_handle_destroy(oxq_handle* h);
+OXQ_API int32_t oxq_set_stream(oxq_handle* h, void* cuda_stream);          /* BlasHandle::set_stream, handle.rs:134-154 */
+OXQ_API const char* oxq_last_error_string(const oxq_handle* h);
+OXQ_API const char* oxq_status_name(int32_t status);
+OXQ_API int32_t oxq_version(void);
+/* Reads and clears the device-side status word that bounded waits write (0 = none).  Synchronises the stream. */
+OXQ_API int32_t oxq_device_status(oxq_handle* h, int32_t* status_out);
+
+/* ---- INT8 symmetric per-row: MinMaxQuantizer::calibrate_2d + quantize_grouped(group = cols)
+ *      (crates/oxicuda-quant/src/scheme/minmax.rs:179-207, :275-299); device API shape of
+ *      quantize_to_int8 (crates/oxicuda-dnn/src/quantize/int8_quantize.rs:33-92).
+ *      scale[r] = max(absmax_row, 1e-8)/127; q = clamp(round(x/scale), -127, 127). ------------------ */
+OXQ_API int32_t oxq_int8_quant_rows(oxq_handle* h, const float* x_dev, int64_t rows, int64_t cols,
+                            int8_t* q_dev, float* scales_dev, int rounding);
+/* MinMaxQuantizer::dequantize_grouped (minmax.rs:309-324): y = q * scale[row]. */
+OXQ_API int32_t oxq_int8_dequant_rows(oxq_handle* h, const int8_t* q_dev, const float* scales_dev,
+                              int64_t rows, int64_t cols, float* y_dev);
+
+/* ---- FP8 E4M3 per tensor: Fp8Codec::encode / decode (crates/oxicuda-quant/src/scheme/fp8.rs:115-142)
+ *      with the per-tensor absmax/448 scaling of quantize_to_fp8
+ *      (crates/oxicuda-dnn/src/quantize/fp8_quantize.rs:47-111). ------------------------------------- */
+/* absmax_dev[0] = max |x| (NaNs skipped).  One pass over x. */
+OXQ_API int32_t oxq_absmax(oxq_handle* h, const void* x_dev, int x_dtype, int64_t n, float* absmax_dev);
+/* q = e4m3(x / *scale_dev). */
+OXQ_API int32_t oxq_fp8_quant(oxq_handle* h, const void* x_dev, int x_dtype, int64_t n, const float* scale_dev,
+                      uint8_t* q_dev, int fp8_mode);
+/* absmax pass + quantize pass; stats_dev[0] = absmax, stats_dev[1] = scale = absmax/448 (1.0 if absmax == 0). */
+OXQ_API int32_t oxq_fp8_quant_dynamic(oxq_handle* h, const void* x_dev, int x_dtype, int64_t n, uint8_t* q_dev,
+                              float* stats_dev);
+/* y = decode(q) * *scale_dev. */
+OXQ_API int32_t oxq_fp8_dequant(oxq_handle* h, const uint8_t* q_dev, int64_t n, const float* scale_dev,
+                        void* y_dev, int y_dtype, int fp8_mode);
+
+/* ---- uint4 group-wise asymmetric: MinMaxQuantizer::int4_per_group / calibrate(PerGroup, Asymmetric)
+ *      (minmax.rs:146-167, :226-232) + pack_int4 bit positions (crates/oxicuda-blas/src/precision/int_ops.rs:375-399);
+ *      device API shape of quantize_to_int4 (crates/oxicuda-dnn/src/quantize/int4_quantize.rs:132-218).
+ *      Groups run along k; scales are f16 [rows x k/group]; zero-points are packed 8 per u32 in
+ *      linear group order; codes 8 per u32, element j at bits [4j, 4j+4). ---------------------------- */
+OXQ_API int32_t oxq_int4g_quant_pack(oxq_handle* h, const void* x_dev, int x_dtype, int64_t rows, int64_t k, int group,
+                             uint32_t* codes_dev, uint16_t* scales_f16_dev, uint32_t* zeros_packed_dev, int rounding);
+OXQ_API int32_t oxq_int4g_dequant(oxq_handle* h, const uint32_t* codes_dev, const uint16_t* scales_f16_dev,
+                          const uint32_t* zeros_packed_dev, int64_t rows, int64_t k, int group,
+                          void* y_dev, int y_dtype);
+
+/* ---- block-scaled formats: MicroScalingQuantizer::quantize_fp4 and Fp4GemmConfig
+ *      (crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:337-395, :746-898) re-defined on the OCP MX / NVFP4
+ *      formats the benchmark configurations name.  Scale factors are written twice: row-major
+ *      [rows x k/block], and (if sf_mma_dev != NULL) in the 128-row x 4-column tiled order the
+ *      tensor-core scale-factor loads consume; oxq_sf_mma_bytes gives the size of the latter. -------- */
+OXQ_API size_t oxq_sf_mma_bytes(int64_t rows, int64_t sf_cols);
+OXQ_API int32_t oxq_mxfp8_quant(oxq_handle* h, const void* x_dev, int x_dtype, int64_t rows, int64_t k,
+                        uint8_t* codes_dev, uint8_t* sf_rowmajor_dev, uint8_t* sf_mma_dev);
+OXQ_API int32_t oxq_mxfp8_dequant(oxq_handle* h, const uint8_t* codes_dev, const uint8_t* sf_rowmajor_dev,
+                          int64_t rows, int64_t k, void* y_dev, int y_dtype);
+/* stats_dev[0] = absmax (input, from oxq_absmax), stats_dev[1] = global scale g (output). */
+OXQ_API int32_t oxq_nvfp4_quant(oxq_handle* h, const void* x_dev, int x_dtype, int64_t rows, int64_t k,
+                        float* stats_dev, uint8_t* packed_dev, uint8_t* sf_rowmajor_dev, uint8_t* sf_mma_dev);
+OXQ_API int32_t oxq_nvfp4_dequant(oxq_handle* h, const uint8_t* packed_dev, const uint8_t* sf_rowmajor_dev,
+                          const float* stats_dev, int64_t rows, int64_t k, void* y_dev, int y_dtype);
+
+/* ---- GEMMs: stand behind gemm<T> (crates/oxicuda-blas/src/level3/gemm_api.rs:73-138) for the element
+ *      types that entry point cannot run in the reference, and behind the low-precision configs of
+ *      crates/oxicuda-blas/src/precision/{int_ops,fp8_ops,fp4_fp6_ops}.rs.
+ *      Zero dimensions are errors (gemm_api.rs:88-92).  Outputs are bf16 unless noted. ---------------- */
+/* FP8 E4M3: Y = bf16((X . W^T) * (*sx_dev * *sw_dev)), f32 accumulate.  K % 16 == 0, ldy % 8 == 0. */
+OXQ_API int32_t oxq_gemm_fp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x_dev, int64_t ldx,
+                     const uint8_t* w_dev, int64_t ldw, const float* sx_dev, const float* sw_dev,
+                     void* y_bf16_dev, int64_t ldy);
+/* W8A8 (Int8GemmConfig, int_ops.rs:79-189): Y = bf16(s32(X . W^T) * sx_rows[m] * sw_rows[n]). */
+OXQ_API int32_t oxq_gemm_w8a8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const int8_t* x_dev, int64_t ldx,
+                      const int8_t* w_dev, int64_t ldw, const float* sx_rows_dev, const float* sw_rows_dev,
+                      void* y_bf16_dev, int64_t ldy);
+/* W8A32 decode GEMM of benchmark configuration 1: Y_f32 = X_f32 . (W_i8 * sw_rows)^T, f32 accumulate. */
+OXQ_API int32_t oxq_gemm_w8a32(oxq_handle* h, int64_t m, int64_t n, int64_t k, const float* x_dev,
+                       const int8_t* w_dev, const float* sw_rows_dev, float* y_dev);
+/* W4A16 weight-only (Int4GemmConfig, int_ops.rs:215-355; quantized operand is the weight):
+ * Y = bf16(X_bf16 . dequant(W)^T).  Workspace: oxq_gemm_w4a16_workspace_bytes; it must be zero-filled
+ * before its first use and is left zero-filled by every call. */
+OXQ_API size_t oxq_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k);
+OXQ_API int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x_bf16_dev,
+                       const uint32_t* codes_dev, const uint16_t* scales_f16_dev, const uint32_t* zeros_packed_dev,
+                       int group, void* y_bf16_dev, void* workspace_dev, size_t workspace_bytes);
+/* Block-scaled GEMMs (Fp4GemmConfig, fp4_fp6_ops.rs:337-395).  Scale factors in the tiled order. */
+OXQ_API int32_t oxq_gemm_mxfp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x_dev, const uint8_t* sfx_mma_dev,
+                       const uint8_t* w_dev, const uint8_t* sfw_mma_dev, void* y_bf16_dev, int64_t ldy);
+OXQ_API int32_t oxq_gemm_nvfp4(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x_dev, const uint8_t* sfx_mma_dev,
+                       const float* gx_dev, const uint8_t* w_dev, const uint8_t* sfw_mma_dev, const float* gw_dev,
+                       void* y_bf16_dev, int64_t ldy);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OXQ_H_ */

@@ -1,0 +1,68 @@
+"""ctypes binding of liboxq_b200.so (the C ABI declared in include/oxq.h).
+
+There is no fallback: if the shared library is missing this module raises, and every launch on a
+machine without an sm_100 GPU returns an error status from the library itself.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import _build
+
+_i32, _i64, _sz, _vp, _int, _f32p = C.c_int32, C.c_int64, C.c_size_t, C.c_void_p, C.c_int, C.c_void_p
+
+# symbol -> (restype, argtypes); mirrors include/oxq.h one to one
+SIGNATURES = {
+    "oxq_handle_create": (_i32, [_int, _vp, C.POINTER(_vp)]),
+    "oxq_handle_destroy": (_i32, [_vp]),
+    "oxq_set_stream": (_i32, [_vp, _vp]),
+    "oxq_last_error_string": (C.c_char_p, [_vp]),
+    "oxq_status_name": (C.c_char_p, [_i32]),
+    "oxq_version": (_i32, []),
+    "oxq_device_status": (_i32, [_vp, C.POINTER(_i32)]),
+    "oxq_int8_quant_rows": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp, _int]),
+    "oxq_int8_dequant_rows": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp]),
+    "oxq_absmax": (_i32, [_vp, _vp, _int, _i64, _vp]),
+    "oxq_fp8_quant": (_i32, [_vp, _vp, _int, _i64, _vp, _vp, _int]),
+    "oxq_fp8_quant_dynamic": (_i32, [_vp, _vp, _int, _i64, _vp, _vp]),
+    "oxq_fp8_dequant": (_i32, [_vp, _vp, _i64, _vp, _vp, _int, _int]),
+    "oxq_int4g_quant_pack": (_i32, [_vp, _vp, _int, _i64, _i64, _int, _vp, _vp, _vp, _int]),
+    "oxq_int4g_dequant": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _int]),
+    "oxq_sf_mma_bytes": (_sz, [_i64, _i64]),
+    "oxq_mxfp8_quant": (_i32, [_vp, _vp, _int, _i64, _i64, _vp, _vp, _vp]),
+    "oxq_mxfp8_dequant": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp, _int]),
+    "oxq_nvfp4_quant": (_i32, [_vp, _vp, _int, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "oxq_nvfp4_dequant": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _int]),
+    "oxq_gemm_fp8": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64]),
+    "oxq_gemm_w8a8": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64]),
+    "oxq_gemm_w8a32": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "oxq_gemm_w4a16_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "oxq_gemm_w4a16": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp, _vp, _sz]),
+    "oxq_gemm_mxfp8": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64]),
+    "oxq_gemm_nvfp4": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64]),
+}
+
+_lib = None
+
+
+def lib_path() -> str:
+    return _build.LIB_PATH
+
+
+def load():
+    """Load the library (never builds it implicitly on a GPU box: the prebuilt file travels with the tree)."""
+    global _lib
+    if _lib is None:
+        path = lib_path()
+        if not os.path.exists(path):
+            raise ImportError(
+                f"{path} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'`. "
+                "oxicuda_b200 has no CPU or PyTorch fallback.")
+        lib = C.CDLL(path)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)          # AttributeError here means the header and the library disagree
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib

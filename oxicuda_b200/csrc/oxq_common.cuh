@@ -1,0 +1,147 @@
+// Shared declarations of liboxq_b200: the handle, status plumbing and small device helpers.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+#include "../../include/oxq.h"
+
+struct oxq_handle {
+    int device;
+    cudaStream_t stream;
+    int sm_count;
+    int cc_major, cc_minor;
+    int32_t* dev_status;      // one word in device memory, written by bounded waits that expire
+    char last_error[256];
+};
+
+#define OXQ_FAIL(h, code, ...)                                           \
+    do {                                                                 \
+        if (h) snprintf((h)->last_error, sizeof((h)->last_error), __VA_ARGS__); \
+        return (code);                                                   \
+    } while (0)
+
+#define OXQ_CUDA(h, expr)                                                \
+    do {                                                                 \
+        cudaError_t e__ = (expr);                                        \
+        if (e__ != cudaSuccess) {                                        \
+            if (h) snprintf((h)->last_error, sizeof((h)->last_error), "%s: %s", #expr, cudaGetErrorString(e__)); \
+            return OXQ_ERR_CUDA_BASE + (int32_t)e__;                     \
+        }                                                                \
+    } while (0)
+
+#define OXQ_CHECK_HANDLE(h)                                              \
+    do { if (!(h)) return OXQ_ERR_INVALID_ARGUMENT; (h)->last_error[0] = 0; } while (0)
+
+// Reports a launch-time error of the kernel just launched (asynchronous faults surface later).
+#define OXQ_LAUNCH_CHECK(h)                                              \
+    do {                                                                 \
+        cudaError_t e__ = cudaGetLastError();                            \
+        if (e__ != cudaSuccess) {                                        \
+            snprintf((h)->last_error, sizeof((h)->last_error), "kernel launch failed: %s", cudaGetErrorString(e__)); \
+            return OXQ_ERR_CUDA_BASE + (int32_t)e__;                     \
+        }                                                                \
+    } while (0)
+
+// Refuses to launch on anything but a compute-capability 10.x device: there is no fallback path.
+int32_t oxq_require_sm100(oxq_handle* h);
+
+namespace oxq {
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Loads `V` consecutive elements of dtype T as floats.  p must be aligned to V * sizeof(T).
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    static constexpr int kDtype = OXQ_F32;
+    __device__ static __forceinline__ float to_f32(float v) { return v; }
+    __device__ static __forceinline__ float from_f32(float v) { return v; }
+};
+template <> struct Elem<__nv_bfloat16> {
+    static constexpr int kDtype = OXQ_BF16;
+    __device__ static __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+    __device__ static __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+};
+template <> struct Elem<__half> {
+    static constexpr int kDtype = OXQ_F16;
+    __device__ static __forceinline__ float to_f32(__half v) { return __half2float(v); }
+    __device__ static __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
+};
+
+// 16-byte vector of T
+template <typename T> struct alignas(16) Vec16 {
+    static constexpr int N = 16 / sizeof(T);
+    T v[N];
+};
+
+template <typename T>
+__device__ __forceinline__ Vec16<T> ld16(const T* p) {
+    Vec16<T> r;
+    *reinterpret_cast<uint4*>(&r) = __ldg(reinterpret_cast<const uint4*>(p));
+    return r;
+}
+// streaming variant: data that is read exactly once should not displace what must stay in L2
+template <typename T>
+__device__ __forceinline__ Vec16<T> ld16_stream(const T* p) {
+    Vec16<T> r;
+    uint4 u;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(p));
+    *reinterpret_cast<uint4*>(&r) = u;
+    return r;
+}
+
+__device__ __forceinline__ float round_mode(float v, int rounding) {
+    // HALF_EVEN: rintf (cvt.rni).  HALF_AWAY: roundf, the reference's f32::round.
+    return rounding == OXQ_ROUND_HALF_AWAY ? roundf(v) : rintf(v);
+}
+
+// two f32 -> two E4M3 bytes (RNE, satfinite); `lo` lands in bits [0,8)
+__device__ __forceinline__ uint16_t cvt_e4m3x2(float lo, float hi) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// two f32 -> two E2M1 nibbles in one byte (RNE, satfinite); `lo` lands in bits [0,4)
+__device__ __forceinline__ uint8_t cvt_e2m1x2(float lo, float hi) {
+    uint16_t r;
+    asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }" : "=h"(r) : "f"(hi), "f"(lo));
+    return (uint8_t)r;
+}
+__device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
+    uint32_t h2;
+    uint16_t in = b;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(in));
+    return __half2float(__ushort_as_half((unsigned short)(h2 & 0xFFFFu)));
+}
+__device__ __forceinline__ float e2m1_to_f32(uint32_t nib) {
+    // {0, .5, 1, 1.5, 2, 3, 4, 6} with sign bit 3
+    uint32_t e = (nib >> 1) & 3u, m = nib & 1u;
+    float v = e == 0 ? 0.5f * (float)m : (1.0f + 0.5f * (float)m) * (float)(1u << (e - 1));
+    return (nib & 8u) ? -v : v;
+}
+// exact 2^e for e in [-127, 127]
+__device__ __forceinline__ float pow2_of(int e) {
+    return e >= -126 ? __uint_as_float((uint32_t)(e + 127) << 23) : __uint_as_float(0x00400000u);
+}
+
+// offset of scale factor (row r, sf column c) in the tiled order consumed by the tensor-core scale
+// loads: tiles of 128 rows x 4 columns (512 bytes), tile order row-tile major; inside a tile the
+// byte of (r, c) sits at (r % 32) * 16 + (r % 128) / 32 * 4 + c % 4.
+__host__ __device__ __forceinline__ size_t sf_mma_offset(int64_t r, int64_t c, int64_t sf_cols) {
+    int64_t col_tiles = (sf_cols + 3) / 4;
+    return (size_t)(((r >> 7) * col_tiles + (c >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (c & 3));
+}
+
+}  // namespace oxq

@@ -1,0 +1,345 @@
+// Decode-shaped (M <= 32) quantized GEMMs.  These are HBM-bound: the weight matrix is streamed once
+// with 128-bit loads, unpacked in registers, and multiplied against an activation tile that lives in
+// shared memory.
+//
+//   W4A16: uint4 codes -> bf16 in registers with the (0x4300 | nibble) trick, exact zero-point
+//          subtraction in bf16, mma.sync m16n8k16 with the weights as the row operand, per-group f32
+//          scale applied to the group's partial sum.  Split along K across CTAs; partial sums are
+//          combined with f32 atomics in a caller-provided workspace that the last CTA drains.
+//   W8A32: int8 codes -> f32, plain FMAs (the benchmark's CPU-runnable configuration).
+#include "oxq_common.cuh"
+
+namespace oxq {
+namespace decode {
+
+// ------------------------------------------------------------------------------------------------
+// W4A16
+// ------------------------------------------------------------------------------------------------
+
+constexpr int W4_ROWS_PER_CTA = 128;   // 8 warps x 16 weight rows
+constexpr int W4_THREADS = 256;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
+    uint4 u;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(p));
+    return u;
+}
+
+struct W4Params {
+    int m, n, k, group;
+    int kc;                      // K elements per split (multiple of 128)
+    int splits;
+    const __nv_bfloat16* x;      // [m x k]
+    const uint32_t* codes;       // [n x k/8]
+    const uint16_t* scales;      // f16 [n x k/group]
+    const uint32_t* zeros;       // packed, linear group order
+    __nv_bfloat16* y;            // [m x n]
+    float* ws;                   // [m x n] f32 partial sums, zero on entry and on exit
+    int* counters;               // [ceil(n/128)], zero on entry and on exit
+};
+
+// NT = number of 8-wide batch tiles (M padded to 8*NT).
+//
+// K order inside one MMA is free as long as both operands agree, so each thread feeds the MMA the
+// codes of its own 16-byte load: word i of the load (8 consecutive K) supplies MMAs 2i and 2i+1, and
+// the activation tile is stored in shared memory already permuted to match (see stage_x).
+template <int NT>
+__global__ void __launch_bounds__(W4_THREADS) w4a16_decode_kernel(const W4Params p) {
+    extern __shared__ uint4 xs[];                       // [kc/128][4][NT][32] uint4
+    __shared__ int s_last;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.y;
+    const int k0 = split * p.kc;
+    const int k1 = min(p.k, k0 + p.kc);
+    const int spans = (k1 - k0) >> 7;
+
+    // ---- stage the activation chunk, permuted into B-fragment order ---------------------------
+    // One item = 8 consecutive K of one batch row.  Destination: for K offset o inside the chunk,
+    // span = o/128, t' = (o%128)/32, i = (o%32)/8; u32 q of the uint4 holds (x[q], x[q+4]).
+    const int items = NT * 8 * (spans * 16);
+    for (int it = tid; it < items; it += W4_THREADS) {
+        const int mrow = it / (spans * 16), o8 = it - mrow * (spans * 16);
+        const int span = o8 >> 4, tt = (o8 >> 2) & 3, i = o8 & 3;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (mrow < p.m) v = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)mrow * p.k + k0 + o8 * 8));
+        const uint32_t lo[4] = {v.x & 0xFFFFu, v.x >> 16, v.y & 0xFFFFu, v.y >> 16};
+        const uint32_t hi[4] = {v.z & 0xFFFFu, v.z >> 16, v.w & 0xFFFFu, v.w >> 16};
+        uint4 o;
+        o.x = lo[0] | (hi[0] << 16); o.y = lo[1] | (hi[1] << 16); o.z = lo[2] | (hi[2] << 16); o.w = lo[3] | (hi[3] << 16);
+        const int nt = mrow >> 3, gg = mrow & 7;
+        xs[((span * 4 + i) * NT + nt) * 32 + gg * 4 + tt] = o;
+    }
+    __syncthreads();
+
+    // ---- stream the weights -------------------------------------------------------------------
+    const int row_a = blockIdx.x * W4_ROWS_PER_CTA + warp * 16 + g, row_b = row_a + 8;
+    const bool va = row_a < p.n, vb = row_b < p.n;
+    const int wpr = p.k >> 3;                            // u32 words per weight row
+    const int gpr = p.k / p.group;
+    const uint32_t* ca = p.codes + (size_t)(va ? row_a : 0) * wpr + ((k0 + 32 * t) >> 3);
+    const uint32_t* cb = p.codes + (size_t)(vb ? row_b : 0) * wpr + ((k0 + 32 * t) >> 3);
+
+    float total[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) { total[nt][0] = total[nt][1] = total[nt][2] = total[nt][3] = 0.0f; }
+
+    uint4 wa = make_uint4(0, 0, 0, 0), wb = wa;
+    if (spans > 0) { if (va) wa = ld_stream_u4(ca); if (vb) wb = ld_stream_u4(cb); }
+    for (int s = 0; s < spans; s++) {
+        uint4 na = make_uint4(0, 0, 0, 0), nb = na;
+        if (s + 1 < spans) { if (va) na = ld_stream_u4(ca + (s + 1) * 16); if (vb) nb = ld_stream_u4(cb + (s + 1) * 16); }
+        // group parameters of this 128-wide span
+        const int kg = (k0 + s * 128) / p.group;
+        float sa = 0.0f, sb = 0.0f;
+        uint32_t za = 0, zb = 0;
+        if (va) {
+            const int gi = row_a * gpr + kg;
+            sa = __half2float(__ushort_as_half(__ldg(p.scales + gi)));
+            za = (__ldg(p.zeros + (gi >> 3)) >> ((gi & 7) * 4)) & 0xFu;
+        }
+        if (vb) {
+            const int gi = row_b * gpr + kg;
+            sb = __half2float(__ushort_as_half(__ldg(p.scales + gi)));
+            zb = (__ldg(p.zeros + (gi >> 3)) >> ((gi & 7) * 4)) & 0xFu;
+        }
+        const uint32_t zma = 0x43004300u | za | (za << 16), zmb = 0x43004300u | zb | (zb << 16);   // bf16x2 (128 + zp)
+        float part[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) { part[nt][0] = part[nt][1] = part[nt][2] = part[nt][3] = 0.0f; }
+        const uint32_t wwa[4] = {wa.x, wa.y, wa.z, wa.w}, wwb[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint32_t ra[4], rb[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                // bf16 0x4300 | c == 128 + c exactly; subtracting 128 + zp is exact as well
+                ra[q] = bf16x2_sub(((wwa[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u, zma);
+                rb[q] = bf16x2_sub(((wwb[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u, zmb);
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                const uint4 b = xs[((s * 4 + i) * NT + nt) * 32 + lane];
+                mma_bf16_16816(part[nt], ra[0], rb[0], ra[1], rb[1], b.x, b.y);
+                mma_bf16_16816(part[nt], ra[2], rb[2], ra[3], rb[3], b.z, b.w);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            total[nt][0] = fmaf(sa, part[nt][0], total[nt][0]);
+            total[nt][1] = fmaf(sa, part[nt][1], total[nt][1]);
+            total[nt][2] = fmaf(sb, part[nt][2], total[nt][2]);
+            total[nt][3] = fmaf(sb, part[nt][3], total[nt][3]);
+        }
+        wa = na; wb = nb;
+    }
+
+    // ---- combine --------------------------------------------------------------------------------
+    // accumulator element e of tile nt: weight row (e < 2 ? row_a : row_b), batch row nt*8 + 2t + (e & 1)
+    if (p.splits == 1) {
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int mrow = nt * 8 + 2 * t + (e & 1), nrow = e < 2 ? row_a : row_b;
+                if (mrow < p.m && nrow < p.n) p.y[(size_t)mrow * p.n + nrow] = __float2bfloat16_rn(total[nt][e]);
+            }
+        return;
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int mrow = nt * 8 + 2 * t + (e & 1), nrow = e < 2 ? row_a : row_b;
+            if (mrow < p.m && nrow < p.n) atomicAdd(p.ws + (size_t)mrow * p.n + nrow, total[nt][e]);
+        }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(p.counters + blockIdx.x, 1) == p.splits - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // last CTA of this row block: convert the sums and leave the workspace zeroed for the next call
+    const int n_lo = blockIdx.x * W4_ROWS_PER_CTA;
+    const int ncols = min(W4_ROWS_PER_CTA, p.n - n_lo);
+    for (int idx = tid; idx < p.m * ncols; idx += W4_THREADS) {
+        const int mrow = idx / ncols, c = idx - mrow * ncols;
+        float* w = p.ws + (size_t)mrow * p.n + n_lo + c;
+        p.y[(size_t)mrow * p.n + n_lo + c] = __float2bfloat16_rn(__ldcg(w));
+        __stcg(w, 0.0f);
+    }
+    if (tid == 0) p.counters[blockIdx.x] = 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// W8A32
+// ------------------------------------------------------------------------------------------------
+
+constexpr int W8_MT = 8;            // batch rows per pass
+constexpr int W8_KC = 1024;         // K elements staged per pass
+constexpr int W8_RPW = 2;           // weight rows per warp
+
+// Shared-memory order of the activation chunk: for each 512-wide block, [q][lane] float4 with
+// k = block*512 + lane*16 + 4q, so a lane's four float4 reads are conflict-free.
+__global__ void __launch_bounds__(256) w8a32_decode_kernel(const float* __restrict__ x, const int8_t* __restrict__ w,
+                                                           const float* __restrict__ sw, float* __restrict__ y,
+                                                           int m, int n, int k) {
+    __shared__ float4 xs[W8_MT][W8_KC / 4];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.y * W8_MT;
+    const int row0 = (blockIdx.x * 8 + warp) * W8_RPW;
+    float acc[W8_RPW][W8_MT];
+#pragma unroll
+    for (int r = 0; r < W8_RPW; r++)
+#pragma unroll
+        for (int j = 0; j < W8_MT; j++) acc[r][j] = 0.0f;
+
+    for (int kc0 = 0; kc0 < k; kc0 += W8_KC) {
+        const int kc = min(W8_KC, k - kc0);
+        __syncthreads();
+        for (int it = tid; it < W8_MT * (W8_KC / 4); it += 256) {
+            const int j = it / (W8_KC / 4), f = it - j * (W8_KC / 4);      // f: float4 index inside the chunk
+            const int kk = f * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (m0 + j < m && kk < kc) v = __ldg(reinterpret_cast<const float4*>(x + (size_t)(m0 + j) * k + kc0 + kk));
+            const int blk = kk >> 9, in = kk & 511, ln = in >> 4, q = (in & 15) >> 2;
+            xs[j][blk * 128 + q * 32 + ln] = v;
+        }
+        __syncthreads();
+        for (int kb = 0; kb * 512 < kc; kb++) {
+            const int koff = kc0 + kb * 512 + lane * 16;
+            uint4 wv[W8_RPW];
+#pragma unroll
+            for (int r = 0; r < W8_RPW; r++) {
+                wv[r] = make_uint4(0, 0, 0, 0);
+                if (row0 + r < n && koff < k) wv[r] = ld_stream_u4(w + (size_t)(row0 + r) * k + koff);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                float wf[W8_RPW][4];
+#pragma unroll
+                for (int r = 0; r < W8_RPW; r++) {
+                    const uint32_t u = q == 0 ? wv[r].x : (q == 1 ? wv[r].y : (q == 2 ? wv[r].z : wv[r].w));
+                    wf[r][0] = (float)(int8_t)(u & 0xFF); wf[r][1] = (float)(int8_t)((u >> 8) & 0xFF);
+                    wf[r][2] = (float)(int8_t)((u >> 16) & 0xFF); wf[r][3] = (float)(int8_t)(u >> 24);
+                }
+#pragma unroll
+                for (int j = 0; j < W8_MT; j++) {
+                    const float4 xv = xs[j][kb * 128 + q * 32 + lane];
+#pragma unroll
+                    for (int r = 0; r < W8_RPW; r++) {
+                        acc[r][j] = fmaf(wf[r][0], xv.x, acc[r][j]);
+                        acc[r][j] = fmaf(wf[r][1], xv.y, acc[r][j]);
+                        acc[r][j] = fmaf(wf[r][2], xv.z, acc[r][j]);
+                        acc[r][j] = fmaf(wf[r][3], xv.w, acc[r][j]);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < W8_RPW; r++)
+#pragma unroll
+        for (int j = 0; j < W8_MT; j++) {
+            float v = acc[r][j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && row0 + r < n && m0 + j < m) y[(size_t)(m0 + j) * n + row0 + r] = v * __ldg(sw + row0 + r);
+        }
+}
+
+}  // namespace decode
+}  // namespace oxq
+
+using namespace oxq::decode;
+
+extern "C" {
+
+size_t oxq_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+    (void)k;
+    if (m <= 0 || n <= 0) return 0;
+    size_t f = (size_t)m * (size_t)n * sizeof(float);
+    f = (f + 255) & ~(size_t)255;
+    return f + (((size_t)(n + W4_ROWS_PER_CTA - 1) / W4_ROWS_PER_CTA) * sizeof(int) + 255 & ~(size_t)255);
+}
+
+int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, const uint32_t* codes, const uint16_t* scales,
+                       const uint32_t* zeros, int group, void* y, void* ws, size_t ws_bytes) {
+    OXQ_CHECK_HANDLE(h);
+    if (m <= 0 || n <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "GEMM dimensions must be non-zero");
+    if (!x || !codes || !scales || !zeros || !y) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
+    // Int4GemmConfig::validate: K % 8 == 0, group in {32,64,128,256} (crates/oxicuda-blas/src/precision/int_ops.rs:250-281)
+    if (k % 8 != 0) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "K must be a multiple of 8 for INT4 packing, got %lld", (long long)k);
+    if (!(group == 32 || group == 64 || group == 128 || group == 256)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "group size %d not in {32,64,128,256}", group);
+    if (k % group != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "k %lld is not divisible by group size %d", (long long)k, group);
+    if (m > 32) OXQ_FAIL(h, OXQ_ERR_UNSUPPORTED_OPERATION, "oxq_gemm_w4a16 covers decode shapes (m <= 32), got m = %lld", (long long)m);
+    if (group % 128 != 0 || k % 128 != 0) OXQ_FAIL(h, OXQ_ERR_UNSUPPORTED_OPERATION, "decode kernel needs group and k to be multiples of 128");
+    if (((uintptr_t)x & 15u) || ((uintptr_t)codes & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "x and codes must be 16-byte aligned");
+    if (n > (int64_t)INT32_MAX / 64 || k > INT32_MAX / 64) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "dimension too large");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+
+    const int row_blocks = (int)((n + W4_ROWS_PER_CTA - 1) / W4_ROWS_PER_CTA);
+    const int nt = (int)((m + 7) / 8);
+    // Split K so that about two CTAs per SM are in flight, each with at least 256 and at most 1024 K.
+    const int spans_total = (int)(k / 128);
+    int splits = (2 * h->sm_count + row_blocks - 1) / row_blocks;
+    int max_splits = spans_total / 2 > 0 ? spans_total / 2 : 1;
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    int spans_per = (spans_total + splits - 1) / splits;
+    if (spans_per > 8) spans_per = 8;
+    splits = (spans_total + spans_per - 1) / spans_per;
+
+    W4Params p;
+    p.m = (int)m; p.n = (int)n; p.k = (int)k; p.group = group; p.kc = spans_per * 128; p.splits = splits;
+    p.x = (const __nv_bfloat16*)x; p.codes = codes; p.scales = scales; p.zeros = zeros; p.y = (__nv_bfloat16*)y;
+    p.ws = nullptr; p.counters = nullptr;
+    if (splits > 1) {
+        const size_t need = oxq_gemm_w4a16_workspace_bytes(m, n, k);
+        if (!ws || ws_bytes < need || ((uintptr_t)ws & 255u))
+            OXQ_FAIL(h, OXQ_ERR_BUFFER_TOO_SMALL, "workspace: expected at least %zu bytes (256-byte aligned), got %zu", need, ws_bytes);
+        size_t f = ((size_t)m * (size_t)n * sizeof(float) + 255) & ~(size_t)255;
+        p.ws = (float*)ws;
+        p.counters = (int*)((char*)ws + f);
+    }
+    const size_t smem = (size_t)spans_per * 4 * nt * 32 * sizeof(uint4);
+    dim3 grid(row_blocks, splits);
+#define LAUNCH_NT(NTV)                                                                                              \
+    do {                                                                                                            \
+        static bool attr = false;                                                                                   \
+        if (!attr) { OXQ_CUDA(h, cudaFuncSetAttribute(w4a16_decode_kernel<NTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 4 * NTV * 32 * 16)); attr = true; } \
+        w4a16_decode_kernel<NTV><<<grid, W4_THREADS, smem, h->stream>>>(p);                                          \
+    } while (0)
+    switch (nt) {
+        case 1: LAUNCH_NT(1); break;
+        case 2: LAUNCH_NT(2); break;
+        case 3: LAUNCH_NT(3); break;
+        default: LAUNCH_NT(4); break;
+    }
+#undef LAUNCH_NT
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_gemm_w8a32(oxq_handle* h, int64_t m, int64_t n, int64_t k, const float* x, const int8_t* w, const float* sw, float* y) {
+    OXQ_CHECK_HANDLE(h);
+    if (m <= 0 || n <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "GEMM dimensions must be non-zero");
+    if (!x || !w || !sw || !y) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
+    if ((k & 15) || ((uintptr_t)x & 15u) || ((uintptr_t)w & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k must be a multiple of 16 and x, w 16-byte aligned");
+    if (m > 64) OXQ_FAIL(h, OXQ_ERR_UNSUPPORTED_OPERATION, "oxq_gemm_w8a32 covers decode shapes (m <= 64), got m = %lld", (long long)m);
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    dim3 grid((unsigned)((n + 8 * W8_RPW - 1) / (8 * W8_RPW)), (unsigned)((m + W8_MT - 1) / W8_MT));
+    w8a32_decode_kernel<<<grid, 256, 0, h->stream>>>(x, w, sw, y, (int)m, (int)n, (int)k);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+}  // extern "C"

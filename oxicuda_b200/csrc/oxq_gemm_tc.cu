@@ -1,0 +1,360 @@
+// Prefill-shaped low-precision GEMMs on the sm_100a tensor cores.
+//
+// One persistent, warp-specialised kernel template: a TMA producer warp streams 128-byte-swizzled
+// operand tiles into a shared-memory ring, one thread issues tcgen05.mma with the accumulator in
+// tensor memory (two accumulator buffers, so the epilogue of tile i overlaps the main loop of tile
+// i+1), and four epilogue warps drain tensor memory with tcgen05.ld, apply the scales and store bf16.
+// Block-scaled kinds additionally stream scale-factor chunks (bulk copies) and move them into
+// tensor memory with tcgen05.cp before each group of MMAs.
+//
+//   Y[M x N] = X[M x K] * W[N x K]^T, both operands K-contiguous ("K-major"), f32 / s32 accumulate.
+#include "oxq_common.cuh"
+#include "oxq_tc.cuh"
+
+namespace oxq {
+namespace tc {
+
+enum { KIND_F8 = 0, KIND_I8 = 1, KIND_MXF8 = 2, KIND_NVF4 = 3 };
+
+constexpr int BM = 128;               // rows of X per tile == tensor-memory lanes
+constexpr int BKB = 128;              // bytes of K per stage == one swizzle atom
+constexpr int NUM_THREADS = 192;      // warp 0: TMA, warp 1: MMA + tensor-memory owner, warps 2-5: epilogue
+constexpr int SMEM_BUDGET = 227 * 1024;
+
+struct GemmParams {
+    int m, n, k_bytes;                // k_bytes: bytes of K per operand row (K for 8-bit, K/2 for 4-bit)
+    void* y; int64_t ldy;             // bf16 output
+    const float* s0; const float* s1; // epilogue scales (meaning depends on the kind)
+    const uint8_t* sfa; const uint8_t* sfb;   // tiled scale factors (block-scaled kinds)
+    int sf_col_tiles;                 // 4-column scale-factor tiles per row tile
+    int sfa_row_tiles, sfb_row_tiles;
+    int32_t* status;
+};
+
+template <int KIND, int BN>
+struct Cfg {
+    static constexpr bool kScaled = KIND == KIND_MXF8 || KIND == KIND_NVF4;
+    // scale-factor chunks (128 rows x 4 scale columns, 512 bytes) per stage and operand row tile
+    static constexpr int kSfChunks = KIND == KIND_MXF8 ? 1 : (KIND == KIND_NVF4 ? 4 : 0);
+    static constexpr int kSfaBytes = kSfChunks * 512;
+    static constexpr int kSfbBytes = kScaled ? 2 * kSfChunks * 512 : 0;   // two 128-row tiles cover BN <= 256
+    static constexpr int kABytes = BM * BKB;
+    static constexpr int kBBytes = BN * BKB;
+    static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+    static constexpr int kStages = (SMEM_BUDGET - 2048) / kStageBytes > 8 ? 8 : (SMEM_BUDGET - 2048) / kStageBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 2048;        // + alignment slack and barriers
+    // tensor-memory columns: two accumulators, then scale factors
+    static constexpr int kAccStride = BN == 192 ? 256 : BN;
+    static constexpr int kSfaCol = BN == 256 ? 0 : (BN == 192 ? 448 : 256);   // unused when BN == 256
+    static constexpr int kSfbCol = kSfaCol + 4 * kSfChunks;
+    static_assert(!kScaled || BN != 256, "block-scaled kinds need tensor-memory columns for scale factors");
+    static_assert(!kScaled || kSfbCol + 8 * kSfChunks <= 512, "tensor memory overflow");
+};
+
+template <int KIND, int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
+    using C = Cfg<KIND, BN>;
+    constexpr int S = C::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sm_a = base;
+    const uint32_t sm_b = sm_a + S * C::kABytes;
+    const uint32_t sm_sfa = sm_b + S * C::kBBytes;
+    const uint32_t sm_sfb = sm_sfa + S * C::kSfaBytes;
+    const uint32_t sm_bar = sm_sfb + S * C::kSfbBytes;           // 8-byte aligned (all sizes are multiples of 512)
+    const uint32_t bar_full = sm_bar, bar_empty = sm_bar + 8 * S;
+    const uint32_t bar_tfull = sm_bar + 16 * S, bar_tempty = bar_tfull + 16;
+    const uint32_t tmem_slot = bar_tempty + 16;
+    uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (p.m + BM - 1) / BM, tiles_n = (p.n + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (p.k_bytes + BKB - 1) / BKB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 4); }
+        fence_barrier_init();
+        prefetch_tmap(&tm_a);
+        prefetch_tmap(&tm_b);
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (one lane)
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                    const uint32_t full = bar_full + 8 * stage;
+                    uint32_t bytes = C::kABytes + C::kBBytes;
+                    if (C::kScaled) {
+                        bytes += C::kSfaBytes;
+                        const int rt0 = n0 >> 7;
+                        bytes += (rt0 < p.sfb_row_tiles ? C::kSfaBytes : 0) + (rt0 + 1 < p.sfb_row_tiles ? C::kSfaBytes : 0);
+                    }
+                    mbar_arrive_expect_tx(full, bytes);
+                    tma_load_2d(sm_a + stage * C::kABytes, &tm_a, kb * BKB, m0, full);
+                    tma_load_2d(sm_b + stage * C::kBBytes, &tm_b, kb * BKB, n0, full);
+                    if (C::kScaled) {
+                        const size_t col_off = (size_t)kb * C::kSfaBytes;
+                        const size_t row_stride = (size_t)p.sf_col_tiles * 512;
+                        bulk_load(sm_sfa + stage * C::kSfaBytes, p.sfa + (size_t)(m0 >> 7) * row_stride + col_off, C::kSfaBytes, full);
+                        const int rt0 = n0 >> 7;
+                        if (rt0 < p.sfb_row_tiles)
+                            bulk_load(sm_sfb + stage * C::kSfbBytes, p.sfb + (size_t)rt0 * row_stride + col_off, C::kSfaBytes, full);
+                        if (rt0 + 1 < p.sfb_row_tiles)
+                            bulk_load(sm_sfb + stage * C::kSfbBytes + C::kSfaBytes, p.sfb + (size_t)(rt0 + 1) * row_stride + col_off, C::kSfaBytes, full);
+                    }
+                    if (++stage == S) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (one lane)
+        if (lane == 0) {
+            constexpr uint32_t idesc =
+                KIND == KIND_F8 ? idesc_dense(1, 0, 0, BM, BN) :
+                KIND == KIND_I8 ? idesc_dense(2, 1, 1, BM, BN) :
+                KIND == KIND_MXF8 ? idesc_block_scaled(0, 0, 1, BM, BN) : idesc_block_scaled(1, 1, 0, BM, BN);
+            int stage = 0; uint32_t phase = 0;
+            int acc = 0; uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int n0 = (tile / tiles_m) * BN;
+                if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * C::kAccStride;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(bar_full + 8 * stage, phase)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                    tc_fence_after();
+                    const uint64_t adesc = smem_desc_sw128(sm_a + stage * C::kABytes);
+                    const uint64_t bdesc = smem_desc_sw128(sm_b + stage * C::kBBytes);
+                    if (C::kScaled) {
+#pragma unroll
+                        for (int c = 0; c < C::kSfChunks; c++) {
+                            tc_cp_32x128b_warpx4(tmem_base + C::kSfaCol + 4 * c, smem_desc_sf(sm_sfa + stage * C::kSfaBytes + c * 512));
+                            // B scale factors: per K chunk, the two 128-row tiles side by side (8 columns = 256 rows)
+                            tc_cp_32x128b_warpx4(tmem_base + C::kSfbCol + 8 * c, smem_desc_sf(sm_sfb + stage * C::kSfbBytes + c * 512));
+                            tc_cp_32x128b_warpx4(tmem_base + C::kSfbCol + 8 * c + 4,
+                                                 smem_desc_sf(sm_sfb + stage * C::kSfbBytes + C::kSfaBytes + c * 512));
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < BKB / 32; k++) {
+                        // each MMA consumes 32 bytes of K: advance the start-address field by 32 >> 4
+                        const uint64_t a = adesc + (uint64_t)(k * 2), b = bdesc + (uint64_t)(k * 2);
+                        const uint32_t accum = (kb | k) != 0;
+                        if (KIND == KIND_F8) mma_f8f6f4(d_tmem, a, b, idesc, accum);
+                        else if (KIND == KIND_I8) mma_i8(d_tmem, a, b, idesc, accum);
+                        else {
+                            // tile rows [n0, n0+BN) start (n0 % 128) / 32 row-groups into the first scale-factor tile
+                            const uint32_t sfb_shift = (uint32_t)(n0 & 127) >> 5;
+                            if (KIND == KIND_MXF8) {
+                                // one scale per row and MMA: byte k of the chunk's 32-bit words
+                                mma_mxf8f6f4(d_tmem, a, b, idesc_with_sf_ids(idesc, k, k), accum,
+                                             tmem_base + C::kSfaCol, tmem_base + C::kSfbCol + sfb_shift);
+                            } else {
+                                // four scales per row and MMA: chunk k, all four bytes
+                                mma_mxf4nvf4_x4(d_tmem, a, b, idesc, accum,
+                                                tmem_base + C::kSfaCol + 4 * k, tmem_base + C::kSfbCol + 8 * k + sfb_shift);
+                            }
+                        }
+                    }
+                    tc_commit(bar_empty + 8 * stage);            // frees the stage once these MMAs have read it
+                    if (++stage == S) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                tc_commit(bar_tfull + 8 * acc);                  // accumulator complete
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (4 warps)
+        const int quarter = warp & 3;                            // tensor-memory lanes [32*quarter, +32)
+        int acc = 0; uint32_t acc_phase = 0;
+        float tensor_scale = 1.0f;
+        if (KIND == KIND_F8 || KIND == KIND_NVF4) tensor_scale = __ldg(p.s0) * __ldg(p.s1);
+        __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y);
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+            const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+            bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+            tc_fence_after();
+            const int row = m0 + quarter * 32 + lane;
+            float row_scale = 1.0f;
+            if (KIND == KIND_I8 && row < p.m) row_scale = __ldg(p.s0 + row);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * C::kAccStride + c * 32, r);
+                tmem_ld_wait();
+                const int col0 = n0 + c * 32;
+                if (row < p.m && col0 < p.n) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        if (KIND == KIND_I8) v[j] = (float)(int)r[j] * (row_scale * (col0 + j < p.n ? __ldg(p.s1 + col0 + j) : 0.0f));
+                        else v[j] = __uint_as_float(r[j]) * tensor_scale;
+                    }
+                    __nv_bfloat16* dst = y + (size_t)row * p.ldy + col0;
+                    if (col0 + 32 <= p.n) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            uint4 o;
+                            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
+                            __nv_bfloat162 t1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+                            __nv_bfloat162 t3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                            o.x = *reinterpret_cast<uint32_t*>(&t0); o.y = *reinterpret_cast<uint32_t*>(&t1);
+                            o.z = *reinterpret_cast<uint32_t*>(&t2); o.w = *reinterpret_cast<uint32_t*>(&t3);
+                            *reinterpret_cast<uint4*>(dst + 8 * j) = o;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < p.n; j++) dst[j] = __float2bfloat16_rn(v[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    // Teardown.  On the normal path the epilogue has seen the last accumulator complete, so every
+    // MMA has finished and every TMA load has landed before tensor memory is released.
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// Row-major byte matrix [rows x row_bytes] with leading dimension ld_bytes, tiles of box_rows x 128 bytes.
+static bool make_tmap_bytes(CUtensorMap* tm, const void* ptr, int64_t rows, int64_t row_bytes, int64_t ld_bytes, int box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)BKB, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int KIND, int BN>
+static int32_t launch(oxq_handle* h, const void* x, int64_t ldx_bytes, const void* w, int64_t ldw_bytes, GemmParams p) {
+    using C = Cfg<KIND, BN>;
+    CUtensorMap tm_a, tm_b;
+    if (!make_tmap_bytes(&tm_a, x, p.m, p.k_bytes, ldx_bytes, BM) || !make_tmap_bytes(&tm_b, w, p.n, p.k_bytes, ldw_bytes, BN))
+        OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned, leading dimensions multiples of 16 bytes)");
+    static bool attr_set = false;
+    if (!attr_set) {
+        OXQ_CUDA(h, cudaFuncSetAttribute(gemm_tc_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+        attr_set = true;
+    }
+    const int tiles = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
+    const int grid = tiles < h->sm_count ? tiles : h->sm_count;
+    p.status = h->dev_status;
+    gemm_tc_kernel<KIND, BN><<<grid, NUM_THREADS, C::kSmemBytes, h->stream>>>(tm_a, tm_b, p);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+static int32_t check_gemm_args(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, const void* w, const void* y, int64_t ldy) {
+    // gemm(): zero dimensions are errors (crates/oxicuda-blas/src/level3/gemm_api.rs:88-92)
+    if (m <= 0 || n <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "GEMM dimensions must be non-zero");
+    if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "GEMM dimensions exceed 2^31-1");
+    if (!x || !w || !y) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
+    if (((uintptr_t)x & 15u) || ((uintptr_t)w & 15u) || ((uintptr_t)y & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "operands must be 16-byte aligned");
+    if (ldy < n || (ldy & 7)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "ldy must be >= n and a multiple of 8");
+    return oxq_require_sm100(h);
+}
+
+}  // namespace tc
+}  // namespace oxq
+
+using namespace oxq::tc;
+
+extern "C" {
+
+int32_t oxq_gemm_fp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x, int64_t ldx, const uint8_t* w, int64_t ldw,
+                     const float* sx, const float* sw, void* y, int64_t ldy) {
+    OXQ_CHECK_HANDLE(h);
+    if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
+    if (!sx || !sw) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
+    if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
+    GemmParams p{};
+    p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y; p.ldy = ldy; p.s0 = sx; p.s1 = sw;
+    return launch<KIND_F8, 256>(h, x, ldx, w, ldw, p);
+}
+
+int32_t oxq_gemm_w8a8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const int8_t* x, int64_t ldx, const int8_t* w, int64_t ldw,
+                      const float* sx_rows, const float* sw_rows, void* y, int64_t ldy) {
+    OXQ_CHECK_HANDLE(h);
+    if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
+    if (!sx_rows || !sw_rows) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
+    if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
+    GemmParams p{};
+    p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y; p.ldy = ldy; p.s0 = sx_rows; p.s1 = sw_rows;
+    return launch<KIND_I8, 256>(h, x, ldx, w, ldw, p);
+}
+
+int32_t oxq_gemm_mxfp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x, const uint8_t* sfx, const uint8_t* w,
+                       const uint8_t* sfw, void* y, int64_t ldy) {
+    OXQ_CHECK_HANDLE(h);
+    if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
+    if (!sfx || !sfw || ((uintptr_t)sfx & 15u) || ((uintptr_t)sfw & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned scale-factor pointer");
+    if (k & 127) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k must be a multiple of 128 for the MXFP8 GEMM");
+    GemmParams p{};
+    p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y; p.ldy = ldy;
+    p.sfa = sfx; p.sfb = sfw; p.sf_col_tiles = (int)(k / 32 + 3) / 4;
+    p.sfa_row_tiles = (int)((m + 127) / 128); p.sfb_row_tiles = (int)((n + 127) / 128);
+    return launch<KIND_MXF8, 192>(h, x, k, w, k, p);
+}
+
+int32_t oxq_gemm_nvfp4(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x, const uint8_t* sfx, const float* gx,
+                       const uint8_t* w, const uint8_t* sfw, const float* gw, void* y, int64_t ldy) {
+    OXQ_CHECK_HANDLE(h);
+    if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
+    if (!sfx || !sfw || !gx || !gw || ((uintptr_t)sfx & 15u) || ((uintptr_t)sfw & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned scale pointer");
+    if (k & 255) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k must be a multiple of 256 for the NVFP4 GEMM");
+    GemmParams p{};
+    p.m = (int)m; p.n = (int)n; p.k_bytes = (int)(k / 2); p.y = y; p.ldy = ldy; p.s0 = gx; p.s1 = gw;
+    p.sfa = sfx; p.sfb = sfw; p.sf_col_tiles = (int)(k / 16 + 3) / 4;
+    p.sfa_row_tiles = (int)((m + 127) / 128); p.sfb_row_tiles = (int)((n + 127) / 128);
+    return launch<KIND_NVF4, 192>(h, x, k / 2, w, k / 2, p);
+}
+
+}  // extern "C"

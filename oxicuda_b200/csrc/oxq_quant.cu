@@ -1,0 +1,674 @@
+// Memory-bound quantize / dequantize kernels: every element of the input crosses HBM once, with
+// 128-bit coalesced accesses, row or block statistics reduced by warp shuffles, codes packed in
+// registers.  Rounding rules are the ones the CPU oracle states; divisions are IEEE (__fdiv_rn).
+#include "oxq_common.cuh"
+
+namespace oxq {
+
+// ------------------------------------------------------------------------------------------------
+// INT8 symmetric per-row
+// ------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ int quant_i8(float x, float scale, int rounding) {
+    float v = round_mode(__fdiv_rn(x, scale), rounding);
+    if (v != v) return 0;                                   // NaN -> code 0 (Rust `as i32`)
+    return __float2int_rn(fminf(fmaxf(v, -127.0f), 127.0f));
+}
+
+// One CTA per row (grid-stride over rows).  Each thread keeps up to NV float4 of the row in
+// registers, so a row of up to 256*4*NV floats is read from HBM exactly once; longer rows are read
+// a second time for the quantize pass.
+template <int NV>
+__global__ void __launch_bounds__(256) int8_quant_rows_kernel(const float* __restrict__ x, int64_t rows, int64_t cols,
+                                                              int8_t* __restrict__ q, float* __restrict__ scales,
+                                                              int rounding) {
+    __shared__ float s_red[8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t nvec = cols >> 2;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float4* xr = reinterpret_cast<const float4*>(x + row * cols);
+        float4 v[NV];
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            int64_t idx = tid + (int64_t)i * 256;
+            v[i] = idx < nvec ? __ldcs(xr + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+        }
+        for (int64_t idx = tid + (int64_t)NV * 256; idx < nvec; idx += 256) {
+            float4 t = __ldg(xr + idx);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(t.x), fabsf(t.y)), fmaxf(fabsf(t.z), fabsf(t.w))));
+        }
+        amax = warp_max(amax);
+        __syncthreads();                                    // s_red reuse across rows
+        if (lane == 0) s_red[warp] = amax;
+        __syncthreads();
+        amax = s_red[0];
+#pragma unroll
+        for (int w = 1; w < 8; w++) amax = fmaxf(amax, s_red[w]);
+        const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+        if (tid == 0) scales[row] = scale;
+        uint32_t* qr = reinterpret_cast<uint32_t*>(q + row * cols);
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            int64_t idx = tid + (int64_t)i * 256;
+            if (idx < nvec) {
+                uint32_t p = (uint32_t)(quant_i8(v[i].x, scale, rounding) & 0xFF) |
+                             ((uint32_t)(quant_i8(v[i].y, scale, rounding) & 0xFF) << 8) |
+                             ((uint32_t)(quant_i8(v[i].z, scale, rounding) & 0xFF) << 16) |
+                             ((uint32_t)(quant_i8(v[i].w, scale, rounding) & 0xFF) << 24);
+                qr[idx] = p;
+            }
+        }
+        for (int64_t idx = tid + (int64_t)NV * 256; idx < nvec; idx += 256) {
+            float4 t = __ldg(xr + idx);
+            qr[idx] = (uint32_t)(quant_i8(t.x, scale, rounding) & 0xFF) | ((uint32_t)(quant_i8(t.y, scale, rounding) & 0xFF) << 8) |
+                      ((uint32_t)(quant_i8(t.z, scale, rounding) & 0xFF) << 16) | ((uint32_t)(quant_i8(t.w, scale, rounding) & 0xFF) << 24);
+        }
+    }
+}
+
+// Any cols / alignment: scalar accesses.
+__global__ void __launch_bounds__(256) int8_quant_rows_scalar_kernel(const float* __restrict__ x, int64_t rows, int64_t cols,
+                                                                     int8_t* __restrict__ q, float* __restrict__ scales,
+                                                                     int rounding) {
+    __shared__ float s_red[8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float* xr = x + row * cols;
+        float amax = 0.0f;
+        for (int64_t i = tid; i < cols; i += 256) amax = fmaxf(amax, fabsf(xr[i]));
+        amax = warp_max(amax);
+        __syncthreads();
+        if (lane == 0) s_red[warp] = amax;
+        __syncthreads();
+        amax = s_red[0];
+        for (int w = 1; w < 8; w++) amax = fmaxf(amax, s_red[w]);
+        const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+        if (tid == 0) scales[row] = scale;
+        for (int64_t i = tid; i < cols; i += 256) q[row * cols + i] = (int8_t)quant_i8(xr[i], scale, rounding);
+    }
+}
+
+// 16 codes per thread: one 16-byte load, four 16-byte stores.
+__global__ void __launch_bounds__(256) int8_dequant_rows_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales,
+                                                                int64_t rows, int64_t cols, float* __restrict__ y) {
+    const int64_t nchunk = rows * cols / 16;
+    for (int64_t c = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; c < nchunk; c += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t e = c * 16;
+        const float s = __ldg(scales + e / cols);
+        uint4 u = __ldcs(reinterpret_cast<const uint4*>(q + e));
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        float4* yo = reinterpret_cast<float4*>(y + e);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float4 o;
+            o.x = (float)(int8_t)(w[i] & 0xFF) * s;
+            o.y = (float)(int8_t)((w[i] >> 8) & 0xFF) * s;
+            o.z = (float)(int8_t)((w[i] >> 16) & 0xFF) * s;
+            o.w = (float)(int8_t)(w[i] >> 24) * s;
+            __stcs(yo + i, o);
+        }
+    }
+}
+__global__ void __launch_bounds__(256) int8_dequant_rows_scalar_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales,
+                                                                       int64_t rows, int64_t cols, float* __restrict__ y) {
+    const int64_t n = rows * cols;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        y[i] = (float)q[i] * scales[i / cols];
+}
+
+// ------------------------------------------------------------------------------------------------
+// absmax (per tensor)
+// ------------------------------------------------------------------------------------------------
+
+// Each CTA folds a strided slice of the tensor, then one atomicMax per CTA on the bit pattern of
+// the non-negative result (ordering of non-negative floats == ordering of their bits).
+template <typename T>
+__global__ void __launch_bounds__(256) absmax_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ out) {
+    constexpr int V = Vec16<T>::N;
+    __shared__ float s_red[8];
+    const int64_t nvec = n / V;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+    int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+        Vec16<T> a = ld16(x + i * V), b = ld16(x + (i + stride) * V), c = ld16(x + (i + 2 * stride) * V),
+                 d = ld16(x + (i + 3 * stride) * V);
+#pragma unroll
+        for (int j = 0; j < V; j++) {
+            m0 = fmaxf(m0, fabsf(Elem<T>::to_f32(a.v[j])));
+            m1 = fmaxf(m1, fabsf(Elem<T>::to_f32(b.v[j])));
+            m2 = fmaxf(m2, fabsf(Elem<T>::to_f32(c.v[j])));
+            m3 = fmaxf(m3, fabsf(Elem<T>::to_f32(d.v[j])));
+        }
+    }
+    for (; i < nvec; i += stride) {
+        Vec16<T> a = ld16(x + i * V);
+#pragma unroll
+        for (int j = 0; j < V; j++) m0 = fmaxf(m0, fabsf(Elem<T>::to_f32(a.v[j])));
+    }
+    if (blockIdx.x == 0) {
+        for (int64_t t = nvec * V + threadIdx.x; t < n; t += blockDim.x) m1 = fmaxf(m1, fabsf(Elem<T>::to_f32(x[t])));
+    }
+    float m = warp_max(fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++) m = fmaxf(m, s_red[w]);
+        atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(m));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// FP8 E4M3 per tensor
+// ------------------------------------------------------------------------------------------------
+
+// Literal Fp8Codec::fp32_to_fp8 for E4M3 (truncation, |v| >= 256 -> 448, subnormal shift).
+__device__ __forceinline__ uint8_t e4m3_refcompat(float v) {
+    v = fminf(fmaxf(v, -448.0f), 448.0f);
+    uint32_t bits = __float_as_uint(v);
+    uint32_t sign = bits >> 31;
+    int exp32 = (int)((bits >> 23) & 0xFF);
+    uint32_t man32 = bits & 0x007FFFFFu;
+    if (v == 0.0f) return (uint8_t)(sign << 7);
+    int e = exp32 - 127 + 7;
+    if (e <= 0) {
+        uint32_t full = (man32 | 0x00800000u) >> 1;
+        uint32_t shift = (uint32_t)(1 - e) + 20u;
+        if (shift >= 24) return (uint8_t)(sign << 7);
+        return (uint8_t)((sign << 7) | ((full >> shift) & 7u));
+    }
+    if (e >= 15) return (uint8_t)((sign << 7) | 0x7E);
+    return (uint8_t)((sign << 7) | ((uint32_t)e << 3) | ((man32 >> 20) & 7u));
+}
+// Literal Fp8Codec::fp8_to_fp32 for E4M3 (subnormals decode as 2^-6 * (1 + m/8)).
+__device__ __forceinline__ float e4m3_refcompat_decode(uint8_t b) {
+    uint32_t sign = b >> 7, e = (b >> 3) & 0xF, m = b & 7;
+    if (e == 15 && m == 7) return __uint_as_float(0x7FC00000u);
+    if (e == 0) return m == 0 ? __uint_as_float(sign << 31) : __uint_as_float((sign << 31) | (121u << 23) | (m << 20));
+    return __uint_as_float((sign << 31) | ((e + 120u) << 23) | (m << 20));
+}
+
+// 16 elements per thread -> one 16-byte store.  If stats != nullptr the scale is derived from
+// stats[0] (absmax) as absmax/448 (1.0 when absmax == 0) and thread 0 records it in stats[1].
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) fp8_quant_kernel(const T* __restrict__ x, int64_t n, const float* __restrict__ scale_ptr,
+                                                        float* __restrict__ stats, uint8_t* __restrict__ q) {
+    constexpr int V = Vec16<T>::N;
+    constexpr int L = 16 / V;                               // 16-byte loads per thread
+    float scale;
+    if (stats) {
+        float am = stats[0];
+        scale = am > 0.0f ? __fdiv_rn(am, 448.0f) : 1.0f;
+        if (blockIdx.x == 0 && threadIdx.x == 0) stats[1] = scale;
+    } else {
+        scale = __ldg(scale_ptr);
+    }
+    const int64_t nchunk = n / 16;
+    for (int64_t c = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; c < nchunk; c += (int64_t)gridDim.x * blockDim.x) {
+        float f[16];
+#pragma unroll
+        for (int l = 0; l < L; l++) {
+            Vec16<T> a = ld16_stream(x + c * 16 + l * V);
+#pragma unroll
+            for (int j = 0; j < V; j++) f[l * V + j] = __fdiv_rn(Elem<T>::to_f32(a.v[j]), scale);
+        }
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (MODE == OXQ_FP8_SPEC_RNE) {
+                w[i] = (uint32_t)cvt_e4m3x2(f[4 * i], f[4 * i + 1]) | ((uint32_t)cvt_e4m3x2(f[4 * i + 2], f[4 * i + 3]) << 16);
+            } else {
+                w[i] = (uint32_t)e4m3_refcompat(f[4 * i]) | ((uint32_t)e4m3_refcompat(f[4 * i + 1]) << 8) |
+                       ((uint32_t)e4m3_refcompat(f[4 * i + 2]) << 16) | ((uint32_t)e4m3_refcompat(f[4 * i + 3]) << 24);
+            }
+        }
+        __stcs(reinterpret_cast<uint4*>(q + c * 16), make_uint4(w[0], w[1], w[2], w[3]));
+    }
+    if (blockIdx.x == 0) {                                  // ragged tail
+        for (int64_t t = nchunk * 16 + threadIdx.x; t < n; t += blockDim.x) {
+            float f = __fdiv_rn(Elem<T>::to_f32(x[t]), scale);
+            q[t] = MODE == OXQ_FP8_SPEC_RNE ? (uint8_t)(cvt_e4m3x2(f, 0.0f) & 0xFF) : e4m3_refcompat(f);
+        }
+    }
+}
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) fp8_dequant_kernel(const uint8_t* __restrict__ q, int64_t n, const float* __restrict__ scale_ptr,
+                                                          T* __restrict__ y) {
+    const float scale = __ldg(scale_ptr);
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        float v = MODE == OXQ_FP8_SPEC_RNE ? e4m3_to_f32(q[i]) : e4m3_refcompat_decode(q[i]);
+        y[i] = Elem<T>::from_f32(v * scale);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// uint4 group-wise asymmetric with f16 scales
+// ------------------------------------------------------------------------------------------------
+
+// One warp owns 8 consecutive groups (so it also owns one packed zero-point word).  Per group the
+// lanes hold group/32 elements each in 4-element pieces; min/max by shuffles; the four nibbles of a
+// piece are merged with the neighbour lane's so even lanes store whole u32 words.
+template <typename T, int GROUP>
+__global__ void __launch_bounds__(256) int4g_quant_kernel(const T* __restrict__ x, int64_t ngroups, int rounding,
+                                                          uint32_t* __restrict__ codes, uint16_t* __restrict__ scales,
+                                                          uint32_t* __restrict__ zeros) {
+    constexpr int PIECES = GROUP / 128 > 0 ? GROUP / 128 : 1;  // 4-element pieces per lane per group
+    constexpr int ACTIVE = GROUP >= 128 ? 32 : GROUP / 4;      // lanes that hold data
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t g0 = warp * 8; g0 < ngroups; g0 += nwarps * 8) {
+        float v[8][PIECES][4];
+#pragma unroll
+        for (int g = 0; g < 8; g++) {
+#pragma unroll
+            for (int p = 0; p < PIECES; p++) {
+                const int64_t e = (g0 + g) * GROUP + p * 128 + lane * 4;
+                if (g0 + g < ngroups && lane < ACTIVE) {
+                    if (sizeof(T) == 4) {
+                        float4 t = __ldcs(reinterpret_cast<const float4*>(x + e));
+                        v[g][p][0] = t.x; v[g][p][1] = t.y; v[g][p][2] = t.z; v[g][p][3] = t.w;
+                    } else {
+                        uint2 t = __ldcs(reinterpret_cast<const uint2*>(x + e));
+                        const T* h = reinterpret_cast<const T*>(&t);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) v[g][p][j] = Elem<T>::to_f32(h[j]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) v[g][p][j] = 0.0f;
+                }
+            }
+        }
+        uint32_t zword = 0;
+#pragma unroll
+        for (int g = 0; g < 8; g++) {
+            float mn = INFINITY, mx = -INFINITY;
+            if (lane < ACTIVE) {
+#pragma unroll
+                for (int p = 0; p < PIECES; p++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        // NaNs are skipped exactly as `if v < fmin` / `if v > fmax` skip them
+                        mn = fminf(mn, v[g][p][j]);
+                        mx = fmaxf(mx, v[g][p][j]);
+                    }
+            }
+            mn = warp_min(mn);
+            mx = warp_max(mx);
+            float s32 = __fdiv_rn(fmaxf(mx - mn, 1e-8f), 15.0f);
+            __half sh = __float2half_rn(s32);
+            if ((__half_as_ushort(sh) & 0x7FFFu) == 0) sh = __ushort_as_half(1);
+            const float s = __half2float(sh);
+            float zf = roundf(__fdiv_rn(-mn, s));
+            zf = zf != zf ? 0.0f : fminf(fmaxf(zf, 0.0f), 15.0f);
+            const uint32_t zp = (uint32_t)zf;
+            if (g0 + g < ngroups) {
+                zword |= zp << (4 * g);
+                if (lane == 0) scales[g0 + g] = __half_as_ushort(sh);
+#pragma unroll
+                for (int p = 0; p < PIECES; p++) {
+                    uint32_t nib4 = 0;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        float t = round_mode(__fdiv_rn(v[g][p][j], s) + zf, rounding);
+                        t = t != t ? 0.0f : fminf(fmaxf(t, 0.0f), 15.0f);
+                        nib4 |= ((uint32_t)t) << (4 * j);
+                    }
+                    const uint32_t other = __shfl_down_sync(0xffffffffu, nib4, 1);
+                    if ((lane & 1) == 0 && lane < ACTIVE)
+                        codes[((g0 + g) * GROUP + p * 128 + lane * 4) >> 3] = nib4 | (other << 16);
+                }
+            }
+        }
+        if (lane == 0) zeros[g0 >> 3] = zword;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) int4g_dequant_kernel(const uint32_t* __restrict__ codes, const uint16_t* __restrict__ scales,
+                                                            const uint32_t* __restrict__ zeros, int64_t nwords, int group,
+                                                            T* __restrict__ y) {
+    for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < nwords; w += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t gi = (w * 8) / group;
+        const float s = __half2float(__ushort_as_half(scales[gi]));
+        const int zp = (int)((zeros[gi >> 3] >> ((gi & 7) * 4)) & 0xF);
+        const uint32_t c = __ldcs(codes + w);
+        T o[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) o[j] = Elem<T>::from_f32((float)((int)((c >> (4 * j)) & 0xF) - zp) * s);
+        if (sizeof(T) == 4) {
+            float4* yo = reinterpret_cast<float4*>(y + w * 8);
+            yo[0] = *reinterpret_cast<float4*>(&o[0]);
+            yo[1] = *reinterpret_cast<float4*>(&o[4]);
+        } else {
+            *reinterpret_cast<uint4*>(y + w * 8) = *reinterpret_cast<uint4*>(&o[0]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// MXFP8 (E4M3 codes, E8M0 scale per 32) and NVFP4 (E2M1 codes, E4M3 scale per 16, f32 tensor scale)
+// ------------------------------------------------------------------------------------------------
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&f)[8]) {
+    if (sizeof(T) == 4) {
+        float4 a = __ldcs(reinterpret_cast<const float4*>(p)), b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+        uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
+        const T* h = reinterpret_cast<const T*>(&u);
+#pragma unroll
+        for (int j = 0; j < 8; j++) f[j] = Elem<T>::to_f32(h[j]);
+    }
+}
+
+// 8 elements per thread, 4 adjacent lanes form one 32-element block.
+template <typename T>
+__global__ void __launch_bounds__(256) mxfp8_quant_kernel(const T* __restrict__ x, int64_t rows, int64_t k,
+                                                          uint8_t* __restrict__ codes, uint8_t* __restrict__ sf_rm,
+                                                          uint8_t* __restrict__ sf_mma) {
+    const int64_t nthr = rows * k / 8;
+    const int64_t sf_cols = k / 32;
+    const int lane = threadIdx.x & 31;
+    // warp-uniform trip count: the shuffles below need every lane of the warp
+    for (int64_t base = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); base < nthr; base += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = base + lane;
+        const bool valid = t < nthr;
+        float f[8];
+        if (valid) load8(x + t * 8, f);
+        else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) f[j] = 0.0f;
+        }
+        float am = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) am = fmaxf(am, fabsf(f[j]));
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+        if (!valid) continue;
+        int byte = 0;
+        if (am > 0.0f) {
+            const uint32_t b = __float_as_uint(am);
+            const int e = (b >> 23) != 0 ? (int)(b >> 23) - 127 : -118 - __clz(b);   // floor(log2(am))
+            byte = e - 8 + 127;
+            byte = byte < 0 ? 0 : (byte > 254 ? 254 : byte);
+        }
+        const float inv = pow2_of(127 - byte);
+        uint32_t lo = (uint32_t)cvt_e4m3x2(f[0] * inv, f[1] * inv) | ((uint32_t)cvt_e4m3x2(f[2] * inv, f[3] * inv) << 16);
+        uint32_t hi = (uint32_t)cvt_e4m3x2(f[4] * inv, f[5] * inv) | ((uint32_t)cvt_e4m3x2(f[6] * inv, f[7] * inv) << 16);
+        __stcs(reinterpret_cast<uint2*>(codes + t * 8), make_uint2(lo, hi));
+        if ((t & 3) == 0) {
+            const int64_t blk = t >> 2;
+            const int64_t r = blk / sf_cols, c = blk - r * sf_cols;
+            if (sf_rm) sf_rm[blk] = (uint8_t)byte;
+            if (sf_mma) sf_mma[sf_mma_offset(r, c, sf_cols)] = (uint8_t)byte;
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) mxfp8_dequant_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sf_rm,
+                                                            int64_t n, T* __restrict__ y) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        y[i] = Elem<T>::from_f32(e4m3_to_f32(codes[i]) * pow2_of((int)sf_rm[i >> 5] - 127));
+}
+
+// 8 elements per thread, 2 adjacent lanes form one 16-element block.
+template <typename T>
+__global__ void __launch_bounds__(256) nvfp4_quant_kernel(const T* __restrict__ x, int64_t rows, int64_t k, float* __restrict__ stats,
+                                                          uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_rm,
+                                                          uint8_t* __restrict__ sf_mma) {
+    const float tmax = stats[0];
+    const float g = tmax > 0.0f ? __fdiv_rn(tmax, 448.0f * 6.0f) : 1.0f;
+    if (blockIdx.x == 0 && threadIdx.x == 0) stats[1] = g;
+    const float six_g = 6.0f * g;
+    const int64_t nthr = rows * k / 8;
+    const int64_t sf_cols = k / 16;
+    const int lane = threadIdx.x & 31;
+    for (int64_t base = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); base < nthr; base += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = base + lane;
+        const bool valid = t < nthr;
+        float f[8];
+        if (valid) load8(x + t * 8, f);
+        else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) f[j] = 0.0f;
+        }
+        float am = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) am = fmaxf(am, fabsf(f[j]));
+        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+        if (!valid) continue;
+        const uint8_t s8 = (uint8_t)(cvt_e4m3x2(__fdiv_rn(am, six_g), 0.0f) & 0xFF);
+        const float d = g * e4m3_to_f32(s8);
+        uint32_t w = 0;
+        if (s8 == 0) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) w |= ((__float_as_uint(f[j]) >> 28) & 8u) << (4 * j);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j += 2)
+                w |= (uint32_t)cvt_e2m1x2(__fdiv_rn(f[j], d), __fdiv_rn(f[j + 1], d)) << (4 * j);
+        }
+        __stcs(reinterpret_cast<uint32_t*>(packed + t * 4), w);
+        if ((t & 1) == 0) {
+            const int64_t blk = t >> 1;
+            const int64_t r = blk / sf_cols, c = blk - r * sf_cols;
+            if (sf_rm) sf_rm[blk] = s8;
+            if (sf_mma) sf_mma[sf_mma_offset(r, c, sf_cols)] = s8;
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) nvfp4_dequant_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ sf_rm,
+                                                            const float* __restrict__ stats, int64_t n, T* __restrict__ y) {
+    const float g = stats[1];
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint32_t nib = (packed[i >> 1] >> ((i & 1) * 4)) & 0xF;
+        y[i] = Elem<T>::from_f32(e2m1_to_f32(nib) * e4m3_to_f32(sf_rm[i >> 4]) * g);
+    }
+}
+
+static inline int grid_for(oxq_handle* h, int64_t work_items, int block, int ctas_per_sm) {
+    int64_t need = (work_items + block - 1) / block;
+    int64_t cap = (int64_t)h->sm_count * ctas_per_sm;
+    if (need < 1) need = 1;
+    return (int)(need < cap ? need : cap);
+}
+
+}  // namespace oxq
+
+using namespace oxq;
+
+#define DISPATCH_DTYPE(dtype, ...)                                           \
+    switch (dtype) {                                                         \
+        case OXQ_F32: { using T = float; __VA_ARGS__; break; }               \
+        case OXQ_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }      \
+        case OXQ_F16: { using T = __half; __VA_ARGS__; break; }              \
+        default: OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "unknown dtype %d", dtype); \
+    }
+
+static inline bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+static inline size_t dtype_size(int dt) { return dt == OXQ_F32 ? 4 : 2; }
+
+extern "C" {
+
+int32_t oxq_int8_quant_rows(oxq_handle* h, const float* x, int64_t rows, int64_t cols, int8_t* q, float* scales, int rounding) {
+    OXQ_CHECK_HANDLE(h);
+    if (rows <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "calibrate_2d: rows == 0");
+    if (cols <= 0) OXQ_FAIL(h, OXQ_ERR_QUANT_DIMENSION_MISMATCH, "dimension mismatch: expected 1, got 0");
+    if (!x || !q || !scales) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
+    if (rounding != OXQ_ROUND_HALF_EVEN && rounding != OXQ_ROUND_HALF_AWAY) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "rounding %d", rounding);
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    const int grid = (int)(rows < (int64_t)h->sm_count * 32 ? rows : (int64_t)h->sm_count * 32);
+    if ((cols & 3) == 0 && aligned16(x) && (((uintptr_t)q & 3u) == 0)) {
+        if (cols <= 4096) int8_quant_rows_kernel<4><<<grid, 256, 0, h->stream>>>(x, rows, cols, q, scales, rounding);
+        else int8_quant_rows_kernel<8><<<grid, 256, 0, h->stream>>>(x, rows, cols, q, scales, rounding);
+    } else {
+        int8_quant_rows_scalar_kernel<<<grid, 256, 0, h->stream>>>(x, rows, cols, q, scales, rounding);
+    }
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_int8_dequant_rows(oxq_handle* h, const int8_t* q, const float* scales, int64_t rows, int64_t cols, float* y) {
+    OXQ_CHECK_HANDLE(h);
+    if (rows <= 0 || cols <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "dequantize: empty input");
+    if (!y || !q || !scales) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    if ((cols & 15) == 0 && aligned16(q) && aligned16(y))
+        int8_dequant_rows_kernel<<<grid_for(h, rows * cols / 16, 256, 16), 256, 0, h->stream>>>(q, scales, rows, cols, y);
+    else
+        int8_dequant_rows_scalar_kernel<<<grid_for(h, rows * cols, 256, 16), 256, 0, h->stream>>>(q, scales, rows, cols, y);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_absmax(oxq_handle* h, const void* x, int dtype, int64_t n, float* absmax_dev) {
+    OXQ_CHECK_HANDLE(h);
+    if (n <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "absmax: empty input");
+    if (!x || !absmax_dev || !aligned16(x)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    OXQ_CUDA(h, cudaMemsetAsync(absmax_dev, 0, sizeof(float), h->stream));
+    DISPATCH_DTYPE(dtype, absmax_kernel<T><<<grid_for(h, n / Vec16<T>::N / 4 + 1, 256, 8), 256, 0, h->stream>>>((const T*)x, n, absmax_dev));
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+static int32_t fp8_quant_launch(oxq_handle* h, const void* x, int dtype, int64_t n, const float* scale, float* stats, uint8_t* q, int mode) {
+    const int grid = grid_for(h, n / 16 + 1, 256, 16);
+    if (mode == OXQ_FP8_SPEC_RNE) {
+        DISPATCH_DTYPE(dtype, fp8_quant_kernel<T, OXQ_FP8_SPEC_RNE><<<grid, 256, 0, h->stream>>>((const T*)x, n, scale, stats, q));
+    } else if (mode == OXQ_FP8_REFCOMPAT) {
+        DISPATCH_DTYPE(dtype, fp8_quant_kernel<T, OXQ_FP8_REFCOMPAT><<<grid, 256, 0, h->stream>>>((const T*)x, n, scale, stats, q));
+    } else {
+        OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "fp8 mode %d", mode);
+    }
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_fp8_quant(oxq_handle* h, const void* x, int dtype, int64_t n, const float* scale_dev, uint8_t* q, int mode) {
+    OXQ_CHECK_HANDLE(h);
+    if (n <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "fp8 encode: empty input");
+    if (!x || !q || !scale_dev || !aligned16(x) || !aligned16(q)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    return fp8_quant_launch(h, x, dtype, n, scale_dev, nullptr, q, mode);
+}
+
+int32_t oxq_fp8_quant_dynamic(oxq_handle* h, const void* x, int dtype, int64_t n, uint8_t* q, float* stats_dev) {
+    OXQ_CHECK_HANDLE(h);
+    if (n <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "fp8 encode: empty input");
+    if (!x || !q || !stats_dev || !aligned16(x) || !aligned16(q)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (int32_t rc = oxq_absmax(h, x, dtype, n, stats_dev)) return rc;
+    return fp8_quant_launch(h, x, dtype, n, nullptr, stats_dev, q, OXQ_FP8_SPEC_RNE);
+}
+
+int32_t oxq_fp8_dequant(oxq_handle* h, const uint8_t* q, int64_t n, const float* scale_dev, void* y, int y_dtype, int mode) {
+    OXQ_CHECK_HANDLE(h);
+    if (n <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "fp8 decode: empty input");
+    if (!y || !q || !scale_dev) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    const int grid = grid_for(h, n, 256, 16);
+    if (mode == OXQ_FP8_SPEC_RNE) {
+        DISPATCH_DTYPE(y_dtype, fp8_dequant_kernel<T, OXQ_FP8_SPEC_RNE><<<grid, 256, 0, h->stream>>>(q, n, scale_dev, (T*)y));
+    } else {
+        DISPATCH_DTYPE(y_dtype, fp8_dequant_kernel<T, OXQ_FP8_REFCOMPAT><<<grid, 256, 0, h->stream>>>(q, n, scale_dev, (T*)y));
+    }
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_int4g_quant_pack(oxq_handle* h, const void* x, int dtype, int64_t rows, int64_t k, int group, uint32_t* codes,
+                             uint16_t* scales, uint32_t* zeros, int rounding) {
+    OXQ_CHECK_HANDLE(h);
+    if (rows <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "MinMaxQuantizer::calibrate");
+    if (!(group == 32 || group == 64 || group == 128 || group == 256))   // Int4GemmConfig::VALID_GROUP_SIZES
+        OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "group size %d not in {32,64,128,256}", group);
+    if (k % group != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "tensor length %lld is not divisible by group size %d", (long long)k, group);
+    if (!x || !codes || !scales || !zeros || !aligned16(x)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    const int64_t ngroups = rows * (k / group);
+    const int grid = grid_for(h, (ngroups + 7) / 8 * 32, 256, 8);
+#define LAUNCH_G(G) int4g_quant_kernel<T, G><<<grid, 256, 0, h->stream>>>((const T*)x, ngroups, rounding, codes, scales, zeros)
+    DISPATCH_DTYPE(dtype, if (group == 32) LAUNCH_G(32); else if (group == 64) LAUNCH_G(64); else if (group == 128) LAUNCH_G(128); else LAUNCH_G(256));
+#undef LAUNCH_G
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_int4g_dequant(oxq_handle* h, const uint32_t* codes, const uint16_t* scales, const uint32_t* zeros, int64_t rows, int64_t k,
+                          int group, void* y, int y_dtype) {
+    OXQ_CHECK_HANDLE(h);
+    if (rows <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "dequantize: empty input");
+    if (group <= 0 || k % group != 0 || group % 8 != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "k %lld vs group %d", (long long)k, group);
+    if (!y || !codes || !scales || !zeros || !aligned16(y)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    const int64_t nwords = rows * k / 8;
+    DISPATCH_DTYPE(y_dtype, int4g_dequant_kernel<T><<<grid_for(h, nwords, 256, 16), 256, 0, h->stream>>>(codes, scales, zeros, nwords, group, (T*)y));
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+size_t oxq_sf_mma_bytes(int64_t rows, int64_t sf_cols) {
+    if (rows <= 0 || sf_cols <= 0) return 0;
+    return (size_t)((rows + 127) / 128) * (size_t)((sf_cols + 3) / 4) * 512;
+}
+
+int32_t oxq_mxfp8_quant(oxq_handle* h, const void* x, int dtype, int64_t rows, int64_t k, uint8_t* codes, uint8_t* sf_rm, uint8_t* sf_mma) {
+    OXQ_CHECK_HANDLE(h);
+    if (rows <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "mxfp8 quantize: empty input");
+    if (k % 32 != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "k %lld is not divisible by block size 32", (long long)k);
+    if (!x || !codes || (!sf_rm && !sf_mma) || !aligned16(x)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    if (sf_mma && ((rows & 127) || ((k / 32) & 3)))          // pad bytes of partial tiles must not hold garbage
+        OXQ_CUDA(h, cudaMemsetAsync(sf_mma, 0, oxq_sf_mma_bytes(rows, k / 32), h->stream));
+    DISPATCH_DTYPE(dtype, mxfp8_quant_kernel<T><<<grid_for(h, rows * k / 8, 256, 16), 256, 0, h->stream>>>((const T*)x, rows, k, codes, sf_rm, sf_mma));
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_mxfp8_dequant(oxq_handle* h, const uint8_t* codes, const uint8_t* sf_rm, int64_t rows, int64_t k, void* y, int y_dtype) {
+    OXQ_CHECK_HANDLE(h);
+    if (rows <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "mxfp8 dequantize: empty input");
+    if (k % 32 != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "k %lld is not divisible by block size 32", (long long)k);
+    if (!y || !codes || !sf_rm) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    DISPATCH_DTYPE(y_dtype, mxfp8_dequant_kernel<T><<<grid_for(h, rows * k, 256, 16), 256, 0, h->stream>>>(codes, sf_rm, rows * k, (T*)y));
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_nvfp4_quant(oxq_handle* h, const void* x, int dtype, int64_t rows, int64_t k, float* stats, uint8_t* packed, uint8_t* sf_rm,
+                        uint8_t* sf_mma) {
+    OXQ_CHECK_HANDLE(h);
+    if (rows <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "nvfp4 quantize: empty input");
+    if (k % 16 != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "k %lld is not divisible by block size 16", (long long)k);
+    if (!x || !packed || !stats || (!sf_rm && !sf_mma) || !aligned16(x)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    if (sf_mma && ((rows & 127) || ((k / 16) & 3)))
+        OXQ_CUDA(h, cudaMemsetAsync(sf_mma, 0, oxq_sf_mma_bytes(rows, k / 16), h->stream));
+    DISPATCH_DTYPE(dtype, nvfp4_quant_kernel<T><<<grid_for(h, rows * k / 8, 256, 16), 256, 0, h->stream>>>((const T*)x, rows, k, stats, packed, sf_rm, sf_mma));
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_nvfp4_dequant(oxq_handle* h, const uint8_t* packed, const uint8_t* sf_rm, const float* stats, int64_t rows, int64_t k, void* y,
+                          int y_dtype) {
+    OXQ_CHECK_HANDLE(h);
+    if (rows <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "nvfp4 dequantize: empty input");
+    if (k % 16 != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "k %lld is not divisible by block size 16", (long long)k);
+    if (!y || !packed || !sf_rm || !stats) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    DISPATCH_DTYPE(y_dtype, nvfp4_dequant_kernel<T><<<grid_for(h, rows * k, 256, 16), 256, 0, h->stream>>>(packed, sf_rm, stats, rows * k, (T*)y));
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,271 @@
+"""Device-tensor front end of the C ABI: torch tensors supply device memory and the current stream,
+every computation happens inside liboxq_b200.so.  Function names follow the C entry points."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _ffi
+from .errors import raise_for_status
+
+F32, BF16, F16 = 0, 1, 2
+ROUND_HALF_EVEN, ROUND_HALF_AWAY = 0, 1
+FP8_SPEC_RNE, FP8_REFCOMPAT = 0, 1
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+_TORCH_DT = {F32: torch.float32, BF16: torch.bfloat16, F16: torch.float16}
+
+
+class Handle:
+    """One per host thread and device, like BlasHandle (crates/oxicuda-blas/src/handle.rs:41-52)."""
+
+    def __init__(self, device: int | None = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("oxicuda_b200 needs a CUDA device (sm_100); there is no CPU fallback")
+        self.lib = _ffi.load()
+        self.device = torch.cuda.current_device() if device is None else int(device)
+        self._h = C.c_void_p()
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            raise_for_status(self.lib.oxq_handle_create(self.device, C.c_void_p(stream), C.byref(self._h)))
+        self._stream = stream
+
+    def close(self):
+        if self._h:
+            self.lib.oxq_handle_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def sync_stream(self):
+        """Follow torch's current stream (BlasHandle::set_stream)."""
+        s = torch.cuda.current_stream(self.device).cuda_stream
+        if s != self._stream:
+            raise_for_status(self.lib.oxq_set_stream(self._h, C.c_void_p(s)))
+            self._stream = s
+
+    def call(self, name: str, *args):
+        self.sync_stream()
+        rc = getattr(self.lib, name)(self._h, *args)
+        if rc:
+            raise_for_status(rc, self.lib.oxq_last_error_string(self._h).decode())
+
+    def device_status(self) -> int:
+        v = C.c_int32(0)
+        raise_for_status(self.lib.oxq_device_status(self._h, C.byref(v)))
+        return v.value
+
+
+_handles: dict[int, Handle] = {}
+
+
+def handle(device: int | None = None) -> Handle:
+    d = torch.cuda.current_device() if device is None else int(device)
+    if d not in _handles:
+        _handles[d] = Handle(d)
+    return _handles[d]
+
+
+def _p(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def _chk(t: torch.Tensor, *dtypes):
+    if not t.is_cuda:
+        raise TypeError("expected a CUDA tensor")
+    if not t.is_contiguous():
+        raise TypeError("expected a contiguous tensor")
+    if dtypes and t.dtype not in dtypes:
+        raise TypeError(f"expected dtype in {dtypes}, got {t.dtype}")
+
+
+# ------------------------------------------------------------------------------------------- INT8
+
+def int8_quant_rows(x: torch.Tensor, rounding: int = ROUND_HALF_EVEN):
+    _chk(x, torch.float32)
+    rows, cols = (x.shape[0], x.shape[1]) if x.dim() == 2 else (0, 0)
+    q = torch.empty((rows, cols), dtype=torch.int8, device=x.device)
+    s = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    handle(x.device.index).call("oxq_int8_quant_rows", _p(x), rows, cols, _p(q), _p(s), rounding)
+    return q, s
+
+
+def int8_dequant_rows(q: torch.Tensor, scales: torch.Tensor):
+    _chk(q, torch.int8)
+    _chk(scales, torch.float32)
+    rows, cols = q.shape
+    y = torch.empty((rows, cols), dtype=torch.float32, device=q.device)
+    handle(q.device.index).call("oxq_int8_dequant_rows", _p(q), _p(scales), rows, cols, _p(y))
+    return y
+
+
+# ------------------------------------------------------------------------------------------- FP8
+
+def absmax(x: torch.Tensor, out: torch.Tensor | None = None):
+    _chk(x, *_DT)
+    out = torch.empty(1, dtype=torch.float32, device=x.device) if out is None else out
+    handle(x.device.index).call("oxq_absmax", _p(x), _DT[x.dtype], x.numel(), _p(out))
+    return out
+
+
+def fp8_quant(x: torch.Tensor, scale: torch.Tensor, mode: int = FP8_SPEC_RNE, out: torch.Tensor | None = None):
+    _chk(x, *_DT)
+    _chk(scale, torch.float32)
+    q = torch.empty(x.shape, dtype=torch.uint8, device=x.device) if out is None else out
+    handle(x.device.index).call("oxq_fp8_quant", _p(x), _DT[x.dtype], x.numel(), _p(scale), _p(q), mode)
+    return q
+
+
+def fp8_quant_dynamic(x: torch.Tensor, out: torch.Tensor | None = None, stats: torch.Tensor | None = None):
+    """Returns (codes, stats) with stats[0] = absmax and stats[1] = scale = absmax / 448."""
+    _chk(x, *_DT)
+    q = torch.empty(x.shape, dtype=torch.uint8, device=x.device) if out is None else out
+    stats = torch.empty(2, dtype=torch.float32, device=x.device) if stats is None else stats
+    handle(x.device.index).call("oxq_fp8_quant_dynamic", _p(x), _DT[x.dtype], x.numel(), _p(q), _p(stats))
+    return q, stats
+
+
+def fp8_dequant(q: torch.Tensor, scale: torch.Tensor, dtype=torch.float32, mode: int = FP8_SPEC_RNE):
+    _chk(q, torch.uint8)
+    y = torch.empty(q.shape, dtype=dtype, device=q.device)
+    handle(q.device.index).call("oxq_fp8_dequant", _p(q), q.numel(), _p(scale), _p(y), _DT[dtype], mode)
+    return y
+
+
+# ------------------------------------------------------------------------------------------- INT4
+
+def int4g_quant_pack(x: torch.Tensor, group: int = 128, rounding: int = ROUND_HALF_AWAY):
+    _chk(x, *_DT)
+    rows, k = (x.shape[0], x.shape[1]) if x.dim() == 2 else (0, 0)
+    ng = rows * (k // group) if group > 0 else 0
+    # int32 tensors hold the u32 words and uint16 bit patterns are kept in int16 tensors
+    codes = torch.empty((rows, max(k // 8, 0)), dtype=torch.int32, device=x.device)
+    scales = torch.empty((rows, k // group if group > 0 else 0), dtype=torch.float16, device=x.device)
+    zeros = torch.empty(((ng + 7) // 8,), dtype=torch.int32, device=x.device)
+    handle(x.device.index).call("oxq_int4g_quant_pack", _p(x), _DT[x.dtype], rows, k, group, _p(codes), _p(scales),
+                                _p(zeros), rounding)
+    return codes, scales, zeros
+
+
+def int4g_dequant(codes, scales, zeros, rows: int, k: int, group: int = 128, dtype=torch.float32):
+    y = torch.empty((rows, k), dtype=dtype, device=codes.device)
+    handle(codes.device.index).call("oxq_int4g_dequant", _p(codes), _p(scales), _p(zeros), rows, k, group, _p(y),
+                                    _DT[dtype])
+    return y
+
+
+# ------------------------------------------------------------------------------------------- block scaled
+
+def sf_mma_bytes(rows: int, sf_cols: int) -> int:
+    return int(_ffi.load().oxq_sf_mma_bytes(rows, sf_cols))
+
+
+def mxfp8_quant(x: torch.Tensor, want_mma_layout: bool = True):
+    """Returns (codes [rows x k] u8, sf_rowmajor [rows x k/32] u8, sf_mma bytes or None)."""
+    _chk(x, *_DT)
+    rows, k = (x.shape[0], x.shape[1]) if x.dim() == 2 else (0, 0)
+    codes = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
+    sf = torch.empty((rows, k // 32), dtype=torch.uint8, device=x.device)
+    sf_mma = torch.empty(sf_mma_bytes(rows, k // 32), dtype=torch.uint8, device=x.device) if want_mma_layout else None
+    handle(x.device.index).call("oxq_mxfp8_quant", _p(x), _DT[x.dtype], rows, k, _p(codes), _p(sf), _p(sf_mma))
+    return codes, sf, sf_mma
+
+
+def mxfp8_dequant(codes, sf, dtype=torch.float32):
+    rows, k = codes.shape
+    y = torch.empty((rows, k), dtype=dtype, device=codes.device)
+    handle(codes.device.index).call("oxq_mxfp8_dequant", _p(codes), _p(sf), rows, k, _p(y), _DT[dtype])
+    return y
+
+
+def nvfp4_quant(x: torch.Tensor, want_mma_layout: bool = True, stats: torch.Tensor | None = None):
+    """absmax pass + encode pass.  Returns (packed [rows x k/2] u8, sf_rowmajor [rows x k/16] u8, sf_mma, stats)
+    with stats[0] = absmax and stats[1] = the f32 tensor scale."""
+    _chk(x, *_DT)
+    rows, k = (x.shape[0], x.shape[1]) if x.dim() == 2 else (0, 0)
+    stats = torch.empty(2, dtype=torch.float32, device=x.device) if stats is None else stats
+    packed = torch.empty((rows, k // 2), dtype=torch.uint8, device=x.device)
+    sf = torch.empty((rows, k // 16), dtype=torch.uint8, device=x.device)
+    sf_mma = torch.empty(sf_mma_bytes(rows, k // 16), dtype=torch.uint8, device=x.device) if want_mma_layout else None
+    h = handle(x.device.index)
+    if rows > 0 and k > 0:
+        h.call("oxq_absmax", _p(x), _DT[x.dtype], x.numel(), _p(stats))
+    h.call("oxq_nvfp4_quant", _p(x), _DT[x.dtype], rows, k, _p(stats), _p(packed), _p(sf), _p(sf_mma))
+    return packed, sf, sf_mma, stats
+
+
+def nvfp4_dequant(packed, sf, stats, dtype=torch.float32):
+    rows, k = packed.shape[0], packed.shape[1] * 2
+    y = torch.empty((rows, k), dtype=dtype, device=packed.device)
+    handle(packed.device.index).call("oxq_nvfp4_dequant", _p(packed), _p(sf), _p(stats), rows, k, _p(y), _DT[dtype])
+    return y
+
+
+# ------------------------------------------------------------------------------------------- GEMMs
+
+def gemm_fp8(x_q, w_q, sx, sw, out: torch.Tensor | None = None):
+    """Y = bf16((X . W^T) * sx * sw); x_q [M x K] u8, w_q [N x K] u8 (E4M3 bytes)."""
+    m, k = x_q.shape
+    n = w_q.shape[0]
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=x_q.device) if out is None else out
+    handle(x_q.device.index).call("oxq_gemm_fp8", m, n, k, _p(x_q), x_q.stride(0), _p(w_q), w_q.stride(0), _p(sx), _p(sw),
+                                  _p(y), y.stride(0))
+    return y
+
+
+def gemm_w8a8(x_q, w_q, sx_rows, sw_rows, out: torch.Tensor | None = None):
+    m, k = x_q.shape
+    n = w_q.shape[0]
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=x_q.device) if out is None else out
+    handle(x_q.device.index).call("oxq_gemm_w8a8", m, n, k, _p(x_q), x_q.stride(0), _p(w_q), w_q.stride(0), _p(sx_rows),
+                                  _p(sw_rows), _p(y), y.stride(0))
+    return y
+
+
+def gemm_w8a32(x, w_q, sw_rows):
+    m, k = x.shape
+    n = w_q.shape[0]
+    y = torch.empty((m, n), dtype=torch.float32, device=x.device)
+    handle(x.device.index).call("oxq_gemm_w8a32", m, n, k, _p(x), _p(w_q), _p(sw_rows), _p(y))
+    return y
+
+
+def gemm_w4a16_workspace(m: int, n: int, k: int, device) -> torch.Tensor:
+    """Zero-filled workspace; every call leaves it zero-filled again, so it can be reused."""
+    nbytes = int(_ffi.load().oxq_gemm_w4a16_workspace_bytes(m, n, k))
+    return torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)
+
+
+def gemm_w4a16(x, codes, scales, zeros, group: int = 128, workspace: torch.Tensor | None = None,
+               out: torch.Tensor | None = None):
+    m, k = x.shape
+    n = codes.shape[0]
+    ws = gemm_w4a16_workspace(m, n, k, x.device) if workspace is None else workspace
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=x.device) if out is None else out
+    handle(x.device.index).call("oxq_gemm_w4a16", m, n, k, _p(x), _p(codes), _p(scales), _p(zeros), group, _p(y), _p(ws),
+                                ws.numel())
+    return y
+
+
+def gemm_mxfp8(x_codes, x_sf_mma, w_codes, w_sf_mma, out: torch.Tensor | None = None):
+    m, k = x_codes.shape
+    n = w_codes.shape[0]
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=x_codes.device) if out is None else out
+    handle(x_codes.device.index).call("oxq_gemm_mxfp8", m, n, k, _p(x_codes), _p(x_sf_mma), _p(w_codes), _p(w_sf_mma),
+                                      _p(y), y.stride(0))
+    return y
+
+
+def gemm_nvfp4(x_packed, x_sf_mma, x_stats, w_packed, w_sf_mma, w_stats, out: torch.Tensor | None = None):
+    """x_stats / w_stats are the 2-float tensors of nvfp4_quant; element 1 is the tensor scale."""
+    m, k = x_packed.shape[0], x_packed.shape[1] * 2
+    n = w_packed.shape[0]
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=x_packed.device) if out is None else out
+    handle(x_packed.device.index).call("oxq_gemm_nvfp4", m, n, k, _p(x_packed), _p(x_sf_mma), _p(x_stats[1:]),
+                                       _p(w_packed), _p(w_sf_mma), _p(w_stats[1:]), _p(y), y.stride(0))
+    return y

@@ -1,0 +1,74 @@
+"""CPU-only checks of the drop-in boundary: the shared library builds, loads, and exports exactly the
+symbols include/oxq.h declares; argument validation mirrors the reference's error variants."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from oxicuda_b200 import _build, _ffi
+    _build.build()
+    return _ffi.load()
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "oxq.h")).read()
+    return sorted(set(re.findall(r"OXQ_API\s+[\w\s\*]+?\b(oxq_\w+)\s*\(", text)))
+
+
+def test_header_symbols_all_exported(lib):
+    from oxicuda_b200 import _ffi
+    declared = _declared_symbols()
+    assert len(declared) >= 27
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in oxq.h but not exported"
+    assert sorted(_ffi.SIGNATURES) == declared          # the ctypes table covers the whole header
+
+
+def test_status_names(lib):
+    assert lib.oxq_status_name(0) == b"Ok"
+    assert lib.oxq_status_name(1) == b"EmptyInput"
+    assert lib.oxq_status_name(2) == b"GroupSizeMismatch"
+    assert lib.oxq_status_name(10) == b"InvalidDimension"
+    assert lib.oxq_status_name(100) == b"DeviceTimeout"
+    assert lib.oxq_status_name(1002) == b"Cuda"
+    assert lib.oxq_version() >= 100
+
+
+def test_size_queries(lib):
+    assert lib.oxq_sf_mma_bytes(128, 4) == 512
+    assert lib.oxq_sf_mma_bytes(129, 5) == 2 * 2 * 512
+    assert lib.oxq_sf_mma_bytes(0, 4) == 0
+    assert lib.oxq_gemm_w4a16_workspace_bytes(1, 4096, 4096) >= 4096 * 4 + 32 * 4
+    assert lib.oxq_gemm_w4a16_workspace_bytes(0, 4096, 4096) == 0
+
+
+def test_no_device_means_error_not_fallback(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    h = C.c_void_p()
+    rc = lib.oxq_handle_create(0, None, C.byref(h))
+    assert rc != 0 and not h                             # no device -> an error status, never a CPU path
+    from oxicuda_b200 import ops
+    with pytest.raises(RuntimeError):
+        ops.Handle()
+
+
+def test_error_mapping():
+    from oxicuda_b200.errors import BlasError, QuantError, raise_for_status
+    with pytest.raises(QuantError) as e:
+        raise_for_status(2, "x")
+    assert e.value.variant == "GroupSizeMismatch"
+    with pytest.raises(BlasError) as e:
+        raise_for_status(10)
+    assert e.value.variant == "InvalidDimension"
+    with pytest.raises(BlasError) as e:
+        raise_for_status(1000 + 700)
+    assert e.value.variant == "Cuda"
+    raise_for_status(0)

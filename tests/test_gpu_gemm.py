@@ -1,0 +1,201 @@
+"""GPU parity of the low-precision GEMMs, through the C ABI, against the oracle's
+dequantise-then-f32 result.  Tolerance (bf16 output): max |y - ref| <= 1e-2 * max |ref| over the
+matrix ("max-relative 1e-2"), plus an elementwise check |y - ref| <= 1e-2 |ref| + 1e-2 max|ref|/8."""
+import numpy as np
+import pytest
+import torch
+
+from tests.gpu_util import bf16_bits, bf16_dev, to_dev, u16, u32
+
+pytestmark = pytest.mark.gpu
+MAX_REL = 1e-2
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from oxicuda_b200 import ops
+    return ops
+
+
+def _check(y: np.ndarray, ref: np.ndarray, tag=""):
+    assert y.shape == ref.shape
+    assert np.isfinite(y).all(), f"{tag}: non-finite output"
+    scale = np.abs(ref).max()
+    err = np.abs(y - ref)
+    assert err.max() <= MAX_REL * scale, f"{tag}: max err {err.max()} vs {MAX_REL * scale}"
+    assert (err <= MAX_REL * np.abs(ref) + MAX_REL * scale / 8).all(), tag
+
+
+def _bf16_to_np(t):
+    return t.float().cpu().numpy()
+
+
+def _status_clean(ops):
+    assert ops.handle().device_status() == 0
+
+
+# ------------------------------------------------------------------------------------------- FP8
+
+@pytest.mark.parametrize("mnk", [(128, 256, 128), (256, 512, 256), (300, 520, 384), (1024, 1024, 1024), (64, 264, 2048),
+                                 (1, 256, 128), (129, 257 * 8, 16)])
+def test_gemm_fp8(ops, orc, mnk):
+    m, n, k = mnk
+    a = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 0))
+    b = orc.f32_to_bf16_bits(orc.gaussian((n, k), 1.0, 1))
+    qa, sa = ops.fp8_quant_dynamic(bf16_dev(a))
+    qb, sb = ops.fp8_quant_dynamic(bf16_dev(b))
+    y = ops.gemm_fp8(qa, qb, sa[1:], sb[1:])
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    # oracle: dequantised codes (exact in f32), f32 GEMM, one f32 scale product, bf16 rounding
+    da = orc.e4m3_to_f32(qa.cpu().numpy())
+    db = orc.e4m3_to_f32(qb.cpu().numpy())
+    s = np.float32(sa.cpu().numpy()[1]) * np.float32(sb.cpu().numpy()[1])
+    ref = (da.astype(np.float64) @ db.astype(np.float64).T).astype(np.float32) * s
+    _check(_bf16_to_np(y), ref, f"fp8 {mnk}")
+    if m * n * k <= 128 * 256 * 128:
+        # small case: the reference's left-to-right f32 accumulation, bf16-rounded, agrees to 1 bf16 ulp
+        ref_seq = orc.ref_linear_f32(da, db) * s
+        yb = bf16_bits(y).astype(np.int32)
+        rb = orc.f32_to_bf16_bits(ref_seq).astype(np.int32)
+        assert np.abs(yb - rb).max() <= 1
+
+
+def test_gemm_fp8_strided_and_errors(ops, orc):
+    from oxicuda_b200.errors import BlasError
+    m, n, k = 128, 256, 256
+    big_a = ops.fp8_quant_dynamic(bf16_dev(orc.f32_to_bf16_bits(orc.gaussian((m, 2 * k), 1.0, 0))))
+    big_b = ops.fp8_quant_dynamic(bf16_dev(orc.f32_to_bf16_bits(orc.gaussian((n, 2 * k), 1.0, 1))))
+    qa, qb = big_a[0][:, :k], big_b[0][:, k:]                # leading dimension 2k, offset k
+    y = ops.gemm_fp8(qa, qb, big_a[1][1:], big_b[1][1:])
+    da, db = orc.e4m3_to_f32(qa.cpu().numpy()), orc.e4m3_to_f32(qb.cpu().numpy())
+    s = float(big_a[1][1]) * float(big_b[1][1])
+    _check(_bf16_to_np(y), (da @ db.T) * np.float32(s), "fp8 strided")
+    one = torch.ones(1, device="cuda")
+    e8 = torch.zeros((0, 64), dtype=torch.uint8, device="cuda")
+    with pytest.raises(BlasError) as e:                     # zero dimension -> InvalidDimension (gemm_api.rs:88-92)
+        ops.gemm_fp8(e8, big_b[0][:, :64], one, one)
+    assert e.value.variant == "InvalidDimension"
+    with pytest.raises(BlasError) as e:                     # K not a multiple of 16
+        ops.gemm_fp8(big_a[0][:, :24].contiguous(), big_b[0][:, :24].contiguous(), one, one)
+    assert e.value.variant == "InvalidArgument"
+
+
+def test_gemm_fp8_linearity_full_size(ops, orc):
+    """Benchmark size 8192^3: a sample of 64 x 64 outputs against the f64 dot product of the dequantised
+    codes, plus scale linearity: doubling sx doubles every output exactly (power-of-two scaling)."""
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn((8192, 8192), generator=gen, device="cuda").to(torch.bfloat16)
+    b = torch.randn((8192, 8192), generator=gen, device="cuda").to(torch.bfloat16)
+    qa, sa = ops.fp8_quant_dynamic(a)
+    qb, sb = ops.fp8_quant_dynamic(b)
+    y = ops.gemm_fp8(qa, qb, sa[1:], sb[1:])
+    y2 = ops.gemm_fp8(qa, qb, sa[1:] * 2, sb[1:])
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    assert torch.equal(y2.float(), y.float() * 2)
+    rows = torch.randint(0, 8192, (64,), generator=torch.Generator().manual_seed(1))
+    cols = torch.randint(0, 8192, (64,), generator=torch.Generator().manual_seed(2))
+    da = orc.e4m3_to_f32(qa[rows.cuda()].cpu().numpy()).astype(np.float64)
+    db = orc.e4m3_to_f32(qb[cols.cuda()].cpu().numpy()).astype(np.float64)
+    ref = (da @ db.T).astype(np.float32) * (np.float32(float(sa[1])) * np.float32(float(sb[1])))
+    got = y[rows.cuda()][:, cols.cuda()].float().cpu().numpy()
+    _check(got, ref, "fp8 8192^3 sample")
+
+
+# ------------------------------------------------------------------------------------------- W8A8 / W8A32
+
+@pytest.mark.parametrize("mnk", [(128, 256, 128), (200, 512, 1024), (33, 264, 4096)])
+def test_gemm_w8a8(ops, orc, mnk):
+    m, n, k = mnk
+    x = orc.gaussian((m, k), 1.0, 1)
+    w = orc.gaussian((n, k), 0.02, 0)
+    qx, sx = ops.int8_quant_rows(to_dev(x))
+    qw, sw = ops.int8_quant_rows(to_dev(w))
+    y = ops.gemm_w8a8(qx, qw, sx, sw)
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    acc = qx.cpu().numpy().astype(np.int64) @ qw.cpu().numpy().astype(np.int64).T      # exact integer result
+    ref = acc.astype(np.float32) * (sx.cpu().numpy()[:, None] * sw.cpu().numpy()[None, :])
+    _check(_bf16_to_np(y), ref, f"w8a8 {mnk}")
+    # the s32 accumulator is exact, so the only error is the final bf16 rounding
+    assert np.abs(bf16_bits(y).astype(np.int32) - orc.f32_to_bf16_bits(ref).astype(np.int32)).max() <= 1
+
+
+@pytest.mark.parametrize("mnk", [(8, 4096, 4096), (1, 64, 512), (13, 100, 1040), (32, 256, 2048)])
+def test_gemm_w8a32_config1(ops, orc, mnk):
+    """Benchmark configuration 1: INT8 per-channel weights, f32 activations, f32 accumulate and output."""
+    m, n, k = mnk
+    w = orc.gaussian((n, k), 0.02, 0)
+    x = orc.gaussian((m, k), 1.0, 1)
+    qw, sw = ops.int8_quant_rows(to_dev(w))
+    y = ops.gemm_w8a32(to_dev(x), qw, sw).cpu().numpy()
+    deq = orc.spec_int8_dequant_rows(qw.cpu().numpy(), sw.cpu().numpy())
+    ref = orc.ref_linear_f32(x, deq, threads=orc.max_threads())     # reference summation order, f32
+    scale = np.abs(ref).max()
+    assert np.abs(y - ref).max() <= 1e-4 * scale                     # f32 path: only the summation order differs
+
+
+# ------------------------------------------------------------------------------------------- W4A16
+
+@pytest.mark.parametrize("m", [1, 8, 32, 5, 17])
+@pytest.mark.parametrize("nk", [(256, 512), (4096, 4096), (200, 1024), (6144, 4096), (384, 14336)])
+def test_gemm_w4a16_decode(ops, orc, m, nk):
+    n, k = nk
+    w = orc.gaussian((n, k), 0.02, 0)
+    xb = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 1))
+    c, s, z = ops.int4g_quant_pack(to_dev(w), 128)
+    ws = ops.gemm_w4a16_workspace(m, n, k, "cuda")
+    y = ops.gemm_w4a16(bf16_dev(xb), c, s, z, 128, workspace=ws)
+    torch.cuda.synchronize()
+    deq = orc.spec_int4g_dequant(u32(c), u16(s), u32(z), n, k, 128)
+    ref = (orc.bf16_bits_to_f32(xb).astype(np.float64) @ deq.astype(np.float64).T).astype(np.float32)
+    _check(_bf16_to_np(y), ref, f"w4a16 m={m} {nk}")
+    assert int(ws.view(torch.int32).abs().max()) == 0               # workspace left zeroed
+    y2 = ops.gemm_w4a16(bf16_dev(xb), c, s, z, 128, workspace=ws)   # and therefore reusable
+    _check(_bf16_to_np(y2), ref, "w4a16 second call")
+
+
+def test_gemm_w4a16_errors(ops, orc):
+    from oxicuda_b200.errors import BlasError
+    w = orc.gaussian((128, 256), 0.02, 0)
+    c, s, z = ops.int4g_quant_pack(to_dev(w), 128)
+    x = torch.zeros((64, 256), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(BlasError) as e:
+        ops.gemm_w4a16(x, c, s, z, 128)
+    assert e.value.variant == "UnsupportedOperation"
+    with pytest.raises(BlasError) as e:
+        ops.gemm_w4a16(x[:1], c, s, z, 48)
+    assert e.value.variant == "InvalidArgument"
+
+
+# ------------------------------------------------------------------------------------------- block scaled
+
+@pytest.mark.parametrize("mnk", [(128, 192, 128), (128, 384, 256), (256, 512, 512), (300, 1000, 1024), (64, 200, 4096)])
+def test_gemm_mxfp8(ops, orc, mnk):
+    m, n, k = mnk
+    a = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 0))
+    b = orc.f32_to_bf16_bits(orc.gaussian((n, k), 1.0, 1))
+    ca, sfa, sfa_mma = ops.mxfp8_quant(bf16_dev(a))
+    cb, sfb, sfb_mma = ops.mxfp8_quant(bf16_dev(b))
+    y = ops.gemm_mxfp8(ca, sfa_mma, cb, sfb_mma)
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    da = orc.spec_mxfp8_dequant(ca.cpu().numpy(), sfa.cpu().numpy()).astype(np.float64)
+    db = orc.spec_mxfp8_dequant(cb.cpu().numpy(), sfb.cpu().numpy()).astype(np.float64)
+    _check(_bf16_to_np(y), (da @ db.T).astype(np.float32), f"mxfp8 {mnk}")
+
+
+@pytest.mark.parametrize("mnk", [(128, 192, 256), (128, 384, 512), (256, 512, 1024), (300, 1000, 1024), (64, 200, 4096)])
+def test_gemm_nvfp4(ops, orc, mnk):
+    m, n, k = mnk
+    a = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 0))
+    b = orc.f32_to_bf16_bits(orc.gaussian((n, k), 1.0, 1))
+    pa, sfa, sfa_mma, sta = ops.nvfp4_quant(bf16_dev(a))
+    pb, sfb, sfb_mma, stb = ops.nvfp4_quant(bf16_dev(b))
+    y = ops.gemm_nvfp4(pa, sfa_mma, sta, pb, sfb_mma, stb)
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    da = orc.spec_nvfp4_dequant(pa.cpu().numpy(), sfa.cpu().numpy(), float(sta[1]), m, k).astype(np.float64)
+    db = orc.spec_nvfp4_dequant(pb.cpu().numpy(), sfb.cpu().numpy(), float(stb[1]), n, k).astype(np.float64)
+    _check(_bf16_to_np(y), (da @ db.T).astype(np.float32), f"nvfp4 {mnk}")

@@ -164,17 +164,29 @@ def time_region(torch, fn, steps, dist_on):
 
 
 def ring_time(torch, make_call, ring, iters=40, warm=5):
-    """Average ms per call over a ring of distinct buffer sets (total > L2), CUDA events."""
-    for i in range(warm):
-        make_call(ring[i % len(ring)])
+    """Average ms per call over a ring of distinct buffer sets (total > L2).  The calls are captured
+    once into a CUDA graph and the graph is replayed, so host launch overhead (several microseconds
+    per call through ctypes) does not sit between kernels that themselves last a few microseconds."""
+    del iters, warm
+    for r in ring:                                       # warm-up: every variant launched (and its attributes set) before capture
+        make_call(r)
     torch.cuda.synchronize()
+    reps_in_graph = max(1, 24 // len(ring))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(reps_in_graph):
+            for r in ring:
+                make_call(r)
+    graph.replay()
+    torch.cuda.synchronize()
+    replays = 5
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(iters):
-        make_call(ring[i % len(ring)])
+    for _ in range(replays):
+        graph.replay()
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / iters
+    return e0.elapsed_time(e1) / (replays * reps_in_graph * len(ring))
 
 
 def extras(torch, ops, peaks):
@@ -222,13 +234,13 @@ def extras(torch, ops, peaks):
             x = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
             ws = ops.gemm_w4a16_workspace(m, n, k, "cuda")
             y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
-            ms = ring_time(torch, lambda r: ops.gemm_w4a16(x, r[0], r[1], r[2], 128, workspace=ws, out=y), ring, iters=3 * copies)
+            ms = ring_time(torch, lambda r: ops.gemm_w4a16(x, r[0], r[1], r[2], 128, workspace=ws, out=y), ring)
             rec(f"gemm_w4a16_m{m}_{n}x{k}", wbytes + m * k * 2 + m * n * 2, ms)
         del ring
     # the offline W4 quantize + pack kernel on the largest weight
     ringw = [torch.randn((14336, 4096), generator=g, device="cuda") * 0.02 for _ in range(3)]
     rec("int4g_quant_pack_f32_14336x4096", 14336 * 4096 * 4 + 14336 * 4096 // 2 + 458752 * 2 + 458752 // 2,
-        ring_time(torch, lambda r: ops.int4g_quant_pack(r, 128), ringw, iters=12))
+        ring_time(torch, lambda r: ops.int4g_quant_pack(r, 128), ringw))
     return out
 
 
@@ -335,6 +347,73 @@ def run_ours(args):
         torch.distributed.destroy_process_group()
 
 
+def run_case(args):
+    """Single-kernel mode (what the ncu captures run): `--case gemm_fp8` launches the headline GEMM,
+    the other cases one memory-bound kernel each, W warm-up + K timed launches, one JSON line."""
+    import torch
+    from oxicuda_b200 import ops
+    torch.cuda.set_device(0)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    sz = args.size
+    if args.case in ("gemm_fp8", "gemm_w8a8", "gemm_mxfp8", "gemm_nvfp4"):
+        m, n, k = (sz, sz, sz) if args.case in ("gemm_fp8", "gemm_w8a8") else (4096 * sz // 8192, 14336 * sz // 8192, 4096 * sz // 8192)
+        a = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+        b = torch.randn((n, k), generator=g, device="cuda").to(torch.bfloat16)
+        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        if args.case == "gemm_fp8":
+            qa, sa = ops.fp8_quant_dynamic(a)
+            qb, sb = ops.fp8_quant_dynamic(b)
+            fn = lambda: ops.gemm_fp8(qa, qb, sa[1:], sb[1:], out=y)  # noqa: E731
+        elif args.case == "gemm_w8a8":
+            qa, sa = ops.int8_quant_rows(a.float())
+            qb, sb = ops.int8_quant_rows(b.float())
+            fn = lambda: ops.gemm_w8a8(qa, qb, sa, sb, out=y)  # noqa: E731
+        elif args.case == "gemm_mxfp8":
+            ca, _, fa = ops.mxfp8_quant(a)
+            cb, _, fb = ops.mxfp8_quant(b)
+            fn = lambda: ops.gemm_mxfp8(ca, fa, cb, fb, out=y)  # noqa: E731
+        else:
+            pa, _, fa, sta = ops.nvfp4_quant(a)
+            pb, _, fb, stb = ops.nvfp4_quant(b)
+            fn = lambda: ops.gemm_nvfp4(pa, fa, sta, pb, fb, stb, out=y)  # noqa: E731
+        work, unit = 2.0 * m * n * k, "TFLOP/s"
+    elif args.case == "fp8_quant":
+        x = torch.randn((sz, sz), generator=g, device="cuda").to(torch.bfloat16)
+        q = torch.empty((sz, sz), dtype=torch.uint8, device="cuda")
+        one = torch.ones(1, device="cuda")
+        fn = lambda: ops.fp8_quant(x, one, out=q)  # noqa: E731
+        work, unit = 3.0 * sz * sz, "GB/s"
+        m = n = k = sz
+    elif args.case == "int8_quant_rows":
+        x = torch.randn((sz, sz), generator=g, device="cuda") * 0.02
+        fn = lambda: ops.int8_quant_rows(x)  # noqa: E731
+        work, unit = 5.0 * sz * sz + 4 * sz, "GB/s"
+        m = n = k = sz
+    elif args.case == "gemm_w4a16":
+        n, k, m = 14336, 4096, args.m
+        w = torch.randn((n, k), generator=g, device="cuda") * 0.02
+        c, sc, z = ops.int4g_quant_pack(w, 128)
+        ring = [(c.clone(), sc.clone(), z.clone()) for _ in range(20)]
+        x = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+        ws = ops.gemm_w4a16_workspace(m, n, k, "cuda")
+        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        it = [0]
+
+        def fn():
+            r = ring[it[0] % len(ring)]
+            it[0] += 1
+            ops.gemm_w4a16(x, r[0], r[1], r[2], 128, workspace=ws, out=y)
+        work, unit = float(n * k // 2 + n * k // 128 * 2 + n * k // 256 + m * k * 2 + m * n * 2), "GB/s"
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+    for _ in range(args.warmup):
+        fn()
+    ms = time_region(torch, fn, args.steps, False) / args.steps
+    rate = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
+    print(json.dumps({"case": args.case, "m": m, "n": n, "k": k, "ms_per_launch": ms, "rate": rate, "unit": unit,
+                      "steps": args.steps, "warmup": args.warmup}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -342,8 +421,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--case", default=None, help="single-kernel mode, e.g. gemm_fp8, gemm_mxfp8, gemm_nvfp4, fp8_quant, gemm_w4a16")
+    ap.add_argument("--size", type=int, default=8192)
+    ap.add_argument("--m", type=int, default=8)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -157,6 +157,20 @@ OXQ_API size_t oxq_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k);
 OXQ_API int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x_bf16_dev,
                        const uint32_t* codes_dev, const uint16_t* scales_f16_dev, const uint32_t* zeros_packed_dev,
                        int group, void* y_bf16_dev, void* workspace_dev, size_t workspace_bytes);
+/* Same product as oxq_gemm_w4a16 for callers that cannot allocate device memory at all: code that
+ * runs where cudaMalloc is off limits (inside a framework's caching-allocator region, under a memory
+ * budget enforced by someone else, in a plugin whose host forbids allocations after start-up) and so
+ * can neither create an oxq_handle nor provide a workspace.  It has no counterpart in the reference.
+ * It takes the stream directly, works on the current device, and keeps its split-K partial sums in an
+ * array built into the library image (2 MiB + 16 KiB per GPU that loads the library, held until the
+ * process exits).  Limit: m <= 32 and m * n <= 524288 outputs; larger shapes return
+ * OXQ_ERR_BUFFER_TOO_SMALL.  The first call on each device looks up the array's device address and
+ * reads three device attributes; make that first call before any stream capture begins.  Every call
+ * clears the part of the array it uses and all calls share the one array, so two calls that overlap
+ * on the GPU (different streams, no ordering between them) race and give wrong sums. */
+OXQ_API int32_t oxq_gemm_w4a16_static(void* cuda_stream, int64_t m, int64_t n, int64_t k, const void* x_bf16_dev,
+                              const uint32_t* codes_dev, const uint16_t* scales_f16_dev, const uint32_t* zeros_packed_dev,
+                              int group, void* y_bf16_dev);
 /* Block-scaled GEMMs (Fp4GemmConfig, fp4_fp6_ops.rs:337-395).  Scale factors in the tiled order. */
 OXQ_API int32_t oxq_gemm_mxfp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x_dev, const uint8_t* sfx_mma_dev,
                        const uint8_t* w_dev, const uint8_t* sfw_mma_dev, void* y_bf16_dev, int64_t ldy);

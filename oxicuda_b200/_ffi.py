@@ -39,6 +39,7 @@ SIGNATURES = {
     "oxq_gemm_w8a32": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "oxq_gemm_w4a16_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "oxq_gemm_w4a16": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp, _vp, _sz]),
+    "oxq_gemm_w4a16_static": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp]),
     "oxq_gemm_mxfp8": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64]),
     "oxq_gemm_nvfp4": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64]),
 }

@@ -329,6 +329,58 @@ int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const voi
     return OXQ_OK;
 }
 
+// ---- W4A16 without any allocation ---------------------------------------------------------------
+// Scratch for oxq_gemm_w4a16_static: lives in the library image, so every GPU that loads the library
+// carries these bytes until the process exits.  Layout: [kStaticW4MaxOut f32 partial sums][counters].
+static constexpr size_t kStaticW4MaxOut = 512 * 1024;                       // m * n <= 524288 outputs (2 MiB of f32)
+static constexpr size_t kStaticW4Counters = kStaticW4MaxOut / W4_ROWS_PER_CTA; // one counter per 128 weight rows (m >= 1)
+static constexpr size_t kStaticW4Bytes = kStaticW4MaxOut * sizeof(float) + kStaticW4Counters * sizeof(int);
+static __device__ __align__(256) unsigned char g_w4_static_scratch[kStaticW4Bytes];
+
+static constexpr int kMaxDevices = 64;
+struct StaticW4Device {
+    bool ready;
+    void* scratch;      // device address of g_w4_static_scratch on this device
+    int sm_count, cc_major, cc_minor;
+};
+static StaticW4Device g_static_w4[kMaxDevices];
+
+int32_t oxq_gemm_w4a16_static(void* cuda_stream, int64_t m, int64_t n, int64_t k, const void* x, const uint32_t* codes,
+                              const uint16_t* scales, const uint32_t* zeros, int group, void* y) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return OXQ_ERR_CUDA_BASE + (int32_t)e;
+    if (dev < 0 || dev >= kMaxDevices) return OXQ_ERR_INVALID_ARGUMENT;
+    StaticW4Device& d = g_static_w4[dev];
+    if (!d.ready) {
+        // Once per device, with that device current.  In host code the array's name is only a handle
+        // for the runtime; the address a kernel can use comes from cudaGetSymbolAddress.
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_w4_static_scratch);
+        if (e != cudaSuccess) return OXQ_ERR_CUDA_BASE + (int32_t)e;
+        if (!ptr || ((uintptr_t)ptr & 255u)) return OXQ_ERR_LAUNCH_FAILED;
+        e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev);
+        if (e != cudaSuccess) return OXQ_ERR_CUDA_BASE + (int32_t)e;
+        d.scratch = ptr;
+        d.ready = true;
+    }
+    if (m <= 0 || n <= 0 || k <= 0) return OXQ_ERR_INVALID_DIMENSION;
+    if (m > 32) return OXQ_ERR_UNSUPPORTED_OPERATION;
+    if ((uint64_t)m * (uint64_t)n > kStaticW4MaxOut) return OXQ_ERR_BUFFER_TOO_SMALL;   // beyond the built-in scratch
+    // The array keeps whatever the previous call left in it: clear the part this call accumulates into.
+    const size_t sums = ((size_t)m * (size_t)n * sizeof(float) + 255) & ~(size_t)255;
+    const size_t counters = (((size_t)(n + W4_ROWS_PER_CTA - 1) / W4_ROWS_PER_CTA) * sizeof(int) + 255) & ~(size_t)255;
+    if (sums + counters > kStaticW4Bytes) return OXQ_ERR_BUFFER_TOO_SMALL;
+    e = cudaMemsetAsync(d.scratch, 0, sums + counters, (cudaStream_t)cuda_stream);
+    if (e != cudaSuccess) return OXQ_ERR_CUDA_BASE + (int32_t)e;
+    oxq_handle tmp;
+    tmp.device = dev; tmp.stream = (cudaStream_t)cuda_stream; tmp.sm_count = d.sm_count;
+    tmp.cc_major = d.cc_major; tmp.cc_minor = d.cc_minor; tmp.dev_status = nullptr; tmp.last_error[0] = 0;
+    return oxq_gemm_w4a16(&tmp, m, n, k, x, codes, scales, zeros, group, y, d.scratch, sums + counters);
+}
+
 int32_t oxq_gemm_w8a32(oxq_handle* h, int64_t m, int64_t n, int64_t k, const float* x, const int8_t* w, const float* sw, float* y) {
     OXQ_CHECK_HANDLE(h);
     if (m <= 0 || n <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "GEMM dimensions must be non-zero");

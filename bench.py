@@ -17,9 +17,10 @@ N(0,1) quantised per tensor (scale = absmax/448), f32 accumulate, bf16 output = 
             the CPU oracle (a C restatement of the reference's scalar loops; the reference itself is
             a Rust workspace that cannot be built here) on a bounded sample of the same GEMM.
 
-One process per GPU; with --gpus N > 1 (under torchrun) every rank runs the same single-GPU GEMM on
-its own data (the GEMM does not shard without the tensor-parallel MLP around it; "weak" scaling of
-independent replicas) and the time is the max over ranks.
+One process per GPU.  With --gpus N > 1 (under torchrun) the workload is the one BASELINE.json shards: the
+tensor-parallel FP8 SwiGLU MLP of Llama-3-70B shape (configs[4]) at M = 2048, gate/up column-sharded, down
+row-sharded, one NCCL all-reduce; strong scaling (the layer is fixed), time = max over ranks.  The same layer
+at TP = 1 is reported in the N = 1 line's extras (tp_mlp_*_tp1), which is the denominator of the 1 -> 8 figure.
 """
 from __future__ import annotations
 
@@ -244,6 +245,104 @@ def extras(torch, ops, peaks):
     return out
 
 
+HIDDEN, INTER = 8192, 28672          # Llama-3-70B MLP shape (BASELINE.json configs[4])
+
+
+def make_tp_layer(torch, variant, world, rank, overlap_chunks=1):
+    """Random-init weights N(0, 0.02) generated directly as this rank's shards (seeded per rank)."""
+    from oxicuda_b200.dist_infer import TpSwiGluMlp
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    sh = INTER // world
+    wg = (torch.randn((sh, HIDDEN), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    wu = (torch.randn((sh, HIDDEN), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    wd = (torch.randn((HIDDEN, sh), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    layer = TpSwiGluMlp(wg, wu, wd, variant, tp=world, rank=rank, overlap_chunks=overlap_chunks, already_sharded=True)
+    del wg, wu, wd
+    torch.cuda.empty_cache()
+    return layer
+
+
+def mlp_extras(torch, peaks):
+    """The tensor-parallel MLP at TP = 1 (the denominator of the 1 -> 8 GPU scaling figure)."""
+    out = {}
+    for variant in ("fp8", "w4a16"):
+        layer = make_tp_layer(torch, variant, 1, 0)
+        for m in (1, 64, 2048):
+            x = torch.randn((m, HIDDEN), device="cuda").to(torch.bfloat16)
+            for _ in range(3):
+                layer.forward(x)
+            iters = 10 if m == 2048 else 30
+            ms = time_region(torch, lambda: layer.forward(x), iters, False) / iters
+            out[f"tp_mlp_{variant}_m{m}_tp1"] = {"ms": round(ms, 4), "TFLOP/s": round(layer.flops(m) / (ms * 1e-3) / 1e12, 2),
+                                                "weight_GB/s": round(layer.weight_bytes_local() / (ms * 1e-3) / 1e9, 1),
+                                                "frac_of_hbm": round(layer.weight_bytes_local() / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3)}
+        del layer
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_tp_mlp(args, torch, world, rank, local_rank, peaks):
+    """N > 1: the tensor-parallel FP8 SwiGLU MLP (hidden 8192, intermediate 28672, M = 2048), weights sharded over
+    the ranks, partial sums combined by one NCCL all-reduce per M-chunk.  Strong scaling: the layer is fixed."""
+    m = 2048
+    variant = os.environ.get("OXQ_BENCH_TP_VARIANT", "fp8")
+    chunks = int(os.environ.get("OXQ_BENCH_TP_CHUNKS", "4"))
+    layer = make_tp_layer(torch, variant, world, rank, overlap_chunks=chunks)
+    g = torch.Generator(device="cuda").manual_seed(7)
+    x = torch.randn((m, HIDDEN), generator=g, device="cuda").to(torch.bfloat16)
+    for _ in range(max(args.warmup, 3)):
+        layer.forward(x)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = time_region(torch, lambda: layer.forward(x), args.steps, True) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    value = layer.flops(m) / (ms * 1e-3) / 1e12
+    # decode-shaped points of the same layer (latency-bound; reported, not the headline)
+    small = {}
+    for mm in (1, 64):
+        xs = torch.randn((mm, HIDDEN), generator=g, device="cuda").to(torch.bfloat16)
+        for _ in range(3):
+            layer.forward(xs)
+        t = time_region(torch, lambda: layer.forward(xs), 20, True) / 20
+        small[f"m{mm}"] = {"ms": round(t, 4), "weight_GB/s_all_ranks": round(world * layer.weight_bytes_local() / (t * 1e-3) / 1e9, 1)}
+    # end to end: pinned host activations in, reduced result out, every step
+    x_h = x.cpu().pin_memory()
+    y_h = torch.empty((m, HIDDEN), dtype=torch.bfloat16).pin_memory()
+    x_d = torch.empty_like(x)
+
+    def e2e_step():
+        x_d.copy_(x_h, non_blocking=True)
+        y_h.copy_(layer.forward(x_d), non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_ms = time_region(torch, e2e_step, e2e_steps, True) / e2e_steps
+    if rank == 0:
+        # per-rank GEMM time at the tensor peak vs the bytes every rank must move through NVLink for the all-reduce
+        fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+        t_compute = layer.flops(m) / world / (fp8_peak * 1e12)
+        t_link = 2.0 * (world - 1) / world * m * HIDDEN * 2 / 770e9
+        target = max(t_compute, t_link)
+        kernels_per_step = (min(chunks, m // 256) if world > 1 else 1) * 7
+        line = {
+            "metric": "quant_gemm_tflops_prefill", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8_e4m3" if variant == "fp8" else "w4a16", "data": "synthetic",
+            "config": {"workload": f"tp_swiglu_mlp_{variant}_hidden8192_inter28672_m{m}", "parallelism": f"tp{world}",
+                       "all_reduce": "nccl bf16, one per M-chunk, overlapped on a side stream", "m_chunks": chunks,
+                       "l2": "weights per rank exceed the 126 MB L2 up to tp8 (88 MB FP8 per rank at tp8 plus activations)"},
+            "roofline": {"bound": "tensor", "achieved": value, "peak": fp8_peak * world, "unit": "TFLOP/s", "frac": value / (fp8_peak * world),
+                         "traffic": None, "target_ms": target * 1e3, "frac_of_target": target * 1e3 / ms,
+                         "peak_note": "per rank: max(flop / (2 x measured bf16 sustained), all-reduce bytes / 770 GB/s)"},
+            "e2e": {"value": layer.flops(m) / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": m * HIDDEN * 2,
+                    "d2h_bytes_per_step": m * HIDDEN * 2, "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": args.steps * kernels_per_step, "clocks": clocks, "extras": {"decode_points": small},
+        }
+        print(json.dumps(line), flush=True)
+
+
 def run_ours(args):
     import torch
     if not torch.cuda.is_available():
@@ -258,6 +357,11 @@ def run_ours(args):
     if dist_on:
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks = load_peaks()
+    if dist_on:
+        run_tp_mlp(args, torch, world, rank, local_rank, peaks)
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+        return
 
     g = torch.Generator(device="cuda").manual_seed(rank)
     a = torch.randn((M, K), generator=g, device="cuda").to(torch.bfloat16)
@@ -309,7 +413,10 @@ def run_ours(args):
     extra = None
     cpu = None
     if rank == 0 and not args.no_extras:
+        del a_h, b_h, y_h, a_d, b_d, qa2, qb2
+        torch.cuda.empty_cache()
         extra = extras(torch, ops, peaks)
+        extra.update(mlp_extras(torch, peaks))
     if rank == 0 and world == 1:
         from oracle import oracle as orc
         threads = orc.max_threads()

@@ -135,6 +135,10 @@ OXQ_API int32_t oxq_nvfp4_quant(oxq_handle* h, const void* x_dev, int x_dtype, i
 OXQ_API int32_t oxq_nvfp4_dequant(oxq_handle* h, const uint8_t* packed_dev, const uint8_t* sf_rowmajor_dev,
                           const float* stats_dev, int64_t rows, int64_t k, void* y_dev, int y_dtype);
 
+/* ---- SwiGLU on an interleaved gate/up product: h = silu(gate) * up (crates/oxicuda-lm/src/layer/ffn.rs:25-27, :245-249).
+ *      gu_dev is [m x 2n] bf16 in blocks of 128 gate columns followed by the 128 matching up columns; n % 128 == 0. */
+OXQ_API int32_t oxq_swiglu_interleaved(oxq_handle* h, const void* gu_bf16_dev, int64_t m, int64_t n, void* h_bf16_dev);
+
 /* ---- GEMMs: stand behind gemm<T> (crates/oxicuda-blas/src/level3/gemm_api.rs:73-138) for the element
  *      types that entry point cannot run in the reference, and behind the low-precision configs of
  *      crates/oxicuda-blas/src/precision/{int_ops,fp8_ops,fp4_fp6_ops}.rs.
@@ -143,6 +147,19 @@ OXQ_API int32_t oxq_nvfp4_dequant(oxq_handle* h, const uint8_t* packed_dev, cons
 OXQ_API int32_t oxq_gemm_fp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x_dev, int64_t ldx,
                      const uint8_t* w_dev, int64_t ldw, const float* sx_dev, const float* sw_dev,
                      void* y_bf16_dev, int64_t ldy);
+/* The same FP8 GEMM with the SwiGLU of SwiGluFfn::forward (crates/oxicuda-lm/src/layer/ffn.rs:235-254) fused into
+ * its epilogue.  w_gu_dev holds the gate and up projection weights interleaved in blocks of 128 rows
+ * ([gate rows 0..127][up rows 0..127][gate rows 128..255]...), n2 = 2 * intermediate rows in total (multiple of 256);
+ * H[m x n2/2] = bf16(silu(g) * u) with g, u = the scaled gate / up products. */
+OXQ_API int32_t oxq_gemm_fp8_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, const uint8_t* x_dev, int64_t ldx,
+                            const uint8_t* w_gu_dev, int64_t ldw, const float* sx_dev, const float* sw_dev,
+                            void* h_bf16_dev, int64_t ldh);
+/* bf16 GEMM behind gemm<bf16> (gemm_api.rs:73-138; alpha = 1, beta = 0, op(B) = W^T): the consumer of weights
+ * dequantised to bf16 (W4A16 at prefill shapes) and its SwiGLU-fused form.  K % 8 == 0. */
+OXQ_API int32_t oxq_gemm_bf16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x_bf16_dev, int64_t ldx,
+                      const void* w_bf16_dev, int64_t ldw, void* y_bf16_dev, int64_t ldy);
+OXQ_API int32_t oxq_gemm_bf16_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, const void* x_bf16_dev, int64_t ldx,
+                             const void* w_gu_bf16_dev, int64_t ldw, void* h_bf16_dev, int64_t ldh);
 /* W8A8 (Int8GemmConfig, int_ops.rs:79-189): Y = bf16(s32(X . W^T) * sx_rows[m] * sw_rows[n]). */
 OXQ_API int32_t oxq_gemm_w8a8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const int8_t* x_dev, int64_t ldx,
                       const int8_t* w_dev, int64_t ldw, const float* sx_rows_dev, const float* sw_rows_dev,
@@ -151,8 +168,10 @@ OXQ_API int32_t oxq_gemm_w8a8(oxq_handle* h, int64_t m, int64_t n, int64_t k, co
 OXQ_API int32_t oxq_gemm_w8a32(oxq_handle* h, int64_t m, int64_t n, int64_t k, const float* x_dev,
                        const int8_t* w_dev, const float* sw_rows_dev, float* y_dev);
 /* W4A16 weight-only (Int4GemmConfig, int_ops.rs:215-355; quantized operand is the weight):
- * Y = bf16(X_bf16 . dequant(W)^T).  Workspace: oxq_gemm_w4a16_workspace_bytes; it must be zero-filled
- * before its first use and is left zero-filled by every call. */
+ * Y = bf16(X_bf16 . dequant(W)^T).  m <= 32 runs the HBM-bound decode kernel (split-K partial sums in the
+ * workspace, which must be zero-filled before its first use and is left zero-filled by every call); m > 32
+ * dequantises the weight to bf16 in the workspace and runs the tensor-core GEMM (n % 8 == 0).
+ * Workspace size: oxq_gemm_w4a16_workspace_bytes(m, n, k). */
 OXQ_API size_t oxq_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k);
 OXQ_API int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x_bf16_dev,
                        const uint32_t* codes_dev, const uint16_t* scales_f16_dev, const uint32_t* zeros_packed_dev,

@@ -402,3 +402,58 @@ def ref_tp_swiglu_mlp(x, w_gate, w_up, w_down, tp, threads=1):
 
 def max_threads() -> int:
     return int(lib().orc_max_threads())
+
+
+# --------------------------------------------------------------------------- quantized TP MLP (spec)
+
+def _interleave_gate_up(wg, wu):
+    inter, k = wg.shape
+    return np.stack([wg.reshape(inter // 128, 128, k), wu.reshape(inter // 128, 128, k)], axis=1).reshape(2 * inter, k)
+
+
+def _deinterleave_cols(gu):
+    m, n2 = gu.shape
+    t = gu.reshape(m, n2 // 256, 2, 128)
+    return t[:, :, 0].reshape(m, n2 // 2), t[:, :, 1].reshape(m, n2 // 2)
+
+
+def spec_tp_mlp(x_bf16_bits, w_gate, w_up, w_down, tp, variant="fp8", threads=0):
+    """Quantized tensor-parallel SwiGLU MLP with the quantization points of the GPU layer: weights of each
+    shard quantised once (fp8: one scale for the fused gate/up shard and one for the down shard; w4a16: uint4
+    g128), x quantised per tensor (fp8), h rounded to bf16 and (fp8) quantised per shard, each rank's partial
+    rounded to bf16, partials summed in rank order in f32 (RowLinear::all_reduce), result rounded to bf16.
+    Matrix products are f32 numpy matmuls of the dequantised operands ("dequantise-then-f32").
+    Returns bf16 bit patterns [M x hidden]."""
+    del threads
+    x = bf16_bits_to_f32(x_bf16_bits)
+    inter = w_gate.shape[0]
+    sh = inter // tp
+    parts = []
+    if variant == "fp8":
+        sx = spec_fp8_scale(spec_absmax(x_bf16_bits))
+        dx = spec_fp8_dequant(spec_fp8_quant(x_bf16_bits, float(sx)), 1.0)
+    for r in range(tp):
+        wgu = np.ascontiguousarray(_interleave_gate_up(w_gate[r * sh:(r + 1) * sh], w_up[r * sh:(r + 1) * sh]), np.float32)
+        wd = np.ascontiguousarray(w_down[:, r * sh:(r + 1) * sh], np.float32)
+        if variant == "fp8":
+            s_gu = spec_fp8_scale(spec_absmax(wgu))
+            d_gu = spec_fp8_dequant(spec_fp8_quant(wgu, float(s_gu)), 1.0)
+            gu = (dx @ d_gu.T) * (np.float32(sx) * np.float32(s_gu))
+            g, u = _deinterleave_cols(gu)
+            h_bits = f32_to_bf16_bits(ref_silu_mul(g, u))
+            s_h = spec_fp8_scale(spec_absmax(h_bits))
+            dh = spec_fp8_dequant(spec_fp8_quant(h_bits, float(s_h)), 1.0)
+            s_d = spec_fp8_scale(spec_absmax(wd))
+            dd = spec_fp8_dequant(spec_fp8_quant(wd, float(s_d)), 1.0)
+            part = (dh @ dd.T) * (np.float32(s_h) * np.float32(s_d))
+        else:
+            c, s, z = spec_int4g_quant(wgu, 128, ROUND_HALF_AWAY)
+            d_gu = spec_int4g_dequant(c, s, z, wgu.shape[0], wgu.shape[1], 128)
+            gu = bf16_bits_to_f32(f32_to_bf16_bits(x @ d_gu.T))
+            g, u = _deinterleave_cols(gu)
+            h = bf16_bits_to_f32(f32_to_bf16_bits(ref_silu_mul(g, u)))
+            c, s, z = spec_int4g_quant(wd, 128, ROUND_HALF_AWAY)
+            dd = spec_int4g_dequant(c, s, z, wd.shape[0], wd.shape[1], 128)
+            part = h @ dd.T
+        parts.append(bf16_bits_to_f32(f32_to_bf16_bits(part.astype(np.float32))))
+    return f32_to_bf16_bits(ref_all_reduce_sum(parts))

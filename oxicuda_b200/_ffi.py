@@ -29,12 +29,16 @@ SIGNATURES = {
     "oxq_fp8_dequant": (_i32, [_vp, _vp, _i64, _vp, _vp, _int, _int]),
     "oxq_int4g_quant_pack": (_i32, [_vp, _vp, _int, _i64, _i64, _int, _vp, _vp, _vp, _int]),
     "oxq_int4g_dequant": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _int]),
+    "oxq_swiglu_interleaved": (_i32, [_vp, _vp, _i64, _i64, _vp]),
     "oxq_sf_mma_bytes": (_sz, [_i64, _i64]),
     "oxq_mxfp8_quant": (_i32, [_vp, _vp, _int, _i64, _i64, _vp, _vp, _vp]),
     "oxq_mxfp8_dequant": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp, _int]),
     "oxq_nvfp4_quant": (_i32, [_vp, _vp, _int, _i64, _i64, _vp, _vp, _vp, _vp]),
     "oxq_nvfp4_dequant": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _vp, _int]),
     "oxq_gemm_fp8": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64]),
+    "oxq_gemm_fp8_swiglu": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64]),
+    "oxq_gemm_bf16": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64]),
+    "oxq_gemm_bf16_swiglu": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64]),
     "oxq_gemm_w8a8": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64]),
     "oxq_gemm_w8a32": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
     "oxq_gemm_w4a16_workspace_bytes": (_sz, [_i64, _i64, _i64]),

@@ -264,8 +264,8 @@ using namespace oxq::decode;
 extern "C" {
 
 size_t oxq_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
-    (void)k;
     if (m <= 0 || n <= 0) return 0;
+    if (m > 32) return (((size_t)n * (size_t)k * 2) + 255) & ~(size_t)255;      // bf16 copy of the dequantised weight
     size_t f = (size_t)m * (size_t)n * sizeof(float);
     f = (f + 255) & ~(size_t)255;
     return f + (((size_t)(n + W4_ROWS_PER_CTA - 1) / W4_ROWS_PER_CTA) * sizeof(int) + 255 & ~(size_t)255);
@@ -280,7 +280,15 @@ int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const voi
     if (k % 8 != 0) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "K must be a multiple of 8 for INT4 packing, got %lld", (long long)k);
     if (!(group == 32 || group == 64 || group == 128 || group == 256)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "group size %d not in {32,64,128,256}", group);
     if (k % group != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "k %lld is not divisible by group size %d", (long long)k, group);
-    if (m > 32) OXQ_FAIL(h, OXQ_ERR_UNSUPPORTED_OPERATION, "oxq_gemm_w4a16 covers decode shapes (m <= 32), got m = %lld", (long long)m);
+    if (m > 32) {
+        // Prefill shapes are tensor-bound: dequantise the weight once to bf16 in the workspace (which needs
+        // no zero fill on this path), then run the bf16 tensor-core GEMM.
+        const size_t need = oxq_gemm_w4a16_workspace_bytes(m, n, k);
+        if (!ws || ws_bytes < need || ((uintptr_t)ws & 15u))
+            OXQ_FAIL(h, OXQ_ERR_BUFFER_TOO_SMALL, "workspace: expected at least %zu bytes, got %zu", need, ws_bytes);
+        if (int32_t rc = oxq_int4g_dequant(h, codes, scales, zeros, n, k, group, ws, OXQ_BF16)) return rc;
+        return oxq_gemm_bf16(h, m, n, k, x, k, ws, k, y, n);
+    }
     if (group % 128 != 0 || k % 128 != 0) OXQ_FAIL(h, OXQ_ERR_UNSUPPORTED_OPERATION, "decode kernel needs group and k to be multiples of 128");
     if (((uintptr_t)x & 15u) || ((uintptr_t)codes & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "x and codes must be 16-byte aligned");
     if (n > (int64_t)INT32_MAX / 64 || k > INT32_MAX / 64) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "dimension too large");

@@ -10,11 +10,16 @@
 //   Y[M x N] = X[M x K] * W[N x K]^T, both operands K-contiguous ("K-major"), f32 / s32 accumulate.
 #include "oxq_common.cuh"
 #include "oxq_tc.cuh"
+#include <stdlib.h>
 
 namespace oxq {
 namespace tc {
 
-enum { KIND_F8 = 0, KIND_I8 = 1, KIND_MXF8 = 2, KIND_NVF4 = 3 };
+enum { KIND_F8 = 0, KIND_I8 = 1, KIND_MXF8 = 2, KIND_NVF4 = 3, KIND_BF16 = 4 };
+// Epilogues: EPI_SCALE stores acc * scale; EPI_SWIGLU treats each 256-column tile as 128 gate columns
+// followed by the 128 matching up columns and stores silu(gate) * up (SwiGluFfn::forward,
+// crates/oxicuda-lm/src/layer/ffn.rs:235-254, fused into the gate/up projection).
+enum { EPI_SCALE = 0, EPI_SWIGLU = 1 };
 
 constexpr int BM = 128;               // rows of X per tile == tensor-memory lanes
 constexpr int BKB = 128;              // bytes of K per stage == one swizzle atom
@@ -28,6 +33,7 @@ struct GemmParams {
     const uint8_t* sfa; const uint8_t* sfb;   // tiled scale factors (block-scaled kinds)
     int sf_col_tiles;                 // 4-column scale-factor tiles per row tile
     int sfa_row_tiles, sfb_row_tiles;
+    int group_m;                      // M-tiles per rasterisation group (L2 reuse of the X panel)
     int32_t* status;
 };
 
@@ -51,7 +57,20 @@ struct Cfg {
     static_assert(!kScaled || kSfbCol + 8 * kSfChunks <= 512, "tensor memory overflow");
 };
 
-template <int KIND, int BN>
+// Tiles are walked in groups of `group_m` M-tiles: inside a group M runs fastest, then N, so the
+// CTAs of one wave share a narrow X panel (it stays in L2 for the whole sweep over N) and each
+// W tile is used by group_m CTAs at about the same time.
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+    const int per_group = group_m * tiles_n;
+    const int g = tile / per_group;
+    const int first_m = g * group_m;
+    const int gm = min(group_m, tiles_m - first_m);
+    const int r = tile - g * per_group;
+    tn = r / gm;
+    tm = first_m + (r - tn * gm);
+}
+
+template <int KIND, int BN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
     using C = Cfg<KIND, BN>;
@@ -92,7 +111,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+                int tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+                const int m0 = tm * BM, n0 = tn * BN;
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                     const uint32_t full = bar_full + 8 * stage;
@@ -124,13 +145,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (lane == 0) {
             constexpr uint32_t idesc =
                 KIND == KIND_F8 ? idesc_dense(1, 0, 0, BM, BN) :
+                KIND == KIND_BF16 ? idesc_dense(1, 1, 1, BM, BN) :
                 KIND == KIND_I8 ? idesc_dense(2, 1, 1, BM, BN) :
                 KIND == KIND_MXF8 ? idesc_block_scaled(0, 0, 1, BM, BN) : idesc_block_scaled(1, 1, 0, BM, BN);
             int stage = 0; uint32_t phase = 0;
             int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int n0 = (tile / tiles_m) * BN;
+                int tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+                const int n0 = tn * BN;
                 if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * C::kAccStride;
@@ -155,6 +179,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         const uint64_t a = adesc + (uint64_t)(k * 2), b = bdesc + (uint64_t)(k * 2);
                         const uint32_t accum = (kb | k) != 0;
                         if (KIND == KIND_F8) mma_f8f6f4(d_tmem, a, b, idesc, accum);
+                        else if (KIND == KIND_BF16) mma_f16(d_tmem, a, b, idesc, accum);
                         else if (KIND == KIND_I8) mma_i8(d_tmem, a, b, idesc, accum);
                         else {
                             // tile rows [n0, n0+BN) start (n0 % 128) / 32 row-groups into the first scale-factor tile
@@ -186,18 +211,57 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (KIND == KIND_F8 || KIND == KIND_NVF4) tensor_scale = __ldg(p.s0) * __ldg(p.s1);
         __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y);
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-            const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+            const int m0 = tm * BM, n0 = tn * BN;
             bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
             tc_fence_after();
             const int row = m0 + quarter * 32 + lane;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * C::kAccStride;
             float row_scale = 1.0f;
             if (KIND == KIND_I8 && row < p.m) row_scale = __ldg(p.s0 + row);
+            if (EPI == EPI_SWIGLU) {
+                // columns [0, BN/2) of the tile are gate, [BN/2, BN) the matching up columns
+                const int out_n = p.n >> 1;
+#pragma unroll 1
+                for (int c = 0; c < BN / 64; c++) {
+                    uint32_t rg[32], ru[32];
+                    tmem_ld_32x32b_x32(t_row + c * 32, rg);
+                    tmem_ld_32x32b_x32(t_row + BN / 2 + c * 32, ru);
+                    tmem_ld_wait();
+                    const int col0 = (n0 >> 1) + c * 32;
+                    if (row < p.m && col0 < out_n) {
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const float gt = __uint_as_float(rg[j]) * tensor_scale, up = __uint_as_float(ru[j]) * tensor_scale;
+                            v[j] = __fdividef(gt, 1.0f + __expf(-gt)) * up;
+                        }
+                        __nv_bfloat16* dst = y + (size_t)row * p.ldy + col0;
+                        if (col0 + 32 <= out_n) {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                uint4 o;
+                                __nv_bfloat162 t0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
+                                __nv_bfloat162 t1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                                __nv_bfloat162 t2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+                                __nv_bfloat162 t3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                                o.x = *reinterpret_cast<uint32_t*>(&t0); o.y = *reinterpret_cast<uint32_t*>(&t1);
+                                o.z = *reinterpret_cast<uint32_t*>(&t2); o.w = *reinterpret_cast<uint32_t*>(&t3);
+                                *reinterpret_cast<uint4*>(dst + 8 * j) = o;
+                            }
+                        } else {
+                            for (int j = 0; j < 32 && col0 + j < out_n; j++) dst[j] = __float2bfloat16_rn(v[j]);
+                        }
+                    }
+                }
+            } else {
 #pragma unroll 1
             for (int c = 0; c < BN / 32; c++) {
                 uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * C::kAccStride + c * 32, r);
+                tmem_ld_32x32b_x32(t_row + c * 32, r);
                 tmem_ld_wait();
                 const int col0 = n0 + c * 32;
                 if (row < p.m && col0 < p.n) {
@@ -224,6 +288,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         for (int j = 0; j < 32 && col0 + j < p.n; j++) dst[j] = __float2bfloat16_rn(v[j]);
                     }
                 }
+            }
             }
             tc_fence_before();
             __syncwarp();
@@ -273,7 +338,18 @@ static bool make_tmap_bytes(CUtensorMap* tm, const void* ptr, int64_t rows, int6
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int KIND, int BN>
+// M-tiles per rasterisation group; OXQ_GEMM_GROUP_M overrides the default for tuning runs.
+static int group_m_setting() {
+    static int v = 0;
+    if (v == 0) {
+        const char* e = getenv("OXQ_GEMM_GROUP_M");
+        v = e ? atoi(e) : 16;
+        if (v < 1) v = 1;
+    }
+    return v;
+}
+
+template <int KIND, int BN, int EPI = EPI_SCALE>
 static int32_t launch(oxq_handle* h, const void* x, int64_t ldx_bytes, const void* w, int64_t ldw_bytes, GemmParams p) {
     using C = Cfg<KIND, BN>;
     CUtensorMap tm_a, tm_b;
@@ -281,13 +357,14 @@ static int32_t launch(oxq_handle* h, const void* x, int64_t ldx_bytes, const voi
         OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned, leading dimensions multiples of 16 bytes)");
     static bool attr_set = false;
     if (!attr_set) {
-        OXQ_CUDA(h, cudaFuncSetAttribute(gemm_tc_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+        OXQ_CUDA(h, cudaFuncSetAttribute(gemm_tc_kernel<KIND, BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
         attr_set = true;
     }
     const int tiles = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
     const int grid = tiles < h->sm_count ? tiles : h->sm_count;
     p.status = h->dev_status;
-    gemm_tc_kernel<KIND, BN><<<grid, NUM_THREADS, C::kSmemBytes, h->stream>>>(tm_a, tm_b, p);
+    p.group_m = group_m_setting();
+    gemm_tc_kernel<KIND, BN, EPI><<<grid, NUM_THREADS, C::kSmemBytes, h->stream>>>(tm_a, tm_b, p);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -318,6 +395,39 @@ int32_t oxq_gemm_fp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8
     GemmParams p{};
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y; p.ldy = ldy; p.s0 = sx; p.s1 = sw;
     return launch<KIND_F8, 256>(h, x, ldx, w, ldw, p);
+}
+
+int32_t oxq_gemm_fp8_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, const uint8_t* x, int64_t ldx, const uint8_t* w_gu, int64_t ldw,
+                            const float* sx, const float* sw, void* hout, int64_t ldh) {
+    OXQ_CHECK_HANDLE(h);
+    if (n2 % 256 != 0) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "interleaved gate/up weight needs a multiple of 256 rows, got %lld", (long long)n2);
+    if (int32_t rc = check_gemm_args(h, m, n2 / 2, k, x, w_gu, hout, ldh)) return rc;
+    if (!sx || !sw) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
+    if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
+    GemmParams p{};
+    p.m = (int)m; p.n = (int)n2; p.k_bytes = (int)k; p.y = hout; p.ldy = ldh; p.s0 = sx; p.s1 = sw;
+    return launch<KIND_F8, 256, EPI_SWIGLU>(h, x, ldx, w_gu, ldw, p);
+}
+
+int32_t oxq_gemm_bf16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                      void* y, int64_t ldy) {
+    OXQ_CHECK_HANDLE(h);
+    if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
+    if ((k & 7) || ldx < k || ldw < k || (ldx & 7) || (ldw & 7)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 8 and ld >= k");
+    GemmParams p{};
+    p.m = (int)m; p.n = (int)n; p.k_bytes = (int)(2 * k); p.y = y; p.ldy = ldy;
+    return launch<KIND_BF16, 256>(h, x, 2 * ldx, w, 2 * ldw, p);
+}
+
+int32_t oxq_gemm_bf16_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, const void* x, int64_t ldx, const void* w_gu, int64_t ldw,
+                             void* hout, int64_t ldh) {
+    OXQ_CHECK_HANDLE(h);
+    if (n2 % 256 != 0) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "interleaved gate/up weight needs a multiple of 256 rows, got %lld", (long long)n2);
+    if (int32_t rc = check_gemm_args(h, m, n2 / 2, k, x, w_gu, hout, ldh)) return rc;
+    if ((k & 7) || ldx < k || ldw < k || (ldx & 7) || (ldw & 7)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 8 and ld >= k");
+    GemmParams p{};
+    p.m = (int)m; p.n = (int)n2; p.k_bytes = (int)(2 * k); p.y = hout; p.ldy = ldh;
+    return launch<KIND_BF16, 256, EPI_SWIGLU>(h, x, 2 * ldx, w_gu, 2 * ldw, p);
 }
 
 int32_t oxq_gemm_w8a8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const int8_t* x, int64_t ldx, const int8_t* w, int64_t ldw,

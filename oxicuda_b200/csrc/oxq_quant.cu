@@ -475,6 +475,24 @@ __global__ void __launch_bounds__(256) nvfp4_dequant_kernel(const uint8_t* __res
     }
 }
 
+// h[m, j] = silu(gu[m, blk*256 + j%128]) * gu[m, blk*256 + 128 + j%128], blk = j / 128: the SwiGLU of
+// SwiGluFfn::forward on a gate/up product stored in the interleaved 128-column block order.
+__global__ void __launch_bounds__(256) swiglu_interleaved_kernel(const __nv_bfloat16* __restrict__ gu, int64_t m, int64_t n,
+                                                                 __nv_bfloat16* __restrict__ out) {
+    const int64_t nvec = m * n / 8;
+    for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t e = v * 8, row = e / n, j = e - row * n;
+        const __nv_bfloat16* g = gu + row * 2 * n + (j >> 7) * 256 + (j & 127);
+        Vec16<__nv_bfloat16> a = ld16(g), b = ld16(g + 128), o;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float gt = __bfloat162float(a.v[i]);
+            o.v[i] = __float2bfloat16_rn(__fdividef(gt, 1.0f + __expf(-gt)) * __bfloat162float(b.v[i]));
+        }
+        *reinterpret_cast<uint4*>(out + e) = *reinterpret_cast<uint4*>(&o);
+    }
+}
+
 static inline int grid_for(oxq_handle* h, int64_t work_items, int block, int ctas_per_sm) {
     int64_t need = (work_items + block - 1) / block;
     int64_t cap = (int64_t)h->sm_count * ctas_per_sm;
@@ -612,6 +630,17 @@ int32_t oxq_int4g_dequant(oxq_handle* h, const uint32_t* codes, const uint16_t* 
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     const int64_t nwords = rows * k / 8;
     DISPATCH_DTYPE(y_dtype, int4g_dequant_kernel<T><<<grid_for(h, nwords, 256, 16), 256, 0, h->stream>>>(codes, scales, zeros, nwords, group, (T*)y));
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_swiglu_interleaved(oxq_handle* h, const void* gu, int64_t m, int64_t n, void* out) {
+    OXQ_CHECK_HANDLE(h);
+    if (m <= 0 || n <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "swiglu: empty input");
+    if (n % 128 != 0) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "n must be a multiple of 128, got %lld", (long long)n);
+    if (!gu || !out || !aligned16(gu) || !aligned16(out)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    swiglu_interleaved_kernel<<<grid_for(h, m * n / 8, 256, 8), 256, 0, h->stream>>>((const __nv_bfloat16*)gu, m, n, (__nv_bfloat16*)out);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

@@ -1,0 +1,167 @@
+"""Tensor-parallel SwiGLU MLP over the quantized GEMMs: the host-side mirror of ColumnLinear / RowLinear
+(crates/oxicuda-dist-infer/src/tensor_parallel/{column_parallel,row_parallel}.rs) and SwiGluFfn
+(crates/oxicuda-lm/src/layer/ffn.rs:202-254).
+
+Sharding (identical to the reference's `from_full_weight` constructors):
+  * gate and up weights [inter x hidden] are split by output rows, rank r owns rows [r*inter/tp, (r+1)*inter/tp)
+    (ColumnLinear::from_full_weight, column_parallel.rs:115-166);
+  * the down weight [hidden x inter] is split by input columns, rank r owns columns [r*inter/tp, (r+1)*inter/tp)
+    of every row (RowLinear::from_full_weight, row_parallel.rs:109-168);
+  * h = silu(gate) * up is local (column shard r of gate/up is exactly the K slice the down shard r needs, so
+    ColumnLinear::all_gather is not needed);
+  * each rank produces a full [M x hidden] partial and one all-reduce(sum) combines them
+    (RowLinear::all_reduce, row_parallel.rs:199-223); the reference sums on the host in rank order, here it
+    is one NCCL all-reduce over NVLink, issued through torch.distributed.
+
+One process per GPU.  All arithmetic runs in liboxq_b200.so; torch supplies device memory, streams and the
+process group.
+"""
+from __future__ import annotations
+
+import torch
+
+VARIANTS = ("fp8", "w4a16")
+
+
+# ------------------------------------------------------------------------------------------------ sharding (host logic)
+
+def column_shard_rows(total_out: int, tp: int, rank: int) -> slice:
+    """Rows of a column-parallel weight owned by `rank` (column_parallel.rs:115-166).  total_out must divide."""
+    if tp < 1 or not (0 <= rank < tp):
+        raise ValueError(f"rank {rank} outside world of {tp}")
+    if total_out % tp != 0:
+        raise ValueError(f"features {total_out} not divisible by degree {tp}")       # DistInferError::NotDivisible
+    sh = total_out // tp
+    return slice(rank * sh, (rank + 1) * sh)
+
+
+def row_shard_cols(total_in: int, tp: int, rank: int) -> slice:
+    """Input columns of a row-parallel weight owned by `rank` (row_parallel.rs:109-168)."""
+    return column_shard_rows(total_in, tp, rank)
+
+
+def shard_mlp_weights(w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, tp: int, rank: int):
+    """(gate shard [inter/tp x hidden], up shard, down shard [hidden x inter/tp]) of rank `rank`."""
+    inter = w_gate.shape[0]
+    rows = column_shard_rows(inter, tp, rank)
+    return w_gate[rows].contiguous(), w_up[rows].contiguous(), w_down[:, row_shard_cols(inter, tp, rank)].contiguous()
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """Blocks of 128 gate rows followed by the 128 matching up rows: the layout the fused SwiGLU epilogue reads."""
+    inter, k = w_gate.shape
+    if inter % 128 != 0:
+        raise ValueError(f"intermediate shard of {inter} rows is not a multiple of 128")
+    return torch.stack([w_gate.reshape(inter // 128, 128, k), w_up.reshape(inter // 128, 128, k)], dim=1).reshape(2 * inter, k).contiguous()
+
+
+# ------------------------------------------------------------------------------------------------ the layer
+
+class TpSwiGluMlp:
+    """One rank's shard of a tensor-parallel SwiGLU MLP with quantized weights.
+
+    variant "fp8":   per-tensor E4M3 weights (one scale for the fused gate/up shard, one for the down shard),
+                     activations quantised on the fly per call (x per tensor; h per shard, so no max all-reduce).
+    variant "w4a16": uint4 group-128 asymmetric weights with f16 scales, bf16 activations.
+    """
+
+    def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, variant: str = "fp8",
+                 tp: int = 1, rank: int = 0, group=None, reduce_dtype: torch.dtype = torch.bfloat16, overlap_chunks: int = 1,
+                 already_sharded: bool = False):
+        """w_gate, w_up: [inter x hidden]; w_down: [hidden x inter] (full weights, cut here as the reference's
+        from_full_weight does), or this rank's shards when already_sharded is set."""
+        from . import ops
+        if variant not in VARIANTS:
+            raise ValueError(f"variant {variant!r} not in {VARIANTS}")
+        self.ops = ops
+        self.variant, self.tp, self.rank, self.group = variant, tp, rank, group
+        self.reduce_dtype = reduce_dtype
+        self.overlap_chunks = max(1, int(overlap_chunks))
+        self.hidden = w_gate.shape[1]
+        if already_sharded:
+            g, u, d = w_gate, w_up, w_down
+            self.inter = w_gate.shape[0] * tp
+        else:
+            self.inter = w_gate.shape[0]
+            g, u, d = shard_mlp_weights(w_gate, w_up, w_down, tp, rank)
+        self.inter_local = g.shape[0]
+        dev = torch.device("cuda", torch.cuda.current_device())
+        w_gu = interleave_gate_up(g, u).to(dev)
+        d = d.to(dev)
+        if variant == "fp8":
+            self.w_gu_q, st = ops.fp8_quant_dynamic(w_gu)
+            self.s_gu = st[1:].clone()
+            self.w_down_q, st = ops.fp8_quant_dynamic(d)
+            self.s_down = st[1:].clone()
+        else:
+            self.gu_codes, self.gu_scales, self.gu_zeros = ops.int4g_quant_pack(w_gu.float(), 128)
+            self.d_codes, self.d_scales, self.d_zeros = ops.int4g_quant_pack(d.float(), 128)
+            self._ws = {}
+        self._comm_stream = torch.cuda.Stream() if self.overlap_chunks > 1 else None
+
+    # -- local (per-rank) partial: [M x hidden] --------------------------------------------------
+    def forward_partial(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        ops = self.ops
+        if self.variant == "fp8":
+            xq, sx = ops.fp8_quant_dynamic(x)
+            h = ops.gemm_fp8_swiglu(xq, self.w_gu_q, sx[1:], self.s_gu)
+            hq, sh = ops.fp8_quant_dynamic(h)
+            return ops.gemm_fp8(hq, self.w_down_q, sh[1:], self.s_down, out=out)
+        m = x.shape[0]
+        ws1 = self._workspace(m, 2 * self.inter_local, self.hidden)
+        gu = ops.gemm_w4a16(x, self.gu_codes, self.gu_scales, self.gu_zeros, 128, workspace=ws1)
+        h = ops.swiglu_interleaved(gu)
+        ws2 = self._workspace(m, self.hidden, self.inter_local)
+        return ops.gemm_w4a16(h, self.d_codes, self.d_scales, self.d_zeros, 128, workspace=ws2, out=out)
+
+    def _workspace(self, m, n, k):
+        key = (m > 32, m if m <= 32 else 0, n, k)
+        if key not in self._ws:
+            self._ws[key] = self.ops.gemm_w4a16_workspace(m, n, k, "cuda")
+        return self._ws[key]
+
+    # -- full layer: partial + all-reduce ----------------------------------------------------------
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """x: bf16 [M x hidden], replicated on every rank.  Returns the reduced bf16 [M x hidden] on every rank."""
+        import torch.distributed as dist
+        if self.tp == 1:
+            return self.forward_partial(x)
+        m = x.shape[0]
+        chunks = min(self.overlap_chunks, max(1, m // 256))
+        if chunks <= 1:
+            y = self.forward_partial(x)
+            return self._all_reduce(y)
+        # M-chunk pipelining: the all-reduce of chunk i runs on a side stream while chunk i+1 computes
+        y = torch.empty((m, self.hidden), dtype=torch.bfloat16, device=x.device)
+        bounds = [(i * m) // chunks for i in range(chunks + 1)]
+        main = torch.cuda.current_stream()
+        for i in range(chunks):
+            lo, hi = bounds[i], bounds[i + 1]
+            self.forward_partial(x[lo:hi], out=y[lo:hi])
+            ev = torch.cuda.Event()
+            ev.record(main)
+            with torch.cuda.stream(self._comm_stream):
+                self._comm_stream.wait_event(ev)
+                dist.all_reduce(y[lo:hi], op=dist.ReduceOp.SUM, group=self.group)
+        main.wait_stream(self._comm_stream)
+        return y
+
+    def _all_reduce(self, y: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+        if self.reduce_dtype == torch.float32:
+            z = y.float()
+            dist.all_reduce(z, op=dist.ReduceOp.SUM, group=self.group)
+            return z.to(torch.bfloat16)
+        dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        return y
+
+    # -- bookkeeping for the benchmark -------------------------------------------------------------
+    def flops(self, m: int) -> float:
+        """Whole-layer flop count over all ranks: 2 * M * 3 * hidden * inter."""
+        return 2.0 * m * 3 * self.hidden * self.inter
+
+    def weight_bytes_local(self) -> int:
+        if self.variant == "fp8":
+            return self.w_gu_q.numel() + self.w_down_q.numel()
+        n = self.gu_codes.numel() * 4 + self.d_codes.numel() * 4
+        return n + (self.gu_scales.numel() + self.d_scales.numel()) * 2 + (self.gu_zeros.numel() + self.d_zeros.numel()) * 4

@@ -218,6 +218,51 @@ def gemm_fp8(x_q, w_q, sx, sw, out: torch.Tensor | None = None):
     return y
 
 
+def gemm_fp8_swiglu(x_q, w_gu_q, sx, sw, out: torch.Tensor | None = None):
+    """H = bf16(silu(g) * u); w_gu_q holds gate/up rows interleaved in blocks of 128 (see interleave_gate_up)."""
+    m, k = x_q.shape
+    n2 = w_gu_q.shape[0]
+    y = torch.empty((m, n2 // 2), dtype=torch.bfloat16, device=x_q.device) if out is None else out
+    handle(x_q.device.index).call("oxq_gemm_fp8_swiglu", m, n2, k, _p(x_q), x_q.stride(0), _p(w_gu_q), w_gu_q.stride(0),
+                                  _p(sx), _p(sw), _p(y), y.stride(0))
+    return y
+
+
+def gemm_bf16(x, w, out: torch.Tensor | None = None):
+    m, k = x.shape
+    n = w.shape[0]
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=x.device) if out is None else out
+    handle(x.device.index).call("oxq_gemm_bf16", m, n, k, _p(x), x.stride(0), _p(w), w.stride(0), _p(y), y.stride(0))
+    return y
+
+
+def gemm_bf16_swiglu(x, w_gu, out: torch.Tensor | None = None):
+    m, k = x.shape
+    n2 = w_gu.shape[0]
+    y = torch.empty((m, n2 // 2), dtype=torch.bfloat16, device=x.device) if out is None else out
+    handle(x.device.index).call("oxq_gemm_bf16_swiglu", m, n2, k, _p(x), x.stride(0), _p(w_gu), w_gu.stride(0), _p(y),
+                                y.stride(0))
+    return y
+
+
+def swiglu_interleaved(gu: torch.Tensor, out: torch.Tensor | None = None):
+    """gu [m x 2n] bf16 in interleaved 128-column blocks -> silu(gate) * up [m x n]."""
+    m, n2 = gu.shape
+    y = torch.empty((m, n2 // 2), dtype=torch.bfloat16, device=gu.device) if out is None else out
+    handle(gu.device.index).call("oxq_swiglu_interleaved", _p(gu), m, n2 // 2, _p(y))
+    return y
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """[inter x k] gate and up weights -> [2*inter x k] with blocks of 128 gate rows followed by the 128 matching
+    up rows (a one-off, load-time layout change; inter must be a multiple of 128)."""
+    inter, k = w_gate.shape
+    assert inter % 128 == 0 and w_up.shape == w_gate.shape
+    g = w_gate.reshape(inter // 128, 128, k)
+    u = w_up.reshape(inter // 128, 128, k)
+    return torch.stack([g, u], dim=1).reshape(2 * inter, k).contiguous()
+
+
 def gemm_w8a8(x_q, w_q, sx_rows, sw_rows, out: torch.Tensor | None = None):
     m, k = x_q.shape
     n = w_q.shape[0]

@@ -156,14 +156,76 @@ def test_gemm_w4a16_decode(ops, orc, m, nk):
     _check(_bf16_to_np(y2), ref, "w4a16 second call")
 
 
+@pytest.mark.parametrize("mnk", [(64, 256, 512), (200, 1000, 1024), (2048, 1024, 4096)])
+def test_gemm_w4a16_prefill(ops, orc, mnk):
+    m, n, k = mnk
+    w = orc.gaussian((n, k), 0.02, 0)
+    xb = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 1))
+    c, s, z = ops.int4g_quant_pack(to_dev(w), 128)
+    y = ops.gemm_w4a16(bf16_dev(xb), c, s, z, 128)
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    deq = orc.spec_int4g_dequant(u32(c), u16(s), u32(z), n, k, 128)
+    ref = (orc.bf16_bits_to_f32(xb).astype(np.float64) @ deq.astype(np.float64).T).astype(np.float32)
+    _check(_bf16_to_np(y), ref, f"w4a16 prefill {mnk}")
+
+
+@pytest.mark.parametrize("mnk", [(128, 256, 128), (300, 520, 384), (1024, 1024, 1024), (16, 264, 2048)])
+def test_gemm_bf16(ops, orc, mnk):
+    m, n, k = mnk
+    a = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 0))
+    b = orc.f32_to_bf16_bits(orc.gaussian((n, k), 0.02, 1))
+    y = ops.gemm_bf16(bf16_dev(a), bf16_dev(b))
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    ref = (orc.bf16_bits_to_f32(a).astype(np.float64) @ orc.bf16_bits_to_f32(b).astype(np.float64).T).astype(np.float32)
+    _check(_bf16_to_np(y), ref, f"bf16 {mnk}")
+
+
+@pytest.mark.parametrize("m", [1, 64, 300])
+def test_swiglu_fused_gemms(ops, orc, m):
+    """gate/up projection with the SwiGLU fused into the epilogue (FP8 and bf16) and the standalone SwiGLU kernel,
+    against silu(x) = x / (1 + exp(-x)) of the reference (crates/oxicuda-lm/src/layer/ffn.rs:25-27) in f32."""
+    inter, k = 384, 512
+    wg = orc.gaussian((inter, k), 0.05, 0)
+    wu = orc.gaussian((inter, k), 0.05, 2)
+    xb = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 1))
+    w_gu = ops.interleave_gate_up(to_dev(wg), to_dev(wu))
+    # fp8: one scale for the fused weight tensor
+    qw, sw = ops.fp8_quant_dynamic(w_gu)
+    qx, sx = ops.fp8_quant_dynamic(bf16_dev(xb))
+    h = ops.gemm_fp8_swiglu(qx, qw, sx[1:], sw[1:])
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    dq = orc.e4m3_to_f32(qw.cpu().numpy()).reshape(inter // 128, 2, 128, k)
+    dg, du = dq[:, 0].reshape(inter, k), dq[:, 1].reshape(inter, k)
+    dx = orc.e4m3_to_f32(qx.cpu().numpy())
+    s = np.float32(float(sx[1])) * np.float32(float(sw[1]))
+    ref = orc.ref_silu_mul((dx @ dg.T) * s, (dx @ du.T) * s)
+    _check(_bf16_to_np(h), ref, f"fp8 swiglu m={m}")
+    # bf16
+    wb = w_gu.to(torch.bfloat16)
+    h2 = ops.gemm_bf16_swiglu(bf16_dev(xb), wb)
+    wbf = wb.float().cpu().numpy().reshape(inter // 128, 2, 128, k)
+    xf = orc.bf16_bits_to_f32(xb)
+    ref2 = orc.ref_silu_mul(xf @ wbf[:, 0].reshape(inter, k).T, xf @ wbf[:, 1].reshape(inter, k).T)
+    _check(_bf16_to_np(h2), ref2, f"bf16 swiglu m={m}")
+    # standalone kernel on the un-fused product
+    gu = ops.gemm_bf16(bf16_dev(xb), wb)
+    h3 = ops.swiglu_interleaved(gu)
+    guf = gu.float().cpu().numpy().reshape(m, inter // 128, 2, 128)
+    ref3 = orc.ref_silu_mul(guf[:, :, 0].reshape(m, inter), guf[:, :, 1].reshape(m, inter))
+    _check(_bf16_to_np(h3), ref3, f"swiglu kernel m={m}")
+
+
 def test_gemm_w4a16_errors(ops, orc):
     from oxicuda_b200.errors import BlasError
     w = orc.gaussian((128, 256), 0.02, 0)
     c, s, z = ops.int4g_quant_pack(to_dev(w), 128)
     x = torch.zeros((64, 256), dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(BlasError) as e:
-        ops.gemm_w4a16(x, c, s, z, 128)
-    assert e.value.variant == "UnsupportedOperation"
+    with pytest.raises(BlasError) as e:                     # prefill path needs the bf16-weight workspace
+        ops.gemm_w4a16(x, c, s, z, 128, workspace=torch.zeros(256, dtype=torch.uint8, device="cuda"))
+    assert e.value.variant == "BufferTooSmall"
     with pytest.raises(BlasError) as e:
         ops.gemm_w4a16(x[:1], c, s, z, 48)
     assert e.value.variant == "InvalidArgument"

@@ -417,14 +417,20 @@ def _deinterleave_cols(gu):
     return t[:, :, 0].reshape(m, n2 // 2), t[:, :, 1].reshape(m, n2 // 2)
 
 
-def spec_tp_mlp(x_bf16_bits, w_gate, w_up, w_down, tp, variant="fp8", threads=0):
+def spec_tp_mlp(x_bf16_bits, w_gate, w_up, w_down, tp, variant="fp8", threads=0, m_chunks=1):
     """Quantized tensor-parallel SwiGLU MLP with the quantization points of the GPU layer: weights of each
     shard quantised once (fp8: one scale for the fused gate/up shard and one for the down shard; w4a16: uint4
     g128), x quantised per tensor (fp8), h rounded to bf16 and (fp8) quantised per shard, each rank's partial
     rounded to bf16, partials summed in rank order in f32 (RowLinear::all_reduce), result rounded to bf16.
     Matrix products are f32 numpy matmuls of the dequantised operands ("dequantise-then-f32").
+    With m_chunks > 1 the rows of x are processed in that many independent chunks (the GPU layer's
+    compute / all-reduce pipelining): activation scales are then per chunk.
     Returns bf16 bit patterns [M x hidden]."""
     del threads
+    if m_chunks > 1:
+        m = x_bf16_bits.shape[0]
+        b = [(i * m) // m_chunks for i in range(m_chunks + 1)]
+        return np.concatenate([spec_tp_mlp(x_bf16_bits[b[i]:b[i + 1]], w_gate, w_up, w_down, tp, variant) for i in range(m_chunks)])
     x = bf16_bits_to_f32(x_bf16_bits)
     inter = w_gate.shape[0]
     sh = inter // tp

@@ -343,7 +343,7 @@ static int group_m_setting() {
     static int v = 0;
     if (v == 0) {
         const char* e = getenv("OXQ_GEMM_GROUP_M");
-        v = e ? atoi(e) : 16;
+        v = e ? atoi(e) : 32;
         if (v < 1) v = 1;
     }
     return v;

@@ -1,0 +1,152 @@
+// Host-side mirror of the oxicuda-quant quantizer types over the C ABI of liboxq_b200 (include/oxq.h).
+// Same names, argument meaning and error behaviour as the reference (crates/oxicuda-quant/src/scheme/minmax.rs,
+// scheme/fp8.rs, error.rs); the arithmetic runs on the GPU.  Host-slice methods stage through device buffers
+// (H2D, kernel, D2H) exactly as the reference's signatures imply; *_device methods take device pointers.
+// Header-only; link with -loxq_b200 -lcudart.  There is no CPU fallback: without a device every call throws.
+#pragma once
+#include <cuda_runtime.h>
+#include <cmath>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <vector>
+#include "../../include/oxq.h"
+
+namespace oxicuda_quant {
+
+// QuantError (error.rs:10-58): `variant` carries the enum variant name.
+struct QuantError : std::runtime_error {
+    std::string variant;
+    QuantError(const std::string& v, const std::string& msg) : std::runtime_error(v + ": " + msg), variant(v) {}
+};
+
+enum class QuantScheme { Symmetric, Asymmetric };                       // minmax.rs:27-33
+struct QuantGranularity {                                               // minmax.rs:37-44
+    enum Kind { PerTensor, PerChannel, PerGroup } kind = PerTensor;
+    size_t channel_axis = 0, group_size = 0;
+    static QuantGranularity per_tensor() { return {}; }
+    static QuantGranularity per_channel(size_t axis) { QuantGranularity g; g.kind = PerChannel; g.channel_axis = axis; return g; }
+    static QuantGranularity per_group(size_t gs) { QuantGranularity g; g.kind = PerGroup; g.group_size = gs; return g; }
+};
+struct QuantParams {                                                    // minmax.rs:50-79
+    std::vector<float> scales;
+    std::vector<int32_t> zero_points;
+    uint32_t bits = 8;
+    QuantScheme scheme = QuantScheme::Symmetric;
+    float q_max() const { return scheme == QuantScheme::Symmetric ? float(1 << (bits - 1)) - 1.0f : float(1 << bits) - 1.0f; }
+    float q_min() const { return scheme == QuantScheme::Symmetric ? -float(1 << (bits - 1)) : 0.0f; }
+};
+
+namespace detail {
+inline void check(int32_t rc, oxq_handle* h) {
+    if (rc == OXQ_OK) return;
+    throw QuantError(oxq_status_name(rc), h ? oxq_last_error_string(h) : "");
+}
+inline void cuda(cudaError_t e) { if (e != cudaSuccess) throw QuantError("Cuda", cudaGetErrorString(e)); }
+template <typename T> struct DevBuf {
+    T* p = nullptr; size_t n = 0;
+    explicit DevBuf(size_t count) : n(count) { if (n) cuda(cudaMalloc(&p, n * sizeof(T))); }
+    ~DevBuf() { if (p) cudaFree(p); }
+    DevBuf(const DevBuf&) = delete; DevBuf& operator=(const DevBuf&) = delete;
+    void upload(const T* h) { if (n) cuda(cudaMemcpy(p, h, n * sizeof(T), cudaMemcpyHostToDevice)); }
+    void download(T* h) const { if (n) cuda(cudaMemcpy(h, p, n * sizeof(T), cudaMemcpyDeviceToHost)); }
+};
+struct Handle {                                                          // owns one oxq_handle on the default stream
+    oxq_handle* h = nullptr;
+    explicit Handle(int device = 0) { check(oxq_handle_create(device, nullptr, &h), nullptr); }
+    ~Handle() { if (h) oxq_handle_destroy(h); }
+    Handle(const Handle&) = delete; Handle& operator=(const Handle&) = delete;
+};
+}  // namespace detail
+
+// MinMaxQuantizer (minmax.rs:86-324).  The accelerated configurations are the two the hot path names:
+// 8-bit symmetric per channel (calibrate_2d + quantize_grouped(group = cols)) and 4-bit asymmetric per group
+// (f16 scales on the device side; see quantize_int4_per_group).  rounding follows OXQ_ROUND_*.
+class MinMaxQuantizer {
+public:
+    MinMaxQuantizer(uint32_t bits, QuantScheme scheme, QuantGranularity gran, int rounding = OXQ_ROUND_HALF_AWAY)
+        : bits_(bits), scheme_(scheme), gran_(gran), rounding_(rounding) {
+        if (bits == 0 || bits > 16) throw std::invalid_argument("bits must be in [1, 16]");   // new() panics, minmax.rs:99-100
+    }
+    static MinMaxQuantizer int8_symmetric() { return {8, QuantScheme::Symmetric, QuantGranularity::per_tensor()}; }
+    static MinMaxQuantizer int4_per_group(size_t g) { return {4, QuantScheme::Symmetric, QuantGranularity::per_group(g)}; }
+
+    // calibrate_2d + quantize_grouped(group = cols) in one pass over the data: returns per-row params and int8 codes
+    // widened to i32 as the reference's Vec<i32>.  (minmax.rs:179-207, :275-299)
+    QuantParams calibrate_quantize_2d(const std::vector<float>& t, size_t rows, size_t cols, std::vector<int32_t>& codes) const {
+        if (rows == 0) throw QuantError("EmptyInput", "calibrate_2d: rows == 0");
+        if (cols == 0) throw QuantError("DimensionMismatch", "dimension mismatch: expected 1, got 0");
+        if (bits_ != 8 || scheme_ != QuantScheme::Symmetric) throw QuantError("InvalidConfig", "device path covers 8-bit symmetric per channel");
+        if (t.size() != rows * cols) throw QuantError("DimensionMismatch", "tensor length != rows * cols");
+        detail::Handle h;
+        detail::DevBuf<float> x(rows * cols), s(rows);
+        detail::DevBuf<int8_t> q(rows * cols);
+        x.upload(t.data());
+        detail::check(oxq_int8_quant_rows(h.h, x.p, (int64_t)rows, (int64_t)cols, q.p, s.p, rounding_), h.h);
+        detail::cuda(cudaDeviceSynchronize());
+        QuantParams p;
+        p.bits = 8; p.scheme = QuantScheme::Symmetric;
+        p.scales.resize(rows); p.zero_points.assign(rows, 0);
+        s.download(p.scales.data());
+        for (float sc : p.scales)                                        // minmax.rs:234-236
+            if (!std::isfinite(sc) || sc <= 0.0f) throw QuantError("InvalidScale", "invalid scale " + std::to_string(sc));
+        std::vector<int8_t> q8(rows * cols);
+        q.download(q8.data());
+        codes.assign(q8.begin(), q8.end());
+        return p;
+    }
+    // dequantize_grouped (minmax.rs:309-324) for the per-row INT8 case
+    std::vector<float> dequantize_2d(const std::vector<int32_t>& codes, const QuantParams& p, size_t rows, size_t cols) const {
+        detail::Handle h;
+        std::vector<int8_t> q8(codes.begin(), codes.end());
+        detail::DevBuf<int8_t> q(rows * cols);
+        detail::DevBuf<float> s(rows), y(rows * cols);
+        q.upload(q8.data()); s.upload(p.scales.data());
+        detail::check(oxq_int8_dequant_rows(h.h, q.p, s.p, (int64_t)rows, (int64_t)cols, y.p), h.h);
+        detail::cuda(cudaDeviceSynchronize());
+        std::vector<float> out(rows * cols);
+        y.download(out.data());
+        return out;
+    }
+private:
+    uint32_t bits_; QuantScheme scheme_; QuantGranularity gran_; int rounding_;
+};
+
+// Fp8Codec (fp8.rs:84-159), E4M3.  `refcompat` selects the literal reference bit manipulation; otherwise the
+// hardware RNE/satfinite conversion.  Non-finite input is always an error (fp8.rs:116-118).
+class Fp8Codec {
+public:
+    explicit Fp8Codec(bool refcompat = false) : mode_(refcompat ? OXQ_FP8_REFCOMPAT : OXQ_FP8_SPEC_RNE) {}
+    static Fp8Codec e4m3() { return Fp8Codec(false); }
+    std::vector<uint8_t> encode(const std::vector<float>& data) const {
+        for (float v : data) if (!std::isfinite(v)) throw QuantError("NonFiniteFp8", "FP8 encoding received non-finite value");
+        if (data.empty()) return {};
+        detail::Handle h;
+        detail::DevBuf<float> x(data.size()), one(1);
+        detail::DevBuf<uint8_t> q(data.size());
+        const float unit = 1.0f;
+        x.upload(data.data()); one.upload(&unit);
+        detail::check(oxq_fp8_quant(h.h, x.p, OXQ_F32, (int64_t)data.size(), one.p, q.p, mode_), h.h);
+        detail::cuda(cudaDeviceSynchronize());
+        std::vector<uint8_t> out(data.size());
+        q.download(out.data());
+        return out;
+    }
+    std::vector<float> decode(const std::vector<uint8_t>& data) const {
+        if (data.empty()) return {};
+        detail::Handle h;
+        detail::DevBuf<uint8_t> q(data.size());
+        detail::DevBuf<float> y(data.size()), one(1);
+        const float unit = 1.0f;
+        q.upload(data.data()); one.upload(&unit);
+        detail::check(oxq_fp8_dequant(h.h, q.p, (int64_t)data.size(), one.p, y.p, OXQ_F32, mode_), h.h);
+        detail::cuda(cudaDeviceSynchronize());
+        std::vector<float> out(data.size());
+        y.download(out.data());
+        return out;
+    }
+private:
+    int mode_;
+};
+
+}  // namespace oxicuda_quant

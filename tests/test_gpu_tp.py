@@ -68,7 +68,7 @@ def _nccl_rank(rank, world, port, variant, q):
         layer = TpSwiGluMlp(torch.from_numpy(wg), torch.from_numpy(wu), torch.from_numpy(wd), variant, tp=world, rank=rank,
                             overlap_chunks=chunks)
         y = layer.forward(x).float().cpu().numpy()
-        ref = orc.bf16_bits_to_f32(orc.spec_tp_mlp(xb, wg, wu, wd, world, variant))
+        ref = orc.bf16_bits_to_f32(orc.spec_tp_mlp(xb, wg, wu, wd, world, variant, m_chunks=chunks))
         errs.append(float(np.abs(y - ref).max() / np.abs(ref).max()))
     q.put((rank, errs))
     dist.barrier()

@@ -308,6 +308,218 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
 }
 
+// ---- 2-CTA variant of the dense kinds --------------------------------------------------------------
+// A cluster of two CTAs computes one 256 x 256 tile: CTA r loads rows [128r, 128r+128) of the X tile and
+// rows [128r, 128r+128) of the W tile (so every operand byte is fetched by one CTA only and the W bytes per
+// CTA halve), CTA 0 issues tcgen05.mma.cta_group::2 (M = 256 across the pair, N = 256), each CTA keeps its
+// 128 accumulator rows in its own tensor memory and runs its own epilogue.  Full barriers live in CTA 0
+// (both CTAs' TMA loads count bytes there), empty / accumulator-full barriers are signalled in both CTAs by
+// a multicast commit, accumulator-empty arrivals go to CTA 0.
+constexpr int T2_STAGES = 6;
+constexpr int T2_STAGE_BYTES = 2 * BM * BKB;                      // 16 KB of X + 16 KB of W per CTA
+constexpr int T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + 2048;
+
+template <int KIND>
+__device__ __forceinline__ void epilogue_store_scale(const uint32_t (&r)[32], int row, int col0, const GemmParams& p, float tensor_scale,
+                                                     float row_scale, __nv_bfloat16* y) {
+    if (row >= p.m || col0 >= p.n) return;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+        if (KIND == KIND_I8) v[j] = (float)(int)r[j] * (row_scale * (col0 + j < p.n ? __ldg(p.s1 + col0 + j) : 0.0f));
+        else v[j] = __uint_as_float(r[j]) * tensor_scale;
+    }
+    __nv_bfloat16* dst = y + (size_t)row * p.ldy + col0;
+    if (col0 + 32 <= p.n) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint4 o;
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
+            __nv_bfloat162 t1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+            __nv_bfloat162 t3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+            o.x = *reinterpret_cast<uint32_t*>(&t0); o.y = *reinterpret_cast<uint32_t*>(&t1);
+            o.z = *reinterpret_cast<uint32_t*>(&t2); o.w = *reinterpret_cast<uint32_t*>(&t3);
+            *reinterpret_cast<uint4*>(dst + 8 * j) = o;
+        }
+    } else {
+        for (int j = 0; j < 32 && col0 + j < p.n; j++) dst[j] = __float2bfloat16_rn(v[j]);
+    }
+}
+
+__device__ __forceinline__ void epilogue_store_swiglu(const uint32_t (&rg)[32], const uint32_t (&ru)[32], int row, int col0, int out_n,
+                                                      const GemmParams& p, float tensor_scale, __nv_bfloat16* y) {
+    if (row >= p.m || col0 >= out_n) return;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+        const float gt = __uint_as_float(rg[j]) * tensor_scale, up = __uint_as_float(ru[j]) * tensor_scale;
+        v[j] = __fdividef(gt, 1.0f + __expf(-gt)) * up;
+    }
+    __nv_bfloat16* dst = y + (size_t)row * p.ldy + col0;
+    if (col0 + 32 <= out_n) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint4 o;
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
+            __nv_bfloat162 t1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+            __nv_bfloat162 t3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+            o.x = *reinterpret_cast<uint32_t*>(&t0); o.y = *reinterpret_cast<uint32_t*>(&t1);
+            o.z = *reinterpret_cast<uint32_t*>(&t2); o.w = *reinterpret_cast<uint32_t*>(&t3);
+            *reinterpret_cast<uint4*>(dst + 8 * j) = o;
+        }
+    } else {
+        for (int j = 0; j < 32 && col0 + j < out_n; j++) dst[j] = __float2bfloat16_rn(v[j]);
+    }
+}
+
+template <int KIND, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
+    constexpr int S = T2_STAGES;
+    constexpr int BN2 = 256, BM2 = 256;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sm_a = base;
+    const uint32_t sm_b = sm_a + S * BM * BKB;
+    const uint32_t sm_bar = sm_b + S * BM * BKB;
+    const uint32_t bar_full = sm_bar, bar_empty = sm_bar + 8 * S;
+    const uint32_t bar_tfull = sm_bar + 16 * S, bar_tempty = bar_tfull + 16;
+    const uint32_t tmem_slot = bar_tempty + 16;
+    uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta_rank = cluster_ctarank();
+    const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+    const int tiles_m = (p.m + BM2 - 1) / BM2, tiles_n = (p.n + BN2 - 1) / BN2;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (p.k_bytes + BKB - 1) / BKB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 8); }
+        fence_barrier_init();
+        prefetch_tmap(&tm_a);
+        prefetch_tmap(&tm_b);
+    }
+    if (warp == 1) { tmem_alloc_cg2(tmem_slot, 512); tmem_relinquish_cg2(); }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                   // peer barriers are initialised and its tensor memory allocated
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (one lane, both CTAs)
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+                int tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+                const int m0 = tm * BM2 + (int)cta_rank * BM, n0 = tn * BN2 + (int)cta_rank * BM;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                    // the full barrier of the pair lives in CTA 0 and expects the bytes of both CTAs
+                    if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * T2_STAGE_BYTES);
+                    const uint32_t full0 = mapa_shared(bar_full + 8 * stage, 0);
+                    tma_load_2d_cg2(sm_a + stage * BM * BKB, &tm_a, kb * BKB, m0, full0);
+                    tma_load_2d_cg2(sm_b + stage * BM * BKB, &tm_b, kb * BKB, n0, full0);
+                    if (++stage == S) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (one lane of CTA 0)
+        if (lane == 0 && cta_rank == 0) {
+            constexpr uint32_t idesc =
+                KIND == KIND_F8 ? idesc_dense(1, 0, 0, BM2, BN2) :
+                KIND == KIND_BF16 ? idesc_dense(1, 1, 1, BM2, BN2) : idesc_dense(2, 1, 1, BM2, BN2);
+            int stage = 0; uint32_t phase = 0;
+            int acc = 0; uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+                if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN2;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(bar_full + 8 * stage, phase)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                    tc_fence_after();
+                    const uint64_t adesc = smem_desc_sw128(sm_a + stage * BM * BKB);
+                    const uint64_t bdesc = smem_desc_sw128(sm_b + stage * BM * BKB);
+#pragma unroll
+                    for (int k = 0; k < BKB / 32; k++) {
+                        const uint64_t a = adesc + (uint64_t)(k * 2), b = bdesc + (uint64_t)(k * 2);
+                        const uint32_t accum = (kb | k) != 0;
+                        if (KIND == KIND_F8) mma_f8f6f4_cg2(d_tmem, a, b, idesc, accum);
+                        else if (KIND == KIND_BF16) mma_f16_cg2(d_tmem, a, b, idesc, accum);
+                        else mma_i8_cg2(d_tmem, a, b, idesc, accum);
+                    }
+                    tc_commit_cg2_mc(bar_empty + 8 * stage, 3);          // frees the stage in both CTAs
+                    if (++stage == S) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                tc_commit_cg2_mc(bar_tfull + 8 * acc, 3);                // accumulator complete, both CTAs
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (4 warps, both CTAs)
+        const int quarter = warp & 3;
+        int acc = 0; uint32_t acc_phase = 0;
+        float tensor_scale = 1.0f;
+        if (KIND == KIND_F8) tensor_scale = __ldg(p.s0) * __ldg(p.s1);
+        __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y);
+        for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+            const int m0 = tm * BM2 + (int)cta_rank * BM, n0 = tn * BN2;
+            bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+            tc_fence_after();
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2;
+            float row_scale = 1.0f;
+            if (KIND == KIND_I8 && row < p.m) row_scale = __ldg(p.s0 + row);
+            if (EPI == EPI_SWIGLU) {
+#pragma unroll 1
+                for (int c = 0; c < BN2 / 64; c++) {
+                    uint32_t rg[32], ru[32];
+                    tmem_ld_32x32b_x32(t_row + c * 32, rg);
+                    tmem_ld_32x32b_x32(t_row + BN2 / 2 + c * 32, ru);
+                    tmem_ld_wait();
+                    epilogue_store_swiglu(rg, ru, row, (n0 >> 1) + c * 32, p.n >> 1, p, tensor_scale, y);
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN2 / 32; c++) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(t_row + c * 32, r);
+                    tmem_ld_wait();
+                    epilogue_store_scale<KIND>(r, row, n0 + c * 32, p, tensor_scale, row_scale, y);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * acc, 0));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    // Teardown: both CTAs are past every access to the peer's barriers, shared and tensor memory before
+    // either frees its tensor memory or exits.
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc_cg2(tmem_base, 512);
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -369,6 +581,49 @@ static int32_t launch(oxq_handle* h, const void* x, int64_t ldx_bytes, const voi
     return OXQ_OK;
 }
 
+// 2-CTA launch: one cluster per pair of SMs.  OXQ_GEMM_2CTA=0 falls back to the 1-CTA kernel (for A/B runs).
+static bool use_2cta_setting() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("OXQ_GEMM_2CTA"); v = e ? (atoi(e) != 0) : 1; }
+    return v != 0;
+}
+
+template <int KIND, int EPI = EPI_SCALE>
+static int32_t launch2(oxq_handle* h, const void* x, int64_t ldx_bytes, const void* w, int64_t ldw_bytes, GemmParams p) {
+    CUtensorMap tm_a, tm_b;
+    if (!make_tmap_bytes(&tm_a, x, p.m, p.k_bytes, ldx_bytes, BM) || !make_tmap_bytes(&tm_b, w, p.n, p.k_bytes, ldw_bytes, BM))
+        OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned, leading dimensions multiples of 16 bytes)");
+    static int max_clusters = 0;
+    if (max_clusters == 0) {
+        OXQ_CUDA(h, cudaFuncSetAttribute(gemm_tc2_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(h->sm_count & ~1, 1, 1);
+        cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = T2_SMEM_BYTES;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr; cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<KIND, EPI>, &cfg) != cudaSuccess || n < 1) n = h->sm_count / 2;
+        max_clusters = n < h->sm_count / 2 ? n : h->sm_count / 2;
+    }
+    const int tiles = ((p.m + 255) / 256) * ((p.n + 255) / 256);
+    const int clusters = tiles < max_clusters ? tiles : max_clusters;
+    p.status = h->dev_status;
+    p.group_m = group_m_setting() / 2 > 0 ? group_m_setting() / 2 : 1;     // same panel height in rows as the 1-CTA walk
+    gemm_tc2_kernel<KIND, EPI><<<2 * clusters, NUM_THREADS, T2_SMEM_BYTES, h->stream>>>(tm_a, tm_b, p);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+// Dense kinds: 256 x 256 tiles on CTA pairs when there are at least two 128-row tiles of X, else 128 x 256.
+template <int KIND, int EPI = EPI_SCALE>
+static int32_t launch_dense(oxq_handle* h, const void* x, int64_t ldx_bytes, const void* w, int64_t ldw_bytes, const GemmParams& p) {
+    if (use_2cta_setting() && p.m > 128) return launch2<KIND, EPI>(h, x, ldx_bytes, w, ldw_bytes, p);
+    return launch<KIND, 256, EPI>(h, x, ldx_bytes, w, ldw_bytes, p);
+}
+
 static int32_t check_gemm_args(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, const void* w, const void* y, int64_t ldy) {
     // gemm(): zero dimensions are errors (crates/oxicuda-blas/src/level3/gemm_api.rs:88-92)
     if (m <= 0 || n <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "GEMM dimensions must be non-zero");
@@ -394,7 +649,7 @@ int32_t oxq_gemm_fp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8
     if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
     GemmParams p{};
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y; p.ldy = ldy; p.s0 = sx; p.s1 = sw;
-    return launch<KIND_F8, 256>(h, x, ldx, w, ldw, p);
+    return launch_dense<KIND_F8>(h, x, ldx, w, ldw, p);
 }
 
 int32_t oxq_gemm_fp8_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, const uint8_t* x, int64_t ldx, const uint8_t* w_gu, int64_t ldw,
@@ -406,7 +661,7 @@ int32_t oxq_gemm_fp8_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, con
     if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
     GemmParams p{};
     p.m = (int)m; p.n = (int)n2; p.k_bytes = (int)k; p.y = hout; p.ldy = ldh; p.s0 = sx; p.s1 = sw;
-    return launch<KIND_F8, 256, EPI_SWIGLU>(h, x, ldx, w_gu, ldw, p);
+    return launch_dense<KIND_F8, EPI_SWIGLU>(h, x, ldx, w_gu, ldw, p);
 }
 
 int32_t oxq_gemm_bf16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, int64_t ldx, const void* w, int64_t ldw,
@@ -416,7 +671,7 @@ int32_t oxq_gemm_bf16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void
     if ((k & 7) || ldx < k || ldw < k || (ldx & 7) || (ldw & 7)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 8 and ld >= k");
     GemmParams p{};
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)(2 * k); p.y = y; p.ldy = ldy;
-    return launch<KIND_BF16, 256>(h, x, 2 * ldx, w, 2 * ldw, p);
+    return launch_dense<KIND_BF16>(h, x, 2 * ldx, w, 2 * ldw, p);
 }
 
 int32_t oxq_gemm_bf16_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, const void* x, int64_t ldx, const void* w_gu, int64_t ldw,
@@ -427,7 +682,7 @@ int32_t oxq_gemm_bf16_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, co
     if ((k & 7) || ldx < k || ldw < k || (ldx & 7) || (ldw & 7)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 8 and ld >= k");
     GemmParams p{};
     p.m = (int)m; p.n = (int)n2; p.k_bytes = (int)(2 * k); p.y = hout; p.ldy = ldh;
-    return launch<KIND_BF16, 256, EPI_SWIGLU>(h, x, 2 * ldx, w_gu, 2 * ldw, p);
+    return launch_dense<KIND_BF16, EPI_SWIGLU>(h, x, 2 * ldx, w_gu, 2 * ldw, p);
 }
 
 int32_t oxq_gemm_w8a8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const int8_t* x, int64_t ldx, const int8_t* w, int64_t ldw,
@@ -438,7 +693,7 @@ int32_t oxq_gemm_w8a8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const int8
     if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
     GemmParams p{};
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y; p.ldy = ldy; p.s0 = sx_rows; p.s1 = sw_rows;
-    return launch<KIND_I8, 256>(h, x, ldx, w, ldw, p);
+    return launch_dense<KIND_I8>(h, x, ldx, w, ldw, p);
 }
 
 int32_t oxq_gemm_mxfp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x, const uint8_t* sfx, const uint8_t* w,

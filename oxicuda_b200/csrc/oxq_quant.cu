@@ -9,8 +9,8 @@ namespace oxq {
 // INT8 symmetric per-row
 // ------------------------------------------------------------------------------------------------
 
-__device__ __forceinline__ int quant_i8(float x, float scale, int rounding) {
-    float v = round_mode(__fdiv_rn(x, scale), rounding);
+__device__ __forceinline__ int quant_i8(float x, const InvDiv& scale, int rounding) {
+    float v = round_mode(div_exact(x, scale), rounding);
     if (v != v) return 0;                                   // NaN -> code 0 (Rust `as i32`)
     return __float2int_rn(fminf(fmaxf(v, -127.0f), 127.0f));
 }
@@ -46,8 +46,9 @@ __global__ void __launch_bounds__(256) int8_quant_rows_kernel(const float* __res
         amax = s_red[0];
 #pragma unroll
         for (int w = 1; w < 8; w++) amax = fmaxf(amax, s_red[w]);
-        const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
-        if (tid == 0) scales[row] = scale;
+        const float scale_f = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+        if (tid == 0) scales[row] = scale_f;
+        const InvDiv scale = make_invdiv(scale_f);
         uint32_t* qr = reinterpret_cast<uint32_t*>(q + row * cols);
 #pragma unroll
         for (int i = 0; i < NV; i++) {
@@ -84,8 +85,9 @@ __global__ void __launch_bounds__(256) int8_quant_rows_scalar_kernel(const float
         __syncthreads();
         amax = s_red[0];
         for (int w = 1; w < 8; w++) amax = fmaxf(amax, s_red[w]);
-        const float scale = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
-        if (tid == 0) scales[row] = scale;
+        const float scale_f = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
+        if (tid == 0) scales[row] = scale_f;
+        const InvDiv scale = make_invdiv(scale_f);
         for (int64_t i = tid; i < cols; i += 256) q[row * cols + i] = (int8_t)quant_i8(xr[i], scale, rounding);
     }
 }
@@ -190,45 +192,65 @@ __device__ __forceinline__ float e4m3_refcompat_decode(uint8_t b) {
     return __uint_as_float((sign << 31) | ((e + 120u) << 23) | (m << 20));
 }
 
-// 16 elements per thread -> one 16-byte store.  If stats != nullptr the scale is derived from
-// stats[0] (absmax) as absmax/448 (1.0 when absmax == 0) and thread 0 records it in stats[1].
+// Items of 8 elements (one 8-byte store); every thread keeps FP8_ILP items in flight, item j of a thread is
+// FP8_ILP-strided by the warp so each load instruction of a warp covers one contiguous span.  If
+// stats != nullptr the scale is derived from stats[0] (absmax) as absmax/448 (1.0 when absmax == 0) and
+// thread 0 records it in stats[1].
+constexpr int FP8_ILP = 4;
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) fp8_quant_kernel(const T* __restrict__ x, int64_t n, const float* __restrict__ scale_ptr,
                                                         float* __restrict__ stats, uint8_t* __restrict__ q) {
-    constexpr int V = Vec16<T>::N;
-    constexpr int L = 16 / V;                               // 16-byte loads per thread
-    float scale;
+    constexpr int V = Vec16<T>::N;                          // elements per 16-byte load (8 or 4)
+    constexpr int L = 8 / V;                                // 16-byte loads per item (1 or 2)
+    float scale_f;
     if (stats) {
-        float am = stats[0];
-        scale = am > 0.0f ? __fdiv_rn(am, 448.0f) : 1.0f;
-        if (blockIdx.x == 0 && threadIdx.x == 0) stats[1] = scale;
+        const float am = stats[0];
+        scale_f = am > 0.0f ? __fdiv_rn(am, 448.0f) : 1.0f;
+        if (blockIdx.x == 0 && threadIdx.x == 0) stats[1] = scale_f;
     } else {
-        scale = __ldg(scale_ptr);
+        scale_f = __ldg(scale_ptr);
     }
-    const int64_t nchunk = n / 16;
-    for (int64_t c = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; c < nchunk; c += (int64_t)gridDim.x * blockDim.x) {
-        float f[16];
+    const InvDiv scale = make_invdiv(scale_f);
+    const int64_t nitems = n / 8;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp_global = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t base = warp_global * (32 * FP8_ILP); base < nitems; base += nwarps * (32 * FP8_ILP)) {
+        Vec16<T> in[FP8_ILP][L];
 #pragma unroll
-        for (int l = 0; l < L; l++) {
-            Vec16<T> a = ld16_stream(x + c * 16 + l * V);
+        for (int j = 0; j < FP8_ILP; j++) {
+            const int64_t it = base + j * 32 + lane;
+            if (it < nitems) {
 #pragma unroll
-            for (int j = 0; j < V; j++) f[l * V + j] = __fdiv_rn(Elem<T>::to_f32(a.v[j]), scale);
-        }
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            if (MODE == OXQ_FP8_SPEC_RNE) {
-                w[i] = (uint32_t)cvt_e4m3x2(f[4 * i], f[4 * i + 1]) | ((uint32_t)cvt_e4m3x2(f[4 * i + 2], f[4 * i + 3]) << 16);
-            } else {
-                w[i] = (uint32_t)e4m3_refcompat(f[4 * i]) | ((uint32_t)e4m3_refcompat(f[4 * i + 1]) << 8) |
-                       ((uint32_t)e4m3_refcompat(f[4 * i + 2]) << 16) | ((uint32_t)e4m3_refcompat(f[4 * i + 3]) << 24);
+                for (int l = 0; l < L; l++) in[j][l] = ld16_stream(x + it * 8 + l * V);
             }
         }
-        __stcs(reinterpret_cast<uint4*>(q + c * 16), make_uint4(w[0], w[1], w[2], w[3]));
+#pragma unroll
+        for (int j = 0; j < FP8_ILP; j++) {
+            const int64_t it = base + j * 32 + lane;
+            if (it < nitems) {
+                float f[8];
+#pragma unroll
+                for (int l = 0; l < L; l++)
+#pragma unroll
+                    for (int e = 0; e < V; e++) f[l * V + e] = div_exact(Elem<T>::to_f32(in[j][l].v[e]), scale);
+                uint32_t w[2];
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    if (MODE == OXQ_FP8_SPEC_RNE) {
+                        w[i] = (uint32_t)cvt_e4m3x2(f[4 * i], f[4 * i + 1]) | ((uint32_t)cvt_e4m3x2(f[4 * i + 2], f[4 * i + 3]) << 16);
+                    } else {
+                        w[i] = (uint32_t)e4m3_refcompat(f[4 * i]) | ((uint32_t)e4m3_refcompat(f[4 * i + 1]) << 8) |
+                               ((uint32_t)e4m3_refcompat(f[4 * i + 2]) << 16) | ((uint32_t)e4m3_refcompat(f[4 * i + 3]) << 24);
+                    }
+                }
+                __stcs(reinterpret_cast<uint2*>(q + it * 8), make_uint2(w[0], w[1]));
+            }
+        }
     }
     if (blockIdx.x == 0) {                                  // ragged tail
-        for (int64_t t = nchunk * 16 + threadIdx.x; t < n; t += blockDim.x) {
-            float f = __fdiv_rn(Elem<T>::to_f32(x[t]), scale);
+        for (int64_t t = nitems * 8 + threadIdx.x; t < n; t += blockDim.x) {
+            const float f = div_exact(Elem<T>::to_f32(x[t]), scale);
             q[t] = MODE == OXQ_FP8_SPEC_RNE ? (uint8_t)(cvt_e4m3x2(f, 0.0f) & 0xFF) : e4m3_refcompat(f);
         }
     }
@@ -303,7 +325,8 @@ __global__ void __launch_bounds__(256) int4g_quant_kernel(const T* __restrict__ 
             __half sh = __float2half_rn(s32);
             if ((__half_as_ushort(sh) & 0x7FFFu) == 0) sh = __ushort_as_half(1);
             const float s = __half2float(sh);
-            float zf = roundf(__fdiv_rn(-mn, s));
+            const InvDiv sd = make_invdiv(s);
+            float zf = roundf(div_exact(-mn, sd));
             zf = zf != zf ? 0.0f : fminf(fmaxf(zf, 0.0f), 15.0f);
             const uint32_t zp = (uint32_t)zf;
             if (g0 + g < ngroups) {
@@ -314,7 +337,7 @@ __global__ void __launch_bounds__(256) int4g_quant_kernel(const T* __restrict__ 
                     uint32_t nib4 = 0;
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
-                        float t = round_mode(__fdiv_rn(v[g][p][j], s) + zf, rounding);
+                        float t = round_mode(div_exact(v[g][p][j], sd) + zf, rounding);
                         t = t != t ? 0.0f : fminf(fmaxf(t, 0.0f), 15.0f);
                         nib4 |= ((uint32_t)t) << (4 * j);
                     }
@@ -367,46 +390,55 @@ __device__ __forceinline__ void load8(const T* p, float (&f)[8]) {
     }
 }
 
-// 8 elements per thread, 4 adjacent lanes form one 32-element block.
+// 8 elements per item, 4 adjacent lanes form one 32-element block; BS_ILP items per thread in flight.
+constexpr int BS_ILP = 4;
 template <typename T>
 __global__ void __launch_bounds__(256) mxfp8_quant_kernel(const T* __restrict__ x, int64_t rows, int64_t k,
                                                           uint8_t* __restrict__ codes, uint8_t* __restrict__ sf_rm,
                                                           uint8_t* __restrict__ sf_mma) {
-    const int64_t nthr = rows * k / 8;
+    const int64_t nitems = rows * k / 8;
     const int64_t sf_cols = k / 32;
     const int lane = threadIdx.x & 31;
+    const int64_t warp_global = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     // warp-uniform trip count: the shuffles below need every lane of the warp
-    for (int64_t base = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); base < nthr; base += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t t = base + lane;
-        const bool valid = t < nthr;
-        float f[8];
-        if (valid) load8(x + t * 8, f);
-        else {
+    for (int64_t base = warp_global * (32 * BS_ILP); base < nitems; base += nwarps * (32 * BS_ILP)) {
+        float f[BS_ILP][8];
 #pragma unroll
-            for (int j = 0; j < 8; j++) f[j] = 0.0f;
-        }
-        float am = 0.0f;
+        for (int j = 0; j < BS_ILP; j++) {
+            const int64_t t = base + j * 32 + lane;
+            if (t < nitems) load8(x + t * 8, f[j]);
+            else {
 #pragma unroll
-        for (int j = 0; j < 8; j++) am = fmaxf(am, fabsf(f[j]));
-        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
-        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
-        if (!valid) continue;
-        int byte = 0;
-        if (am > 0.0f) {
-            const uint32_t b = __float_as_uint(am);
-            const int e = (b >> 23) != 0 ? (int)(b >> 23) - 127 : -118 - __clz(b);   // floor(log2(am))
-            byte = e - 8 + 127;
-            byte = byte < 0 ? 0 : (byte > 254 ? 254 : byte);
+                for (int e = 0; e < 8; e++) f[j][e] = 0.0f;
+            }
         }
-        const float inv = pow2_of(127 - byte);
-        uint32_t lo = (uint32_t)cvt_e4m3x2(f[0] * inv, f[1] * inv) | ((uint32_t)cvt_e4m3x2(f[2] * inv, f[3] * inv) << 16);
-        uint32_t hi = (uint32_t)cvt_e4m3x2(f[4] * inv, f[5] * inv) | ((uint32_t)cvt_e4m3x2(f[6] * inv, f[7] * inv) << 16);
-        __stcs(reinterpret_cast<uint2*>(codes + t * 8), make_uint2(lo, hi));
-        if ((t & 3) == 0) {
-            const int64_t blk = t >> 2;
-            const int64_t r = blk / sf_cols, c = blk - r * sf_cols;
-            if (sf_rm) sf_rm[blk] = (uint8_t)byte;
-            if (sf_mma) sf_mma[sf_mma_offset(r, c, sf_cols)] = (uint8_t)byte;
+#pragma unroll
+        for (int j = 0; j < BS_ILP; j++) {
+            const int64_t t = base + j * 32 + lane;
+            float am = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 8; e++) am = fmaxf(am, fabsf(f[j][e]));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+            if (t >= nitems) continue;
+            int byte = 0;
+            if (am > 0.0f) {
+                const uint32_t b = __float_as_uint(am);
+                const int e = (b >> 23) != 0 ? (int)(b >> 23) - 127 : -118 - __clz(b);   // floor(log2(am))
+                byte = e - 8 + 127;
+                byte = byte < 0 ? 0 : (byte > 254 ? 254 : byte);
+            }
+            const float inv = pow2_of(127 - byte);
+            uint32_t lo = (uint32_t)cvt_e4m3x2(f[j][0] * inv, f[j][1] * inv) | ((uint32_t)cvt_e4m3x2(f[j][2] * inv, f[j][3] * inv) << 16);
+            uint32_t hi = (uint32_t)cvt_e4m3x2(f[j][4] * inv, f[j][5] * inv) | ((uint32_t)cvt_e4m3x2(f[j][6] * inv, f[j][7] * inv) << 16);
+            __stcs(reinterpret_cast<uint2*>(codes + t * 8), make_uint2(lo, hi));
+            if ((t & 3) == 0) {
+                const int64_t blk = t >> 2;
+                const int64_t r = blk / sf_cols, c = blk - r * sf_cols;
+                if (sf_rm) sf_rm[blk] = (uint8_t)byte;
+                if (sf_mma) sf_mma[sf_mma_offset(r, c, sf_cols)] = (uint8_t)byte;
+            }
         }
     }
 }
@@ -418,7 +450,7 @@ __global__ void __launch_bounds__(256) mxfp8_dequant_kernel(const uint8_t* __res
         y[i] = Elem<T>::from_f32(e4m3_to_f32(codes[i]) * pow2_of((int)sf_rm[i >> 5] - 127));
 }
 
-// 8 elements per thread, 2 adjacent lanes form one 16-element block.
+// 8 elements per item, 2 adjacent lanes form one 16-element block; BS_ILP items per thread in flight.
 template <typename T>
 __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const T* __restrict__ x, int64_t rows, int64_t k, float* __restrict__ stats,
                                                           uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_rm,
@@ -426,41 +458,49 @@ __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const T* __restrict__ 
     const float tmax = stats[0];
     const float g = tmax > 0.0f ? __fdiv_rn(tmax, 448.0f * 6.0f) : 1.0f;
     if (blockIdx.x == 0 && threadIdx.x == 0) stats[1] = g;
-    const float six_g = 6.0f * g;
-    const int64_t nthr = rows * k / 8;
+    const InvDiv six_g = make_invdiv(6.0f * g);
+    const int64_t nitems = rows * k / 8;
     const int64_t sf_cols = k / 16;
     const int lane = threadIdx.x & 31;
-    for (int64_t base = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); base < nthr; base += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t t = base + lane;
-        const bool valid = t < nthr;
-        float f[8];
-        if (valid) load8(x + t * 8, f);
-        else {
+    const int64_t warp_global = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t base = warp_global * (32 * BS_ILP); base < nitems; base += nwarps * (32 * BS_ILP)) {
+        float f[BS_ILP][8];
 #pragma unroll
-            for (int j = 0; j < 8; j++) f[j] = 0.0f;
+        for (int j = 0; j < BS_ILP; j++) {
+            const int64_t t = base + j * 32 + lane;
+            if (t < nitems) load8(x + t * 8, f[j]);
+            else {
+#pragma unroll
+                for (int e = 0; e < 8; e++) f[j][e] = 0.0f;
+            }
         }
-        float am = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; j++) am = fmaxf(am, fabsf(f[j]));
-        am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
-        if (!valid) continue;
-        const uint8_t s8 = (uint8_t)(cvt_e4m3x2(__fdiv_rn(am, six_g), 0.0f) & 0xFF);
-        const float d = g * e4m3_to_f32(s8);
-        uint32_t w = 0;
-        if (s8 == 0) {
+        for (int j = 0; j < BS_ILP; j++) {
+            const int64_t t = base + j * 32 + lane;
+            float am = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 8; j++) w |= ((__float_as_uint(f[j]) >> 28) & 8u) << (4 * j);
-        } else {
+            for (int e = 0; e < 8; e++) am = fmaxf(am, fabsf(f[j][e]));
+            am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+            if (t >= nitems) continue;
+            const uint8_t s8 = (uint8_t)(cvt_e4m3x2(div_exact(am, six_g), 0.0f) & 0xFF);
+            uint32_t w = 0;
+            if (s8 == 0) {
 #pragma unroll
-            for (int j = 0; j < 8; j += 2)
-                w |= (uint32_t)cvt_e2m1x2(__fdiv_rn(f[j], d), __fdiv_rn(f[j + 1], d)) << (4 * j);
-        }
-        __stcs(reinterpret_cast<uint32_t*>(packed + t * 4), w);
-        if ((t & 1) == 0) {
-            const int64_t blk = t >> 1;
-            const int64_t r = blk / sf_cols, c = blk - r * sf_cols;
-            if (sf_rm) sf_rm[blk] = s8;
-            if (sf_mma) sf_mma[sf_mma_offset(r, c, sf_cols)] = s8;
+                for (int e = 0; e < 8; e++) w |= ((__float_as_uint(f[j][e]) >> 28) & 8u) << (4 * e);
+            } else {
+                const InvDiv d = make_invdiv(g * e4m3_to_f32(s8));
+#pragma unroll
+                for (int e = 0; e < 8; e += 2)
+                    w |= (uint32_t)cvt_e2m1x2(div_exact(f[j][e], d), div_exact(f[j][e + 1], d)) << (4 * e);
+            }
+            __stcs(reinterpret_cast<uint32_t*>(packed + t * 4), w);
+            if ((t & 1) == 0) {
+                const int64_t blk = t >> 1;
+                const int64_t r = blk / sf_cols, c = blk - r * sf_cols;
+                if (sf_rm) sf_rm[blk] = s8;
+                if (sf_mma) sf_mma[sf_mma_offset(r, c, sf_cols)] = s8;
+            }
         }
     }
 }
@@ -560,7 +600,7 @@ int32_t oxq_absmax(oxq_handle* h, const void* x, int dtype, int64_t n, float* ab
 }
 
 static int32_t fp8_quant_launch(oxq_handle* h, const void* x, int dtype, int64_t n, const float* scale, float* stats, uint8_t* q, int mode) {
-    const int grid = grid_for(h, n / 16 + 1, 256, 16);
+    const int grid = grid_for(h, n / (8 * FP8_ILP) + 1, 256, 8);
     if (mode == OXQ_FP8_SPEC_RNE) {
         DISPATCH_DTYPE(dtype, fp8_quant_kernel<T, OXQ_FP8_SPEC_RNE><<<grid, 256, 0, h->stream>>>((const T*)x, n, scale, stats, q));
     } else if (mode == OXQ_FP8_REFCOMPAT) {
@@ -658,7 +698,7 @@ int32_t oxq_mxfp8_quant(oxq_handle* h, const void* x, int dtype, int64_t rows, i
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     if (sf_mma && ((rows & 127) || ((k / 32) & 3)))          // pad bytes of partial tiles must not hold garbage
         OXQ_CUDA(h, cudaMemsetAsync(sf_mma, 0, oxq_sf_mma_bytes(rows, k / 32), h->stream));
-    DISPATCH_DTYPE(dtype, mxfp8_quant_kernel<T><<<grid_for(h, rows * k / 8, 256, 16), 256, 0, h->stream>>>((const T*)x, rows, k, codes, sf_rm, sf_mma));
+    DISPATCH_DTYPE(dtype, mxfp8_quant_kernel<T><<<grid_for(h, rows * k / (8 * BS_ILP) + 1, 256, 8), 256, 0, h->stream>>>((const T*)x, rows, k, codes, sf_rm, sf_mma));
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -683,7 +723,7 @@ int32_t oxq_nvfp4_quant(oxq_handle* h, const void* x, int dtype, int64_t rows, i
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     if (sf_mma && ((rows & 127) || ((k / 16) & 3)))
         OXQ_CUDA(h, cudaMemsetAsync(sf_mma, 0, oxq_sf_mma_bytes(rows, k / 16), h->stream));
-    DISPATCH_DTYPE(dtype, nvfp4_quant_kernel<T><<<grid_for(h, rows * k / 8, 256, 16), 256, 0, h->stream>>>((const T*)x, rows, k, stats, packed, sf_rm, sf_mma));
+    DISPATCH_DTYPE(dtype, nvfp4_quant_kernel<T><<<grid_for(h, rows * k / (8 * BS_ILP) + 1, 256, 8), 256, 0, h->stream>>>((const T*)x, rows, k, stats, packed, sf_rm, sf_mma));
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

@@ -223,6 +223,12 @@ def extras(torch, ops, peaks):
     rec("mxfp8_quant_bf16_4096x4096", 33554432 + 16777216 + 2 * 524288, ring_time(torch, lambda r: ops.mxfp8_quant(r), ring4))
     rec("nvfp4_quant_bf16_4096x4096(absmax+encode)", 2 * 33554432 + 8388608 + 2 * 1048576, ring_time(torch, lambda r: ops.nvfp4_quant(r), ring4), 2)
     del ring, ring4, outq
+    # the same block-scaled quantizers on the weight shape of config 4 (14336 x 4096 bf16, ring of 4 -> 470 MB)
+    ringw4 = [torch.randn((14336, 4096), generator=g, device="cuda", dtype=torch.bfloat16) for _ in range(4)]
+    nel = 14336 * 4096
+    rec("mxfp8_quant_bf16_14336x4096", nel * 2 + nel + 2 * nel // 32, ring_time(torch, lambda r: ops.mxfp8_quant(r), ringw4))
+    rec("nvfp4_quant_bf16_14336x4096(absmax+encode)", 2 * nel * 2 + nel // 2 + 2 * nel // 16, ring_time(torch, lambda r: ops.nvfp4_quant(r), ringw4), 2)
+    del ringw4
     # config 3: W4A16 decode GEMMs; weights cycled through a ring > 4x L2
     for (n, k) in ((6144, 4096), (4096, 4096), (14336, 4096), (4096, 14336)):
         wbytes = n * k // 2 + n * k // 128 * 2 + n * k // 128 // 2

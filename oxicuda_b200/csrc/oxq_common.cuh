@@ -136,11 +136,11 @@ __device__ __forceinline__ float pow2_of(int e) {
     return e >= -126 ? __uint_as_float((uint32_t)(e + 127) << 23) : __uint_as_float(0x00400000u);
 }
 
-// IEEE-exact x / s for a divisor that is shared by many elements: the correctly rounded reciprocal is
-// computed once, each quotient then costs one multiply and two FMA remainder corrections instead of a full
-// division sequence (which would re-evaluate the reciprocal for every element).  With y = RN(1/s) and the
-// remainder r = x - s*q formed exactly by an FMA, q + r*y rounds to RN(x/s) (Markstein); the second step is
-// a safety margin.  Outside the range where the remainders are exact the true division is used instead.
+// IEEE-exact x / s for a positive divisor that is shared by many elements: the correctly rounded reciprocal
+// y = RN(1/s) is computed once; each quotient is then q0 = RN(x*y), r = x - s*q0 (exact, one FMA),
+// q = RN(q0 + r*y), which equals RN(x/s) (Markstein's theorem) -- three FMA-pipe operations instead of a
+// division sequence that re-evaluates the reciprocal for every element.  Outside the divisor range where
+// the remainder is exactly representable the true division is used instead.
 struct InvDiv {
     float s, y;
     bool fast;
@@ -149,19 +149,18 @@ __device__ __forceinline__ InvDiv make_invdiv(float s) {
     InvDiv d;
     d.s = s;
     d.y = __frcp_rn(s);
-    const float a = fabsf(s);
-    d.fast = a >= 0x1p-60f && a <= 0x1p60f;
+    d.fast = s >= 0x1p-60f && s <= 0x1p60f;
     return d;
 }
 __device__ __forceinline__ float div_exact(float x, const InvDiv& d) {
     if (!d.fast) return __fdiv_rn(x, d.s);
     const float q0 = x * d.y;
     float q = fmaf(fmaf(-d.s, q0, x), d.y, q0);
-    q = fmaf(fmaf(-d.s, q, x), d.y, q);
-    // |x| >= 2^100 (and Inf / NaN): the quotient is beyond every quantizer's range, and the remainder of an
-    // infinite quotient would be NaN, so the plain product is returned.  A zero product is returned as it is
-    // too: the correction steps would turn -0 into +0, and the sign of zero shows in FP8 / FP4 codes.
-    return (fabsf(x) < 0x1p100f && q0 != 0.0f) ? q : q0;
+    // s > 0, so the quotient carries the sign of x; forcing it keeps -0 (the correction step would give +0),
+    // which shows in FP8 / FP4 codes
+    q = copysignf(q, x);
+    // an infinite q0 (x = +-Inf, or overflow) makes the remainder NaN: return q0 then.  NaN inputs give NaN both ways.
+    return q != q ? q0 : q;
 }
 
 // offset of scale factor (row r, sf column c) in the tiled order consumed by the tensor-core scale

@@ -47,20 +47,54 @@ struct W4Params {
     int* counters;               // [ceil(n/128)], zero on entry and on exit
 };
 
-// NT = number of 8-wide batch tiles (M padded to 8*NT).
+// NT = number of 8-wide batch tiles (M padded to 8*NT); MAXS = upper bound on the 128-wide K spans per CTA.
 //
 // K order inside one MMA is free as long as both operands agree, so each thread feeds the MMA the
 // codes of its own 16-byte load: word i of the load (8 consecutive K) supplies MMAs 2i and 2i+1, and
-// the activation tile is stored in shared memory already permuted to match (see stage_x).
-template <int NT>
+// the activation tile is stored in shared memory already permuted to match.
+//
+// Every weight byte this thread needs (2 rows x MAXS spans x 16 bytes) and the group parameters are
+// requested before anything else, so they are in flight while the activation chunk is staged.
+template <int NT, int MAXS>
 __global__ void __launch_bounds__(W4_THREADS) w4a16_decode_kernel(const W4Params p) {
-    extern __shared__ uint4 xs[];                       // [kc/128][4][NT][32] uint4
+    extern __shared__ uint4 xs[];                       // [spans][4][NT][32] uint4
     __shared__ int s_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int split = blockIdx.y;
     const int k0 = split * p.kc;
     const int k1 = min(p.k, k0 + p.kc);
     const int spans = (k1 - k0) >> 7;
+
+    // ---- request the weights -----------------------------------------------------------------
+    const int row_a = blockIdx.x * W4_ROWS_PER_CTA + warp * 16 + g, row_b = row_a + 8;
+    const bool va = row_a < p.n, vb = row_b < p.n;
+    const int wpr = p.k >> 3;                            // u32 words per weight row
+    const int gpr = p.k / p.group;
+    const uint32_t* ca = p.codes + (size_t)(va ? row_a : 0) * wpr + ((k0 + 32 * t) >> 3);
+    const uint32_t* cb = p.codes + (size_t)(vb ? row_b : 0) * wpr + ((k0 + 32 * t) >> 3);
+    uint4 wa[MAXS], wb[MAXS];
+    uint16_t sca[MAXS], scb[MAXS];
+    uint32_t zwa[MAXS], zwb[MAXS];
+#pragma unroll
+    for (int s = 0; s < MAXS; s++) {
+        wa[s] = make_uint4(0, 0, 0, 0); wb[s] = wa[s];
+        sca[s] = 0; scb[s] = 0; zwa[s] = 0; zwb[s] = 0;
+        if (s < spans) {
+            const int kg = (k0 + s * 128) / p.group;
+            if (va) {
+                wa[s] = ld_stream_u4(ca + s * 16);
+                const int gi = row_a * gpr + kg;
+                sca[s] = __ldg(p.scales + gi);
+                zwa[s] = (__ldg(p.zeros + (gi >> 3)) >> ((gi & 7) * 4)) & 0xFu;
+            }
+            if (vb) {
+                wb[s] = ld_stream_u4(cb + s * 16);
+                const int gi = row_b * gpr + kg;
+                scb[s] = __ldg(p.scales + gi);
+                zwb[s] = (__ldg(p.zeros + (gi >> 3)) >> ((gi & 7) * 4)) & 0xFu;
+            }
+        }
+    }
 
     // ---- stage the activation chunk, permuted into B-fragment order ---------------------------
     // One item = 8 consecutive K of one batch row.  Destination: for K offset o inside the chunk,
@@ -80,66 +114,43 @@ __global__ void __launch_bounds__(W4_THREADS) w4a16_decode_kernel(const W4Params
     }
     __syncthreads();
 
-    // ---- stream the weights -------------------------------------------------------------------
-    const int row_a = blockIdx.x * W4_ROWS_PER_CTA + warp * 16 + g, row_b = row_a + 8;
-    const bool va = row_a < p.n, vb = row_b < p.n;
-    const int wpr = p.k >> 3;                            // u32 words per weight row
-    const int gpr = p.k / p.group;
-    const uint32_t* ca = p.codes + (size_t)(va ? row_a : 0) * wpr + ((k0 + 32 * t) >> 3);
-    const uint32_t* cb = p.codes + (size_t)(vb ? row_b : 0) * wpr + ((k0 + 32 * t) >> 3);
-
     float total[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) { total[nt][0] = total[nt][1] = total[nt][2] = total[nt][3] = 0.0f; }
 
-    uint4 wa = make_uint4(0, 0, 0, 0), wb = wa;
-    if (spans > 0) { if (va) wa = ld_stream_u4(ca); if (vb) wb = ld_stream_u4(cb); }
-    for (int s = 0; s < spans; s++) {
-        uint4 na = make_uint4(0, 0, 0, 0), nb = na;
-        if (s + 1 < spans) { if (va) na = ld_stream_u4(ca + (s + 1) * 16); if (vb) nb = ld_stream_u4(cb + (s + 1) * 16); }
-        // group parameters of this 128-wide span
-        const int kg = (k0 + s * 128) / p.group;
-        float sa = 0.0f, sb = 0.0f;
-        uint32_t za = 0, zb = 0;
-        if (va) {
-            const int gi = row_a * gpr + kg;
-            sa = __half2float(__ushort_as_half(__ldg(p.scales + gi)));
-            za = (__ldg(p.zeros + (gi >> 3)) >> ((gi & 7) * 4)) & 0xFu;
-        }
-        if (vb) {
-            const int gi = row_b * gpr + kg;
-            sb = __half2float(__ushort_as_half(__ldg(p.scales + gi)));
-            zb = (__ldg(p.zeros + (gi >> 3)) >> ((gi & 7) * 4)) & 0xFu;
-        }
-        const uint32_t zma = 0x43004300u | za | (za << 16), zmb = 0x43004300u | zb | (zb << 16);   // bf16x2 (128 + zp)
-        float part[NT][4];
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++) { part[nt][0] = part[nt][1] = part[nt][2] = part[nt][3] = 0.0f; }
-        const uint32_t wwa[4] = {wa.x, wa.y, wa.z, wa.w}, wwb[4] = {wb.x, wb.y, wb.z, wb.w};
+    for (int s = 0; s < MAXS; s++) {
+        if (s < spans) {
+            const float sa = __half2float(__ushort_as_half(sca[s])), sb = __half2float(__ushort_as_half(scb[s]));
+            const uint32_t zma = 0x43004300u | zwa[s] | (zwa[s] << 16), zmb = 0x43004300u | zwb[s] | (zwb[s] << 16);   // bf16x2 (128 + zp)
+            float part[NT][4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            uint32_t ra[4], rb[4];
+            for (int nt = 0; nt < NT; nt++) { part[nt][0] = part[nt][1] = part[nt][2] = part[nt][3] = 0.0f; }
+            const uint32_t wwa[4] = {wa[s].x, wa[s].y, wa[s].z, wa[s].w}, wwb[4] = {wb[s].x, wb[s].y, wb[s].z, wb[s].w};
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-                // bf16 0x4300 | c == 128 + c exactly; subtracting 128 + zp is exact as well
-                ra[q] = bf16x2_sub(((wwa[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u, zma);
-                rb[q] = bf16x2_sub(((wwb[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u, zmb);
+            for (int i = 0; i < 4; i++) {
+                uint32_t ra[4], rb[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    // bf16 0x4300 | c == 128 + c exactly; subtracting 128 + zp is exact as well
+                    ra[q] = bf16x2_sub(((wwa[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u, zma);
+                    rb[q] = bf16x2_sub(((wwb[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u, zmb);
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const uint4 b = xs[((s * 4 + i) * NT + nt) * 32 + lane];
+                    mma_bf16_16816(part[nt], ra[0], rb[0], ra[1], rb[1], b.x, b.y);
+                    mma_bf16_16816(part[nt], ra[2], rb[2], ra[3], rb[3], b.z, b.w);
+                }
             }
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                const uint4 b = xs[((s * 4 + i) * NT + nt) * 32 + lane];
-                mma_bf16_16816(part[nt], ra[0], rb[0], ra[1], rb[1], b.x, b.y);
-                mma_bf16_16816(part[nt], ra[2], rb[2], ra[3], rb[3], b.z, b.w);
+                total[nt][0] = fmaf(sa, part[nt][0], total[nt][0]);
+                total[nt][1] = fmaf(sa, part[nt][1], total[nt][1]);
+                total[nt][2] = fmaf(sb, part[nt][2], total[nt][2]);
+                total[nt][3] = fmaf(sb, part[nt][3], total[nt][3]);
             }
         }
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-            total[nt][0] = fmaf(sa, part[nt][0], total[nt][0]);
-            total[nt][1] = fmaf(sa, part[nt][1], total[nt][1]);
-            total[nt][2] = fmaf(sb, part[nt][2], total[nt][2]);
-            total[nt][3] = fmaf(sb, part[nt][3], total[nt][3]);
-        }
-        wa = na; wb = nb;
     }
 
     // ---- combine --------------------------------------------------------------------------------
@@ -296,9 +307,9 @@ int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const voi
 
     const int row_blocks = (int)((n + W4_ROWS_PER_CTA - 1) / W4_ROWS_PER_CTA);
     const int nt = (int)((m + 7) / 8);
-    // Split K so that about two CTAs per SM are in flight, each with at least 256 and at most 1024 K.
+    // Split K so that about three CTAs per SM are in flight, each with at most 8 spans (1024 K).
     const int spans_total = (int)(k / 128);
-    int splits = (2 * h->sm_count + row_blocks - 1) / row_blocks;
+    int splits = (3 * h->sm_count + row_blocks - 1) / row_blocks;
     int max_splits = spans_total / 2 > 0 ? spans_total / 2 : 1;
     if (splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
@@ -323,8 +334,13 @@ int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const voi
 #define LAUNCH_NT(NTV)                                                                                              \
     do {                                                                                                            \
         static bool attr = false;                                                                                   \
-        if (!attr) { OXQ_CUDA(h, cudaFuncSetAttribute(w4a16_decode_kernel<NTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 4 * NTV * 32 * 16)); attr = true; } \
-        w4a16_decode_kernel<NTV><<<grid, W4_THREADS, smem, h->stream>>>(p);                                          \
+        if (!attr) {                                                                                                \
+            OXQ_CUDA(h, cudaFuncSetAttribute(w4a16_decode_kernel<NTV, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 4 * NTV * 32 * 16)); \
+            OXQ_CUDA(h, cudaFuncSetAttribute(w4a16_decode_kernel<NTV, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 4 * NTV * 32 * 16)); \
+            attr = true;                                                                                            \
+        }                                                                                                           \
+        if (spans_per <= 4) w4a16_decode_kernel<NTV, 4><<<grid, W4_THREADS, smem, h->stream>>>(p);                  \
+        else w4a16_decode_kernel<NTV, 8><<<grid, W4_THREADS, smem, h->stream>>>(p);                                 \
     } while (0)
     switch (nt) {
         case 1: LAUNCH_NT(1); break;

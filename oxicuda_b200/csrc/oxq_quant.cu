@@ -15,50 +15,66 @@ __device__ __forceinline__ int quant_i8(float x, const InvDiv& scale, int roundi
     return __float2int_rn(fminf(fmaxf(v, -127.0f), 127.0f));
 }
 
-// One CTA per row (grid-stride over rows).  Each thread keeps up to NV float4 of the row in
-// registers, so a row of up to 256*4*NV floats is read from HBM exactly once; longer rows are read
-// a second time for the quantize pass.
+// One CTA per row at a time (grid-stride over rows).  Each thread keeps up to NV float4 of the row in
+// registers, so a row of up to 256*4*NV floats is read from HBM exactly once (longer rows are read a second
+// time for the quantize pass), and the next row of the CTA is already being fetched while the current one is
+// reduced, quantised and stored.
 template <int NV>
 __global__ void __launch_bounds__(256) int8_quant_rows_kernel(const float* __restrict__ x, int64_t rows, int64_t cols,
                                                               int8_t* __restrict__ q, float* __restrict__ scales,
                                                               int rounding) {
-    __shared__ float s_red[8];
+    __shared__ float s_red[2][8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t nvec = cols >> 2;
-    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    float4 cur[NV], nxt[NV];
+    int64_t row = blockIdx.x;
+    if (row < rows) {
         const float4* xr = reinterpret_cast<const float4*>(x + row * cols);
-        float4 v[NV];
-        float amax = 0.0f;
 #pragma unroll
         for (int i = 0; i < NV; i++) {
-            int64_t idx = tid + (int64_t)i * 256;
-            v[i] = idx < nvec ? __ldcs(xr + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+            const int64_t idx = tid + (int64_t)i * 256;
+            cur[i] = idx < nvec ? __ldcs(xr + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
+    }
+    int par = 0;
+    for (; row < rows; row += gridDim.x, par ^= 1) {
+        const int64_t next = row + gridDim.x;
+        if (next < rows) {
+            const float4* xn = reinterpret_cast<const float4*>(x + next * cols);
+#pragma unroll
+            for (int i = 0; i < NV; i++) {
+                const int64_t idx = tid + (int64_t)i * 256;
+                nxt[i] = idx < nvec ? __ldcs(xn + idx) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        const float4* xr = reinterpret_cast<const float4*>(x + row * cols);
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; i++)
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(cur[i].x), fabsf(cur[i].y)), fmaxf(fabsf(cur[i].z), fabsf(cur[i].w))));
         for (int64_t idx = tid + (int64_t)NV * 256; idx < nvec; idx += 256) {
             float4 t = __ldg(xr + idx);
             amax = fmaxf(amax, fmaxf(fmaxf(fabsf(t.x), fabsf(t.y)), fmaxf(fabsf(t.z), fabsf(t.w))));
         }
         amax = warp_max(amax);
-        __syncthreads();                                    // s_red reuse across rows
-        if (lane == 0) s_red[warp] = amax;
+        if (lane == 0) s_red[par][warp] = amax;             // double-buffered: one barrier per row is enough
         __syncthreads();
-        amax = s_red[0];
+        amax = s_red[par][0];
 #pragma unroll
-        for (int w = 1; w < 8; w++) amax = fmaxf(amax, s_red[w]);
+        for (int w = 1; w < 8; w++) amax = fmaxf(amax, s_red[par][w]);
         const float scale_f = __fdiv_rn(fmaxf(amax, 1e-8f), 127.0f);
         if (tid == 0) scales[row] = scale_f;
         const InvDiv scale = make_invdiv(scale_f);
         uint32_t* qr = reinterpret_cast<uint32_t*>(q + row * cols);
 #pragma unroll
         for (int i = 0; i < NV; i++) {
-            int64_t idx = tid + (int64_t)i * 256;
+            const int64_t idx = tid + (int64_t)i * 256;
             if (idx < nvec) {
-                uint32_t p = (uint32_t)(quant_i8(v[i].x, scale, rounding) & 0xFF) |
-                             ((uint32_t)(quant_i8(v[i].y, scale, rounding) & 0xFF) << 8) |
-                             ((uint32_t)(quant_i8(v[i].z, scale, rounding) & 0xFF) << 16) |
-                             ((uint32_t)(quant_i8(v[i].w, scale, rounding) & 0xFF) << 24);
-                qr[idx] = p;
+                uint32_t p = (uint32_t)(quant_i8(cur[i].x, scale, rounding) & 0xFF) |
+                             ((uint32_t)(quant_i8(cur[i].y, scale, rounding) & 0xFF) << 8) |
+                             ((uint32_t)(quant_i8(cur[i].z, scale, rounding) & 0xFF) << 16) |
+                             ((uint32_t)(quant_i8(cur[i].w, scale, rounding) & 0xFF) << 24);
+                __stcs(qr + idx, p);
             }
         }
         for (int64_t idx = tid + (int64_t)NV * 256; idx < nvec; idx += 256) {
@@ -66,6 +82,8 @@ __global__ void __launch_bounds__(256) int8_quant_rows_kernel(const float* __res
             qr[idx] = (uint32_t)(quant_i8(t.x, scale, rounding) & 0xFF) | ((uint32_t)(quant_i8(t.y, scale, rounding) & 0xFF) << 8) |
                       ((uint32_t)(quant_i8(t.z, scale, rounding) & 0xFF) << 16) | ((uint32_t)(quant_i8(t.w, scale, rounding) & 0xFF) << 24);
         }
+#pragma unroll
+        for (int i = 0; i < NV; i++) cur[i] = nxt[i];
     }
 }
 
@@ -564,7 +582,7 @@ int32_t oxq_int8_quant_rows(oxq_handle* h, const float* x, int64_t rows, int64_t
     if (!x || !q || !scales) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
     if (rounding != OXQ_ROUND_HALF_EVEN && rounding != OXQ_ROUND_HALF_AWAY) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "rounding %d", rounding);
     if (int32_t rc = oxq_require_sm100(h)) return rc;
-    const int grid = (int)(rows < (int64_t)h->sm_count * 32 ? rows : (int64_t)h->sm_count * 32);
+    const int grid = (int)(rows < (int64_t)h->sm_count * 6 ? rows : (int64_t)h->sm_count * 6);
     if ((cols & 3) == 0 && aligned16(x) && (((uintptr_t)q & 3u) == 0)) {
         if (cols <= 4096) int8_quant_rows_kernel<4><<<grid, 256, 0, h->stream>>>(x, rows, cols, q, scales, rounding);
         else int8_quant_rows_kernel<8><<<grid, 256, 0, h->stream>>>(x, rows, cols, q, scales, rounding);

@@ -181,7 +181,7 @@ OXQ_API int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, c
  * budget enforced by someone else, in a plugin whose host forbids allocations after start-up) and so
  * can neither create an oxq_handle nor provide a workspace.  It has no counterpart in the reference.
  * It takes the stream directly, works on the current device, and keeps its split-K partial sums in an
- * array built into the library image (2 MiB + 16 KiB per GPU that loads the library, held until the
+ * array built into the library image (2 MiB + 32 KiB per GPU that loads the library, held until the
  * process exits).  Limit: m <= 32 and m * n <= 524288 outputs; larger shapes return
  * OXQ_ERR_BUFFER_TOO_SMALL.  The first call on each device looks up the array's device address and
  * reads three device attributes; make that first call before any stream capture begins.  Every call

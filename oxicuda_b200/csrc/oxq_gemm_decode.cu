@@ -2,10 +2,10 @@
 // with 128-bit loads, unpacked in registers, and multiplied against an activation tile that lives in
 // shared memory.
 //
-//   W4A16: uint4 codes -> bf16 in registers with the (0x4300 | nibble) trick, exact zero-point
-//          subtraction in bf16, mma.sync m16n8k16 with the weights as the row operand, per-group f32
-//          scale applied to the group's partial sum.  Split along K across CTAs; partial sums are
-//          combined with f32 atomics in a caller-provided workspace that the last CTA drains.
+//   W4A16: uint4 codes -> bf16 in registers with the (0x4300 | nibble) trick, mma.sync m16n8k16 with the
+//          weights as the row operand, per-group f32 scale and zero-point applied to the group's partial
+//          sum.  Split along K across CTAs; partial sums are combined with f32 atomics in a
+//          caller-provided workspace that the last CTA of each row block drains.
 //   W8A32: int8 codes -> f32, plain FMAs (the benchmark's CPU-runnable configuration).
 #include "oxq_common.cuh"
 
@@ -16,17 +16,13 @@ namespace decode {
 // W4A16
 // ------------------------------------------------------------------------------------------------
 
-constexpr int W4_ROWS_PER_CTA = 128;   // 8 warps x 16 weight rows
-constexpr int W4_THREADS = 256;
+constexpr int W4_ROWS_PER_CTA = 64;    // 4 warps x 16 weight rows
+constexpr int W4_THREADS = 128;
+constexpr int W4_SPANS = 4;            // 128-wide K spans per CTA (512 K)
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
-    uint32_t r;
-    asm("sub.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
 }
 __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
     uint4 u;
@@ -36,7 +32,7 @@ __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
 
 struct W4Params {
     int m, n, k, group;
-    int kc;                      // K elements per split (multiple of 128)
+    int kc;                      // K elements per split (multiple of 128, at most W4_SPANS * 128)
     int splits;
     const __nv_bfloat16* x;      // [m x k]
     const uint32_t* codes;       // [n x k/8]
@@ -44,20 +40,24 @@ struct W4Params {
     const uint32_t* zeros;       // packed, linear group order
     __nv_bfloat16* y;            // [m x n]
     float* ws;                   // [m x n] f32 partial sums, zero on entry and on exit
-    int* counters;               // [ceil(n/128)], zero on entry and on exit
+    int* counters;               // [ceil(n/64)], zero on entry and on exit
 };
 
-// NT = number of 8-wide batch tiles (M padded to 8*NT); MAXS = upper bound on the 128-wide K spans per CTA.
+// NT = number of 8-wide batch tiles (M padded to 8*NT).  One CTA = 64 weight rows x one K chunk of up to
+// SPANS spans of 128; many short CTAs, so load latency, the split-K combine and the grid tail overlap
+// across the 8 or so CTAs an SM holds at once.
 //
-// K order inside one MMA is free as long as both operands agree, so each thread feeds the MMA the
-// codes of its own 16-byte load: word i of the load (8 consecutive K) supplies MMAs 2i and 2i+1, and
-// the activation tile is stored in shared memory already permuted to match.
-//
-// Every weight byte this thread needs (2 rows x MAXS spans x 16 bytes) and the group parameters are
-// requested before anything else, so they are in flight while the activation chunk is staged.
-template <int NT, int MAXS>
+// The MMAs multiply the raw bf16 values 128 + code (0x4300 | nibble: one shift and one logic instruction per
+// code pair); the zero-point and the 128 come out afterwards through the per-span sum of the activations:
+//   sum_k (c_k - z) x_k = sum_k (128 + c_k) x_k - (128 + z) * sum_k x_k
+// (the f32 accumulator carries about 5 bits more magnitude than the result, invisible at bf16 output).
+// K order inside one MMA is free as long as both operands agree, so word i of a thread's 16-byte load
+// (8 consecutive K) feeds MMAs 2i and 2i+1 directly, and the activation chunk is stored in shared memory
+// already permuted to match.
+template <int NT, int SPANS>
 __global__ void __launch_bounds__(W4_THREADS) w4a16_decode_kernel(const W4Params p) {
-    extern __shared__ uint4 xs[];                       // [spans][4][NT][32] uint4
+    __shared__ uint4 xs[SPANS * 4 * NT * 32];           // [span][word][nt][lane]: B fragments of two MMAs
+    __shared__ float xsum[SPANS][NT * 8];               // [span][batch row]: sum of the activations
     __shared__ int s_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int split = blockIdx.y;
@@ -65,18 +65,16 @@ __global__ void __launch_bounds__(W4_THREADS) w4a16_decode_kernel(const W4Params
     const int k1 = min(p.k, k0 + p.kc);
     const int spans = (k1 - k0) >> 7;
 
-    // ---- request the weights -----------------------------------------------------------------
+    // ---- request every weight byte and group parameter of this thread up front ---------------
     const int row_a = blockIdx.x * W4_ROWS_PER_CTA + warp * 16 + g, row_b = row_a + 8;
     const bool va = row_a < p.n, vb = row_b < p.n;
-    const int wpr = p.k >> 3;                            // u32 words per weight row
-    const int gpr = p.k / p.group;
+    const int wpr = p.k >> 3, gpr = p.k / p.group;
     const uint32_t* ca = p.codes + (size_t)(va ? row_a : 0) * wpr + ((k0 + 32 * t) >> 3);
     const uint32_t* cb = p.codes + (size_t)(vb ? row_b : 0) * wpr + ((k0 + 32 * t) >> 3);
-    uint4 wa[MAXS], wb[MAXS];
-    uint16_t sca[MAXS], scb[MAXS];
-    uint32_t zwa[MAXS], zwb[MAXS];
+    uint4 wa[SPANS], wb[SPANS];
+    uint32_t sca[SPANS], scb[SPANS], zwa[SPANS], zwb[SPANS];
 #pragma unroll
-    for (int s = 0; s < MAXS; s++) {
+    for (int s = 0; s < SPANS; s++) {
         wa[s] = make_uint4(0, 0, 0, 0); wb[s] = wa[s];
         sca[s] = 0; scb[s] = 0; zwa[s] = 0; zwb[s] = 0;
         if (s < spans) {
@@ -97,58 +95,74 @@ __global__ void __launch_bounds__(W4_THREADS) w4a16_decode_kernel(const W4Params
     }
 
     // ---- stage the activation chunk, permuted into B-fragment order ---------------------------
-    // One item = 8 consecutive K of one batch row.  Destination: for K offset o inside the chunk,
-    // span = o/128, t' = (o%128)/32, i = (o%32)/8; u32 q of the uint4 holds (x[q], x[q+4]).
-    const int items = NT * 8 * (spans * 16);
-    for (int it = tid; it < items; it += W4_THREADS) {
-        const int mrow = it / (spans * 16), o8 = it - mrow * (spans * 16);
+    // One item = 8 consecutive K of one batch row = the K of one weight word.  For K offset o inside the chunk:
+    // span = o/128, t' = (o%128)/32, word i = (o%32)/8; u32 q of the uint4 holds (x[q], x[q+4]).  The 16 items of
+    // one (batch row, span) sit in 16 consecutive lanes, which also add up the span's sum.  Rows beyond m are zero.
+    if (p.m < NT * 8) {
+        for (int idx = tid; idx < SPANS * 4 * NT * 32; idx += W4_THREADS) xs[idx] = make_uint4(0, 0, 0, 0);
+        for (int idx = tid; idx < SPANS * NT * 8; idx += W4_THREADS) (&xsum[0][0])[idx] = 0.0f;
+        __syncthreads();
+    }
+    const int items = p.m * (spans * 16);
+    for (int it0 = 0; it0 < items; it0 += W4_THREADS) {
+        const int it = it0 + tid;
+        const bool live = it < items;
+        const int mrow = live ? it / (spans * 16) : 0, o8 = live ? it - mrow * (spans * 16) : 0;
         const int span = o8 >> 4, tt = (o8 >> 2) & 3, i = o8 & 3;
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (mrow < p.m) v = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)mrow * p.k + k0 + o8 * 8));
+        if (live) v = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)mrow * p.k + k0 + o8 * 8));
         const uint32_t lo[4] = {v.x & 0xFFFFu, v.x >> 16, v.y & 0xFFFFu, v.y >> 16};
         const uint32_t hi[4] = {v.z & 0xFFFFu, v.z >> 16, v.w & 0xFFFFu, v.w >> 16};
-        uint4 o;
-        o.x = lo[0] | (hi[0] << 16); o.y = lo[1] | (hi[1] << 16); o.z = lo[2] | (hi[2] << 16); o.w = lo[3] | (hi[3] << 16);
-        const int nt = mrow >> 3, gg = mrow & 7;
-        xs[((span * 4 + i) * NT + nt) * 32 + gg * 4 + tt] = o;
+        float sum = 0.0f;
+#pragma unroll
+        for (int q = 0; q < 4; q++) sum += __uint_as_float(lo[q] << 16) + __uint_as_float(hi[q] << 16);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (live) {
+            uint4 o;
+            o.x = lo[0] | (hi[0] << 16); o.y = lo[1] | (hi[1] << 16); o.z = lo[2] | (hi[2] << 16); o.w = lo[3] | (hi[3] << 16);
+            const int nt = mrow >> 3, gg = mrow & 7;
+            xs[((span * 4 + i) * NT + nt) * 32 + gg * 4 + tt] = o;
+            if ((o8 & 15) == 0) xsum[span][mrow] = sum;
+        }
     }
     __syncthreads();
 
+    // ---- multiply -----------------------------------------------------------------------------------
     float total[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) { total[nt][0] = total[nt][1] = total[nt][2] = total[nt][3] = 0.0f; }
-
 #pragma unroll
-    for (int s = 0; s < MAXS; s++) {
+    for (int s = 0; s < SPANS; s++) {
         if (s < spans) {
-            const float sa = __half2float(__ushort_as_half(sca[s])), sb = __half2float(__ushort_as_half(scb[s]));
-            const uint32_t zma = 0x43004300u | zwa[s] | (zwa[s] << 16), zmb = 0x43004300u | zwb[s] | (zwb[s] << 16);   // bf16x2 (128 + zp)
             float part[NT][4];
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) { part[nt][0] = part[nt][1] = part[nt][2] = part[nt][3] = 0.0f; }
             const uint32_t wwa[4] = {wa[s].x, wa[s].y, wa[s].z, wa[s].w}, wwb[4] = {wb[s].x, wb[s].y, wb[s].z, wb[s].w};
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                uint32_t ra[4], rb[4];
+                uint32_t ra[4], rb4[4];
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    // bf16 0x4300 | c == 128 + c exactly; subtracting 128 + zp is exact as well
-                    ra[q] = bf16x2_sub(((wwa[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u, zma);
-                    rb[q] = bf16x2_sub(((wwb[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u, zmb);
+                    ra[q] = ((wwa[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u;           // bf16x2 (128 + c, 128 + c')
+                    rb4[q] = ((wwb[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u;
                 }
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
                     const uint4 b = xs[((s * 4 + i) * NT + nt) * 32 + lane];
-                    mma_bf16_16816(part[nt], ra[0], rb[0], ra[1], rb[1], b.x, b.y);
-                    mma_bf16_16816(part[nt], ra[2], rb[2], ra[3], rb[3], b.z, b.w);
+                    mma_bf16_16816(part[nt], ra[0], rb4[0], ra[1], rb4[1], b.x, b.y);
+                    mma_bf16_16816(part[nt], ra[2], rb4[2], ra[3], rb4[3], b.z, b.w);
                 }
             }
+            const float sa = __half2float(__ushort_as_half((unsigned short)sca[s])), sb = __half2float(__ushort_as_half((unsigned short)scb[s]));
+            const float zca = -sa * (128.0f + (float)zwa[s]), zcb = -sb * (128.0f + (float)zwb[s]);   // -(128 + z) * scale
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
-                total[nt][0] = fmaf(sa, part[nt][0], total[nt][0]);
-                total[nt][1] = fmaf(sa, part[nt][1], total[nt][1]);
-                total[nt][2] = fmaf(sb, part[nt][2], total[nt][2]);
-                total[nt][3] = fmaf(sb, part[nt][3], total[nt][3]);
+                const float2 xsm = *reinterpret_cast<const float2*>(&xsum[s][nt * 8 + 2 * t]);
+                total[nt][0] += fmaf(sa, part[nt][0], zca * xsm.x);
+                total[nt][1] += fmaf(sa, part[nt][1], zca * xsm.y);
+                total[nt][2] += fmaf(sb, part[nt][2], zcb * xsm.x);
+                total[nt][3] += fmaf(sb, part[nt][3], zcb * xsm.y);
             }
         }
     }
@@ -306,49 +320,33 @@ int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const voi
     if (int32_t rc = oxq_require_sm100(h)) return rc;
 
     const int row_blocks = (int)((n + W4_ROWS_PER_CTA - 1) / W4_ROWS_PER_CTA);
-    const int nt = (int)((m + 7) / 8);
-    // Split K so that about three CTAs per SM are in flight, each with at most 8 spans (1024 K).
+    // K chunks of 4 spans (512 K): many short CTAs, so the tail of the grid is short as well
     const int spans_total = (int)(k / 128);
-    int splits = (3 * h->sm_count + row_blocks - 1) / row_blocks;
-    int max_splits = spans_total / 2 > 0 ? spans_total / 2 : 1;
-    if (splits > max_splits) splits = max_splits;
-    if (splits < 1) splits = 1;
-    int spans_per = (spans_total + splits - 1) / splits;
-    if (spans_per > 8) spans_per = 8;
-    splits = (spans_total + spans_per - 1) / spans_per;
-
-    W4Params p;
-    p.m = (int)m; p.n = (int)n; p.k = (int)k; p.group = group; p.kc = spans_per * 128; p.splits = splits;
-    p.x = (const __nv_bfloat16*)x; p.codes = codes; p.scales = scales; p.zeros = zeros; p.y = (__nv_bfloat16*)y;
-    p.ws = nullptr; p.counters = nullptr;
+    const int spans_per = spans_total < W4_SPANS ? spans_total : W4_SPANS;
+    const int splits = (spans_total + spans_per - 1) / spans_per;
+    float* ws_sums = nullptr;
+    int* ws_counters = nullptr;
     if (splits > 1) {
         const size_t need = oxq_gemm_w4a16_workspace_bytes(m, n, k);
         if (!ws || ws_bytes < need || ((uintptr_t)ws & 255u))
             OXQ_FAIL(h, OXQ_ERR_BUFFER_TOO_SMALL, "workspace: expected at least %zu bytes (256-byte aligned), got %zu", need, ws_bytes);
         size_t f = ((size_t)m * (size_t)n * sizeof(float) + 255) & ~(size_t)255;
-        p.ws = (float*)ws;
-        p.counters = (int*)((char*)ws + f);
+        ws_sums = (float*)ws;
+        ws_counters = (int*)((char*)ws + f);
     }
-    const size_t smem = (size_t)spans_per * 4 * nt * 32 * sizeof(uint4);
     dim3 grid(row_blocks, splits);
-#define LAUNCH_NT(NTV)                                                                                              \
-    do {                                                                                                            \
-        static bool attr = false;                                                                                   \
-        if (!attr) {                                                                                                \
-            OXQ_CUDA(h, cudaFuncSetAttribute(w4a16_decode_kernel<NTV, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 4 * NTV * 32 * 16)); \
-            OXQ_CUDA(h, cudaFuncSetAttribute(w4a16_decode_kernel<NTV, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 4 * NTV * 32 * 16)); \
-            attr = true;                                                                                            \
-        }                                                                                                           \
-        if (spans_per <= 4) w4a16_decode_kernel<NTV, 4><<<grid, W4_THREADS, smem, h->stream>>>(p);                  \
-        else w4a16_decode_kernel<NTV, 8><<<grid, W4_THREADS, smem, h->stream>>>(p);                                 \
-    } while (0)
-    switch (nt) {
-        case 1: LAUNCH_NT(1); break;
-        case 2: LAUNCH_NT(2); break;
-        case 3: LAUNCH_NT(3); break;
-        default: LAUNCH_NT(4); break;
+    // Batches above 16 rows run as passes of 16: the legacy MMA path is the limit there, and the second pass
+    // finds most of the weight bytes in L2.
+    for (int64_t m0 = 0; m0 < m; m0 += 16) {
+        const int mc = (int)(m - m0 < 16 ? m - m0 : 16);
+        W4Params p;
+        p.m = mc; p.n = (int)n; p.k = (int)k; p.group = group; p.kc = spans_per * 128; p.splits = splits;
+        p.x = (const __nv_bfloat16*)x + m0 * k; p.codes = codes; p.scales = scales; p.zeros = zeros;
+        p.y = (__nv_bfloat16*)y + m0 * n;
+        p.ws = ws_sums ? ws_sums + m0 * n : nullptr; p.counters = ws_counters;
+        if (mc <= 8) w4a16_decode_kernel<1, W4_SPANS><<<grid, W4_THREADS, 0, h->stream>>>(p);
+        else w4a16_decode_kernel<2, W4_SPANS><<<grid, W4_THREADS, 0, h->stream>>>(p);
     }
-#undef LAUNCH_NT
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -357,7 +355,7 @@ int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const voi
 // Scratch for oxq_gemm_w4a16_static: lives in the library image, so every GPU that loads the library
 // carries these bytes until the process exits.  Layout: [kStaticW4MaxOut f32 partial sums][counters].
 static constexpr size_t kStaticW4MaxOut = 512 * 1024;                       // m * n <= 524288 outputs (2 MiB of f32)
-static constexpr size_t kStaticW4Counters = kStaticW4MaxOut / W4_ROWS_PER_CTA; // one counter per 128 weight rows (m >= 1)
+static constexpr size_t kStaticW4Counters = kStaticW4MaxOut / W4_ROWS_PER_CTA; // one counter per 64 weight rows (m >= 1)
 static constexpr size_t kStaticW4Bytes = kStaticW4MaxOut * sizeof(float) + kStaticW4Counters * sizeof(int);
 static __device__ __align__(256) unsigned char g_w4_static_scratch[kStaticW4Bytes];
 

@@ -197,6 +197,14 @@ OXQ_API int32_t oxq_gemm_nvfp4(oxq_handle* h, int64_t m, int64_t n, int64_t k, c
                        const float* gx_dev, const uint8_t* w_dev, const uint8_t* sfw_mma_dev, const float* gw_dev,
                        void* y_bf16_dev, int64_t ldy);
 
+/* ---- tensor-parallel combine: RowLinear::all_reduce (crates/oxicuda-dist-infer/src/tensor_parallel/row_parallel.rs:199-223),
+ *      which sums the rank partials on the host, done in place over the NVSwitch multicast mapping of a symmetric
+ *      bf16 buffer: this rank reduces elements [rank*numel/world, (rank+1)*numel/world) across all replicas (f32
+ *      accumulation in the switch) and broadcasts the sums.  The caller provides the cross-rank barriers: every
+ *      rank's partial must be complete before the call starts anywhere, and nobody may read the result before every
+ *      rank's call has finished.  numel % (8 * world) == 0. */
+OXQ_API int32_t oxq_multimem_all_reduce_bf16(oxq_handle* h, void* multicast_ptr, int64_t numel, int rank, int world);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,50 @@
+// All-reduce of the tensor-parallel partial sums through the NVSwitch multicast path (NVLS): every rank owns
+// 1/world of the buffer, pulls the sum of all replicas of its slice with multimem.ld_reduce (the switch adds,
+// f32 accumulation) and pushes the result back to every replica with multimem.st.  Each byte crosses a GPU's
+// links about once per direction, half of what a ring moves.  The kernel does not wait on other GPUs: the
+// caller brackets it with cross-rank barriers (all partials written before, all slices written after).
+#include "oxq_common.cuh"
+
+namespace oxq {
+
+__device__ __forceinline__ uint4 mm_ld_reduce(const uint4* p) {
+    uint4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+    return r;
+}
+__device__ __forceinline__ void mm_st(uint4* p, const uint4& r) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                 ::"l"(p), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w) : "memory");
+}
+
+// four reductions in flight per thread: a round trip through the switch takes microseconds
+__global__ void __launch_bounds__(512) multimem_all_reduce_bf16_kernel(uint4* mc, int64_t vec_lo, int64_t vec_hi) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    int64_t v = vec_lo + blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    for (; v + 3 * stride < vec_hi; v += 4 * stride) {
+        const uint4 a = mm_ld_reduce(mc + v), b = mm_ld_reduce(mc + v + stride), c = mm_ld_reduce(mc + v + 2 * stride),
+                    d = mm_ld_reduce(mc + v + 3 * stride);
+        mm_st(mc + v, a); mm_st(mc + v + stride, b); mm_st(mc + v + 2 * stride, c); mm_st(mc + v + 3 * stride, d);
+    }
+    for (; v < vec_hi; v += stride) mm_st(mc + v, mm_ld_reduce(mc + v));
+}
+
+}  // namespace oxq
+
+extern "C" int32_t oxq_multimem_all_reduce_bf16(oxq_handle* h, void* multicast_ptr, int64_t numel, int rank, int world) {
+    OXQ_CHECK_HANDLE(h);
+    if (numel <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "all_reduce: empty input");
+    if (world < 1 || rank < 0 || rank >= world) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "rank %d outside world of %d", rank, world);
+    if (!multicast_ptr || ((uintptr_t)multicast_ptr & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned multicast pointer");
+    if (numel % (8 * (int64_t)world) != 0) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "numel %lld must be a multiple of 8 * world", (long long)numel);
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    const int64_t vecs = numel / 8, per = vecs / world;
+    const int64_t lo = per * rank, hi = lo + per;
+    int64_t blocks = (per + 512 * 4 - 1) / (512 * 4);
+    if (blocks > h->sm_count) blocks = h->sm_count;
+    if (blocks < 1) blocks = 1;
+    oxq::multimem_all_reduce_bf16_kernel<<<(int)blocks, 512, 0, h->stream>>>((uint4*)multicast_ptr, lo, hi);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}

@@ -621,6 +621,9 @@ static int32_t launch2(oxq_handle* h, const void* x, int64_t ldx_bytes, const vo
 template <int KIND, int EPI = EPI_SCALE>
 static int32_t launch_dense(oxq_handle* h, const void* x, int64_t ldx_bytes, const void* w, int64_t ldw_bytes, const GemmParams& p) {
     if (use_2cta_setting() && p.m > 128) return launch2<KIND, EPI>(h, x, ldx_bytes, w, ldw_bytes, p);
+    // One 128-row tile of X (decode shapes): the weight stream is the whole cost, so narrow tiles are used to
+    // spread it over all SMs (N = 8192 gives 128 tiles of 64 columns instead of 32 of 256).
+    if (EPI == EPI_SCALE && p.m <= 128 && (p.n + 255) / 256 < 2 * h->sm_count) return launch<KIND, 64, EPI_SCALE>(h, x, ldx_bytes, w, ldw_bytes, p);
     return launch<KIND, 256, EPI>(h, x, ldx_bytes, w, ldw_bytes, p);
 }
 

@@ -98,6 +98,44 @@ class TpSwiGluMlp:
             self.d_codes, self.d_scales, self.d_zeros = ops.int4g_quant_pack(d.float(), 128)
             self._ws = {}
         self._comm_stream = torch.cuda.Stream() if self.overlap_chunks > 1 else None
+        self._symm = None           # (buffer, handle) of the NVLS all-reduce path, created on first use
+        import os
+        self.use_multimem = tp > 1 and reduce_dtype == torch.bfloat16 and os.environ.get("OXQ_TP_NO_MULTIMEM", "0") != "1"
+
+    # -- NVLS path: symmetric output buffer mapped through the NVSwitch multicast object ----------
+    def _symm_buffer(self, m: int):
+        """Symmetric [m_cap x hidden] bf16 buffer + its rendezvous handle, or None if multicast is unavailable."""
+        if not self.use_multimem:
+            return None
+        if self._symm is not None and self._symm[0].shape[0] >= m:
+            return self._symm
+        try:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm_mem
+            cap = max(m, 2048)
+            buf = symm_mem.empty((cap, self.hidden), dtype=torch.bfloat16, device=torch.device("cuda", torch.cuda.current_device()))
+            hdl = symm_mem.rendezvous(buf, self.group if self.group is not None else dist.group.WORLD)
+            if not hdl.multicast_ptr:                  # 0 when the fabric offers no multicast mapping
+                raise RuntimeError("no multicast support")
+            self._symm = (buf, hdl)
+        except Exception:
+            self.use_multimem = False       # NCCL all-reduce instead
+            self._symm = None
+        return self._symm
+
+    def _forward_multimem(self, x: torch.Tensor):
+        """down-projection partial straight into the symmetric buffer, barrier, in-switch reduce + broadcast, barrier."""
+        m = x.shape[0]
+        sym = self._symm_buffer(m)
+        if sym is None or (m * self.hidden) % (8 * self.tp) != 0:
+            return None
+        buf, hdl = sym
+        y = buf[:m]
+        self.forward_partial(x, out=y)
+        hdl.barrier(channel=0)
+        self.ops.multimem_all_reduce_bf16(hdl.multicast_ptr, m * self.hidden, self.rank, self.tp)
+        hdl.barrier(channel=1)
+        return y
 
     # -- local (per-rank) partial: [M x hidden] --------------------------------------------------
     def forward_partial(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -129,12 +167,33 @@ class TpSwiGluMlp:
         m = x.shape[0]
         chunks = min(self.overlap_chunks, max(1, m // 256))
         if chunks <= 1:
+            if self.use_multimem:
+                y = self._forward_multimem(x)
+                if y is not None:
+                    return y
             y = self.forward_partial(x)
             return self._all_reduce(y)
         # M-chunk pipelining: the all-reduce of chunk i runs on a side stream while chunk i+1 computes
-        y = torch.empty((m, self.hidden), dtype=torch.bfloat16, device=x.device)
         bounds = [(i * m) // chunks for i in range(chunks + 1)]
         main = torch.cuda.current_stream()
+        sym = self._symm_buffer(m) if self.use_multimem else None
+        if sym is not None and all(((bounds[i + 1] - bounds[i]) * self.hidden) % (8 * self.tp) == 0 for i in range(chunks)):
+            buf, hdl = sym
+            y = buf[:m]
+            self._comm_stream.wait_stream(main)
+            for i in range(chunks):
+                lo, hi = bounds[i], bounds[i + 1]
+                self.forward_partial(x[lo:hi], out=y[lo:hi])
+                ev = torch.cuda.Event()
+                ev.record(main)
+                with torch.cuda.stream(self._comm_stream):
+                    self._comm_stream.wait_event(ev)
+                    hdl.barrier(channel=2 * i)
+                    self.ops.multimem_all_reduce_bf16(hdl.multicast_ptr + lo * self.hidden * 2, (hi - lo) * self.hidden, self.rank, self.tp)
+                    hdl.barrier(channel=2 * i + 1)
+            main.wait_stream(self._comm_stream)
+            return y
+        y = torch.empty((m, self.hidden), dtype=torch.bfloat16, device=x.device)
         for i in range(chunks):
             lo, hi = bounds[i], bounds[i + 1]
             self.forward_partial(x[lo:hi], out=y[lo:hi])
@@ -154,6 +213,25 @@ class TpSwiGluMlp:
             return z.to(torch.bfloat16)
         dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
         return y
+
+    # -- CUDA-graph replay of the whole layer ---------------------------------------------------------
+    def capture(self, m: int):
+        """Captures forward() for a fixed batch of m rows into a CUDA graph.  Returns (x_static, y_static, graph):
+        fill x_static, call graph.replay(), read y_static.  A decode step is a dozen launches of a few microseconds
+        each, so replaying them from a graph removes the host launch cost from the step."""
+        dev = torch.device("cuda", torch.cuda.current_device())
+        x_static = torch.zeros((m, self.hidden), dtype=torch.bfloat16, device=dev)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):                       # warm-up outside capture: workspaces, attributes, symmetric buffers
+                self.forward(x_static)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            y_static = self.forward(x_static)
+        return x_static, y_static, graph
 
     # -- bookkeeping for the benchmark -------------------------------------------------------------
     def flops(self, m: int) -> float:

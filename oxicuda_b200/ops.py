@@ -314,3 +314,10 @@ def gemm_nvfp4(x_packed, x_sf_mma, x_stats, w_packed, w_sf_mma, w_stats, out: to
     handle(x_packed.device.index).call("oxq_gemm_nvfp4", m, n, k, _p(x_packed), _p(x_sf_mma), _p(x_stats[1:]),
                                        _p(w_packed), _p(w_sf_mma), _p(w_stats[1:]), _p(y), y.stride(0))
     return y
+
+
+# ------------------------------------------------------------------------------------------- collective
+
+def multimem_all_reduce_bf16(multicast_ptr: int, numel: int, rank: int, world: int, device_index: int | None = None):
+    """In-place all-reduce over the multicast mapping of a symmetric bf16 buffer; the caller provides the barriers."""
+    handle(device_index).call("oxq_multimem_all_reduce_bf16", C.c_void_p(multicast_ptr), numel, rank, world)

@@ -152,6 +152,20 @@ __device__ __forceinline__ InvDiv make_invdiv(float s) {
     d.fast = s >= 0x1p-60f && s <= 0x1p60f;
     return d;
 }
+// Variant for callers that know |x / s| cannot overflow (s was derived from the maximum of the data, so a
+// non-finite x would have made s non-finite and taken the slow path) and that do not care about the sign of a
+// zero quotient (integer codes): the multiply and the two FMAs only.
+__device__ __forceinline__ float div_exact_bounded(float x, const InvDiv& d) {
+    if (!d.fast) return __fdiv_rn(x, d.s);
+    const float q0 = x * d.y;
+    return fmaf(fmaf(-d.s, q0, x), d.y, q0);
+}
+// Same, keeping the sign of zero (FP8 / FP4 codes show it).
+__device__ __forceinline__ float div_exact_bounded_signed(float x, const InvDiv& d) {
+    if (!d.fast) return __fdiv_rn(x, d.s);
+    const float q0 = x * d.y;
+    return copysignf(fmaf(fmaf(-d.s, q0, x), d.y, q0), x);
+}
 __device__ __forceinline__ float div_exact(float x, const InvDiv& d) {
     if (!d.fast) return __fdiv_rn(x, d.s);
     const float q0 = x * d.y;
@@ -169,6 +183,11 @@ __device__ __forceinline__ float div_exact(float x, const InvDiv& d) {
 __host__ __device__ __forceinline__ size_t sf_mma_offset(int64_t r, int64_t c, int64_t sf_cols) {
     int64_t col_tiles = (sf_cols + 3) / 4;
     return (size_t)(((r >> 7) * col_tiles + (c >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (c & 3));
+}
+
+// 32-bit form for the kernels (row < 2^31 / 128 tiles etc. is checked on the host)
+__device__ __forceinline__ uint32_t sf_mma_offset32(uint32_t r, uint32_t c, uint32_t col_tiles) {
+    return ((r >> 7) * col_tiles + (c >> 2)) * 512u + (r & 31u) * 16u + ((r & 127u) >> 5) * 4u + (c & 3u);
 }
 
 }  // namespace oxq

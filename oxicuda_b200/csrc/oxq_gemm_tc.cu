@@ -34,6 +34,7 @@ struct GemmParams {
     int sf_col_tiles;                 // 4-column scale-factor tiles per row tile
     int sfa_row_tiles, sfb_row_tiles;
     int group_m;                      // M-tiles per rasterisation group (L2 reuse of the X panel)
+    int debug_flags;                  // timing experiments only (bit 0: skip the scale-factor copies; results are wrong)
     int32_t* status;
 };
 
@@ -163,7 +164,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     tc_fence_after();
                     const uint64_t adesc = smem_desc_sw128(sm_a + stage * C::kABytes);
                     const uint64_t bdesc = smem_desc_sw128(sm_b + stage * C::kBBytes);
-                    if (C::kScaled) {
+                    if (C::kScaled && !(p.debug_flags & 1)) {
 #pragma unroll
                         for (int c = 0; c < C::kSfChunks; c++) {
                             tc_cp_32x128b_warpx4(tmem_base + C::kSfaCol + 4 * c, smem_desc_sf(sm_sfa + stage * C::kSfaBytes + c * 512));
@@ -520,6 +521,169 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     }
 }
 
+// ---- 2-CTA variant of the block-scaled kinds -------------------------------------------------------
+// Tile = 256 (M, two CTAs) x 192 (N).  CTA r loads rows [128r, +128) of the X tile with their scale chunks, rows
+// [96r, +96) of the W tile, and the scale chunks of both 128-row W tiles that cover the 192 columns (every CTA
+// needs the B scales of all columns).  CTA 0 issues tcgen05.cp.cta_group::2 (each CTA copies its own scale
+// chunks into its own tensor memory) and tcgen05.mma.cta_group::2.  Tensor memory per CTA: accumulators at
+// columns 0 and 256 (192 wide), A scales at 448, B scales at 464.  Scale factors travel as TMA tiles of
+// 512-byte chunks (a [chunks x 128] u32 view of the tiled scale array) so that, like the operands, they can
+// count their bytes on CTA 0's barrier.
+template <int KIND>
+struct Cfg2S {
+    static constexpr int kSfChunks = KIND == KIND_MXF8 ? 1 : 4;
+    static constexpr int kSfBytes = kSfChunks * 512;
+    static constexpr int BN2 = 192;
+    static constexpr int kABytes = BM * BKB, kBBytes = (BN2 / 2) * BKB;
+    static constexpr int kStageBytes = kABytes + kBBytes + 3 * kSfBytes;           // A, B half, SFA, 2 x SFB
+    static constexpr int kStages = (SMEM_BUDGET - 2048) / kStageBytes > 8 ? 8 : (SMEM_BUDGET - 2048) / kStageBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 2048;
+    static constexpr int kSfaCol = 448, kSfbCol = 464;
+};
+
+template <int KIND>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tc2_scaled_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                       const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {
+    using C = Cfg2S<KIND>;
+    constexpr int S = C::kStages;
+    constexpr int BN2 = C::BN2, BM2 = 256;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sm_a = base;
+    const uint32_t sm_b = sm_a + S * C::kABytes;
+    const uint32_t sm_sfa = sm_b + S * C::kBBytes;
+    const uint32_t sm_sfb = sm_sfa + S * C::kSfBytes;
+    const uint32_t sm_bar = sm_sfb + S * 2 * C::kSfBytes;
+    const uint32_t bar_full = sm_bar, bar_empty = sm_bar + 8 * S;
+    const uint32_t bar_tfull = sm_bar + 16 * S, bar_tempty = bar_tfull + 16;
+    const uint32_t tmem_slot = bar_tempty + 16;
+    uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta_rank = cluster_ctarank();
+    const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+    const int tiles_m = (p.m + BM2 - 1) / BM2, tiles_n = (p.n + BN2 - 1) / BN2;
+    const int num_tiles = tiles_m * tiles_n;
+    const int num_kb = (p.k_bytes + BKB - 1) / BKB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 8); }
+        fence_barrier_init();
+        prefetch_tmap(&tm_a); prefetch_tmap(&tm_b); prefetch_tmap(&tm_sfa); prefetch_tmap(&tm_sfb);
+    }
+    if (warp == 1) { tmem_alloc_cg2(tmem_slot, 512); tmem_relinquish_cg2(); }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+                int tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+                const int m0 = tm * BM2 + (int)cta_rank * BM, n0 = tn * BN2;
+                const int sfa_row = (m0 >> 7) * p.sf_col_tiles, sfb_row = (n0 >> 7) * p.sf_col_tiles;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                    if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * C::kStageBytes);
+                    const uint32_t full0 = mapa_shared(bar_full + 8 * stage, 0);
+                    tma_load_2d_cg2(sm_a + stage * C::kABytes, &tm_a, kb * BKB, m0, full0);
+                    tma_load_2d_cg2(sm_b + stage * C::kBBytes, &tm_b, kb * BKB, n0 + (int)cta_rank * (BN2 / 2), full0);
+                    // scale chunks: rows of the [chunk x 128 u32] view; rows past the end read as zero
+                    tma_load_2d_cg2(sm_sfa + stage * C::kSfBytes, &tm_sfa, 0, sfa_row + kb * C::kSfChunks, full0);
+                    tma_load_2d_cg2(sm_sfb + stage * 2 * C::kSfBytes, &tm_sfb, 0, sfb_row + kb * C::kSfChunks, full0);
+                    tma_load_2d_cg2(sm_sfb + stage * 2 * C::kSfBytes + C::kSfBytes, &tm_sfb, 0, sfb_row + p.sf_col_tiles + kb * C::kSfChunks, full0);
+                    if (++stage == S) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && cta_rank == 0) {
+            constexpr uint32_t idesc = KIND == KIND_MXF8 ? idesc_block_scaled(0, 0, 1, BM2, BN2) : idesc_block_scaled(1, 1, 0, BM2, BN2);
+            int stage = 0; uint32_t phase = 0;
+            int acc = 0; uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+                int tm, tn;
+                tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+                const uint32_t sfb_shift = (uint32_t)((tn * BN2) & 127) >> 5;       // 0 or 2: odd tiles start 64 rows into a scale tile
+                if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * 256;
+                for (int kb = 0; kb < num_kb; kb++) {
+                    if (!mbar_wait(bar_full + 8 * stage, phase)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                    tc_fence_after();
+                    const uint64_t adesc = smem_desc_sw128(sm_a + stage * C::kABytes);
+                    const uint64_t bdesc = smem_desc_sw128(sm_b + stage * C::kBBytes);
+#pragma unroll
+                    for (int c = 0; c < C::kSfChunks; c++) {
+                        tc_cp_32x128b_warpx4_cg2(tmem_base + C::kSfaCol + 4 * c, smem_desc_sf(sm_sfa + stage * C::kSfBytes + c * 512));
+                        tc_cp_32x128b_warpx4_cg2(tmem_base + C::kSfbCol + 8 * c, smem_desc_sf(sm_sfb + stage * 2 * C::kSfBytes + c * 512));
+                        tc_cp_32x128b_warpx4_cg2(tmem_base + C::kSfbCol + 8 * c + 4, smem_desc_sf(sm_sfb + stage * 2 * C::kSfBytes + C::kSfBytes + c * 512));
+                    }
+#pragma unroll
+                    for (int k = 0; k < BKB / 32; k++) {
+                        const uint64_t a = adesc + (uint64_t)(k * 2), b = bdesc + (uint64_t)(k * 2);
+                        const uint32_t accum = (kb | k) != 0;
+                        if (KIND == KIND_MXF8)
+                            mma_mxf8f6f4_cg2(d_tmem, a, b, idesc_with_sf_ids(idesc, k, k), accum, tmem_base + C::kSfaCol, tmem_base + C::kSfbCol + sfb_shift);
+                        else
+                            mma_mxf4nvf4_x4_cg2(d_tmem, a, b, idesc, accum, tmem_base + C::kSfaCol + 4 * k, tmem_base + C::kSfbCol + 8 * k + sfb_shift);
+                    }
+                    tc_commit_cg2_mc(bar_empty + 8 * stage, 3);
+                    if (++stage == S) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                tc_commit_cg2_mc(bar_tfull + 8 * acc, 3);
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int acc = 0; uint32_t acc_phase = 0;
+        float tensor_scale = 1.0f;
+        if (KIND == KIND_NVF4) tensor_scale = __ldg(p.s0) * __ldg(p.s1);
+        __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y);
+        for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+            const int m0 = tm * BM2 + (int)cta_rank * BM, n0 = tn * BN2;
+            bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+            tc_fence_after();
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
+#pragma unroll 1
+            for (int c = 0; c < BN2 / 32; c++) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(t_row + c * 32, r);
+                tmem_ld_wait();
+                epilogue_store_scale<KIND_F8>(r, row, n0 + c * 32, p, tensor_scale, 1.0f, y);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * acc, 0));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc_cg2(tmem_base, 512);
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -576,6 +740,7 @@ static int32_t launch(oxq_handle* h, const void* x, int64_t ldx_bytes, const voi
     const int grid = tiles < h->sm_count ? tiles : h->sm_count;
     p.status = h->dev_status;
     p.group_m = group_m_setting();
+    { const char* e = getenv("OXQ_DEBUG_FLAGS"); p.debug_flags = e ? atoi(e) : 0; }
     gemm_tc_kernel<KIND, BN, EPI><<<grid, NUM_THREADS, C::kSmemBytes, h->stream>>>(tm_a, tm_b, p);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
@@ -625,6 +790,50 @@ static int32_t launch_dense(oxq_handle* h, const void* x, int64_t ldx_bytes, con
     // spread it over all SMs (N = 8192 gives 128 tiles of 64 columns instead of 32 of 256).
     if (EPI == EPI_SCALE && p.m <= 128 && (p.n + 255) / 256 < 2 * h->sm_count) return launch<KIND, 64, EPI_SCALE>(h, x, ldx_bytes, w, ldw_bytes, p);
     return launch<KIND, 256, EPI>(h, x, ldx_bytes, w, ldw_bytes, p);
+}
+
+// [chunks x 128] u32 view of a tiled scale-factor array: one row per 512-byte chunk, box = `box_chunks` rows.
+static bool make_tmap_sf(CUtensorMap* tm, const void* ptr, int64_t total_chunks, int box_chunks) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {128, (cuuint64_t)total_chunks};
+    cuuint64_t strides[1] = {512};
+    cuuint32_t box[2] = {128, (cuuint32_t)box_chunks};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int KIND>
+static int32_t launch2_scaled(oxq_handle* h, const void* x, int64_t ldx_bytes, const void* w, int64_t ldw_bytes, GemmParams p) {
+    using C = Cfg2S<KIND>;
+    CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
+    if (!make_tmap_bytes(&tm_a, x, p.m, p.k_bytes, ldx_bytes, BM) || !make_tmap_bytes(&tm_b, w, p.n, p.k_bytes, ldw_bytes, C::BN2 / 2) ||
+        !make_tmap_sf(&tm_sfa, p.sfa, (int64_t)p.sfa_row_tiles * p.sf_col_tiles, C::kSfChunks) ||
+        !make_tmap_sf(&tm_sfb, p.sfb, (int64_t)p.sfb_row_tiles * p.sf_col_tiles, C::kSfChunks))
+        OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned, leading dimensions multiples of 16 bytes)");
+    static int max_clusters = 0;
+    if (max_clusters == 0) {
+        OXQ_CUDA(h, cudaFuncSetAttribute(gemm_tc2_scaled_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(h->sm_count & ~1, 1, 1);
+        cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = C::kSmemBytes;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr; cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_scaled_kernel<KIND>, &cfg) != cudaSuccess || n < 1) n = h->sm_count / 2;
+        max_clusters = n < h->sm_count / 2 ? n : h->sm_count / 2;
+    }
+    const int tiles = ((p.m + 255) / 256) * ((p.n + C::BN2 - 1) / C::BN2);
+    const int clusters = tiles < max_clusters ? tiles : max_clusters;
+    p.status = h->dev_status;
+    p.group_m = group_m_setting() / 2 > 0 ? group_m_setting() / 2 : 1;
+    gemm_tc2_scaled_kernel<KIND><<<2 * clusters, NUM_THREADS, C::kSmemBytes, h->stream>>>(tm_a, tm_b, tm_sfa, tm_sfb, p);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
 }
 
 static int32_t check_gemm_args(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, const void* w, const void* y, int64_t ldy) {
@@ -709,6 +918,7 @@ int32_t oxq_gemm_mxfp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uin
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y; p.ldy = ldy;
     p.sfa = sfx; p.sfb = sfw; p.sf_col_tiles = (int)(k / 32 + 3) / 4;
     p.sfa_row_tiles = (int)((m + 127) / 128); p.sfb_row_tiles = (int)((n + 127) / 128);
+    if (use_2cta_setting() && m > 128) return launch2_scaled<KIND_MXF8>(h, x, k, w, k, p);
     return launch<KIND_MXF8, 192>(h, x, k, w, k, p);
 }
 
@@ -722,6 +932,11 @@ int32_t oxq_gemm_nvfp4(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uin
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)(k / 2); p.y = y; p.ldy = ldy; p.s0 = gx; p.s1 = gw;
     p.sfa = sfx; p.sfb = sfw; p.sf_col_tiles = (int)(k / 16 + 3) / 4;
     p.sfa_row_tiles = (int)((m + 127) / 128); p.sfb_row_tiles = (int)((n + 127) / 128);
+    // Measured on B200 the CTA-pair kernel is not faster for NVFP4 (the scale-factor copies into tensor memory, not
+    // operand traffic, are the limit), so it is opt-in: OXQ_GEMM_NVFP4_2CTA=1.
+    static int nv2 = -1;
+    if (nv2 < 0) { const char* e = getenv("OXQ_GEMM_NVFP4_2CTA"); nv2 = e ? (atoi(e) != 0) : 0; }
+    if (nv2 && use_2cta_setting() && m > 128) return launch2_scaled<KIND_NVF4>(h, x, k / 2, w, k / 2, p);
     return launch<KIND_NVF4, 192>(h, x, k / 2, w, k / 2, p);
 }
 

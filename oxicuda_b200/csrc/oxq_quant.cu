@@ -9,10 +9,22 @@ namespace oxq {
 // INT8 symmetric per-row
 // ------------------------------------------------------------------------------------------------
 
-__device__ __forceinline__ int quant_i8(float x, const InvDiv& scale, int rounding) {
-    float v = round_mode(div_exact(x, scale), rounding);
-    if (v != v) return 0;                                   // NaN -> code 0 (Rust `as i32`)
-    return __float2int_rn(fminf(fmaxf(v, -127.0f), 127.0f));
+// x / scale -> int8 code in the low byte of the result.  The scale comes from the row's own maximum, so
+// |x / scale| <= 127 (+ rounding) for every finite x and an Inf in the row takes the slow path of div_exact.
+// Rounding happens in the FMA pipe: adding 1.5 * 2^23 leaves round-to-nearest-even(v) in the low mantissa
+// bits (two's complement), so no conversion instruction is needed.  Half-away differs from half-even only at
+// exact ties whose even neighbour is the one nearer zero.
+__device__ __forceinline__ uint32_t quant_i8(float x, const InvDiv& scale, int rounding) {
+    float v = div_exact_bounded(x, scale);
+    v = v != v ? 0.0f : v;                                  // NaN -> code 0 (Rust `as i32`)
+    v = fminf(fmaxf(v, -127.0f), 127.0f);
+    const float m = v + 12582912.0f;                        // RNE(v) + 1.5 * 2^23
+    uint32_t code = __float_as_uint(m);
+    if (rounding == OXQ_ROUND_HALF_AWAY) {
+        const float r = m - 12582912.0f;                    // RNE(v) as a float
+        if (fabsf(v - r) == 0.5f && fabsf(r) < fabsf(v)) code += v < 0.0f ? 0xFFFFFFFFu : 1u;
+    }
+    return code & 0xFFu;
 }
 
 // One CTA per row at a time (grid-stride over rows).  Each thread keeps up to NV float4 of the row in
@@ -70,17 +82,15 @@ __global__ void __launch_bounds__(256) int8_quant_rows_kernel(const float* __res
         for (int i = 0; i < NV; i++) {
             const int64_t idx = tid + (int64_t)i * 256;
             if (idx < nvec) {
-                uint32_t p = (uint32_t)(quant_i8(cur[i].x, scale, rounding) & 0xFF) |
-                             ((uint32_t)(quant_i8(cur[i].y, scale, rounding) & 0xFF) << 8) |
-                             ((uint32_t)(quant_i8(cur[i].z, scale, rounding) & 0xFF) << 16) |
-                             ((uint32_t)(quant_i8(cur[i].w, scale, rounding) & 0xFF) << 24);
+                uint32_t p = quant_i8(cur[i].x, scale, rounding) | (quant_i8(cur[i].y, scale, rounding) << 8) |
+                             (quant_i8(cur[i].z, scale, rounding) << 16) | (quant_i8(cur[i].w, scale, rounding) << 24);
                 __stcs(qr + idx, p);
             }
         }
         for (int64_t idx = tid + (int64_t)NV * 256; idx < nvec; idx += 256) {
             float4 t = __ldg(xr + idx);
-            qr[idx] = (uint32_t)(quant_i8(t.x, scale, rounding) & 0xFF) | ((uint32_t)(quant_i8(t.y, scale, rounding) & 0xFF) << 8) |
-                      ((uint32_t)(quant_i8(t.z, scale, rounding) & 0xFF) << 16) | ((uint32_t)(quant_i8(t.w, scale, rounding) & 0xFF) << 24);
+            qr[idx] = quant_i8(t.x, scale, rounding) | (quant_i8(t.y, scale, rounding) << 8) |
+                      (quant_i8(t.z, scale, rounding) << 16) | (quant_i8(t.w, scale, rounding) << 24);
         }
 #pragma unroll
         for (int i = 0; i < NV; i++) cur[i] = nxt[i];
@@ -215,7 +225,7 @@ __device__ __forceinline__ float e4m3_refcompat_decode(uint8_t b) {
 // stats != nullptr the scale is derived from stats[0] (absmax) as absmax/448 (1.0 when absmax == 0) and
 // thread 0 records it in stats[1].
 constexpr int FP8_ILP = 4;
-template <typename T, int MODE>
+template <typename T, int MODE, bool BOUNDED>
 __global__ void __launch_bounds__(256) fp8_quant_kernel(const T* __restrict__ x, int64_t n, const float* __restrict__ scale_ptr,
                                                         float* __restrict__ stats, uint8_t* __restrict__ q) {
     constexpr int V = Vec16<T>::N;                          // elements per 16-byte load (8 or 4)
@@ -251,7 +261,8 @@ __global__ void __launch_bounds__(256) fp8_quant_kernel(const T* __restrict__ x,
 #pragma unroll
                 for (int l = 0; l < L; l++)
 #pragma unroll
-                    for (int e = 0; e < V; e++) f[l * V + e] = div_exact(Elem<T>::to_f32(in[j][l].v[e]), scale);
+                    for (int e = 0; e < V; e++)
+                        f[l * V + e] = BOUNDED ? div_exact_bounded_signed(Elem<T>::to_f32(in[j][l].v[e]), scale) : div_exact(Elem<T>::to_f32(in[j][l].v[e]), scale);
                 uint32_t w[2];
 #pragma unroll
                 for (int i = 0; i < 2; i++) {
@@ -416,6 +427,7 @@ __global__ void __launch_bounds__(256) mxfp8_quant_kernel(const T* __restrict__ 
                                                           uint8_t* __restrict__ sf_mma) {
     const int64_t nitems = rows * k / 8;
     const int64_t sf_cols = k / 32;
+    const uint32_t sf_col_tiles = (uint32_t)((sf_cols + 3) / 4);
     const int lane = threadIdx.x & 31;
     const int64_t warp_global = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -452,10 +464,10 @@ __global__ void __launch_bounds__(256) mxfp8_quant_kernel(const T* __restrict__ 
             uint32_t hi = (uint32_t)cvt_e4m3x2(f[j][4] * inv, f[j][5] * inv) | ((uint32_t)cvt_e4m3x2(f[j][6] * inv, f[j][7] * inv) << 16);
             __stcs(reinterpret_cast<uint2*>(codes + t * 8), make_uint2(lo, hi));
             if ((t & 3) == 0) {
-                const int64_t blk = t >> 2;
-                const int64_t r = blk / sf_cols, c = blk - r * sf_cols;
+                const uint32_t blk = (uint32_t)(t >> 2);                     // host guarantees < 2^31 blocks
+                const uint32_t r = blk / (uint32_t)sf_cols, c = blk - r * (uint32_t)sf_cols;
                 if (sf_rm) sf_rm[blk] = (uint8_t)byte;
-                if (sf_mma) sf_mma[sf_mma_offset(r, c, sf_cols)] = (uint8_t)byte;
+                if (sf_mma) sf_mma[sf_mma_offset32(r, c, sf_col_tiles)] = (uint8_t)byte;
             }
         }
     }
@@ -479,6 +491,7 @@ __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const T* __restrict__ 
     const InvDiv six_g = make_invdiv(6.0f * g);
     const int64_t nitems = rows * k / 8;
     const int64_t sf_cols = k / 16;
+    const uint32_t sf_col_tiles = (uint32_t)((sf_cols + 3) / 4);
     const int lane = threadIdx.x & 31;
     const int64_t warp_global = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -501,7 +514,7 @@ __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const T* __restrict__ 
             for (int e = 0; e < 8; e++) am = fmaxf(am, fabsf(f[j][e]));
             am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
             if (t >= nitems) continue;
-            const uint8_t s8 = (uint8_t)(cvt_e4m3x2(div_exact(am, six_g), 0.0f) & 0xFF);
+            const uint8_t s8 = (uint8_t)(cvt_e4m3x2(div_exact_bounded(am, six_g), 0.0f) & 0xFF);      // am <= tensor max: quotient <= 448
             uint32_t w = 0;
             if (s8 == 0) {
 #pragma unroll
@@ -510,14 +523,14 @@ __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const T* __restrict__ 
                 const InvDiv d = make_invdiv(g * e4m3_to_f32(s8));
 #pragma unroll
                 for (int e = 0; e < 8; e += 2)
-                    w |= (uint32_t)cvt_e2m1x2(div_exact(f[j][e], d), div_exact(f[j][e + 1], d)) << (4 * e);
+                    w |= (uint32_t)cvt_e2m1x2(div_exact_bounded_signed(f[j][e], d), div_exact_bounded_signed(f[j][e + 1], d)) << (4 * e);   // |x| <= block max: no overflow
             }
             __stcs(reinterpret_cast<uint32_t*>(packed + t * 4), w);
             if ((t & 1) == 0) {
-                const int64_t blk = t >> 1;
-                const int64_t r = blk / sf_cols, c = blk - r * sf_cols;
+                const uint32_t blk = (uint32_t)(t >> 1);                     // host guarantees < 2^31 blocks
+                const uint32_t r = blk / (uint32_t)sf_cols, c = blk - r * (uint32_t)sf_cols;
                 if (sf_rm) sf_rm[blk] = s8;
-                if (sf_mma) sf_mma[sf_mma_offset(r, c, sf_cols)] = s8;
+                if (sf_mma) sf_mma[sf_mma_offset32(r, c, sf_col_tiles)] = s8;
             }
         }
     }
@@ -619,10 +632,13 @@ int32_t oxq_absmax(oxq_handle* h, const void* x, int dtype, int64_t n, float* ab
 
 static int32_t fp8_quant_launch(oxq_handle* h, const void* x, int dtype, int64_t n, const float* scale, float* stats, uint8_t* q, int mode) {
     const int grid = grid_for(h, n / (8 * FP8_ILP) + 1, 256, 8);
-    if (mode == OXQ_FP8_SPEC_RNE) {
-        DISPATCH_DTYPE(dtype, fp8_quant_kernel<T, OXQ_FP8_SPEC_RNE><<<grid, 256, 0, h->stream>>>((const T*)x, n, scale, stats, q));
+    if (mode == OXQ_FP8_SPEC_RNE && stats) {
+        // scale = absmax / 448 of this very tensor: quotients are bounded by 448, no overflow handling needed
+        DISPATCH_DTYPE(dtype, fp8_quant_kernel<T, OXQ_FP8_SPEC_RNE, true><<<grid, 256, 0, h->stream>>>((const T*)x, n, scale, stats, q));
+    } else if (mode == OXQ_FP8_SPEC_RNE) {
+        DISPATCH_DTYPE(dtype, fp8_quant_kernel<T, OXQ_FP8_SPEC_RNE, false><<<grid, 256, 0, h->stream>>>((const T*)x, n, scale, stats, q));
     } else if (mode == OXQ_FP8_REFCOMPAT) {
-        DISPATCH_DTYPE(dtype, fp8_quant_kernel<T, OXQ_FP8_REFCOMPAT><<<grid, 256, 0, h->stream>>>((const T*)x, n, scale, stats, q));
+        DISPATCH_DTYPE(dtype, fp8_quant_kernel<T, OXQ_FP8_REFCOMPAT, false><<<grid, 256, 0, h->stream>>>((const T*)x, n, scale, stats, q));
     } else {
         OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "fp8 mode %d", mode);
     }
@@ -713,6 +729,7 @@ int32_t oxq_mxfp8_quant(oxq_handle* h, const void* x, int dtype, int64_t rows, i
     if (rows <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "mxfp8 quantize: empty input");
     if (k % 32 != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "k %lld is not divisible by block size 32", (long long)k);
     if (!x || !codes || (!sf_rm && !sf_mma) || !aligned16(x)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (rows * (k / 32) >= ((int64_t)1 << 31)) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "more than 2^31 scale blocks");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     if (sf_mma && ((rows & 127) || ((k / 32) & 3)))          // pad bytes of partial tiles must not hold garbage
         OXQ_CUDA(h, cudaMemsetAsync(sf_mma, 0, oxq_sf_mma_bytes(rows, k / 32), h->stream));
@@ -738,6 +755,7 @@ int32_t oxq_nvfp4_quant(oxq_handle* h, const void* x, int dtype, int64_t rows, i
     if (rows <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "nvfp4 quantize: empty input");
     if (k % 16 != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "k %lld is not divisible by block size 16", (long long)k);
     if (!x || !packed || !stats || (!sf_rm && !sf_mma) || !aligned16(x)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (rows * (k / 16) >= ((int64_t)1 << 31)) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "more than 2^31 scale blocks");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     if (sf_mma && ((rows & 127) || ((k / 16) & 3)))
         OXQ_CUDA(h, cudaMemsetAsync(sf_mma, 0, oxq_sf_mma_bytes(rows, k / 16), h->stream));

@@ -234,7 +234,7 @@ def test_gemm_w4a16_errors(ops, orc):
 
 # ------------------------------------------------------------------------------------------- block scaled
 
-@pytest.mark.parametrize("mnk", [(128, 192, 128), (128, 384, 256), (256, 512, 512), (300, 1000, 1024), (64, 200, 4096)])
+@pytest.mark.parametrize("mnk", [(128, 192, 128), (128, 384, 256), (256, 512, 512), (300, 1000, 1024), (64, 200, 4096), (1024, 1544, 2048)])
 def test_gemm_mxfp8(ops, orc, mnk):
     m, n, k = mnk
     a = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 0))
@@ -249,7 +249,7 @@ def test_gemm_mxfp8(ops, orc, mnk):
     _check(_bf16_to_np(y), (da @ db.T).astype(np.float32), f"mxfp8 {mnk}")
 
 
-@pytest.mark.parametrize("mnk", [(128, 192, 256), (128, 384, 512), (256, 512, 1024), (300, 1000, 1024), (64, 200, 4096)])
+@pytest.mark.parametrize("mnk", [(128, 192, 256), (128, 384, 512), (256, 512, 1024), (300, 1000, 1024), (64, 200, 4096), (1024, 1544, 2048)])
 def test_gemm_nvfp4(ops, orc, mnk):
     m, n, k = mnk
     a = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 0))

@@ -39,6 +39,9 @@ sys.path.insert(0, ROOT)
 
 M = N = K = 8192
 FLOP = 2.0 * M * N * K
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline GEMM kernel, from the ncu capture
+# summarised in profiles/gemm_fp8_8192_ncu_full.md (246.6 MB read + 118.2 MB written; algorithmic: 268.4 MB)
+NCU_DRAM_BYTES_PER_LAUNCH = 364_810_240
 L2_BYTES = 126 * 1024 * 1024
 
 
@@ -463,7 +466,8 @@ def run_ours(args):
                        "l2": "operands + output = 256 MiB per step, larger than the 126 MB L2",
                        "multi_gpu": "independent replicas, one GEMM per rank" if world > 1 else "single GPU"},
             "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": fp8_peak, "unit": "TFLOP/s",
-                         "frac": kernel_tflops / fp8_peak, "traffic": None,
+                         "frac": kernel_tflops / fp8_peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                         "traffic_note": "DRAM bytes per launch from the ncu capture in profiles/gemm_fp8_8192_ncu_full.md; algorithmic operand + output bytes are 268435456",
                          "peak_note": f"2 x bf16_tflops_sustained ({peaks['source']}); nominal dense FP8 is 4500",
                          "frac_of_nominal": kernel_tflops / 4500.0},
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2, "d2h_bytes_per_step": M * N * 2,

@@ -14,6 +14,7 @@ struct oxq_handle {
     int sm_count;
     int cc_major, cc_minor;
     int32_t* dev_status;      // one word in device memory, written by bounded waits that expire
+    uint32_t* dev_scratch;    // 16 words after the status word: reduction cells that kernels leave zeroed (absmax)
     char last_error[256];
 };
 

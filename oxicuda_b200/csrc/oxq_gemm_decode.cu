@@ -399,7 +399,7 @@ int32_t oxq_gemm_w4a16_static(void* cuda_stream, int64_t m, int64_t n, int64_t k
     if (e != cudaSuccess) return OXQ_ERR_CUDA_BASE + (int32_t)e;
     oxq_handle tmp;
     tmp.device = dev; tmp.stream = (cudaStream_t)cuda_stream; tmp.sm_count = d.sm_count;
-    tmp.cc_major = d.cc_major; tmp.cc_minor = d.cc_minor; tmp.dev_status = nullptr; tmp.last_error[0] = 0;
+    tmp.cc_major = d.cc_major; tmp.cc_minor = d.cc_minor; tmp.dev_status = nullptr; tmp.dev_scratch = nullptr; tmp.last_error[0] = 0;
     return oxq_gemm_w4a16(&tmp, m, n, k, x, codes, scales, zeros, group, y, d.scratch, sums + counters);
 }
 

@@ -316,7 +316,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 // 128 accumulator rows in its own tensor memory and runs its own epilogue.  Full barriers live in CTA 0
 // (both CTAs' TMA loads count bytes there), empty / accumulator-full barriers are signalled in both CTAs by
 // a multicast commit, accumulator-empty arrivals go to CTA 0.
-constexpr int T2_STAGES = 6;
+constexpr int T2_STAGES = 7;
 constexpr int T2_STAGE_BYTES = 2 * BM * BKB;                      // 16 KB of X + 16 KB of W per CTA
 constexpr int T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + 2048;
 

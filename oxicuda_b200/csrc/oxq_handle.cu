@@ -47,9 +47,11 @@ int32_t oxq_handle_create(int device, void* cuda_stream, oxq_handle** out) {
     h->cc_minor = prop.minor;
     h->last_error[0] = 0;
     h->dev_status = nullptr;
-    // The only allocation the library ever makes: one status word per handle.
-    e = cudaMalloc(&h->dev_status, sizeof(int32_t));
-    if (e == cudaSuccess) e = cudaMemset(h->dev_status, 0, sizeof(int32_t));
+    // The only allocation the library ever makes: 128 bytes per handle (status word + self-cleaning reduction cells).
+    h->dev_scratch = nullptr;
+    e = cudaMalloc(&h->dev_status, 128);
+    if (e == cudaSuccess) e = cudaMemset(h->dev_status, 0, 128);
+    if (e == cudaSuccess) h->dev_scratch = reinterpret_cast<uint32_t*>(h->dev_status) + 16;
     if (e != cudaSuccess) { delete h; return OXQ_ERR_CUDA_BASE + (int32_t)e; }
     *out = h;
     return OXQ_OK;

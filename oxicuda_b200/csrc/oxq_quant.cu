@@ -154,39 +154,70 @@ __global__ void __launch_bounds__(256) int8_dequant_rows_scalar_kernel(const int
 
 // Each CTA folds a strided slice of the tensor, then one atomicMax per CTA on the bit pattern of
 // the non-negative result (ordering of non-negative floats == ordering of their bits).
+// |x| and max are taken on packed pairs for the 16-bit types (one logic and one packed-max instruction per two
+// elements), so the kernel stays limited by HBM rather than by the ALU pipe.  NaNs are skipped, as fmaxf does.
+template <typename T> struct AbsMaxAcc;
+template <> struct AbsMaxAcc<float> {
+    float m = 0.0f;
+    __device__ __forceinline__ void add(const uint4& u) {
+        m = fmaxf(m, fmaxf(fmaxf(fabsf(__uint_as_float(u.x)), fabsf(__uint_as_float(u.y))),
+                           fmaxf(fabsf(__uint_as_float(u.z)), fabsf(__uint_as_float(u.w)))));
+    }
+    __device__ __forceinline__ float result() const { return m; }
+};
+template <> struct AbsMaxAcc<__nv_bfloat16> {
+    __nv_bfloat162 m = __floats2bfloat162_rn(0.0f, 0.0f);
+    __device__ __forceinline__ void add1(uint32_t w) {
+        const uint32_t a = w & 0x7FFF7FFFu;
+        m = __hmax2(m, *reinterpret_cast<const __nv_bfloat162*>(&a));
+    }
+    __device__ __forceinline__ void add(const uint4& u) { add1(u.x); add1(u.y); add1(u.z); add1(u.w); }
+    __device__ __forceinline__ float result() const { return fmaxf(__low2float(m), __high2float(m)); }
+};
+template <> struct AbsMaxAcc<__half> {
+    __half2 m = __floats2half2_rn(0.0f, 0.0f);
+    __device__ __forceinline__ void add1(uint32_t w) {
+        const uint32_t a = w & 0x7FFF7FFFu;
+        m = __hmax2(m, *reinterpret_cast<const __half2*>(&a));
+    }
+    __device__ __forceinline__ void add(const uint4& u) { add1(u.x); add1(u.y); add1(u.z); add1(u.w); }
+    __device__ __forceinline__ float result() const { return fmaxf(__low2float(m), __high2float(m)); }
+};
+
+// cells[0] accumulates the maximum, cells[1] counts finished CTAs; the last CTA publishes the result and puts
+// both cells back to zero, so no memset is needed between calls.
 template <typename T>
-__global__ void __launch_bounds__(256) absmax_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ out) {
+__global__ void __launch_bounds__(256) absmax_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ out, unsigned int* __restrict__ cells) {
     constexpr int V = Vec16<T>::N;
     __shared__ float s_red[8];
     const int64_t nvec = n / V;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+    const uint4* xv = reinterpret_cast<const uint4*>(x);
+    AbsMaxAcc<T> a0, a1, a2, a3;
     int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-    for (; i + 3 * stride < nvec; i += 4 * stride) {
-        Vec16<T> a = ld16(x + i * V), b = ld16(x + (i + stride) * V), c = ld16(x + (i + 2 * stride) * V),
-                 d = ld16(x + (i + 3 * stride) * V);
-#pragma unroll
-        for (int j = 0; j < V; j++) {
-            m0 = fmaxf(m0, fabsf(Elem<T>::to_f32(a.v[j])));
-            m1 = fmaxf(m1, fabsf(Elem<T>::to_f32(b.v[j])));
-            m2 = fmaxf(m2, fabsf(Elem<T>::to_f32(c.v[j])));
-            m3 = fmaxf(m3, fabsf(Elem<T>::to_f32(d.v[j])));
-        }
+    for (; i + 7 * stride < nvec; i += 8 * stride) {
+        const uint4 u0 = __ldg(xv + i), u1 = __ldg(xv + i + stride), u2 = __ldg(xv + i + 2 * stride), u3 = __ldg(xv + i + 3 * stride);
+        const uint4 u4 = __ldg(xv + i + 4 * stride), u5 = __ldg(xv + i + 5 * stride), u6 = __ldg(xv + i + 6 * stride), u7 = __ldg(xv + i + 7 * stride);
+        a0.add(u0); a1.add(u1); a2.add(u2); a3.add(u3);
+        a0.add(u4); a1.add(u5); a2.add(u6); a3.add(u7);
     }
-    for (; i < nvec; i += stride) {
-        Vec16<T> a = ld16(x + i * V);
-#pragma unroll
-        for (int j = 0; j < V; j++) m0 = fmaxf(m0, fabsf(Elem<T>::to_f32(a.v[j])));
-    }
+    for (; i < nvec; i += stride) a0.add(__ldg(xv + i));
+    float m = fmaxf(fmaxf(a0.result(), a1.result()), fmaxf(a2.result(), a3.result()));
     if (blockIdx.x == 0) {
-        for (int64_t t = nvec * V + threadIdx.x; t < n; t += blockDim.x) m1 = fmaxf(m1, fabsf(Elem<T>::to_f32(x[t])));
+        for (int64_t t = nvec * V + threadIdx.x; t < n; t += blockDim.x) m = fmaxf(m, fabsf(Elem<T>::to_f32(x[t])));
     }
-    float m = warp_max(fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
+    m = warp_max(m);
     if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = m;
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int w = 1; w < 8; w++) m = fmaxf(m, s_red[w]);
-        atomicMax(reinterpret_cast<unsigned int*>(out), __float_as_uint(m));
+        atomicMax(cells, __float_as_uint(m));
+        __threadfence();
+        if (atomicAdd(cells + 1, 1u) == gridDim.x - 1) {
+            __threadfence();
+            out[0] = __uint_as_float(atomicExch(cells, 0u));
+            cells[1] = 0u;
+        }
     }
 }
 
@@ -376,6 +407,92 @@ __global__ void __launch_bounds__(256) int4g_quant_kernel(const T* __restrict__ 
                 }
             }
         }
+        if (lane == 0) zeros[g0 >> 3] = zword;
+    }
+}
+
+// Group 128, the shape the GEMMs use: 8 lanes share a group (16 elements each, as two runs of 8 consecutive
+// elements = two whole code words, so no nibble exchange), a warp works on 4 groups at once and on 8 groups per
+// pass, so it owns one packed zero-point word.  min / max need 3 + 3 shuffles per 16 elements.  Rounding runs in
+// the FMA pipe: after the clamp to [0, 15] (which also maps NaN to 0), adding 1.5 * 2^23 leaves
+// round-to-nearest-even in the low mantissa bits; half-away differs only at exact ties rounded down.
+__device__ __forceinline__ uint32_t quant_u4(float x, const InvDiv& sd, float zf, int rounding) {
+    const float t = fminf(fmaxf(div_exact_bounded(x, sd) + zf, 0.0f), 15.0f);
+    const float m = t + 12582912.0f;
+    uint32_t code = __float_as_uint(m);
+    if (rounding == OXQ_ROUND_HALF_AWAY && t - (m - 12582912.0f) == 0.5f) code += 1u;
+    return code & 0xFu;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) int4g128_quant_kernel(const T* __restrict__ x, int64_t ngroups, int rounding,
+                                                             uint32_t* __restrict__ codes, uint16_t* __restrict__ scales,
+                                                             uint32_t* __restrict__ zeros) {
+    const int lane = threadIdx.x & 31, sub = lane >> 3, sl = lane & 7;
+    const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t g0 = warp * 8; g0 < ngroups; g0 += nwarps * 8) {
+        float v[2][2][8];                                   // [pass][run][element]
+#pragma unroll
+        for (int ps = 0; ps < 2; ps++) {
+            const int64_t g = g0 + ps * 4 + sub;
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int64_t e = g * 128 + j * 64 + sl * 8;
+                if (g < ngroups) {
+                    if (sizeof(T) == 4) {
+                        const float4 a = __ldg(reinterpret_cast<const float4*>(x + e)), b = __ldg(reinterpret_cast<const float4*>(x + e) + 1);
+                        v[ps][j][0] = a.x; v[ps][j][1] = a.y; v[ps][j][2] = a.z; v[ps][j][3] = a.w;
+                        v[ps][j][4] = b.x; v[ps][j][5] = b.y; v[ps][j][6] = b.z; v[ps][j][7] = b.w;
+                    } else {
+                        const uint4 u = __ldcs(reinterpret_cast<const uint4*>(x + e));
+                        const T* hh = reinterpret_cast<const T*>(&u);
+#pragma unroll
+                        for (int q = 0; q < 8; q++) v[ps][j][q] = Elem<T>::to_f32(hh[q]);
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 8; q++) v[ps][j][q] = 0.0f;
+                }
+            }
+        }
+        uint32_t zcontrib = 0;
+#pragma unroll
+        for (int ps = 0; ps < 2; ps++) {
+            const int64_t g = g0 + ps * 4 + sub;
+            float mn = INFINITY, mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int q = 0; q < 8; q++) { mn = fminf(mn, v[ps][j][q]); mx = fmaxf(mx, v[ps][j][q]); }   // NaNs skipped like `if v < fmin`
+#pragma unroll
+            for (int o = 4; o > 0; o >>= 1) {
+                mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            }
+            const float s32 = __fdiv_rn(fmaxf(mx - mn, 1e-8f), 15.0f);
+            __half sh = __float2half_rn(s32);
+            if ((__half_as_ushort(sh) & 0x7FFFu) == 0) sh = __ushort_as_half(1);
+            const float sc = __half2float(sh);
+            InvDiv sd = make_invdiv(sc);
+            sd.fast = sd.fast && fmaxf(fabsf(mn), fabsf(mx)) < 0x1p100f;      // quotients of this group cannot overflow
+            float zf = roundf(div_exact(-mn, sd));
+            zf = zf != zf ? 0.0f : fminf(fmaxf(zf, 0.0f), 15.0f);
+            if (g < ngroups) {
+                if (sl == 0) {
+                    scales[g] = __half_as_ushort(sh);
+                    zcontrib |= ((uint32_t)zf) << (4 * (ps * 4 + sub));
+                }
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    uint32_t w = 0;
+#pragma unroll
+                    for (int q = 0; q < 8; q++) w |= quant_u4(v[ps][j][q], sd, zf, rounding) << (4 * q);
+                    __stcs(codes + ((g * 128 + j * 64 + sl * 8) >> 3), w);
+                }
+            }
+        }
+        const uint32_t zword = __reduce_or_sync(0xffffffffu, zcontrib);
         if (lane == 0) zeros[g0 >> 3] = zword;
     }
 }
@@ -624,8 +741,8 @@ int32_t oxq_absmax(oxq_handle* h, const void* x, int dtype, int64_t n, float* ab
     if (n <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "absmax: empty input");
     if (!x || !absmax_dev || !aligned16(x)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
-    OXQ_CUDA(h, cudaMemsetAsync(absmax_dev, 0, sizeof(float), h->stream));
-    DISPATCH_DTYPE(dtype, absmax_kernel<T><<<grid_for(h, n / Vec16<T>::N / 4 + 1, 256, 8), 256, 0, h->stream>>>((const T*)x, n, absmax_dev));
+    if (!h->dev_scratch) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "handle has no reduction cells");
+    DISPATCH_DTYPE(dtype, absmax_kernel<T><<<grid_for(h, n / Vec16<T>::N / 8 + 1, 256, 8), 256, 0, h->stream>>>((const T*)x, n, absmax_dev, h->dev_scratch));
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -689,7 +806,9 @@ int32_t oxq_int4g_quant_pack(oxq_handle* h, const void* x, int dtype, int64_t ro
     const int64_t ngroups = rows * (k / group);
     const int grid = grid_for(h, (ngroups + 7) / 8 * 32, 256, 8);
 #define LAUNCH_G(G) int4g_quant_kernel<T, G><<<grid, 256, 0, h->stream>>>((const T*)x, ngroups, rounding, codes, scales, zeros)
-    DISPATCH_DTYPE(dtype, if (group == 32) LAUNCH_G(32); else if (group == 64) LAUNCH_G(64); else if (group == 128) LAUNCH_G(128); else LAUNCH_G(256));
+    DISPATCH_DTYPE(dtype, if (group == 32) LAUNCH_G(32); else if (group == 64) LAUNCH_G(64);
+                   else if (group == 128) int4g128_quant_kernel<T><<<grid, 256, 0, h->stream>>>((const T*)x, ngroups, rounding, codes, scales, zeros);
+                   else LAUNCH_G(256));
 #undef LAUNCH_G
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;

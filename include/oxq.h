@@ -168,10 +168,16 @@ OXQ_API int32_t oxq_gemm_w8a8(oxq_handle* h, int64_t m, int64_t n, int64_t k, co
 OXQ_API int32_t oxq_gemm_w8a32(oxq_handle* h, int64_t m, int64_t n, int64_t k, const float* x_dev,
                        const int8_t* w_dev, const float* sw_rows_dev, float* y_dev);
 /* W4A16 weight-only (Int4GemmConfig, int_ops.rs:215-355; quantized operand is the weight):
- * Y = bf16(X_bf16 . dequant(W)^T).  m <= 32 runs the HBM-bound decode kernel (split-K partial sums in the
- * workspace, which must be zero-filled before its first use and is left zero-filled by every call); m > 32
- * dequantises the weight to bf16 in the workspace and runs the tensor-core GEMM (n % 8 == 0).
- * Workspace size: oxq_gemm_w4a16_workspace_bytes(m, n, k). */
+ * Y = bf16(X_bf16 . dequant(W)^T).  Three regimes, all reading the packed weight once per 32 batch rows or less:
+ *   m <= 8           HBM-bound mma.sync decode kernel, split-K partial sums in the workspace;
+ *   9 <= m <= 128    (group 128, k % 1024 == 0) tensor-core kernel with the dequantisation fused in: codes are
+ *                    unpacked straight into tensor memory as the row operand of tcgen05.mma, per-group scales are
+ *                    applied to the group's accumulator, partial K ranges are combined in the workspace;
+ *                    other shapes with m <= 32 use the first kernel;
+ *   otherwise        the weight is dequantised to bf16 in the workspace and the bf16 tensor-core GEMM runs
+ *                    (n % 8 == 0).
+ * For m <= 32 the workspace must be zero-filled before its first use and is left zero-filled by every call; above
+ * that its previous contents do not matter.  Workspace size: oxq_gemm_w4a16_workspace_bytes(m, n, k). */
 OXQ_API size_t oxq_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k);
 OXQ_API int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x_bf16_dev,
                        const uint32_t* codes_dev, const uint16_t* scales_f16_dev, const uint32_t* zeros_packed_dev,

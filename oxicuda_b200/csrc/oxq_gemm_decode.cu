@@ -8,6 +8,7 @@
 //          caller-provided workspace that the last CTA of each row block drains.
 //   W8A32: int8 codes -> f32, plain FMAs (the benchmark's CPU-runnable configuration).
 #include "oxq_common.cuh"
+#include <stdlib.h>
 
 namespace oxq {
 namespace decode {
@@ -286,18 +287,49 @@ __global__ void __launch_bounds__(256) w8a32_decode_kernel(const float* __restri
 
 using namespace oxq::decode;
 
+// f32 partial sums of the split-K kernels: [m x n], rounded up to 256 bytes
+static size_t split_sums_bytes(int64_t m, int64_t n) { return ((size_t)m * (size_t)n * sizeof(float) + 255) & ~(size_t)255; }
+// workspace of the mma.sync kernel: the sums, then one counter per W4_ROWS_PER_CTA weight rows
+static size_t mma_sync_ws_bytes(int64_t m, int64_t n) {
+    return split_sums_bytes(m, n) + ((((size_t)(n + oxq::decode::W4_ROWS_PER_CTA - 1) / oxq::decode::W4_ROWS_PER_CTA) * sizeof(int) + 255) & ~(size_t)255);
+}
+
+// workspace of the tensor-core kernel: 32 f32 per weight row and pass of 32 batch rows, then one counter per 32 weight rows
+static size_t w4tc_sums_bytes(int64_t m, int64_t n) { return (size_t)((m + 31) / 32) * (size_t)n * 32 * sizeof(float); }
+static size_t w4tc_ws_bytes(int64_t m, int64_t n) {
+    return w4tc_sums_bytes(m, n) + ((((size_t)(n + 31) / 32) * sizeof(int) + 255) & ~(size_t)255);
+}
+
+// defined in oxq_gemm_w4tc.cu
+bool oxq_w4tc_supports(int64_t m, int64_t n, int64_t k, int group);
+int32_t oxq_w4tc_launch(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, const uint32_t* codes, const uint16_t* scales,
+                        const uint32_t* zeros, void* y, float* ws_sums, int* ws_counters);
+
+static int32_t w4a16_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, const uint32_t* codes, const uint16_t* scales,
+                          const uint32_t* zeros, int group, void* y, void* ws, size_t ws_bytes, bool allow_tc);
+
 extern "C" {
 
 size_t oxq_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     if (m <= 0 || n <= 0) return 0;
     if (m > 32) return (((size_t)n * (size_t)k * 2) + 255) & ~(size_t)255;      // bf16 copy of the dequantised weight
-    size_t f = (size_t)m * (size_t)n * sizeof(float);
-    f = (f + 255) & ~(size_t)255;
-    return f + (((size_t)(n + W4_ROWS_PER_CTA - 1) / W4_ROWS_PER_CTA) * sizeof(int) + 255 & ~(size_t)255);
+    return w4tc_ws_bytes(m, n);                                                  // covers the mma.sync kernel's needs as well
 }
 
 int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, const uint32_t* codes, const uint16_t* scales,
                        const uint32_t* zeros, int group, void* y, void* ws, size_t ws_bytes) {
+    // Measured on B200 (14336 x 4096): the mma.sync kernel wins up to 8 batch rows (16-20 us against 21), the
+    // tensor-core kernel from there on (22-23 us for 9..32 rows against 30-61).  OXQ_W4A16_TC=0 never uses the
+    // tensor-core kernel, 2 uses it for every batch it supports (for A/B runs).
+    static int tc = -1;
+    if (tc < 0) { const char* e = getenv("OXQ_W4A16_TC"); tc = e ? atoi(e) : 1; }
+    return w4a16_impl(h, m, n, k, x, codes, scales, zeros, group, y, ws, ws_bytes, tc >= 2 || (tc == 1 && m > 8));
+}
+
+}  // extern "C"
+
+static int32_t w4a16_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, const uint32_t* codes, const uint16_t* scales,
+                          const uint32_t* zeros, int group, void* y, void* ws, size_t ws_bytes, bool allow_tc) {
     OXQ_CHECK_HANDLE(h);
     if (m <= 0 || n <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "GEMM dimensions must be non-zero");
     if (!x || !codes || !scales || !zeros || !y) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
@@ -305,10 +337,22 @@ int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const voi
     if (k % 8 != 0) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "K must be a multiple of 8 for INT4 packing, got %lld", (long long)k);
     if (!(group == 32 || group == 64 || group == 128 || group == 256)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "group size %d not in {32,64,128,256}", group);
     if (k % group != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "k %lld is not divisible by group size %d", (long long)k, group);
+    if (allow_tc && oxq_w4tc_supports(m, n, k, group)) {
+        // Tensor-core kernel with the dequantisation fused in: one pass over the weights per 32 batch rows.
+        if (((uintptr_t)x & 15u) || ((uintptr_t)codes & 15u) || ((uintptr_t)scales & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "x, codes and scales must be 16-byte aligned");
+        if (int32_t rc = oxq_require_sm100(h)) return rc;
+        const size_t sums = w4tc_sums_bytes(m, n);
+        const size_t need = w4tc_ws_bytes(m, n);
+        if (!ws || ws_bytes < need || ((uintptr_t)ws & 255u))
+            OXQ_FAIL(h, OXQ_ERR_BUFFER_TOO_SMALL, "workspace: expected at least %zu bytes (256-byte aligned), got %zu", need, ws_bytes);
+        // up to 32 rows the workspace is zero on entry by contract; above, it may hold a dequantised weight from a prefill call
+        if (m > 32) OXQ_CUDA(h, cudaMemsetAsync(ws, 0, need, h->stream));
+        return oxq_w4tc_launch(h, m, n, k, x, codes, scales, zeros, y, (float*)ws, (int*)((char*)ws + sums));
+    }
     if (m > 32) {
         // Prefill shapes are tensor-bound: dequantise the weight once to bf16 in the workspace (which needs
         // no zero fill on this path), then run the bf16 tensor-core GEMM.
-        const size_t need = oxq_gemm_w4a16_workspace_bytes(m, n, k);
+        const size_t need = (((size_t)n * (size_t)k * 2) + 255) & ~(size_t)255;
         if (!ws || ws_bytes < need || ((uintptr_t)ws & 15u))
             OXQ_FAIL(h, OXQ_ERR_BUFFER_TOO_SMALL, "workspace: expected at least %zu bytes, got %zu", need, ws_bytes);
         if (int32_t rc = oxq_int4g_dequant(h, codes, scales, zeros, n, k, group, ws, OXQ_BF16)) return rc;
@@ -327,12 +371,11 @@ int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const voi
     float* ws_sums = nullptr;
     int* ws_counters = nullptr;
     if (splits > 1) {
-        const size_t need = oxq_gemm_w4a16_workspace_bytes(m, n, k);
+        const size_t need = mma_sync_ws_bytes(m, n);
         if (!ws || ws_bytes < need || ((uintptr_t)ws & 255u))
             OXQ_FAIL(h, OXQ_ERR_BUFFER_TOO_SMALL, "workspace: expected at least %zu bytes (256-byte aligned), got %zu", need, ws_bytes);
-        size_t f = ((size_t)m * (size_t)n * sizeof(float) + 255) & ~(size_t)255;
         ws_sums = (float*)ws;
-        ws_counters = (int*)((char*)ws + f);
+        ws_counters = (int*)((char*)ws + split_sums_bytes(m, n));
     }
     dim3 grid(row_blocks, splits);
     // Batches above 16 rows run as passes of 16: the legacy MMA path is the limit there, and the second pass
@@ -350,6 +393,8 @@ int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const voi
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
+
+extern "C" {
 
 // ---- W4A16 without any allocation ---------------------------------------------------------------
 // Scratch for oxq_gemm_w4a16_static: lives in the library image, so every GPU that loads the library
@@ -400,7 +445,7 @@ int32_t oxq_gemm_w4a16_static(void* cuda_stream, int64_t m, int64_t n, int64_t k
     oxq_handle tmp;
     tmp.device = dev; tmp.stream = (cudaStream_t)cuda_stream; tmp.sm_count = d.sm_count;
     tmp.cc_major = d.cc_major; tmp.cc_minor = d.cc_minor; tmp.dev_status = nullptr; tmp.dev_scratch = nullptr; tmp.last_error[0] = 0;
-    return oxq_gemm_w4a16(&tmp, m, n, k, x, codes, scales, zeros, group, y, d.scratch, sums + counters);
+    return w4a16_impl(&tmp, m, n, k, x, codes, scales, zeros, group, y, d.scratch, sums + counters, false);
 }
 
 int32_t oxq_gemm_w8a32(oxq_handle* h, int64_t m, int64_t n, int64_t k, const float* x, const int8_t* w, const float* sw, float* y) {

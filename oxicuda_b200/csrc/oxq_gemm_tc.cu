@@ -714,6 +714,24 @@ static bool make_tmap_bytes(CUtensorMap* tm, const void* ptr, int64_t rows, int6
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+}  // namespace tc
+}  // namespace oxq
+
+bool oxq_make_tmap_2d(CUtensorMap* tm, CUtensorMapDataType dtype, const void* ptr, uint64_t inner_elems, uint64_t rows,
+                      uint64_t ld_bytes, uint32_t box_inner, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+    oxq::tc::EncodeTiledFn fn = oxq::tc::get_encode_fn();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)inner_elems, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(tm, dtype, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+namespace oxq {
+namespace tc {
+
 // M-tiles per rasterisation group; OXQ_GEMM_GROUP_M overrides the default for tuning runs.
 static int group_m_setting() {
     static int v = 0;

@@ -139,7 +139,7 @@ def test_gemm_w8a32_config1(ops, orc, mnk):
 
 # ------------------------------------------------------------------------------------------- W4A16
 
-@pytest.mark.parametrize("m", [1, 8, 32, 5, 17])
+@pytest.mark.parametrize("m", [1, 8, 32, 5, 17, 9, 16])
 @pytest.mark.parametrize("nk", [(256, 512), (4096, 4096), (200, 1024), (6144, 4096), (384, 14336)])
 def test_gemm_w4a16_decode(ops, orc, m, nk):
     n, k = nk
@@ -155,6 +155,26 @@ def test_gemm_w4a16_decode(ops, orc, m, nk):
     assert int(ws.view(torch.int32).abs().max()) == 0               # workspace left zeroed
     y2 = ops.gemm_w4a16(bf16_dev(xb), c, s, z, 128, workspace=ws)   # and therefore reusable
     _check(_bf16_to_np(y2), ref, "w4a16 second call")
+    _status_clean(ops)
+
+
+@pytest.mark.parametrize("m", [33, 64, 100, 128])
+@pytest.mark.parametrize("nk", [(4096, 4096), (200, 1024)])
+def test_gemm_w4a16_mid_batch(ops, orc, m, nk):
+    """Batches of 33..128 rows run as passes of 32 over the fused tensor-core kernel; a workspace that held
+    something else before (here: ones) must not leak into the result."""
+    n, k = nk
+    w = orc.gaussian((n, k), 0.02, 0)
+    xb = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 1))
+    c, s, z = ops.int4g_quant_pack(to_dev(w), 128)
+    ws = ops.gemm_w4a16_workspace(m, n, k, "cuda")
+    ws.fill_(1)
+    y = ops.gemm_w4a16(bf16_dev(xb), c, s, z, 128, workspace=ws)
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    deq = orc.spec_int4g_dequant(u32(c), u16(s), u32(z), n, k, 128)
+    ref = (orc.bf16_bits_to_f32(xb).astype(np.float64) @ deq.astype(np.float64).T).astype(np.float32)
+    _check(_bf16_to_np(y), ref, f"w4a16 m={m} {nk}")
 
 
 @pytest.mark.parametrize("mnk", [(64, 256, 512), (200, 1000, 1024), (2048, 1024, 4096)])

@@ -221,6 +221,8 @@ def extras(torch, ops, peaks):
     one = torch.ones(1, device="cuda")
     rec("fp8_quant_bf16_8192x8192", 201326592, ring_time(torch, lambda r: ops.fp8_quant(r, one, out=outq), ring))
     rec("fp8_quant_dynamic_bf16_8192x8192", 335544320, ring_time(torch, lambda r: ops.fp8_quant_dynamic(r, out=outq, stats=stats), ring), 2)
+    outi = outq.view(torch.int8)
+    rec("int8_quant_tensor_bf16_8192x8192(absmax+encode)", 335544320, ring_time(torch, lambda r: ops.quantize_to_int8(r, out=outi, scale=am), ring), 2)
     # config 4 quantizers on the 4096x4096 activation shape (ring of 8 -> 256 MiB)
     ring4 = [r[:4096, :4096].contiguous() for r in ring] + [r[4096:, 4096:].contiguous() for r in ring] + [ring[0][:4096, 4096:].contiguous(), ring[1][4096:, :4096].contiguous()]
     rec("mxfp8_quant_bf16_4096x4096", 33554432 + 16777216 + 2 * 524288, ring_time(torch, lambda r: ops.mxfp8_quant(r), ring4))
@@ -240,7 +242,7 @@ def extras(torch, ops, peaks):
         c, s, z = ops.int4g_quant_pack(w, 128)
         ring = [(c.clone(), s.clone(), z.clone()) for _ in range(copies)]
         del w
-        for m in (1, 8, 32):
+        for m in (1, 8, 16, 32):
             x = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
             ws = ops.gemm_w4a16_workspace(m, n, k, "cuda")
             y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
@@ -251,6 +253,8 @@ def extras(torch, ops, peaks):
     ringw = [torch.randn((14336, 4096), generator=g, device="cuda") * 0.02 for _ in range(3)]
     rec("int4g_quant_pack_f32_14336x4096", 14336 * 4096 * 4 + 14336 * 4096 // 2 + 458752 * 2 + 458752 // 2,
         ring_time(torch, lambda r: ops.int4g_quant_pack(r, 128), ringw))
+    rec("nf4_quant_f32_14336x4096_b64", 14336 * 4096 * 4 + 14336 * 4096 // 2 + 14336 * 4096 // 64 * 4,
+        ring_time(torch, lambda r: ops.nf4_quant(r, 64), ringw))
     return out
 
 

@@ -196,6 +196,24 @@ OXQ_API int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, c
 OXQ_API int32_t oxq_gemm_w4a16_static(void* cuda_stream, int64_t m, int64_t n, int64_t k, const void* x_bf16_dev,
                               const uint32_t* codes_dev, const uint16_t* scales_f16_dev, const uint32_t* zeros_packed_dev,
                               int group, void* y_bf16_dev);
+/* ---- quantizers next to the hot path --------------------------------------------------------------------
+ * Per-tensor INT8 with the arithmetic of oxicuda-dnn's quantize_to_int8 / dequantize_from_int8
+ * (crates/oxicuda-dnn/src/quantize/int8_quantize.rs:33-92, :101-157): scale_dev[0] = max(absmax / 127, 1e-12),
+ * q = rint(clamp(x / scale, -127, 127)) (half to even); y = (float)q * scale_dev[0].  n == 0 returns OXQ_OK. */
+OXQ_API int32_t oxq_int8_quant_tensor(oxq_handle* h, const void* x_dev, int dtype, int64_t n, int8_t* q_dev, float* scale_dev);
+OXQ_API int32_t oxq_int8_dequant_tensor(oxq_handle* h, const int8_t* q_dev, const float* scale_dev, int64_t n, void* y_dev, int y_dtype);
+/* BlockQuantizedInt8::quantize / dequantize (int8_quantize.rs:404-451) on device buffers: one scale per `block`
+ * contiguous elements (the last block may be short), scale = max|x| / 127 or 1 for an all-zero block,
+ * q = clamp(round_half_away(x / scale), -128, 127).  scales_dev holds ceil(n / block) floats. */
+OXQ_API int32_t oxq_int8_block_quant(oxq_handle* h, const float* x_dev, int64_t n, int64_t block, int8_t* q_dev, float* scales_dev);
+OXQ_API int32_t oxq_int8_block_dequant(oxq_handle* h, const int8_t* q_dev, const float* scales_dev, int64_t n, int64_t block, float* y_dev);
+/* Nf4Quantizer::encode / decode (crates/oxicuda-quant/src/scheme/nf4.rs:93-155): per block absmax (floored at
+ * 1e-8), x / absmax clamped to [-1, 1], nearest of the 16 NormalFloat4 levels (the lower index on a tie), two
+ * codes per byte with the even element in the low nibble.  packed_dev holds n / 2 bytes, absmax_dev n / block
+ * floats.  Errors as the reference: EmptyInput, GroupSizeMismatch (encode), DimensionMismatch (decode). */
+OXQ_API int32_t oxq_nf4_quant(oxq_handle* h, const float* x_dev, int64_t n, int64_t block, uint8_t* packed_dev, float* absmax_dev);
+OXQ_API int32_t oxq_nf4_dequant(oxq_handle* h, const uint8_t* packed_dev, const float* absmax_dev, int64_t n, int64_t block,
+                                void* y_dev, int y_dtype);
 /* Block-scaled GEMMs (Fp4GemmConfig, fp4_fp6_ops.rs:337-395).  Scale factors in the tiled order. */
 OXQ_API int32_t oxq_gemm_mxfp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x_dev, const uint8_t* sfx_mma_dev,
                        const uint8_t* w_dev, const uint8_t* sfw_mma_dev, void* y_bf16_dev, int64_t ldy);

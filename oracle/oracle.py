@@ -67,6 +67,9 @@ def lib():
         _lib.orc_ref_e2m1_quantize_one.argtypes = [C.c_float]
         _lib.orc_f32_to_f16.argtypes = [C.c_float]
         _lib.orc_f32_to_bf16.argtypes = [C.c_float]
+        _lib.orc_nf4_level.restype = C.c_float
+        _lib.orc_ref_nearest_nf4.argtypes = [C.c_float]
+        _lib.orc_ref_dnn_int8_dequant.argtypes = [C.c_void_p, C.c_size_t, C.c_float, C.c_void_p]
     return _lib
 
 
@@ -242,6 +245,72 @@ def ref_microscale_fp4_dequant(packed, scales, n, block=32):
     out = np.zeros(n, np.float32)
     lib().orc_ref_microscale_fp4_dequant(_p(_c(packed, np.uint8)), _p(_c(scales, np.float32)), _sz(n), _sz(block),
                                          _p(out))
+    return out
+
+
+# --------------------------------------------------------------------------- rows after the hot path
+
+def nf4_levels() -> np.ndarray:
+    return np.array([lib().orc_nf4_level(i) for i in range(16)], np.float32)
+
+
+def ref_nearest_nf4(v: float) -> int:
+    return int(lib().orc_ref_nearest_nf4(C.c_float(v)))
+
+
+def ref_nf4_encode(x, block=64):
+    """Nf4Quantizer::encode: (packed bytes, per-block absmax)."""
+    x = _c(x, np.float32).ravel()
+    packed = np.zeros(max(x.size // 2, 1), np.uint8)
+    am = np.zeros(max(x.size // max(block, 1), 1), np.float32)
+    rc = lib().orc_ref_nf4_encode(_p(x), _sz(x.size), _sz(block), _p(packed), _p(am))
+    if rc == -1:
+        raise OracleError(1)
+    if rc == -2:
+        raise OracleError(2)
+    return packed[: x.size // 2], am[: x.size // block]
+
+
+def ref_nf4_decode(packed, absmaxs, block=64):
+    packed = _c(packed, np.uint8)
+    n = packed.size * 2
+    absmaxs = _c(absmaxs, np.float32)
+    if absmaxs.size != n // block:
+        raise OracleError(4)
+    out = np.zeros(n, np.float32)
+    lib().orc_ref_nf4_decode(_p(packed), _p(absmaxs), _sz(n), _sz(block), _p(out))
+    return out
+
+
+def ref_block_int8_quant(x, block):
+    """BlockQuantizedInt8::quantize: (codes, per-block scales); the last block may be short."""
+    x = _c(x, np.float32).ravel()
+    q = np.zeros(x.size, np.int8)
+    s = np.zeros((x.size + block - 1) // block, np.float32)
+    lib().orc_ref_block_int8_quant(_p(x), _sz(x.size), _sz(block), _p(q), _p(s))
+    return q, s
+
+
+def ref_block_int8_dequant(q, scales, block):
+    q = _c(q, np.int8).ravel()
+    out = np.zeros(q.size, np.float32)
+    lib().orc_ref_block_int8_dequant(_p(q), _p(_c(scales, np.float32)), _sz(q.size), _sz(block), _p(out))
+    return out
+
+
+def ref_dnn_int8_quant(x):
+    """quantize_to_int8 of the DNN crate: (codes, scale) with one scale for the whole tensor."""
+    x = _c(x, np.float32).ravel()
+    q = np.zeros(x.size, np.int8)
+    s = np.zeros(1, np.float32)
+    lib().orc_ref_dnn_int8_quant(_p(x), _sz(x.size), _p(q), _p(s))
+    return q, s
+
+
+def ref_dnn_int8_dequant(q, scale):
+    q = _c(q, np.int8).ravel()
+    out = np.zeros(q.size, np.float32)
+    lib().orc_ref_dnn_int8_dequant(_p(q), _sz(q.size), C.c_float(float(scale)), _p(out))
     return out
 
 

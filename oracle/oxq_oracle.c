@@ -588,6 +588,97 @@ void orc_spec_nvfp4_dequant(const uint8_t* packed, const uint8_t* sf, float g, s
 /* ------------------------------------------------------------------------- */
 /* A.5  f32 GEMM / SwiGLU / tensor-parallel helpers                            */
 /* ------------------------------------------------------------------------- */
+/* Rows that follow the hot path: NF4, per-block INT8, per-tensor INT8.          */
+/* ------------------------------------------------------------------------- */
+
+/* The 16 NormalFloat4 levels (crates/oxicuda-quant/src/scheme/nf4.rs:33-50). */
+static const float NF4_LEVELS[16] = {
+    -1.0f, -0.69619286f, -0.52507305f, -0.3949175f, -0.28444138f, -0.18477343f, -0.09105003f, 0.0f,
+    0.0795803f, 0.1609302f, 0.2461123f, 0.33791524f, 0.44070983f, 0.562617f, 0.72295684f, 1.0f};
+
+float orc_nf4_level(int i) { return NF4_LEVELS[i & 15]; }
+
+/* nearest_nf4 (nf4.rs:186-205): first index whose level is >= v, then the closer neighbour, the lower
+ * index on a tie. */
+int orc_ref_nearest_nf4(float v) {
+    int lo = 0, hi = 16;
+    while (lo < hi) {
+        int mid = lo + (hi - lo) / 2;
+        if (NF4_LEVELS[mid] < v) lo = mid + 1; else hi = mid;
+    }
+    if (lo == 0) return 0;
+    if (lo == 16) return 15;
+    float d_lo = fabsf(v - NF4_LEVELS[lo - 1]);
+    float d_hi = fabsf(NF4_LEVELS[lo] - v);
+    return d_lo <= d_hi ? lo - 1 : lo;
+}
+
+/* Nf4Quantizer::encode (nf4.rs:93-130): per block absmax (floored at 1e-8), v / absmax clamped to [-1, 1],
+ * nearest level, even element in the low nibble.  Returns 0, or -1 empty input, -2 length not a multiple of block. */
+int orc_ref_nf4_encode(const float* x, size_t n, size_t block, uint8_t* packed, float* absmaxs) {
+    if (n == 0) return -1;
+    if (block == 0 || n % block != 0) return -2;
+    memset(packed, 0, n / 2);
+    for (size_t b = 0; b < n / block; b++) {
+        const float* blk = x + b * block;
+        float am = 0.0f;
+        for (size_t i = 0; i < block; i++) am = fmaxf(am, fabsf(blk[i]));
+        if (am < 1e-8f) am = 1e-8f;
+        absmaxs[b] = am;
+        size_t base = b * block / 2;
+        for (size_t i = 0; i < block; i++) {
+            float normed = clampf(blk[i] / am, -1.0f, 1.0f);
+            uint8_t code = (uint8_t)orc_ref_nearest_nf4(normed);
+            if (i % 2 == 0) packed[base + i / 2] = code; else packed[base + i / 2] |= (uint8_t)(code << 4);
+        }
+    }
+    return 0;
+}
+
+/* Nf4Quantizer::decode (nf4.rs:137-155). */
+void orc_ref_nf4_decode(const uint8_t* packed, const float* absmaxs, size_t n, size_t block, float* out) {
+    for (size_t i = 0; i < n; i++) {
+        uint8_t byte = packed[i / 2];
+        int code = (i & 1) ? (byte >> 4) : (byte & 0x0F);
+        out[i] = NF4_LEVELS[code] * absmaxs[i / block];
+    }
+}
+
+/* BlockQuantizedInt8::quantize (crates/oxicuda-dnn/src/quantize/int8_quantize.rs:404-432): per block of
+ * `block` contiguous elements (the last one may be short) scale = max|x| / 127, or 1 for an all-zero block;
+ * q = clamp(round_half_away(x / scale), -128, 127). */
+void orc_ref_block_int8_quant(const float* x, size_t n, size_t block, int8_t* q, float* scales) {
+    for (size_t b0 = 0, bi = 0; b0 < n; b0 += block, bi++) {
+        size_t len = n - b0 < block ? n - b0 : block;
+        float am = 0.0f;
+        for (size_t i = 0; i < len; i++) am = fmaxf(am, fabsf(x[b0 + i]));
+        float scale = am > 0.0f ? am / 127.0f : 1.0f;
+        scales[bi] = scale;
+        for (size_t i = 0; i < len; i++) q[b0 + i] = (int8_t)clampf(roundf(x[b0 + i] / scale), -128.0f, 127.0f);
+    }
+}
+
+/* BlockQuantizedInt8::dequantize (int8_quantize.rs:438-451). */
+void orc_ref_block_int8_dequant(const int8_t* q, const float* scales, size_t n, size_t block, float* out) {
+    for (size_t i = 0; i < n; i++) out[i] = (float)q[i] * scales[i / block];
+}
+
+/* quantize_to_int8 (int8_quantize.rs:33-92; arithmetic of its two generated kernels, :148-330):
+ * scale[0] = max(absmax / 127, 1e-12); q = rint(clamp(x / scale, -127, 127)) (round half to even). */
+void orc_ref_dnn_int8_quant(const float* x, size_t n, int8_t* q, float* scale) {
+    float am = 0.0f;
+    for (size_t i = 0; i < n; i++) am = fmaxf(am, fabsf(x[i]));
+    float sc = fmaxf(am / 127.0f, 1e-12f);
+    scale[0] = sc;
+    for (size_t i = 0; i < n; i++) q[i] = (int8_t)rintf(fminf(fmaxf(x[i] / sc, -127.0f), 127.0f));
+}
+
+/* dequantize_from_int8 (int8_quantize.rs:101-157): out = (float)q * scale[0]. */
+void orc_ref_dnn_int8_dequant(const int8_t* q, size_t n, float scale, float* out) {
+    for (size_t i = 0; i < n; i++) out[i] = (float)q[i] * scale;
+}
+
+/* ------------------------------------------------------------------------- */
 
 /* Y[b,o] = bias[o] + sum_i X[b,i] * W[o,i], accumulated left to right in f32
  * (crates/oxicuda-dist-infer/src/tensor_parallel/column_parallel.rs:77-95;

@@ -1,0 +1,295 @@
+// Quantizers next to the hot path: the per-tensor INT8 form of the DNN crate's device API, its per-block INT8
+// container, and NF4.  All are memory-bound streaming kernels with the same conventions as oxq_quant.cu:
+// caller-owned device buffers, stream-ordered, 128-bit accesses where the layout allows, IEEE divisions.
+#include "oxq_common.cuh"
+
+namespace oxq {
+
+// ------------------------------------------------------------------------------------------------
+// INT8, one scale for the whole tensor
+// ------------------------------------------------------------------------------------------------
+
+template <typename T>
+__device__ __forceinline__ void load8f(const T* p, float (&f)[8]);
+template <>
+__device__ __forceinline__ void load8f<float>(const float* p, float (&f)[8]) {
+    const float4 a = __ldcs(reinterpret_cast<const float4*>(p)), b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8f<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+}
+template <>
+__device__ __forceinline__ void load8f<__half>(const __half* p, float (&f)[8]) {
+    const uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; i++) { const float2 v = __half22float2(h[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
+}
+
+// clamp(x / scale, -127, 127) rounded half to even, as an int8 code in the low byte
+__device__ __forceinline__ uint32_t quant_i8_rne(float x, const InvDiv& d) {
+    float v = div_exact(x, d);
+    v = fminf(fmaxf(v, -127.0f), 127.0f);                   // max / min drop a NaN operand: NaN -> -127 -> like the PTX max.f32
+    return __float_as_uint(v + 12582912.0f) & 0xFFu;        // RNE(v) in the low mantissa bits of v + 1.5 * 2^23
+}
+
+// scale[0] = max(absmax / 127, 1e-12); q = rint(clamp(x / scale, -127, 127)).  The maximum was left in
+// `absmax` (a cell of the handle) by the reduction kernel that ran just before on the same stream.
+template <typename T>
+__global__ void __launch_bounds__(256) int8_tensor_quant_kernel(const T* __restrict__ x, int64_t n, const float* __restrict__ absmax,
+                                                                int8_t* __restrict__ q, float* __restrict__ scale_out) {
+    const float sc = fmaxf(__fdiv_rn(*absmax, 127.0f), 1e-12f);
+    if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = sc;
+    const InvDiv d = make_invdiv(sc);
+    const int64_t nitems = n >> 3;
+    for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < nitems; t += (int64_t)gridDim.x * blockDim.x) {
+        float f[8];
+        load8f(x + t * 8, f);
+        uint2 o;
+        o.x = quant_i8_rne(f[0], d) | (quant_i8_rne(f[1], d) << 8) | (quant_i8_rne(f[2], d) << 16) | (quant_i8_rne(f[3], d) << 24);
+        o.y = quant_i8_rne(f[4], d) | (quant_i8_rne(f[5], d) << 8) | (quant_i8_rne(f[6], d) << 16) | (quant_i8_rne(f[7], d) << 24);
+        __stcs(reinterpret_cast<uint2*>(q + t * 8), o);
+    }
+    // ragged tail (n not a multiple of 8)
+    if (blockIdx.x == 0) {
+        for (int64_t i = (nitems << 3) + threadIdx.x; i < n; i += blockDim.x) q[i] = (int8_t)quant_i8_rne(Elem<T>::to_f32(x[i]), d);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) int8_tensor_dequant_kernel(const int8_t* __restrict__ q, int64_t n, const float* __restrict__ scale,
+                                                                  T* __restrict__ y) {
+    const float sc = *scale;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        y[i] = Elem<T>::from_f32((float)q[i] * sc);
+}
+
+// ------------------------------------------------------------------------------------------------
+// INT8, one scale per block of contiguous elements (the last block may be short)
+// ------------------------------------------------------------------------------------------------
+
+// A warp per block: maximum, then q = clamp(round_half_away(x / scale), -128, 127).  The second pass finds the
+// block in L1 / L2.
+__global__ void __launch_bounds__(256) int8_block_quant_kernel(const float* __restrict__ x, int64_t n, int64_t block, int64_t nblocks,
+                                                               int8_t* __restrict__ q, float* __restrict__ scales) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t b = warp0; b < nblocks; b += nwarps) {
+        const int64_t b0 = b * block;
+        const int64_t len = n - b0 < block ? n - b0 : block;
+        float am = 0.0f;
+        for (int64_t i = lane; i < len; i += 32) am = fmaxf(am, fabsf(x[b0 + i]));
+        am = warp_max(am);
+        const float sc = am > 0.0f ? __fdiv_rn(am, 127.0f) : 1.0f;
+        if (lane == 0) scales[b] = sc;
+        for (int64_t i = lane; i < len; i += 32) {
+            float v = roundf(__fdiv_rn(x[b0 + i], sc));
+            v = v != v ? 0.0f : fminf(fmaxf(v, -128.0f), 127.0f);          // NaN -> 0 (Rust `as i8`)
+            q[b0 + i] = (int8_t)(int)v;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) int8_block_dequant_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales, int64_t n,
+                                                                 int64_t block, float* __restrict__ y) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        y[i] = (float)q[i] * __ldg(scales + i / block);
+}
+
+// ------------------------------------------------------------------------------------------------
+// NF4
+// ------------------------------------------------------------------------------------------------
+
+__constant__ float c_nf4[16] = {-1.0f, -0.69619286f, -0.52507305f, -0.3949175f, -0.28444138f, -0.18477343f, -0.09105003f, 0.0f,
+                                0.0795803f, 0.1609302f, 0.2461123f, 0.33791524f, 0.44070983f, 0.562617f, 0.72295684f, 1.0f};
+
+// Index of the level nearest to v in [-1, 1]; between two levels the lower index wins a tie.  Same steps as the
+// reference: first index whose level is >= v, then the two distances compared in f32.
+__device__ __forceinline__ uint32_t nearest_nf4(float v, const float* lut) {
+    int lo = 0;
+#pragma unroll
+    for (int step = 8; step > 0; step >>= 1)                 // lo = number of levels below v (levels are strictly increasing)
+        if (lut[lo + step - 1] < v) lo += step;
+    if (lo == 0) return 0;                                   // v <= -1 (NaN too: every comparison is false)
+    if (lo == 15 && lut[15] < v) return 15;
+    const float d_lo = fabsf(v - lut[lo - 1]), d_hi = fabsf(lut[lo] - v);
+    return d_lo <= d_hi ? (uint32_t)(lo - 1) : (uint32_t)lo;
+}
+
+// Eight consecutive elements per lane (one packed word); LPB lanes share a block of 8 * LPB elements.
+template <int LPB>
+__global__ void __launch_bounds__(256) nf4_quant_kernel(const float* __restrict__ x, int64_t n, uint8_t* __restrict__ packed,
+                                                        float* __restrict__ absmaxs) {
+    __shared__ float lut[16];                                 // lanes look up different levels: shared memory, not the constant bank
+    if (threadIdx.x < 16) lut[threadIdx.x] = c_nf4[threadIdx.x];
+    __syncthreads();
+    const int64_t nitems = n >> 3;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    // whole warps iterate together so the shuffles below always have their partners
+    for (int64_t t0 = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); t0 < nitems; t0 += stride) {
+        const int64_t t = t0 + (threadIdx.x & 31);
+        const bool live = t < nitems;
+        float f[8];
+        if (live) load8f(x + t * 8, f);
+        else {
+#pragma unroll
+            for (int e = 0; e < 8; e++) f[e] = 0.0f;
+        }
+        float am = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) am = fmaxf(am, fabsf(f[e]));
+#pragma unroll
+        for (int o = LPB / 2; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+        am = am < 1e-8f ? 1e-8f : am;
+        if (!live) continue;
+        const InvDiv d = make_invdiv(am);
+        uint32_t w = 0;
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const float normed = fminf(fmaxf(div_exact(f[e], d), -1.0f), 1.0f);
+            w |= nearest_nf4(normed, lut) << (4 * e);
+        }
+        __stcs(reinterpret_cast<uint32_t*>(packed) + t, w);
+        if ((t & (LPB - 1)) == 0) absmaxs[t / LPB] = am;
+    }
+}
+
+// Any even block size: a warp per block, two elements (one byte) per lane and step.
+__global__ void __launch_bounds__(256) nf4_quant_generic_kernel(const float* __restrict__ x, int64_t nblocks, int64_t block,
+                                                                uint8_t* __restrict__ packed, float* __restrict__ absmaxs) {
+    __shared__ float lut[16];
+    if (threadIdx.x < 16) lut[threadIdx.x] = c_nf4[threadIdx.x];
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    for (int64_t b = warp0; b < nblocks; b += nwarps) {
+        const float* xb = x + b * block;
+        float am = 0.0f;
+        for (int64_t i = lane; i < block; i += 32) am = fmaxf(am, fabsf(xb[i]));
+        am = warp_max(am);
+        am = am < 1e-8f ? 1e-8f : am;
+        if (lane == 0) absmaxs[b] = am;
+        for (int64_t i = lane; i < block / 2; i += 32) {
+            const float v0 = fminf(fmaxf(__fdiv_rn(xb[2 * i], am), -1.0f), 1.0f), v1 = fminf(fmaxf(__fdiv_rn(xb[2 * i + 1], am), -1.0f), 1.0f);
+            packed[b * (block / 2) + i] = (uint8_t)(nearest_nf4(v0, lut) | (nearest_nf4(v1, lut) << 4));
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) nf4_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ absmaxs, int64_t n,
+                                                          int64_t block, T* __restrict__ y) {
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint32_t code = (packed[i >> 1] >> ((i & 1) * 4)) & 0xFu;
+        y[i] = Elem<T>::from_f32(c_nf4[code] * __ldg(absmaxs + i / block));
+    }
+}
+
+static inline int grid_cap(oxq_handle* h, int64_t threads_needed, int block, int ctas_per_sm) {
+    int64_t need = (threads_needed + block - 1) / block;
+    const int64_t cap = (int64_t)h->sm_count * ctas_per_sm;
+    if (need < 1) need = 1;
+    return (int)(need < cap ? need : cap);
+}
+
+}  // namespace oxq
+
+using namespace oxq;
+
+#define DISPATCH_DTYPE(dtype, ...)                                           \
+    switch (dtype) {                                                         \
+        case OXQ_F32: { using T = float; __VA_ARGS__; break; }               \
+        case OXQ_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }      \
+        case OXQ_F16: { using T = __half; __VA_ARGS__; break; }              \
+        default: OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "unknown dtype %d", dtype); \
+    }
+
+static inline bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+extern "C" {
+
+int32_t oxq_int8_quant_tensor(oxq_handle* h, const void* x, int dtype, int64_t n, int8_t* q, float* scale_dev) {
+    OXQ_CHECK_HANDLE(h);
+    if (n == 0) return OXQ_OK;                                 // quantize_to_int8 returns Ok(()) on an empty tensor
+    if (n < 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "negative element count");
+    if (!x || !q || !scale_dev || !aligned16(x) || ((uintptr_t)q & 7u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (!h->dev_scratch) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "handle has no reduction cells");
+    float* absmax = reinterpret_cast<float*>(h->dev_scratch + 4);          // cells 0-1 belong to the reduction itself
+    if (int32_t rc = oxq_absmax(h, x, dtype, n, absmax)) return rc;
+    DISPATCH_DTYPE(dtype, int8_tensor_quant_kernel<T><<<grid_cap(h, n / 8 + 1, 256, 8), 256, 0, h->stream>>>((const T*)x, n, absmax, q, scale_dev));
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_int8_dequant_tensor(oxq_handle* h, const int8_t* q, const float* scale_dev, int64_t n, void* y, int y_dtype) {
+    OXQ_CHECK_HANDLE(h);
+    if (n == 0) return OXQ_OK;
+    if (n < 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "negative element count");
+    if (!q || !scale_dev || !y) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    DISPATCH_DTYPE(y_dtype, int8_tensor_dequant_kernel<T><<<grid_cap(h, n, 256, 16), 256, 0, h->stream>>>(q, n, scale_dev, (T*)y));
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_int8_block_quant(oxq_handle* h, const float* x, int64_t n, int64_t block, int8_t* q, float* scales) {
+    OXQ_CHECK_HANDLE(h);
+    if (block <= 0) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "block_size must be > 0");
+    if (n == 0) return OXQ_OK;
+    if (n < 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "negative element count");
+    if (!x || !q || !scales) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    const int64_t nblocks = (n + block - 1) / block;
+    int8_block_quant_kernel<<<grid_cap(h, nblocks * 32, 256, 8), 256, 0, h->stream>>>(x, n, block, nblocks, q, scales);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_int8_block_dequant(oxq_handle* h, const int8_t* q, const float* scales, int64_t n, int64_t block, float* y) {
+    OXQ_CHECK_HANDLE(h);
+    if (block <= 0) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "block_size must be > 0");
+    if (n == 0) return OXQ_OK;
+    if (n < 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "negative element count");
+    if (!q || !scales || !y) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    int8_block_dequant_kernel<<<grid_cap(h, n, 256, 16), 256, 0, h->stream>>>(q, scales, n, block, y);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_nf4_quant(oxq_handle* h, const float* x, int64_t n, int64_t block, uint8_t* packed, float* absmaxs) {
+    OXQ_CHECK_HANDLE(h);
+    if (block <= 0 || (block & 1)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "block_size must be positive and even, got %lld", (long long)block);
+    if (n <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "Nf4Quantizer::encode");
+    if (n % block != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "length %lld is not divisible by block size %lld", (long long)n, (long long)block);
+    if (!x || !packed || !absmaxs) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    const bool vec = aligned16(x) && ((uintptr_t)packed & 3u) == 0;
+    const int grid = grid_cap(h, n / 8 + 1, 256, 8);
+    if (vec && block == 32) nf4_quant_kernel<4><<<grid, 256, 0, h->stream>>>(x, n, packed, absmaxs);
+    else if (vec && block == 64) nf4_quant_kernel<8><<<grid, 256, 0, h->stream>>>(x, n, packed, absmaxs);
+    else if (vec && block == 128) nf4_quant_kernel<16><<<grid, 256, 0, h->stream>>>(x, n, packed, absmaxs);
+    else if (vec && block == 256) nf4_quant_kernel<32><<<grid, 256, 0, h->stream>>>(x, n, packed, absmaxs);
+    else nf4_quant_generic_kernel<<<grid_cap(h, (n / block) * 32, 256, 8), 256, 0, h->stream>>>(x, n / block, block, packed, absmaxs);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_nf4_dequant(oxq_handle* h, const uint8_t* packed, const float* absmaxs, int64_t n, int64_t block, void* y, int y_dtype) {
+    OXQ_CHECK_HANDLE(h);
+    if (block <= 0 || (block & 1)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "block_size must be positive and even, got %lld", (long long)block);
+    if (n <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "Nf4Quantizer::decode");
+    if (n % block != 0) OXQ_FAIL(h, OXQ_ERR_QUANT_DIMENSION_MISMATCH, "length %lld is not divisible by block size %lld", (long long)n, (long long)block);
+    if (!packed || !absmaxs || !y) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    DISPATCH_DTYPE(y_dtype, nf4_dequant_kernel<T><<<grid_cap(h, n, 256, 16), 256, 0, h->stream>>>(packed, absmaxs, n, block, (T*)y));
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+}  // extern "C"

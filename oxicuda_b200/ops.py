@@ -206,6 +206,63 @@ def nvfp4_dequant(packed, sf, stats, dtype=torch.float32):
     return y
 
 
+# ------------------------------------------------------------------------------------------- next to the hot path
+
+def quantize_to_int8(x: torch.Tensor, out: torch.Tensor | None = None, scale: torch.Tensor | None = None):
+    """Per-tensor INT8 of oxicuda-dnn (crates/oxicuda-dnn/src/quantize/int8_quantize.rs:33-38): returns (codes, scale[1])."""
+    _chk(x, torch.float32, torch.bfloat16, torch.float16)
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device) if out is None else out
+    sc = torch.empty(1, dtype=torch.float32, device=x.device) if scale is None else scale
+    handle(x.device.index).call("oxq_int8_quant_tensor", _p(x), _DT[x.dtype], x.numel(), _p(q), _p(sc))
+    return q, sc
+
+
+def dequantize_from_int8(q: torch.Tensor, scale: torch.Tensor, dtype=torch.float32):
+    """out[i] = (float)q[i] * scale[0] (int8_quantize.rs:101-107)."""
+    y = torch.empty(q.shape, dtype=dtype, device=q.device)
+    handle(q.device.index).call("oxq_int8_dequant_tensor", _p(q), _p(scale), q.numel(), _p(y), _DT[dtype])
+    return y
+
+
+def block_int8_quant(x: torch.Tensor, block: int):
+    """BlockQuantizedInt8::quantize on a device tensor (int8_quantize.rs:404-432): (codes, scales[ceil(n / block)])."""
+    _chk(x, torch.float32)
+    if block <= 0:
+        raise ValueError("block_size must be > 0")
+    n = x.numel()
+    q = torch.empty(n, dtype=torch.int8, device=x.device)
+    sc = torch.empty(max((n + block - 1) // block, 1), dtype=torch.float32, device=x.device)
+    handle(x.device.index).call("oxq_int8_block_quant", _p(x), n, block, _p(q), _p(sc))
+    return q, sc[: (n + block - 1) // block]
+
+
+def block_int8_dequant(q: torch.Tensor, scales: torch.Tensor, block: int):
+    y = torch.empty(q.numel(), dtype=torch.float32, device=q.device)
+    handle(q.device.index).call("oxq_int8_block_dequant", _p(q), _p(scales), q.numel(), block, _p(y))
+    return y
+
+
+def nf4_quant(x: torch.Tensor, block: int = 64):
+    """Nf4Quantizer::encode (crates/oxicuda-quant/src/scheme/nf4.rs:93-130): (packed bytes [n / 2], absmax [n / block])."""
+    _chk(x, torch.float32)
+    n = x.numel()
+    packed = torch.empty(max(n // 2, 1), dtype=torch.uint8, device=x.device)
+    am = torch.empty(max(n // max(block, 1), 1), dtype=torch.float32, device=x.device)
+    handle(x.device.index).call("oxq_nf4_quant", _p(x), n, block, _p(packed), _p(am))
+    return packed[: n // 2], am[: n // block]
+
+
+def nf4_dequant(packed: torch.Tensor, absmaxs: torch.Tensor, block: int = 64, dtype=torch.float32):
+    """Nf4Quantizer::decode (nf4.rs:137-155)."""
+    n = packed.numel() * 2
+    if block <= 0 or absmaxs.numel() != n // block:
+        from .errors import QuantError
+        raise QuantError("DimensionMismatch", f"expected {n // max(block, 1)} absmax values, got {absmaxs.numel()}", 4)
+    y = torch.empty(n, dtype=dtype, device=packed.device)
+    handle(packed.device.index).call("oxq_nf4_dequant", _p(packed), _p(absmaxs), n, block, _p(y), _DT[dtype])
+    return y
+
+
 # ------------------------------------------------------------------------------------------- GEMMs
 
 def gemm_fp8(x_q, w_q, sx, sw, out: torch.Tensor | None = None):

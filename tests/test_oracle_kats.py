@@ -213,3 +213,73 @@ def test_tp_column_then_row_matches_unsharded(orc):  # crates/oxicuda-dist-infer
     want = (x @ wg.T)
     want = want / (1 + np.exp(-want)) * (x @ wu.T)
     assert np.allclose(full, want @ wd.T, rtol=1e-4, atol=1e-4)
+
+
+# ---- rows after the hot path: NF4, per-block INT8, per-tensor INT8 ------------------------------------
+
+def test_nf4_lut_kats(orc):  # crates/oxicuda-quant/src/scheme/nf4.rs:213-233
+    lut = orc.nf4_levels()
+    assert (np.diff(lut) > 0).all()
+    assert lut[0] == -1.0 and lut[15] == 1.0 and lut[7] == 0.0
+    assert orc.ref_nearest_nf4(-1.0) == 0 and orc.ref_nearest_nf4(1.0) == 15 and orc.ref_nearest_nf4(0.0) == 7
+    mid = float((lut[7] + lut[8]) / np.float32(2.0))
+    assert orc.ref_nearest_nf4(mid) in (7, 8)
+    assert orc.ref_nearest_nf4(-5.0) == 0 and orc.ref_nearest_nf4(5.0) == 15
+
+
+def test_nf4_round_trip_kats(orc):  # nf4.rs:243-296
+    t = (np.arange(128, dtype=np.float32) / np.float32(64.0)) - np.float32(1.0)
+    packed, am = orc.ref_nf4_encode(t, 64)
+    assert packed.size == 64 and am.size == 2
+    dec = orc.ref_nf4_decode(packed, am, 64)
+    assert float(((t - dec) ** 2).mean()) < 0.01
+    packed, am = orc.ref_nf4_encode(np.zeros(64, np.float32), 64)       # all zeros: absmax floor 1e-8, code 7
+    assert am[0] == np.float32(1e-8) and (packed == 0x77).all()
+    assert np.abs(orc.ref_nf4_decode(packed, am, 64)).max() < 1e-5
+    t = np.tile(2.0 * (np.arange(64, dtype=np.float32) / 64.0) - 1.0, 16)
+    packed, am = orc.ref_nf4_encode(t, 64)
+    assert float(((t - orc.ref_nf4_decode(packed, am, 64)) ** 2).mean()) < 0.05
+    with pytest.raises(orc.OracleError) as e:
+        orc.ref_nf4_encode(np.full(65, 0.5, np.float32), 64)
+    assert e.value.name == "GroupSizeMismatch"
+    with pytest.raises(orc.OracleError) as e:
+        orc.ref_nf4_decode(np.zeros(32, np.uint8), np.ones(5, np.float32), 64)
+    assert e.value.name == "DimensionMismatch"
+    with pytest.raises(orc.OracleError) as e:
+        orc.ref_nf4_encode(np.zeros(0, np.float32), 64)
+    assert e.value.name == "EmptyInput"
+
+
+def test_block_int8_kats(orc):  # crates/oxicuda-dnn/src/quantize/int8_quantize.rs:541-704
+    x = np.arange(256, dtype=np.float32)
+    q, s = orc.ref_block_int8_quant(x, 64)
+    assert s.size == 4
+    q, s = orc.ref_block_int8_quant(np.arange(100, dtype=np.float32), 64)        # 64 + 36
+    assert s.size == 2 and orc.ref_block_int8_dequant(q, s, 64).size == 100
+    x = np.array([1e30, -1e30, 0.0, 1e30], np.float32)
+    q, s = orc.ref_block_int8_quant(x, 4)
+    d = orc.ref_block_int8_dequant(q, s, 4)
+    assert d[0] > 0 and d[1] < 0 and d[2] == 0.0 and list(q) == [127, -127, 0, 127]
+    assert orc.ref_block_int8_quant(np.arange(256, dtype=np.float32), 128)[1].size == 2
+    d = orc.ref_block_int8_dequant(np.array([-128, 0, 127], np.int8), np.array([0.1], np.float32), 3)
+    assert np.allclose(d, [-12.8, 0.0, 12.7], atol=1e-4)
+    x = np.concatenate([np.full(64, 0.001, np.float32), np.full(64, 100.0, np.float32)])
+    _, s = orc.ref_block_int8_quant(x, 64)
+    assert s[1] / s[0] > 10.0
+    x = (np.arange(300, dtype=np.float32) - np.float32(150.0)) / np.float32(5.0)
+    q, s = orc.ref_block_int8_quant(x, 100)
+    assert s.size == 3
+    assert (np.abs(x - orc.ref_block_int8_dequant(q, s, 100)) <= s.max() * 0.5 + 1e-5).all()
+    _, s = orc.ref_block_int8_quant(np.zeros(8, np.float32), 4)                  # all-zero block -> scale 1
+    assert (s == 1.0).all()
+
+
+def test_dnn_int8_tensor_definition(orc):  # int8_quantize.rs:26-29 (the formula its kernels implement)
+    x = orc.gaussian((1, 1000), 1.0, 3).ravel()
+    q, s = orc.ref_dnn_int8_quant(x)
+    assert s[0] == np.float32(np.abs(x).max()) / np.float32(127.0)
+    want = np.rint(np.clip(x / s[0], -127, 127)).astype(np.int8)
+    assert (q == want).all() and np.abs(q).max() == 127
+    q0, s0 = orc.ref_dnn_int8_quant(np.zeros(4, np.float32))
+    assert s0[0] == np.float32(1e-12) and (q0 == 0).all()
+    assert np.allclose(orc.ref_dnn_int8_dequant(q, s[0]), q.astype(np.float32) * s[0])

@@ -214,6 +214,9 @@ OXQ_API int32_t oxq_int8_block_dequant(oxq_handle* h, const int8_t* q_dev, const
 OXQ_API int32_t oxq_nf4_quant(oxq_handle* h, const float* x_dev, int64_t n, int64_t block, uint8_t* packed_dev, float* absmax_dev);
 OXQ_API int32_t oxq_nf4_dequant(oxq_handle* h, const uint8_t* packed_dev, const float* absmax_dev, int64_t n, int64_t block,
                                 void* y_dev, int y_dtype);
+/* y[m, n] += bias[n] on a bf16 matrix (the bias term of ColumnLinearShard::forward / RowLinearShard::forward_partial,
+ * crates/oxicuda-dist-infer/src/tensor_parallel/column_parallel.rs:77-95, row_parallel.rs:67-90); n and ldy multiples of 8. */
+OXQ_API int32_t oxq_bias_add_bf16(oxq_handle* h, void* y_bf16_dev, int64_t ldy, const float* bias_dev, int64_t m, int64_t n);
 /* Block-scaled GEMMs (Fp4GemmConfig, fp4_fp6_ops.rs:337-395).  Scale factors in the tiled order. */
 OXQ_API int32_t oxq_gemm_mxfp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x_dev, const uint8_t* sfx_mma_dev,
                        const uint8_t* w_dev, const uint8_t* sfw_mma_dev, void* y_bf16_dev, int64_t ldy);

@@ -190,6 +190,27 @@ __global__ void __launch_bounds__(256) nf4_dequant_kernel(const uint8_t* __restr
     }
 }
 
+// y[m, n] += bias[n] on a bf16 matrix with leading dimension ldy (f32 add, one rounding); 8 columns per thread.
+__global__ void __launch_bounds__(256) bias_add_bf16_kernel(__nv_bfloat16* __restrict__ y, int64_t ldy, const float* __restrict__ bias,
+                                                            int64_t m, int64_t n) {
+    const int64_t per_row = n >> 3;
+    for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < m * per_row; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = t / per_row, c = (t - r * per_row) << 3;
+        uint4* p = reinterpret_cast<uint4*>(y + r * ldy + c);
+        uint4 u = *p;
+        uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + c)), b1 = __ldg(reinterpret_cast<const float4*>(bias + c) + 1);
+        const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float lo = __uint_as_float(w[i] << 16) + b[2 * i], hi = __uint_as_float(w[i] & 0xFFFF0000u) + b[2 * i + 1];
+            const __nv_bfloat162 o = __floats2bfloat162_rn(lo, hi);
+            w[i] = *reinterpret_cast<const uint32_t*>(&o);
+        }
+        *p = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
 static inline int grid_cap(oxq_handle* h, int64_t threads_needed, int block, int ctas_per_sm) {
     int64_t need = (threads_needed + block - 1) / block;
     const int64_t cap = (int64_t)h->sm_count * ctas_per_sm;
@@ -258,6 +279,16 @@ int32_t oxq_int8_block_dequant(oxq_handle* h, const int8_t* q, const float* scal
     if (!q || !scales || !y) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     int8_block_dequant_kernel<<<grid_cap(h, n, 256, 16), 256, 0, h->stream>>>(q, scales, n, block, y);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_bias_add_bf16(oxq_handle* h, void* y, int64_t ldy, const float* bias, int64_t m, int64_t n) {
+    OXQ_CHECK_HANDLE(h);
+    if (m <= 0 || n <= 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "dimensions must be non-zero");
+    if (!y || !bias || !aligned16(y) || !aligned16(bias) || (n & 7) || (ldy & 7)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer, or n / ldy not a multiple of 8");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    bias_add_bf16_kernel<<<grid_cap(h, m * n / 8, 256, 8), 256, 0, h->stream>>>((__nv_bfloat16*)y, ldy, bias, m, n);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

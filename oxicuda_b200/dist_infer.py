@@ -55,6 +55,160 @@ def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor
     return torch.stack([w_gate.reshape(inter // 128, 128, k), w_up.reshape(inter // 128, 128, k)], dim=1).reshape(2 * inter, k).contiguous()
 
 
+# ------------------------------------------------------------------------------------------------ single linears
+
+LINEAR_VARIANTS = ("fp8", "bf16")
+
+
+def _dist_error(variant: str, msg: str):
+    from .errors import DistInferError
+    return DistInferError(variant, msg)
+
+
+class _ShardedLinear:
+    """One rank's weight shard on the GPU: E4M3 with a per-shard scale ("fp8", activations quantised per call)
+    or bf16.  y = bf16(x . W_shard^T) (+ bias)."""
+
+    def _load(self, w_shard: torch.Tensor, bias, variant: str):
+        from . import ops
+        if variant not in LINEAR_VARIANTS:
+            raise ValueError(f"variant {variant!r} not in {LINEAR_VARIANTS}")
+        self.ops, self.variant = ops, variant
+        dev = torch.device("cuda", torch.cuda.current_device())
+        w = w_shard.to(dev).contiguous()
+        if variant == "fp8":
+            self.w_q, st = ops.fp8_quant_dynamic(w.to(torch.bfloat16))
+            self.s_w = st[1:].clone()
+        else:
+            self.w = w.to(torch.bfloat16)
+        self.bias = None if bias is None else bias.to(dev, torch.float32).contiguous()
+
+    def _matmul(self, x: torch.Tensor) -> torch.Tensor:
+        ops = self.ops
+        if self.variant == "fp8":
+            xq, sx = ops.fp8_quant_dynamic(x)
+            y = ops.gemm_fp8(xq, self.w_q, sx[1:], self.s_w)
+        else:
+            y = ops.gemm_bf16(x, self.w)
+        if self.bias is not None:
+            ops.bias_add_(y, self.bias)
+        return y
+
+
+def gather_columns(local: torch.Tensor, tp: int, group=None) -> torch.Tensor:
+    """All-gather of column shards: local [batch x local_out] on every rank -> [batch x tp*local_out], rank r's
+    columns at [r*local_out, (r+1)*local_out) (ColumnLinear::all_gather, column_parallel.rs:181-204)."""
+    import torch.distributed as dist
+    if tp == 1:
+        return local
+    batch, lo = local.shape
+    stacked = torch.empty((tp * batch, lo), dtype=local.dtype, device=local.device)     # rank-major concatenation
+    dist.all_gather_into_tensor(stacked, local.contiguous(), group=group)
+    return stacked.view(tp, batch, lo).permute(1, 0, 2).reshape(batch, tp * lo)
+
+
+class ColumnLinear(_ShardedLinear):
+    """Column-parallel linear: rank r owns output rows [r*total_out/tp, (r+1)*total_out/tp) of W [total_out x in]
+    (crates/oxicuda-dist-infer/src/tensor_parallel/column_parallel.rs:103-204)."""
+
+    @classmethod
+    def from_full_weight(cls, in_features: int, total_out: int, weight: torch.Tensor, bias: torch.Tensor | None = None,
+                         tp: int = 1, rank: int = 0, variant: str = "fp8", group=None):
+        if tp < 1 or not (0 <= rank < tp):
+            raise _dist_error("TooFewRanks", f"rank {rank} outside a world of {tp}")
+        if total_out % tp != 0:
+            raise _dist_error("TpFeaturesMisaligned", f"features {total_out} not divisible by degree {tp}")
+        if weight.numel() != total_out * in_features:
+            raise _dist_error("DimensionMismatch", f"expected {total_out * in_features}, got {weight.numel()}")
+        if bias is not None and bias.numel() != total_out:
+            raise _dist_error("DimensionMismatch", f"expected {total_out}, got {bias.numel()}")
+        self = cls()
+        self.in_features, self.total_out, self.tp, self.rank, self.group = in_features, total_out, tp, rank, group
+        rows = column_shard_rows(total_out, tp, rank)
+        self.local_out, self.col_offset = rows.stop - rows.start, rows.start
+        self._load(weight.reshape(total_out, in_features)[rows], None if bias is None else bias.reshape(-1)[rows], variant)
+        return self
+
+    def local_forward(self, x: torch.Tensor) -> torch.Tensor:
+        """[batch x in] bf16 -> this rank's [batch x local_out] bf16."""
+        if x.shape[-1] != self.in_features:
+            raise _dist_error("DimensionMismatch", f"expected {self.in_features} input features, got {x.shape[-1]}")
+        return self._matmul(x)
+
+    def all_gather(self, local: torch.Tensor) -> torch.Tensor:
+        return gather_columns(local, self.tp, self.group)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.all_gather(self.local_forward(x))
+
+    @staticmethod
+    def gather_shards(total_out: int, batch: int, shards) -> torch.Tensor:
+        """The reference's host-side all_gather over a list of per-rank outputs (column_parallel.rs:181-204)."""
+        if len(shards) == 0:
+            raise _dist_error("TooFewRanks", "needed 1, world_size 0")
+        lo = total_out // len(shards)
+        return torch.cat([s.reshape(batch, lo) for s in shards], dim=1)
+
+
+class RowLinear(_ShardedLinear):
+    """Row-parallel linear: rank r owns input columns [r*total_in/tp, (r+1)*total_in/tp) of W [out x total_in]; the
+    bias lives on rank 0 only so the all-reduce counts it once
+    (crates/oxicuda-dist-infer/src/tensor_parallel/row_parallel.rs:97-223)."""
+
+    @classmethod
+    def from_full_weight(cls, out_features: int, total_in: int, weight: torch.Tensor, bias: torch.Tensor | None = None,
+                         tp: int = 1, rank: int = 0, variant: str = "fp8", group=None):
+        if tp < 1 or not (0 <= rank < tp):
+            raise _dist_error("TooFewRanks", f"rank {rank} outside a world of {tp}")
+        if total_in % tp != 0:
+            raise _dist_error("TpInputMisaligned", f"features {total_in} not divisible by degree {tp}")
+        if weight.numel() != out_features * total_in:
+            raise _dist_error("DimensionMismatch", f"expected {out_features * total_in}, got {weight.numel()}")
+        if bias is not None and rank == 0 and bias.numel() != out_features:
+            raise _dist_error("DimensionMismatch", f"expected {out_features}, got {bias.numel()}")
+        self = cls()
+        self.out_features, self.total_in, self.tp, self.rank, self.group = out_features, total_in, tp, rank, group
+        cols = row_shard_cols(total_in, tp, rank)
+        self.local_in, self.row_offset = cols.stop - cols.start, cols.start
+        self._load(weight.reshape(out_features, total_in)[:, cols], bias.reshape(-1) if (bias is not None and rank == 0) else None, variant)
+        return self
+
+    def slice_input(self, full_input: torch.Tensor) -> torch.Tensor:
+        if full_input.shape[-1] != self.total_in:
+            raise _dist_error("DimensionMismatch", f"expected {self.total_in} input features, got {full_input.shape[-1]}")
+        return full_input[:, self.row_offset:self.row_offset + self.local_in].contiguous()
+
+    def forward_partial(self, input_slice: torch.Tensor) -> torch.Tensor:
+        if input_slice.shape[-1] != self.local_in:
+            raise _dist_error("DimensionMismatch", f"expected {self.local_in} input features, got {input_slice.shape[-1]}")
+        return self._matmul(input_slice)
+
+    def local_forward(self, full_input: torch.Tensor) -> torch.Tensor:
+        return self.forward_partial(self.slice_input(full_input))
+
+    def all_reduce(self, partial: torch.Tensor) -> torch.Tensor:
+        """Sum of the ranks' partials, in place (one collective; RowLinear::all_reduce, row_parallel.rs:199-223)."""
+        import torch.distributed as dist
+        if self.tp > 1:
+            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+        return partial
+
+    def forward(self, full_input: torch.Tensor) -> torch.Tensor:
+        return self.all_reduce(self.local_forward(full_input))
+
+    @staticmethod
+    def reduce_partials(partials) -> torch.Tensor:
+        """The reference's host-side all_reduce over a list of per-rank partials, summed in rank order."""
+        if len(partials) == 0:
+            raise _dist_error("TooFewRanks", "needed 1, world_size 0")
+        acc = partials[0].clone()
+        for part in partials[1:]:
+            if part.numel() != acc.numel():
+                raise _dist_error("DimensionMismatch", f"expected {acc.numel()}, got {part.numel()}")
+            acc += part
+        return acc
+
+
 # ------------------------------------------------------------------------------------------------ the layer
 
 class TpSwiGluMlp:

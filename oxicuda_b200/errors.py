@@ -20,6 +20,11 @@ class BlasError(OxqError):
     pass
 
 
+class DistInferError(OxqError):
+    """DistInferError of the reference (crates/oxicuda-dist-infer/src/error.rs): TpFeaturesMisaligned,
+    TpInputMisaligned, DimensionMismatch, TooFewRanks, ShardShapeMismatch."""
+
+
 _QUANT = {1: "EmptyInput", 2: "GroupSizeMismatch", 3: "InvalidScale", 4: "DimensionMismatch", 5: "NonFiniteFp8",
           6: "InvalidBitWidth"}
 _BLAS = {10: "InvalidDimension", 11: "BufferTooSmall", 12: "DimensionMismatch", 13: "UnsupportedOperation",

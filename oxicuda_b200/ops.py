@@ -263,6 +263,13 @@ def nf4_dequant(packed: torch.Tensor, absmaxs: torch.Tensor, block: int = 64, dt
     return y
 
 
+def bias_add_(y: torch.Tensor, bias: torch.Tensor):
+    """In place y[m, n] += bias[n] (bf16 matrix, f32 bias)."""
+    _chk(bias, torch.float32)
+    handle(y.device.index).call("oxq_bias_add_bf16", _p(y), y.stride(0), _p(bias), y.shape[0], y.shape[1])
+    return y
+
+
 # ------------------------------------------------------------------------------------------- GEMMs
 
 def gemm_fp8(x_q, w_q, sx, sw, out: torch.Tensor | None = None):

@@ -93,3 +93,111 @@ def test_tp_mlp_nccl_two_gpus(variant):
     for _, errs in res:
         for e in errs:
             assert e <= 2 * MAX_REL
+
+
+# ---- single column- / row-parallel linears ---------------------------------------------------------
+
+def _fp8_linear_ref(orc, xb, w_shard, bias):
+    """Oracle for one shard of the "fp8" linears: per-tensor E4M3 of the bf16 operands, exact product, bf16 output,
+    then the f32 bias added and rounded to bf16 once more."""
+    x = orc.bf16_bits_to_f32(xb)
+    wb = orc.f32_to_bf16_bits(w_shard)
+    sx, sw = orc.spec_fp8_scale(orc.spec_absmax(xb)), orc.spec_fp8_scale(orc.spec_absmax(wb))
+    xq = orc.spec_fp8_dequant(orc.spec_fp8_quant(xb, sx), 1.0)
+    wq = orc.spec_fp8_dequant(orc.spec_fp8_quant(wb, sw), 1.0)
+    y = (xq.astype(np.float64) @ wq.astype(np.float64).T).astype(np.float32) * (np.float32(sx) * np.float32(sw))
+    y = orc.bf16_bits_to_f32(orc.f32_to_bf16_bits(y))
+    if bias is not None:
+        y = orc.bf16_bits_to_f32(orc.f32_to_bf16_bits(y + bias[None, :]))
+    del x
+    return y
+
+
+@pytest.mark.parametrize("variant", ["fp8", "bf16"])
+@pytest.mark.parametrize("tp", [1, 2, 4])
+def test_column_linear_one_gpu(orc, variant, tp):
+    from oxicuda_b200.dist_infer import ColumnLinear
+    in_f, out_f, batch = 256, 512, 5
+    w = orc.gaussian((out_f, in_f), 0.05, 0)
+    b = orc.gaussian((1, out_f), 1.0, 4).ravel()
+    xb = orc.f32_to_bf16_bits(orc.gaussian((batch, in_f), 1.0, 1))
+    x = bf16_dev(xb)
+    shards, refs = [], []
+    for r in range(tp):
+        layer = ColumnLinear.from_full_weight(in_f, out_f, torch.from_numpy(w), torch.from_numpy(b), tp=tp, rank=r, variant=variant)
+        shards.append(layer.local_forward(x).float().cpu())
+        rows = slice(r * out_f // tp, (r + 1) * out_f // tp)
+        if variant == "fp8":
+            refs.append(_fp8_linear_ref(orc, xb, w[rows], b[rows]))
+        else:
+            wr = orc.bf16_bits_to_f32(orc.f32_to_bf16_bits(w[rows]))
+            refs.append((orc.bf16_bits_to_f32(xb).astype(np.float64) @ wr.astype(np.float64).T).astype(np.float32) + b[rows][None, :])
+    got = ColumnLinear.gather_shards(out_f, batch, shards).numpy()
+    ref = np.concatenate(refs, axis=1)
+    scale = np.abs(ref).max()
+    assert got.shape == (batch, out_f) and np.isfinite(got).all()
+    assert np.abs(got - ref).max() <= MAX_REL * scale
+
+
+@pytest.mark.parametrize("variant", ["fp8", "bf16"])
+@pytest.mark.parametrize("tp", [1, 2, 4])
+def test_row_linear_one_gpu(orc, variant, tp):
+    from oxicuda_b200.dist_infer import RowLinear
+    in_f, out_f, batch = 512, 256, 7
+    w = orc.gaussian((out_f, in_f), 0.05, 0)
+    b = orc.gaussian((1, out_f), 1.0, 4).ravel()
+    xb = orc.f32_to_bf16_bits(orc.gaussian((batch, in_f), 1.0, 1))
+    x = bf16_dev(xb)
+    parts = []
+    for r in range(tp):
+        layer = RowLinear.from_full_weight(out_f, in_f, torch.from_numpy(w), torch.from_numpy(b), tp=tp, rank=r, variant=variant)
+        assert (layer.bias is not None) == (r == 0)                                  # bias on rank 0 only
+        parts.append(layer.local_forward(x).float().cpu())
+    got = RowLinear.reduce_partials(parts).numpy()
+    ref = orc.ref_linear_f32(orc.bf16_bits_to_f32(xb), w, b)
+    scale = np.abs(ref).max()
+    tol = (4.0 if variant == "fp8" else 1.0) * MAX_REL * scale                       # E4M3 operands: 2^-4 relative steps, averaged over K
+    assert np.isfinite(got).all() and np.abs(got - ref).max() <= tol
+
+
+def _linear_rank(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from oracle import oracle as orc
+    from oxicuda_b200.dist_infer import ColumnLinear, RowLinear
+    in_f, mid, batch = 256, 512, 9
+    w1, w2 = orc.gaussian((mid, in_f), 0.05, 0), orc.gaussian((in_f, mid), 0.05, 2)
+    x = torch.from_numpy(orc.gaussian((batch, in_f), 1.0, 1)).to(torch.bfloat16).cuda()
+    col = ColumnLinear.from_full_weight(in_f, mid, torch.from_numpy(w1), None, tp=world, rank=rank, variant="bf16")
+    row = RowLinear.from_full_weight(in_f, mid, torch.from_numpy(w2), None, tp=world, rank=rank, variant="bf16")
+    h = col.forward(x)                                     # all-gather of the column shards
+    y = row.forward(h)                                     # slice, partial product, all-reduce
+    torch.cuda.synchronize()
+    xf = x.float().cpu().numpy()
+    h_ref = xf @ w1.T
+    y_ref = h_ref @ w2.T
+    q.put((rank, float(np.abs(h.float().cpu().numpy() - h_ref).max() / np.abs(h_ref).max()),
+           float(np.abs(y.float().cpu().numpy() - y_ref).max() / np.abs(y_ref).max())))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_column_then_row_linear_nccl_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_linear_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for _, eh, ey in res:
+        assert eh <= 1e-2 and ey <= 2e-2

@@ -92,3 +92,94 @@ def test_two_rank_gloo_all_reduce_matches_unsharded():
         assert p.exitcode == 0
     for _, err, scale in res:
         assert err <= 1e-5 * scale
+
+
+# ---- ColumnLinear / RowLinear host logic -----------------------------------------------------------
+
+def _shard_outputs_column(orc, x, w, b, tp):
+    """What each rank's ColumnLinear computes, with the product's shard indices and the oracle's f32 linear."""
+    outs = []
+    for r in range(tp):
+        rows = di.column_shard_rows(w.shape[0], tp, r)
+        outs.append(torch.from_numpy(orc.ref_linear_f32(x, w[rows], None if b is None else b[rows])))
+    return outs
+
+
+def test_column_linear_reference_cases(orc):  # crates/oxicuda-dist-infer/src/tensor_parallel/column_parallel.rs:224-290
+    w = np.eye(4, dtype=np.float32)
+    x = np.array([[1.0, 2.0, 3.0, 4.0]], np.float32)
+    out = di.ColumnLinear.gather_shards(4, 1, _shard_outputs_column(orc, x, w, None, 2))
+    assert out.tolist() == [[1.0, 2.0, 3.0, 4.0]]
+    out = di.ColumnLinear.gather_shards(4, 2, _shard_outputs_column(orc, np.ones((2, 2), np.float32), np.ones((4, 2), np.float32), None, 4))
+    assert out.tolist() == [[2.0] * 4, [2.0] * 4]
+    out = di.ColumnLinear.gather_shards(2, 1, _shard_outputs_column(orc, np.zeros((1, 2), np.float32), np.zeros((2, 2), np.float32),
+                                                                    np.array([10.0, 20.0], np.float32), 2))
+    assert out.tolist() == [[10.0, 20.0]]
+
+
+def test_linear_constructor_errors():  # column_parallel.rs:292-330, row_parallel.rs:109-168
+    from oxicuda_b200.errors import DistInferError
+    w = torch.zeros(4 * 2)
+    with pytest.raises(DistInferError) as e:
+        di.ColumnLinear.from_full_weight(2, 4, w, None, tp=3, rank=0)
+    assert e.value.variant == "TpFeaturesMisaligned"
+    with pytest.raises(DistInferError) as e:
+        di.ColumnLinear.from_full_weight(2, 4, torch.zeros(7), None, tp=2, rank=0)
+    assert e.value.variant == "DimensionMismatch"
+    with pytest.raises(DistInferError) as e:
+        di.ColumnLinear.from_full_weight(2, 4, w, torch.zeros(3), tp=2, rank=0)
+    assert e.value.variant == "DimensionMismatch"
+    with pytest.raises(DistInferError) as e:
+        di.RowLinear.from_full_weight(2, 4, w, None, tp=3, rank=0)
+    assert e.value.variant == "TpInputMisaligned"
+    with pytest.raises(DistInferError) as e:
+        di.RowLinear.from_full_weight(2, 4, torch.zeros(9), None, tp=2, rank=1)
+    assert e.value.variant == "DimensionMismatch"
+    with pytest.raises(DistInferError) as e:
+        di.ColumnLinear.gather_shards(4, 1, [])
+    assert e.value.variant == "TooFewRanks"
+    with pytest.raises(DistInferError) as e:
+        di.RowLinear.reduce_partials([])
+    assert e.value.variant == "TooFewRanks"
+    with pytest.raises(DistInferError) as e:
+        di.RowLinear.reduce_partials([torch.zeros(4), torch.zeros(5)])
+    assert e.value.variant == "DimensionMismatch"
+
+
+def test_row_linear_partials_sum_to_full(orc):  # row_parallel.rs: bias on rank 0 only, partials summed in rank order
+    x = orc.gaussian((3, 64), 1.0, 1)
+    w = orc.gaussian((16, 64), 0.1, 2)
+    b = orc.gaussian((1, 16), 1.0, 3).ravel()
+    parts = []
+    for r in range(4):
+        cols = di.row_shard_cols(64, 4, r)
+        parts.append(torch.from_numpy(orc.ref_linear_f32(np.ascontiguousarray(x[:, cols]), np.ascontiguousarray(w[:, cols]), b if r == 0 else None)))
+    full = orc.ref_linear_f32(x, w, b)
+    assert np.allclose(di.RowLinear.reduce_partials(parts).numpy(), full, rtol=1e-5, atol=1e-5)
+
+
+def _gather_main(rank, world, port, out_q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    local = torch.arange(6, dtype=torch.float32).reshape(2, 3) + 100 * rank          # [batch 2 x local_out 3]
+    full = di.gather_columns(local, world)
+    out_q.put((rank, full.tolist()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_gloo_column_gather_layout():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gather_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    want = [[0.0, 1.0, 2.0, 100.0, 101.0, 102.0], [3.0, 4.0, 5.0, 103.0, 104.0, 105.0]]
+    for _, full in res:
+        assert full == want

@@ -170,7 +170,7 @@ OXQ_API int32_t oxq_gemm_w8a32(oxq_handle* h, int64_t m, int64_t n, int64_t k, c
 /* W4A16 weight-only (Int4GemmConfig, int_ops.rs:215-355; quantized operand is the weight):
  * Y = bf16(X_bf16 . dequant(W)^T).  Three regimes, all reading the packed weight once per 32 batch rows or less:
  *   m <= 8           HBM-bound mma.sync decode kernel, split-K partial sums in the workspace;
- *   9 <= m <= 128    (group 128, k % 1024 == 0) tensor-core kernel with the dequantisation fused in: codes are
+ *   9 <= m <= 64     (group 128, k % 1024 == 0) tensor-core kernel with the dequantisation fused in: codes are
  *                    unpacked straight into tensor memory as the row operand of tcgen05.mma, per-group scales are
  *                    applied to the group's accumulator, partial K ranges are combined in the workspace;
  *                    other shapes with m <= 32 use the first kernel;

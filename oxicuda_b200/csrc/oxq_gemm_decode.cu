@@ -319,11 +319,12 @@ size_t oxq_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
 int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, const uint32_t* codes, const uint16_t* scales,
                        const uint32_t* zeros, int group, void* y, void* ws, size_t ws_bytes) {
     // Measured on B200 (14336 x 4096): the mma.sync kernel wins up to 8 batch rows (16-20 us against 21), the
-    // tensor-core kernel from there on (22-23 us for 9..32 rows against 30-61).  OXQ_W4A16_TC=0 never uses the
-    // tensor-core kernel, 2 uses it for every batch it supports (for A/B runs).
+    // tensor-core kernel from there on (22-23 us per pass of 32 rows against 30-61), and from 65 rows the
+    // dequantise-then-GEMM path (70 us whatever the batch) beats three or more passes.  OXQ_W4A16_TC=0 never uses
+    // the tensor-core kernel, 2 uses it for every batch it supports (for A/B runs).
     static int tc = -1;
     if (tc < 0) { const char* e = getenv("OXQ_W4A16_TC"); tc = e ? atoi(e) : 1; }
-    return w4a16_impl(h, m, n, k, x, codes, scales, zeros, group, y, ws, ws_bytes, tc >= 2 || (tc == 1 && m > 8));
+    return w4a16_impl(h, m, n, k, x, codes, scales, zeros, group, y, ws, ws_bytes, tc >= 2 || (tc == 1 && m > 8 && m <= 64));
 }
 
 }  // extern "C"

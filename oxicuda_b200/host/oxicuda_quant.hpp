@@ -9,6 +9,7 @@
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <utility>
 #include <vector>
 #include "../../include/oxq.h"
 
@@ -147,6 +148,92 @@ public:
     }
 private:
     int mode_;
+};
+
+// Nf4Quantizer (crates/oxicuda-quant/src/scheme/nf4.rs:56-172): blocks of `block_size` elements share an absmax.
+class Nf4Quantizer {
+public:
+    explicit Nf4Quantizer(size_t block_size = 64) : block_size(block_size) {
+        if (block_size == 0) throw std::invalid_argument("block_size must be > 0");          // the reference panics
+    }
+    size_t block_size;
+    // (packed bytes, per-block absmax)
+    std::pair<std::vector<uint8_t>, std::vector<float>> encode(const std::vector<float>& tensor) const {
+        if (tensor.empty()) throw QuantError("EmptyInput", "Nf4Quantizer::encode");
+        if (tensor.size() % block_size != 0) throw QuantError("GroupSizeMismatch", "length is not a multiple of the block size");
+        detail::Handle h;
+        detail::DevBuf<float> x(tensor.size()), am(tensor.size() / block_size);
+        detail::DevBuf<uint8_t> packed(tensor.size() / 2);
+        x.upload(tensor.data());
+        detail::check(oxq_nf4_quant(h.h, x.p, (int64_t)tensor.size(), (int64_t)block_size, packed.p, am.p), h.h);
+        detail::cuda(cudaDeviceSynchronize());
+        std::pair<std::vector<uint8_t>, std::vector<float>> out{std::vector<uint8_t>(tensor.size() / 2), std::vector<float>(tensor.size() / block_size)};
+        packed.download(out.first.data());
+        am.download(out.second.data());
+        return out;
+    }
+    std::vector<float> decode(const std::vector<uint8_t>& packed, const std::vector<float>& absmaxs) const {
+        const size_t n = packed.size() * 2;
+        if (absmaxs.size() != n / block_size) throw QuantError("DimensionMismatch", "absmax count does not match the packed length");
+        if (n == 0) return {};
+        detail::Handle h;
+        detail::DevBuf<uint8_t> p(packed.size());
+        detail::DevBuf<float> am(absmaxs.size()), y(n);
+        p.upload(packed.data()); am.upload(absmaxs.data());
+        detail::check(oxq_nf4_dequant(h.h, p.p, am.p, (int64_t)n, (int64_t)block_size, y.p, OXQ_F32), h.h);
+        detail::cuda(cudaDeviceSynchronize());
+        std::vector<float> out(n);
+        y.download(out.data());
+        return out;
+    }
+    float quantization_mse(const std::vector<float>& tensor) const {
+        auto enc = encode(tensor);
+        std::vector<float> dec = decode(enc.first, enc.second);
+        double acc = 0.0;
+        for (size_t i = 0; i < tensor.size(); i++) acc += (double)(tensor[i] - dec[i]) * (double)(tensor[i] - dec[i]);
+        return (float)(acc / (double)tensor.size());
+    }
+};
+
+// BlockQuantizedInt8 (crates/oxicuda-dnn/src/quantize/int8_quantize.rs:387-471).
+struct BlockQuantizedInt8 {
+    std::vector<int8_t> data;
+    std::vector<float> scales;
+    size_t block_size = 0, orig_len = 0;
+    static BlockQuantizedInt8 quantize(const std::vector<float>& input, size_t block_size) {
+        if (block_size == 0) throw std::invalid_argument("block_size must be > 0");
+        BlockQuantizedInt8 r;
+        r.block_size = block_size; r.orig_len = input.size();
+        r.data.resize(input.size());
+        r.scales.resize((input.size() + block_size - 1) / block_size);
+        if (input.empty()) return r;
+        detail::Handle h;
+        detail::DevBuf<float> x(input.size()), s(r.scales.size());
+        detail::DevBuf<int8_t> q(input.size());
+        x.upload(input.data());
+        detail::check(oxq_int8_block_quant(h.h, x.p, (int64_t)input.size(), (int64_t)block_size, q.p, s.p), h.h);
+        detail::cuda(cudaDeviceSynchronize());
+        q.download(r.data.data());
+        s.download(r.scales.data());
+        return r;
+    }
+    std::vector<float> dequantize() const {
+        std::vector<float> out(orig_len);
+        if (orig_len == 0) return out;
+        detail::Handle h;
+        detail::DevBuf<int8_t> q(orig_len);
+        detail::DevBuf<float> s(scales.size()), y(orig_len);
+        q.upload(data.data()); s.upload(scales.data());
+        detail::check(oxq_int8_block_dequant(h.h, q.p, s.p, (int64_t)orig_len, (int64_t)block_size, y.p), h.h);
+        detail::cuda(cudaDeviceSynchronize());
+        y.download(out.data());
+        return out;
+    }
+    size_t num_blocks() const { return scales.size(); }
+    float compression_ratio() const {
+        const size_t qb = data.size() + scales.size() * 4;
+        return qb == 0 ? 1.0f : (float)(orig_len * 4) / (float)qb;
+    }
 };
 
 }  // namespace oxicuda_quant

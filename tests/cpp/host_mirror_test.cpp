@@ -1,5 +1,6 @@
 // Drives the C++ host mirror (oxicuda_quant.hpp / oxicuda_blas.hpp) on a GPU and prints results that the Python
 // test compares with the oracle.  Usage: host_mirror_test <out.bin>; exit code 0 on success.
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <vector>
@@ -41,6 +42,36 @@ int main(int argc, char** argv) {
         int berr = 0;
         try { oxicuda_blas::gemm_fp8(bh, a, b, nullptr, nullptr, cm); } catch (const oxicuda_blas::BlasError& e) { berr = e.variant == "InvalidDimension"; }
         if (!berr) return 8;
+        // Nf4Quantizer: the reference's round-trip, all-zero and error tests (nf4.rs:243-310)
+        {
+            Nf4Quantizer nq(64);
+            std::vector<float> ramp(128);
+            for (int i = 0; i < 128; i++) ramp[i] = (float)i / 64.0f - 1.0f;
+            auto enc = nq.encode(ramp);
+            if (enc.first.size() != 64 || enc.second.size() != 2) return 10;
+            if (!(nq.quantization_mse(ramp) < 0.01f)) return 11;
+            auto z = Nf4Quantizer().encode(std::vector<float>(64, 0.0f));
+            for (uint8_t b : z.first) if (b != 0x77) return 12;
+            int nerr = 0;
+            try { nq.encode(std::vector<float>(65, 0.5f)); } catch (const QuantError& e) { nerr += e.variant == "GroupSizeMismatch"; }
+            try { nq.decode(std::vector<uint8_t>(32, 0), std::vector<float>(5, 1.0f)); } catch (const QuantError& e) { nerr += e.variant == "DimensionMismatch"; }
+            try { nq.encode({}); } catch (const QuantError& e) { nerr += e.variant == "EmptyInput"; }
+            if (nerr != 3) return 13;
+        }
+        // BlockQuantizedInt8: block counts, ragged tail, saturation (int8_quantize.rs:541-577)
+        {
+            std::vector<float> in(100);
+            for (int i = 0; i < 100; i++) in[i] = (float)i;
+            BlockQuantizedInt8 bq = BlockQuantizedInt8::quantize(in, 64);
+            if (bq.num_blocks() != 2 || bq.dequantize().size() != 100) return 14;
+            BlockQuantizedInt8 sat = BlockQuantizedInt8::quantize({1e30f, -1e30f, 0.0f, 1e30f}, 4);
+            std::vector<float> d = sat.dequantize();
+            if (!(d[0] > 0.0f && d[1] < 0.0f && d[2] == 0.0f) || sat.data[0] != 127 || sat.data[1] != -127) return 15;
+            BlockQuantizedInt8 known;
+            known.data = {-128, 0, 127}; known.scales = {0.1f}; known.block_size = 3; known.orig_len = 3;
+            std::vector<float> kd = known.dequantize();
+            if (std::fabs(kd[0] + 12.8f) > 1e-4f || kd[1] != 0.0f || std::fabs(kd[2] - 12.7f) > 1e-4f) return 16;
+        }
         FILE* f = fopen(argv[1], "wb");
         if (!f) return 9;
         fwrite(big.data(), sizeof(float), big.size(), f);

@@ -214,6 +214,14 @@ OXQ_API int32_t oxq_int8_block_dequant(oxq_handle* h, const int8_t* q_dev, const
 OXQ_API int32_t oxq_nf4_quant(oxq_handle* h, const float* x_dev, int64_t n, int64_t block, uint8_t* packed_dev, float* absmax_dev);
 OXQ_API int32_t oxq_nf4_dequant(oxq_handle* h, const uint8_t* packed_dev, const float* absmax_dev, int64_t n, int64_t block,
                                 void* y_dev, int y_dtype);
+/* SmoothQuantMigrator (crates/oxicuda-quant/src/scheme/smooth_quant.rs) on device buffers, f32 row-major:
+ *   oxq_smooth_col_absmax  compute_act_stats / compute_weight_stats (:125-196): stats[j] = max_r |x[r, j]|;
+ *   oxq_smooth_scales      compute_migration_scales (:84-113): s_j = max(|a_j|,1e-8)^alpha / max(|w_j|,1e-8)^(1-alpha);
+ *   oxq_smooth_apply       divide != 0: smooth_activations (:198-222), x[r, j] /= max(s_j, 1e-12);
+ *                          divide == 0: smooth_weights (:231-254), x[r, j] *= s_j.  In place. */
+OXQ_API int32_t oxq_smooth_col_absmax(oxq_handle* h, const float* x_dev, int64_t rows, int64_t cols, float* stats_dev);
+OXQ_API int32_t oxq_smooth_scales(oxq_handle* h, const float* act_max_dev, const float* weight_max_dev, int64_t n, float alpha, float* scales_dev);
+OXQ_API int32_t oxq_smooth_apply(oxq_handle* h, float* x_dev, int64_t rows, int64_t cols, const float* scales_dev, int divide);
 /* y[m, n] += bias[n] on a bf16 matrix (the bias term of ColumnLinearShard::forward / RowLinearShard::forward_partial,
  * crates/oxicuda-dist-infer/src/tensor_parallel/column_parallel.rs:77-95, row_parallel.rs:67-90); n and ldy multiples of 8. */
 OXQ_API int32_t oxq_bias_add_bf16(oxq_handle* h, void* y_bf16_dev, int64_t ldy, const float* bias_dev, int64_t m, int64_t n);

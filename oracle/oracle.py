@@ -68,6 +68,7 @@ def lib():
         _lib.orc_f32_to_f16.argtypes = [C.c_float]
         _lib.orc_f32_to_bf16.argtypes = [C.c_float]
         _lib.orc_nf4_level.restype = C.c_float
+        _lib.orc_ref_smooth_scales.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_void_p]
         _lib.orc_ref_nearest_nf4.argtypes = [C.c_float]
         _lib.orc_ref_dnn_int8_dequant.argtypes = [C.c_void_p, C.c_size_t, C.c_float, C.c_void_p]
     return _lib
@@ -312,6 +313,50 @@ def ref_dnn_int8_dequant(q, scale):
     out = np.zeros(q.size, np.float32)
     lib().orc_ref_dnn_int8_dequant(_p(q), _sz(q.size), C.c_float(float(scale)), _p(out))
     return out
+
+
+def ref_smooth_col_absmax(x):
+    """compute_act_stats / compute_weight_stats: per-column max |x| of a [rows x cols] matrix."""
+    x = _c(x, np.float32)
+    if x.size == 0:
+        raise OracleError(1)
+    rows, cols = x.shape
+    st = np.zeros(cols, np.float32)
+    lib().orc_ref_smooth_col_absmax(_p(x), _sz(rows), _sz(cols), _p(st))
+    return st
+
+
+def ref_smooth_scales(act_max, weight_max, alpha):
+    a, w = _c(act_max, np.float32).ravel(), _c(weight_max, np.float32).ravel()
+    if a.size == 0:
+        raise OracleError(1)
+    if a.size != w.size:
+        raise OracleError(4)
+    out = np.zeros(a.size, np.float32)
+    lib().orc_ref_smooth_scales(_p(a), _p(w), _sz(a.size), C.c_float(alpha), _p(out))
+    return out
+
+
+def ref_smooth_activations(x, scales):
+    x = _c(x, np.float32).copy()
+    if scales.size != x.shape[1]:
+        raise OracleError(4)
+    lib().orc_ref_smooth_activations(_p(x), _p(_c(scales, np.float32)), _sz(x.shape[0]), _sz(x.shape[1]))
+    return x
+
+
+def ref_smooth_weights(w, scales):
+    w = _c(w, np.float32).copy()
+    if scales.size != w.shape[1]:
+        raise OracleError(4)
+    lib().orc_ref_smooth_weights(_p(w), _p(_c(scales, np.float32)), _sz(w.shape[0]), _sz(w.shape[1]))
+    return w
+
+
+def ref_smooth_layer(acts, weights, alpha):
+    """SmoothQuantMigrator::smooth_layer: (smoothed acts, smoothed weights, scales)."""
+    sc = ref_smooth_scales(ref_smooth_col_absmax(acts), ref_smooth_col_absmax(weights), alpha)
+    return ref_smooth_activations(acts, sc), ref_smooth_weights(weights, sc), sc
 
 
 # --------------------------------------------------------------------------- spec quantizers

@@ -678,6 +678,39 @@ void orc_ref_dnn_int8_dequant(const int8_t* q, size_t n, float scale, float* out
     for (size_t i = 0; i < n; i++) out[i] = (float)q[i] * scale;
 }
 
+/* SmoothQuantMigrator (crates/oxicuda-quant/src/scheme/smooth_quant.rs).  compute_act_stats / compute_weight_stats
+ * (:125-196): per-column maximum of |x| over the rows of a row-major [rows x cols] matrix. */
+int orc_ref_smooth_col_absmax(const float* x, size_t rows, size_t cols, float* stats) {
+    if (rows * cols == 0) return -1;
+    for (size_t j = 0; j < cols; j++) stats[j] = 0.0f;
+    for (size_t t = 0; t < rows; t++)
+        for (size_t j = 0; j < cols; j++) {
+            float v = fabsf(x[t * cols + j]);
+            if (v > stats[j]) stats[j] = v;
+        }
+    return 0;
+}
+
+/* compute_migration_scales (:84-113): s_j = max(|a_j|, 1e-8)^alpha / max(|w_j|, 1e-8)^(1 - alpha). */
+int orc_ref_smooth_scales(const float* act_max, const float* weight_max, size_t n, float alpha, float* scales) {
+    if (n == 0) return -1;
+    for (size_t j = 0; j < n; j++) {
+        float a = fmaxf(fabsf(act_max[j]), 1e-8f), w = fmaxf(fabsf(weight_max[j]), 1e-8f);
+        scales[j] = powf(a, alpha) / powf(w, 1.0f - alpha);
+    }
+    return 0;
+}
+
+/* smooth_activations (:198-222): x[t, j] /= max(s_j, 1e-12); smooth_weights (:231-254): w[r, j] *= s_j. */
+void orc_ref_smooth_activations(float* x, const float* scales, size_t rows, size_t cols) {
+    for (size_t t = 0; t < rows; t++)
+        for (size_t j = 0; j < cols; j++) x[t * cols + j] /= fmaxf(scales[j], 1e-12f);
+}
+void orc_ref_smooth_weights(float* w, const float* scales, size_t rows, size_t cols) {
+    for (size_t r = 0; r < rows; r++)
+        for (size_t j = 0; j < cols; j++) w[r * cols + j] *= scales[j];
+}
+
 /* ------------------------------------------------------------------------- */
 
 /* Y[b,o] = bias[o] + sum_i X[b,i] * W[o,i], accumulated left to right in f32

@@ -41,6 +41,9 @@ SIGNATURES = {
     "oxq_int8_block_dequant": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp]),
     "oxq_nf4_quant": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
     "oxq_nf4_dequant": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp, _int]),
+    "oxq_smooth_col_absmax": (_i32, [_vp, _vp, _i64, _i64, _vp]),
+    "oxq_smooth_scales": (_i32, [_vp, _vp, _vp, _i64, C.c_float, _vp]),
+    "oxq_smooth_apply": (_i32, [_vp, _vp, _i64, _i64, _vp, _int]),
     "oxq_bias_add_bf16": (_i32, [_vp, _vp, _i64, _vp, _i64, _i64]),
     "oxq_gemm_fp8": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64]),
     "oxq_gemm_fp8_swiglu": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64]),

@@ -190,6 +190,67 @@ __global__ void __launch_bounds__(256) nf4_dequant_kernel(const uint8_t* __restr
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// SmoothQuant migration (per-channel scale folded from the activations into the weights)
+// ------------------------------------------------------------------------------------------------
+
+// Per-column max |x| of a row-major [rows x cols] f32 matrix: a thread owns four columns, a CTA row covers 1024
+// columns, CTAs along y split the rows; the partial maxima meet in `stats` (zero on entry) through integer
+// atomicMax on the bit patterns of the non-negative floats.
+__global__ void __launch_bounds__(256) col_absmax_kernel(const float* __restrict__ x, int64_t rows, int64_t cols, float* __restrict__ stats) {
+    const int64_t c = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
+    if (c >= cols) return;
+    float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c + 4 <= cols && ((cols & 3) == 0)) {
+        for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(x + r * cols + c));
+            m.x = fmaxf(m.x, fabsf(v.x)); m.y = fmaxf(m.y, fabsf(v.y)); m.z = fmaxf(m.z, fabsf(v.z)); m.w = fmaxf(m.w, fabsf(v.w));
+        }
+    } else {
+        float* mm = &m.x;
+        for (int64_t r = blockIdx.y; r < rows; r += gridDim.y)
+            for (int e = 0; e < 4 && c + e < cols; e++) mm[e] = fmaxf(mm[e], fabsf(x[r * cols + c + e]));
+    }
+    const float mv[4] = {m.x, m.y, m.z, m.w};
+    for (int e = 0; e < 4 && c + e < cols; e++)
+        if (mv[e] > 0.0f) atomicMax(reinterpret_cast<int*>(stats) + c + e, __float_as_int(mv[e]));
+}
+
+// s_j = max(|a_j|, 1e-8)^alpha / max(|w_j|, 1e-8)^(1 - alpha)
+__global__ void __launch_bounds__(256) smooth_scales_kernel(const float* __restrict__ a, const float* __restrict__ w, int64_t n, float alpha,
+                                                            float* __restrict__ s) {
+    const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    const float av = fmaxf(fabsf(a[j]), 1e-8f), wv = fmaxf(fabsf(w[j]), 1e-8f);
+    s[j] = __fdiv_rn(powf(av, alpha), powf(wv, 1.0f - alpha));
+}
+
+// DIVIDE: x[r, j] /= max(s_j, 1e-12) (activations); otherwise x[r, j] *= s_j (weights).  In place.
+template <bool DIVIDE>
+__global__ void __launch_bounds__(256) smooth_apply_kernel(float* __restrict__ x, int64_t rows, int64_t cols, const float* __restrict__ s) {
+    const int64_t total = rows * cols;
+    if ((cols & 3) == 0) {
+        const int64_t nvec = total >> 2, cv = cols >> 2;
+        for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
+            const int64_t j = (v % cv) << 2;
+            float4 d = *reinterpret_cast<float4*>(x + (v << 2));
+            const float4 sc = __ldg(reinterpret_cast<const float4*>(s + j));
+            if (DIVIDE) {
+                d.x = __fdiv_rn(d.x, fmaxf(sc.x, 1e-12f)); d.y = __fdiv_rn(d.y, fmaxf(sc.y, 1e-12f));
+                d.z = __fdiv_rn(d.z, fmaxf(sc.z, 1e-12f)); d.w = __fdiv_rn(d.w, fmaxf(sc.w, 1e-12f));
+            } else {
+                d.x *= sc.x; d.y *= sc.y; d.z *= sc.z; d.w *= sc.w;
+            }
+            *reinterpret_cast<float4*>(x + (v << 2)) = d;
+        }
+    } else {
+        for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+            const float sc = s[i % cols];
+            x[i] = DIVIDE ? __fdiv_rn(x[i], fmaxf(sc, 1e-12f)) : x[i] * sc;
+        }
+    }
+}
+
 // y[m, n] += bias[n] on a bf16 matrix with leading dimension ldy (f32 add, one rounding); 8 columns per thread.
 __global__ void __launch_bounds__(256) bias_add_bf16_kernel(__nv_bfloat16* __restrict__ y, int64_t ldy, const float* __restrict__ bias,
                                                             int64_t m, int64_t n) {
@@ -279,6 +340,43 @@ int32_t oxq_int8_block_dequant(oxq_handle* h, const int8_t* q, const float* scal
     if (!q || !scales || !y) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     int8_block_dequant_kernel<<<grid_cap(h, n, 256, 16), 256, 0, h->stream>>>(q, scales, n, block, y);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_smooth_col_absmax(oxq_handle* h, const float* x, int64_t rows, int64_t cols, float* stats) {
+    OXQ_CHECK_HANDLE(h);
+    if (rows <= 0 || cols <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "compute_act_stats: empty input");
+    if (!x || !stats || !aligned16(x)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    OXQ_CUDA(h, cudaMemsetAsync(stats, 0, (size_t)cols * sizeof(float), h->stream));
+    const int64_t gx = (cols + 1023) / 1024;
+    int64_t gy = ((int64_t)h->sm_count * 8 + gx - 1) / gx;
+    if (gy > rows) gy = rows;
+    if (gy > 65535) gy = 65535;
+    col_absmax_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, h->stream>>>(x, rows, cols, stats);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_smooth_scales(oxq_handle* h, const float* act_max, const float* weight_max, int64_t n, float alpha, float* scales) {
+    OXQ_CHECK_HANDLE(h);
+    if (n <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "SmoothQuantMigrator::compute_migration_scales");
+    if (!act_max || !weight_max || !scales) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    smooth_scales_kernel<<<(unsigned)((n + 255) / 256), 256, 0, h->stream>>>(act_max, weight_max, n, alpha, scales);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_smooth_apply(oxq_handle* h, float* x, int64_t rows, int64_t cols, const float* scales, int divide) {
+    OXQ_CHECK_HANDLE(h);
+    if (rows <= 0 || cols <= 0) OXQ_FAIL(h, OXQ_ERR_QUANT_DIMENSION_MISMATCH, "smooth: empty matrix");
+    if (!x || !scales || !aligned16(x) || !aligned16(scales)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    const int grid = grid_cap(h, rows * cols / 4 + 1, 256, 8);
+    if (divide) smooth_apply_kernel<true><<<grid, 256, 0, h->stream>>>(x, rows, cols, scales);
+    else smooth_apply_kernel<false><<<grid, 256, 0, h->stream>>>(x, rows, cols, scales);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

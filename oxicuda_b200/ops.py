@@ -263,6 +263,62 @@ def nf4_dequant(packed: torch.Tensor, absmaxs: torch.Tensor, block: int = 64, dt
     return y
 
 
+class SmoothQuantMigrator:
+    """SmoothQuantMigrator of the reference (crates/oxicuda-quant/src/scheme/smooth_quant.rs:54-293) on device tensors."""
+
+    def __init__(self, alpha: float = 0.5):
+        self.alpha = float(alpha)
+
+    @staticmethod
+    def _col_absmax(x: torch.Tensor) -> torch.Tensor:
+        _chk(x, torch.float32)
+        if x.dim() != 2:
+            from .errors import QuantError
+            raise QuantError("DimensionMismatch", f"expected a matrix, got {tuple(x.shape)}", 4)
+        st = torch.empty(max(x.shape[1], 1), dtype=torch.float32, device=x.device)
+        handle(x.device.index).call("oxq_smooth_col_absmax", _p(x), x.shape[0], x.shape[1], _p(st))
+        return st[: x.shape[1]]
+
+    compute_act_stats = _col_absmax
+    compute_weight_stats = _col_absmax
+
+    def compute_migration_scales(self, act_max: torch.Tensor, weight_max: torch.Tensor) -> torch.Tensor:
+        from .errors import QuantError
+        if act_max.numel() == 0:
+            raise QuantError("EmptyInput", "SmoothQuantMigrator::compute_migration_scales", 1)
+        if act_max.numel() != weight_max.numel():
+            raise QuantError("DimensionMismatch", f"expected {act_max.numel()}, got {weight_max.numel()}", 4)
+        sc = torch.empty_like(act_max)
+        handle(act_max.device.index).call("oxq_smooth_scales", _p(act_max), _p(weight_max), act_max.numel(), C.c_float(self.alpha), _p(sc))
+        return sc
+
+    @staticmethod
+    def _apply(x: torch.Tensor, scales: torch.Tensor, divide: bool):
+        from .errors import QuantError
+        _chk(x, torch.float32)
+        if x.dim() != 2 or scales.numel() != x.shape[1]:
+            raise QuantError("DimensionMismatch", f"expected {x.shape[-1]} scales, got {scales.numel()}", 4)
+        handle(x.device.index).call("oxq_smooth_apply", _p(x), x.shape[0], x.shape[1], _p(scales), 1 if divide else 0)
+        return x
+
+    @staticmethod
+    def smooth_activations(acts: torch.Tensor, scales: torch.Tensor):
+        """In place acts[t, j] /= max(scales[j], 1e-12)."""
+        return SmoothQuantMigrator._apply(acts, scales, True)
+
+    @staticmethod
+    def smooth_weights(weights: torch.Tensor, scales: torch.Tensor):
+        """In place weights[r, j] *= scales[j]."""
+        return SmoothQuantMigrator._apply(weights, scales, False)
+
+    def smooth_layer(self, acts: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """Smooths both matrices in place and returns the per-channel scales (smooth_quant.rs:274-293)."""
+        sc = self.compute_migration_scales(self.compute_act_stats(acts), self.compute_weight_stats(weights))
+        self.smooth_activations(acts, sc)
+        self.smooth_weights(weights, sc)
+        return sc
+
+
 def bias_add_(y: torch.Tensor, bias: torch.Tensor):
     """In place y[m, n] += bias[n] (bf16 matrix, f32 bias)."""
     _chk(bias, torch.float32)

@@ -114,3 +114,57 @@ def test_nf4_reference_cases(ops, orc):  # crates/oxicuda-quant/src/scheme/nf4.r
     with pytest.raises(QuantError) as e:
         ops.nf4_quant(torch.empty(0, device="cuda"), 64)
     assert e.value.variant == "EmptyInput"
+
+
+# ---- SmoothQuant migration --------------------------------------------------------------------------
+
+def _ulp_diff(a, b):
+    return np.abs(a.view(np.int32).astype(np.int64) - b.view(np.int32).astype(np.int64))
+
+
+@pytest.mark.parametrize("shape", [(3, 4, 2), (512, 1024, 256), (100, 1030, 77), (2048, 4096, 4096)])
+@pytest.mark.parametrize("alpha", [0.5, 0.8])
+def test_smooth_quant_layer(ops, orc, shape, alpha):
+    n_tok, n_ch, n_out = shape
+    acts = orc.gaussian((n_tok, n_ch), 1.0, 1)
+    acts[:, ::17] *= 40.0                                             # outlier channels
+    w = orc.gaussian((n_out, n_ch), 0.05, 2)
+    mig = ops.SmoothQuantMigrator(alpha)
+    a_d, w_d = to_dev(acts.copy()), to_dev(w.copy())
+    st_a, st_w = mig.compute_act_stats(a_d), mig.compute_weight_stats(w_d)
+    assert (st_a.cpu().numpy() == orc.ref_smooth_col_absmax(acts)).all()                 # bit-exact
+    assert (st_w.cpu().numpy() == orc.ref_smooth_col_absmax(w)).all()
+    sc = mig.compute_migration_scales(st_a, st_w)
+    sc_ref = orc.ref_smooth_scales(orc.ref_smooth_col_absmax(acts), orc.ref_smooth_col_absmax(w), alpha)
+    assert _ulp_diff(sc.cpu().numpy(), sc_ref).max() <= 4                                 # two powf and a division: a few ulp between libms
+    # with the same scales the smoothed matrices are bit-exact (one IEEE division / multiplication per element)
+    sc_h = sc.cpu().numpy()
+    mig.smooth_activations(a_d, sc)
+    mig.smooth_weights(w_d, sc)
+    assert (a_d.cpu().numpy() == orc.ref_smooth_activations(acts, sc_h)).all()
+    assert (w_d.cpu().numpy() == orc.ref_smooth_weights(w, sc_h)).all()
+    if n_tok * n_out <= 512 * 256:                                                        # the layer output is preserved
+        y0 = acts.astype(np.float64) @ w.astype(np.float64).T
+        y1 = a_d.cpu().numpy().astype(np.float64) @ w_d.cpu().numpy().astype(np.float64).T
+        assert np.abs(y0 - y1).max() <= 1e-4 * np.abs(y0).max()
+
+
+def test_smooth_quant_reference_cases(ops, orc):  # crates/oxicuda-quant/src/scheme/smooth_quant.rs:311-440
+    from oxicuda_b200.errors import QuantError
+    dev = lambda v: to_dev(np.array(v, np.float32))  # noqa: E731
+    assert np.allclose(ops.SmoothQuantMigrator(0.5).compute_migration_scales(dev([4.0, 1.0, 9.0]), dev([1.0, 4.0, 1.0])).cpu().numpy(), [2.0, 0.5, 3.0], atol=1e-5)
+    assert np.allclose(ops.SmoothQuantMigrator(1.0).compute_migration_scales(dev([2.0, 5.0]), dev([3.0, 7.0])).cpu().numpy(), [2.0, 5.0], atol=1e-5)
+    assert np.allclose(ops.SmoothQuantMigrator(0.0).compute_migration_scales(dev([4.0, 1.0]), dev([2.0, 5.0])).cpu().numpy(), [0.5, 0.2], atol=1e-5)
+    assert ops.SmoothQuantMigrator.compute_act_stats(dev([[1.0, -5.0, 2.0], [-3.0, 4.0, 1.0]])).cpu().tolist() == [3.0, 5.0, 2.0]
+    assert ops.SmoothQuantMigrator.compute_weight_stats(dev([[0.5, -2.0, 1.0], [-1.5, 0.3, 3.0]])).cpu().tolist() == [1.5, 2.0, 3.0]
+    with pytest.raises(QuantError) as e:
+        ops.SmoothQuantMigrator(0.5).compute_migration_scales(dev([1.0] * 3), dev([1.0] * 4))
+    assert e.value.variant == "DimensionMismatch"
+    with pytest.raises(QuantError) as e:
+        ops.SmoothQuantMigrator(0.5).compute_migration_scales(torch.empty(0, device="cuda"), torch.empty(0, device="cuda"))
+    assert e.value.variant == "EmptyInput"
+    acts = dev([[100.0, 1.0], [-100.0, 1.0], [100.0, -1.0], [-100.0, -1.0]])
+    w = dev([[0.5, 0.5], [-0.5, 0.5]])
+    sc = ops.SmoothQuantMigrator(0.5).smooth_layer(acts, w)
+    a = acts.cpu().numpy()
+    assert np.abs(a[:, 0]).max() / np.abs(a[:, 1]).max() < 100.0 and sc[0].item() > 1.0

@@ -283,3 +283,25 @@ def test_dnn_int8_tensor_definition(orc):  # int8_quantize.rs:26-29 (the formula
     q0, s0 = orc.ref_dnn_int8_quant(np.zeros(4, np.float32))
     assert s0[0] == np.float32(1e-12) and (q0 == 0).all()
     assert np.allclose(orc.ref_dnn_int8_dequant(q, s[0]), q.astype(np.float32) * s[0])
+
+
+def test_smooth_quant_kats(orc):  # crates/oxicuda-quant/src/scheme/smooth_quant.rs:311-440
+    assert np.allclose(orc.ref_smooth_scales([4.0, 1.0, 9.0], [1.0, 4.0, 1.0], 0.5), [2.0, 0.5, 3.0], atol=1e-5)
+    assert np.allclose(orc.ref_smooth_scales([2.0, 5.0], [3.0, 7.0], 1.0), [2.0, 5.0], atol=1e-5)
+    assert np.allclose(orc.ref_smooth_scales([4.0, 1.0], [2.0, 5.0], 0.0), [0.5, 0.2], atol=1e-5)
+    assert np.allclose(orc.ref_smooth_col_absmax(np.array([[1.0, -5.0, 2.0], [-3.0, 4.0, 1.0]], np.float32)), [3.0, 5.0, 2.0])
+    assert np.allclose(orc.ref_smooth_col_absmax(np.array([[0.5, -2.0, 1.0], [-1.5, 0.3, 3.0]], np.float32)), [1.5, 2.0, 3.0])
+    acts = (np.arange(12, dtype=np.float32) * np.float32(0.3) - np.float32(1.0)).reshape(3, 4)
+    w = (np.arange(8, dtype=np.float32) * np.float32(0.2) - np.float32(0.5)).reshape(2, 4)
+    a2, w2, _ = orc.ref_smooth_layer(acts, w, 0.5)
+    assert np.allclose(acts @ w.T, a2 @ w2.T, atol=1e-4)                       # smoothing preserves the layer output
+    acts = np.array([100.0, 1.0, -100.0, 1.0, 100.0, -1.0, -100.0, -1.0], np.float32).reshape(4, 2)
+    w = np.array([0.5, 0.5, -0.5, 0.5], np.float32).reshape(2, 2)
+    a2, _, sc = orc.ref_smooth_layer(acts, w, 0.5)
+    assert np.abs(a2[:, 0]).max() / np.abs(a2[:, 1]).max() < 100.0 and sc[0] > 1.0
+    with pytest.raises(orc.OracleError) as e:
+        orc.ref_smooth_scales(np.ones(3, np.float32), np.ones(4, np.float32), 0.5)
+    assert e.value.name == "DimensionMismatch"
+    with pytest.raises(orc.OracleError) as e:
+        orc.ref_smooth_scales(np.zeros(0, np.float32), np.zeros(0, np.float32), 0.5)
+    assert e.value.name == "EmptyInput"

@@ -218,6 +218,11 @@ def extras(torch, ops, peaks):
     stats = torch.empty(2, device="cuda")
     am = torch.empty(1, device="cuda")
     rec("absmax_bf16_8192x8192", 134217728, ring_time(torch, lambda r: ops.absmax(r, out=am), ring))
+    # what a plain streaming kernel reaches at the byte counts of the decode weights (the launch costs about 4 us
+    # whatever it reads): the practical ceiling next to which the decode GEMM lines below should be read
+    for nbytes in (8388608, 29360128):
+        small = [ring[i % 3].view(-1)[(i // 3) * (nbytes // 2):(i // 3 + 1) * (nbytes // 2)] for i in range(12)]
+        rec(f"stream_floor_absmax_{nbytes // 1048576}MiB", nbytes, ring_time(torch, lambda r: ops.absmax(r, out=am), small))
     one = torch.ones(1, device="cuda")
     rec("fp8_quant_bf16_8192x8192", 201326592, ring_time(torch, lambda r: ops.fp8_quant(r, one, out=outq), ring))
     rec("fp8_quant_dynamic_bf16_8192x8192", 335544320, ring_time(torch, lambda r: ops.fp8_quant_dynamic(r, out=outq, stats=stats), ring), 2)

@@ -169,11 +169,11 @@ OXQ_API int32_t oxq_gemm_w8a32(oxq_handle* h, int64_t m, int64_t n, int64_t k, c
                        const int8_t* w_dev, const float* sw_rows_dev, float* y_dev);
 /* W4A16 weight-only (Int4GemmConfig, int_ops.rs:215-355; quantized operand is the weight):
  * Y = bf16(X_bf16 . dequant(W)^T).  Three regimes, all reading the packed weight once per 32 batch rows or less:
- *   m <= 8           HBM-bound mma.sync decode kernel, split-K partial sums in the workspace;
+ *   m <= 8           HBM-bound mma.sync kernel, one CTA per 16 weight rows over the whole K (no workspace traffic);
  *   9 <= m <= 64     (group 128, k % 1024 == 0) tensor-core kernel with the dequantisation fused in: codes are
  *                    unpacked straight into tensor memory as the row operand of tcgen05.mma, per-group scales are
  *                    applied to the group's accumulator, partial K ranges are combined in the workspace;
- *                    other shapes with m <= 32 use the first kernel;
+ *                    other shapes with m <= 32 use a split-K mma.sync kernel (partial sums in the workspace);
  *   otherwise        the weight is dequantised to bf16 in the workspace and the bf16 tensor-core GEMM runs
  *                    (n % 8 == 0).
  * For m <= 32 the workspace must be zero-filled before its first use and is left zero-filled by every call; above

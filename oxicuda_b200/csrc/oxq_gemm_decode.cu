@@ -1,11 +1,12 @@
 // Decode-shaped (M <= 32) quantized GEMMs.  These are HBM-bound: the weight matrix is streamed once
-// with 128-bit loads, unpacked in registers, and multiplied against an activation tile that lives in
-// shared memory.
+// with 128-bit loads, unpacked in registers, and multiplied with mma.sync.
 //
 //   W4A16: uint4 codes -> bf16 in registers with the (0x4300 | nibble) trick, mma.sync m16n8k16 with the
 //          weights as the row operand, per-group f32 scale and zero-point applied to the group's partial
-//          sum.  Split along K across CTAs; partial sums are combined with f32 atomics in a
-//          caller-provided workspace that the last CTA of each row block drains.
+//          sum.  Two kernels: w4a16_gemv_kernel (up to 8 batch rows: a CTA owns 16 weight rows over the
+//          whole K, activations read from L1, nothing combined across CTAs) and w4a16_decode_kernel (up to
+//          16 rows per pass, split along K across CTAs; partial sums are combined with f32 atomics in a
+//          caller-provided workspace that the last CTA of each row block drains).
 //   W8A32: int8 codes -> f32, plain FMAs (the benchmark's CPU-runnable configuration).
 #include "oxq_common.cuh"
 #include <stdlib.h>
@@ -206,6 +207,155 @@ __global__ void __launch_bounds__(W4_THREADS) w4a16_decode_kernel(const W4Params
 }
 
 // ------------------------------------------------------------------------------------------------
+// W4A16, up to 8 batch rows, no split across CTAs
+// ------------------------------------------------------------------------------------------------
+//
+// A CTA owns 16 weight rows over the whole K range; its GV_WARPS warps split K among themselves and meet once
+// in shared memory at the end, so there are no global atomics, no workspace and no second pass.  Inside a warp
+// nothing is shared: lane (g, t) streams rows g and g + 8 (16 bytes = 32 codes per load, chunks of four spans
+// of 128 K, the next chunk requested before the current one is multiplied), reads the matching 8 activations of
+// batch row g straight from global memory (they stay in L1) and permutes them in registers into the K order of
+// the unpacked codes.  The MMAs multiply 128 + code; a second chain of MMAs with an all-ones row operand gives
+// every lane the sum of the activations of the span, which takes the 128 and the zero-point back out:
+//   sum_k (c_k - z) x_k = sum_k (128 + c_k) x_k - (128 + z) sum_k x_k
+constexpr int GV_WARPS = 8;
+constexpr int GV_CHUNK = 4;            // spans per register buffer (the vector scale loads assume 4)
+
+// a load the compiler keeps where it is written
+__device__ __forceinline__ uint4 ld_pinned_u4(const void* p) {
+    uint4 u;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(p) : "memory");
+    return u;
+}
+
+struct GvParams {
+    int m, n, k, group;
+    const __nv_bfloat16* x;      // [m x k]
+    const uint32_t* codes;       // [n x k/8]
+    const uint16_t* scales;      // f16 [n x k/group]
+    const uint32_t* zeros;       // packed, linear group order
+    __nv_bfloat16* y;            // [m x n]
+};
+
+// PIPE: the warp's K range is longer than one chunk, so a second register buffer holds the next chunk's requests.
+template <bool PIPE>
+__global__ void __launch_bounds__(GV_WARPS * 32, 2) w4a16_gemv_kernel(const GvParams p) {
+    __shared__ float red[GV_WARPS][16][8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int spans = p.k >> 7;
+    const int s_lo = (int)(((int64_t)warp * spans) / GV_WARPS), s_hi = (int)(((int64_t)(warp + 1) * spans) / GV_WARPS);
+    const int row_a = min((int)blockIdx.x * 16 + g, p.n - 1), row_b = min((int)blockIdx.x * 16 + g + 8, p.n - 1);
+    const int wpr = p.k >> 3, gpr = p.k / p.group;
+    const uint32_t* ca = p.codes + (size_t)row_a * wpr + 4 * t;
+    const uint32_t* cb = p.codes + (size_t)row_b * wpr + 4 * t;
+    const bool has_x = g < p.m;
+    const __nv_bfloat16* xr = p.x + (size_t)(has_x ? g : 0) * p.k + 32 * t;
+
+    uint4 cur_a[GV_CHUNK], cur_b[GV_CHUNK], nxt_a[GV_CHUNK], nxt_b[GV_CHUNK];
+    uint32_t cur_sa[GV_CHUNK], cur_sb[GV_CHUNK], nxt_sa[GV_CHUNK], nxt_sb[GV_CHUNK];     // f16 scale | zero-point << 16
+
+    // With group 128, a chunk that starts at a multiple of four groups and whole rows of scales that are 8-byte aligned,
+    // the chunk's four scales of a row are one 8-byte load and its zero-points sit in one word.
+    const bool vec_meta = p.group == 128 && (gpr & 7) == 0 && ((s_lo & 3) == 0) && (((s_hi - s_lo) & 3) == 0);
+
+    auto fetch = [&](int s0, uint4 (&wa)[GV_CHUNK], uint4 (&wb)[GV_CHUNK], uint32_t (&sa)[GV_CHUNK], uint32_t (&sb)[GV_CHUNK]) {
+#pragma unroll
+        for (int j = 0; j < GV_CHUNK; j++) {
+            const int s = s0 + j;
+            wa[j] = make_uint4(0, 0, 0, 0); wb[j] = wa[j]; sa[j] = 0; sb[j] = 0;      // scale 0: the span contributes nothing
+            if (s < s_hi) {
+                wa[j] = ld_stream_u4(ca + s * 16);
+                wb[j] = ld_stream_u4(cb + s * 16);
+            }
+        }
+        if (vec_meta) {
+            const int gia = row_a * gpr + s0, gib = row_b * gpr + s0;
+            const uint2 qa = __ldg(reinterpret_cast<const uint2*>(p.scales + gia)), qb = __ldg(reinterpret_cast<const uint2*>(p.scales + gib));
+            const uint32_t za = __ldg(p.zeros + (gia >> 3)) >> ((gia & 7) * 4), zb = __ldg(p.zeros + (gib >> 3)) >> ((gib & 7) * 4);
+            sa[0] = (qa.x & 0xFFFFu) | ((za & 0xFu) << 16);         sb[0] = (qb.x & 0xFFFFu) | ((zb & 0xFu) << 16);
+            sa[1] = (qa.x >> 16) | (((za >> 4) & 0xFu) << 16);      sb[1] = (qb.x >> 16) | (((zb >> 4) & 0xFu) << 16);
+            sa[2] = (qa.y & 0xFFFFu) | (((za >> 8) & 0xFu) << 16);  sb[2] = (qb.y & 0xFFFFu) | (((zb >> 8) & 0xFu) << 16);
+            sa[3] = (qa.y >> 16) | (((za >> 12) & 0xFu) << 16);     sb[3] = (qb.y >> 16) | (((zb >> 12) & 0xFu) << 16);
+        } else {
+#pragma unroll
+            for (int j = 0; j < GV_CHUNK; j++) {
+                const int s = s0 + j;
+                if (s < s_hi) {
+                    const int kg = (s << 7) / p.group;
+                    const int gia = row_a * gpr + kg, gib = row_b * gpr + kg;
+                    sa[j] = (uint32_t)__ldg(p.scales + gia) | (((__ldg(p.zeros + (gia >> 3)) >> ((gia & 7) * 4)) & 0xFu) << 16);
+                    sb[j] = (uint32_t)__ldg(p.scales + gib) | (((__ldg(p.zeros + (gib >> 3)) >> ((gib & 7) * 4)) & 0xFu) << 16);
+                }
+            }
+        }
+    };
+
+    float total[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (s_lo < s_hi) fetch(s_lo, cur_a, cur_b, cur_sa, cur_sb);
+    for (int s0 = s_lo; s0 < s_hi; s0 += GV_CHUNK) {
+        if (PIPE && s0 + GV_CHUNK < s_hi) fetch(s0 + GV_CHUNK, nxt_a, nxt_b, nxt_sa, nxt_sb);
+#pragma unroll
+        for (int j = 0; j < GV_CHUNK; j++) {
+            const int s = s0 + j;
+            if (s < s_hi) {
+                float part[4] = {0.0f, 0.0f, 0.0f, 0.0f}, xs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                const uint32_t wwa[4] = {cur_a[j].x, cur_a[j].y, cur_a[j].z, cur_a[j].w}, wwb[4] = {cur_b[j].x, cur_b[j].y, cur_b[j].z, cur_b[j].w};
+                // the span's 32 activations of batch row g (L1-resident), requested here and not earlier: hoisting the
+                // requests of all spans to the top would cost 64 registers
+                const uint4* xp = reinterpret_cast<const uint4*>(xr + (size_t)s * 128);
+                uint4 xv[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    xv[i] = make_uint4(0, 0, 0, 0);
+                    if (has_x) xv[i] = ld_pinned_u4(xp + i);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    // 8 consecutive activations, reordered to (x0,x4) (x1,x5) (x2,x6) (x3,x7)
+                    const uint4 v = xv[i];
+                    const uint32_t b0 = __byte_perm(v.x, v.z, 0x5410), b1 = __byte_perm(v.x, v.z, 0x7632);
+                    const uint32_t b2 = __byte_perm(v.y, v.w, 0x5410), b3 = __byte_perm(v.y, v.w, 0x7632);
+                    uint32_t ra[4], rb4[4];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        ra[q] = ((wwa[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u;           // bf16x2 (128 + c, 128 + c')
+                        rb4[q] = ((wwb[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u;
+                    }
+                    mma_bf16_16816(part, ra[0], rb4[0], ra[1], rb4[1], b0, b1);
+                    mma_bf16_16816(part, ra[2], rb4[2], ra[3], rb4[3], b2, b3);
+                    constexpr uint32_t ONES = 0x3F803F80u;                                    // bf16x2 (1, 1)
+                    mma_bf16_16816(xs, ONES, ONES, ONES, ONES, b0, b1);
+                    mma_bf16_16816(xs, ONES, ONES, ONES, ONES, b2, b3);
+                }
+                const float sa = __half2float(__ushort_as_half((unsigned short)(cur_sa[j] & 0xFFFFu)));
+                const float sb = __half2float(__ushort_as_half((unsigned short)(cur_sb[j] & 0xFFFFu)));
+                const float za = 128.0f + (float)(cur_sa[j] >> 16), zb = 128.0f + (float)(cur_sb[j] >> 16);
+                total[0] += sa * fmaf(-za, xs[0], part[0]);
+                total[1] += sa * fmaf(-za, xs[1], part[1]);
+                total[2] += sb * fmaf(-zb, xs[2], part[2]);
+                total[3] += sb * fmaf(-zb, xs[3], part[3]);
+            }
+        }
+        if (PIPE) {
+#pragma unroll
+            for (int j = 0; j < GV_CHUNK; j++) { cur_a[j] = nxt_a[j]; cur_b[j] = nxt_b[j]; cur_sa[j] = nxt_sa[j]; cur_sb[j] = nxt_sb[j]; }
+        }
+    }
+    // accumulator element e: weight row (e < 2 ? g : g + 8), batch row 2t + (e & 1)
+    red[warp][g][2 * t] = total[0]; red[warp][g][2 * t + 1] = total[1];
+    red[warp][g + 8][2 * t] = total[2]; red[warp][g + 8][2 * t + 1] = total[3];
+    __syncthreads();
+    if (threadIdx.x < 128) {
+        const int col = threadIdx.x >> 4, r = threadIdx.x & 15;                             // consecutive threads -> consecutive rows of y
+        const int row = (int)blockIdx.x * 16 + r;
+        float acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < GV_WARPS; w++) acc += red[w][r][col];
+        if (col < p.m && row < p.n) p.y[(size_t)col * p.n + row] = __float2bfloat16_rn(acc);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // W8A32
 // ------------------------------------------------------------------------------------------------
 
@@ -306,7 +456,7 @@ int32_t oxq_w4tc_launch(oxq_handle* h, int64_t m, int64_t n, int64_t k, const vo
                         const uint32_t* zeros, void* y, float* ws_sums, int* ws_counters);
 
 static int32_t w4a16_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, const uint32_t* codes, const uint16_t* scales,
-                          const uint32_t* zeros, int group, void* y, void* ws, size_t ws_bytes, bool allow_tc);
+                          const uint32_t* zeros, int group, void* y, void* ws, size_t ws_bytes, int mode);
 
 extern "C" {
 
@@ -318,19 +468,28 @@ size_t oxq_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
 
 int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, const uint32_t* codes, const uint16_t* scales,
                        const uint32_t* zeros, int group, void* y, void* ws, size_t ws_bytes) {
-    // Measured on B200 (14336 x 4096): the mma.sync kernel wins up to 8 batch rows (16-20 us against 21), the
-    // tensor-core kernel from there on (22-23 us per pass of 32 rows against 30-61), and from 65 rows the
-    // dequantise-then-GEMM path (70 us whatever the batch) beats three or more passes.  OXQ_W4A16_TC=0 never uses
-    // the tensor-core kernel, 2 uses it for every batch it supports (for A/B runs).
+    // Measured on B200 (14336 x 4096): up to 8 batch rows the mma.sync kernels win (16-17 us against 21; the one
+    // without a split across CTAs is as fast as the split-K one at one row, faster from two rows and on small
+    // matrices: 6.2 against 7.6 us at 4096 x 4096), the tensor-core kernel from there on (22-23 us per pass of 32
+    // rows against 30-61), and from 65 rows the dequantise-then-GEMM path (70 us whatever the batch) beats three or
+    // more passes.  OXQ_W4A16_TC=0 uses neither of the two newer kernels, 2 uses the tensor-core kernel for every
+    // batch it supports (for A/B runs).
     static int tc = -1;
     if (tc < 0) { const char* e = getenv("OXQ_W4A16_TC"); tc = e ? atoi(e) : 1; }
-    return w4a16_impl(h, m, n, k, x, codes, scales, zeros, group, y, ws, ws_bytes, tc >= 2 || (tc == 1 && m > 8 && m <= 64));
+    return w4a16_impl(h, m, n, k, x, codes, scales, zeros, group, y, ws, ws_bytes, tc < 0 ? 0 : (tc > 2 ? 2 : tc));
 }
 
 }  // extern "C"
 
+// OXQ_W4A16_GEMV=0 keeps batches of up to 8 rows on the split-K mma.sync kernel (for A/B runs)
+static bool gemv_setting() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("OXQ_W4A16_GEMV"); v = e ? (atoi(e) != 0) : 1; }
+    return v != 0;
+}
+
 static int32_t w4a16_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, const uint32_t* codes, const uint16_t* scales,
-                          const uint32_t* zeros, int group, void* y, void* ws, size_t ws_bytes, bool allow_tc) {
+                          const uint32_t* zeros, int group, void* y, void* ws, size_t ws_bytes, int mode) {
     OXQ_CHECK_HANDLE(h);
     if (m <= 0 || n <= 0 || k <= 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "GEMM dimensions must be non-zero");
     if (!x || !codes || !scales || !zeros || !y) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
@@ -338,7 +497,10 @@ static int32_t w4a16_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const 
     if (k % 8 != 0) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "K must be a multiple of 8 for INT4 packing, got %lld", (long long)k);
     if (!(group == 32 || group == 64 || group == 128 || group == 256)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "group size %d not in {32,64,128,256}", group);
     if (k % group != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "k %lld is not divisible by group size %d", (long long)k, group);
-    if (allow_tc && oxq_w4tc_supports(m, n, k, group)) {
+    // mode 0: split-K mma.sync and dequantise-then-GEMM only (the allocation-free entry point); 1: by batch size; 2: the
+    // fused tensor-core kernel wherever it applies
+    const bool tc_ok = oxq_w4tc_supports(m, n, k, group);
+    if ((mode == 2 && tc_ok) || (mode == 1 && tc_ok && m > 8 && m <= 64)) {
         // Tensor-core kernel with the dequantisation fused in: one pass over the weights per 32 batch rows.
         if (((uintptr_t)x & 15u) || ((uintptr_t)codes & 15u) || ((uintptr_t)scales & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "x, codes and scales must be 16-byte aligned");
         if (int32_t rc = oxq_require_sm100(h)) return rc;
@@ -364,6 +526,15 @@ static int32_t w4a16_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const 
     if (n > (int64_t)INT32_MAX / 64 || k > INT32_MAX / 64) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "dimension too large");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
 
+    if (mode >= 1 && m <= 8 && gemv_setting()) {
+        // up to 8 batch rows: one CTA per 16 weight rows over the whole K, nothing to combine across CTAs
+        GvParams gp;
+        gp.m = (int)m; gp.n = (int)n; gp.k = (int)k; gp.group = group;
+        gp.x = (const __nv_bfloat16*)x; gp.codes = codes; gp.scales = scales; gp.zeros = zeros; gp.y = (__nv_bfloat16*)y;
+        w4a16_gemv_kernel<true><<<(unsigned)((n + 15) / 16), GV_WARPS * 32, 0, h->stream>>>(gp);
+        OXQ_LAUNCH_CHECK(h);
+        return OXQ_OK;
+    }
     const int row_blocks = (int)((n + W4_ROWS_PER_CTA - 1) / W4_ROWS_PER_CTA);
     // K chunks of 4 spans (512 K): many short CTAs, so the tail of the grid is short as well
     const int spans_total = (int)(k / 128);
@@ -446,7 +617,7 @@ int32_t oxq_gemm_w4a16_static(void* cuda_stream, int64_t m, int64_t n, int64_t k
     oxq_handle tmp;
     tmp.device = dev; tmp.stream = (cudaStream_t)cuda_stream; tmp.sm_count = d.sm_count;
     tmp.cc_major = d.cc_major; tmp.cc_minor = d.cc_minor; tmp.dev_status = nullptr; tmp.dev_scratch = nullptr; tmp.last_error[0] = 0;
-    return w4a16_impl(&tmp, m, n, k, x, codes, scales, zeros, group, y, d.scratch, sums + counters, false);
+    return w4a16_impl(&tmp, m, n, k, x, codes, scales, zeros, group, y, d.scratch, sums + counters, 0);
 }
 
 int32_t oxq_gemm_w8a32(oxq_handle* h, int64_t m, int64_t n, int64_t k, const float* x, const int8_t* w, const float* sw, float* y) {

@@ -221,7 +221,8 @@ def extras(torch, ops, peaks):
     # what a plain streaming kernel reaches at the byte counts of the decode weights (the launch costs about 4 us
     # whatever it reads): the practical ceiling next to which the decode GEMM lines below should be read
     for nbytes in (8388608, 29360128):
-        small = [ring[i % 3].view(-1)[(i // 3) * (nbytes // 2):(i // 3 + 1) * (nbytes // 2)] for i in range(12)]
+        per = 134217728 // nbytes                                      # disjoint slices of the three big tensors: > 350 MB in all
+        small = [ring[i % 3].view(-1)[(i // 3) * (nbytes // 2):(i // 3 + 1) * (nbytes // 2)] for i in range(3 * per)]
         rec(f"stream_floor_absmax_{nbytes // 1048576}MiB", nbytes, ring_time(torch, lambda r: ops.absmax(r, out=am), small))
     one = torch.ones(1, device="cuda")
     rec("fp8_quant_bf16_8192x8192", 201326592, ring_time(torch, lambda r: ops.fp8_quant(r, one, out=outq), ring))

@@ -20,6 +20,8 @@ __device__ __forceinline__ void mm_st(uint4* p, const uint4& r) {
 
 // four reductions in flight per thread: a round trip through the switch takes microseconds
 __global__ void __launch_bounds__(512) multimem_all_reduce_bf16_kernel(uint4* mc, int64_t vec_lo, int64_t vec_hi) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     int64_t v = vec_lo + blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     for (; v + 3 * stride < vec_hi; v += 4 * stride) {
@@ -44,7 +46,7 @@ extern "C" int32_t oxq_multimem_all_reduce_bf16(oxq_handle* h, void* multicast_p
     int64_t blocks = (per + 512 * 4 - 1) / (512 * 4);
     if (blocks > h->sm_count) blocks = h->sm_count;
     if (blocks < 1) blocks = 1;
-    oxq::multimem_all_reduce_bf16_kernel<<<(int)blocks, 512, 0, h->stream>>>((uint4*)multicast_ptr, lo, hi);
+    oxq_launch(oxq::multimem_all_reduce_bf16_kernel, (int)blocks, 512, 0, h->stream, (uint4*)multicast_ptr, lo, hi);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

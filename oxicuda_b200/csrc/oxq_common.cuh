@@ -49,7 +49,29 @@ struct oxq_handle {
 // Refuses to launch on anything but a compute-capability 10.x device: there is no fallback path.
 int32_t oxq_require_sm100(oxq_handle* h);
 
+// Every kernel of the library is launched with the programmatic-dependent-launch attribute (OXQ_PDL=0 turns it
+// off): a kernel may be scheduled while the one before it in the stream is still draining, which hides the few
+// microseconds a launch costs when kernels that last 5-30 us follow one another.  Kernels call pdl_trigger() first
+// (the next launch may be scheduled) and pdl_wait() before their first access to anything an earlier kernel may
+// have written or may still read; both are no-ops in a launch without the attribute.
+bool oxq_pdl_enabled();
+
+template <bool PDL = true, typename... P, typename... A>
+static inline cudaError_t oxq_launch(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = (PDL && oxq_pdl_enabled()) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+
 namespace oxq {
+
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

@@ -58,6 +58,8 @@ struct W4Params {
 // already permuted to match.
 template <int NT, int SPANS>
 __global__ void __launch_bounds__(W4_THREADS) w4a16_decode_kernel(const W4Params p) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ uint4 xs[SPANS * 4 * NT * 32];           // [span][word][nt][lane]: B fragments of two MMAs
     __shared__ float xsum[SPANS][NT * 8];               // [span][batch row]: sum of the activations
     __shared__ int s_last;
@@ -291,7 +293,11 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 2) w4a16_gemv_kernel(const GvPa
     };
 
     float total[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // The weights do not depend on the kernel before this one in the stream, so their first requests go out while
+    // that kernel is still finishing; the activations and the output wait for it.
+    pdl_trigger();
     if (s_lo < s_hi) fetch(s_lo, cur_a, cur_b, cur_sa, cur_sb);
+    pdl_wait();
     for (int s0 = s_lo; s0 < s_hi; s0 += GV_CHUNK) {
         if (PIPE && s0 + GV_CHUNK < s_hi) fetch(s0 + GV_CHUNK, nxt_a, nxt_b, nxt_sa, nxt_sb);
 #pragma unroll
@@ -368,6 +374,8 @@ constexpr int W8_RPW = 2;           // weight rows per warp
 __global__ void __launch_bounds__(256) w8a32_decode_kernel(const float* __restrict__ x, const int8_t* __restrict__ w,
                                                            const float* __restrict__ sw, float* __restrict__ y,
                                                            int m, int n, int k) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float4 xs[W8_MT][W8_KC / 4];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m0 = blockIdx.y * W8_MT;
@@ -531,8 +539,7 @@ static int32_t w4a16_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const 
         GvParams gp;
         gp.m = (int)m; gp.n = (int)n; gp.k = (int)k; gp.group = group;
         gp.x = (const __nv_bfloat16*)x; gp.codes = codes; gp.scales = scales; gp.zeros = zeros; gp.y = (__nv_bfloat16*)y;
-        w4a16_gemv_kernel<true><<<(unsigned)((n + 15) / 16), GV_WARPS * 32, 0, h->stream>>>(gp);
-        OXQ_LAUNCH_CHECK(h);
+        OXQ_CUDA(h, oxq_launch(w4a16_gemv_kernel<true>, (unsigned)((n + 15) / 16), GV_WARPS * 32, 0, h->stream, gp));
         return OXQ_OK;
     }
     const int row_blocks = (int)((n + W4_ROWS_PER_CTA - 1) / W4_ROWS_PER_CTA);
@@ -559,8 +566,8 @@ static int32_t w4a16_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const 
         p.x = (const __nv_bfloat16*)x + m0 * k; p.codes = codes; p.scales = scales; p.zeros = zeros;
         p.y = (__nv_bfloat16*)y + m0 * n;
         p.ws = ws_sums ? ws_sums + m0 * n : nullptr; p.counters = ws_counters;
-        if (mc <= 8) w4a16_decode_kernel<1, W4_SPANS><<<grid, W4_THREADS, 0, h->stream>>>(p);
-        else w4a16_decode_kernel<2, W4_SPANS><<<grid, W4_THREADS, 0, h->stream>>>(p);
+        if (mc <= 8) oxq_launch(w4a16_decode_kernel<1, W4_SPANS>, grid, W4_THREADS, 0, h->stream, p);
+        else oxq_launch(w4a16_decode_kernel<2, W4_SPANS>, grid, W4_THREADS, 0, h->stream, p);
     }
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
@@ -628,7 +635,9 @@ int32_t oxq_gemm_w8a32(oxq_handle* h, int64_t m, int64_t n, int64_t k, const flo
     if (m > 64) OXQ_FAIL(h, OXQ_ERR_UNSUPPORTED_OPERATION, "oxq_gemm_w8a32 covers decode shapes (m <= 64), got m = %lld", (long long)m);
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     dim3 grid((unsigned)((n + 8 * W8_RPW - 1) / (8 * W8_RPW)), (unsigned)((m + W8_MT - 1) / W8_MT));
-    w8a32_decode_kernel<<<grid, 256, 0, h->stream>>>(x, w, sw, y, (int)m, (int)n, (int)k);
+    // launched without the dependent-launch attribute: with it this kernel measured 20-25 % slower (19.7 -> 24.2 us
+    // at 4096 x 4096, one batch row)
+    oxq_launch<false>(w8a32_decode_kernel, grid, 256, 0, h->stream, x, w, sw, y, (int)m, (int)n, (int)k);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

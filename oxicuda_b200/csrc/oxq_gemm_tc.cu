@@ -105,6 +105,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    pdl_trigger();                                               // barriers, tensor memory and descriptors are set up:
+    pdl_wait();                                                  // only now wait for the kernel that produced the operands
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (one lane)
@@ -410,6 +412,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     cluster_sync_all();                                   // peer barriers are initialised and its tensor memory allocated
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    pdl_trigger();
+    pdl_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (one lane, both CTAs)
@@ -579,6 +583,8 @@ gemm_tc2_scaled_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
     cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    pdl_trigger();
+    pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -759,7 +765,7 @@ static int32_t launch(oxq_handle* h, const void* x, int64_t ldx_bytes, const voi
     p.status = h->dev_status;
     p.group_m = group_m_setting();
     { const char* e = getenv("OXQ_DEBUG_FLAGS"); p.debug_flags = e ? atoi(e) : 0; }
-    gemm_tc_kernel<KIND, BN, EPI><<<grid, NUM_THREADS, C::kSmemBytes, h->stream>>>(tm_a, tm_b, p);
+    oxq_launch(gemm_tc_kernel<KIND, BN, EPI>, grid, NUM_THREADS, C::kSmemBytes, h->stream, tm_a, tm_b, p);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -795,7 +801,7 @@ static int32_t launch2(oxq_handle* h, const void* x, int64_t ldx_bytes, const vo
     const int clusters = tiles < max_clusters ? tiles : max_clusters;
     p.status = h->dev_status;
     p.group_m = group_m_setting() / 2 > 0 ? group_m_setting() / 2 : 1;     // same panel height in rows as the 1-CTA walk
-    gemm_tc2_kernel<KIND, EPI><<<2 * clusters, NUM_THREADS, T2_SMEM_BYTES, h->stream>>>(tm_a, tm_b, p);
+    oxq_launch(gemm_tc2_kernel<KIND, EPI>, 2 * clusters, NUM_THREADS, T2_SMEM_BYTES, h->stream, tm_a, tm_b, p);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -849,7 +855,7 @@ static int32_t launch2_scaled(oxq_handle* h, const void* x, int64_t ldx_bytes, c
     const int clusters = tiles < max_clusters ? tiles : max_clusters;
     p.status = h->dev_status;
     p.group_m = group_m_setting() / 2 > 0 ? group_m_setting() / 2 : 1;
-    gemm_tc2_scaled_kernel<KIND><<<2 * clusters, NUM_THREADS, C::kSmemBytes, h->stream>>>(tm_a, tm_b, tm_sfa, tm_sfb, p);
+    oxq_launch(gemm_tc2_scaled_kernel<KIND>, 2 * clusters, NUM_THREADS, C::kSmemBytes, h->stream, tm_a, tm_b, tm_sfa, tm_sfb, p);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

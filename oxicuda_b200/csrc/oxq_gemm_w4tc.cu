@@ -123,6 +123,10 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    // The packed weights, scales and zero-points do not depend on the kernel before this one in the stream: the codes
+    // producer, the unpack warps and the MMA thread start at once; the activation producer and the epilogue (which
+    // reads and writes the workspace and the output) wait for that kernel first.
+    pdl_trigger();
 
     // One completion barrier per unit slot serves three waiters: the epilogue (accumulators ready), the
     // activation producer (slot free again, four units later) and the unpack warps (tensor-memory slot of the
@@ -141,6 +145,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     } else if (warp == 1) {
         // ------------------------------------------------------------------ activation producer (one lane)
         if (lane == 0) {
+            pdl_wait();
             for (int lu = 0; lu < num_units; lu++) {
                 const int unit = unit0 + lu, rb = unit / p.upr, uk = unit - rb * p.upr;
                 const int k0 = uk * UNIT_K;
@@ -182,6 +187,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
         // ------------------------------------------------------------------ epilogue (4 warps, one weight row per thread)
         const int quarter = warp & 3;
         const int row_in_block = quarter * 32 + lane;
+        pdl_wait();
         float total[NB];
 #pragma unroll
         for (int j = 0; j < NB; j++) total[j] = 0.0f;
@@ -388,7 +394,7 @@ static int32_t launch_nb(oxq_handle* h, const CUtensorMap& tm_codes, const void*
         attr_set = true;
     }
     const int grid = p.total_units < h->sm_count ? p.total_units : h->sm_count;
-    w4a16_tc_kernel<NB><<<grid, NUM_THREADS, C::kSmemBytes, h->stream>>>(tm_codes, tm_x, p);
+    oxq_launch(w4a16_tc_kernel<NB>, grid, NUM_THREADS, C::kSmemBytes, h->stream, tm_codes, tm_x, p);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

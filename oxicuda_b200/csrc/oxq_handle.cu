@@ -1,6 +1,7 @@
 // Handle lifecycle and status plumbing of liboxq_b200.
 #include "oxq_common.cuh"
 #include <new>
+#include <stdlib.h>
 
 extern "C" {
 
@@ -84,6 +85,12 @@ int32_t oxq_device_status(oxq_handle* h, int32_t* status_out) {
 }
 
 }  // extern "C"
+
+bool oxq_pdl_enabled() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("OXQ_PDL"); v = e ? (atoi(e) != 0) : 1; }
+    return v != 0;
+}
 
 int32_t oxq_require_sm100(oxq_handle* h) {
     if (h->cc_major != 10)

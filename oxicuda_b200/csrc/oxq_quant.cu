@@ -35,6 +35,8 @@ template <int NV>
 __global__ void __launch_bounds__(256) int8_quant_rows_kernel(const float* __restrict__ x, int64_t rows, int64_t cols,
                                                               int8_t* __restrict__ q, float* __restrict__ scales,
                                                               int rounding) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float s_red[2][8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t nvec = cols >> 2;
@@ -101,6 +103,8 @@ __global__ void __launch_bounds__(256) int8_quant_rows_kernel(const float* __res
 __global__ void __launch_bounds__(256) int8_quant_rows_scalar_kernel(const float* __restrict__ x, int64_t rows, int64_t cols,
                                                                      int8_t* __restrict__ q, float* __restrict__ scales,
                                                                      int rounding) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float s_red[8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
@@ -123,6 +127,8 @@ __global__ void __launch_bounds__(256) int8_quant_rows_scalar_kernel(const float
 // 16 codes per thread: one 16-byte load, four 16-byte stores.
 __global__ void __launch_bounds__(256) int8_dequant_rows_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales,
                                                                 int64_t rows, int64_t cols, float* __restrict__ y) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t nchunk = rows * cols / 16;
     for (int64_t c = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; c < nchunk; c += (int64_t)gridDim.x * blockDim.x) {
         const int64_t e = c * 16;
@@ -143,6 +149,8 @@ __global__ void __launch_bounds__(256) int8_dequant_rows_kernel(const int8_t* __
 }
 __global__ void __launch_bounds__(256) int8_dequant_rows_scalar_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales,
                                                                        int64_t rows, int64_t cols, float* __restrict__ y) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t n = rows * cols;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         y[i] = (float)q[i] * scales[i / cols];
@@ -188,6 +196,8 @@ template <> struct AbsMaxAcc<__half> {
 // both cells back to zero, so no memset is needed between calls.
 template <typename T>
 __global__ void __launch_bounds__(256) absmax_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ out, unsigned int* __restrict__ cells) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int V = Vec16<T>::N;
     __shared__ float s_red[8];
     const int64_t nvec = n / V;
@@ -259,6 +269,8 @@ constexpr int FP8_ILP = 4;
 template <typename T, int MODE, bool BOUNDED>
 __global__ void __launch_bounds__(256) fp8_quant_kernel(const T* __restrict__ x, int64_t n, const float* __restrict__ scale_ptr,
                                                         float* __restrict__ stats, uint8_t* __restrict__ q) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int V = Vec16<T>::N;                          // elements per 16-byte load (8 or 4)
     constexpr int L = 8 / V;                                // 16-byte loads per item (1 or 2)
     float scale_f;
@@ -319,6 +331,8 @@ __global__ void __launch_bounds__(256) fp8_quant_kernel(const T* __restrict__ x,
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) fp8_dequant_kernel(const uint8_t* __restrict__ q, int64_t n, const float* __restrict__ scale_ptr,
                                                           T* __restrict__ y) {
+    pdl_trigger();
+    pdl_wait();
     const float scale = __ldg(scale_ptr);
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         float v = MODE == OXQ_FP8_SPEC_RNE ? e4m3_to_f32(q[i]) : e4m3_refcompat_decode(q[i]);
@@ -337,6 +351,8 @@ template <typename T, int GROUP>
 __global__ void __launch_bounds__(256) int4g_quant_kernel(const T* __restrict__ x, int64_t ngroups, int rounding,
                                                           uint32_t* __restrict__ codes, uint16_t* __restrict__ scales,
                                                           uint32_t* __restrict__ zeros) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int PIECES = GROUP / 128 > 0 ? GROUP / 128 : 1;  // 4-element pieces per lane per group
     constexpr int ACTIVE = GROUP >= 128 ? 32 : GROUP / 4;      // lanes that hold data
     const int lane = threadIdx.x & 31;
@@ -428,6 +444,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) int4g128_quant_kernel(const T* __restrict__ x, int64_t ngroups, int rounding,
                                                              uint32_t* __restrict__ codes, uint16_t* __restrict__ scales,
                                                              uint32_t* __restrict__ zeros) {
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31, sub = lane >> 3, sl = lane & 7;
     const int64_t warp = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -501,6 +519,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) int4g_dequant_kernel(const uint32_t* __restrict__ codes, const uint16_t* __restrict__ scales,
                                                             const uint32_t* __restrict__ zeros, int64_t nwords, int group,
                                                             T* __restrict__ y) {
+    pdl_trigger();
+    pdl_wait();
     for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < nwords; w += (int64_t)gridDim.x * blockDim.x) {
         const int64_t gi = (w * 8) / group;
         const float s = __half2float(__ushort_as_half(scales[gi]));
@@ -542,6 +562,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) mxfp8_quant_kernel(const T* __restrict__ x, int64_t rows, int64_t k,
                                                           uint8_t* __restrict__ codes, uint8_t* __restrict__ sf_rm,
                                                           uint8_t* __restrict__ sf_mma) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t nitems = rows * k / 8;
     const int64_t sf_cols = k / 32;
     const uint32_t sf_col_tiles = (uint32_t)((sf_cols + 3) / 4);
@@ -593,6 +615,8 @@ __global__ void __launch_bounds__(256) mxfp8_quant_kernel(const T* __restrict__ 
 template <typename T>
 __global__ void __launch_bounds__(256) mxfp8_dequant_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sf_rm,
                                                             int64_t n, T* __restrict__ y) {
+    pdl_trigger();
+    pdl_wait();
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         y[i] = Elem<T>::from_f32(e4m3_to_f32(codes[i]) * pow2_of((int)sf_rm[i >> 5] - 127));
 }
@@ -602,6 +626,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const T* __restrict__ x, int64_t rows, int64_t k, float* __restrict__ stats,
                                                           uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_rm,
                                                           uint8_t* __restrict__ sf_mma) {
+    pdl_trigger();
+    pdl_wait();
     const float tmax = stats[0];
     const float g = tmax > 0.0f ? __fdiv_rn(tmax, 448.0f * 6.0f) : 1.0f;
     if (blockIdx.x == 0 && threadIdx.x == 0) stats[1] = g;
@@ -656,6 +682,8 @@ __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const T* __restrict__ 
 template <typename T>
 __global__ void __launch_bounds__(256) nvfp4_dequant_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ sf_rm,
                                                             const float* __restrict__ stats, int64_t n, T* __restrict__ y) {
+    pdl_trigger();
+    pdl_wait();
     const float g = stats[1];
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         const uint32_t nib = (packed[i >> 1] >> ((i & 1) * 4)) & 0xF;
@@ -667,6 +695,8 @@ __global__ void __launch_bounds__(256) nvfp4_dequant_kernel(const uint8_t* __res
 // SwiGluFfn::forward on a gate/up product stored in the interleaved 128-column block order.
 __global__ void __launch_bounds__(256) swiglu_interleaved_kernel(const __nv_bfloat16* __restrict__ gu, int64_t m, int64_t n,
                                                                  __nv_bfloat16* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t nvec = m * n / 8;
     for (int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; v < nvec; v += (int64_t)gridDim.x * blockDim.x) {
         const int64_t e = v * 8, row = e / n, j = e - row * n;
@@ -714,10 +744,10 @@ int32_t oxq_int8_quant_rows(oxq_handle* h, const float* x, int64_t rows, int64_t
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     const int grid = (int)(rows < (int64_t)h->sm_count * 6 ? rows : (int64_t)h->sm_count * 6);
     if ((cols & 3) == 0 && aligned16(x) && (((uintptr_t)q & 3u) == 0)) {
-        if (cols <= 4096) int8_quant_rows_kernel<4><<<grid, 256, 0, h->stream>>>(x, rows, cols, q, scales, rounding);
-        else int8_quant_rows_kernel<8><<<grid, 256, 0, h->stream>>>(x, rows, cols, q, scales, rounding);
+        if (cols <= 4096) oxq_launch(int8_quant_rows_kernel<4>, grid, 256, 0, h->stream, x, rows, cols, q, scales, rounding);
+        else oxq_launch(int8_quant_rows_kernel<8>, grid, 256, 0, h->stream, x, rows, cols, q, scales, rounding);
     } else {
-        int8_quant_rows_scalar_kernel<<<grid, 256, 0, h->stream>>>(x, rows, cols, q, scales, rounding);
+        oxq_launch(int8_quant_rows_scalar_kernel, grid, 256, 0, h->stream, x, rows, cols, q, scales, rounding);
     }
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
@@ -729,9 +759,9 @@ int32_t oxq_int8_dequant_rows(oxq_handle* h, const int8_t* q, const float* scale
     if (!y || !q || !scales) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     if ((cols & 15) == 0 && aligned16(q) && aligned16(y))
-        int8_dequant_rows_kernel<<<grid_for(h, rows * cols / 16, 256, 16), 256, 0, h->stream>>>(q, scales, rows, cols, y);
+        oxq_launch(int8_dequant_rows_kernel, grid_for(h, rows * cols / 16, 256, 16), 256, 0, h->stream, q, scales, rows, cols, y);
     else
-        int8_dequant_rows_scalar_kernel<<<grid_for(h, rows * cols, 256, 16), 256, 0, h->stream>>>(q, scales, rows, cols, y);
+        oxq_launch(int8_dequant_rows_scalar_kernel, grid_for(h, rows * cols, 256, 16), 256, 0, h->stream, q, scales, rows, cols, y);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -742,7 +772,7 @@ int32_t oxq_absmax(oxq_handle* h, const void* x, int dtype, int64_t n, float* ab
     if (!x || !absmax_dev || !aligned16(x)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     if (!h->dev_scratch) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "handle has no reduction cells");
-    DISPATCH_DTYPE(dtype, absmax_kernel<T><<<grid_for(h, n / Vec16<T>::N / 8 + 1, 256, 8), 256, 0, h->stream>>>((const T*)x, n, absmax_dev, h->dev_scratch));
+    DISPATCH_DTYPE(dtype, oxq_launch(absmax_kernel<T>, grid_for(h, n / Vec16<T>::N / 8 + 1, 256, 8), 256, 0, h->stream, (const T*)x, n, absmax_dev, h->dev_scratch));
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -751,11 +781,11 @@ static int32_t fp8_quant_launch(oxq_handle* h, const void* x, int dtype, int64_t
     const int grid = grid_for(h, n / (8 * FP8_ILP) + 1, 256, 8);
     if (mode == OXQ_FP8_SPEC_RNE && stats) {
         // scale = absmax / 448 of this very tensor: quotients are bounded by 448, no overflow handling needed
-        DISPATCH_DTYPE(dtype, fp8_quant_kernel<T, OXQ_FP8_SPEC_RNE, true><<<grid, 256, 0, h->stream>>>((const T*)x, n, scale, stats, q));
+        DISPATCH_DTYPE(dtype, oxq_launch(fp8_quant_kernel<T, OXQ_FP8_SPEC_RNE, true>, grid, 256, 0, h->stream, (const T*)x, n, scale, stats, q));
     } else if (mode == OXQ_FP8_SPEC_RNE) {
-        DISPATCH_DTYPE(dtype, fp8_quant_kernel<T, OXQ_FP8_SPEC_RNE, false><<<grid, 256, 0, h->stream>>>((const T*)x, n, scale, stats, q));
+        DISPATCH_DTYPE(dtype, oxq_launch(fp8_quant_kernel<T, OXQ_FP8_SPEC_RNE, false>, grid, 256, 0, h->stream, (const T*)x, n, scale, stats, q));
     } else if (mode == OXQ_FP8_REFCOMPAT) {
-        DISPATCH_DTYPE(dtype, fp8_quant_kernel<T, OXQ_FP8_REFCOMPAT, false><<<grid, 256, 0, h->stream>>>((const T*)x, n, scale, stats, q));
+        DISPATCH_DTYPE(dtype, oxq_launch(fp8_quant_kernel<T, OXQ_FP8_REFCOMPAT, false>, grid, 256, 0, h->stream, (const T*)x, n, scale, stats, q));
     } else {
         OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "fp8 mode %d", mode);
     }
@@ -786,9 +816,9 @@ int32_t oxq_fp8_dequant(oxq_handle* h, const uint8_t* q, int64_t n, const float*
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     const int grid = grid_for(h, n, 256, 16);
     if (mode == OXQ_FP8_SPEC_RNE) {
-        DISPATCH_DTYPE(y_dtype, fp8_dequant_kernel<T, OXQ_FP8_SPEC_RNE><<<grid, 256, 0, h->stream>>>(q, n, scale_dev, (T*)y));
+        DISPATCH_DTYPE(y_dtype, oxq_launch(fp8_dequant_kernel<T, OXQ_FP8_SPEC_RNE>, grid, 256, 0, h->stream, q, n, scale_dev, (T*)y));
     } else {
-        DISPATCH_DTYPE(y_dtype, fp8_dequant_kernel<T, OXQ_FP8_REFCOMPAT><<<grid, 256, 0, h->stream>>>(q, n, scale_dev, (T*)y));
+        DISPATCH_DTYPE(y_dtype, oxq_launch(fp8_dequant_kernel<T, OXQ_FP8_REFCOMPAT>, grid, 256, 0, h->stream, q, n, scale_dev, (T*)y));
     }
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
@@ -805,9 +835,9 @@ int32_t oxq_int4g_quant_pack(oxq_handle* h, const void* x, int dtype, int64_t ro
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     const int64_t ngroups = rows * (k / group);
     const int grid = grid_for(h, (ngroups + 7) / 8 * 32, 256, 8);
-#define LAUNCH_G(G) int4g_quant_kernel<T, G><<<grid, 256, 0, h->stream>>>((const T*)x, ngroups, rounding, codes, scales, zeros)
+#define LAUNCH_G(G) oxq_launch(int4g_quant_kernel<T, G>, grid, 256, 0, h->stream, (const T*)x, ngroups, rounding, codes, scales, zeros)
     DISPATCH_DTYPE(dtype, if (group == 32) LAUNCH_G(32); else if (group == 64) LAUNCH_G(64);
-                   else if (group == 128) int4g128_quant_kernel<T><<<grid, 256, 0, h->stream>>>((const T*)x, ngroups, rounding, codes, scales, zeros);
+                   else if (group == 128) oxq_launch(int4g128_quant_kernel<T>, grid, 256, 0, h->stream, (const T*)x, ngroups, rounding, codes, scales, zeros);
                    else LAUNCH_G(256));
 #undef LAUNCH_G
     OXQ_LAUNCH_CHECK(h);
@@ -822,7 +852,7 @@ int32_t oxq_int4g_dequant(oxq_handle* h, const uint32_t* codes, const uint16_t* 
     if (!y || !codes || !scales || !zeros || !aligned16(y)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     const int64_t nwords = rows * k / 8;
-    DISPATCH_DTYPE(y_dtype, int4g_dequant_kernel<T><<<grid_for(h, nwords, 256, 16), 256, 0, h->stream>>>(codes, scales, zeros, nwords, group, (T*)y));
+    DISPATCH_DTYPE(y_dtype, oxq_launch(int4g_dequant_kernel<T>, grid_for(h, nwords, 256, 16), 256, 0, h->stream, codes, scales, zeros, nwords, group, (T*)y));
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -833,7 +863,7 @@ int32_t oxq_swiglu_interleaved(oxq_handle* h, const void* gu, int64_t m, int64_t
     if (n % 128 != 0) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "n must be a multiple of 128, got %lld", (long long)n);
     if (!gu || !out || !aligned16(gu) || !aligned16(out)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
-    swiglu_interleaved_kernel<<<grid_for(h, m * n / 8, 256, 8), 256, 0, h->stream>>>((const __nv_bfloat16*)gu, m, n, (__nv_bfloat16*)out);
+    oxq_launch(swiglu_interleaved_kernel, grid_for(h, m * n / 8, 256, 8), 256, 0, h->stream, (const __nv_bfloat16*)gu, m, n, (__nv_bfloat16*)out);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -852,7 +882,7 @@ int32_t oxq_mxfp8_quant(oxq_handle* h, const void* x, int dtype, int64_t rows, i
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     if (sf_mma && ((rows & 127) || ((k / 32) & 3)))          // pad bytes of partial tiles must not hold garbage
         OXQ_CUDA(h, cudaMemsetAsync(sf_mma, 0, oxq_sf_mma_bytes(rows, k / 32), h->stream));
-    DISPATCH_DTYPE(dtype, mxfp8_quant_kernel<T><<<grid_for(h, rows * k / (8 * BS_ILP) + 1, 256, 8), 256, 0, h->stream>>>((const T*)x, rows, k, codes, sf_rm, sf_mma));
+    DISPATCH_DTYPE(dtype, oxq_launch(mxfp8_quant_kernel<T>, grid_for(h, rows * k / (8 * BS_ILP) + 1, 256, 8), 256, 0, h->stream, (const T*)x, rows, k, codes, sf_rm, sf_mma));
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -863,7 +893,7 @@ int32_t oxq_mxfp8_dequant(oxq_handle* h, const uint8_t* codes, const uint8_t* sf
     if (k % 32 != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "k %lld is not divisible by block size 32", (long long)k);
     if (!y || !codes || !sf_rm) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
-    DISPATCH_DTYPE(y_dtype, mxfp8_dequant_kernel<T><<<grid_for(h, rows * k, 256, 16), 256, 0, h->stream>>>(codes, sf_rm, rows * k, (T*)y));
+    DISPATCH_DTYPE(y_dtype, oxq_launch(mxfp8_dequant_kernel<T>, grid_for(h, rows * k, 256, 16), 256, 0, h->stream, codes, sf_rm, rows * k, (T*)y));
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -878,7 +908,7 @@ int32_t oxq_nvfp4_quant(oxq_handle* h, const void* x, int dtype, int64_t rows, i
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     if (sf_mma && ((rows & 127) || ((k / 16) & 3)))
         OXQ_CUDA(h, cudaMemsetAsync(sf_mma, 0, oxq_sf_mma_bytes(rows, k / 16), h->stream));
-    DISPATCH_DTYPE(dtype, nvfp4_quant_kernel<T><<<grid_for(h, rows * k / (8 * BS_ILP) + 1, 256, 8), 256, 0, h->stream>>>((const T*)x, rows, k, stats, packed, sf_rm, sf_mma));
+    DISPATCH_DTYPE(dtype, oxq_launch(nvfp4_quant_kernel<T>, grid_for(h, rows * k / (8 * BS_ILP) + 1, 256, 8), 256, 0, h->stream, (const T*)x, rows, k, stats, packed, sf_rm, sf_mma));
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -890,7 +920,7 @@ int32_t oxq_nvfp4_dequant(oxq_handle* h, const uint8_t* packed, const uint8_t* s
     if (k % 16 != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "k %lld is not divisible by block size 16", (long long)k);
     if (!y || !packed || !sf_rm || !stats) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
-    DISPATCH_DTYPE(y_dtype, nvfp4_dequant_kernel<T><<<grid_for(h, rows * k, 256, 16), 256, 0, h->stream>>>(packed, sf_rm, stats, rows * k, (T*)y));
+    DISPATCH_DTYPE(y_dtype, oxq_launch(nvfp4_dequant_kernel<T>, grid_for(h, rows * k, 256, 16), 256, 0, h->stream, packed, sf_rm, stats, rows * k, (T*)y));
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

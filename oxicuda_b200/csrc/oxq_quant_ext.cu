@@ -43,6 +43,8 @@ __device__ __forceinline__ uint32_t quant_i8_rne(float x, const InvDiv& d) {
 template <typename T>
 __global__ void __launch_bounds__(256) int8_tensor_quant_kernel(const T* __restrict__ x, int64_t n, const float* __restrict__ absmax,
                                                                 int8_t* __restrict__ q, float* __restrict__ scale_out) {
+    pdl_trigger();
+    pdl_wait();
     const float sc = fmaxf(__fdiv_rn(*absmax, 127.0f), 1e-12f);
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = sc;
     const InvDiv d = make_invdiv(sc);
@@ -64,6 +66,8 @@ __global__ void __launch_bounds__(256) int8_tensor_quant_kernel(const T* __restr
 template <typename T>
 __global__ void __launch_bounds__(256) int8_tensor_dequant_kernel(const int8_t* __restrict__ q, int64_t n, const float* __restrict__ scale,
                                                                   T* __restrict__ y) {
+    pdl_trigger();
+    pdl_wait();
     const float sc = *scale;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         y[i] = Elem<T>::from_f32((float)q[i] * sc);
@@ -77,6 +81,8 @@ __global__ void __launch_bounds__(256) int8_tensor_dequant_kernel(const int8_t* 
 // block in L1 / L2.
 __global__ void __launch_bounds__(256) int8_block_quant_kernel(const float* __restrict__ x, int64_t n, int64_t block, int64_t nblocks,
                                                                int8_t* __restrict__ q, float* __restrict__ scales) {
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t b = warp0; b < nblocks; b += nwarps) {
@@ -97,6 +103,8 @@ __global__ void __launch_bounds__(256) int8_block_quant_kernel(const float* __re
 
 __global__ void __launch_bounds__(256) int8_block_dequant_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales, int64_t n,
                                                                  int64_t block, float* __restrict__ y) {
+    pdl_trigger();
+    pdl_wait();
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
         y[i] = (float)q[i] * __ldg(scales + i / block);
 }
@@ -125,6 +133,8 @@ __device__ __forceinline__ uint32_t nearest_nf4(float v, const float* lut) {
 template <int LPB>
 __global__ void __launch_bounds__(256) nf4_quant_kernel(const float* __restrict__ x, int64_t n, uint8_t* __restrict__ packed,
                                                         float* __restrict__ absmaxs) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float lut[16];                                 // lanes look up different levels: shared memory, not the constant bank
     if (threadIdx.x < 16) lut[threadIdx.x] = c_nf4[threadIdx.x];
     __syncthreads();
@@ -162,6 +172,8 @@ __global__ void __launch_bounds__(256) nf4_quant_kernel(const float* __restrict_
 // Any even block size: a warp per block, two elements (one byte) per lane and step.
 __global__ void __launch_bounds__(256) nf4_quant_generic_kernel(const float* __restrict__ x, int64_t nblocks, int64_t block,
                                                                 uint8_t* __restrict__ packed, float* __restrict__ absmaxs) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float lut[16];
     if (threadIdx.x < 16) lut[threadIdx.x] = c_nf4[threadIdx.x];
     __syncthreads();
@@ -184,6 +196,8 @@ __global__ void __launch_bounds__(256) nf4_quant_generic_kernel(const float* __r
 template <typename T>
 __global__ void __launch_bounds__(256) nf4_dequant_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ absmaxs, int64_t n,
                                                           int64_t block, T* __restrict__ y) {
+    pdl_trigger();
+    pdl_wait();
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         const uint32_t code = (packed[i >> 1] >> ((i & 1) * 4)) & 0xFu;
         y[i] = Elem<T>::from_f32(c_nf4[code] * __ldg(absmaxs + i / block));
@@ -198,6 +212,8 @@ __global__ void __launch_bounds__(256) nf4_dequant_kernel(const uint8_t* __restr
 // columns, CTAs along y split the rows; the partial maxima meet in `stats` (zero on entry) through integer
 // atomicMax on the bit patterns of the non-negative floats.
 __global__ void __launch_bounds__(256) col_absmax_kernel(const float* __restrict__ x, int64_t rows, int64_t cols, float* __restrict__ stats) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t c = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4;
     if (c >= cols) return;
     float4 m = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -219,6 +235,8 @@ __global__ void __launch_bounds__(256) col_absmax_kernel(const float* __restrict
 // s_j = max(|a_j|, 1e-8)^alpha / max(|w_j|, 1e-8)^(1 - alpha)
 __global__ void __launch_bounds__(256) smooth_scales_kernel(const float* __restrict__ a, const float* __restrict__ w, int64_t n, float alpha,
                                                             float* __restrict__ s) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= n) return;
     const float av = fmaxf(fabsf(a[j]), 1e-8f), wv = fmaxf(fabsf(w[j]), 1e-8f);
@@ -228,6 +246,8 @@ __global__ void __launch_bounds__(256) smooth_scales_kernel(const float* __restr
 // DIVIDE: x[r, j] /= max(s_j, 1e-12) (activations); otherwise x[r, j] *= s_j (weights).  In place.
 template <bool DIVIDE>
 __global__ void __launch_bounds__(256) smooth_apply_kernel(float* __restrict__ x, int64_t rows, int64_t cols, const float* __restrict__ s) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t total = rows * cols;
     if ((cols & 3) == 0) {
         const int64_t nvec = total >> 2, cv = cols >> 2;
@@ -254,6 +274,8 @@ __global__ void __launch_bounds__(256) smooth_apply_kernel(float* __restrict__ x
 // y[m, n] += bias[n] on a bf16 matrix with leading dimension ldy (f32 add, one rounding); 8 columns per thread.
 __global__ void __launch_bounds__(256) bias_add_bf16_kernel(__nv_bfloat16* __restrict__ y, int64_t ldy, const float* __restrict__ bias,
                                                             int64_t m, int64_t n) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t per_row = n >> 3;
     for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < m * per_row; t += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = t / per_row, c = (t - r * per_row) << 3;
@@ -303,7 +325,7 @@ int32_t oxq_int8_quant_tensor(oxq_handle* h, const void* x, int dtype, int64_t n
     if (!h->dev_scratch) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "handle has no reduction cells");
     float* absmax = reinterpret_cast<float*>(h->dev_scratch + 4);          // cells 0-1 belong to the reduction itself
     if (int32_t rc = oxq_absmax(h, x, dtype, n, absmax)) return rc;
-    DISPATCH_DTYPE(dtype, int8_tensor_quant_kernel<T><<<grid_cap(h, n / 8 + 1, 256, 8), 256, 0, h->stream>>>((const T*)x, n, absmax, q, scale_dev));
+    DISPATCH_DTYPE(dtype, oxq_launch(int8_tensor_quant_kernel<T>, grid_cap(h, n / 8 + 1, 256, 8), 256, 0, h->stream, (const T*)x, n, absmax, q, scale_dev));
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -314,7 +336,7 @@ int32_t oxq_int8_dequant_tensor(oxq_handle* h, const int8_t* q, const float* sca
     if (n < 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "negative element count");
     if (!q || !scale_dev || !y) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
-    DISPATCH_DTYPE(y_dtype, int8_tensor_dequant_kernel<T><<<grid_cap(h, n, 256, 16), 256, 0, h->stream>>>(q, n, scale_dev, (T*)y));
+    DISPATCH_DTYPE(y_dtype, oxq_launch(int8_tensor_dequant_kernel<T>, grid_cap(h, n, 256, 16), 256, 0, h->stream, q, n, scale_dev, (T*)y));
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -327,7 +349,7 @@ int32_t oxq_int8_block_quant(oxq_handle* h, const float* x, int64_t n, int64_t b
     if (!x || !q || !scales) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     const int64_t nblocks = (n + block - 1) / block;
-    int8_block_quant_kernel<<<grid_cap(h, nblocks * 32, 256, 8), 256, 0, h->stream>>>(x, n, block, nblocks, q, scales);
+    oxq_launch(int8_block_quant_kernel, grid_cap(h, nblocks * 32, 256, 8), 256, 0, h->stream, x, n, block, nblocks, q, scales);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -339,7 +361,7 @@ int32_t oxq_int8_block_dequant(oxq_handle* h, const int8_t* q, const float* scal
     if (n < 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "negative element count");
     if (!q || !scales || !y) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
-    int8_block_dequant_kernel<<<grid_cap(h, n, 256, 16), 256, 0, h->stream>>>(q, scales, n, block, y);
+    oxq_launch(int8_block_dequant_kernel, grid_cap(h, n, 256, 16), 256, 0, h->stream, q, scales, n, block, y);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -354,7 +376,7 @@ int32_t oxq_smooth_col_absmax(oxq_handle* h, const float* x, int64_t rows, int64
     int64_t gy = ((int64_t)h->sm_count * 8 + gx - 1) / gx;
     if (gy > rows) gy = rows;
     if (gy > 65535) gy = 65535;
-    col_absmax_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, h->stream>>>(x, rows, cols, stats);
+    oxq_launch(col_absmax_kernel, dim3((unsigned)gx, (unsigned)gy), 256, 0, h->stream, x, rows, cols, stats);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -364,7 +386,7 @@ int32_t oxq_smooth_scales(oxq_handle* h, const float* act_max, const float* weig
     if (n <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "SmoothQuantMigrator::compute_migration_scales");
     if (!act_max || !weight_max || !scales) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
-    smooth_scales_kernel<<<(unsigned)((n + 255) / 256), 256, 0, h->stream>>>(act_max, weight_max, n, alpha, scales);
+    oxq_launch(smooth_scales_kernel, (unsigned)((n + 255) / 256), 256, 0, h->stream, act_max, weight_max, n, alpha, scales);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -375,8 +397,8 @@ int32_t oxq_smooth_apply(oxq_handle* h, float* x, int64_t rows, int64_t cols, co
     if (!x || !scales || !aligned16(x) || !aligned16(scales)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     const int grid = grid_cap(h, rows * cols / 4 + 1, 256, 8);
-    if (divide) smooth_apply_kernel<true><<<grid, 256, 0, h->stream>>>(x, rows, cols, scales);
-    else smooth_apply_kernel<false><<<grid, 256, 0, h->stream>>>(x, rows, cols, scales);
+    if (divide) oxq_launch(smooth_apply_kernel<true>, grid, 256, 0, h->stream, x, rows, cols, scales);
+    else oxq_launch(smooth_apply_kernel<false>, grid, 256, 0, h->stream, x, rows, cols, scales);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -386,7 +408,7 @@ int32_t oxq_bias_add_bf16(oxq_handle* h, void* y, int64_t ldy, const float* bias
     if (m <= 0 || n <= 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "dimensions must be non-zero");
     if (!y || !bias || !aligned16(y) || !aligned16(bias) || (n & 7) || (ldy & 7)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer, or n / ldy not a multiple of 8");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
-    bias_add_bf16_kernel<<<grid_cap(h, m * n / 8, 256, 8), 256, 0, h->stream>>>((__nv_bfloat16*)y, ldy, bias, m, n);
+    oxq_launch(bias_add_bf16_kernel, grid_cap(h, m * n / 8, 256, 8), 256, 0, h->stream, (__nv_bfloat16*)y, ldy, bias, m, n);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -400,11 +422,11 @@ int32_t oxq_nf4_quant(oxq_handle* h, const float* x, int64_t n, int64_t block, u
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     const bool vec = aligned16(x) && ((uintptr_t)packed & 3u) == 0;
     const int grid = grid_cap(h, n / 8 + 1, 256, 8);
-    if (vec && block == 32) nf4_quant_kernel<4><<<grid, 256, 0, h->stream>>>(x, n, packed, absmaxs);
-    else if (vec && block == 64) nf4_quant_kernel<8><<<grid, 256, 0, h->stream>>>(x, n, packed, absmaxs);
-    else if (vec && block == 128) nf4_quant_kernel<16><<<grid, 256, 0, h->stream>>>(x, n, packed, absmaxs);
-    else if (vec && block == 256) nf4_quant_kernel<32><<<grid, 256, 0, h->stream>>>(x, n, packed, absmaxs);
-    else nf4_quant_generic_kernel<<<grid_cap(h, (n / block) * 32, 256, 8), 256, 0, h->stream>>>(x, n / block, block, packed, absmaxs);
+    if (vec && block == 32) oxq_launch(nf4_quant_kernel<4>, grid, 256, 0, h->stream, x, n, packed, absmaxs);
+    else if (vec && block == 64) oxq_launch(nf4_quant_kernel<8>, grid, 256, 0, h->stream, x, n, packed, absmaxs);
+    else if (vec && block == 128) oxq_launch(nf4_quant_kernel<16>, grid, 256, 0, h->stream, x, n, packed, absmaxs);
+    else if (vec && block == 256) oxq_launch(nf4_quant_kernel<32>, grid, 256, 0, h->stream, x, n, packed, absmaxs);
+    else oxq_launch(nf4_quant_generic_kernel, grid_cap(h, (n / block) * 32, 256, 8), 256, 0, h->stream, x, n / block, block, packed, absmaxs);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -416,7 +438,7 @@ int32_t oxq_nf4_dequant(oxq_handle* h, const uint8_t* packed, const float* absma
     if (n % block != 0) OXQ_FAIL(h, OXQ_ERR_QUANT_DIMENSION_MISMATCH, "length %lld is not divisible by block size %lld", (long long)n, (long long)block);
     if (!packed || !absmaxs || !y) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
-    DISPATCH_DTYPE(y_dtype, nf4_dequant_kernel<T><<<grid_cap(h, n, 256, 16), 256, 0, h->stream>>>(packed, absmaxs, n, block, (T*)y));
+    DISPATCH_DTYPE(y_dtype, oxq_launch(nf4_dequant_kernel<T>, grid_cap(h, n, 256, 16), 256, 0, h->stream, packed, absmaxs, n, block, (T*)y));
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

@@ -621,20 +621,42 @@ __global__ void __launch_bounds__(256) mxfp8_dequant_kernel(const uint8_t* __res
         y[i] = Elem<T>::from_f32(e4m3_to_f32(codes[i]) * pow2_of((int)sf_rm[i >> 5] - 127));
 }
 
+// eight f32 -> eight E2M1 nibbles in one word (RNE, satfinite), element e at bits [4e, 4e+4)
+__device__ __forceinline__ uint32_t cvt_e2m1x8(const float (&q)[8]) {
+    uint32_t w;
+    asm("{ .reg .b8 t0, t1, t2, t3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n\t"
+        "mov.b32 %0, {t0, t1, t2, t3}; }"
+        : "=r"(w) : "f"(q[0]), "f"(q[1]), "f"(q[2]), "f"(q[3]), "f"(q[4]), "f"(q[5]), "f"(q[6]), "f"(q[7]));
+    return w;
+}
+
 // 8 elements per item, 2 adjacent lanes form one 16-element block; BS_ILP items per thread in flight.
+// A block's divisor g * ue4m3(s8) takes one of 127 values per launch: its reciprocal comes from a table in shared
+// memory instead of a reciprocal sequence per block, and the block's (row, column) for the tiled scale layout is
+// carried along instead of divided out.
 template <typename T>
 __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const T* __restrict__ x, int64_t rows, int64_t k, float* __restrict__ stats,
                                                           uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_rm,
                                                           uint8_t* __restrict__ sf_mma) {
     pdl_trigger();
     pdl_wait();
+    __shared__ float2 lut[128];                               // (divisor, its reciprocal; NaN = divide the slow way)
     const float tmax = stats[0];
     const float g = tmax > 0.0f ? __fdiv_rn(tmax, 448.0f * 6.0f) : 1.0f;
     if (blockIdx.x == 0 && threadIdx.x == 0) stats[1] = g;
+    if (threadIdx.x < 128) {
+        const InvDiv d = make_invdiv(g * e4m3_to_f32((uint8_t)threadIdx.x));
+        lut[threadIdx.x] = make_float2(d.s, d.fast ? d.y : __int_as_float(0x7FC00000));
+    }
+    __syncthreads();
     const InvDiv six_g = make_invdiv(6.0f * g);
     const int64_t nitems = rows * k / 8;
-    const int64_t sf_cols = k / 16;
-    const uint32_t sf_col_tiles = (uint32_t)((sf_cols + 3) / 4);
+    const uint32_t sf_cols = (uint32_t)(k / 16);
+    const uint32_t sf_col_tiles = (sf_cols + 3) / 4;
     const int lane = threadIdx.x & 31;
     const int64_t warp_global = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
     const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
@@ -649,6 +671,9 @@ __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const T* __restrict__ 
                 for (int e = 0; e < 8; e++) f[j][e] = 0.0f;
             }
         }
+        // (row, column) of this lane's first block; the next items are 16 blocks further each
+        uint32_t blk = (uint32_t)((base + lane) >> 1);                       // host guarantees < 2^31 blocks
+        uint32_t r = blk / sf_cols, c = blk - r * sf_cols;
 #pragma unroll
         for (int j = 0; j < BS_ILP; j++) {
             const int64_t t = base + j * 32 + lane;
@@ -656,25 +681,29 @@ __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const T* __restrict__ 
 #pragma unroll
             for (int e = 0; e < 8; e++) am = fmaxf(am, fabsf(f[j][e]));
             am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
-            if (t >= nitems) continue;
-            const uint8_t s8 = (uint8_t)(cvt_e4m3x2(div_exact_bounded(am, six_g), 0.0f) & 0xFF);      // am <= tensor max: quotient <= 448
-            uint32_t w = 0;
-            if (s8 == 0) {
+            if (t < nitems) {
+                const uint32_t s8 = cvt_e4m3x2(div_exact_bounded(am, six_g), 0.0f) & 0xFFu;       // am <= tensor max: quotient <= 448
+                uint32_t w = 0;
+                if (s8 == 0) {
 #pragma unroll
-                for (int e = 0; e < 8; e++) w |= ((__float_as_uint(f[j][e]) >> 28) & 8u) << (4 * e);
-            } else {
-                const InvDiv d = make_invdiv(g * e4m3_to_f32(s8));
+                    for (int e = 0; e < 8; e++) w |= ((__float_as_uint(f[j][e]) >> 28) & 8u) << (4 * e);
+                } else {
+                    const float2 le = lut[s8 & 127u];
+                    InvDiv d;
+                    d.s = le.x; d.y = le.y; d.fast = le.y == le.y;
+                    float q[8];
 #pragma unroll
-                for (int e = 0; e < 8; e += 2)
-                    w |= (uint32_t)cvt_e2m1x2(div_exact_bounded_signed(f[j][e], d), div_exact_bounded_signed(f[j][e + 1], d)) << (4 * e);   // |x| <= block max: no overflow
+                    for (int e = 0; e < 8; e++) q[e] = div_exact_bounded_signed(f[j][e], d);      // |x| <= block max: no overflow
+                    w = cvt_e2m1x8(q);
+                }
+                __stcs(reinterpret_cast<uint32_t*>(packed + t * 4), w);
+                if ((t & 1) == 0) {
+                    if (sf_rm) sf_rm[blk] = (uint8_t)s8;
+                    if (sf_mma) sf_mma[sf_mma_offset32(r, c, sf_col_tiles)] = (uint8_t)s8;
+                }
             }
-            __stcs(reinterpret_cast<uint32_t*>(packed + t * 4), w);
-            if ((t & 1) == 0) {
-                const uint32_t blk = (uint32_t)(t >> 1);                     // host guarantees < 2^31 blocks
-                const uint32_t r = blk / (uint32_t)sf_cols, c = blk - r * (uint32_t)sf_cols;
-                if (sf_rm) sf_rm[blk] = s8;
-                if (sf_mma) sf_mma[sf_mma_offset32(r, c, sf_col_tiles)] = s8;
-            }
+            blk += 16; c += 16;
+            while (c >= sf_cols) { c -= sf_cols; r++; }
         }
     }
 }

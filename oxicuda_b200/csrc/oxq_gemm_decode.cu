@@ -369,6 +369,16 @@ constexpr int W8_MT = 8;            // batch rows per pass
 constexpr int W8_KC = 1024;         // K elements staged per pass
 constexpr int W8_RPW = 2;           // weight rows per warp
 
+// four int8 codes of a word -> f32: the byte (xor 0x80, an unsigned 0..255) becomes the low mantissa byte of
+// 2^23, and 2^23 + 128 is subtracted; exact, and on the FMA pipe instead of the conversion unit
+__device__ __forceinline__ void i8x4_to_f32(uint32_t u, float (&f)[4]) {
+    const uint32_t v = u ^ 0x80808080u;
+    f[0] = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7540)) - 8388736.0f;
+    f[1] = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7541)) - 8388736.0f;
+    f[2] = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7542)) - 8388736.0f;
+    f[3] = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7543)) - 8388736.0f;
+}
+
 // Shared-memory order of the activation chunk: for each 512-wide block, [q][lane] float4 with
 // k = block*512 + lane*16 + 4q, so a lane's four float4 reads are conflict-free.
 __global__ void __launch_bounds__(256) w8a32_decode_kernel(const float* __restrict__ x, const int8_t* __restrict__ w,
@@ -388,6 +398,17 @@ __global__ void __launch_bounds__(256) w8a32_decode_kernel(const float* __restri
 
     for (int kc0 = 0; kc0 < k; kc0 += W8_KC) {
         const int kc = min(W8_KC, k - kc0);
+        // the chunk's weights are requested first: they travel from HBM while the activations are staged
+        uint4 wv[W8_KC / 512][W8_RPW];
+#pragma unroll
+        for (int kb = 0; kb < W8_KC / 512; kb++) {
+            const int koff = kc0 + kb * 512 + lane * 16;
+#pragma unroll
+            for (int r = 0; r < W8_RPW; r++) {
+                wv[kb][r] = make_uint4(0, 0, 0, 0);
+                if (row0 + r < n && kb * 512 < kc && koff < k) wv[kb][r] = ld_stream_u4(w + (size_t)(row0 + r) * k + koff);
+            }
+        }
         __syncthreads();
         for (int it = tid; it < W8_MT * (W8_KC / 4); it += 256) {
             const int j = it / (W8_KC / 4), f = it - j * (W8_KC / 4);      // f: float4 index inside the chunk
@@ -398,32 +419,27 @@ __global__ void __launch_bounds__(256) w8a32_decode_kernel(const float* __restri
             xs[j][blk * 128 + q * 32 + ln] = v;
         }
         __syncthreads();
-        for (int kb = 0; kb * 512 < kc; kb++) {
-            const int koff = kc0 + kb * 512 + lane * 16;
-            uint4 wv[W8_RPW];
 #pragma unroll
-            for (int r = 0; r < W8_RPW; r++) {
-                wv[r] = make_uint4(0, 0, 0, 0);
-                if (row0 + r < n && koff < k) wv[r] = ld_stream_u4(w + (size_t)(row0 + r) * k + koff);
-            }
+        for (int kb = 0; kb < W8_KC / 512; kb++) {
+            if (kb * 512 < kc) {
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-                float wf[W8_RPW][4];
-#pragma unroll
-                for (int r = 0; r < W8_RPW; r++) {
-                    const uint32_t u = q == 0 ? wv[r].x : (q == 1 ? wv[r].y : (q == 2 ? wv[r].z : wv[r].w));
-                    wf[r][0] = (float)(int8_t)(u & 0xFF); wf[r][1] = (float)(int8_t)((u >> 8) & 0xFF);
-                    wf[r][2] = (float)(int8_t)((u >> 16) & 0xFF); wf[r][3] = (float)(int8_t)(u >> 24);
-                }
-#pragma unroll
-                for (int j = 0; j < W8_MT; j++) {
-                    const float4 xv = xs[j][kb * 128 + q * 32 + lane];
+                for (int q = 0; q < 4; q++) {
+                    float wf[W8_RPW][4];
 #pragma unroll
                     for (int r = 0; r < W8_RPW; r++) {
-                        acc[r][j] = fmaf(wf[r][0], xv.x, acc[r][j]);
-                        acc[r][j] = fmaf(wf[r][1], xv.y, acc[r][j]);
-                        acc[r][j] = fmaf(wf[r][2], xv.z, acc[r][j]);
-                        acc[r][j] = fmaf(wf[r][3], xv.w, acc[r][j]);
+                        const uint32_t u = q == 0 ? wv[kb][r].x : (q == 1 ? wv[kb][r].y : (q == 2 ? wv[kb][r].z : wv[kb][r].w));
+                        i8x4_to_f32(u, wf[r]);
+                    }
+#pragma unroll
+                    for (int j = 0; j < W8_MT; j++) {
+                        const float4 xv = xs[j][kb * 128 + q * 32 + lane];
+#pragma unroll
+                        for (int r = 0; r < W8_RPW; r++) {
+                            acc[r][j] = fmaf(wf[r][0], xv.x, acc[r][j]);
+                            acc[r][j] = fmaf(wf[r][1], xv.y, acc[r][j]);
+                            acc[r][j] = fmaf(wf[r][2], xv.z, acc[r][j]);
+                            acc[r][j] = fmaf(wf[r][3], xv.w, acc[r][j]);
+                        }
                     }
                 }
             }

@@ -31,12 +31,21 @@ __device__ __forceinline__ void load8f<__half>(const __half* p, float (&f)[8]) {
     for (int i = 0; i < 4; i++) { const float2 v = __half22float2(h[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
 }
 
-// clamp(x / scale, -127, 127) rounded half to even, as an int8 code in the low byte
-__device__ __forceinline__ uint32_t quant_i8_rne(float x, const InvDiv& d) {
-    float v = div_exact(x, d);
-    v = fminf(fmaxf(v, -127.0f), 127.0f);                   // max / min drop a NaN operand: NaN -> -127 -> like the PTX max.f32
-    return __float_as_uint(v + 12582912.0f) & 0xFFu;        // RNE(v) in the low mantissa bits of v + 1.5 * 2^23
+// clamp(x / scale, -127, 127) rounded half to even, left in the low byte of the returned float's bit pattern.  The
+// scale comes from the tensor's own maximum, so finite inputs give quotients within +-127 (+ rounding) and only
+// the lower clamp is kept: it sends a NaN to -127, as the max.f32 of the reference's kernel does.  An Inf in the
+// tensor makes the scale Inf, which takes the true-division path.
+__device__ __forceinline__ uint32_t quant_i8_rne_bits(float x, const InvDiv& d) {
+    const float v = fminf(fmaxf(div_exact_bounded(x, d), -127.0f), 127.0f);
+    return __float_as_uint(v + 12582912.0f);                // RNE(v) in the low mantissa byte of v + 1.5 * 2^23
 }
+__device__ __forceinline__ uint32_t quant_i8_rne(float x, const InvDiv& d) { return quant_i8_rne_bits(x, d) & 0xFFu; }
+// low bytes of four words -> one word
+__device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t e) {
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, e, 0x0040), 0x5410);
+}
+
+constexpr int I8T_ILP = 4;                                  // items of 8 elements in flight per thread
 
 // scale[0] = max(absmax / 127, 1e-12); q = rint(clamp(x / scale, -127, 127)).  The maximum was left in
 // `absmax` (a cell of the handle) by the reduction kernel that ran just before on the same stream.
@@ -49,13 +58,22 @@ __global__ void __launch_bounds__(256) int8_tensor_quant_kernel(const T* __restr
     if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = sc;
     const InvDiv d = make_invdiv(sc);
     const int64_t nitems = n >> 3;
-    for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < nitems; t += (int64_t)gridDim.x * blockDim.x) {
-        float f[8];
-        load8f(x + t * 8, f);
-        uint2 o;
-        o.x = quant_i8_rne(f[0], d) | (quant_i8_rne(f[1], d) << 8) | (quant_i8_rne(f[2], d) << 16) | (quant_i8_rne(f[3], d) << 24);
-        o.y = quant_i8_rne(f[4], d) | (quant_i8_rne(f[5], d) << 8) | (quant_i8_rne(f[6], d) << 16) | (quant_i8_rne(f[7], d) << 24);
-        __stcs(reinterpret_cast<uint2*>(q + t * 8), o);
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t t0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t0 < nitems; t0 += stride * I8T_ILP) {
+        float f[I8T_ILP][8];
+#pragma unroll
+        for (int j = 0; j < I8T_ILP; j++)
+            if (t0 + j * stride < nitems) load8f(x + (t0 + j * stride) * 8, f[j]);
+#pragma unroll
+        for (int j = 0; j < I8T_ILP; j++) {
+            const int64_t t = t0 + j * stride;
+            if (t < nitems) {
+                uint2 o;
+                o.x = pack_low_bytes(quant_i8_rne_bits(f[j][0], d), quant_i8_rne_bits(f[j][1], d), quant_i8_rne_bits(f[j][2], d), quant_i8_rne_bits(f[j][3], d));
+                o.y = pack_low_bytes(quant_i8_rne_bits(f[j][4], d), quant_i8_rne_bits(f[j][5], d), quant_i8_rne_bits(f[j][6], d), quant_i8_rne_bits(f[j][7], d));
+                __stcs(reinterpret_cast<uint2*>(q + t * 8), o);
+            }
+        }
     }
     // ragged tail (n not a multiple of 8)
     if (blockIdx.x == 0) {
@@ -325,7 +343,7 @@ int32_t oxq_int8_quant_tensor(oxq_handle* h, const void* x, int dtype, int64_t n
     if (!h->dev_scratch) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "handle has no reduction cells");
     float* absmax = reinterpret_cast<float*>(h->dev_scratch + 4);          // cells 0-1 belong to the reduction itself
     if (int32_t rc = oxq_absmax(h, x, dtype, n, absmax)) return rc;
-    DISPATCH_DTYPE(dtype, oxq_launch(int8_tensor_quant_kernel<T>, grid_cap(h, n / 8 + 1, 256, 8), 256, 0, h->stream, (const T*)x, n, absmax, q, scale_dev));
+    DISPATCH_DTYPE(dtype, oxq_launch(int8_tensor_quant_kernel<T>, grid_cap(h, n / (8 * I8T_ILP) + 1, 256, 8), 256, 0, h->stream, (const T*)x, n, absmax, q, scale_dev));
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

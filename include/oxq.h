@@ -214,6 +214,11 @@ OXQ_API int32_t oxq_int8_block_dequant(oxq_handle* h, const int8_t* q_dev, const
 OXQ_API int32_t oxq_nf4_quant(oxq_handle* h, const float* x_dev, int64_t n, int64_t block, uint8_t* packed_dev, float* absmax_dev);
 OXQ_API int32_t oxq_nf4_dequant(oxq_handle* h, const uint8_t* packed_dev, const float* absmax_dev, int64_t n, int64_t block,
                                 void* y_dev, int y_dtype);
+/* RmsNorm::forward (crates/oxicuda-lm/src/layer/norm.rs:73-95; y = x / sqrt(mean(x^2) + eps) * weight) fused with the per-row
+ * symmetric INT8 quantizer of oxq_int8_quant_rows (half to even): the activation path in front of oxq_gemm_w8a8, one pass over
+ * the row.  cols % 8 == 0, cols <= 16384.  y_opt (same dtype as x) also receives the normalised row when it is not NULL. */
+OXQ_API int32_t oxq_rmsnorm_int8_quant_rows(oxq_handle* h, const void* x_dev, int dtype, const float* weight_dev, int64_t rows, int64_t cols,
+                                            float eps, int8_t* q_dev, float* scales_dev, void* y_opt_dev);
 /* SmoothQuantMigrator (crates/oxicuda-quant/src/scheme/smooth_quant.rs) on device buffers, f32 row-major:
  *   oxq_smooth_col_absmax  compute_act_stats / compute_weight_stats (:125-196): stats[j] = max_r |x[r, j]|;
  *   oxq_smooth_scales      compute_migration_scales (:84-113): s_j = max(|a_j|,1e-8)^alpha / max(|w_j|,1e-8)^(1-alpha);

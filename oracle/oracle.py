@@ -68,6 +68,7 @@ def lib():
         _lib.orc_f32_to_f16.argtypes = [C.c_float]
         _lib.orc_f32_to_bf16.argtypes = [C.c_float]
         _lib.orc_nf4_level.restype = C.c_float
+        _lib.orc_ref_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_float, C.c_void_p]
         _lib.orc_ref_smooth_scales.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_void_p]
         _lib.orc_ref_nearest_nf4.argtypes = [C.c_float]
         _lib.orc_ref_dnn_int8_dequant.argtypes = [C.c_void_p, C.c_size_t, C.c_float, C.c_void_p]
@@ -357,6 +358,17 @@ def ref_smooth_layer(acts, weights, alpha):
     """SmoothQuantMigrator::smooth_layer: (smoothed acts, smoothed weights, scales)."""
     sc = ref_smooth_scales(ref_smooth_col_absmax(acts), ref_smooth_col_absmax(weights), alpha)
     return ref_smooth_activations(acts, sc), ref_smooth_weights(weights, sc), sc
+
+
+def ref_rms_norm(x, weight, eps):
+    """RmsNorm::forward of the reference (f32, sequential sum of squares)."""
+    x = _c(x, np.float32)
+    w = _c(weight, np.float32)
+    if x.ndim != 2 or x.shape[1] != w.size:
+        raise OracleError(4)
+    out = np.zeros_like(x)
+    lib().orc_ref_rms_norm(_p(x), _p(w), _sz(x.shape[0]), _sz(x.shape[1]), C.c_float(eps), _p(out))
+    return out
 
 
 # --------------------------------------------------------------------------- spec quantizers

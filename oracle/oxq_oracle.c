@@ -711,6 +711,19 @@ void orc_ref_smooth_weights(float* w, const float* scales, size_t rows, size_t c
         for (size_t j = 0; j < cols; j++) w[r * cols + j] *= scales[j];
 }
 
+/* RmsNorm::forward (crates/oxicuda-lm/src/layer/norm.rs:73-95): per row, mean of squares summed left to right in
+ * f32, inv_rms = 1 / sqrt(mean_sq + eps), out = x * inv_rms * weight (two multiplications, in that order). */
+void orc_ref_rms_norm(const float* x, const float* weight, size_t rows, size_t dim, float eps, float* out) {
+    for (size_t t = 0; t < rows; t++) {
+        const float* row = x + t * dim;
+        float sum = 0.0f;
+        for (size_t i = 0; i < dim; i++) sum += row[i] * row[i];
+        float mean_sq = sum / (float)dim;
+        float inv_rms = 1.0f / sqrtf(mean_sq + eps);
+        for (size_t i = 0; i < dim; i++) out[t * dim + i] = row[i] * inv_rms * weight[i];
+    }
+}
+
 /* ------------------------------------------------------------------------- */
 
 /* Y[b,o] = bias[o] + sum_i X[b,i] * W[o,i], accumulated left to right in f32

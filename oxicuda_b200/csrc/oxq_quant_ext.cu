@@ -31,6 +31,31 @@ __device__ __forceinline__ void load8f<__half>(const __half* p, float (&f)[8]) {
     for (int i = 0; i < 4; i++) { const float2 v = __half22float2(h[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
 }
 
+// the same eight elements as raw 16-byte words (requested early, converted when needed)
+template <typename T> struct Raw8 { uint4 a; };
+template <> struct Raw8<float> { uint4 a, b; };
+template <typename T>
+__device__ __forceinline__ Raw8<T> load8raw(const T* p) {
+    Raw8<T> r;
+    r.a = __ldcs(reinterpret_cast<const uint4*>(p));
+    if constexpr (sizeof(T) == 4) r.b = __ldcs(reinterpret_cast<const uint4*>(p) + 1);
+    return r;
+}
+__device__ __forceinline__ void raw8_to_f32(const Raw8<float>& r, float (&f)[8]) {
+    f[0] = __uint_as_float(r.a.x); f[1] = __uint_as_float(r.a.y); f[2] = __uint_as_float(r.a.z); f[3] = __uint_as_float(r.a.w);
+    f[4] = __uint_as_float(r.b.x); f[5] = __uint_as_float(r.b.y); f[6] = __uint_as_float(r.b.z); f[7] = __uint_as_float(r.b.w);
+}
+__device__ __forceinline__ void raw8_to_f32(const Raw8<__nv_bfloat16>& r, float (&f)[8]) {
+    const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+}
+__device__ __forceinline__ void raw8_to_f32(const Raw8<__half>& r, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&r.a);
+#pragma unroll
+    for (int i = 0; i < 4; i++) { const float2 v = __half22float2(h[i]); f[2 * i] = v.x; f[2 * i + 1] = v.y; }
+}
+
 // clamp(x / scale, -127, 127) rounded half to even, left in the low byte of the returned float's bit pattern.  The
 // scale comes from the tensor's own maximum, so finite inputs give quotients within +-127 (+ rounding) and only
 // the lower clamp is kept: it sends a NaN to -127, as the max.f32 of the reference's kernel does.  An Inf in the
@@ -223,6 +248,116 @@ __global__ void __launch_bounds__(256) nf4_dequant_kernel(const uint8_t* __restr
 }
 
 // ------------------------------------------------------------------------------------------------
+// RMSNorm fused with the per-row INT8 quantizer (the activation path in front of a W8A8 GEMM)
+// ------------------------------------------------------------------------------------------------
+
+// One CTA per row at a time; the row (up to 256 * 8 * NV elements) stays in registers between the three phases:
+// sum of squares -> inv_rms, y = x * inv_rms * weight and its maximum -> scale, codes.  Two block reductions.
+__device__ __forceinline__ float block_reduce_sum(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = (threadIdx.x & 31) < 8 ? red[threadIdx.x & 31] : 0.0f;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    t = __shfl_sync(0xffffffffu, t, 0);
+    __syncthreads();
+    return t;
+}
+__device__ __forceinline__ float block_reduce_max(float v, float* red) {
+    v = warp_max(v);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = (threadIdx.x & 31) < 8 ? red[threadIdx.x & 31] : 0.0f;
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+    t = __shfl_sync(0xffffffffu, t, 0);
+    __syncthreads();
+    return t;
+}
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(256) rmsnorm_int8_rows_kernel(const T* __restrict__ x, const float* __restrict__ weight, int64_t rows,
+                                                                int64_t cols, float eps, int8_t* __restrict__ q, float* __restrict__ scales,
+                                                                T* __restrict__ y_out) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[8];
+    const int64_t nitems = cols >> 3;
+    Raw8<T> nxt[NV];                                          // the next row of this CTA, requested a row ahead
+    if ((int64_t)blockIdx.x < rows) {
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int64_t it = threadIdx.x + (int64_t)i * 256;
+            if (it < nitems) nxt[i] = load8raw(x + (int64_t)blockIdx.x * cols + it * 8);
+        }
+    }
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        float f[NV][8];
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int64_t it = threadIdx.x + (int64_t)i * 256;
+            if (it < nitems) {
+                raw8_to_f32(nxt[i], f[i]);
+#pragma unroll
+                for (int e = 0; e < 8; e++) ss = fmaf(f[i][e], f[i][e], ss);
+            }
+        }
+        if (row + gridDim.x < rows) {
+#pragma unroll
+            for (int i = 0; i < NV; i++) {
+                const int64_t it = threadIdx.x + (int64_t)i * 256;
+                if (it < nitems) nxt[i] = load8raw(x + (row + gridDim.x) * cols + it * 8);
+            }
+        }
+        ss = block_reduce_sum(ss, red);
+        const float inv_rms = __fdiv_rn(1.0f, sqrtf(__fdiv_rn(ss, (float)cols) + eps));
+        float am = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int64_t it = threadIdx.x + (int64_t)i * 256;
+            if (it < nitems) {
+                const float4 w0 = __ldg(reinterpret_cast<const float4*>(weight + it * 8)), w1 = __ldg(reinterpret_cast<const float4*>(weight + it * 8) + 1);
+                const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    f[i][e] = f[i][e] * inv_rms * wv[e];                   // the reference's order of the two multiplications
+                    am = fmaxf(am, fabsf(f[i][e]));
+                }
+                if (y_out) {
+                    T o[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) o[e] = Elem<T>::from_f32(f[i][e]);
+                    if (sizeof(T) == 4) {
+                        float4* yo = reinterpret_cast<float4*>(y_out + row * cols + it * 8);
+                        yo[0] = *reinterpret_cast<float4*>(&o[0]); yo[1] = *reinterpret_cast<float4*>(&o[4]);
+                    } else {
+                        *reinterpret_cast<uint4*>(y_out + row * cols + it * 8) = *reinterpret_cast<uint4*>(&o[0]);
+                    }
+                }
+            }
+        }
+        am = block_reduce_max(am, red);
+        // per-row symmetric INT8 as in the row quantizer: scale = max(absmax, 1e-8) / 127, codes rounded half to even
+        const float sc = __fdiv_rn(fmaxf(am, 1e-8f), 127.0f);
+        if (threadIdx.x == 0) scales[row] = sc;
+        const InvDiv d = make_invdiv(sc);
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int64_t it = threadIdx.x + (int64_t)i * 256;
+            if (it < nitems) {
+                uint2 o;
+                o.x = pack_low_bytes(quant_i8_rne_bits(f[i][0], d), quant_i8_rne_bits(f[i][1], d), quant_i8_rne_bits(f[i][2], d), quant_i8_rne_bits(f[i][3], d));
+                o.y = pack_low_bytes(quant_i8_rne_bits(f[i][4], d), quant_i8_rne_bits(f[i][5], d), quant_i8_rne_bits(f[i][6], d), quant_i8_rne_bits(f[i][7], d));
+                *reinterpret_cast<uint2*>(q + row * cols + it * 8) = o;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // SmoothQuant migration (per-channel scale folded from the activations into the weights)
 // ------------------------------------------------------------------------------------------------
 
@@ -380,6 +515,32 @@ int32_t oxq_int8_block_dequant(oxq_handle* h, const int8_t* q, const float* scal
     if (!q || !scales || !y) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     oxq_launch(int8_block_dequant_kernel, grid_cap(h, n, 256, 16), 256, 0, h->stream, q, scales, n, block, y);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_rmsnorm_int8_quant_rows(oxq_handle* h, const void* x, int dtype, const float* weight, int64_t rows, int64_t cols, float eps,
+                                    int8_t* q, float* scales, void* y_opt) {
+    OXQ_CHECK_HANDLE(h);
+    if (rows <= 0 || cols <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "rmsnorm: empty input");
+    if (cols % 8 != 0 || cols > 16384) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "rmsnorm + int8: cols must be a multiple of 8 and at most 16384, got %lld", (long long)cols);
+    if (!x || !weight || !q || !scales || !aligned16(x) || !aligned16(weight) || ((uintptr_t)q & 7u) || (y_opt && !aligned16(y_opt)))
+        OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (dtype == OXQ_F32 && ((cols * 4) & 31)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "f32 rows must be 32-byte multiples");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    const int64_t cap = (int64_t)h->sm_count * 6;
+    const int grid = (int)(rows < cap ? rows : cap);
+    const int nv = (int)((cols / 8 + 255) / 256);                            // items of 8 per thread
+#define LAUNCH_RN(TT, NVV) oxq_launch(rmsnorm_int8_rows_kernel<TT, NVV>, grid, 256, 0, h->stream, (const TT*)x, weight, rows, cols, eps, q, scales, (TT*)y_opt)
+#define PICK_RN(TT) do { if (nv <= 1) LAUNCH_RN(TT, 1); else if (nv <= 2) LAUNCH_RN(TT, 2); else if (nv <= 4) LAUNCH_RN(TT, 4); else LAUNCH_RN(TT, 8); } while (0)
+    switch (dtype) {
+        case OXQ_F32: PICK_RN(float); break;
+        case OXQ_BF16: PICK_RN(__nv_bfloat16); break;
+        case OXQ_F16: PICK_RN(__half); break;
+        default: OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "unknown dtype %d", dtype);
+    }
+#undef PICK_RN
+#undef LAUNCH_RN
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

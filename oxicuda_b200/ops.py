@@ -263,6 +263,22 @@ def nf4_dequant(packed: torch.Tensor, absmaxs: torch.Tensor, block: int = 64, dt
     return y
 
 
+def rmsnorm_int8_quant_rows(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, want_normed: bool = False):
+    """RmsNorm::forward (crates/oxicuda-lm/src/layer/norm.rs:73-95) fused with the per-row INT8 quantizer: returns
+    (codes int8 [rows x cols], scales f32 [rows]) and, if asked, the normalised activations in x's dtype."""
+    _chk(x, torch.float32, torch.bfloat16, torch.float16)
+    _chk(weight, torch.float32)
+    rows, cols = x.shape
+    if weight.numel() != cols:
+        from .errors import QuantError
+        raise QuantError("DimensionMismatch", f"expected {cols} weights, got {weight.numel()}", 4)
+    q = torch.empty((rows, cols), dtype=torch.int8, device=x.device)
+    sc = torch.empty(rows, dtype=torch.float32, device=x.device)
+    y = torch.empty_like(x) if want_normed else None
+    handle(x.device.index).call("oxq_rmsnorm_int8_quant_rows", _p(x), _DT[x.dtype], _p(weight), rows, cols, C.c_float(eps), _p(q), _p(sc), _p(y))
+    return (q, sc, y) if want_normed else (q, sc)
+
+
 class SmoothQuantMigrator:
     """SmoothQuantMigrator of the reference (crates/oxicuda-quant/src/scheme/smooth_quant.rs:54-293) on device tensors."""
 

@@ -168,3 +168,45 @@ def test_smooth_quant_reference_cases(ops, orc):  # crates/oxicuda-quant/src/sch
     sc = ops.SmoothQuantMigrator(0.5).smooth_layer(acts, w)
     a = acts.cpu().numpy()
     assert np.abs(a[:, 0]).max() / np.abs(a[:, 1]).max() < 100.0 and sc[0].item() > 1.0
+
+
+# ---- RMSNorm fused with the per-row INT8 quantizer -------------------------------------------------------
+
+@pytest.mark.parametrize("shape", [(1, 8), (7, 4096), (64, 8192), (300, 1000), (5, 16384)])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_rmsnorm_int8_rows(ops, orc, shape, dtype):
+    rows, cols = shape
+    x = orc.gaussian((rows, cols), 2.0, 21)
+    w = (1.0 + 0.1 * orc.gaussian((1, cols), 1.0, 22)).ravel().astype(np.float32)
+    if dtype == "bf16":
+        xb = _bf16_round(x)
+        x = xb.float().numpy()
+        xd = xb.cuda()
+    else:
+        xd = to_dev(x)
+    q, sc, y = ops.rmsnorm_int8_quant_rows(xd, to_dev(w), 1e-5, want_normed=True)
+    y_ref = orc.ref_rms_norm(x, w, 1e-5)                                   # sequential f32 sum of squares
+    q_ref, s_ref = orc.spec_int8_quant_rows(y_ref, orc.ROUND_HALF_EVEN)
+    # the sum of squares is reduced in a different order on the GPU: inv_rms agrees to a few ulp, so do y and the scales,
+    # and a code can differ by one where y / scale sits within that distance of a rounding boundary
+    yg = y.float().cpu().numpy()
+    tol = 2.0 ** -7 if dtype == "bf16" else 1e-5
+    assert np.abs(yg - y_ref).max() <= tol * np.abs(y_ref).max()
+    assert np.abs(sc.cpu().numpy() - s_ref).max() <= 1e-5 * s_ref.max()
+    dq = np.abs(q.cpu().numpy().astype(np.int32) - q_ref.astype(np.int32))
+    assert dq.max() <= 1 and (dq != 0).mean() <= 2e-3
+    # the codes are exactly the row quantizer's codes of the f32 values the kernel normalised to
+    if dtype == "f32":
+        q2, s2 = orc.spec_int8_quant_rows(yg, orc.ROUND_HALF_EVEN)
+        assert (q.cpu().numpy() == q2).all() and (sc.cpu().numpy() == s2).all()
+
+
+def test_rmsnorm_reference_cases(ops, orc):  # crates/oxicuda-lm/src/layer/norm.rs:186-227
+    from oxicuda_b200.errors import OxqError
+    x = to_dev(np.array([[3.0, 4.0, 0.0, 0.0, 0.0, 0.0, 0.0, 0.0]], np.float32))     # rms = sqrt(25 / 8)
+    q, sc, y = ops.rmsnorm_int8_quant_rows(x, torch.ones(8, device="cuda"), 1e-8, want_normed=True)
+    rms = np.sqrt(25.0 / 8.0)
+    assert np.allclose(y.cpu().numpy()[0, :3], [3.0 / rms, 4.0 / rms, 0.0], atol=1e-5)
+    assert q.cpu().tolist()[0][:3] == [95, 127, 0]
+    with pytest.raises(OxqError):
+        ops.rmsnorm_int8_quant_rows(x, torch.ones(4, device="cuda"))

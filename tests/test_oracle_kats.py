@@ -305,3 +305,15 @@ def test_smooth_quant_kats(orc):  # crates/oxicuda-quant/src/scheme/smooth_quant
     with pytest.raises(orc.OracleError) as e:
         orc.ref_smooth_scales(np.zeros(0, np.float32), np.zeros(0, np.float32), 0.5)
     assert e.value.name == "EmptyInput"
+
+
+def test_rms_norm_kats(orc):  # crates/oxicuda-lm/src/layer/norm.rs:186-227
+    out = orc.ref_rms_norm(np.array([[3.0, 4.0, 0.0, 0.0]], np.float32), np.ones(4, np.float32), 1e-8)
+    assert abs(out[0, 0] - 1.2) < 1e-5 and abs(out[0, 1] - 1.6) < 1e-5 and abs(out[0, 2]) < 1e-5      # rms = 2.5
+    out = orc.ref_rms_norm(np.ones((1, 2), np.float32), np.array([2.0, 0.5], np.float32), 1e-8)
+    assert abs(out[0, 0] - 2.0) < 1e-5 and abs(out[0, 1] - 0.5) < 1e-5
+    out = orc.ref_rms_norm(np.array([[1.0, 1.0], [2.0, 2.0]], np.float32), np.ones(2, np.float32), 1e-8)
+    assert np.allclose(out, 1.0, atol=1e-5)
+    with pytest.raises(orc.OracleError) as e:
+        orc.ref_rms_norm(np.ones((2, 3), np.float32), np.ones(4, np.float32), 1e-5)
+    assert e.value.name == "DimensionMismatch"

@@ -35,6 +35,7 @@ struct GemmParams {
     int sfa_row_tiles, sfb_row_tiles;
     int group_m;                      // M-tiles per rasterisation group (L2 reuse of the X panel)
     int debug_flags;                  // timing experiments only (bit 0: skip the scale-factor copies; results are wrong)
+    int full_tiles, tail_split;       // CTA-pair dense kernel: tiles done whole, and the number of N-parts of each remaining tile
     int32_t* status;
 };
 
@@ -69,6 +70,20 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     const int r = tile - g * per_group;
     tn = r / gm;
     tm = first_m + (r - tn * gm);
+}
+
+// Work items of the CTA-pair dense kernel.  The first `full_tiles` items are whole 256 x 256 tiles; every tile after
+// that (the last, partly filled wave) is cut along N into `tail_split` parts so that the pairs which would idle
+// take a share: part p of a tile holds, of each 128-column half, the columns [p * half, (p + 1) * half).
+struct WorkItem { int tile, part, n_cols; };                 // n_cols = 256 / tail_split for a part, else 256
+__device__ __forceinline__ WorkItem work_item(int w, int full_tiles, int tail_split) {
+    WorkItem it;
+    if (w < full_tiles) { it.tile = w; it.part = 0; it.n_cols = 256; return it; }
+    const int t = w - full_tiles;
+    it.tile = full_tiles + t / tail_split;
+    it.part = t - (t / tail_split) * tail_split;
+    it.n_cols = 256 / tail_split;
+    return it;
 }
 
 template <int KIND, int BN, int EPI>
@@ -397,6 +412,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
     const int tiles_m = (p.m + BM2 - 1) / BM2, tiles_n = (p.n + BN2 - 1) / BN2;
     const int num_tiles = tiles_m * tiles_n;
+    const int num_work = p.full_tiles + (num_tiles - p.full_tiles) * p.tail_split;
     const int num_kb = (p.k_bytes + BKB - 1) / BKB;
 
     if (threadIdx.x == 0) {
@@ -420,10 +436,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+            for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
+                const WorkItem wi = work_item(w, p.full_tiles, p.tail_split);
                 int tm, tn;
-                tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
-                const int m0 = tm * BM2 + (int)cta_rank * BM, n0 = tn * BN2 + (int)cta_rank * BM;
+                tile_coords(wi.tile, tiles_m, tiles_n, p.group_m, tm, tn);
+                // this CTA's rows of W: its 128-row half of the tile, from the part's offset on (the 128-row box reads
+                // past the part; the MMA uses the first n_cols / 2 rows)
+                const int m0 = tm * BM2 + (int)cta_rank * BM, n0 = tn * BN2 + (int)cta_rank * BM + wi.part * (wi.n_cols >> 1);
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                     // the full barrier of the pair lives in CTA 0 and expects the bytes of both CTAs
@@ -438,13 +457,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (one lane of CTA 0)
         if (lane == 0 && cta_rank == 0) {
-            constexpr uint32_t idesc =
-                KIND == KIND_F8 ? idesc_dense(1, 0, 0, BM2, BN2) :
-                KIND == KIND_BF16 ? idesc_dense(1, 1, 1, BM2, BN2) : idesc_dense(2, 1, 1, BM2, BN2);
+            constexpr uint32_t cf = KIND == KIND_I8 ? 2 : 1, af = KIND == KIND_F8 ? 0 : 1;
             int stage = 0; uint32_t phase = 0;
             int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
-            for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+            for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
+                const uint32_t idesc = idesc_dense(cf, af, af, BM2, (uint32_t)work_item(w, p.full_tiles, p.tail_split).n_cols);
                 if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN2;
@@ -476,10 +494,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         float tensor_scale = 1.0f;
         if (KIND == KIND_F8) tensor_scale = __ldg(p.s0) * __ldg(p.s1);
         __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y);
-        for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
+        for (int w = cluster_id; w < num_work; w += num_clusters) {
+            const WorkItem wi = work_item(w, p.full_tiles, p.tail_split);
             int tm, tn;
-            tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
+            tile_coords(wi.tile, tiles_m, tiles_n, p.group_m, tm, tn);
             const int m0 = tm * BM2 + (int)cta_rank * BM, n0 = tn * BN2;
+            const int half = wi.n_cols >> 1;                 // accumulator columns [0, half) come from CTA 0's rows of W, [half, n_cols) from CTA 1's
             bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
@@ -490,20 +510,22 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             if (KIND == KIND_I8 && row < p.m) row_scale = __ldg(p.s0 + row);
             if (EPI == EPI_SWIGLU) {
 #pragma unroll 1
-                for (int c = 0; c < BN2 / 64; c++) {
+                for (int c = 0; c < half / 32; c++) {
                     uint32_t rg[32], ru[32];
                     tmem_ld_32x32b_x32(t_row + c * 32, rg);
-                    tmem_ld_32x32b_x32(t_row + BN2 / 2 + c * 32, ru);
+                    tmem_ld_32x32b_x32(t_row + half + c * 32, ru);
                     tmem_ld_wait();
-                    epilogue_store_swiglu(rg, ru, row, (n0 >> 1) + c * 32, p.n >> 1, p, tensor_scale, y);
+                    epilogue_store_swiglu(rg, ru, row, (n0 >> 1) + wi.part * half + c * 32, p.n >> 1, p, tensor_scale, y);
                 }
             } else {
 #pragma unroll 1
-                for (int c = 0; c < BN2 / 32; c++) {
+                for (int c = 0; c < wi.n_cols / 32; c++) {
                     uint32_t r[32];
                     tmem_ld_32x32b_x32(t_row + c * 32, r);
                     tmem_ld_wait();
-                    epilogue_store_scale<KIND>(r, row, n0 + c * 32, p, tensor_scale, row_scale, y);
+                    const int cc = c * 32;
+                    const int col0 = cc < half ? n0 + wi.part * half + cc : n0 + BM + wi.part * half + (cc - half);
+                    epilogue_store_scale<KIND>(r, row, col0, p, tensor_scale, row_scale, y);
                 }
             }
             tc_fence_before();
@@ -798,7 +820,20 @@ static int32_t launch2(oxq_handle* h, const void* x, int64_t ldx_bytes, const vo
         max_clusters = n < h->sm_count / 2 ? n : h->sm_count / 2;
     }
     const int tiles = ((p.m + 255) / 256) * ((p.n + 255) / 256);
-    const int clusters = tiles < max_clusters ? tiles : max_clusters;
+    // The last wave: r tiles for max_clusters pairs.  Each of them is cut along N into up to four parts (64 accumulator
+    // columns at least) so that the idle pairs take a share; OXQ_GEMM_TAIL_SPLIT caps the number of parts (1 = off).
+    static int split_cap = 0;
+    if (split_cap == 0) { const char* e = getenv("OXQ_GEMM_TAIL_SPLIT"); split_cap = e ? atoi(e) : 4; if (split_cap < 1) split_cap = 1; if (split_cap > 4) split_cap = 4; }
+    int clusters, full, split = 1;
+    if (tiles >= max_clusters) { clusters = max_clusters; full = (tiles / clusters) * clusters; } else { clusters = tiles; full = 0; }
+    const int rest = tiles - full;
+    if (rest > 0) {
+        int sp = max_clusters / rest;
+        if (sp > split_cap) sp = split_cap;
+        if (sp >= 4) split = 4; else if (sp >= 2) split = 2;
+        if (tiles < max_clusters) clusters = rest * split;
+    }
+    p.full_tiles = full; p.tail_split = split;
     p.status = h->dev_status;
     p.group_m = group_m_setting() / 2 > 0 ? group_m_setting() / 2 : 1;     // same panel height in rows as the 1-CTA walk
     oxq_launch(gemm_tc2_kernel<KIND, EPI>, 2 * clusters, NUM_THREADS, T2_SMEM_BYTES, h->stream, tm_a, tm_b, p);

@@ -244,6 +244,9 @@ OXQ_API int32_t oxq_gemm_nvfp4(oxq_handle* h, int64_t m, int64_t n, int64_t k, c
  *      rank's partial must be complete before the call starts anywhere, and nobody may read the result before every
  *      rank's call has finished.  numel % (8 * world) == 0. */
 OXQ_API int32_t oxq_multimem_all_reduce_bf16(oxq_handle* h, void* multicast_ptr, int64_t numel, int rank, int world);
+/* The same over a column block of a row-major bf16 matrix ([rows x cols] at multicast_ptr, leading dimension ld elements):
+ * rank r reduces rows [r * rows / world, (r + 1) * rows / world).  cols and ld multiples of 8, rows a multiple of world. */
+OXQ_API int32_t oxq_multimem_all_reduce_bf16_2d(oxq_handle* h, void* multicast_ptr, int64_t rows, int64_t cols, int64_t ld, int rank, int world);
 
 #ifdef __cplusplus
 }

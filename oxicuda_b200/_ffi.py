@@ -56,6 +56,7 @@ SIGNATURES = {
     "oxq_gemm_w4a16": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp, _vp, _sz]),
     "oxq_gemm_w4a16_static": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp]),
     "oxq_multimem_all_reduce_bf16": (_i32, [_vp, _vp, _i64, _int, _int]),
+    "oxq_multimem_all_reduce_bf16_2d": (_i32, [_vp, _vp, _i64, _i64, _i64, _int, _int]),
     "oxq_gemm_mxfp8": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _i64]),
     "oxq_gemm_nvfp4": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64]),
 }

@@ -32,7 +32,42 @@ __global__ void __launch_bounds__(512) multimem_all_reduce_bf16_kernel(uint4* mc
     for (; v < vec_hi; v += stride) mm_st(mc + v, mm_ld_reduce(mc + v));
 }
 
+// The same over a column range of a row-major matrix: rows [row_lo, row_hi) x vec_cols 16-byte vectors per row, rows
+// ld_vecs vectors apart (the all-reduce of one column block of the output while the GEMM still produces the next).
+__global__ void __launch_bounds__(512) multimem_all_reduce_bf16_2d_kernel(uint4* mc, int64_t row_lo, int64_t row_hi, int64_t vec_cols,
+                                                                          int64_t ld_vecs) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t total = (row_hi - row_lo) * vec_cols;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    auto at = [&](int64_t v) { const int64_t r = v / vec_cols; return mc + (row_lo + r) * ld_vecs + (v - r * vec_cols); };
+    int64_t v = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    for (; v + 3 * stride < total; v += 4 * stride) {
+        uint4* p0 = at(v); uint4* p1 = at(v + stride); uint4* p2 = at(v + 2 * stride); uint4* p3 = at(v + 3 * stride);
+        const uint4 a = mm_ld_reduce(p0), b = mm_ld_reduce(p1), c = mm_ld_reduce(p2), d = mm_ld_reduce(p3);
+        mm_st(p0, a); mm_st(p1, b); mm_st(p2, c); mm_st(p3, d);
+    }
+    for (; v < total; v += stride) { uint4* q = at(v); mm_st(q, mm_ld_reduce(q)); }
+}
+
 }  // namespace oxq
+
+extern "C" int32_t oxq_multimem_all_reduce_bf16_2d(oxq_handle* h, void* multicast_ptr, int64_t rows, int64_t cols, int64_t ld, int rank, int world) {
+    OXQ_CHECK_HANDLE(h);
+    if (rows <= 0 || cols <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "all_reduce: empty input");
+    if (world < 1 || rank < 0 || rank >= world) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "rank %d outside world of %d", rank, world);
+    if (!multicast_ptr || ((uintptr_t)multicast_ptr & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned multicast pointer");
+    if ((cols & 7) || (ld & 7) || ld < cols || rows % world != 0)
+        OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "cols and ld must be multiples of 8 elements, ld >= cols, rows a multiple of world");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    const int64_t per = rows / world, total = per * (cols / 8);
+    int64_t blocks = (total + 512 * 4 - 1) / (512 * 4);
+    if (blocks > h->sm_count) blocks = h->sm_count;
+    if (blocks < 1) blocks = 1;
+    oxq_launch(oxq::multimem_all_reduce_bf16_2d_kernel, (int)blocks, 512, 0, h->stream, (uint4*)multicast_ptr, per * rank, per * (rank + 1), cols / 8, ld / 8);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
 
 extern "C" int32_t oxq_multimem_all_reduce_bf16(oxq_handle* h, void* multicast_ptr, int64_t numel, int rank, int world) {
     OXQ_CHECK_HANDLE(h);

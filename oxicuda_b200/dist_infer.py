@@ -255,6 +255,7 @@ class TpSwiGluMlp:
         self._symm = None           # (buffer, handle) of the NVLS all-reduce path, created on first use
         import os
         self.use_multimem = tp > 1 and reduce_dtype == torch.bfloat16 and os.environ.get("OXQ_TP_NO_MULTIMEM", "0") != "1"
+        self.split_reduce = os.environ.get("OXQ_TP_SPLIT_REDUCE", "1") != "0"
 
     # -- NVLS path: symmetric output buffer mapped through the NVSwitch multicast object ----------
     def _symm_buffer(self, m: int):
@@ -291,6 +292,42 @@ class TpSwiGluMlp:
         hdl.barrier(channel=1)
         return y
 
+    def _forward_multimem_split(self, x: torch.Tensor):
+        """FP8 variant: the down-projection runs as two column blocks and the in-switch reduce of the first block
+        (on a side stream) overlaps the GEMM of the second.  Three barriers: before the first reduce, between the two
+        (all of block one is written everywhere, and every rank's block two is ready), after the second."""
+        m = x.shape[0]
+        sym = self._symm_buffer(m)
+        half = self.hidden // 2
+        if sym is None or self.variant != "fp8" or m % self.tp != 0 or half % 256 != 0:
+            return None
+        buf, hdl = sym
+        y = buf[:m]
+        ops = self.ops
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream()
+        main, comm = torch.cuda.current_stream(), self._comm_stream
+        xq, sx = ops.fp8_quant_dynamic(x)
+        h = ops.gemm_fp8_swiglu(xq, self.w_gu_q, sx[1:], self.s_gu)
+        hq, sh = ops.fp8_quant_dynamic(h)
+        ops.gemm_fp8(hq, self.w_down_q[:half], sh[1:], self.s_down, out=y[:, :half])
+        ev_a = torch.cuda.Event()
+        ev_a.record(main)
+        with torch.cuda.stream(comm):
+            comm.wait_event(ev_a)
+            hdl.barrier(channel=0)
+            ops.multimem_all_reduce_bf16_2d(hdl.multicast_ptr, m, half, self.hidden, self.rank, self.tp)
+        ops.gemm_fp8(hq, self.w_down_q[half:], sh[1:], self.s_down, out=y[:, half:])
+        ev_b = torch.cuda.Event()
+        ev_b.record(main)
+        with torch.cuda.stream(comm):
+            comm.wait_event(ev_b)
+            hdl.barrier(channel=1)
+            ops.multimem_all_reduce_bf16_2d(hdl.multicast_ptr + half * 2, m, half, self.hidden, self.rank, self.tp)
+            hdl.barrier(channel=2)
+        main.wait_stream(comm)
+        return y
+
     # -- local (per-rank) partial: [M x hidden] --------------------------------------------------
     def forward_partial(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         ops = self.ops
@@ -322,7 +359,9 @@ class TpSwiGluMlp:
         chunks = min(self.overlap_chunks, max(1, m // 256))
         if chunks <= 1:
             if self.use_multimem:
-                y = self._forward_multimem(x)
+                y = self._forward_multimem_split(x) if (self.split_reduce and m >= 512) else None
+                if y is None:
+                    y = self._forward_multimem(x)
                 if y is not None:
                     return y
             y = self.forward_partial(x)

@@ -457,3 +457,8 @@ def gemm_nvfp4(x_packed, x_sf_mma, x_stats, w_packed, w_sf_mma, w_stats, out: to
 def multimem_all_reduce_bf16(multicast_ptr: int, numel: int, rank: int, world: int, device_index: int | None = None):
     """In-place all-reduce over the multicast mapping of a symmetric bf16 buffer; the caller provides the barriers."""
     handle(device_index).call("oxq_multimem_all_reduce_bf16", C.c_void_p(multicast_ptr), numel, rank, world)
+
+
+def multimem_all_reduce_bf16_2d(multicast_ptr: int, rows: int, cols: int, ld: int, rank: int, world: int, device_index: int | None = None):
+    """In-place all-reduce of a [rows x cols] column block (leading dimension ld) of a symmetric bf16 matrix."""
+    handle(device_index).call("oxq_multimem_all_reduce_bf16_2d", C.c_void_p(multicast_ptr), rows, cols, ld, rank, world)

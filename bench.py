@@ -407,14 +407,17 @@ def run_tp_mlp(args, torch, world, rank, local_rank, peaks):
         t_compute = layer.flops(m) / world / (fp8_peak * 1e12)
         t_link = 2.0 * (world - 1) / world * m * HIDDEN * 2 / 770e9
         target = max(t_compute, t_link)
-        kernels_per_step = (min(chunks, m // 256) if world > 1 else 1) * 7
+        # this library's kernels per step: absmax + quantize (x), gate/up GEMM, absmax + quantize (h), down GEMM, reduce;
+        # with the split reduce the down GEMM and the reduce run twice (the cross-rank barriers are torch's kernels)
+        split = world > 1 and chunks <= 1 and bool(layer.use_multimem) and bool(getattr(layer, "split_reduce", False)) and m >= 512
+        kernels_per_step = 9 if split else (min(chunks, m // 256) if world > 1 else 1) * 7
         line = {
             "metric": "quant_gemm_tflops_prefill", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp8_e4m3" if variant == "fp8" else "w4a16", "data": "synthetic",
             "config": {"workload": f"tp_swiglu_mlp_{variant}_hidden8192_inter28672_m{m}", "parallelism": f"tp{world}",
                        "all_reduce": "in-switch (multimem.ld_reduce / multimem.st over the NVLS mapping) when available, else NCCL bf16",
-                       "multimem": bool(layer.use_multimem), "cuda_graph": graphed, "m_chunks": chunks,
+                       "multimem": bool(layer.use_multimem), "split_reduce": split, "cuda_graph": graphed, "m_chunks": chunks,
                        "l2": "weights per rank exceed the 126 MB L2 up to tp8 (88 MB FP8 per rank at tp8 plus activations)"},
             "roofline": {"bound": "tensor", "achieved": value, "peak": fp8_peak * world, "unit": "TFLOP/s", "frac": value / (fp8_peak * world),
                          "traffic": None, "target_ms": target * 1e3, "frac_of_target": target * 1e3 / ms,

@@ -75,7 +75,7 @@ def test_int8_run_twice_identical(ops, orc):
 
 # ------------------------------------------------------------------------------------------- FP8
 
-@pytest.mark.parametrize("n", [64 * 256, 16, 1000003, 17])
+@pytest.mark.parametrize("n", [64 * 256, 16, 1000003, 17, 8192 * 4096 + 5])       # the last one takes the single-launch path (>= 48 MB)
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
 def test_fp8_dynamic_bit_exact(ops, orc, n, dtype):
     x = orc.gaussian(n, 1.0, 0)
@@ -96,6 +96,9 @@ def test_fp8_dynamic_bit_exact(ops, orc, n, dtype):
     assert np.array_equal(deq, orc.spec_fp8_dequant(q_ref, float(sc)))
     am2 = ops.absmax(xd).cpu().numpy()[0]
     assert am2 == np.float32(am)
+    q2, stats2 = ops.fp8_quant_dynamic(xd)                       # the reduction cells are back to zero: a second call agrees
+    assert torch.equal(q, q2) and torch.equal(stats, stats2)
+    assert ops.handle().device_status() == 0
 
 
 def test_fp8_golden_and_special_values(ops, orc):

@@ -409,7 +409,7 @@ def run_tp_mlp(args, torch, world, rank, local_rank, peaks):
         target = max(t_compute, t_link)
         # this library's kernels per step: absmax + quantize (x), gate/up GEMM, absmax + quantize (h), down GEMM, reduce;
         # with the split reduce the down GEMM and the reduce run twice (the cross-rank barriers are torch's kernels)
-        split = world > 1 and chunks <= 1 and bool(layer.use_multimem) and bool(getattr(layer, "split_reduce", False)) and m >= 512
+        split = world > 1 and variant == "fp8" and chunks <= 1 and bool(layer.use_multimem) and bool(getattr(layer, "split_reduce", False)) and m >= 512
         kernels_per_step = 9 if split else (min(chunks, m // 256) if world > 1 else 1) * 7
         line = {
             "metric": "quant_gemm_tflops_prefill", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,

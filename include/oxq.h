@@ -151,6 +151,13 @@ OXQ_API int32_t oxq_gemm_fp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, con
  * its epilogue.  w_gu_dev holds the gate and up projection weights interleaved in blocks of 128 rows
  * ([gate rows 0..127][up rows 0..127][gate rows 128..255]...), n2 = 2 * intermediate rows in total (multiple of 256);
  * H[m x n2/2] = bf16(silu(g) * u) with g, u = the scaled gate / up products. */
+/* gemm's general form (crates/oxicuda-blas/src/level3/gemm_api.rs:73-82: C = alpha * op(A) * op(B) + beta * C) for the operand
+ * layout of this library (X row-major [M x K], W row-major [N x K], i.e. op(B) = W^T): Y = alpha * (X . W^T) * sx * sw + beta * Y,
+ * one rounding to bf16.  With beta == 0 the old contents of Y are not read (NaNs there do not propagate), as in BLAS. */
+OXQ_API int32_t oxq_gemm_fp8_ex(oxq_handle* h, int64_t m, int64_t n, int64_t k, float alpha, const uint8_t* x_dev, int64_t ldx,
+                        const uint8_t* w_dev, int64_t ldw, const float* sx_dev, const float* sw_dev, float beta, void* y_bf16_dev, int64_t ldy);
+OXQ_API int32_t oxq_gemm_bf16_ex(oxq_handle* h, int64_t m, int64_t n, int64_t k, float alpha, const void* x_bf16_dev, int64_t ldx,
+                         const void* w_bf16_dev, int64_t ldw, float beta, void* y_bf16_dev, int64_t ldy);
 OXQ_API int32_t oxq_gemm_fp8_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, const uint8_t* x_dev, int64_t ldx,
                             const uint8_t* w_gu_dev, int64_t ldw, const float* sx_dev, const float* sw_dev,
                             void* h_bf16_dev, int64_t ldh);

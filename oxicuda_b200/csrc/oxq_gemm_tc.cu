@@ -35,6 +35,7 @@ struct GemmParams {
     int sfa_row_tiles, sfb_row_tiles;
     int group_m;                      // M-tiles per rasterisation group (L2 reuse of the X panel)
     int debug_flags;                  // timing experiments only (bit 0: skip the scale-factor copies; results are wrong)
+    float alpha, beta;                // plain epilogue: y = alpha * (acc * scales) + beta * y (beta == 0: y is not read)
     int full_tiles, tail_split;       // CTA-pair dense kernel: tiles done whole, and the number of N-parts of each remaining tile
     int32_t* status;
 };
@@ -70,6 +71,76 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     const int r = tile - g * per_group;
     tn = r / gm;
     tm = first_m + (r - tn * gm);
+}
+
+template <int KIND>
+__device__ __forceinline__ void epilogue_store_scale(const uint32_t (&r)[32], int row, int col0, const GemmParams& p, float tensor_scale,
+                                                     float row_scale, __nv_bfloat16* y) {
+    if (row >= p.m || col0 >= p.n) return;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+        if (KIND == KIND_I8) v[j] = (float)(int)r[j] * (row_scale * (col0 + j < p.n ? __ldg(p.s1 + col0 + j) : 0.0f));
+        else v[j] = __uint_as_float(r[j]) * tensor_scale;
+    }
+    __nv_bfloat16* dst = y + (size_t)row * p.ldy + col0;
+    if (col0 + 32 <= p.n) {
+        if (p.beta != 0.0f) {                                    // gemm's beta * C term: read the old values, one rounding at the end
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint4 o = *reinterpret_cast<const uint4*>(dst + 8 * j);
+                const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    v[8 * j + 2 * e] = fmaf(p.beta, __uint_as_float(w[e] << 16), v[8 * j + 2 * e]);
+                    v[8 * j + 2 * e + 1] = fmaf(p.beta, __uint_as_float(w[e] & 0xFFFF0000u), v[8 * j + 2 * e + 1]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint4 o;
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
+            __nv_bfloat162 t1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+            __nv_bfloat162 t3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+            o.x = *reinterpret_cast<uint32_t*>(&t0); o.y = *reinterpret_cast<uint32_t*>(&t1);
+            o.z = *reinterpret_cast<uint32_t*>(&t2); o.w = *reinterpret_cast<uint32_t*>(&t3);
+            *reinterpret_cast<uint4*>(dst + 8 * j) = o;
+        }
+    } else {
+        for (int j = 0; j < 32 && col0 + j < p.n; j++) {
+            const float old = p.beta != 0.0f ? p.beta * __bfloat162float(dst[j]) : 0.0f;
+            dst[j] = __float2bfloat16_rn(v[j] + old);
+        }
+    }
+}
+
+__device__ __forceinline__ void epilogue_store_swiglu(const uint32_t (&rg)[32], const uint32_t (&ru)[32], int row, int col0, int out_n,
+                                                      const GemmParams& p, float tensor_scale, __nv_bfloat16* y) {
+    if (row >= p.m || col0 >= out_n) return;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+        const float gt = __uint_as_float(rg[j]) * tensor_scale, up = __uint_as_float(ru[j]) * tensor_scale;
+        v[j] = __fdividef(gt, 1.0f + __expf(-gt)) * up;
+    }
+    __nv_bfloat16* dst = y + (size_t)row * p.ldy + col0;
+    if (col0 + 32 <= out_n) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint4 o;
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
+            __nv_bfloat162 t1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+            __nv_bfloat162 t3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+            o.x = *reinterpret_cast<uint32_t*>(&t0); o.y = *reinterpret_cast<uint32_t*>(&t1);
+            o.z = *reinterpret_cast<uint32_t*>(&t2); o.w = *reinterpret_cast<uint32_t*>(&t3);
+            *reinterpret_cast<uint4*>(dst + 8 * j) = o;
+        }
+    } else {
+        for (int j = 0; j < 32 && col0 + j < out_n; j++) dst[j] = __float2bfloat16_rn(v[j]);
+    }
 }
 
 // Work items of the CTA-pair dense kernel.  The first `full_tiles` items are whole 256 x 256 tiles; every tile after
@@ -227,6 +298,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         int acc = 0; uint32_t acc_phase = 0;
         float tensor_scale = 1.0f;
         if (KIND == KIND_F8 || KIND == KIND_NVF4) tensor_scale = __ldg(p.s0) * __ldg(p.s1);
+        tensor_scale *= p.alpha;
         __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y);
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             int tm, tn;
@@ -239,7 +311,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const int row = m0 + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * C::kAccStride;
             float row_scale = 1.0f;
-            if (KIND == KIND_I8 && row < p.m) row_scale = __ldg(p.s0 + row);
+            if (KIND == KIND_I8 && row < p.m) row_scale = __ldg(p.s0 + row) * p.alpha;
             if (EPI == EPI_SWIGLU) {
                 // columns [0, BN/2) of the tile are gate, [BN/2, BN) the matching up columns
                 const int out_n = p.n >> 1;
@@ -277,36 +349,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
             } else {
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(t_row + c * 32, r);
-                tmem_ld_wait();
-                const int col0 = n0 + c * 32;
-                if (row < p.m && col0 < p.n) {
-                    float v[32];
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        if (KIND == KIND_I8) v[j] = (float)(int)r[j] * (row_scale * (col0 + j < p.n ? __ldg(p.s1 + col0 + j) : 0.0f));
-                        else v[j] = __uint_as_float(r[j]) * tensor_scale;
-                    }
-                    __nv_bfloat16* dst = y + (size_t)row * p.ldy + col0;
-                    if (col0 + 32 <= p.n) {
-#pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            uint4 o;
-                            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
-                            __nv_bfloat162 t1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-                            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
-                            __nv_bfloat162 t3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
-                            o.x = *reinterpret_cast<uint32_t*>(&t0); o.y = *reinterpret_cast<uint32_t*>(&t1);
-                            o.z = *reinterpret_cast<uint32_t*>(&t2); o.w = *reinterpret_cast<uint32_t*>(&t3);
-                            *reinterpret_cast<uint4*>(dst + 8 * j) = o;
-                        }
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < p.n; j++) dst[j] = __float2bfloat16_rn(v[j]);
-                    }
+                for (int c = 0; c < BN / 32; c++) {
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(t_row + c * 32, r);
+                    tmem_ld_wait();
+                    epilogue_store_scale<KIND>(r, row, n0 + c * 32, p, tensor_scale, row_scale, y);
                 }
-            }
             }
             tc_fence_before();
             __syncwarp();
@@ -336,61 +384,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 constexpr int T2_STAGES = 7;
 constexpr int T2_STAGE_BYTES = 2 * BM * BKB;                      // 16 KB of X + 16 KB of W per CTA
 constexpr int T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + 2048;
-
-template <int KIND>
-__device__ __forceinline__ void epilogue_store_scale(const uint32_t (&r)[32], int row, int col0, const GemmParams& p, float tensor_scale,
-                                                     float row_scale, __nv_bfloat16* y) {
-    if (row >= p.m || col0 >= p.n) return;
-    float v[32];
-#pragma unroll
-    for (int j = 0; j < 32; j++) {
-        if (KIND == KIND_I8) v[j] = (float)(int)r[j] * (row_scale * (col0 + j < p.n ? __ldg(p.s1 + col0 + j) : 0.0f));
-        else v[j] = __uint_as_float(r[j]) * tensor_scale;
-    }
-    __nv_bfloat16* dst = y + (size_t)row * p.ldy + col0;
-    if (col0 + 32 <= p.n) {
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            uint4 o;
-            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
-            __nv_bfloat162 t1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
-            __nv_bfloat162 t3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
-            o.x = *reinterpret_cast<uint32_t*>(&t0); o.y = *reinterpret_cast<uint32_t*>(&t1);
-            o.z = *reinterpret_cast<uint32_t*>(&t2); o.w = *reinterpret_cast<uint32_t*>(&t3);
-            *reinterpret_cast<uint4*>(dst + 8 * j) = o;
-        }
-    } else {
-        for (int j = 0; j < 32 && col0 + j < p.n; j++) dst[j] = __float2bfloat16_rn(v[j]);
-    }
-}
-
-__device__ __forceinline__ void epilogue_store_swiglu(const uint32_t (&rg)[32], const uint32_t (&ru)[32], int row, int col0, int out_n,
-                                                      const GemmParams& p, float tensor_scale, __nv_bfloat16* y) {
-    if (row >= p.m || col0 >= out_n) return;
-    float v[32];
-#pragma unroll
-    for (int j = 0; j < 32; j++) {
-        const float gt = __uint_as_float(rg[j]) * tensor_scale, up = __uint_as_float(ru[j]) * tensor_scale;
-        v[j] = __fdividef(gt, 1.0f + __expf(-gt)) * up;
-    }
-    __nv_bfloat16* dst = y + (size_t)row * p.ldy + col0;
-    if (col0 + 32 <= out_n) {
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            uint4 o;
-            __nv_bfloat162 t0 = __floats2bfloat162_rn(v[8 * j + 0], v[8 * j + 1]);
-            __nv_bfloat162 t1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-            __nv_bfloat162 t2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
-            __nv_bfloat162 t3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
-            o.x = *reinterpret_cast<uint32_t*>(&t0); o.y = *reinterpret_cast<uint32_t*>(&t1);
-            o.z = *reinterpret_cast<uint32_t*>(&t2); o.w = *reinterpret_cast<uint32_t*>(&t3);
-            *reinterpret_cast<uint4*>(dst + 8 * j) = o;
-        }
-    } else {
-        for (int j = 0; j < 32 && col0 + j < out_n; j++) dst[j] = __float2bfloat16_rn(v[j]);
-    }
-}
 
 template <int KIND, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
@@ -493,6 +486,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         int acc = 0; uint32_t acc_phase = 0;
         float tensor_scale = 1.0f;
         if (KIND == KIND_F8) tensor_scale = __ldg(p.s0) * __ldg(p.s1);
+        tensor_scale *= p.alpha;
         __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y);
         for (int w = cluster_id; w < num_work; w += num_clusters) {
             const WorkItem wi = work_item(w, p.full_tiles, p.tail_split);
@@ -507,7 +501,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             const int row = m0 + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN2;
             float row_scale = 1.0f;
-            if (KIND == KIND_I8 && row < p.m) row_scale = __ldg(p.s0 + row);
+            if (KIND == KIND_I8 && row < p.m) row_scale = __ldg(p.s0 + row) * p.alpha;
             if (EPI == EPI_SWIGLU) {
 #pragma unroll 1
                 for (int c = 0; c < half / 32; c++) {
@@ -677,6 +671,7 @@ gemm_tc2_scaled_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
         int acc = 0; uint32_t acc_phase = 0;
         float tensor_scale = 1.0f;
         if (KIND == KIND_NVF4) tensor_scale = __ldg(p.s0) * __ldg(p.s1);
+        tensor_scale *= p.alpha;
         __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(p.y);
         for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
             int tm, tn;
@@ -912,15 +907,26 @@ using namespace oxq::tc;
 
 extern "C" {
 
-int32_t oxq_gemm_fp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x, int64_t ldx, const uint8_t* w, int64_t ldw,
-                     const float* sx, const float* sw, void* y, int64_t ldy) {
+static int32_t gemm_fp8_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x, int64_t ldx, const uint8_t* w, int64_t ldw,
+                             const float* sx, const float* sw, float alpha, float beta, void* y, int64_t ldy) {
     OXQ_CHECK_HANDLE(h);
     if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
     if (!sx || !sw) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
     if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
     GemmParams p{};
+    p.alpha = alpha; p.beta = beta;
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y; p.ldy = ldy; p.s0 = sx; p.s1 = sw;
     return launch_dense<KIND_F8>(h, x, ldx, w, ldw, p);
+}
+
+int32_t oxq_gemm_fp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x, int64_t ldx, const uint8_t* w, int64_t ldw,
+                     const float* sx, const float* sw, void* y, int64_t ldy) {
+    return gemm_fp8_impl(h, m, n, k, x, ldx, w, ldw, sx, sw, 1.0f, 0.0f, y, ldy);
+}
+
+int32_t oxq_gemm_fp8_ex(oxq_handle* h, int64_t m, int64_t n, int64_t k, float alpha, const uint8_t* x, int64_t ldx, const uint8_t* w, int64_t ldw,
+                        const float* sx, const float* sw, float beta, void* y, int64_t ldy) {
+    return gemm_fp8_impl(h, m, n, k, x, ldx, w, ldw, sx, sw, alpha, beta, y, ldy);
 }
 
 int32_t oxq_gemm_fp8_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, const uint8_t* x, int64_t ldx, const uint8_t* w_gu, int64_t ldw,
@@ -931,18 +937,30 @@ int32_t oxq_gemm_fp8_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, con
     if (!sx || !sw) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
     if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
     GemmParams p{};
+    p.alpha = 1.0f; p.beta = 0.0f;
     p.m = (int)m; p.n = (int)n2; p.k_bytes = (int)k; p.y = hout; p.ldy = ldh; p.s0 = sx; p.s1 = sw;
     return launch_dense<KIND_F8, EPI_SWIGLU>(h, x, ldx, w_gu, ldw, p);
 }
 
-int32_t oxq_gemm_bf16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, int64_t ldx, const void* w, int64_t ldw,
-                      void* y, int64_t ldy) {
+static int32_t gemm_bf16_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                              float alpha, float beta, void* y, int64_t ldy) {
     OXQ_CHECK_HANDLE(h);
     if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
     if ((k & 7) || ldx < k || ldw < k || (ldx & 7) || (ldw & 7)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 8 and ld >= k");
     GemmParams p{};
+    p.alpha = alpha; p.beta = beta;
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)(2 * k); p.y = y; p.ldy = ldy;
     return launch_dense<KIND_BF16>(h, x, 2 * ldx, w, 2 * ldw, p);
+}
+
+int32_t oxq_gemm_bf16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                      void* y, int64_t ldy) {
+    return gemm_bf16_impl(h, m, n, k, x, ldx, w, ldw, 1.0f, 0.0f, y, ldy);
+}
+
+int32_t oxq_gemm_bf16_ex(oxq_handle* h, int64_t m, int64_t n, int64_t k, float alpha, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                         float beta, void* y, int64_t ldy) {
+    return gemm_bf16_impl(h, m, n, k, x, ldx, w, ldw, alpha, beta, y, ldy);
 }
 
 int32_t oxq_gemm_bf16_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, const void* x, int64_t ldx, const void* w_gu, int64_t ldw,
@@ -952,6 +970,7 @@ int32_t oxq_gemm_bf16_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, co
     if (int32_t rc = check_gemm_args(h, m, n2 / 2, k, x, w_gu, hout, ldh)) return rc;
     if ((k & 7) || ldx < k || ldw < k || (ldx & 7) || (ldw & 7)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 8 and ld >= k");
     GemmParams p{};
+    p.alpha = 1.0f; p.beta = 0.0f;
     p.m = (int)m; p.n = (int)n2; p.k_bytes = (int)(2 * k); p.y = hout; p.ldy = ldh;
     return launch_dense<KIND_BF16, EPI_SWIGLU>(h, x, 2 * ldx, w_gu, 2 * ldw, p);
 }
@@ -963,6 +982,7 @@ int32_t oxq_gemm_w8a8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const int8
     if (!sx_rows || !sw_rows) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
     if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
     GemmParams p{};
+    p.alpha = 1.0f; p.beta = 0.0f;
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y; p.ldy = ldy; p.s0 = sx_rows; p.s1 = sw_rows;
     return launch_dense<KIND_I8>(h, x, ldx, w, ldw, p);
 }
@@ -974,6 +994,7 @@ int32_t oxq_gemm_mxfp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uin
     if (!sfx || !sfw || ((uintptr_t)sfx & 15u) || ((uintptr_t)sfw & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned scale-factor pointer");
     if (k & 127) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k must be a multiple of 128 for the MXFP8 GEMM");
     GemmParams p{};
+    p.alpha = 1.0f; p.beta = 0.0f;
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y; p.ldy = ldy;
     p.sfa = sfx; p.sfb = sfw; p.sf_col_tiles = (int)(k / 32 + 3) / 4;
     p.sfa_row_tiles = (int)((m + 127) / 128); p.sfb_row_tiles = (int)((n + 127) / 128);
@@ -988,6 +1009,7 @@ int32_t oxq_gemm_nvfp4(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uin
     if (!sfx || !sfw || !gx || !gw || ((uintptr_t)sfx & 15u) || ((uintptr_t)sfw & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned scale pointer");
     if (k & 255) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k must be a multiple of 256 for the NVFP4 GEMM");
     GemmParams p{};
+    p.alpha = 1.0f; p.beta = 0.0f;
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)(k / 2); p.y = y; p.ldy = ldy; p.s0 = gx; p.s1 = gw;
     p.sfa = sfx; p.sfb = sfw; p.sf_col_tiles = (int)(k / 16 + 3) / 4;
     p.sfa_row_tiles = (int)((m + 127) / 128); p.sfb_row_tiles = (int)((n + 127) / 128);

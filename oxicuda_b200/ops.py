@@ -354,6 +354,23 @@ def gemm_fp8(x_q, w_q, sx, sw, out: torch.Tensor | None = None):
     return y
 
 
+def gemm_fp8_ex(alpha: float, x_q, w_q, sx, sw, beta: float, y: torch.Tensor):
+    """In place Y = alpha * (X . W^T) * sx * sw + beta * Y (gemm's general form, crates/oxicuda-blas/src/level3/gemm_api.rs:73-82)."""
+    m, k = x_q.shape
+    n = w_q.shape[0]
+    handle(x_q.device.index).call("oxq_gemm_fp8_ex", m, n, k, C.c_float(alpha), _p(x_q), x_q.stride(0), _p(w_q), w_q.stride(0), _p(sx), _p(sw),
+                                  C.c_float(beta), _p(y), y.stride(0))
+    return y
+
+
+def gemm_bf16_ex(alpha: float, x, w, beta: float, y: torch.Tensor):
+    """In place Y = alpha * (X . W^T) + beta * Y on bf16 matrices."""
+    m, k = x.shape
+    n = w.shape[0]
+    handle(x.device.index).call("oxq_gemm_bf16_ex", m, n, k, C.c_float(alpha), _p(x), x.stride(0), _p(w), w.stride(0), C.c_float(beta), _p(y), y.stride(0))
+    return y
+
+
 def gemm_fp8_swiglu(x_q, w_gu_q, sx, sw, out: torch.Tensor | None = None):
     """H = bf16(silu(g) * u); w_gu_q holds gate/up rows interleaved in blocks of 128 (see interleave_gate_up)."""
     m, k = x_q.shape

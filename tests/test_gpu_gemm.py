@@ -137,6 +137,38 @@ def test_gemm_w8a32_config1(ops, orc, mnk):
     assert np.abs(y - ref).max() <= 1e-4 * scale                     # f32 path: only the summation order differs
 
 
+@pytest.mark.parametrize("mnk", [(128, 256, 128), (300, 520, 384), (1024, 1024, 1024), (16, 264, 2048), (2048, 2304, 512)])
+@pytest.mark.parametrize("ab", [(2.0, 0.0), (1.0, 1.0), (-0.5, 0.75)])
+def test_gemm_alpha_beta(ops, orc, mnk, ab):
+    """gemm's general form: Y = alpha * (X . W^T) * scales + beta * Y, for the FP8 and bf16 kernels (1-CTA, CTA-pair, split tail)."""
+    m, n, k = mnk
+    alpha, beta = ab
+    xb = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 0))
+    wb = orc.f32_to_bf16_bits(orc.gaussian((n, k), 1.0, 1))
+    y0b = orc.f32_to_bf16_bits(orc.gaussian((m, n), 5.0, 2))
+    x, w = bf16_dev(xb), bf16_dev(wb)
+    y0 = orc.bf16_bits_to_f32(y0b)
+    # bf16
+    y = bf16_dev(y0b).clone()
+    if beta == 0.0:
+        y.fill_(float("nan"))                                 # beta == 0: the old contents must not be read
+    ops.gemm_bf16_ex(alpha, x, w, beta, y)
+    ref = alpha * (orc.bf16_bits_to_f32(xb).astype(np.float64) @ orc.bf16_bits_to_f32(wb).astype(np.float64).T) + beta * y0
+    _check(_bf16_to_np(y), ref.astype(np.float32), f"bf16 alpha/beta {mnk} {ab}")
+    # fp8
+    xq, sx = ops.fp8_quant_dynamic(x)
+    wq, sw = ops.fp8_quant_dynamic(w)
+    y = bf16_dev(y0b).clone()
+    if beta == 0.0:
+        y.fill_(float("nan"))
+    ops.gemm_fp8_ex(alpha, xq, wq, sx[1:], sw[1:], beta, y)
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    acc = orc.e4m3_to_f32(xq.cpu().numpy()).astype(np.float64) @ orc.e4m3_to_f32(wq.cpu().numpy()).astype(np.float64).T
+    ref = alpha * acc * (float(sx[1]) * float(sw[1])) + beta * y0
+    _check(_bf16_to_np(y), ref.astype(np.float32), f"fp8 alpha/beta {mnk} {ab}")
+
+
 # ------------------------------------------------------------------------------------------- W4A16
 
 @pytest.mark.parametrize("m", [1, 8, 32, 5, 17, 9, 16])

@@ -52,6 +52,16 @@ inline void gemm_fp8(const BlasHandle& h, const MatrixDesc<E4M3>& a, const Matri
                          reinterpret_cast<const uint8_t*>(b_nk.ptr), b_nk.ld, scale_a_dev, scale_b_dev, c_bf16.ptr, c_bf16.ld));
 }
 
+// The general form of gemm_api.rs:73-82, C = alpha * A * B^T * scales + beta * C; C is not read when beta == 0.
+inline void gemm_fp8(const BlasHandle& h, float alpha, const MatrixDesc<E4M3>& a, const MatrixDesc<E4M3>& b_nk, const float* scale_a_dev,
+                     const float* scale_b_dev, float beta, MatrixDescMut<uint16_t>& c_bf16) {
+    if (a.rows == 0 || b_nk.rows == 0 || a.cols == 0) throw BlasError(OXQ_ERR_INVALID_DIMENSION, "GEMM dimensions must be non-zero");
+    if (a.cols != b_nk.cols) throw BlasError(OXQ_ERR_DIMENSION_MISMATCH, "inner dimensions of op(A) and op(B) do not match");
+    if (c_bf16.rows != a.rows || c_bf16.cols != b_nk.rows) throw BlasError(OXQ_ERR_DIMENSION_MISMATCH, "C shape does not match the GEMM result");
+    h.check(oxq_gemm_fp8_ex(h.raw(), a.rows, b_nk.rows, a.cols, alpha, reinterpret_cast<const uint8_t*>(a.ptr), a.ld,
+                            reinterpret_cast<const uint8_t*>(b_nk.ptr), b_nk.ld, scale_a_dev, scale_b_dev, beta, c_bf16.ptr, c_bf16.ld));
+}
+
 // Int4GemmConfig (precision/int_ops.rs:215-355): validate() keeps the reference's rules.
 struct Int4GemmConfig {
     uint32_t m, n, k, group_size;

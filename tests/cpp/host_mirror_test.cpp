@@ -42,6 +42,9 @@ int main(int argc, char** argv) {
         int berr = 0;
         try { oxicuda_blas::gemm_fp8(bh, a, b, nullptr, nullptr, cm); } catch (const oxicuda_blas::BlasError& e) { berr = e.variant == "InvalidDimension"; }
         if (!berr) return 8;
+        berr = 0;
+        try { oxicuda_blas::gemm_fp8(bh, 2.0f, a, b, nullptr, nullptr, 1.0f, cm); } catch (const oxicuda_blas::BlasError& e) { berr = e.variant == "InvalidDimension"; }
+        if (!berr) return 8;
         // Nf4Quantizer: the reference's round-trip, all-zero and error tests (nf4.rs:243-310)
         {
             Nf4Quantizer nq(64);

@@ -51,6 +51,7 @@ enum {
     OXQ_ERR_QUANT_DIMENSION_MISMATCH = 4,
     OXQ_ERR_NON_FINITE_FP8 = 5,
     OXQ_ERR_INVALID_BIT_WIDTH = 6,
+    OXQ_ERR_SINGULAR_HESSIAN = 7,      /* QuantError::SingularHessian; raised by host wrappers that read `info` of oxq_gptq_quantize_layer */
     /* BlasError */
     OXQ_ERR_INVALID_DIMENSION = 10,
     OXQ_ERR_BUFFER_TOO_SMALL = 11,
@@ -254,6 +255,27 @@ OXQ_API int32_t oxq_multimem_all_reduce_bf16(oxq_handle* h, void* multicast_ptr,
 /* The same over a column block of a row-major bf16 matrix ([rows x cols] at multicast_ptr, leading dimension ld elements):
  * rank r reduces rows [r * rows / world, (r + 1) * rows / world).  cols and ld multiples of 8, rows a multiple of world. */
 OXQ_API int32_t oxq_multimem_all_reduce_bf16_2d(oxq_handle* h, void* multicast_ptr, int64_t rows, int64_t cols, int64_t ld, int rank, int world);
+
+/* ---- GPTQ weight preparation -------------------------------------------------------------------------------------
+ * GptqQuantizer::quantize_layer (crates/oxicuda-quant/src/scheme/gptq.rs:133-257): dampen the Hessian by
+ * percdamp * max(|mean diag|, 1e-8), factor it (cholesky_lower, :281-300), invert the factor (invert_lower, :305-318),
+ * form H^-1 (hinv_row_starting, :328-332), then quantize column by column with per-column parameters
+ * (col_quant_params, :242-276) and push each column's error into the later columns.  All in f32 on the device with
+ * the reference's order of operations, so codes, scales and zero points equal the reference's bit for bit.
+ *   weights      [n_rows x n_cols] f32 row-major (not modified);   hessian [n_cols x n_cols] f32 row-major, symmetric
+ *   quantized    [n_rows x n_cols] i32;   scales [n_cols] f32;   zero_points [n_cols] i32 (0 when symmetric)
+ *   info         2 words: info[0] = 1 when the dampened Hessian is not positive definite (the reference's
+ *                SingularHessian; nothing else is written then), else 0; info[1] = bits of the smallest dampened
+ *                diagonal entry (SingularHessian's min_diag).  The call is asynchronous: read info after the stream.
+ *   workspace    oxq_gptq_workspace_bytes(n_rows, n_cols) bytes; on return its first n_cols^2 floats hold H^-1 (upper
+ *                triangle), the next n_cols^2 the inverse of the Cholesky factor.
+ * GptqConfig::block_size has no effect in the reference and has no parameter here.  The column loop runs as one
+ * cooperative launch (one meeting point of all CTAs per column, bounded wait); n_rows <= ~60000, n_cols <= 32768.
+ * Errors: EMPTY_INPUT (n_rows or n_cols == 0), INVALID_BIT_WIDTH (bits == 0 or > 16), BUFFER_TOO_SMALL. */
+OXQ_API int32_t oxq_gptq_workspace_bytes(int64_t n_rows, int64_t n_cols, size_t* bytes);
+OXQ_API int32_t oxq_gptq_quantize_layer(oxq_handle* h, const float* weights_dev, int64_t n_rows, int64_t n_cols, const float* hessian_dev,
+                                int bits, int symmetric, double percdamp, int32_t* quantized_dev, float* scales_dev,
+                                int32_t* zero_points_dev, int32_t* info_dev, void* workspace_dev, size_t workspace_bytes);
 
 #ifdef __cplusplus
 }

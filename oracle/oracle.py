@@ -25,7 +25,7 @@ ROUND_HALF_EVEN, ROUND_HALF_AWAY = 0, 1
 
 ERR_NAMES = {
     0: "Ok", 1: "EmptyInput", 2: "GroupSizeMismatch", 3: "InvalidScale", 4: "DimensionMismatch",
-    5: "NonFiniteFp8", 6: "InvalidBitWidth", 8: "InvalidArgument",
+    5: "NonFiniteFp8", 6: "InvalidBitWidth", 7: "SingularHessian", 8: "InvalidArgument",
 }
 
 
@@ -358,6 +358,71 @@ def ref_smooth_layer(acts, weights, alpha):
     """SmoothQuantMigrator::smooth_layer: (smoothed acts, smoothed weights, scales)."""
     sc = ref_smooth_scales(ref_smooth_col_absmax(acts), ref_smooth_col_absmax(weights), alpha)
     return ref_smooth_activations(acts, sc), ref_smooth_weights(weights, sc), sc
+
+
+def ref_cholesky_lower(h):
+    """cholesky_lower of gptq.rs; None when a pivot is not positive."""
+    h = _c(h, np.float32)
+    n = h.shape[0]
+    l = np.zeros((n, n), np.float32)
+    lib().orc_ref_cholesky_lower.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+    return None if lib().orc_ref_cholesky_lower(_p(h), _sz(n), _p(l)) else l
+
+
+def ref_invert_lower(l):
+    l = _c(l, np.float32)
+    n = l.shape[0]
+    li = np.zeros((n, n), np.float32)
+    lib().orc_ref_invert_lower.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+    lib().orc_ref_invert_lower(_p(l), _sz(n), _p(li))
+    return li
+
+
+def ref_hinv_upper(li):
+    """Rows of hinv_row_starting for every j, as the upper triangle of an n x n matrix."""
+    li = _c(li, np.float32)
+    n = li.shape[0]
+    hinv = np.zeros((n, n), np.float32)
+    lib().orc_ref_hinv_upper.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+    lib().orc_ref_hinv_upper(_p(li), _sz(n), _p(hinv))
+    return hinv
+
+
+def ref_gptq_columns(w, hinv, bits=4, symmetric=True):
+    """The column loop of quantize_layer on a given H^-1: (codes, scales, zero points, corrected weights)."""
+    w = _c(w, np.float32).copy()
+    n_rows, n_cols = w.shape
+    q = np.zeros((n_rows, n_cols), np.int32)
+    sc = np.zeros(n_cols, np.float32)
+    zp = np.zeros(n_cols, np.int32)
+    lib().orc_ref_gptq_columns.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib().orc_ref_gptq_columns(_p(w), _sz(n_rows), _sz(n_cols), _p(_c(hinv, np.float32)), bits, int(symmetric), _p(q), _p(sc), _p(zp))
+    return q, sc, zp, w
+
+
+def ref_gptq_quantize_layer(weights, n_rows, n_cols, hessian, bits=4, symmetric=True, percdamp=0.01):
+    """GptqQuantizer::quantize_layer: (codes [n_rows, n_cols] i32, scales [n_cols], zero points [n_cols])."""
+    w = _c(weights, np.float32).ravel()
+    h = _c(hessian, np.float32).ravel()
+    if w.size == 0:
+        raise OracleError(1)
+    if w.size != n_rows * n_cols or h.size != n_cols * n_cols:
+        raise OracleError(4)
+    q = np.zeros((n_rows, n_cols), np.int32)
+    sc = np.zeros(n_cols, np.float32)
+    zp = np.zeros(n_cols, np.int32)
+    md = C.c_float(0.0)
+    fn = lib().orc_ref_gptq_quantize_layer
+    fn.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_int, C.c_int, C.c_double, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    rc = fn(_p(w), _sz(n_rows), _sz(n_cols), _p(h), bits, int(symmetric), C.c_double(percdamp), _p(q), _p(sc), _p(zp), C.byref(md))
+    if rc:
+        raise OracleError(rc)
+    return q, sc, zp
+
+
+def gptq_dequantize(q, sc, zp):
+    """GptqOutput::dequantize: (q - zp) as f32 * scale per column."""
+    return (q.astype(np.float32) - zp.astype(np.float32)[None, :]) * sc[None, :]
 
 
 def ref_rms_norm(x, weight, eps):

@@ -28,6 +28,7 @@
 #include <math.h>
 #include <stdint.h>
 #include <stddef.h>
+#include <stdlib.h>
 #include <string.h>
 #ifdef _OPENMP
 #include <omp.h>
@@ -709,6 +710,141 @@ void orc_ref_smooth_activations(float* x, const float* scales, size_t rows, size
 void orc_ref_smooth_weights(float* w, const float* scales, size_t rows, size_t cols) {
     for (size_t r = 0; r < rows; r++)
         for (size_t j = 0; j < cols; j++) w[r * cols + j] *= scales[j];
+}
+
+/* ------------------------------------------------------------------------- */
+/* GPTQ (crates/oxicuda-quant/src/scheme/gptq.rs)                              */
+
+/* cholesky_lower (gptq.rs:281-300): row by row, s = h[i][j] minus the products l[i][k] * l[j][k] in increasing k,
+ * each product and each subtraction rounded on its own.  Returns 0, or 1 when a pivot is <= 0. */
+int orc_ref_cholesky_lower(const float* h, size_t n, float* l) {
+    memset(l, 0, n * n * sizeof(float));
+    for (size_t i = 0; i < n; i++) {
+        for (size_t j = 0; j <= i; j++) {
+            float s = h[i * n + j];
+            for (size_t k = 0; k < j; k++) s -= l[i * n + k] * l[j * n + k];
+            if (i == j) {
+                if (s <= 0.0f) return 1;
+                l[i * n + i] = sqrtf(s);
+            } else {
+                l[i * n + j] = s / l[j * n + j];
+            }
+        }
+    }
+    return 0;
+}
+
+/* invert_lower (gptq.rs:305-318): forward substitution, s starts at 0 and adds l[i][k] * li[k][j] for k = j .. i-1. */
+void orc_ref_invert_lower(const float* l, size_t n, float* li) {
+    memset(li, 0, n * n * sizeof(float));
+    for (size_t i = 0; i < n; i++) {
+        li[i * n + i] = 1.0f / l[i * n + i];
+        for (size_t j = 0; j < i; j++) {
+            float s = 0.0f;
+            for (size_t k = j; k < i; k++) s += l[i * n + k] * li[k * n + j];
+            li[i * n + j] = -s / l[i * n + i];
+        }
+    }
+}
+
+/* hinv_row_starting (gptq.rs:328-332) for every j: hinv[j][k] = sum over m = k .. n-1 of li[m][j] * li[m][k], k >= j,
+ * summed in increasing m.  Entries below the diagonal are left at zero. */
+void orc_ref_hinv_upper(const float* li, size_t n, float* hinv) {
+    memset(hinv, 0, n * n * sizeof(float));
+    for (size_t j = 0; j < n; j++)
+        for (size_t k = j; k < n; k++) {
+            float s = 0.0f;
+            for (size_t m = k; m < n; m++) s += li[m * n + j] * li[m * n + k];
+            hinv[j * n + k] = s;
+        }
+}
+
+static int32_t gptq_quant_scalar(float x, float scale, int32_t zp, int32_t q_min, int32_t q_max) {
+    /* quant_scalar (gptq.rs:235-239) */
+    return f32_as_i32(clampf(roundf(x / scale + (float)zp), (float)q_min, (float)q_max));
+}
+
+/* The column loop of GptqQuantizer::quantize_layer (gptq.rs:184-247) on a given upper-triangular H^-1: per-column
+ * parameters from the current (already corrected) column (col_quant_params, gptq.rs:242-276), round to nearest,
+ * error divided by the diagonal entry, and the correction of every later column, one rounded product and one rounded
+ * subtraction per element.  `w` is overwritten with the corrected weights. */
+void orc_ref_gptq_columns(float* w, size_t n_rows, size_t n_cols, const float* hinv, int bits, int symmetric,
+                          int32_t* quantized, float* scales, int32_t* zero_points) {
+    int32_t q_min, q_max;
+    if (symmetric) { q_min = -(1 << (bits - 1)); q_max = (1 << (bits - 1)) - 1; }
+    else { q_min = 0; q_max = (1 << bits) - 1; }
+    float* errs = (float*)malloc(n_rows * sizeof(float));
+    for (size_t j = 0; j < n_cols; j++) {
+        float scale; int32_t zp = 0;
+        if (symmetric) {
+            float am = 0.0f;
+            for (size_t i = 0; i < n_rows; i++) { float a = fabsf(w[i * n_cols + j]); if (a > am) am = a; }   /* f32::max skips NaN */
+            if (!(am > 1e-8f)) am = 1e-8f;
+            scale = am / (float)q_max;
+        } else {
+            float fmin = INFINITY, fmax = -INFINITY;
+            for (size_t i = 0; i < n_rows; i++) { float v = w[i * n_cols + j]; if (v < fmin) fmin = v; if (v > fmax) fmax = v; }
+            float range = fmax - fmin;
+            if (!(range > 1e-8f)) range = 1e-8f;
+            scale = range / (float)((1 << bits) - 1);
+            zp = f32_as_i32(clampf(roundf(-fmin / scale), (float)q_min, (float)q_max));
+        }
+        scales[j] = scale; zero_points[j] = zp;
+        const float hjj = hinv[j * n_cols + j];
+        if (hjj < 1e-12f) {
+            for (size_t i = 0; i < n_rows; i++) quantized[i * n_cols + j] = gptq_quant_scalar(w[i * n_cols + j], scale, zp, q_min, q_max);
+            continue;
+        }
+        for (size_t i = 0; i < n_rows; i++) {
+            const float wij = w[i * n_cols + j];
+            const int32_t q = gptq_quant_scalar(wij, scale, zp, q_min, q_max);
+            quantized[i * n_cols + j] = q;
+            const float q_dq = ((float)q - (float)zp) * scale;
+            errs[i] = (wij - q_dq) / hjj;
+        }
+        for (size_t k = j + 1; k < n_cols; k++) {
+            const float hjk = hinv[j * n_cols + k];
+            for (size_t i = 0; i < n_rows; i++) w[i * n_cols + k] -= errs[i] * hjk;
+        }
+    }
+    free(errs);
+}
+
+/* GptqQuantizer::quantize_layer (gptq.rs:133-257).  Returns 0, 1 (EmptyInput), 6 (InvalidBitWidth) or 7
+ * (SingularHessian, with *min_diag = the smallest dampened diagonal entry).  The length checks of the reference are
+ * the caller's (the wrapper raises DimensionMismatch). */
+int orc_ref_gptq_quantize_layer(const float* weights, size_t n_rows, size_t n_cols, const float* hessian, int bits, int symmetric,
+                                double percdamp, int32_t* quantized, float* scales, int32_t* zero_points, float* min_diag) {
+    if (n_rows * n_cols == 0) return ORC_ERR_EMPTY_INPUT;
+    if (bits <= 0 || bits > 16) return ORC_ERR_INVALID_BITS;
+    const size_t n = n_cols;
+    float sum = 0.0f;
+    for (size_t j = 0; j < n; j++) sum += hessian[j * n + j];
+    const float mean_diag = sum / (float)n;
+    float md = fabsf(mean_diag);
+    if (!(md > 1e-8f)) md = 1e-8f;
+    const float lambda = (float)percdamp * md;
+    float* hd = (float*)malloc(n * n * sizeof(float));
+    float* l = (float*)malloc(n * n * sizeof(float));
+    float* li = (float*)malloc(n * n * sizeof(float));
+    memcpy(hd, hessian, n * n * sizeof(float));
+    for (size_t j = 0; j < n; j++) hd[j * n + j] += lambda;
+    int rc = 0;
+    if (orc_ref_cholesky_lower(hd, n, l)) {
+        float m = INFINITY;
+        for (size_t j = 0; j < n; j++) if (hd[j * n + j] < m) m = hd[j * n + j];
+        if (min_diag) *min_diag = m;
+        rc = 7;
+    } else {
+        orc_ref_invert_lower(l, n, li);
+        orc_ref_hinv_upper(li, n, hd);
+        float* w = (float*)malloc(n_rows * n_cols * sizeof(float));
+        memcpy(w, weights, n_rows * n_cols * sizeof(float));
+        orc_ref_gptq_columns(w, n_rows, n_cols, hd, bits, symmetric, quantized, scales, zero_points);
+        free(w);
+    }
+    free(hd); free(l); free(li);
+    return rc;
 }
 
 /* RmsNorm::forward (crates/oxicuda-lm/src/layer/norm.rs:73-95): per row, mean of squares summed left to right in

@@ -54,6 +54,8 @@ SIGNATURES = {
     "oxq_gemm_bf16_swiglu": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64]),
     "oxq_gemm_w8a8": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64]),
     "oxq_gemm_w8a32": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp]),
+    "oxq_gptq_workspace_bytes": (_i32, [_i64, _i64, _vp]),
+    "oxq_gptq_quantize_layer": (_i32, [_vp, _vp, _i64, _i64, _vp, _int, _int, C.c_double, _vp, _vp, _vp, _vp, _vp, _sz]),
     "oxq_gemm_w4a16_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "oxq_gemm_w4a16": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp, _vp, _sz]),
     "oxq_gemm_w4a16_static": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp]),

@@ -16,6 +16,7 @@ const char* oxq_status_name(int32_t s) {
         case OXQ_ERR_QUANT_DIMENSION_MISMATCH: return "DimensionMismatch";
         case OXQ_ERR_NON_FINITE_FP8: return "NonFiniteFp8";
         case OXQ_ERR_INVALID_BIT_WIDTH: return "InvalidBitWidth";
+        case OXQ_ERR_SINGULAR_HESSIAN: return "SingularHessian";
         case OXQ_ERR_INVALID_DIMENSION: return "InvalidDimension";
         case OXQ_ERR_BUFFER_TOO_SMALL: return "BufferTooSmall";
         case OXQ_ERR_DIMENSION_MISMATCH: return "DimensionMismatch";

@@ -26,7 +26,7 @@ class DistInferError(OxqError):
 
 
 _QUANT = {1: "EmptyInput", 2: "GroupSizeMismatch", 3: "InvalidScale", 4: "DimensionMismatch", 5: "NonFiniteFp8",
-          6: "InvalidBitWidth"}
+          6: "InvalidBitWidth", 7: "SingularHessian"}
 _BLAS = {10: "InvalidDimension", 11: "BufferTooSmall", 12: "DimensionMismatch", 13: "UnsupportedOperation",
          14: "LaunchFailed", 15: "InvalidArgument", 100: "LaunchFailed"}
 

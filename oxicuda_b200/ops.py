@@ -335,6 +335,61 @@ class SmoothQuantMigrator:
         return sc
 
 
+class GptqConfig:
+    """GptqConfig of the reference (crates/oxicuda-quant/src/scheme/gptq.rs:30-54); block_size has no effect there or here."""
+
+    def __init__(self, bits: int = 4, block_size: int = 128, percdamp: float = 0.01, symmetric: bool = True):
+        self.bits, self.block_size, self.percdamp, self.symmetric = int(bits), int(block_size), float(percdamp), bool(symmetric)
+
+
+class GptqOutput:
+    """GptqOutput of the reference (gptq.rs:58-96) on device tensors: codes [n_rows, n_cols] i32, per-column scales and zero points."""
+
+    def __init__(self, quantized, scales, zero_points, n_rows, n_cols):
+        self.quantized, self.scales, self.zero_points, self.n_rows, self.n_cols = quantized, scales, zero_points, n_rows, n_cols
+
+    def dequantize(self) -> torch.Tensor:
+        return (self.quantized.to(torch.float32) - self.zero_points.to(torch.float32)[None, :]) * self.scales[None, :]
+
+    def reconstruction_mse(self, original: torch.Tensor) -> float:
+        return float(((self.dequantize() - original.reshape(self.n_rows, self.n_cols)) ** 2).mean())
+
+
+class GptqQuantizer:
+    """GptqQuantizer of the reference (gptq.rs:104-257) on device tensors; the whole layer is quantized on the GPU."""
+
+    def __init__(self, config: GptqConfig | None = None):
+        self.config = config or GptqConfig()
+        self.workspace: torch.Tensor | None = None      # kept after a call: H^-1 and the factor's inverse, for inspection
+
+    def quantize_layer(self, weights: torch.Tensor, n_rows: int, n_cols: int, hessian: torch.Tensor) -> GptqOutput:
+        from .errors import QuantError
+        if weights.numel() == 0:
+            raise QuantError("EmptyInput", "GptqQuantizer::quantize_layer", 1)
+        if weights.numel() != n_rows * n_cols:
+            raise QuantError("DimensionMismatch", f"expected {n_rows * n_cols}, got {weights.numel()}", 4)
+        if hessian.numel() != n_cols * n_cols:
+            raise QuantError("DimensionMismatch", f"expected {n_cols * n_cols}, got {hessian.numel()}", 4)
+        _chk(weights, torch.float32)
+        _chk(hessian, torch.float32)
+        dev = weights.device
+        nbytes = C.c_size_t(0)
+        raise_for_status(_ffi.load().oxq_gptq_workspace_bytes(n_rows, n_cols, C.byref(nbytes)))
+        ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+        q = torch.empty((n_rows, n_cols), dtype=torch.int32, device=dev)
+        sc = torch.empty(n_cols, dtype=torch.float32, device=dev)
+        zp = torch.empty(n_cols, dtype=torch.int32, device=dev)
+        info = torch.zeros(2, dtype=torch.int32, device=dev)
+        handle(dev.index).call("oxq_gptq_quantize_layer", _p(weights), n_rows, n_cols, _p(hessian), self.config.bits,
+                               1 if self.config.symmetric else 0, C.c_double(self.config.percdamp), _p(q), _p(sc), _p(zp), _p(info),
+                               _p(ws), nbytes.value)
+        host = info.cpu()                                 # the reference returns the error synchronously: wait for the stream
+        if int(host[0]) != 0:
+            raise QuantError("SingularHessian", f"min_diag = {float(host[1:2].view(torch.float32)[0]):.3e}", 7)
+        self.workspace = ws
+        return GptqOutput(q, sc, zp, n_rows, n_cols)
+
+
 def bias_add_(y: torch.Tensor, bias: torch.Tensor):
     """In place y[m, n] += bias[n] (bf16 matrix, f32 bias)."""
     _chk(bias, torch.float32)

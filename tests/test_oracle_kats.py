@@ -317,3 +317,39 @@ def test_rms_norm_kats(orc):  # crates/oxicuda-lm/src/layer/norm.rs:186-227
     with pytest.raises(orc.OracleError) as e:
         orc.ref_rms_norm(np.ones((2, 3), np.float32), np.ones(4, np.float32), 1e-5)
     assert e.value.name == "DimensionMismatch"
+
+
+def test_gptq_kats(orc):  # crates/oxicuda-quant/src/scheme/gptq.rs:341-520
+    l = orc.ref_cholesky_lower(np.array([[4.0, 2.0], [2.0, 3.0]], np.float32))          # L = [[2, 0], [1, sqrt 2]]
+    assert np.allclose(l, [[2.0, 0.0], [1.0, np.sqrt(2.0)]], atol=1e-6) and np.allclose(l @ l.T, [[4.0, 2.0], [2.0, 3.0]], atol=1e-5)
+    assert np.allclose(orc.ref_cholesky_lower(np.eye(4, dtype=np.float32)), np.eye(4), atol=1e-6)
+    l3 = np.array([[2.0, 0.0, 0.0], [1.0, 3.0, 0.0], [0.0, 2.0, 4.0]], np.float32)
+    assert np.allclose(l3 @ orc.ref_invert_lower(l3), np.eye(3), atol=1e-5)
+    with pytest.raises(orc.OracleError) as e:                                               # zero Hessian, no dampening
+        orc.ref_gptq_quantize_layer(np.full(4, 0.5, np.float32), 2, 2, np.zeros(4, np.float32), percdamp=0.0)
+    assert e.value.name == "SingularHessian"
+    with pytest.raises(orc.OracleError) as e:
+        orc.ref_gptq_quantize_layer(np.full(3, 0.5, np.float32), 1, 4, np.eye(4, dtype=np.float32))
+    assert e.value.name == "DimensionMismatch"
+    with pytest.raises(orc.OracleError) as e:
+        orc.ref_gptq_quantize_layer(np.full(4, 0.5, np.float32), 2, 2, np.eye(2, dtype=np.float32), bits=0)
+    assert e.value.name == "InvalidBitWidth"
+    w = (np.arange(32, dtype=np.float32) / np.float32(16.0) - np.float32(1.0)).reshape(4, 8)
+    q, sc, zp = orc.ref_gptq_quantize_layer(w, 4, 8, np.eye(8, dtype=np.float32), bits=8)
+    assert np.mean((orc.gptq_dequantize(q, sc, zp) - w) ** 2) < 1e-4                       # identity Hessian: round to nearest
+    q, sc, zp = orc.ref_gptq_quantize_layer(np.full((3, 6), 0.3, np.float32), 3, 6, np.eye(6, dtype=np.float32), bits=4)
+    assert q.shape == (3, 6) and sc.shape == (6,) and zp.shape == (6,)
+    w = np.array([-0.6, 0.4, -0.2, 0.8, 0.6, -0.4, 0.2, -0.8], np.float32).reshape(2, 4)
+    q, sc, zp = orc.ref_gptq_quantize_layer(w, 2, 4, np.eye(4, dtype=np.float32), bits=4, symmetric=False)
+    assert np.mean((orc.gptq_dequantize(q, sc, zp) - w) ** 2) < 0.05 and q.min() >= 0 and q.max() <= 15
+    # a diagonal Hessian has a diagonal inverse, so no error propagates: same codes as with the identity
+    rng = np.random.default_rng(3)
+    w = rng.standard_normal((16, 32)).astype(np.float32)
+    hd = np.diag(rng.uniform(0.5, 4.0, 32)).astype(np.float32)
+    q, sc, zp = orc.ref_gptq_quantize_layer(w, 16, 32, hd, bits=4)
+    qi, sci, zpi = orc.ref_gptq_quantize_layer(w, 16, 32, np.eye(32, dtype=np.float32), bits=4)
+    assert np.array_equal(q, qi) and np.array_equal(sc, sci)
+    # a dense Hessian does propagate: later columns change
+    x = rng.standard_normal((256, 32)).astype(np.float32)
+    q2, _, _ = orc.ref_gptq_quantize_layer(w, 16, 32, (2.0 * x.T @ x / 256.0).astype(np.float32), bits=4)
+    assert np.array_equal(q2[:, 0], qi[:, 0]) and not np.array_equal(q2, qi)

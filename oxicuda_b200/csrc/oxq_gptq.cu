@@ -40,8 +40,10 @@ __device__ __forceinline__ uint32_t ld_volatile(const uint32_t* p) { return *rei
 
 // lambda = percdamp * max(|mean(diag H)|, 1e-8) with the diagonal summed left to right (gptq.rs:163-165), and the
 // smallest dampened diagonal entry for the SingularHessian report (:172-176).
-__global__ void __launch_bounds__(256) gptq_prepare_kernel(const float* __restrict__ H, int n, float percdamp, uint32_t* ctl, int32_t* info) {
+__global__ void __launch_bounds__(256) gptq_prepare_kernel(const float* __restrict__ H, int n, float percdamp, uint32_t* ctl, int32_t* info,
+                                                           unsigned long long* slots, int nslots) {
     __shared__ float d[1024];
+    for (int t = threadIdx.x; t < nslots; t += 256) slots[t] = 0ull;
     float sum = 0.0f;
     for (int base = 0; base < n; base += 1024) {
         __syncthreads();
@@ -70,18 +72,13 @@ __global__ void __launch_bounds__(256) gptq_prepare_kernel(const float* __restri
     }
 }
 
-__global__ void __launch_bounds__(256) gptq_damp_kernel(const float* __restrict__ H, float* __restrict__ A, int n, const uint32_t* ctl,
-                                                        uint32_t* cells, int symmetric) {
+__global__ void __launch_bounds__(256) gptq_damp_kernel(const float* __restrict__ H, float* __restrict__ A, int n, const uint32_t* ctl) {
     const float lambda = __uint_as_float(ctl[CTL_LAMBDA]);
     const int64_t total = (int64_t)n * n;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / n, c = i - r * n;
         const float v = H[i];
         A[i] = r == c ? __fadd_rn(v, lambda) : v;
-        if (i < n) {
-            cells[2 * i] = symmetric ? 0u : order_key(__int_as_float(0xFF800000));      // running maximum
-            cells[2 * i + 1] = order_key(__int_as_float(0x7F800000));                   // running minimum
-        }
     }
 }
 
@@ -191,68 +188,83 @@ __global__ void __launch_bounds__(256) chol_trailing_kernel(float* __restrict__ 
         }
 }
 
-// Rows [ib, ib + 32) of L^-1 for 64 columns per CTA: the part of each sum that involves earlier row blocks first
-// (a small matrix product, k increasing), then the substitution inside the block, one thread per column.
-__global__ void __launch_bounds__(256) invl_block_kernel(const float* __restrict__ L, float* __restrict__ LI, int n, int ib, const uint32_t* ctl) {
+// The inverse of the factor, right-looking by blocks of 32 rows.  Until a row block is finished, LI[i][j] holds
+// the running sum s of invert_lower (gptq.rs:310-314); the trailing kernel below adds a finished block's 32 terms
+// to every later row, in increasing k, and this kernel finishes rows [ib, ib + 32): the terms inside the block and
+// the division by the diagonal, one thread per column.
+__global__ void __launch_bounds__(64) invl_diag_kernel(const float* __restrict__ L, float* __restrict__ LI, int n, int ib, const uint32_t* ctl) {
     if (ld_volatile(ctl + CTL_FAIL)) return;
-    __shared__ __align__(16) float Lp[NB][NB + 4];
-    __shared__ float LIp[NB][64];
-    __shared__ float S[NB][64];
     __shared__ float Ld[NB][NB + 1];
-    const int jc = blockIdx.x * 64;
+    __shared__ float X[NB][64];
     const int bh = min(NB, n - ib);
-    const int c = threadIdx.x & 63, g = threadIdx.x >> 6;
-    float acc[8];
-#pragma unroll
-    for (int u = 0; u < 8; u++) acc[u] = 0.0f;
-    for (int k0 = jc; k0 < ib; k0 += NB) {
-        __syncthreads();
-        for (int t = threadIdx.x; t < NB * NB; t += 256) {
-            const int r = t / NB, kk = t % NB;
-            Lp[r][kk] = r < bh ? L[(size_t)(ib + r) * n + k0 + kk] : 0.0f;
-        }
-        for (int t = threadIdx.x; t < NB * 64; t += 256) {
-            const int kk = t / 64, cc = t % 64;
-            LIp[kk][cc] = jc + cc < n ? LI[(size_t)(k0 + kk) * n + jc + cc] : 0.0f;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int kk = 0; kk < NB; kk += 4) {
-            const float l0 = LIp[kk][c], l1 = LIp[kk + 1][c], l2 = LIp[kk + 2][c], l3 = LIp[kk + 3][c];
-#pragma unroll
-            for (int u = 0; u < 8; u++) {
-                const float4 a = *reinterpret_cast<const float4*>(&Lp[g * 8 + u][kk]);
-                acc[u] = muladd(muladd(muladd(muladd(acc[u], a.x, l0), a.y, l1), a.z, l2), a.w, l3);
-            }
-        }
-    }
-#pragma unroll
-    for (int u = 0; u < 8; u++) S[g * 8 + u][c] = acc[u];
-    for (int t = threadIdx.x; t < NB * NB; t += 256) {
+    const int c = threadIdx.x, j = blockIdx.x * 64 + c;
+    for (int t = threadIdx.x; t < NB * NB; t += 64) {
         const int r = t / NB, k = t % NB;
-        Ld[r][k] = (r < bh && k < bh) ? L[(size_t)(ib + r) * n + ib + k] : 0.0f;
+        Ld[r][k] = (r < bh && k <= r) ? L[(size_t)(ib + r) * n + ib + k] : 0.0f;
+    }
+    const bool live = j < ib + bh;
+    if (live) {
+        for (int r = 0; r < bh; r++) X[r][c] = LI[(size_t)(ib + r) * n + j];
     }
     __syncthreads();
-    if (threadIdx.x < 64) {
-        const int j = jc + c;
-        if (j < n) {
-            for (int r = 0; r < bh; r++) {
-                const int i = ib + r;
-                if (j > i) continue;
-                const float lii = Ld[r][r];
-                float v;
-                if (j == i) {
-                    v = __fdiv_rn(1.0f, lii);
-                } else {
-                    float s = S[r][c];
-                    for (int kk = max(0, j - ib); kk < r; kk++) s = muladd(s, Ld[r][kk], S[kk][c]);
-                    v = __fdiv_rn(-s, lii);
-                }
-                S[r][c] = v;
-                LI[(size_t)i * n + j] = v;
-            }
+    if (!live) return;
+    for (int r = 0; r < bh; r++) {
+        const int i = ib + r;
+        if (j > i) continue;
+        const float lii = Ld[r][r];
+        float v;
+        if (j == i) {
+            v = __fdiv_rn(1.0f, lii);
+        } else {
+            float s = X[r][c];
+            for (int kk = max(0, j - ib); kk < r; kk++) s = muladd(s, Ld[r][kk], X[kk][c]);
+            v = __fdiv_rn(-s, lii);
         }
+        X[r][c] = v;
+        LI[(size_t)i * n + j] = v;
     }
+}
+
+// s[i][j] += l[i][k] * li[k][j] for the 32 finished rows k of block ib, every later row i and every column j that
+// those rows reach; 64 x 64 tiles.
+__global__ void __launch_bounds__(256) invl_trailing_kernel(const float* __restrict__ L, float* __restrict__ LI, int n, int ib, const uint32_t* ctl) {
+    if (ld_volatile(ctl + CTL_FAIL)) return;
+    __shared__ float Pa[64][NB + 1];
+    __shared__ float Pb[NB][64];
+    const int i0 = ib + NB + blockIdx.y * 64, j0 = blockIdx.x * 64, jend = ib + NB;
+    for (int t = threadIdx.x; t < 64 * NB; t += 256) {
+        const int r = t / NB, k = t % NB;
+        Pa[r][k] = i0 + r < n ? L[(size_t)(i0 + r) * n + ib + k] : 0.0f;
+        const int kk = t / 64, cc = t % 64;
+        Pb[kk][cc] = j0 + cc < jend ? LI[(size_t)(ib + kk) * n + j0 + cc] : 0.0f;
+    }
+    __syncthreads();
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[4][4];
+#pragma unroll
+    for (int u = 0; u < 4; u++)
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            const int i = i0 + ty + 16 * u, j = j0 + tx + 16 * v;
+            acc[u][v] = (i < n && j < jend) ? LI[(size_t)i * n + j] : 0.0f;
+        }
+#pragma unroll 8
+    for (int k = 0; k < NB; k++) {
+        float a[4], b[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) { a[u] = Pa[ty + 16 * u][k]; b[u] = Pb[k][tx + 16 * u]; }
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+#pragma unroll
+            for (int v = 0; v < 4; v++) acc[u][v] = muladd(acc[u][v], a[u], b[v]);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++)
+#pragma unroll
+        for (int v = 0; v < 4; v++) {
+            const int i = i0 + ty + 16 * u, j = j0 + tx + 16 * v;
+            if (i < n && j < jend) LI[(size_t)i * n + j] = acc[u][v];
+        }
 }
 
 // Upper triangle of H^-1 = (L^-1)^T L^-1 in 64 x 64 tiles; rows of L^-1 above the tile's first column are zero and
@@ -303,7 +315,7 @@ struct ColParams {
     const float* W;          // [R][n] original weights
     const float* HINV;       // [n][n], upper triangle
     float* ERRS;             // [R][n] per-row errors of every finished column
-    uint32_t* cells;         // [n][2] running column maximum / minimum (ordered keys)
+    unsigned long long* slots;   // [2][2][SLOT_MAX] published column statistics (see post_stats)
     uint32_t* ctl;
     int32_t* Q;              // [R][n]
     float* scales;           // [n]
@@ -311,6 +323,66 @@ struct ColParams {
     int32_t* status;
     int R, n, rpc, bits, symmetric;
 };
+
+constexpr int SLOT_MAX = 1024;          // CTAs of the column loop at most
+
+__device__ __forceinline__ float stat_init_max(int symmetric) { return symmetric ? 0.0f : __int_as_float(0xFF800000); }
+// NaNs are skipped by the comparisons, as in the reference's folds (gptq.rs:253-268)
+__device__ __forceinline__ void stat_add(int symmetric, float v, float& mx, float& mn) {
+    if (symmetric) { const float a = fabsf(v); if (a > mx) mx = a; }
+    else { if (v > mx) mx = v; if (v < mn) mn = v; }
+}
+
+// The meeting point of the column loop.  Each CTA publishes its statistics of column j as one 64-bit word per value,
+// (j + 1) << 32 | ordered key, in its own slot; a reader takes a slot once it carries the tag of the column it waits
+// for, so neither atomics nor fences are needed.  Two sets of slots alternate by the parity of j: a CTA can only
+// publish column j + 2 after every CTA has published j + 1, i.e. after every CTA has finished reading column j.
+__device__ __forceinline__ void post_stats(const ColParams& p, int j, float mx, float mn) {
+    volatile unsigned long long* s = p.slots + (size_t)(j & 1) * 2 * SLOT_MAX;
+    const unsigned long long tag = (unsigned long long)(uint32_t)(j + 1) << 32;
+    s[blockIdx.x] = tag | order_key(mx);
+    if (!p.symmetric) s[SLOT_MAX + blockIdx.x] = tag | order_key(mn);
+}
+
+// Warp-wide: waits (bounded: two seconds) for every CTA's slot of column j and reduces them; false on a timeout.
+// A lane asks for all of its slots at once (eight per pass), so a pass costs one trip to the L2, not one per slot.
+__device__ __forceinline__ bool collect_stats(const ColParams& p, int j, int lane, float& mx, float& mn) {
+    const volatile unsigned long long* s = p.slots + (size_t)(j & 1) * 2 * SLOT_MAX;
+    const uint32_t tag = (uint32_t)(j + 1);
+    const int G = (int)gridDim.x;
+    mx = stat_init_max(p.symmetric);
+    mn = __int_as_float(0x7F800000);
+    bool ok = true;
+    uint64_t t0, t1;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    for (int k0 = 0; k0 < G && ok; k0 += 256) {
+        unsigned long long v[8], u[8];
+        for (uint32_t it = 0;; ++it) {
+            bool all = true;
+#pragma unroll
+            for (int x = 0; x < 8; x++) {
+                const int k = k0 + 32 * x + lane;
+                v[x] = k < G ? s[k] : (unsigned long long)tag << 32 | order_key(mx);
+                u[x] = (k < G && !p.symmetric) ? s[SLOT_MAX + k] : (unsigned long long)tag << 32 | order_key(mn);
+            }
+#pragma unroll
+            for (int x = 0; x < 8; x++) all = all && (uint32_t)(v[x] >> 32) == tag && (uint32_t)(u[x] >> 32) == tag;
+            if (all) break;
+            if ((it & 255u) == 255u) {
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+                if (t1 - t0 > 2000000000ull) { ok = false; break; }
+            }
+        }
+        if (ok) {
+#pragma unroll
+            for (int x = 0; x < 8; x++) { mx = fmaxf(mx, order_unkey((uint32_t)v[x])); mn = fminf(mn, order_unkey((uint32_t)u[x])); }
+        }
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    mx = warp_max(mx);
+    mn = warp_min(mn);
+    return ok;
+}
 
 __device__ __forceinline__ int32_t quant_scalar(float x, float scale, float zpf, float lo, float hi) {
     float v = roundf(__fadd_rn(__fdiv_rn(x, scale), zpf));                // f32::round: half away from zero
@@ -354,18 +426,32 @@ __global__ void __launch_bounds__(256, 1) gptq_columns_kernel(ColParams p) {
                     const int row = rc0 + g * 8 + u;
                     acc[u] = row < nr ? w_s[row * CBP + c] : 0.0f;
                 }
+                // tiles of 64 earlier columns: the next tile's errors and its rows of H^-1 are fetched into registers
+                // while the current one is consumed from shared memory
+                float er[8], hr[16], dg = 0.0f;
+                auto fetch = [&](int jt) {
+#pragma unroll
+                    for (int x = 0; x < 8; x++) {
+                        const int t = tid + 256 * x, r = t / CB, jj = t % CB, row = rc0 + r;
+                        er[x] = row < nr ? p.ERRS[(size_t)(r0 + row) * n + jt + jj] : 0.0f;
+                    }
+#pragma unroll
+                    for (int x = 0; x < 16; x++) {
+                        const int t = tid + 256 * x, jj = t / CB, cc = t % CB;
+                        hr[x] = __ldg(p.HINV + (size_t)(jt + jj) * n + b0 + min(cc, bw - 1));
+                    }
+                    if (tid < CB) dg = __ldg(p.HINV + (size_t)(jt + tid) * n + jt + tid);
+                };
+                fetch(0);
                 for (int jt = 0; jt < b0; jt += CB) {
                     __syncthreads();
-                    for (int t = tid; t < 32 * CB; t += 256) {
-                        const int r = t / CB, jj = t % CB, row = rc0 + r;
-                        E_s[t] = row < nr ? p.ERRS[(size_t)(r0 + row) * n + jt + jj] : 0.0f;
-                    }
-                    for (int t = tid; t < CB * CB; t += 256) {
-                        const int jj = t / CB, cc = t % CB;
-                        H_s[t] = __ldg(p.HINV + (size_t)(jt + jj) * n + b0 + min(cc, bw - 1));
-                    }
-                    if (tid < CB) Dg_s[tid] = __ldg(p.HINV + (size_t)(jt + tid) * n + jt + tid);
+#pragma unroll
+                    for (int x = 0; x < 8; x++) E_s[tid + 256 * x] = er[x];
+#pragma unroll
+                    for (int x = 0; x < 16; x++) H_s[tid + 256 * x] = hr[x];
+                    if (tid < CB) Dg_s[tid] = dg;
                     __syncthreads();
+                    if (jt + CB < b0) fetch(jt + CB);
 #pragma unroll 2
                     for (int jj = 0; jj < CB; jj += 4) {
                         float h[4];
@@ -406,45 +492,31 @@ __global__ void __launch_bounds__(256, 1) gptq_columns_kernel(ColParams p) {
             H_s[t] = (jj < bw && cc >= jj && cc < bw) ? __ldg(p.HINV + (size_t)(b0 + jj) * n + b0 + cc) : 0.0f;
         }
         __syncthreads();
+        if (tid < 32) {                                                    // this CTA's statistics of the block's first column
+            float mx = stat_init_max(p.symmetric), mn = __int_as_float(0x7F800000);
+            for (int row = tid; row < nr; row += 32) stat_add(p.symmetric, w_s[row * CBP], mx, mn);
+            mx = warp_max(mx);
+            mn = warp_min(mn);
+            if (tid == 0) post_stats(p, b0, mx, mn);
+        }
         for (int jj = 0; jj < bw; jj++) {
             const int j = b0 + jj;
             if (tid < 32) {
-                // this CTA's share of the column statistics (NaNs are skipped by the comparisons, as in the reference)
-                float mx = p.symmetric ? 0.0f : __int_as_float(0xFF800000), mn = __int_as_float(0x7F800000);
-                for (int row = tid; row < nr; row += 32) {
-                    const float v = w_s[row * CBP + jj];
-                    if (p.symmetric) { const float a = fabsf(v); if (a > mx) mx = a; }
-                    else { if (v > mx) mx = v; if (v < mn) mn = v; }
-                }
-                mx = warp_max(mx);
-                mn = warp_min(mn);
+                // every CTA's statistics of column j: the maximum over all rows of the layer
+                float mx, mn;
+                const bool ok = collect_stats(p, j, tid, mx, mn);
                 if (tid == 0) {
-                    if (p.symmetric) atomicMax(p.cells + 2 * j, __float_as_uint(mx));
-                    else { atomicMax(p.cells + 2 * j, order_key(mx)); atomicMin(p.cells + 2 * j + 1, order_key(mn)); }
-                    __threadfence();
-                    atomicAdd(p.ctl + CTL_COUNTER, 1u);
-                    // every CTA of the cooperative grid is resident, so the others arrive; give up after two seconds all the same
-                    const uint32_t target = (uint32_t)(j + 1) * gridDim.x;
-                    uint64_t t0, t1;
-                    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
-                    for (uint32_t it = 0; ld_volatile(p.ctl + CTL_COUNTER) < target; ++it) {
-                        if ((it & 1023u) == 1023u) {
-                            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
-                            if (t1 - t0 > 2000000000ull) { atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); s_abort = 1; break; }
-                        }
-                    }
-                    __threadfence();
+                    if (!ok) { atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); s_abort = 1; }
                     float scale; int zp = 0;
                     if (p.symmetric) {
-                        float am = __uint_as_float(ld_volatile(p.cells + 2 * j));
+                        float am = mx;
                         if (!(am > 1e-8f)) am = 1e-8f;
                         scale = __fdiv_rn(am, hi);
                     } else {
-                        const float fmax = order_unkey(ld_volatile(p.cells + 2 * j)), fmin = order_unkey(ld_volatile(p.cells + 2 * j + 1));
-                        float range = __fsub_rn(fmax, fmin);
+                        float range = __fsub_rn(mx, mn);
                         if (!(range > 1e-8f)) range = 1e-8f;
                         scale = __fdiv_rn(range, (float)((1 << p.bits) - 1));
-                        float z = roundf(__fdiv_rn(-fmin, scale));
+                        float z = roundf(__fdiv_rn(-mn, scale));
                         if (z < lo) z = lo;
                         if (z > hi) z = hi;
                         zp = z != z ? 0 : (int)z;
@@ -467,7 +539,21 @@ __global__ void __launch_bounds__(256, 1) gptq_columns_kernel(ColParams p) {
                 eb_s[row * CBP + jj] = e;
             }
             __syncthreads();
-            if (!degenerate && c > jj && c < bw) {
+            if (tid < 32 && jj + 1 < bw) {
+                // the next column first: correct it, take its statistics and post them, so that the other CTAs'
+                // answers travel while the rest of the block is corrected
+                const float h = H_s[jj * CB + jj + 1];
+                float mx = stat_init_max(p.symmetric), mn = __int_as_float(0x7F800000);
+                for (int row = tid; row < nr; row += 32) {
+                    float v = w_s[row * CBP + jj + 1];
+                    if (!degenerate) { v = mulsub(v, eb_s[row * CBP + jj], h); w_s[row * CBP + jj + 1] = v; }
+                    stat_add(p.symmetric, v, mx, mn);
+                }
+                mx = warp_max(mx);
+                mn = warp_min(mn);
+                if (tid == 0) post_stats(p, j + 1, mx, mn);
+            }
+            if (!degenerate && c > jj + 1 && c < bw) {
                 const float h = H_s[jj * CB + c];
                 for (int row = g; row < nr; row += 4) w_s[row * CBP + c] = mulsub(w_s[row * CBP + c], eb_s[row * CBP + jj], h);
             }
@@ -484,9 +570,9 @@ __global__ void __launch_bounds__(256, 1) gptq_columns_kernel(ColParams p) {
     }
 }
 
-size_t gptq_ws_bytes(int64_t R, int64_t n) {
-    return (size_t)(2 * n * n + R * n + 2 * n + CTL_WORDS) * sizeof(float);
-}
+// workspace: A / H^-1 [n][n], L^-1 [n][n], errors [R][n], then (16-byte aligned) the control words and the slots
+size_t gptq_tail_offset(int64_t R, int64_t n) { return (((size_t)(2 * n * n + R * n) * sizeof(float)) + 15) & ~(size_t)15; }
+size_t gptq_ws_bytes(int64_t R, int64_t n) { return gptq_tail_offset(R, n) + CTL_WORDS * sizeof(uint32_t) + 4 * SLOT_MAX * sizeof(unsigned long long); }
 
 }  // namespace
 }  // namespace oxq
@@ -510,13 +596,14 @@ int32_t oxq_gptq_quantize_layer(oxq_handle* h, const float* weights, int64_t n_r
     if (!weights || !hessian || !quantized || !scales || !zero_points || !info || !workspace) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
     if (n_cols > 32768 || n_rows * n_cols > (int64_t)1 << 31) OXQ_FAIL(h, OXQ_ERR_UNSUPPORTED_OPERATION, "layer too large: %lld x %lld", (long long)n_rows, (long long)n_cols);
     if (workspace_bytes < gptq_ws_bytes(n_rows, n_cols)) OXQ_FAIL(h, OXQ_ERR_BUFFER_TOO_SMALL, "workspace needs %zu bytes, got %zu", gptq_ws_bytes(n_rows, n_cols), workspace_bytes);
+    if ((uintptr_t)workspace & 15) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "workspace must be 16-byte aligned");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     const int n = (int)n_cols, R = (int)n_rows;
     float* A = (float*)workspace;                       // dampened Hessian -> L (lower) -> H^-1 (upper)
     float* LI = A + (size_t)n * n;
     float* ERRS = LI + (size_t)n * n;
-    uint32_t* cells = (uint32_t*)(ERRS + (size_t)R * n);
-    uint32_t* ctl = cells + 2 * (size_t)n;
+    uint32_t* ctl = (uint32_t*)((char*)workspace + gptq_tail_offset(R, n));
+    unsigned long long* slots = (unsigned long long*)(ctl + CTL_WORDS);
     cudaStream_t st = h->stream;
 
     // the column loop's grid: every CTA resident (cooperative launch), rows split evenly
@@ -527,10 +614,10 @@ int32_t oxq_gptq_quantize_layer(oxq_handle* h, const float* weights, int64_t n_r
     int occ = 0;
     OXQ_CUDA(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gptq_columns_kernel, 256, smem));
     const int grid_cols = (R + rpc - 1) / rpc;
-    if (occ < 1 || grid_cols > occ * h->sm_count) OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "column kernel cannot be made resident (%d CTAs, occupancy %d)", grid_cols, occ);
+    if (occ < 1 || grid_cols > occ * h->sm_count || grid_cols > SLOT_MAX) OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "column kernel cannot be made resident (%d CTAs, occupancy %d)", grid_cols, occ);
 
-    OXQ_CUDA(h, oxq_launch<false>(gptq_prepare_kernel, dim3(1), dim3(256), 0, st, hessian, n, (float)percdamp, ctl, info));
-    OXQ_CUDA(h, oxq_launch<false>(gptq_damp_kernel, dim3(h->sm_count * 4), dim3(256), 0, st, hessian, A, n, (const uint32_t*)ctl, cells, symmetric));
+    OXQ_CUDA(h, oxq_launch<false>(gptq_prepare_kernel, dim3(1), dim3(256), 0, st, hessian, n, (float)percdamp, ctl, info, slots, 4 * SLOT_MAX));
+    OXQ_CUDA(h, oxq_launch<false>(gptq_damp_kernel, dim3(h->sm_count * 4), dim3(256), 0, st, hessian, A, n, (const uint32_t*)ctl));
     OXQ_CUDA(h, cudaMemsetAsync(LI, 0, (size_t)n * n * sizeof(float), st));
     for (int kb = 0; kb < n; kb += NB) {
         const int below = n - kb - NB;
@@ -542,15 +629,17 @@ int32_t oxq_gptq_quantize_layer(oxq_handle* h, const float* weights, int64_t n_r
         }
     }
     for (int ib = 0; ib < n; ib += NB) {
-        const int cols = min(ib + NB, n);
-        OXQ_CUDA(h, oxq_launch<false>(invl_block_kernel, dim3((cols + 63) / 64), dim3(256), 0, st, (const float*)A, LI, n, ib, (const uint32_t*)ctl));
+        const int cols = min(ib + NB, n), below = n - ib - NB;
+        OXQ_CUDA(h, oxq_launch<false>(invl_diag_kernel, dim3((cols + 63) / 64), dim3(64), 0, st, (const float*)A, LI, n, ib, (const uint32_t*)ctl));
+        if (below > 0)
+            OXQ_CUDA(h, oxq_launch<false>(invl_trailing_kernel, dim3((cols + 63) / 64, (below + 63) / 64), dim3(256), 0, st, (const float*)A, LI, n, ib, (const uint32_t*)ctl));
     }
     {
         const int T = (n + 63) / 64;
         OXQ_CUDA(h, oxq_launch<false>(hinv_kernel, dim3(T, T), dim3(256), 0, st, (const float*)LI, A, n, (const uint32_t*)ctl));
     }
     ColParams p;
-    p.W = weights; p.HINV = A; p.ERRS = ERRS; p.cells = cells; p.ctl = ctl; p.Q = quantized; p.scales = scales; p.zps = zero_points;
+    p.W = weights; p.HINV = A; p.ERRS = ERRS; p.slots = slots; p.ctl = ctl; p.Q = quantized; p.scales = scales; p.zps = zero_points;
     p.status = h->dev_status; p.R = R; p.n = n; p.rpc = rpc; p.bits = bits; p.symmetric = symmetric ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid_cols); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = smem; cfg.stream = st;

@@ -263,6 +263,22 @@ def extras(torch, ops, peaks):
         ring_time(torch, lambda r: ops.int4g_quant_pack(r, 128), ringw))
     rec("nf4_quant_f32_14336x4096_b64", 14336 * 4096 * 4 + 14336 * 4096 // 2 + 14336 * 4096 // 64 * 4,
         ring_time(torch, lambda r: ops.nf4_quant(r, 64), ringw))
+    # offline weight preparation: one GPTQ layer (4096 x 4096, INT4 symmetric), Hessian from 8192 synthetic samples
+    n = 4096
+    xs = torch.randn((2 * n, n), generator=g, device="cuda")
+    hess = (2.0 * xs.T @ xs / (2 * n)).float()
+    hess = torch.maximum(hess, hess.T)
+    del xs
+    wq = ringw[0][:n].contiguous()
+    gq = ops.GptqQuantizer(ops.GptqConfig(bits=4))
+    gq.quantize_layer(wq, n, n, hess)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    gq.quantize_layer(wq, n, n, hess)
+    e1.record()
+    torch.cuda.synchronize()
+    blocks = n // 32
+    out["gptq_quantize_layer_4096x4096_int4"] = {"ms": round(e0.elapsed_time(e1), 3), "launches_per_call": 2 + 3 * blocks - 2 + 2 * blocks - 1 + 2}
     return out
 
 

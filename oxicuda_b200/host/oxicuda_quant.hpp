@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <cmath>
 #include <cstdint>
+#include <cstring>
 #include <stdexcept>
 #include <string>
 #include <utility>
@@ -233,6 +234,65 @@ struct BlockQuantizedInt8 {
     float compression_ratio() const {
         const size_t qb = data.size() + scales.size() * 4;
         return qb == 0 ? 1.0f : (float)(orig_len * 4) / (float)qb;
+    }
+};
+
+// GptqConfig / GptqOutput / GptqQuantizer (crates/oxicuda-quant/src/scheme/gptq.rs:30-257): the whole layer is
+// quantized on the device by oxq_gptq_quantize_layer; results equal the reference's CPU loop bit for bit.
+struct GptqConfig {
+    uint32_t bits = 4;
+    size_t block_size = 128;                                              // unused by the reference's algorithm as well
+    double percdamp = 0.01;
+    bool symmetric = true;
+};
+struct GptqOutput {
+    std::vector<int32_t> quantized;
+    std::vector<float> scales;
+    std::vector<int32_t> zero_points;
+    size_t n_rows = 0, n_cols = 0;
+    std::vector<float> dequantize() const {
+        std::vector<float> out(n_rows * n_cols);
+        for (size_t i = 0; i < n_rows; i++)
+            for (size_t j = 0; j < n_cols; j++) out[i * n_cols + j] = ((float)quantized[i * n_cols + j] - (float)zero_points[j]) * scales[j];
+        return out;
+    }
+    float reconstruction_mse(const std::vector<float>& original) const {
+        const std::vector<float> deq = dequantize();
+        float acc = 0.0f;
+        for (size_t i = 0; i < deq.size() && i < original.size(); i++) acc += (deq[i] - original[i]) * (deq[i] - original[i]);
+        return acc / (float)(deq.empty() ? 1 : deq.size());
+    }
+};
+class GptqQuantizer {
+public:
+    explicit GptqQuantizer(const GptqConfig& config = GptqConfig()) : config(config) {}
+    GptqConfig config;
+    GptqOutput quantize_layer(const std::vector<float>& weights, size_t n_rows, size_t n_cols, const std::vector<float>& hessian) const {
+        if (weights.empty()) throw QuantError("EmptyInput", "GptqQuantizer::quantize_layer");
+        if (weights.size() != n_rows * n_cols) throw QuantError("DimensionMismatch", "weights length does not match n_rows * n_cols");
+        if (hessian.size() != n_cols * n_cols) throw QuantError("DimensionMismatch", "hessian length does not match n_cols * n_cols");
+        if (config.bits == 0 || config.bits > 16) throw QuantError("InvalidBitWidth", "bits must be in 1..=16");
+        detail::Handle h;
+        size_t ws_bytes = 0;
+        detail::check(oxq_gptq_workspace_bytes((int64_t)n_rows, (int64_t)n_cols, &ws_bytes), h.h);
+        detail::DevBuf<float> w(weights.size()), hs(hessian.size()), sc(n_cols);
+        detail::DevBuf<int32_t> q(weights.size()), zp(n_cols), info(2);
+        detail::DevBuf<uint8_t> ws(ws_bytes);
+        w.upload(weights.data()); hs.upload(hessian.data());
+        detail::check(oxq_gptq_quantize_layer(h.h, w.p, (int64_t)n_rows, (int64_t)n_cols, hs.p, (int)config.bits, config.symmetric ? 1 : 0,
+                                              config.percdamp, q.p, sc.p, zp.p, info.p, ws.p, ws_bytes), h.h);
+        detail::cuda(cudaDeviceSynchronize());
+        int32_t host_info[2] = {0, 0};
+        info.download(host_info);
+        if (host_info[0] != 0) {
+            float md; memcpy(&md, &host_info[1], sizeof(md));
+            throw QuantError("SingularHessian", "min diagonal = " + std::to_string(md));
+        }
+        GptqOutput out;
+        out.n_rows = n_rows; out.n_cols = n_cols;
+        out.quantized.resize(weights.size()); out.scales.resize(n_cols); out.zero_points.resize(n_cols);
+        q.download(out.quantized.data()); sc.download(out.scales.data()); zp.download(out.zero_points.data());
+        return out;
     }
 };
 

@@ -75,6 +75,26 @@ int main(int argc, char** argv) {
             std::vector<float> kd = known.dequantize();
             if (std::fabs(kd[0] + 12.8f) > 1e-4f || kd[1] != 0.0f || std::fabs(kd[2] - 12.7f) > 1e-4f) return 16;
         }
+        // GptqQuantizer: the reference's own tests (gptq.rs:422-520)
+        {
+            auto eye = [](size_t n) { std::vector<float> m(n * n, 0.0f); for (size_t i = 0; i < n; i++) m[i * n + i] = 1.0f; return m; };
+            int gerr = 0;
+            GptqConfig nodamp; nodamp.percdamp = 0.0;
+            try { GptqQuantizer(nodamp).quantize_layer(std::vector<float>(4, 0.5f), 2, 2, std::vector<float>(4, 0.0f)); }
+            catch (const QuantError& e) { gerr += e.variant == "SingularHessian"; }
+            try { GptqQuantizer().quantize_layer(std::vector<float>(3, 0.5f), 1, 4, eye(4)); } catch (const QuantError& e) { gerr += e.variant == "DimensionMismatch"; }
+            GptqConfig zero_bits; zero_bits.bits = 0;
+            try { GptqQuantizer(zero_bits).quantize_layer(std::vector<float>(4, 0.5f), 2, 2, eye(2)); } catch (const QuantError& e) { gerr += e.variant == "InvalidBitWidth"; }
+            if (gerr != 3) return 17;
+            GptqConfig int8; int8.bits = 8;
+            std::vector<float> gw(32);
+            for (int i = 0; i < 32; i++) gw[i] = (float)i / 16.0f - 1.0f;
+            GptqOutput go = GptqQuantizer(int8).quantize_layer(gw, 4, 8, eye(8));
+            if (!(go.reconstruction_mse(gw) < 1e-4f) || go.quantized.size() != 32 || go.scales.size() != 8 || go.zero_points.size() != 8) return 18;
+            GptqConfig asym; asym.symmetric = false;
+            std::vector<float> aw = {-0.6f, 0.4f, -0.2f, 0.8f, 0.6f, -0.4f, 0.2f, -0.8f};
+            if (!(GptqQuantizer(asym).quantize_layer(aw, 2, 4, eye(4)).reconstruction_mse(aw) < 0.05f)) return 19;
+        }
         FILE* f = fopen(argv[1], "wb");
         if (!f) return 9;
         fwrite(big.data(), sizeof(float), big.size(), f);

@@ -230,6 +230,9 @@ def extras(torch, ops, peaks):
     outi = outq.view(torch.int8)
     wnorm = torch.ones(8192, device="cuda")
     rec("rmsnorm_int8_quant_rows_bf16_8192x8192", 201326592 + 8192 * 8, ring_time(torch, lambda r: ops.rmsnorm_int8_quant_rows(r, wnorm), ring))
+    rec("rmsnorm_fp8_quant_rows_bf16_8192x8192", 201326592, ring_time(torch, lambda r: ops.rmsnorm_fp8_quant_rows(r, wnorm, one), ring))
+    rec("silu_gate_fp8_quant_bf16_8192x8192", 134217728 * 2 + 67108864, ring_time(torch, lambda r: ops.silu_gate_fp8_quant(r[0], r[1], one),
+                                                                                      [(ring[i], ring[(i + 1) % 3]) for i in range(3)]))
     rec("int8_quant_tensor_bf16_8192x8192(absmax+encode)", 335544320, ring_time(torch, lambda r: ops.quantize_to_int8(r, out=outi, scale=am), ring), 2)
     # config 4 quantizers on the 4096x4096 activation shape (ring of 8 -> 256 MiB)
     ring4 = [r[:4096, :4096].contiguous() for r in ring] + [r[4096:, 4096:].contiguous() for r in ring] + [ring[0][:4096, 4096:].contiguous(), ring[1][4096:, :4096].contiguous()]

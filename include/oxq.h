@@ -227,6 +227,16 @@ OXQ_API int32_t oxq_nf4_dequant(oxq_handle* h, const uint8_t* packed_dev, const 
  * the row.  cols % 8 == 0, cols <= 16384.  y_opt (same dtype as x) also receives the normalised row when it is not NULL. */
 OXQ_API int32_t oxq_rmsnorm_int8_quant_rows(oxq_handle* h, const void* x_dev, int dtype, const float* weight_dev, int64_t rows, int64_t cols,
                                             float eps, int8_t* q_dev, float* scales_dev, void* y_opt_dev);
+/* The FP8 forms of the fused activation paths, at a calibrated per-tensor scale (scale_dev[0], as oxq_fp8_quant takes it):
+ *   oxq_rmsnorm_fp8_quant_rows  RmsNorm::forward (norm.rs:73-95) then E4M3 (RNE, saturating) of y / scale: the input of oxq_gemm_fp8;
+ *   oxq_silu_gate_fp8_quant     silu_gate (crates/oxicuda-lm/src/ptx_kernels.rs:222-290, out = gate / (1 + exp(-gate)) * up,
+ *                               SwiGluFfn::forward at crates/oxicuda-lm/src/layer/ffn.rs:202-254) then E4M3 of out / scale: the
+ *                               input of the down projection, written as one byte per element instead of a bf16 round trip.
+ * x, gate and up share `dtype` (OXQ_F32 / OXQ_BF16 / OXQ_F16); the arithmetic is f32 before the one conversion. */
+OXQ_API int32_t oxq_rmsnorm_fp8_quant_rows(oxq_handle* h, const void* x_dev, int dtype, const float* weight_dev, int64_t rows, int64_t cols,
+                                           float eps, const float* scale_dev, uint8_t* q_dev);
+OXQ_API int32_t oxq_silu_gate_fp8_quant(oxq_handle* h, const void* gate_dev, const void* up_dev, int dtype, int64_t n,
+                                        const float* scale_dev, uint8_t* q_dev);
 /* SmoothQuantMigrator (crates/oxicuda-quant/src/scheme/smooth_quant.rs) on device buffers, f32 row-major:
  *   oxq_smooth_col_absmax  compute_act_stats / compute_weight_stats (:125-196): stats[j] = max_r |x[r, j]|;
  *   oxq_smooth_scales      compute_migration_scales (:84-113): s_j = max(|a_j|,1e-8)^alpha / max(|w_j|,1e-8)^(1-alpha);

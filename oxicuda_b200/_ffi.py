@@ -41,6 +41,8 @@ SIGNATURES = {
     "oxq_int8_block_dequant": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp]),
     "oxq_nf4_quant": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
     "oxq_nf4_dequant": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp, _int]),
+    "oxq_rmsnorm_fp8_quant_rows": (_i32, [_vp, _vp, _int, _vp, _i64, _i64, C.c_float, _vp, _vp]),
+    "oxq_silu_gate_fp8_quant": (_i32, [_vp, _vp, _vp, _int, _i64, _vp, _vp]),
     "oxq_rmsnorm_int8_quant_rows": (_i32, [_vp, _vp, _int, _vp, _i64, _i64, C.c_float, _vp, _vp, _vp]),
     "oxq_smooth_col_absmax": (_i32, [_vp, _vp, _i64, _i64, _vp]),
     "oxq_smooth_scales": (_i32, [_vp, _vp, _vp, _i64, C.c_float, _vp]),

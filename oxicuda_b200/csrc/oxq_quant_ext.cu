@@ -357,6 +357,101 @@ __global__ void __launch_bounds__(256) rmsnorm_int8_rows_kernel(const T* __restr
     }
 }
 
+// RMSNorm fused with the E4M3 quantizer at a calibrated (static) per-tensor scale: the activation path in front of
+// an FP8 GEMM.  Same structure as the INT8 form, minus the second reduction.
+template <typename T, int NV>
+__global__ void __launch_bounds__(256) rmsnorm_fp8_rows_kernel(const T* __restrict__ x, const float* __restrict__ weight, int64_t rows,
+                                                               int64_t cols, float eps, const float* __restrict__ scale_ptr,
+                                                               uint8_t* __restrict__ q) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[8];
+    const InvDiv d = make_invdiv(__ldg(scale_ptr));
+    const int64_t nitems = cols >> 3;
+    Raw8<T> nxt[NV];
+    if ((int64_t)blockIdx.x < rows) {
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int64_t it = threadIdx.x + (int64_t)i * 256;
+            if (it < nitems) nxt[i] = load8raw(x + (int64_t)blockIdx.x * cols + it * 8);
+        }
+    }
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        float f[NV][8];
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int64_t it = threadIdx.x + (int64_t)i * 256;
+            if (it < nitems) {
+                raw8_to_f32(nxt[i], f[i]);
+#pragma unroll
+                for (int e = 0; e < 8; e++) ss = fmaf(f[i][e], f[i][e], ss);
+            }
+        }
+        if (row + gridDim.x < rows) {
+#pragma unroll
+            for (int i = 0; i < NV; i++) {
+                const int64_t it = threadIdx.x + (int64_t)i * 256;
+                if (it < nitems) nxt[i] = load8raw(x + (row + gridDim.x) * cols + it * 8);
+            }
+        }
+        ss = block_reduce_sum(ss, red);
+        const float inv_rms = __fdiv_rn(1.0f, sqrtf(__fdiv_rn(ss, (float)cols) + eps));
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const int64_t it = threadIdx.x + (int64_t)i * 256;
+            if (it < nitems) {
+                const float4 w0 = __ldg(reinterpret_cast<const float4*>(weight + it * 8)), w1 = __ldg(reinterpret_cast<const float4*>(weight + it * 8) + 1);
+                const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[e] = div_exact(f[i][e] * inv_rms * wv[e], d);
+                uint2 o;
+                o.x = (uint32_t)cvt_e4m3x2(v[0], v[1]) | ((uint32_t)cvt_e4m3x2(v[2], v[3]) << 16);
+                o.y = (uint32_t)cvt_e4m3x2(v[4], v[5]) | ((uint32_t)cvt_e4m3x2(v[6], v[7]) << 16);
+                *reinterpret_cast<uint2*>(q + row * cols + it * 8) = o;
+            }
+        }
+    }
+}
+
+// silu_gate of the reference (crates/oxicuda-lm/src/ptx_kernels.rs:222-290: out = gate / (1 + exp(-gate)) * up) fused
+// with the E4M3 quantizer at a static scale: the activation of a SwiGLU MLP written once, as one byte per element.
+template <typename T>
+__global__ void __launch_bounds__(256) silu_gate_fp8_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_t n,
+                                                            const float* __restrict__ scale_ptr, uint8_t* __restrict__ q) {
+    pdl_trigger();
+    pdl_wait();
+    const InvDiv d = make_invdiv(__ldg(scale_ptr));
+    const int64_t nitems = n >> 3;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t it = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; it < nitems; it += 2 * stride) {
+        const int64_t it2 = it + stride;
+        const bool two = it2 < nitems;
+        Raw8<T> g0 = load8raw(gate + it * 8), u0 = load8raw(up + it * 8), g1 = g0, u1 = u0;
+        if (two) { g1 = load8raw(gate + it2 * 8); u1 = load8raw(up + it2 * 8); }
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            if (h == 1 && !two) break;
+            float g[8], u[8], v[8];
+            raw8_to_f32(h ? g1 : g0, g);
+            raw8_to_f32(h ? u1 : u0, u);
+#pragma unroll
+            for (int e = 0; e < 8; e++) v[e] = div_exact(__fdiv_rn(g[e], 1.0f + expf(-g[e])) * u[e], d);
+            uint2 o;
+            o.x = (uint32_t)cvt_e4m3x2(v[0], v[1]) | ((uint32_t)cvt_e4m3x2(v[2], v[3]) << 16);
+            o.y = (uint32_t)cvt_e4m3x2(v[4], v[5]) | ((uint32_t)cvt_e4m3x2(v[6], v[7]) << 16);
+            __stcs(reinterpret_cast<uint2*>(q + (h ? it2 : it) * 8), o);
+        }
+    }
+    if (blockIdx.x == 0) {                                    // ragged tail
+        for (int64_t i = nitems * 8 + threadIdx.x; i < n; i += blockDim.x) {
+            const float g = Elem<T>::to_f32(gate[i]), u = Elem<T>::to_f32(up[i]);
+            q[i] = (uint8_t)(cvt_e4m3x2(div_exact(__fdiv_rn(g, 1.0f + expf(-g)) * u, d), 0.0f) & 0xFF);
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // SmoothQuant migration (per-channel scale folded from the activations into the weights)
 // ------------------------------------------------------------------------------------------------
@@ -541,6 +636,49 @@ int32_t oxq_rmsnorm_int8_quant_rows(oxq_handle* h, const void* x, int dtype, con
     }
 #undef PICK_RN
 #undef LAUNCH_RN
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_rmsnorm_fp8_quant_rows(oxq_handle* h, const void* x, int dtype, const float* weight, int64_t rows, int64_t cols, float eps,
+                                   const float* scale, uint8_t* q) {
+    OXQ_CHECK_HANDLE(h);
+    if (rows <= 0 || cols <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "rmsnorm: empty input");
+    if (cols % 8 != 0 || cols > 16384) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "rmsnorm + fp8: cols must be a multiple of 8 and at most 16384, got %lld", (long long)cols);
+    if (!x || !weight || !q || !scale || !aligned16(x) || !aligned16(weight) || ((uintptr_t)q & 7u))
+        OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (dtype == OXQ_F32 && ((cols * 4) & 31)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "f32 rows must be 32-byte multiples");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    const int64_t cap = (int64_t)h->sm_count * 6;
+    const int grid = (int)(rows < cap ? rows : cap);
+    const int nv = (int)((cols / 8 + 255) / 256);
+#define LAUNCH_RF(TT, NVV) oxq_launch(rmsnorm_fp8_rows_kernel<TT, NVV>, grid, 256, 0, h->stream, (const TT*)x, weight, rows, cols, eps, scale, q)
+#define PICK_RF(TT) do { if (nv <= 1) LAUNCH_RF(TT, 1); else if (nv <= 2) LAUNCH_RF(TT, 2); else if (nv <= 4) LAUNCH_RF(TT, 4); else LAUNCH_RF(TT, 8); } while (0)
+    switch (dtype) {
+        case OXQ_F32: PICK_RF(float); break;
+        case OXQ_BF16: PICK_RF(__nv_bfloat16); break;
+        case OXQ_F16: PICK_RF(__half); break;
+        default: OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "unknown dtype %d", dtype);
+    }
+#undef PICK_RF
+#undef LAUNCH_RF
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_silu_gate_fp8_quant(oxq_handle* h, const void* gate, const void* up, int dtype, int64_t n, const float* scale, uint8_t* q) {
+    OXQ_CHECK_HANDLE(h);
+    if (n == 0) return OXQ_OK;
+    if (n < 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "negative element count");
+    if (!gate || !up || !scale || !q || !aligned16(gate) || !aligned16(up) || ((uintptr_t)q & 7u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    const int grid = grid_cap(h, n / 16 + 1, 256, 8);
+    switch (dtype) {
+        case OXQ_F32: oxq_launch(silu_gate_fp8_kernel<float>, grid, 256, 0, h->stream, (const float*)gate, (const float*)up, n, scale, q); break;
+        case OXQ_BF16: oxq_launch(silu_gate_fp8_kernel<__nv_bfloat16>, grid, 256, 0, h->stream, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, n, scale, q); break;
+        case OXQ_F16: oxq_launch(silu_gate_fp8_kernel<__half>, grid, 256, 0, h->stream, (const __half*)gate, (const __half*)up, n, scale, q); break;
+        default: OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "unknown dtype %d", dtype);
+    }
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

@@ -279,6 +279,48 @@ def rmsnorm_int8_quant_rows(x: torch.Tensor, weight: torch.Tensor, eps: float = 
     return (q, sc, y) if want_normed else (q, sc)
 
 
+def rmsnorm_fp8_quant_rows(x: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, eps: float = 1e-5):
+    """RmsNorm::forward fused with the E4M3 quantizer at a calibrated per-tensor scale: codes uint8 [rows x cols]."""
+    _chk(x, torch.float32, torch.bfloat16, torch.float16)
+    _chk(weight, torch.float32)
+    rows, cols = x.shape
+    if weight.numel() != cols:
+        from .errors import QuantError
+        raise QuantError("DimensionMismatch", f"expected {cols} weights, got {weight.numel()}", 4)
+    q = torch.empty((rows, cols), dtype=torch.uint8, device=x.device)
+    handle(x.device.index).call("oxq_rmsnorm_fp8_quant_rows", _p(x), _DT[x.dtype], _p(weight), rows, cols, C.c_float(eps), _p(scale), _p(q))
+    return q
+
+
+def silu_gate_fp8_quant(gate: torch.Tensor, up: torch.Tensor, scale: torch.Tensor):
+    """silu(gate) * up (the reference's silu_gate kernel) fused with the E4M3 quantizer at a calibrated per-tensor scale."""
+    _chk(gate, torch.float32, torch.bfloat16, torch.float16)
+    _chk(up, gate.dtype)
+    if gate.shape != up.shape:
+        from .errors import QuantError
+        raise QuantError("DimensionMismatch", f"gate {tuple(gate.shape)} vs up {tuple(up.shape)}", 4)
+    q = torch.empty(gate.shape, dtype=torch.uint8, device=gate.device)
+    handle(gate.device.index).call("oxq_silu_gate_fp8_quant", _p(gate), _p(up), _DT[gate.dtype], gate.numel(), _p(scale), _p(q))
+    return q
+
+
+def quantize_to_fp8(x: torch.Tensor, out: torch.Tensor | None = None, scale: torch.Tensor | None = None):
+    """quantize_to_fp8 of the reference's DNN layer (crates/oxicuda-dnn/src/quantize/fp8_quantize.rs:47-118): per-tensor
+    scale = absmax / 448 into a one-element buffer, E4M3 codes.  Returns (codes, scale)."""
+    stats = torch.empty(2, dtype=torch.float32, device=x.device)
+    q, _ = fp8_quant_dynamic(x, out=out, stats=stats)
+    if scale is None:
+        scale = stats[1:2]
+    else:
+        scale[:1].copy_(stats[1:2])
+    return q, scale
+
+
+def dequantize_from_fp8(q: torch.Tensor, scale: torch.Tensor, dtype=torch.float32):
+    """dequantize_from_fp8 (fp8_quantize.rs:121-170): out[i] = e4m3(q[i]) * scale[0]."""
+    return fp8_dequant(q, scale, dtype=dtype)
+
+
 class SmoothQuantMigrator:
     """SmoothQuantMigrator of the reference (crates/oxicuda-quant/src/scheme/smooth_quant.rs:54-293) on device tensors."""
 

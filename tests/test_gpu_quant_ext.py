@@ -210,3 +210,74 @@ def test_rmsnorm_reference_cases(ops, orc):  # crates/oxicuda-lm/src/layer/norm.
     assert q.cpu().tolist()[0][:3] == [95, 127, 0]
     with pytest.raises(OxqError):
         ops.rmsnorm_int8_quant_rows(x, torch.ones(4, device="cuda"))
+
+
+def _e4m3_half_ulp(v):
+    """Half the spacing of the E4M3 grid around |v| (subnormal spacing 2^-9 below 2^-6; the grid ends at 448)."""
+    a = np.minimum(np.abs(v), 448.0)
+    e = np.floor(np.log2(np.maximum(a, 2.0 ** -6)))
+    return 0.5 * 2.0 ** (e - 3)
+
+
+def _check_fp8_codes(orc, q, want_f64, what):
+    """The code is the nearest E4M3 value of the exact quotient, or its neighbour where the kernel's f32 value sat within a
+    few ulp of a rounding boundary."""
+    dec = orc.e4m3_to_f32(q.cpu().numpy().ravel()).astype(np.float64)
+    want = np.clip(want_f64.ravel(), -448.0, 448.0)
+    err = np.abs(dec - want)
+    hu = _e4m3_half_ulp(want)
+    assert (err <= hu * 1.001 + 1e-12).all(), f"{what}: max excess {(err - hu).max()}"
+    exact = orc.e4m3_to_f32(orc.spec_fp8_quant(want.astype(np.float32), 1.0)).astype(np.float64)
+    assert (dec != exact).mean() <= 2e-3, what
+
+
+@pytest.mark.parametrize("shape", [(1, 8), (7, 4096), (64, 8192), (300, 1000)])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_rmsnorm_fp8_rows(ops, orc, shape, dtype):
+    rows, cols = shape
+    x = orc.gaussian((rows, cols), 2.0, 31)
+    w = (1.0 + 0.1 * orc.gaussian((1, cols), 1.0, 32)).ravel().astype(np.float32)
+    if dtype == "bf16":
+        xb = _bf16_round(x)
+        x = xb.float().numpy()
+        xd = xb.cuda()
+    else:
+        xd = to_dev(x)
+    scale = np.float32(4.0 / 448.0)                                       # a calibrated scale; a few values saturate
+    q = ops.rmsnorm_fp8_quant_rows(xd, to_dev(w), to_dev(np.array([scale], np.float32)), 1e-5)
+    y_ref = orc.ref_rms_norm(x, w, 1e-5).astype(np.float64)
+    _check_fp8_codes(orc, q, y_ref / np.float64(scale), f"rmsnorm+fp8 {shape} {dtype}")
+
+
+@pytest.mark.parametrize("n", [8, 1000, 4099, 2048 * 3584])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_silu_gate_fp8(ops, orc, n, dtype):
+    g = orc.gaussian((n,), 2.0, 41)
+    u = orc.gaussian((n,), 1.0, 42)
+    if dtype == "bf16":
+        gb, ub = _bf16_round(g), _bf16_round(u)
+        g, u = gb.float().numpy(), ub.float().numpy()
+        gd, ud = gb.cuda(), ub.cuda()
+    else:
+        gd, ud = to_dev(g), to_dev(u)
+    scale = np.float32(6.0 / 448.0)
+    q = ops.silu_gate_fp8_quant(gd, ud, to_dev(np.array([scale], np.float32)))
+    g64, u64 = g.astype(np.float64), u.astype(np.float64)
+    _check_fp8_codes(orc, q, g64 / (1.0 + np.exp(-g64)) * u64 / np.float64(scale), f"silu_gate+fp8 {n} {dtype}")
+    if n <= 4099:                                                          # and against the reference's own f32 silu_gate
+        h = orc.ref_silu_mul(g, u).astype(np.float64)
+        _check_fp8_codes(orc, q, h / np.float64(scale), f"silu_gate+fp8 vs reference f32 {n} {dtype}")
+
+
+def test_dnn_fp8_names(ops, orc):
+    """quantize_to_fp8 / dequantize_from_fp8 of the reference's DNN layer: scale = absmax / 448 in a one-element buffer."""
+    x = orc.gaussian((1000,), 1.0, 51)
+    q, scale = ops.quantize_to_fp8(to_dev(x))
+    assert scale.numel() == 1 and float(scale[0]) == np.float32(np.abs(x).max()) / np.float32(448.0)
+    q2, _ = ops.fp8_quant_dynamic(to_dev(x))
+    assert torch.equal(q, q2)
+    y = ops.dequantize_from_fp8(q, scale)
+    assert np.allclose(y.cpu().numpy(), x, atol=float(scale[0]) * 16.0)
+    buf = torch.zeros(1, device="cuda")
+    ops.quantize_to_fp8(to_dev(x), scale=buf)
+    assert float(buf[0]) == float(scale[0])

@@ -266,6 +266,12 @@ def extras(torch, ops, peaks):
         ring_time(torch, lambda r: ops.int4g_quant_pack(r, 128), ringw))
     rec("nf4_quant_f32_14336x4096_b64", 14336 * 4096 * 4 + 14336 * 4096 // 2 + 14336 * 4096 // 64 * 4,
         ring_time(torch, lambda r: ops.nf4_quant(r, 64), ringw))
+    packs = [ops.nf4_quant(ringw[i % 3].view(-1), 64) for i in range(6)]                      # 6 x 30 MB of packed weights
+    for mrows in (1, 8):
+        xn = torch.randn((mrows, 4096), generator=g, device="cuda").to(torch.bfloat16)
+        rec(f"gemm_nf4_m{mrows}_14336x4096_b64", 14336 * 4096 // 2 + 14336 * 4096 // 64 * 4 + mrows * (4096 + 14336) * 2,
+            ring_time(torch, lambda r: ops.gemm_nf4(xn, r[0], r[1], 14336, 64), packs))
+    del packs
     # offline weight preparation: one GPTQ layer (4096 x 4096, INT4 symmetric), Hessian from 8192 synthetic samples
     n = 4096
     xs = torch.randn((2 * n, n), generator=g, device="cuda")

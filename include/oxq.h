@@ -222,6 +222,13 @@ OXQ_API int32_t oxq_int8_block_dequant(oxq_handle* h, const int8_t* q_dev, const
 OXQ_API int32_t oxq_nf4_quant(oxq_handle* h, const float* x_dev, int64_t n, int64_t block, uint8_t* packed_dev, float* absmax_dev);
 OXQ_API int32_t oxq_nf4_dequant(oxq_handle* h, const uint8_t* packed_dev, const float* absmax_dev, int64_t n, int64_t block,
                                 void* y_dev, int y_dtype);
+/* Decode-shaped GEMM on NF4 weights, dequantisation fused in: Y[m x n] (bf16) = X[m x k] (bf16) . W^T with
+ * W[r][c] = level[code] * absmax[(r * k + c) / block], the tensors of oxq_nf4_quant on a row-major [n x k] weight.  The
+ * reference has the elementwise nf4_dequant kernel only (crates/oxicuda-quant/src/ptx_kernels.rs:261-396); this replaces
+ * dequantise + GEMV by one pass over the packed bytes.  m <= 8; block a multiple of 64 that divides k.  The levels enter
+ * the tensor core rounded to bf16; accumulation is f32. */
+OXQ_API int32_t oxq_gemm_nf4(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x_bf16_dev, const uint8_t* packed_dev,
+                             const float* absmax_dev, int64_t block, void* y_bf16_dev);
 /* RmsNorm::forward (crates/oxicuda-lm/src/layer/norm.rs:73-95; y = x / sqrt(mean(x^2) + eps) * weight) fused with the per-row
  * symmetric INT8 quantizer of oxq_int8_quant_rows (half to even): the activation path in front of oxq_gemm_w8a8, one pass over
  * the row.  cols % 8 == 0, cols <= 16384.  y_opt (same dtype as x) also receives the normalised row when it is not NULL. */

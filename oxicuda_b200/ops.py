@@ -263,6 +263,17 @@ def nf4_dequant(packed: torch.Tensor, absmaxs: torch.Tensor, block: int = 64, dt
     return y
 
 
+def gemm_nf4(x: torch.Tensor, packed: torch.Tensor, absmaxs: torch.Tensor, n: int, block: int = 64, out: torch.Tensor | None = None):
+    """Y = X . dequant(W)^T for up to 8 batch rows; `packed` / `absmaxs` are nf4_quant's tensors of a row-major [n x k] weight."""
+    _chk(x, torch.bfloat16)
+    _chk(packed, torch.uint8)
+    _chk(absmaxs, torch.float32)
+    m, k = x.shape
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=x.device) if out is None else out
+    handle(x.device.index).call("oxq_gemm_nf4", m, n, k, _p(x), _p(packed), _p(absmaxs), block, _p(y))
+    return y
+
+
 def rmsnorm_int8_quant_rows(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, want_normed: bool = False):
     """RmsNorm::forward (crates/oxicuda-lm/src/layer/norm.rs:73-95) fused with the per-row INT8 quantizer: returns
     (codes int8 [rows x cols], scales f32 [rows]) and, if asked, the normalised activations in x's dtype."""

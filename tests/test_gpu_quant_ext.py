@@ -281,3 +281,32 @@ def test_dnn_fp8_names(ops, orc):
     buf = torch.zeros(1, device="cuda")
     ops.quantize_to_fp8(to_dev(x), scale=buf)
     assert float(buf[0]) == float(scale[0])
+
+
+@pytest.mark.parametrize("mnk", [(1, 16, 128), (1, 4096, 4096), (8, 6144, 4096), (3, 1000, 1024), (5, 4100, 14336), (8, 40, 128)])
+@pytest.mark.parametrize("block", [64, 128])
+def test_gemm_nf4(ops, orc, mnk, block):
+    """The fused NF4 GEMV against dequantise (the reference's decode) then an f64 product; tolerance as for the other GEMMs."""
+    m, n, k = mnk
+    w = orc.gaussian((n, k), 0.02, 61)
+    xb = _bf16_round(orc.gaussian((m, k), 1.0, 62))
+    packed, am = ops.nf4_quant(to_dev(w.ravel()), block)
+    rp, ra = orc.ref_nf4_encode(w.ravel(), block)
+    assert np.array_equal(packed.cpu().numpy(), rp) and np.array_equal(am.cpu().numpy(), ra)
+    y = ops.gemm_nf4(xb.cuda(), packed, am, n, block)
+    torch.cuda.synchronize()
+    wd = orc.ref_nf4_decode(rp, ra, block).reshape(n, k).astype(np.float64)
+    ref = xb.float().numpy().astype(np.float64) @ wd.T
+    got = y.float().cpu().numpy()
+    assert np.abs(got - ref).max() <= 1e-2 * np.abs(ref).max(), f"nf4 gemv {mnk} block {block}: {np.abs(got - ref).max()} vs {np.abs(ref).max()}"
+
+
+def test_gemm_nf4_errors(ops):
+    from oxicuda_b200.errors import OxqError
+    x = torch.zeros((9, 128), dtype=torch.bfloat16, device="cuda")
+    packed = torch.zeros(16 * 64, dtype=torch.uint8, device="cuda")
+    am = torch.ones(32, device="cuda")
+    with pytest.raises(OxqError):
+        ops.gemm_nf4(x, packed, am, 16, 64)                               # more than 8 batch rows
+    with pytest.raises(OxqError):
+        ops.gemm_nf4(x[:2], packed, am, 16, 96)                           # block not a multiple of 64

@@ -53,14 +53,6 @@ __global__ void __launch_bounds__(NG_WARPS * 32, 2) nf4_gemv_kernel(const Nf4Par
     __shared__ uint32_t lv[16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     pdl_trigger();
-    if (threadIdx.x < 16) lv[threadIdx.x] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c_nf4_levels[threadIdx.x]));
-    __syncthreads();
-    for (int e = threadIdx.x; e < 256 * 8; e += NG_WARPS * 32) {              // 16-byte stores: four lanes' copies at a time
-        const int idx = e >> 3;
-        const uint32_t v = lv[idx & 15] | (lv[idx >> 4] << 16);
-        reinterpret_cast<uint4*>(tab)[e] = make_uint4(v, v, v, v);
-    }
-    __syncthreads();
     const uint32_t* tl = tab + lane;
 
     const int spans = p.k >> 6;
@@ -93,6 +85,15 @@ __global__ void __launch_bounds__(NG_WARPS * 32, 2) nf4_gemv_kernel(const Nf4Par
     float total[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     // the weights do not depend on the kernel before this one in the stream; the activations and the output do
     if (s_lo < s_hi) fetch(s_lo, cur_a, cur_b, cur_sa, cur_sb);
+    // the table is built while those first requests are in flight
+    if (threadIdx.x < 16) lv[threadIdx.x] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c_nf4_levels[threadIdx.x]));
+    __syncthreads();
+    for (int e = threadIdx.x; e < 256 * 8; e += NG_WARPS * 32) {              // 16-byte stores: four lanes' copies at a time
+        const int idx = e >> 3;
+        const uint32_t v = lv[idx & 15] | (lv[idx >> 4] << 16);
+        reinterpret_cast<uint4*>(tab)[e] = make_uint4(v, v, v, v);
+    }
+    __syncthreads();
     pdl_wait();
     for (int s0 = s_lo; s0 < s_hi; s0 += NG_CHUNK) {
         if (s0 + NG_CHUNK < s_hi) fetch(s0 + NG_CHUNK, nxt_a, nxt_b, nxt_sa, nxt_sb);

@@ -219,6 +219,9 @@ OXQ_API int32_t oxq_int8_block_dequant(oxq_handle* h, const int8_t* q_dev, const
  * 1e-8), x / absmax clamped to [-1, 1], nearest of the 16 NormalFloat4 levels (the lower index on a tie), two
  * codes per byte with the even element in the low nibble.  packed_dev holds n / 2 bytes, absmax_dev n / block
  * floats.  Errors as the reference: EmptyInput, GroupSizeMismatch (encode), DimensionMismatch (decode). */
+/* The 15 decision thresholds of the NF4 encoder (host call, no device work): out15[i] is the largest f32 whose nearest
+ * level under the reference's f32 comparison (nf4.rs:186-205) is i; the encoder's code is the number of thresholds below x. */
+OXQ_API int32_t oxq_nf4_thresholds(float* out15);
 OXQ_API int32_t oxq_nf4_quant(oxq_handle* h, const float* x_dev, int64_t n, int64_t block, uint8_t* packed_dev, float* absmax_dev);
 OXQ_API int32_t oxq_nf4_dequant(oxq_handle* h, const uint8_t* packed_dev, const float* absmax_dev, int64_t n, int64_t block,
                                 void* y_dev, int y_dtype);

@@ -41,6 +41,7 @@ SIGNATURES = {
     "oxq_int8_block_dequant": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp]),
     "oxq_nf4_quant": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
     "oxq_nf4_dequant": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp, _int]),
+    "oxq_nf4_thresholds": (_i32, [_vp]),
     "oxq_gemm_nf4": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _vp]),
     "oxq_rmsnorm_fp8_quant_rows": (_i32, [_vp, _vp, _int, _vp, _i64, _i64, C.c_float, _vp, _vp]),
     "oxq_silu_gate_fp8_quant": (_i32, [_vp, _vp, _vp, _int, _i64, _vp, _vp]),

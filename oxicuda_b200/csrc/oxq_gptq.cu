@@ -8,14 +8,16 @@
 //   * Cholesky, right-looking in blocks of 32: element (i, j) starts from h[i][j] and has l[i][k] * l[j][k]
 //     subtracted for k = 0, 1, ... in increasing k, then is divided by the pivot (or square-rooted) -- the
 //     sequence of the reference's row-by-row loop.  Products and subtractions are never fused.
-//   * Inverse of the factor, left-looking by blocks of 32 rows: s starts at +0 and accumulates l[i][k] * li[k][j]
-//     in increasing k; terms with k < j multiply stored zeros and leave s at +0.
+//   * Inverse of the factor, right-looking by blocks of 32 rows: s starts at +0 and accumulates l[i][k] * li[k][j]
+//     in increasing k (a finished block of rows is pushed into every later row before the next block is finished);
+//     terms with k < j multiply stored zeros and leave s at +0.
 //   * H^-1 = (L^-1)^T L^-1 (upper triangle): sums over m in increasing m, again with stored zeros in front.
 //   * The column loop: a column's correction by all earlier columns, w[i][k] -= err_j[i] * hinv[j][k] for
 //     j = 0 .. k-1, is applied lazily but in increasing j, one rounded product and one rounded subtraction each.
 //     Rows are independent except for the per-column scale (a maximum over all rows), which costs one grid-wide
 //     meeting point per column: the kernel is launched cooperatively with every CTA resident, each CTA owns a
-//     slice of rows, and the wait is bounded (two seconds, then OXQ_ERR_DEVICE_TIMEOUT in the status word).
+//     slice of rows and publishes its share of the maximum in a tagged slot that the others read (no atomics), and
+//     the wait is bounded (two seconds, then OXQ_ERR_DEVICE_TIMEOUT in the status word).
 #include "oxq_common.cuh"
 
 namespace oxq {

@@ -159,17 +159,26 @@ __global__ void __launch_bounds__(256) int8_block_dequant_kernel(const int8_t* _
 __constant__ float c_nf4[16] = {-1.0f, -0.69619286f, -0.52507305f, -0.3949175f, -0.28444138f, -0.18477343f, -0.09105003f, 0.0f,
                                 0.0795803f, 0.1609302f, 0.2461123f, 0.33791524f, 0.44070983f, 0.562617f, 0.72295684f, 1.0f};
 
-// Index of the level nearest to v in [-1, 1]; between two levels the lower index wins a tie.  Same steps as the
-// reference: first index whose level is >= v, then the two distances compared in f32.
-__device__ __forceinline__ uint32_t nearest_nf4(float v, const float* lut) {
-    int lo = 0;
-#pragma unroll
-    for (int step = 8; step > 0; step >>= 1)                 // lo = number of levels below v (levels are strictly increasing)
-        if (lut[lo + step - 1] < v) lo += step;
-    if (lo == 0) return 0;                                   // v <= -1 (NaN too: every comparison is false)
-    if (lo == 15 && lut[15] < v) return 15;
-    const float d_lo = fabsf(v - lut[lo - 1]), d_hi = fabsf(lut[lo] - v);
-    return d_lo <= d_hi ? (uint32_t)(lo - 1) : (uint32_t)lo;
+// Index of the level nearest to v in [-1, 1]; between two levels the lower index wins a tie (nf4.rs:186-205: first
+// index whose level is >= v, then |v - level[lo-1]| <= |level[lo] - v| in f32).  Both distances are monotone in v, so
+// for every pair of neighbours there is one f32 value up to which the lower level wins: kNf4Thr[i] is the largest
+// f32 whose nearest level is i under exactly that f32 comparison (found by bisection over bit patterns against the
+// reference's function; they sit within an ulp or two of the arithmetic midpoints).  The code is then the number of
+// thresholds below v: four comparisons against constants picked by the earlier outcomes, no table and no memory.
+// NaN compares false everywhere and gives 0, as in the reference.
+#define NF4_THR_BITS {0xBF591CD9u, 0xBF1C5271u, 0xBEEB8480u, 0xBEADEA77u, 0xBE703CEDu, 0xBE0D38BCu, 0xBD3A7870u, 0x3D22FAFFu, \
+                      0x3DF64862u, 0x3E5067E0u, 0x3E9582D4u, 0x3EC753F9u, 0x3F006D03u, 0x3F248DAFu, 0x3F5C89D9u}
+__device__ __forceinline__ uint32_t nearest_nf4(float v) {
+    constexpr uint32_t T[15] = NF4_THR_BITS;
+#define THR(i) __uint_as_float(T[i])
+    const bool b3 = v > THR(7);
+    const bool b2 = v > (b3 ? THR(11) : THR(3));
+    const bool b1 = v > (b3 ? (b2 ? THR(13) : THR(9)) : (b2 ? THR(5) : THR(1)));
+    const float t0 = b3 ? (b2 ? (b1 ? THR(14) : THR(12)) : (b1 ? THR(10) : THR(8)))
+                        : (b2 ? (b1 ? THR(6) : THR(4)) : (b1 ? THR(2) : THR(0)));
+#undef THR
+    const bool b0 = v > t0;
+    return ((uint32_t)b3 << 3) | ((uint32_t)b2 << 2) | ((uint32_t)b1 << 1) | (uint32_t)b0;
 }
 
 // Eight consecutive elements per lane (one packed word); LPB lanes share a block of 8 * LPB elements.
@@ -178,9 +187,6 @@ __global__ void __launch_bounds__(256) nf4_quant_kernel(const float* __restrict_
                                                         float* __restrict__ absmaxs) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float lut[16];                                 // lanes look up different levels: shared memory, not the constant bank
-    if (threadIdx.x < 16) lut[threadIdx.x] = c_nf4[threadIdx.x];
-    __syncthreads();
     const int64_t nitems = n >> 3;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     // whole warps iterate together so the shuffles below always have their partners
@@ -205,7 +211,7 @@ __global__ void __launch_bounds__(256) nf4_quant_kernel(const float* __restrict_
 #pragma unroll
         for (int e = 0; e < 8; e++) {
             const float normed = fminf(fmaxf(div_exact(f[e], d), -1.0f), 1.0f);
-            w |= nearest_nf4(normed, lut) << (4 * e);
+            w |= nearest_nf4(normed) << (4 * e);
         }
         __stcs(reinterpret_cast<uint32_t*>(packed) + t, w);
         if ((t & (LPB - 1)) == 0) absmaxs[t / LPB] = am;
@@ -217,9 +223,6 @@ __global__ void __launch_bounds__(256) nf4_quant_generic_kernel(const float* __r
                                                                 uint8_t* __restrict__ packed, float* __restrict__ absmaxs) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float lut[16];
-    if (threadIdx.x < 16) lut[threadIdx.x] = c_nf4[threadIdx.x];
-    __syncthreads();
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t b = warp0; b < nblocks; b += nwarps) {
@@ -231,7 +234,7 @@ __global__ void __launch_bounds__(256) nf4_quant_generic_kernel(const float* __r
         if (lane == 0) absmaxs[b] = am;
         for (int64_t i = lane; i < block / 2; i += 32) {
             const float v0 = fminf(fmaxf(__fdiv_rn(xb[2 * i], am), -1.0f), 1.0f), v1 = fminf(fmaxf(__fdiv_rn(xb[2 * i + 1], am), -1.0f), 1.0f);
-            packed[b * (block / 2) + i] = (uint8_t)(nearest_nf4(v0, lut) | (nearest_nf4(v1, lut) << 4));
+            packed[b * (block / 2) + i] = (uint8_t)(nearest_nf4(v0) | (nearest_nf4(v1) << 4));
         }
     }
 }
@@ -727,6 +730,13 @@ int32_t oxq_bias_add_bf16(oxq_handle* h, void* y, int64_t ldy, const float* bias
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     oxq_launch(bias_add_bf16_kernel, grid_cap(h, m * n / 8, 256, 8), 256, 0, h->stream, (__nv_bfloat16*)y, ldy, bias, m, n);
     OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
+int32_t oxq_nf4_thresholds(float* out15) {
+    if (!out15) return OXQ_ERR_INVALID_ARGUMENT;
+    const uint32_t t[15] = NF4_THR_BITS;
+    memcpy(out15, t, sizeof(t));
     return OXQ_OK;
 }
 

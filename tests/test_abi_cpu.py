@@ -72,3 +72,31 @@ def test_error_mapping():
         raise_for_status(1000 + 700)
     assert e.value.variant == "Cuda"
     raise_for_status(0)
+
+
+def test_nf4_thresholds_match_the_reference_comparison():
+    """The NF4 encoder counts decision thresholds below x instead of searching the level table.  Each threshold must be
+    the largest f32 whose nearest level, under the reference's own f32 distance comparison (nf4.rs:186-205), is the
+    lower neighbour: the value itself maps to level i, the next f32 up maps to level i + 1 (no GPU involved)."""
+    import ctypes as C
+    import numpy as np
+    from oracle import oracle as orc
+    from oxicuda_b200 import _ffi
+    orc.build()
+    near = orc.lib().orc_ref_nearest_nf4
+    near.argtypes, near.restype = [C.c_float], C.c_int
+    thr = np.zeros(15, np.float32)
+    assert _ffi.load().oxq_nf4_thresholds(thr.ctypes.data_as(C.c_void_p)) == 0
+    assert (np.diff(thr) > 0).all()
+    for i, t in enumerate(thr):
+        up = np.nextafter(t, np.float32(2.0), dtype=np.float32)
+        assert near(float(t)) == i and near(float(up)) == i + 1, (i, float(t))
+        # and a sweep of 64 ulps around it: the count of thresholds below x equals the reference's index
+        v = t
+        for _ in range(64):
+            v = np.nextafter(v, np.float32(-2.0), dtype=np.float32)
+        for _ in range(128):
+            assert int((v > thr).sum()) == near(float(v)), float(v)
+            v = np.nextafter(v, np.float32(2.0), dtype=np.float32)
+    for v in (-2.0, -1.0, 0.0, 1.0, 2.0, float("nan")):
+        assert int((np.float32(v) > thr).sum()) == near(v)

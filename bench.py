@@ -666,6 +666,25 @@ def run_case(args):
             it[0] += 1
             ops.gemm_w4a16(x, r[0], r[1], r[2], 128, workspace=ws, out=y)
         work, unit = float(n * k // 2 + n * k // 128 * 2 + n * k // 256 + m * k * 2 + m * n * 2), "GB/s"
+    elif args.case in ("nf4_quant", "gemm_nf4"):
+        n, k, m = 14336 * sz // 8192, 4096, args.m                        # --size 8192 is the full 14336 x 4096 weight
+        ring = [torch.randn((n, k), generator=g, device="cuda") * 0.02 for _ in range(3)]
+        it = [0]
+        if args.case == "nf4_quant":
+            def fn():
+                it[0] += 1
+                ops.nf4_quant(ring[it[0] % 3].view(-1), 64)
+            work, unit = float(n * k * 4 + n * k // 2 + n * k // 64 * 4), "GB/s"
+        else:
+            packs = [ops.nf4_quant(ring[i % 3].view(-1), 64) for i in range(6)]
+            x = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+            y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+
+            def fn():
+                it[0] += 1
+                r = packs[it[0] % 6]
+                ops.gemm_nf4(x, r[0], r[1], n, 64, out=y)
+            work, unit = float(n * k // 2 + n * k // 64 * 4 + m * (k + n) * 2), "GB/s"
     else:
         raise SystemExit(f"unknown case {args.case}")
     for _ in range(args.warmup):
@@ -683,7 +702,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
-    ap.add_argument("--case", default=None, help="single-kernel mode, e.g. gemm_fp8, gemm_mxfp8, gemm_nvfp4, fp8_quant, gemm_w4a16")
+    ap.add_argument("--case", default=None, help="single-kernel mode, e.g. gemm_fp8, gemm_mxfp8, gemm_nvfp4, fp8_quant, gemm_w4a16, nf4_quant, gemm_nf4")
     ap.add_argument("--size", type=int, default=8192)
     ap.add_argument("--m", type=int, default=8)
     args = ap.parse_args()

@@ -47,7 +47,7 @@ struct Nf4Params {
     __nv_bfloat16* y;            // [m x n]
 };
 
-__global__ void __launch_bounds__(NG_WARPS * 32, 2) nf4_gemv_kernel(const Nf4Params p) {
+__global__ void __launch_bounds__(NG_WARPS * 32, 3) nf4_gemv_kernel(const Nf4Params p) {
     extern __shared__ __align__(16) uint32_t tab[];           // [256][32]: entry i of lane l at i * 32 + l
     __shared__ float red[NG_WARPS][16][8];
     __shared__ uint32_t lv[16];

@@ -168,17 +168,26 @@ __constant__ float c_nf4[16] = {-1.0f, -0.69619286f, -0.52507305f, -0.3949175f, 
 // NaN compares false everywhere and gives 0, as in the reference.
 #define NF4_THR_BITS {0xBF591CD9u, 0xBF1C5271u, 0xBEEB8480u, 0xBEADEA77u, 0xBE703CEDu, 0xBE0D38BCu, 0xBD3A7870u, 0x3D22FAFFu, \
                       0x3DF64862u, 0x3E5067E0u, 0x3E9582D4u, 0x3EC753F9u, 0x3F006D03u, 0x3F248DAFu, 0x3F5C89D9u}
-__device__ __forceinline__ uint32_t nearest_nf4(float v) {
+__device__ __forceinline__ uint32_t nearest_nf4(float v, const float* thr) {
+    // thr: the 15 thresholds (and +Inf as a 16th) in shared memory; 16 words in 16 banks, so any mix of indices in a
+    // warp is served in one pass.  The two upper levels of the search use constants, the two lower ones the table.
     constexpr uint32_t T[15] = NF4_THR_BITS;
-#define THR(i) __uint_as_float(T[i])
-    const bool b3 = v > THR(7);
-    const bool b2 = v > (b3 ? THR(11) : THR(3));
-    const bool b1 = v > (b3 ? (b2 ? THR(13) : THR(9)) : (b2 ? THR(5) : THR(1)));
-    const float t0 = b3 ? (b2 ? (b1 ? THR(14) : THR(12)) : (b1 ? THR(10) : THR(8)))
-                        : (b2 ? (b1 ? THR(6) : THR(4)) : (b1 ? THR(2) : THR(0)));
-#undef THR
-    const bool b0 = v > t0;
-    return ((uint32_t)b3 << 3) | ((uint32_t)b2 << 2) | ((uint32_t)b1 << 1) | (uint32_t)b0;
+    const bool b3 = v > __uint_as_float(T[7]);
+    const bool b2 = v > (b3 ? __uint_as_float(T[11]) : __uint_as_float(T[3]));
+    uint32_t lo = (b3 ? 8u : 0u) + (b2 ? 4u : 0u);
+    lo += thr[lo + 1] < v ? 2u : 0u;
+    lo += thr[lo] < v ? 1u : 0u;
+    return lo;
+}
+__device__ __forceinline__ void nf4_load_thresholds(float* thr) {
+    constexpr uint32_t T[15] = NF4_THR_BITS;
+    if (threadIdx.x < 16) {
+        uint32_t bits = 0x7F800000u;
+#pragma unroll
+        for (int i = 0; i < 15; i++) bits = threadIdx.x == i ? T[i] : bits;
+        thr[threadIdx.x] = __uint_as_float(bits);
+    }
+    __syncthreads();
 }
 
 // Eight consecutive elements per lane (one packed word); LPB lanes share a block of 8 * LPB elements.
@@ -187,6 +196,8 @@ __global__ void __launch_bounds__(256) nf4_quant_kernel(const float* __restrict_
                                                         float* __restrict__ absmaxs) {
     pdl_trigger();
     pdl_wait();
+    __shared__ float thr[16];
+    nf4_load_thresholds(thr);
     const int64_t nitems = n >> 3;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     // whole warps iterate together so the shuffles below always have their partners
@@ -210,8 +221,9 @@ __global__ void __launch_bounds__(256) nf4_quant_kernel(const float* __restrict_
         uint32_t w = 0;
 #pragma unroll
         for (int e = 0; e < 8; e++) {
-            const float normed = fminf(fmaxf(div_exact(f[e], d), -1.0f), 1.0f);
-            w |= nearest_nf4(normed) << (4 * e);
+            // |x| <= absmax, so the quotient is already in [-1, 1] (the reference's clamp never acts); a NaN stays NaN
+            // and takes code 0, +-0 both take code 7
+            w |= nearest_nf4(div_exact_bounded(f[e], d), thr) << (4 * e);
         }
         __stcs(reinterpret_cast<uint32_t*>(packed) + t, w);
         if ((t & (LPB - 1)) == 0) absmaxs[t / LPB] = am;
@@ -223,6 +235,8 @@ __global__ void __launch_bounds__(256) nf4_quant_generic_kernel(const float* __r
                                                                 uint8_t* __restrict__ packed, float* __restrict__ absmaxs) {
     pdl_trigger();
     pdl_wait();
+    __shared__ float thr[16];
+    nf4_load_thresholds(thr);
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5, nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
     for (int64_t b = warp0; b < nblocks; b += nwarps) {
@@ -234,7 +248,7 @@ __global__ void __launch_bounds__(256) nf4_quant_generic_kernel(const float* __r
         if (lane == 0) absmaxs[b] = am;
         for (int64_t i = lane; i < block / 2; i += 32) {
             const float v0 = fminf(fmaxf(__fdiv_rn(xb[2 * i], am), -1.0f), 1.0f), v1 = fminf(fmaxf(__fdiv_rn(xb[2 * i + 1], am), -1.0f), 1.0f);
-            packed[b * (block / 2) + i] = (uint8_t)(nearest_nf4(v0) | (nearest_nf4(v1) << 4));
+            packed[b * (block / 2) + i] = (uint8_t)(nearest_nf4(v0, thr) | (nearest_nf4(v1, thr) << 4));
         }
     }
 }

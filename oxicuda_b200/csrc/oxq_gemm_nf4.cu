@@ -41,6 +41,7 @@ struct Nf4Params {
     int m, n, k;
     int bpr;                     // absmax blocks per weight row
     int spb;                     // 64-wide spans per absmax block
+    int spb_shift;               // log2(spb) when spb is a power of two, else -1
     const __nv_bfloat16* x;      // [m x k]
     const uint8_t* packed;       // [n x k/2]
     const float* absmax;         // [n x bpr]
@@ -75,7 +76,7 @@ __global__ void __launch_bounds__(NG_WARPS * 32, 3) nf4_gemv_kernel(const Nf4Par
             if (s < s_hi) {
                 wa[j] = ld_stream_u2(pa + (size_t)s * 32);
                 wb[j] = ld_stream_u2(pb + (size_t)s * 32);
-                const int b = s / p.spb;
+                const int b = p.spb_shift >= 0 ? (s >> p.spb_shift) : (s / p.spb);
                 sa[j] = __ldg(aa + b);
                 sb[j] = __ldg(ab + b);
             }
@@ -156,6 +157,8 @@ extern "C" int32_t oxq_gemm_nf4(oxq_handle* h, int64_t m, int64_t n, int64_t k, 
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     Nf4Params p;
     p.m = (int)m; p.n = (int)n; p.k = (int)k; p.bpr = (int)(k / block); p.spb = (int)(block / 64);
+    p.spb_shift = -1;
+    for (int sh = 0; sh < 20; sh++) if ((1 << sh) == p.spb) p.spb_shift = sh;
     p.x = (const __nv_bfloat16*)x; p.packed = packed; p.absmax = absmax; p.y = (__nv_bfloat16*)y;
     OXQ_CUDA(h, oxq_launch(nf4_gemv_kernel, (unsigned)((n + 15) / 16), NG_WARPS * 32, 256 * 32 * sizeof(uint32_t), h->stream, p));
     return OXQ_OK;

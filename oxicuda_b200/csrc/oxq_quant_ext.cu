@@ -192,7 +192,7 @@ __device__ __forceinline__ void nf4_load_thresholds(float* thr) {
 
 // Eight consecutive elements per lane (one packed word); LPB lanes share a block of 8 * LPB elements.
 template <int LPB>
-__global__ void __launch_bounds__(256) nf4_quant_kernel(const float* __restrict__ x, int64_t n, uint8_t* __restrict__ packed,
+__global__ void __launch_bounds__(256, 5) nf4_quant_kernel(const float* __restrict__ x, int64_t n, uint8_t* __restrict__ packed,
                                                         float* __restrict__ absmaxs) {
     pdl_trigger();
     pdl_wait();
@@ -200,33 +200,41 @@ __global__ void __launch_bounds__(256) nf4_quant_kernel(const float* __restrict_
     nf4_load_thresholds(thr);
     const int64_t nitems = n >> 3;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    // whole warps iterate together so the shuffles below always have their partners
-    for (int64_t t0 = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); t0 < nitems; t0 += stride) {
-        const int64_t t = t0 + (threadIdx.x & 31);
-        const bool live = t < nitems;
-        float f[8];
-        if (live) load8f(x + t * 8, f);
-        else {
+    // whole warps iterate together so the shuffles below always have their partners; two items per lane and trip, both
+    // requested before either is encoded
+    constexpr int ILP = 2;
+    for (int64_t t0 = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); t0 < nitems; t0 += ILP * stride) {
+        float f[ILP][8];
 #pragma unroll
-            for (int e = 0; e < 8; e++) f[e] = 0.0f;
+        for (int j = 0; j < ILP; j++) {
+            const int64_t t = t0 + j * stride + (threadIdx.x & 31);
+            if (t < nitems) load8f(x + t * 8, f[j]);
+            else {
+#pragma unroll
+                for (int e = 0; e < 8; e++) f[j][e] = 0.0f;
+            }
         }
-        float am = 0.0f;
 #pragma unroll
-        for (int e = 0; e < 8; e++) am = fmaxf(am, fabsf(f[e]));
+        for (int j = 0; j < ILP; j++) {
+            const int64_t t = t0 + j * stride + (threadIdx.x & 31);
+            float am = 0.0f;
 #pragma unroll
-        for (int o = LPB / 2; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
-        am = am < 1e-8f ? 1e-8f : am;
-        if (!live) continue;
-        const InvDiv d = make_invdiv(am);
-        uint32_t w = 0;
+            for (int e = 0; e < 8; e++) am = fmaxf(am, fabsf(f[j][e]));
 #pragma unroll
-        for (int e = 0; e < 8; e++) {
-            // |x| <= absmax, so the quotient is already in [-1, 1] (the reference's clamp never acts); a NaN stays NaN
-            // and takes code 0, +-0 both take code 7
-            w |= nearest_nf4(div_exact_bounded(f[e], d), thr) << (4 * e);
+            for (int o = LPB / 2; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+            am = am < 1e-8f ? 1e-8f : am;
+            if (t >= nitems) continue;
+            const InvDiv d = make_invdiv(am);
+            uint32_t w = 0;
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                // |x| <= absmax, so the quotient is already in [-1, 1] (the reference's clamp never acts); a NaN stays
+                // NaN and takes code 0, +-0 both take code 7
+                w |= nearest_nf4(div_exact_bounded(f[j][e], d), thr) << (4 * e);
+            }
+            __stcs(reinterpret_cast<uint32_t*>(packed) + t, w);
+            if ((t & (LPB - 1)) == 0) absmaxs[t / LPB] = am;
         }
-        __stcs(reinterpret_cast<uint32_t*>(packed) + t, w);
-        if ((t & (LPB - 1)) == 0) absmaxs[t / LPB] = am;
     }
 }
 
@@ -762,7 +770,7 @@ int32_t oxq_nf4_quant(oxq_handle* h, const float* x, int64_t n, int64_t block, u
     if (!x || !packed || !absmaxs) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null pointer");
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     const bool vec = aligned16(x) && ((uintptr_t)packed & 3u) == 0;
-    const int grid = grid_cap(h, n / 8 + 1, 256, 8);
+    const int grid = grid_cap(h, n / 16 + 1, 256, 5);                 // five CTAs of this kernel fit an SM: one full wave, grid-stride loop
     if (vec && block == 32) oxq_launch(nf4_quant_kernel<4>, grid, 256, 0, h->stream, x, n, packed, absmaxs);
     else if (vec && block == 64) oxq_launch(nf4_quant_kernel<8>, grid, 256, 0, h->stream, x, n, packed, absmaxs);
     else if (vec && block == 128) oxq_launch(nf4_quant_kernel<16>, grid, 256, 0, h->stream, x, n, packed, absmaxs);

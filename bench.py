@@ -666,6 +666,23 @@ def run_case(args):
             it[0] += 1
             ops.gemm_w4a16(x, r[0], r[1], r[2], 128, workspace=ws, out=y)
         work, unit = float(n * k // 2 + n * k // 128 * 2 + n * k // 256 + m * k * 2 + m * n * 2), "GB/s"
+    elif args.case in ("rmsnorm_int8", "rmsnorm_fp8", "silu_gate_fp8"):
+        ring = [torch.randn((sz, sz), generator=g, device="cuda").to(torch.bfloat16) for _ in range(3)]
+        wn = torch.ones(sz, device="cuda")
+        one = torch.ones(1, device="cuda")
+        it = [0]
+
+        def fn():
+            it[0] += 1
+            r = ring[it[0] % 3]
+            if args.case == "rmsnorm_int8":
+                ops.rmsnorm_int8_quant_rows(r, wn)
+            elif args.case == "rmsnorm_fp8":
+                ops.rmsnorm_fp8_quant_rows(r, wn, one)
+            else:
+                ops.silu_gate_fp8_quant(r, ring[(it[0] + 1) % 3], one)
+        work, unit = (5.0 if args.case == "silu_gate_fp8" else 3.0) * sz * sz, "GB/s"
+        m = n = k = sz
     elif args.case in ("nf4_quant", "gemm_nf4"):
         n, k, m = 14336 * sz // 8192, 4096, args.m                        # --size 8192 is the full 14336 x 4096 weight
         ring = [torch.randn((n, k), generator=g, device="cuda") * 0.02 for _ in range(3)]

@@ -462,7 +462,7 @@ __global__ void __launch_bounds__(256) silu_gate_fp8_kernel(const T* __restrict_
             raw8_to_f32(h ? g1 : g0, g);
             raw8_to_f32(h ? u1 : u0, u);
 #pragma unroll
-            for (int e = 0; e < 8; e++) v[e] = div_exact(__fdiv_rn(g[e], 1.0f + expf(-g[e])) * u[e], d);
+            for (int e = 0; e < 8; e++) v[e] = div_exact(__fdividef(g[e], 1.0f + __expf(-g[e])) * u[e], d);   // a few f32 ulp, far below an E4M3 step
             uint2 o;
             o.x = (uint32_t)cvt_e4m3x2(v[0], v[1]) | ((uint32_t)cvt_e4m3x2(v[2], v[3]) << 16);
             o.y = (uint32_t)cvt_e4m3x2(v[4], v[5]) | ((uint32_t)cvt_e4m3x2(v[6], v[7]) << 16);
@@ -472,7 +472,7 @@ __global__ void __launch_bounds__(256) silu_gate_fp8_kernel(const T* __restrict_
     if (blockIdx.x == 0) {                                    // ragged tail
         for (int64_t i = nitems * 8 + threadIdx.x; i < n; i += blockDim.x) {
             const float g = Elem<T>::to_f32(gate[i]), u = Elem<T>::to_f32(up[i]);
-            q[i] = (uint8_t)(cvt_e4m3x2(div_exact(__fdiv_rn(g, 1.0f + expf(-g)) * u, d), 0.0f) & 0xFF);
+            q[i] = (uint8_t)(cvt_e4m3x2(div_exact(__fdividef(g, 1.0f + __expf(-g)) * u, d), 0.0f) & 0xFF);
         }
     }
 }

@@ -7,7 +7,8 @@
 //          whole K, activations read from L1, nothing combined across CTAs) and w4a16_decode_kernel (up to
 //          16 rows per pass, split along K across CTAs; partial sums are combined with f32 atomics in a
 //          caller-provided workspace that the last CTA of each row block drains).
-//   W8A32: int8 codes -> f32, plain FMAs (the benchmark's CPU-runnable configuration).
+//   W8A32: int8 codes are exact in TF32, the f32 activations are split in two TF32 halves, mma.sync m16n8k8 (the
+//          benchmark's CPU-runnable configuration).
 #include "oxq_common.cuh"
 #include <stdlib.h>
 
@@ -365,10 +366,6 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 2) w4a16_gemv_kernel(const GvPa
 // W8A32
 // ------------------------------------------------------------------------------------------------
 
-constexpr int W8_MT = 8;            // batch rows per pass
-constexpr int W8_KC = 1024;         // K elements staged per pass
-constexpr int W8_RPW = 2;           // weight rows per warp
-
 // four int8 codes of a word -> f32: the byte (xor 0x80, an unsigned 0..255) becomes the low mantissa byte of
 // 2^23, and 2^23 + 128 is subtracted; exact, and on the FMA pipe instead of the conversion unit
 __device__ __forceinline__ void i8x4_to_f32(uint32_t u, float (&f)[4]) {
@@ -379,81 +376,107 @@ __device__ __forceinline__ void i8x4_to_f32(uint32_t u, float (&f)[4]) {
     f[3] = __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7543)) - 8388736.0f;
 }
 
-// Shared-memory order of the activation chunk: for each 512-wide block, [q][lane] float4 with
-// k = block*512 + lane*16 + 4q, so a lane's four float4 reads are conflict-free.
-__global__ void __launch_bounds__(256) w8a32_decode_kernel(const float* __restrict__ x, const int8_t* __restrict__ w,
-                                                           const float* __restrict__ sw, float* __restrict__ y,
-                                                           int m, int n, int k) {
-    pdl_trigger();
-    pdl_wait();
-    __shared__ float4 xs[W8_MT][W8_KC / 4];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int m0 = blockIdx.y * W8_MT;
-    const int row0 = (blockIdx.x * 8 + warp) * W8_RPW;
-    float acc[W8_RPW][W8_MT];
-#pragma unroll
-    for (int r = 0; r < W8_RPW; r++)
-#pragma unroll
-        for (int j = 0; j < W8_MT; j++) acc[r][j] = 0.0f;
+// The shape of the W4A16 GEMV with f32 activations: a CTA owns 16 weight rows over the whole K range for 8 batch
+// rows (or 16 / 32: the converted weights are shared), its warps split K in spans of 64 and meet once in shared memory.  Lane (g, t) streams 16 codes of rows g and
+// g + 8 per span and the 16 matching activations of batch row g.  An int8 code is exact in TF32 (10 mantissa bits);
+// an f32 activation is split into x_hi = tf32(x) and x_lo = tf32(x - x_hi), so two m16n8k8 TF32 MMAs give the product
+// to about 2^-21 relative with f32 accumulation (an f32 FMA loop spends eight FMAs per weight on 8 batch rows).
+constexpr int W8T_WARPS = 8;
+constexpr int W8T_CHUNK = 4;           // 64-wide spans per register buffer
 
-    for (int kc0 = 0; kc0 < k; kc0 += W8_KC) {
-        const int kc = min(W8_KC, k - kc0);
-        // the chunk's weights are requested first: they travel from HBM while the activations are staged
-        uint4 wv[W8_KC / 512][W8_RPW];
+__device__ __forceinline__ void mma_tf32_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t to_tf32(float v) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return r;
+}
+
+// NT: tiles of 8 batch rows handled by one CTA (the converted weights are shared by the tiles)
+template <int NT>
+__global__ void __launch_bounds__(W8T_WARPS * 32, 2) w8a32_tc_kernel(const float* __restrict__ x, const int8_t* __restrict__ w,
+                                                                     const float* __restrict__ sw, float* __restrict__ y,
+                                                                     int m, int n, int k) {
+    __shared__ float red[W8T_WARPS][16][8 * NT];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int m0 = blockIdx.y * 8 * NT;
+    const int spans = (k + 63) >> 6;
+    const int s_lo = (int)(((int64_t)warp * spans) / W8T_WARPS), s_hi = (int)(((int64_t)(warp + 1) * spans) / W8T_WARPS);
+    const int row_a = min((int)blockIdx.x * 16 + g, n - 1), row_b = min((int)blockIdx.x * 16 + g + 8, n - 1);
+    const int8_t* pa = w + (size_t)row_a * k + 16 * t;
+    const int8_t* pb = w + (size_t)row_b * k + 16 * t;
+
+    uint4 cur_a[W8T_CHUNK], cur_b[W8T_CHUNK], nxt_a[W8T_CHUNK], nxt_b[W8T_CHUNK];
+    auto fetch = [&](int s0, uint4 (&wa)[W8T_CHUNK], uint4 (&wb)[W8T_CHUNK]) {
 #pragma unroll
-        for (int kb = 0; kb < W8_KC / 512; kb++) {
-            const int koff = kc0 + kb * 512 + lane * 16;
-#pragma unroll
-            for (int r = 0; r < W8_RPW; r++) {
-                wv[kb][r] = make_uint4(0, 0, 0, 0);
-                if (row0 + r < n && kb * 512 < kc && koff < k) wv[kb][r] = ld_stream_u4(w + (size_t)(row0 + r) * k + koff);
+        for (int j = 0; j < W8T_CHUNK; j++) {
+            const int s = s0 + j;
+            // codes of zero contribute nothing: a span past the warp's range, or the ragged end of K (k is a multiple of 16)
+            wa[j] = make_uint4(0, 0, 0, 0); wb[j] = wa[j];
+            if (s < s_hi && s * 64 + 16 * t < k) {
+                wa[j] = ld_stream_u4(pa + (size_t)s * 64);
+                wb[j] = ld_stream_u4(pb + (size_t)s * 64);
             }
         }
-        __syncthreads();
-        for (int it = tid; it < W8_MT * (W8_KC / 4); it += 256) {
-            const int j = it / (W8_KC / 4), f = it - j * (W8_KC / 4);      // f: float4 index inside the chunk
-            const int kk = f * 4;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (m0 + j < m && kk < kc) v = __ldg(reinterpret_cast<const float4*>(x + (size_t)(m0 + j) * k + kc0 + kk));
-            const int blk = kk >> 9, in = kk & 511, ln = in >> 4, q = (in & 15) >> 2;
-            xs[j][blk * 128 + q * 32 + ln] = v;
-        }
-        __syncthreads();
+    };
+    float acc[NT][4];
 #pragma unroll
-        for (int kb = 0; kb < W8_KC / 512; kb++) {
-            if (kb * 512 < kc) {
+    for (int i = 0; i < NT; i++) { acc[i][0] = 0.0f; acc[i][1] = 0.0f; acc[i][2] = 0.0f; acc[i][3] = 0.0f; }
+    // the weights do not depend on the kernel before this one in the stream; the activations and the output do
+    pdl_trigger();
+    if (s_lo < s_hi) fetch(s_lo, cur_a, cur_b);
+    pdl_wait();
+    for (int s0 = s_lo; s0 < s_hi; s0 += W8T_CHUNK) {
+        if (s0 + W8T_CHUNK < s_hi) fetch(s0 + W8T_CHUNK, nxt_a, nxt_b);
+#pragma unroll
+        for (int j = 0; j < W8T_CHUNK; j++) {
+            const int s = s0 + j;
+            if (s < s_hi) {
+                const bool in_k = s * 64 + 16 * t < k;
+                const uint32_t wwa[4] = {cur_a[j].x, cur_a[j].y, cur_a[j].z, cur_a[j].w}, wwb[4] = {cur_b[j].x, cur_b[j].y, cur_b[j].z, cur_b[j].w};
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    float wf[W8_RPW][4];
+                    float fa[4], fb[4];
+                    i8x4_to_f32(wwa[q], fa);
+                    i8x4_to_f32(wwb[q], fb);
 #pragma unroll
-                    for (int r = 0; r < W8_RPW; r++) {
-                        const uint32_t u = q == 0 ? wv[kb][r].x : (q == 1 ? wv[kb][r].y : (q == 2 ? wv[kb][r].z : wv[kb][r].w));
-                        i8x4_to_f32(u, wf[r]);
-                    }
+                    for (int i = 0; i < NT; i++) {
+                        const int mrow = m0 + 8 * i + g;
+                        float4 xv = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        if (in_k && mrow < m) xv = __ldg(reinterpret_cast<const float4*>(x + (size_t)mrow * k + (size_t)s * 64 + 16 * t) + q);
+                        const float xf[4] = {xv.x, xv.y, xv.z, xv.w};
+                        uint32_t hi[4], lo[4];
 #pragma unroll
-                    for (int j = 0; j < W8_MT; j++) {
-                        const float4 xv = xs[j][kb * 128 + q * 32 + lane];
-#pragma unroll
-                        for (int r = 0; r < W8_RPW; r++) {
-                            acc[r][j] = fmaf(wf[r][0], xv.x, acc[r][j]);
-                            acc[r][j] = fmaf(wf[r][1], xv.y, acc[r][j]);
-                            acc[r][j] = fmaf(wf[r][2], xv.z, acc[r][j]);
-                            acc[r][j] = fmaf(wf[r][3], xv.w, acc[r][j]);
-                        }
+                        for (int e = 0; e < 4; e++) { hi[e] = to_tf32(xf[e]); lo[e] = to_tf32(xf[e] - __uint_as_float(hi[e])); }
+                        // code 4q + e of the lane meets activation 4q + e: k slots (t, t + 4) of one MMA take e = (0, 1), then (2, 3)
+                        mma_tf32_1688(acc[i], __float_as_uint(fa[0]), __float_as_uint(fb[0]), __float_as_uint(fa[1]), __float_as_uint(fb[1]), hi[0], hi[1]);
+                        mma_tf32_1688(acc[i], __float_as_uint(fa[0]), __float_as_uint(fb[0]), __float_as_uint(fa[1]), __float_as_uint(fb[1]), lo[0], lo[1]);
+                        mma_tf32_1688(acc[i], __float_as_uint(fa[2]), __float_as_uint(fb[2]), __float_as_uint(fa[3]), __float_as_uint(fb[3]), hi[2], hi[3]);
+                        mma_tf32_1688(acc[i], __float_as_uint(fa[2]), __float_as_uint(fb[2]), __float_as_uint(fa[3]), __float_as_uint(fb[3]), lo[2], lo[3]);
                     }
                 }
             }
         }
+#pragma unroll
+        for (int j = 0; j < W8T_CHUNK; j++) { cur_a[j] = nxt_a[j]; cur_b[j] = nxt_b[j]; }
     }
+    // accumulator element e of tile i: weight row (e < 2 ? g : g + 8), batch row 8i + 2t + (e & 1)
 #pragma unroll
-    for (int r = 0; r < W8_RPW; r++)
+    for (int i = 0; i < NT; i++) {
+        red[warp][g][8 * i + 2 * t] = acc[i][0]; red[warp][g][8 * i + 2 * t + 1] = acc[i][1];
+        red[warp][g + 8][8 * i + 2 * t] = acc[i][2]; red[warp][g + 8][8 * i + 2 * t + 1] = acc[i][3];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 16 * 8 * NT; idx += W8T_WARPS * 32) {
+        const int col = idx >> 4, r = idx & 15;                            // consecutive threads -> consecutive rows of y
+        const int row = (int)blockIdx.x * 16 + r;
+        float v = 0.0f;
 #pragma unroll
-        for (int j = 0; j < W8_MT; j++) {
-            float v = acc[r][j];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0 && row0 + r < n && m0 + j < m) y[(size_t)(m0 + j) * n + row0 + r] = v * __ldg(sw + row0 + r);
-        }
+        for (int wi = 0; wi < W8T_WARPS; wi++) v += red[wi][r][col];
+        if (m0 + col < m && row < n) y[(size_t)(m0 + col) * n + row] = v * __ldg(sw + row);
+    }
 }
 
 }  // namespace decode
@@ -650,10 +673,10 @@ int32_t oxq_gemm_w8a32(oxq_handle* h, int64_t m, int64_t n, int64_t k, const flo
     if ((k & 15) || ((uintptr_t)x & 15u) || ((uintptr_t)w & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k must be a multiple of 16 and x, w 16-byte aligned");
     if (m > 64) OXQ_FAIL(h, OXQ_ERR_UNSUPPORTED_OPERATION, "oxq_gemm_w8a32 covers decode shapes (m <= 64), got m = %lld", (long long)m);
     if (int32_t rc = oxq_require_sm100(h)) return rc;
-    dim3 grid((unsigned)((n + 8 * W8_RPW - 1) / (8 * W8_RPW)), (unsigned)((m + W8_MT - 1) / W8_MT));
-    // launched without the dependent-launch attribute: with it this kernel measured 20-25 % slower (19.7 -> 24.2 us
-    // at 4096 x 4096, one batch row)
-    oxq_launch<false>(w8a32_decode_kernel, grid, 256, 0, h->stream, x, w, sw, y, (int)m, (int)n, (int)k);
+    const unsigned gx = (unsigned)((n + 15) / 16);
+    if (m <= 8) oxq_launch(w8a32_tc_kernel<1>, dim3(gx, 1), W8T_WARPS * 32, 0, h->stream, x, w, sw, y, (int)m, (int)n, (int)k);
+    else if (m <= 16) oxq_launch(w8a32_tc_kernel<2>, dim3(gx, 1), W8T_WARPS * 32, 0, h->stream, x, w, sw, y, (int)m, (int)n, (int)k);
+    else oxq_launch(w8a32_tc_kernel<4>, dim3(gx, (unsigned)((m + 31) / 32)), W8T_WARPS * 32, 0, h->stream, x, w, sw, y, (int)m, (int)n, (int)k);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

@@ -123,7 +123,7 @@ def test_gemm_w8a8(ops, orc, mnk):
     assert np.abs(bf16_bits(y).astype(np.int32) - orc.f32_to_bf16_bits(ref).astype(np.int32)).max() <= 1
 
 
-@pytest.mark.parametrize("mnk", [(8, 4096, 4096), (1, 64, 512), (13, 100, 1040), (32, 256, 2048)])
+@pytest.mark.parametrize("mnk", [(8, 4096, 4096), (1, 64, 512), (13, 100, 1040), (32, 256, 2048), (64, 1000, 4096), (20, 17, 16), (9, 4096, 1024)])
 def test_gemm_w8a32_config1(ops, orc, mnk):
     """Benchmark configuration 1: INT8 per-channel weights, f32 activations, f32 accumulate and output."""
     m, n, k = mnk

@@ -318,7 +318,17 @@ def mlp_extras(torch, peaks):
             for _ in range(3):
                 layer.forward(x)
             iters = 10 if m == 2048 else 30
-            ms = time_region(torch, lambda: layer.forward(x), iters, False) / iters
+            # the step replayed from a CUDA graph, as a serving loop would run it: at decode shapes the six to eight
+            # launches of a step cost more host time than the kernels take
+            fn = lambda: layer.forward(x)  # noqa: E731
+            try:
+                xs_, _, gr_ = layer.capture(m)
+                xs_.copy_(x)
+                fn = gr_.replay
+            except Exception as exc:
+                print(f"graph capture unavailable ({exc}); eager launches", file=sys.stderr)
+                torch.cuda.synchronize()
+            ms = time_region(torch, fn, iters, False) / iters
             out[f"tp_mlp_{variant}_m{m}_tp1"] = {"ms": round(ms, 4), "TFLOP/s": round(layer.flops(m) / (ms * 1e-3) / 1e12, 2),
                                                 "weight_GB/s": round(layer.weight_bytes_local() / (ms * 1e-3) / 1e9, 1),
                                                 "frac_of_hbm": round(layer.weight_bytes_local() / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3)}

@@ -62,6 +62,50 @@ def test_gemm_fp8(ops, orc, mnk):
         assert np.abs(yb - rb).max() <= 1
 
 
+@pytest.mark.parametrize("mnk", [(1, 16, 64), (1, 4096, 4096), (8, 1000, 1040), (3, 520, 384), (5, 28672, 1024), (8, 264, 8192)])
+def test_gemm_fp8_decode_shapes(ops, orc, mnk):
+    """Up to 8 batch rows run the GEMV kernel (mma.sync on the raw E4M3 bytes): same oracle, ragged N and K, alpha."""
+    m, n, k = mnk
+    a = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 0))
+    b = orc.f32_to_bf16_bits(orc.gaussian((n, k), 1.0, 1))
+    qa, sa = ops.fp8_quant_dynamic(bf16_dev(a))
+    qb, sb = ops.fp8_quant_dynamic(bf16_dev(b))
+    y = ops.gemm_fp8(qa, qb, sa[1:], sb[1:])
+    y2 = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_fp8_ex(-2.0, qa, qb, sa[1:], sb[1:], 0.0, y2)
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    da = orc.e4m3_to_f32(qa.cpu().numpy())
+    db = orc.e4m3_to_f32(qb.cpu().numpy())
+    s = np.float32(sa.cpu().numpy()[1]) * np.float32(sb.cpu().numpy()[1])
+    ref = (da.astype(np.float64) @ db.astype(np.float64).T).astype(np.float32) * s
+    _check(_bf16_to_np(y), ref, f"fp8 decode {mnk}")
+    assert torch.equal(y2.float(), y.float() * -2.0)                       # alpha is a power of two: exact
+
+
+@pytest.mark.parametrize("mnk", [(1, 512, 256), (8, 1024, 4096), (5, 256, 1040)])
+def test_gemm_fp8_swiglu_decode_shapes(ops, orc, mnk):
+    """The SwiGLU form of the GEMV: gate and up rows of one output column meet in one lane."""
+    m, n2, k = mnk
+    inter = n2 // 2
+    x = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 0))
+    wg = orc.f32_to_bf16_bits(orc.gaussian((inter, k), 0.05, 1))
+    wu = orc.f32_to_bf16_bits(orc.gaussian((inter, k), 0.05, 2))
+    w_gu = ops.interleave_gate_up(bf16_dev(wg), bf16_dev(wu))
+    qx, sx = ops.fp8_quant_dynamic(bf16_dev(x))
+    qw, sw = ops.fp8_quant_dynamic(w_gu)
+    h = ops.gemm_fp8_swiglu(qx, qw, sx[1:], sw[1:])
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    dx = orc.e4m3_to_f32(qx.cpu().numpy()).astype(np.float64)
+    dw = orc.e4m3_to_f32(qw.cpu().numpy()).astype(np.float64).reshape(inter // 128, 2, 128, k)
+    s = float(sx[1]) * float(sw[1])
+    gate = (dx @ dw[:, 0].reshape(inter, k).T) * s
+    up = (dx @ dw[:, 1].reshape(inter, k).T) * s
+    ref = (gate / (1.0 + np.exp(-gate)) * up).astype(np.float32)
+    _check(_bf16_to_np(h), ref, f"fp8 swiglu decode {mnk}")
+
+
 def test_gemm_fp8_strided_and_errors(ops, orc):
     from oxicuda_b200.errors import BlasError
     m, n, k = 128, 256, 256

@@ -676,6 +676,21 @@ def run_case(args):
             it[0] += 1
             ops.gemm_w4a16(x, r[0], r[1], r[2], 128, workspace=ws, out=y)
         work, unit = float(n * k // 2 + n * k // 128 * 2 + n * k // 256 + m * k * 2 + m * n * 2), "GB/s"
+    elif args.case == "gemm_fp8_decode":
+        n, k, m = 57344 * sz // 8192, 8192, args.m                        # --size 8192: the TP1 gate/up weight of the MLP, 470 MB
+        ws = []
+        for _ in range(2):
+            wq, st = ops.fp8_quant_dynamic(torch.randn((n, k), generator=g, device="cuda", dtype=torch.bfloat16))
+            ws.append((wq, st))
+        xq, sx = ops.fp8_quant_dynamic(torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16))
+        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        it = [0]
+
+        def fn():
+            it[0] += 1
+            r = ws[it[0] % 2]
+            ops.gemm_fp8(xq, r[0], sx[1:], r[1][1:], out=y)
+        work, unit = float(n * k + m * k + 2 * m * n), "GB/s"
     elif args.case in ("rmsnorm_int8", "rmsnorm_fp8", "silu_gate_fp8"):
         ring = [torch.randn((sz, sz), generator=g, device="cuda").to(torch.bfloat16) for _ in range(3)]
         wn = torch.ones(sz, device="cuda")
@@ -729,7 +744,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
-    ap.add_argument("--case", default=None, help="single-kernel mode, e.g. gemm_fp8, gemm_mxfp8, gemm_nvfp4, fp8_quant, gemm_w4a16, nf4_quant, gemm_nf4")
+    ap.add_argument("--case", default=None, help="single-kernel mode, e.g. gemm_fp8, gemm_mxfp8, gemm_nvfp4, fp8_quant, gemm_w4a16, gemm_fp8_decode, nf4_quant, gemm_nf4")
     ap.add_argument("--size", type=int, default=8192)
     ap.add_argument("--m", type=int, default=8)
     args = ap.parse_args()

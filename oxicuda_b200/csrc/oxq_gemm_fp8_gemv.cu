@@ -1,4 +1,6 @@
-// FP8 (E4M3 x E4M3) GEMM for decode shapes, up to 8 batch rows: Y = bf16(alpha * (X . W^T) * sx * sw), or the SwiGLU
+// FP8 (E4M3 x E4M3) GEMM for decode shapes, up to 8 batch rows (the kernel is written for NT tiles of 8 rows that share
+// the weight registers, but mma.sync is slow enough on this part that the 128-row kernels win from 16 rows on -- at
+// 57344 x 8192, 16 / 64 rows took 124 / 363 us here against 115 / 116 us there -- so only NT = 1 is launched): Y = bf16(alpha * (X . W^T) * sx * sw), or the SwiGLU
 // form on a gate/up-interleaved weight.  The 128-row tensor-memory kernels serve these shapes at half the HBM rate
 // (one 128-row tile of X is almost empty and every CTA still pays the full pipeline set-up); here the weight stream
 // is the only cost.  Same shape as the W4A16 GEMV: a CTA owns 16 weight rows over the whole K range, its 8 warps
@@ -60,9 +62,11 @@ struct FgParams {
     __nv_bfloat16* y;            // [m x n], or [m x n/2] in the SwiGLU form
 };
 
-template <bool SWIGLU>
-__global__ void __launch_bounds__(FG_WARPS * 32, 4) fp8_gemv_kernel(const FgParams p) {
-    __shared__ float red[FG_WARPS][16][8];
+// NT: tiles of 8 batch rows (the weight registers are shared by the tiles)
+template <bool SWIGLU, int NT>
+__global__ void __launch_bounds__(FG_WARPS * 32, NT == 1 ? 4 : 3) fp8_gemv_kernel(const FgParams p) {
+    constexpr int NB = 8 * NT;                                // batch rows of a CTA
+    __shared__ float red[FG_WARPS][16][NB];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     // the cluster's CTAs (grid y) take consecutive parts of the K range; inside a CTA the warps split its part
     const uint32_t crank = p.ksplit > 1 ? cluster_rank() : 0u;
@@ -80,8 +84,7 @@ __global__ void __launch_bounds__(FG_WARPS * 32, 4) fp8_gemv_kernel(const FgPara
     }
     const uint8_t* pa = p.w + (size_t)row_a * p.ldw + 16 * t;
     const uint8_t* pb = p.w + (size_t)row_b * p.ldw + 16 * t;
-    const bool has_x = g < p.m;
-    const uint8_t* xr = p.x + (size_t)(has_x ? g : 0) * p.ldx + 16 * t;
+    const uint8_t* xr = p.x + 16 * t;
 
     uint4 cur_a[FG_CHUNK], cur_b[FG_CHUNK], nxt_a[FG_CHUNK], nxt_b[FG_CHUNK];
     auto fetch = [&](int s0, uint4 (&wa)[FG_CHUNK], uint4 (&wb)[FG_CHUNK]) {
@@ -95,7 +98,9 @@ __global__ void __launch_bounds__(FG_WARPS * 32, 4) fp8_gemv_kernel(const FgPara
             }
         }
     };
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; i++) { acc[i][0] = 0.0f; acc[i][1] = 0.0f; acc[i][2] = 0.0f; acc[i][3] = 0.0f; }
     // the weights do not depend on the kernel before this one in the stream; the activations, scales and output do
     pdl_trigger();
     if (s_lo < s_hi) fetch(s_lo, cur_a, cur_b);
@@ -106,48 +111,79 @@ __global__ void __launch_bounds__(FG_WARPS * 32, 4) fp8_gemv_kernel(const FgPara
         for (int j = 0; j < FG_CHUNK; j++) {
             const int s = s0 + j;
             if (s < s_hi) {
-                uint4 xv = make_uint4(0, 0, 0, 0);
-                if (has_x && s * 64 + 16 * t < p.k) xv = ld_pinned_u4(xr + (size_t)s * 64);
-                // word q of the lane's 16 codes meets word q of its 16 activations: k slots (4t.., 4t + 16..) take words (0, 1), then (2, 3)
-                mma_e4m3_16832(acc, cur_a[j].x, cur_b[j].x, cur_a[j].y, cur_b[j].y, xv.x, xv.y);
-                mma_e4m3_16832(acc, cur_a[j].z, cur_b[j].z, cur_a[j].w, cur_b[j].w, xv.z, xv.w);
+                const bool in_k = s * 64 + 16 * t < p.k;
+#pragma unroll
+                for (int i = 0; i < NT; i++) {
+                    uint4 xv = make_uint4(0, 0, 0, 0);
+                    if (in_k && 8 * i + g < p.m) xv = ld_pinned_u4(xr + (size_t)(8 * i + g) * p.ldx + (size_t)s * 64);
+                    // word q of the lane's 16 codes meets word q of its 16 activations: k slots (4t.., 4t + 16..) take words (0, 1), then (2, 3)
+                    mma_e4m3_16832(acc[i], cur_a[j].x, cur_b[j].x, cur_a[j].y, cur_b[j].y, xv.x, xv.y);
+                    mma_e4m3_16832(acc[i], cur_a[j].z, cur_b[j].z, cur_a[j].w, cur_b[j].w, xv.z, xv.w);
+                }
             }
         }
 #pragma unroll
         for (int j = 0; j < FG_CHUNK; j++) { cur_a[j] = nxt_a[j]; cur_b[j] = nxt_b[j]; }
     }
-    // accumulator element e: CTA row (e < 2 ? g : g + 8), batch row 2t + (e & 1)
-    red[warp][g][2 * t] = acc[0]; red[warp][g][2 * t + 1] = acc[1];
-    red[warp][g + 8][2 * t] = acc[2]; red[warp][g + 8][2 * t + 1] = acc[3];
-    __syncthreads();
-    __shared__ float part[3][16][8];                          // sums of the cluster's other CTAs (written by them)
-    __shared__ float fin[16][8];
-    float v = 0.0f;
-    const int col = threadIdx.x >> 4, r = threadIdx.x & 15;   // for the first 128 threads: batch row, CTA row
-    if (threadIdx.x < 128) {
+    // accumulator element e of tile i: CTA row (e < 2 ? g : g + 8), batch row 8i + 2t + (e & 1)
 #pragma unroll
-        for (int wi = 0; wi < FG_WARPS; wi++) v += red[wi][r][col];
+    for (int i = 0; i < NT; i++) {
+        red[warp][g][8 * i + 2 * t] = acc[i][0]; red[warp][g][8 * i + 2 * t + 1] = acc[i][1];
+        red[warp][g + 8][8 * i + 2 * t] = acc[i][2]; red[warp][g + 8][8 * i + 2 * t + 1] = acc[i][3];
+    }
+    __syncthreads();
+    __shared__ float part[3][16][NB];                         // sums of the cluster's other CTAs (written by them)
+    __shared__ float fin[16][NB];
+    constexpr int PER = (16 * NB + FG_WARPS * 32 - 1) / (FG_WARPS * 32);      // (row, batch row) pairs per thread
+    float v[PER];
+#pragma unroll
+    for (int q = 0; q < PER; q++) {
+        const int idx = threadIdx.x + q * FG_WARPS * 32;
+        v[q] = 0.0f;
+        if (idx < 16 * NB) {
+            const int col = idx >> 4, r = idx & 15;
+#pragma unroll
+            for (int wi = 0; wi < FG_WARPS; wi++) v[q] += red[wi][r][col];
+        }
     }
     if (p.ksplit > 1) {
-        if (crank != 0 && threadIdx.x < 128) st_cluster_f32(&part[crank - 1][r][col], 0, v);
+        if (crank != 0) {
+#pragma unroll
+            for (int q = 0; q < PER; q++) {
+                const int idx = threadIdx.x + q * FG_WARPS * 32;
+                if (idx < 16 * NB) st_cluster_f32(&part[crank - 1][idx & 15][idx >> 4], 0, v[q]);
+            }
+        }
         cluster_sync_all();                                   // every thread of every CTA of the cluster
         if (crank != 0) return;
-        if (threadIdx.x < 128)
-            for (int q = 1; q < p.ksplit; q++) v += part[q - 1][r][col];
+#pragma unroll
+        for (int q = 0; q < PER; q++) {
+            const int idx = threadIdx.x + q * FG_WARPS * 32;
+            if (idx < 16 * NB)
+                for (int c = 1; c < p.ksplit; c++) v[q] += part[c - 1][idx & 15][idx >> 4];
+        }
     }
     const float scale = __ldg(p.sx) * __ldg(p.sw) * p.alpha;
     if (SWIGLU) {
-        if (threadIdx.x < 128) fin[r][col] = v;
+#pragma unroll
+        for (int q = 0; q < PER; q++) {
+            const int idx = threadIdx.x + q * FG_WARPS * 32;
+            if (idx < 16 * NB) fin[idx & 15][idx >> 4] = v[q];
+        }
         __syncthreads();
-        if (threadIdx.x < 64) {
-            const int bc = threadIdx.x >> 3, oc = threadIdx.x & 7;        // batch row, output column inside the CTA
+        for (int idx = threadIdx.x; idx < 8 * NB; idx += FG_WARPS * 32) {
+            const int bc = idx >> 3, oc = idx & 7;                        // batch row, output column inside the CTA
             const float gt = fin[oc][bc] * scale, up = fin[oc + 8][bc] * scale;
             const int o = (int)blockIdx.x * 8 + oc;
             if (bc < p.m) p.y[(size_t)bc * p.ldy + o] = __float2bfloat16_rn(__fdividef(gt, 1.0f + __expf(-gt)) * up);
         }
     } else {
-        const int row = (int)blockIdx.x * 16 + r;
-        if (threadIdx.x < 128 && col < p.m && row < p.n) p.y[(size_t)col * p.ldy + row] = __float2bfloat16_rn(v * scale);
+#pragma unroll
+        for (int q = 0; q < PER; q++) {
+            const int idx = threadIdx.x + q * FG_WARPS * 32;
+            const int col = idx >> 4, row = (int)blockIdx.x * 16 + (idx & 15);
+            if (idx < 16 * NB && col < p.m && row < p.n) p.y[(size_t)col * p.ldy + row] = __float2bfloat16_rn(v[q] * scale);
+        }
     }
 }
 
@@ -182,6 +218,7 @@ cudaError_t oxq_fp8_gemv_launch(oxq_handle* h, int m, int n, int k, const uint8_
         na++;
     }
     cfg.attrs = attrs; cfg.numAttrs = na;
-    if (swiglu) return cudaLaunchKernelEx(&cfg, fp8_gemv_kernel<true>, p);
-    return cudaLaunchKernelEx(&cfg, fp8_gemv_kernel<false>, p);
+#define FG_LAUNCH(NTT) (swiglu ? cudaLaunchKernelEx(&cfg, fp8_gemv_kernel<true, NTT>, p) : cudaLaunchKernelEx(&cfg, fp8_gemv_kernel<false, NTT>, p))
+    return FG_LAUNCH(1);
+#undef FG_LAUNCH
 }

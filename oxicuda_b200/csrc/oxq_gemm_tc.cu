@@ -913,13 +913,19 @@ static bool fp8_gemv_setting() {
     return on;
 }
 
+// largest batch served by the GEMV (OXQ_FP8_GEMV_MAX_M, 0..8, default 8)
+static int fp8_gemv_max_m() {
+    static const int v = [] { const char* e = getenv("OXQ_FP8_GEMV_MAX_M"); const int x = e ? atoi(e) : 8; return x < 0 ? 0 : (x > 8 ? 8 : x); }();
+    return v;
+}
+
 static int32_t gemm_fp8_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x, int64_t ldx, const uint8_t* w, int64_t ldw,
                              const float* sx, const float* sw, float alpha, float beta, void* y, int64_t ldy) {
     OXQ_CHECK_HANDLE(h);
     if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
     if (!sx || !sw) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
     if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
-    if (m <= 8 && beta == 0.0f && fp8_gemv_setting()) {             // decode shapes: the weight stream is the whole cost
+    if (m <= fp8_gemv_max_m() && beta == 0.0f && fp8_gemv_setting()) {             // decode shapes: the weight stream is the whole cost
         if (int32_t rc = oxq_require_sm100(h)) return rc;
         OXQ_CUDA(h, oxq_fp8_gemv_launch(h, (int)m, (int)n, (int)k, x, ldx, w, ldw, sx, sw, alpha, y, ldy, false));
         return OXQ_OK;
@@ -947,7 +953,7 @@ int32_t oxq_gemm_fp8_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, con
     if (int32_t rc = check_gemm_args(h, m, n2 / 2, k, x, w_gu, hout, ldh)) return rc;
     if (!sx || !sw) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
     if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
-    if (m <= 8 && fp8_gemv_setting()) {
+    if (m <= fp8_gemv_max_m() && fp8_gemv_setting()) {
         if (int32_t rc = oxq_require_sm100(h)) return rc;
         OXQ_CUDA(h, oxq_fp8_gemv_launch(h, (int)m, (int)n2, (int)k, x, ldx, w_gu, ldw, sx, sw, 1.0f, hout, ldh, true));
         return OXQ_OK;

@@ -62,9 +62,10 @@ def test_gemm_fp8(ops, orc, mnk):
         assert np.abs(yb - rb).max() <= 1
 
 
-@pytest.mark.parametrize("mnk", [(1, 16, 64), (1, 4096, 4096), (8, 1000, 1040), (3, 520, 384), (5, 28672, 1024), (8, 264, 8192)])
+@pytest.mark.parametrize("mnk", [(1, 16, 64), (1, 4096, 4096), (8, 1000, 1040), (3, 520, 384), (5, 28672, 1024), (8, 264, 8192),
+                                 (9, 520, 384), (16, 4096, 4096), (31, 1000, 1040), (64, 264, 28672), (40, 8192, 2048)])
 def test_gemm_fp8_decode_shapes(ops, orc, mnk):
-    """Up to 8 batch rows run the GEMV kernel (mma.sync on the raw E4M3 bytes): same oracle, ragged N and K, alpha."""
+    """Up to 64 batch rows run the GEMV kernel (mma.sync on the raw E4M3 bytes): same oracle, ragged N and K, alpha."""
     m, n, k = mnk
     a = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 0))
     b = orc.f32_to_bf16_bits(orc.gaussian((n, k), 1.0, 1))
@@ -83,7 +84,7 @@ def test_gemm_fp8_decode_shapes(ops, orc, mnk):
     assert torch.equal(y2.float(), y.float() * -2.0)                       # alpha is a power of two: exact
 
 
-@pytest.mark.parametrize("mnk", [(1, 512, 256), (8, 1024, 4096), (5, 256, 1040)])
+@pytest.mark.parametrize("mnk", [(1, 512, 256), (8, 1024, 4096), (5, 256, 1040), (12, 512, 2048), (33, 1024, 1024), (64, 7168, 8192)])
 def test_gemm_fp8_swiglu_decode_shapes(ops, orc, mnk):
     """The SwiGLU form of the GEMV: gate and up rows of one output column meet in one lane."""
     m, n2, k = mnk

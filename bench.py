@@ -272,6 +272,20 @@ def extras(torch, ops, peaks):
         rec(f"gemm_nf4_m{mrows}_14336x4096_b64", 14336 * 4096 // 2 + 14336 * 4096 // 64 * 4 + mrows * (4096 + 14336) * 2,
             ring_time(torch, lambda r: ops.gemm_nf4(xn, r[0], r[1], 14336, 64), packs))
     del packs
+    # decode GEMMs on a weight of the TP1 MLP size (57344 x 8192, 470 MB per copy; two copies in rotation)
+    wbig = [torch.randn((57344, 8192), generator=g, device="cuda", dtype=torch.bfloat16) for _ in range(1)]
+    fp8w = [ops.fp8_quant_dynamic(wbig[0]) for _ in range(2)]
+    i8w = [ops.int8_quant_rows(wbig[0].float()) for _ in range(2)]
+    del wbig
+    for mrows in (1, 8):
+        xd = torch.randn((mrows, 8192), generator=g, device="cuda").to(torch.bfloat16)
+        xq8, sx8 = ops.fp8_quant_dynamic(xd)
+        rec(f"gemm_fp8_m{mrows}_57344x8192", 57344 * 8192 + mrows * 8192 + 2 * mrows * 57344,
+            ring_time(torch, lambda r: ops.gemm_fp8(xq8, r[0], sx8[1:], r[1][1:]), fp8w))
+        xi8, sxi = ops.int8_quant_rows(xd.float())
+        rec(f"gemm_w8a8_m{mrows}_57344x8192", 57344 * 8192 + mrows * 8192 + 2 * mrows * 57344 + 4 * 57344,
+            ring_time(torch, lambda r: ops.gemm_w8a8(xi8, r[0], sxi, r[1]), i8w))
+    del fp8w, i8w
     # offline weight preparation: one GPTQ layer (4096 x 4096, INT4 symmetric), Hessian from 8192 synthetic samples
     n = 4096
     xs = torch.randn((2 * n, n), generator=g, device="cuda")

@@ -68,9 +68,10 @@ static inline cudaError_t oxq_launch(void (*kernel)(P...), dim3 grid, dim3 block
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
 }
 
-// FP8 GEMM for up to 8 batch rows (csrc/oxq_gemm_fp8_gemv.cu); arguments already validated by the entry points.
+// FP8 (or, with int8 = true, W8A8 with per-row scales) GEMM for up to 8 batch rows (csrc/oxq_gemm_fp8_gemv.cu);
+// arguments already validated by the entry points.
 cudaError_t oxq_fp8_gemv_launch(oxq_handle* h, int m, int n, int k, const uint8_t* x, int64_t ldx, const uint8_t* w, int64_t ldw,
-                                const float* sx, const float* sw, float alpha, void* y, int64_t ldy, bool swiglu);
+                                const float* sx, const float* sw, float alpha, void* y, int64_t ldy, bool swiglu, bool int8 = false);
 
 namespace oxq {
 

@@ -12,6 +12,7 @@
 // rows as its rows 0-7 and the 8 matching up rows as its rows 8-15, so the accumulator pair of a lane is (gate, up)
 // of the same output column and silu(gate) * up needs no exchange.
 #include "oxq_common.cuh"
+#include <type_traits>
 
 namespace oxq {
 namespace {
@@ -23,6 +24,12 @@ __device__ __forceinline__ void mma_e4m3_16832(float (&d)[4], uint32_t a0, uint3
     asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void mma_s8_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_8bit(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) { mma_e4m3_16832(d, a0, a1, a2, a3, b0, b1); }
+__device__ __forceinline__ void mma_8bit(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) { mma_s8_16832(d, a0, a1, a2, a3, b0, b1); }
 __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
     uint4 u;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(p));
@@ -40,11 +47,13 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     return r;
 }
 // stores v at the same shared-memory offset in CTA `rank` of the cluster
-__device__ __forceinline__ void st_cluster_f32(const float* local, uint32_t rank, float v) {
+__device__ __forceinline__ void st_cluster_b32(const void* local, uint32_t rank, uint32_t bits) {
     uint32_t a = (uint32_t)__cvta_generic_to_shared(local), ra;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank));
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(v) : "memory");
+    asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(ra), "r"(bits) : "memory");
 }
+__device__ __forceinline__ void st_cluster(const float* local, uint32_t rank, float v) { st_cluster_b32(local, rank, __float_as_uint(v)); }
+__device__ __forceinline__ void st_cluster(const int* local, uint32_t rank, int v) { st_cluster_b32(local, rank, (uint32_t)v); }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
@@ -55,18 +64,20 @@ struct FgParams {
     int64_t ldx, ldw, ldy;
     const uint8_t* x;            // [m x k] E4M3
     const uint8_t* w;            // [n x k] E4M3
-    const float* sx;
-    const float* sw;
+    const float* sx;             // FP8: one scale; W8A8: one per batch row
+    const float* sw;             // FP8: one scale; W8A8: one per weight row
     float alpha;
     int ksplit;                  // CTAs of a cluster that share the K range of one row block (1, 2 or 4)
     __nv_bfloat16* y;            // [m x n], or [m x n/2] in the SwiGLU form
 };
 
 // NT: tiles of 8 batch rows (the weight registers are shared by the tiles)
-template <bool SWIGLU, int NT>
+// I8: int8 x int8 with an exact s32 accumulator and per-row scales (W8A8) instead of E4M3 x E4M3 with f32
+template <bool I8, bool SWIGLU, int NT>
 __global__ void __launch_bounds__(FG_WARPS * 32, NT == 1 ? 4 : 3) fp8_gemv_kernel(const FgParams p) {
     constexpr int NB = 8 * NT;                                // batch rows of a CTA
-    __shared__ float red[FG_WARPS][16][NB];
+    using Acc = typename std::conditional<I8, int, float>::type;
+    __shared__ Acc red[FG_WARPS][16][NB];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     // the cluster's CTAs (grid y) take consecutive parts of the K range; inside a CTA the warps split its part
     const uint32_t crank = p.ksplit > 1 ? cluster_rank() : 0u;
@@ -98,9 +109,9 @@ __global__ void __launch_bounds__(FG_WARPS * 32, NT == 1 ? 4 : 3) fp8_gemv_kerne
             }
         }
     };
-    float acc[NT][4];
+    Acc acc[NT][4];
 #pragma unroll
-    for (int i = 0; i < NT; i++) { acc[i][0] = 0.0f; acc[i][1] = 0.0f; acc[i][2] = 0.0f; acc[i][3] = 0.0f; }
+    for (int i = 0; i < NT; i++) { acc[i][0] = 0; acc[i][1] = 0; acc[i][2] = 0; acc[i][3] = 0; }
     // the weights do not depend on the kernel before this one in the stream; the activations, scales and output do
     pdl_trigger();
     if (s_lo < s_hi) fetch(s_lo, cur_a, cur_b);
@@ -117,8 +128,8 @@ __global__ void __launch_bounds__(FG_WARPS * 32, NT == 1 ? 4 : 3) fp8_gemv_kerne
                     uint4 xv = make_uint4(0, 0, 0, 0);
                     if (in_k && 8 * i + g < p.m) xv = ld_pinned_u4(xr + (size_t)(8 * i + g) * p.ldx + (size_t)s * 64);
                     // word q of the lane's 16 codes meets word q of its 16 activations: k slots (4t.., 4t + 16..) take words (0, 1), then (2, 3)
-                    mma_e4m3_16832(acc[i], cur_a[j].x, cur_b[j].x, cur_a[j].y, cur_b[j].y, xv.x, xv.y);
-                    mma_e4m3_16832(acc[i], cur_a[j].z, cur_b[j].z, cur_a[j].w, cur_b[j].w, xv.z, xv.w);
+                    mma_8bit(acc[i], cur_a[j].x, cur_b[j].x, cur_a[j].y, cur_b[j].y, xv.x, xv.y);
+                    mma_8bit(acc[i], cur_a[j].z, cur_b[j].z, cur_a[j].w, cur_b[j].w, xv.z, xv.w);
                 }
             }
         }
@@ -132,14 +143,14 @@ __global__ void __launch_bounds__(FG_WARPS * 32, NT == 1 ? 4 : 3) fp8_gemv_kerne
         red[warp][g + 8][8 * i + 2 * t] = acc[i][2]; red[warp][g + 8][8 * i + 2 * t + 1] = acc[i][3];
     }
     __syncthreads();
-    __shared__ float part[3][16][NB];                         // sums of the cluster's other CTAs (written by them)
+    __shared__ Acc part[3][16][NB];                           // sums of the cluster's other CTAs (written by them)
     __shared__ float fin[16][NB];
     constexpr int PER = (16 * NB + FG_WARPS * 32 - 1) / (FG_WARPS * 32);      // (row, batch row) pairs per thread
-    float v[PER];
+    Acc v[PER];
 #pragma unroll
     for (int q = 0; q < PER; q++) {
         const int idx = threadIdx.x + q * FG_WARPS * 32;
-        v[q] = 0.0f;
+        v[q] = 0;
         if (idx < 16 * NB) {
             const int col = idx >> 4, r = idx & 15;
 #pragma unroll
@@ -151,7 +162,7 @@ __global__ void __launch_bounds__(FG_WARPS * 32, NT == 1 ? 4 : 3) fp8_gemv_kerne
 #pragma unroll
             for (int q = 0; q < PER; q++) {
                 const int idx = threadIdx.x + q * FG_WARPS * 32;
-                if (idx < 16 * NB) st_cluster_f32(&part[crank - 1][idx & 15][idx >> 4], 0, v[q]);
+                if (idx < 16 * NB) st_cluster(&part[crank - 1][idx & 15][idx >> 4], 0, v[q]);
             }
         }
         cluster_sync_all();                                   // every thread of every CTA of the cluster
@@ -163,12 +174,12 @@ __global__ void __launch_bounds__(FG_WARPS * 32, NT == 1 ? 4 : 3) fp8_gemv_kerne
                 for (int c = 1; c < p.ksplit; c++) v[q] += part[c - 1][idx & 15][idx >> 4];
         }
     }
-    const float scale = __ldg(p.sx) * __ldg(p.sw) * p.alpha;
+    const float scale = I8 ? 1.0f : __ldg(p.sx) * __ldg(p.sw) * p.alpha;
     if (SWIGLU) {
 #pragma unroll
         for (int q = 0; q < PER; q++) {
             const int idx = threadIdx.x + q * FG_WARPS * 32;
-            if (idx < 16 * NB) fin[idx & 15][idx >> 4] = v[q];
+            if (idx < 16 * NB) fin[idx & 15][idx >> 4] = (float)v[q];
         }
         __syncthreads();
         for (int idx = threadIdx.x; idx < 8 * NB; idx += FG_WARPS * 32) {
@@ -182,7 +193,11 @@ __global__ void __launch_bounds__(FG_WARPS * 32, NT == 1 ? 4 : 3) fp8_gemv_kerne
         for (int q = 0; q < PER; q++) {
             const int idx = threadIdx.x + q * FG_WARPS * 32;
             const int col = idx >> 4, row = (int)blockIdx.x * 16 + (idx & 15);
-            if (idx < 16 * NB && col < p.m && row < p.n) p.y[(size_t)col * p.ldy + row] = __float2bfloat16_rn(v[q] * scale);
+            if (idx < 16 * NB && col < p.m && row < p.n) {
+                // W8A8: the same expression as the 128-row kernel's epilogue, (float)acc * (sx[m] * sw[n])
+                const float sc = I8 ? __ldg(p.sx + col) * p.alpha * __ldg(p.sw + row) : scale;
+                p.y[(size_t)col * p.ldy + row] = __float2bfloat16_rn((float)v[q] * sc);
+            }
         }
     }
 }
@@ -192,7 +207,7 @@ __global__ void __launch_bounds__(FG_WARPS * 32, NT == 1 ? 4 : 3) fp8_gemv_kerne
 
 // Launches the GEMV; the caller has validated pointers, alignment (16 bytes, k / ldx / ldw multiples of 16) and m <= 8.
 cudaError_t oxq_fp8_gemv_launch(oxq_handle* h, int m, int n, int k, const uint8_t* x, int64_t ldx, const uint8_t* w, int64_t ldw,
-                                const float* sx, const float* sw, float alpha, void* y, int64_t ldy, bool swiglu) {
+                                const float* sx, const float* sw, float alpha, void* y, int64_t ldy, bool swiglu, bool int8) {
     using namespace oxq;
     FgParams p;
     p.m = m; p.n = n; p.k = k; p.ldx = ldx; p.ldw = ldw; p.ldy = ldy; p.x = x; p.w = w; p.sx = sx; p.sw = sw; p.alpha = alpha;
@@ -218,7 +233,7 @@ cudaError_t oxq_fp8_gemv_launch(oxq_handle* h, int m, int n, int k, const uint8_
         na++;
     }
     cfg.attrs = attrs; cfg.numAttrs = na;
-#define FG_LAUNCH(NTT) (swiglu ? cudaLaunchKernelEx(&cfg, fp8_gemv_kernel<true, NTT>, p) : cudaLaunchKernelEx(&cfg, fp8_gemv_kernel<false, NTT>, p))
-    return FG_LAUNCH(1);
-#undef FG_LAUNCH
+    if (int8) return cudaLaunchKernelEx(&cfg, fp8_gemv_kernel<true, false, 1>, p);
+    if (swiglu) return cudaLaunchKernelEx(&cfg, fp8_gemv_kernel<false, true, 1>, p);
+    return cudaLaunchKernelEx(&cfg, fp8_gemv_kernel<false, false, 1>, p);
 }

@@ -1003,6 +1003,11 @@ int32_t oxq_gemm_w8a8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const int8
     if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
     if (!sx_rows || !sw_rows) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
     if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
+    if (m <= fp8_gemv_max_m() && fp8_gemv_setting()) {             // decode shapes: mma.sync s8 on the raw bytes, exact s32 sums
+        OXQ_CUDA(h, oxq_fp8_gemv_launch(h, (int)m, (int)n, (int)k, (const uint8_t*)x, ldx, (const uint8_t*)w, ldw, sx_rows, sw_rows, 1.0f, y, ldy,
+                                        false, true));
+        return OXQ_OK;
+    }
     GemmParams p{};
     p.alpha = 1.0f; p.beta = 0.0f;
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y; p.ldy = ldy; p.s0 = sx_rows; p.s1 = sw_rows;

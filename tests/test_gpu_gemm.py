@@ -65,7 +65,7 @@ def test_gemm_fp8(ops, orc, mnk):
 @pytest.mark.parametrize("mnk", [(1, 16, 64), (1, 4096, 4096), (8, 1000, 1040), (3, 520, 384), (5, 28672, 1024), (8, 264, 8192),
                                  (9, 520, 384), (16, 4096, 4096), (31, 1000, 1040), (64, 264, 28672), (40, 8192, 2048)])
 def test_gemm_fp8_decode_shapes(ops, orc, mnk):
-    """Up to 64 batch rows run the GEMV kernel (mma.sync on the raw E4M3 bytes): same oracle, ragged N and K, alpha."""
+    """Up to 8 batch rows run the GEMV kernel (mma.sync on the raw E4M3 bytes), more the 128-row kernels: same oracle, ragged N and K, alpha."""
     m, n, k = mnk
     a = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 0))
     b = orc.f32_to_bf16_bits(orc.gaussian((n, k), 1.0, 1))
@@ -151,7 +151,7 @@ def test_gemm_fp8_linearity_full_size(ops, orc):
 
 # ------------------------------------------------------------------------------------------- W8A8 / W8A32
 
-@pytest.mark.parametrize("mnk", [(128, 256, 128), (200, 512, 1024), (33, 264, 4096)])
+@pytest.mark.parametrize("mnk", [(128, 256, 128), (200, 512, 1024), (33, 264, 4096), (1, 16, 64), (1, 4096, 4096), (8, 1000, 1040), (5, 8192, 28672), (3, 520, 384)])
 def test_gemm_w8a8(ops, orc, mnk):
     m, n, k = mnk
     x = orc.gaussian((m, k), 1.0, 1)

@@ -81,10 +81,14 @@ def test_gemm_fp8_decode_shapes(ops, orc, mnk):
     s = np.float32(sa.cpu().numpy()[1]) * np.float32(sb.cpu().numpy()[1])
     ref = (da.astype(np.float64) @ db.astype(np.float64).T).astype(np.float32) * s
     _check(_bf16_to_np(y), ref, f"fp8 decode {mnk}")
+    # tighter than the GEMM bar: products are exact and sums are kept in f32, so only the bf16 rounding of the output is left
+    # (a single running FP8 mma.sync accumulator drifts by 0.7 % over K = 8192 and would fail this)
+    assert np.abs(_bf16_to_np(y) - ref).max() <= 4e-3 * np.abs(ref).max()
     assert torch.equal(y2.float(), y.float() * -2.0)                       # alpha is a power of two: exact
 
 
-@pytest.mark.parametrize("mnk", [(1, 512, 256), (8, 1024, 4096), (5, 256, 1040), (12, 512, 2048), (33, 1024, 1024), (64, 7168, 8192)])
+@pytest.mark.parametrize("mnk", [(1, 512, 256), (8, 1024, 4096), (5, 256, 1040), (12, 512, 2048), (33, 1024, 1024), (64, 7168, 8192),
+                                 (4, 512, 8192), (2, 256, 28672), (8, 7168, 8192)])   # the last three: K split over clusters of 2 / 4 CTAs
 def test_gemm_fp8_swiglu_decode_shapes(ops, orc, mnk):
     """The SwiGLU form of the GEMV: gate and up rows of one output column meet in one lane."""
     m, n2, k = mnk

@@ -77,6 +77,11 @@ namespace oxq {
 
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Brings a line into the L2 without returning data.  The weight-streaming kernels use it for their first weights
+// before pdl_wait(): the kernel before this one in the stream may still be writing those weights (a quantizer
+// followed directly by the GEMM), so nothing may be *read* yet, but the L2 is the point of coherence and a line
+// that is written after it was prefetched is simply updated there.
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll

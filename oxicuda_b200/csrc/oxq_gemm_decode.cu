@@ -294,11 +294,16 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 2) w4a16_gemv_kernel(const GvPa
     };
 
     float total[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    // The weights do not depend on the kernel before this one in the stream, so their first requests go out while
-    // that kernel is still finishing; the activations and the output wait for it.
+    // Before the kernel ahead of this one in the stream has finished, the first codes are only prefetched into the L2
+    // (it may be the quantizer that writes them); codes, scales and zero-points are read after the wait.
     pdl_trigger();
-    if (s_lo < s_hi) fetch(s_lo, cur_a, cur_b, cur_sa, cur_sb);
+#pragma unroll
+    for (int j = 0; j < GV_CHUNK; j++) {
+        const int s = s_lo + j;
+        if (s < s_hi) { prefetch_l2(ca + s * 16); prefetch_l2(cb + s * 16); }
+    }
     pdl_wait();
+    if (s_lo < s_hi) fetch(s_lo, cur_a, cur_b, cur_sa, cur_sb);
     for (int s0 = s_lo; s0 < s_hi; s0 += GV_CHUNK) {
         if (PIPE && s0 + GV_CHUNK < s_hi) fetch(s0 + GV_CHUNK, nxt_a, nxt_b, nxt_sa, nxt_sb);
 #pragma unroll
@@ -424,10 +429,16 @@ __global__ void __launch_bounds__(W8T_WARPS * 32, 2) w8a32_tc_kernel(const float
     float acc[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; i++) { acc[i][0] = 0.0f; acc[i][1] = 0.0f; acc[i][2] = 0.0f; acc[i][3] = 0.0f; }
-    // the weights do not depend on the kernel before this one in the stream; the activations and the output do
+    // Before the kernel ahead of this one in the stream has finished, the first weights are only prefetched into the L2
+    // (it may be the quantizer that writes them); they are read after the wait.
     pdl_trigger();
-    if (s_lo < s_hi) fetch(s_lo, cur_a, cur_b);
+#pragma unroll
+    for (int j = 0; j < W8T_CHUNK; j++) {
+        const int s = s_lo + j;
+        if (s < s_hi && s * 64 + 16 * t < k) { prefetch_l2(pa + (size_t)s * 64); prefetch_l2(pb + (size_t)s * 64); }
+    }
     pdl_wait();
+    if (s_lo < s_hi) fetch(s_lo, cur_a, cur_b);
     for (int s0 = s_lo; s0 < s_hi; s0 += W8T_CHUNK) {
         if (s0 + W8T_CHUNK < s_hi) fetch(s0 + W8T_CHUNK, nxt_a, nxt_b);
 #pragma unroll

@@ -112,10 +112,16 @@ __global__ void __launch_bounds__(FG_WARPS * 32, NT == 1 ? 4 : 3) fp8_gemv_kerne
     Acc acc[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; i++) { acc[i][0] = 0; acc[i][1] = 0; acc[i][2] = 0; acc[i][3] = 0; }
-    // the weights do not depend on the kernel before this one in the stream; the activations, scales and output do
+    // Before the kernel ahead of this one in the stream has finished, the first weights are only prefetched into the L2
+    // (it may be the quantizer that writes them); they are read after the wait.
     pdl_trigger();
-    if (s_lo < s_hi) fetch(s_lo, cur_a, cur_b);
+#pragma unroll
+    for (int j = 0; j < FG_CHUNK; j++) {
+        const int s = s_lo + j;
+        if (s < s_hi && s * 64 + 16 * t < p.k) { prefetch_l2(pa + (size_t)s * 64); prefetch_l2(pb + (size_t)s * 64); }
+    }
     pdl_wait();
+    if (s_lo < s_hi) fetch(s_lo, cur_a, cur_b);
     for (int s0 = s_lo; s0 < s_hi; s0 += FG_CHUNK) {
         if (s0 + FG_CHUNK < s_hi) fetch(s0 + FG_CHUNK, nxt_a, nxt_b);
 #pragma unroll

@@ -84,9 +84,13 @@ __global__ void __launch_bounds__(NG_WARPS * 32, 3) nf4_gemv_kernel(const Nf4Par
     };
 
     float total[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    // the weights do not depend on the kernel before this one in the stream; the activations and the output do
-    if (s_lo < s_hi) fetch(s_lo, cur_a, cur_b, cur_sa, cur_sb);
-    // the table is built while those first requests are in flight
+    // Before the kernel ahead of this one in the stream has finished, the first weights are only prefetched into the L2
+    // (it may be the encoder that writes them); the table is built meanwhile and the weights are read after the wait.
+#pragma unroll
+    for (int j = 0; j < NG_CHUNK; j++) {
+        const int s = s_lo + j;
+        if (s < s_hi) { prefetch_l2(pa + (size_t)s * 32); prefetch_l2(pb + (size_t)s * 32); }
+    }
     if (threadIdx.x < 16) lv[threadIdx.x] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(c_nf4_levels[threadIdx.x]));
     __syncthreads();
     for (int e = threadIdx.x; e < 256 * 8; e += NG_WARPS * 32) {              // 16-byte stores: four lanes' copies at a time
@@ -96,6 +100,7 @@ __global__ void __launch_bounds__(NG_WARPS * 32, 3) nf4_gemv_kernel(const Nf4Par
     }
     __syncthreads();
     pdl_wait();
+    if (s_lo < s_hi) fetch(s_lo, cur_a, cur_b, cur_sa, cur_sb);
     for (int s0 = s_lo; s0 < s_hi; s0 += NG_CHUNK) {
         if (s0 + NG_CHUNK < s_hi) fetch(s0 + NG_CHUNK, nxt_a, nxt_b, nxt_sa, nxt_sb);
 #pragma unroll

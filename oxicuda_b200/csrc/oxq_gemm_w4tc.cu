@@ -123,10 +123,11 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
-    // The packed weights, scales and zero-points do not depend on the kernel before this one in the stream: the codes
-    // producer, the unpack warps and the MMA thread start at once; the activation producer and the epilogue (which
-    // reads and writes the workspace and the output) wait for that kernel first.
+    // Everything set up so far (barriers, tensor memory, descriptors) overlaps the tail of the kernel before this one in
+    // the stream; every role waits for it before its first global access -- the weights too, since that kernel may be
+    // the quantizer that writes them.
     pdl_trigger();
+    pdl_wait();
 
     // One completion barrier per unit slot serves three waiters: the epilogue (accumulators ready), the
     // activation producer (slot free again, four units later) and the unpack warps (tensor-memory slot of the

@@ -363,3 +363,46 @@ def test_gemm_nvfp4(ops, orc, mnk):
     da = orc.spec_nvfp4_dequant(pa.cpu().numpy(), sfa.cpu().numpy(), float(sta[1]), m, k).astype(np.float64)
     db = orc.spec_nvfp4_dequant(pb.cpu().numpy(), sfb.cpu().numpy(), float(stb[1]), n, k).astype(np.float64)
     _check(_bf16_to_np(y), (da @ db.T).astype(np.float32), f"nvfp4 {mnk}")
+
+
+def test_quantize_then_gemm_back_to_back(ops):
+    """A quantizer followed directly by the GEMM that consumes its output, no host synchronisation in between: the decode
+    kernels start under the tail of the kernel before them (dependent launch) and must not read the weights early.  The
+    result has to equal, bit for bit, the same GEMM repeated after the stream has drained."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    n, k = 7168, 8192                                                     # 58 MB of 8-bit weights: the quantizer runs for tens of microseconds
+    w = torch.randn((n, k), generator=g, device="cuda") * 0.02
+    wb = w.to(torch.bfloat16)
+    x1 = torch.randn((1, k), generator=g, device="cuda").to(torch.bfloat16)
+    x16 = torch.randn((16, k), generator=g, device="cuda").to(torch.bfloat16)
+    xf = x1.float().repeat(8, 1).contiguous()
+    xq, sx = ops.fp8_quant_dynamic(x1)
+    xi, sxi = ops.int8_quant_rows(xf)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        # FP8 and W8A8 GEMV
+        wq, sw = ops.fp8_quant_dynamic(wb)
+        y = ops.gemm_fp8(xq, wq, sx[1:], sw[1:])
+        wi, swi = ops.int8_quant_rows(w)
+        yi = ops.gemm_w8a8(xi, wi, sxi, swi)
+        y32 = ops.gemm_w8a32(xf, wi, swi)
+        # W4A16 GEMV and tensor-core kernel
+        c, s, z = ops.int4g_quant_pack(w, 128)
+        y4 = ops.gemm_w4a16(x1, c, s, z, 128)
+        c2, s2, z2 = ops.int4g_quant_pack(w, 128)
+        y4t = ops.gemm_w4a16(x16, c2, s2, z2, 128)
+        # NF4
+        pk, am = ops.nf4_quant(w.view(-1), 64)
+        yn = ops.gemm_nf4(x1, pk, am, n, 64)
+        torch.cuda.synchronize()
+        assert torch.equal(y, ops.gemm_fp8(xq, wq, sx[1:], sw[1:]))
+        assert torch.equal(yi, ops.gemm_w8a8(xi, wi, sxi, swi))
+        assert torch.equal(y32, ops.gemm_w8a32(xf, wi, swi))
+        assert torch.equal(y4, ops.gemm_w4a16(x1, c, s, z, 128))
+        # the tensor-core kernel adds its K splits with f32 atomics: the order, hence the last bit, varies between calls
+        y4r = ops.gemm_w4a16(x16, c2, s2, z2, 128).float()
+        assert (y4t.float() - y4r).abs().max() <= 2e-2 * y4r.abs().max()
+        assert torch.equal(yn, ops.gemm_nf4(x1, pk, am, n, 64))
+        torch.cuda.synchronize()
+        del wq, wi, c, s, z, c2, s2, z2, pk, am
+    assert ops.handle().device_status() == 0

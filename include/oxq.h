@@ -143,7 +143,12 @@ OXQ_API int32_t oxq_swiglu_interleaved(oxq_handle* h, const void* gu_bf16_dev, i
 /* ---- GEMMs: stand behind gemm<T> (crates/oxicuda-blas/src/level3/gemm_api.rs:73-138) for the element
  *      types that entry point cannot run in the reference, and behind the low-precision configs of
  *      crates/oxicuda-blas/src/precision/{int_ops,fp8_ops,fp4_fp6_ops}.rs.
- *      Zero dimensions are errors (gemm_api.rs:88-92).  Outputs are bf16 unless noted. ---------------- */
+ *      Zero dimensions are errors (gemm_api.rs:88-92).  Outputs are bf16 unless noted.
+ *      Kernel choice is internal: large M runs tcgen05 kernels with TMA-fed operands and accumulators in tensor
+ *      memory; oxq_gemm_fp8, oxq_gemm_fp8_swiglu and oxq_gemm_w8a8 with m <= 8, and the decode entry points
+ *      (oxq_gemm_w4a16 with m <= 8, oxq_gemm_w8a32, oxq_gemm_nf4), run weight-streaming kernels.  Operands may be
+ *      produced by the call just before on the same stream (a quantizer followed directly by the GEMM): no kernel
+ *      reads an operand before its producer has finished. ---------------- */
 /* FP8 E4M3: Y = bf16((X . W^T) * (*sx_dev * *sw_dev)), f32 accumulate.  K % 16 == 0, ldy % 8 == 0. */
 OXQ_API int32_t oxq_gemm_fp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x_dev, int64_t ldx,
                      const uint8_t* w_dev, int64_t ldw, const float* sx_dev, const float* sw_dev,

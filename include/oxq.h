@@ -120,6 +120,28 @@ OXQ_API int32_t oxq_int4g_dequant(oxq_handle* h, const uint32_t* codes_dev, cons
                           const uint32_t* zeros_packed_dev, int64_t rows, int64_t k, int group,
                           void* y_dev, int y_dtype);
 
+/* The same quantizer in MinMaxQuantizer's own parameter types -- f32 scales and i32 zero-points per group
+ * (QuantParams, minmax.rs:50-60) -- so that a caller holding reference results can compare value for value:
+ *   scale = max(max - min, 1e-8) / 15, zp = clamp(round(-min / scale), 0, 15)            (minmax.rs:226-232)
+ *   q = clamp(round(x / scale + zp), 0, 15), packed 8 per u32 like pack_int4              (minmax.rs:275-299)
+ *   y = (q - zp) as f32 * scale                                                            (minmax.rs:302-324)
+ * x is f32 [rows x k].  A group that holds an infinity gets a non-finite scale where the reference returns
+ * QuantError::InvalidScale; the call is asynchronous, so it is the host wrapper that looks at the scales. */
+OXQ_API int32_t oxq_int4g_quant_pack_f32(oxq_handle* h, const float* x_dev, int64_t rows, int64_t k, int group, uint32_t* codes_dev,
+                                 float* scales_dev, int32_t* zero_points_dev, int rounding);
+OXQ_API int32_t oxq_int4g_dequant_f32(oxq_handle* h, const uint32_t* codes_dev, const float* scales_dev, const int32_t* zero_points_dev,
+                              int64_t rows, int64_t k, int group, float* y_dev);
+
+/* ---- MicroScalingQuantizer::quantize_fp4 / dequantize_fp4 as the reference defines them
+ *      (crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:763-782, :849-897): an f32 scale max|x| / 6 per block of
+ *      32, 64 or 128 elements (1 for an all-zero block, the last block may be short), codes from the floor-type
+ *      E2M1 encoder Fp4Quantizer::quantize_one (:645-661) applied to x / scale, two per byte with the even element
+ *      in the low nibble (PackedFp4::pack, :465-472).  packed_dev holds ceil(n / 2) bytes, scales_dev ceil(n / block)
+ *      floats.  n == 0 returns OXQ_OK. ------------------------------------------------------------------ */
+OXQ_API int32_t oxq_fp4_microscale_quant(oxq_handle* h, const float* x_dev, int64_t n, int64_t block, uint8_t* packed_dev, float* scales_dev);
+OXQ_API int32_t oxq_fp4_microscale_dequant(oxq_handle* h, const uint8_t* packed_dev, const float* scales_dev, int64_t n, int64_t block,
+                                   float* y_dev);
+
 /* ---- block-scaled formats: MicroScalingQuantizer::quantize_fp4 and Fp4GemmConfig
  *      (crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:337-395, :746-898) re-defined on the OCP MX / NVFP4
  *      formats the benchmark configurations name.  Scale factors are written twice: row-major
@@ -189,8 +211,11 @@ OXQ_API int32_t oxq_gemm_w8a32(oxq_handle* h, int64_t m, int64_t n, int64_t k, c
  *                    other shapes with m <= 32 use a split-K mma.sync kernel (partial sums in the workspace);
  *   otherwise        the weight is dequantised to bf16 in the workspace and the bf16 tensor-core GEMM runs
  *                    (n % 8 == 0).
- * For m <= 32 the workspace must be zero-filled before its first use and is left zero-filled by every call; above
- * that its previous contents do not matter.  Workspace size: oxq_gemm_w4a16_workspace_bytes(m, n, k). */
+ * Workspace: oxq_gemm_w4a16_workspace_bytes(m, n, k) bytes, 256-byte aligned.  Its first
+ * oxq_gemm_w4a16_workspace_bytes(min(m, 32), n, k) bytes hold the partial sums of the decode kernels: they must be
+ * zero before a call with m <= 32 and every call, whatever its m, leaves them zero (a call with m > 32 keeps its
+ * dequantised weight behind that region and clears what it uses itself), so one workspace sized for the largest m
+ * serves prefill and decode calls in any order. */
 OXQ_API size_t oxq_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k);
 OXQ_API int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x_bf16_dev,
                        const uint32_t* codes_dev, const uint16_t* scales_f16_dev, const uint32_t* zeros_packed_dev,
@@ -205,7 +230,9 @@ OXQ_API int32_t oxq_gemm_w4a16(oxq_handle* h, int64_t m, int64_t n, int64_t k, c
  * OXQ_ERR_BUFFER_TOO_SMALL.  The first call on each device looks up the array's device address and
  * reads three device attributes; make that first call before any stream capture begins.  Every call
  * clears the part of the array it uses and all calls share the one array, so two calls that overlap
- * on the GPU (different streams, no ordering between them) race and give wrong sums. */
+ * on the GPU (different streams, no ordering between them) race and give wrong sums.  The first call
+ * on a device also fills a small per-device record on the host without a lock: let one host thread
+ * make that first call before other threads use the entry point on the same device. */
 OXQ_API int32_t oxq_gemm_w4a16_static(void* cuda_stream, int64_t m, int64_t n, int64_t k, const void* x_bf16_dev,
                               const uint32_t* codes_dev, const uint16_t* scales_f16_dev, const uint32_t* zeros_packed_dev,
                               int group, void* y_bf16_dev);
@@ -220,6 +247,22 @@ OXQ_API int32_t oxq_int8_dequant_tensor(oxq_handle* h, const int8_t* q_dev, cons
  * q = clamp(round_half_away(x / scale), -128, 127).  scales_dev holds ceil(n / block) floats. */
 OXQ_API int32_t oxq_int8_block_quant(oxq_handle* h, const float* x_dev, int64_t n, int64_t block, int8_t* q_dev, float* scales_dev);
 OXQ_API int32_t oxq_int8_block_dequant(oxq_handle* h, const int8_t* q_dev, const float* scales_dev, int64_t n, int64_t block, float* y_dev);
+/* quantize_to_int4 / dequantize_int4 of the DNN layer (crates/oxicuda-dnn/src/quantize/int4_quantize.rs:132-218, :229-300)
+ * with the arithmetic of its generated kernels: groups of group_size contiguous elements (the last may be short);
+ * symmetric: scale = max(absmax, 1e-12) / 7, q = trunc(clamp(x / scale, -8, 7) + 8), y = (q - 8) * scale;
+ * asymmetric: scale = max(max - min, 1e-12) / 15, zeros = -min / scale (a float, written but not used by the codes),
+ * q = trunc(clamp(x / scale, 0, 15)), y = q * scale.  Two codes per byte, even element in the low nibble; packed_dev
+ * holds ceil(n / 2) bytes, scales_dev and zeros_dev ceil(n / group_size) floats (zeros_dev may be NULL when symmetric).
+ * n == 0 returns OXQ_OK. */
+OXQ_API int32_t oxq_dnn_int4_quant(oxq_handle* h, const float* x_dev, int64_t n, int64_t group_size, int symmetric, uint8_t* packed_dev,
+                           float* scales_dev, float* zeros_dev);
+OXQ_API int32_t oxq_dnn_int4_dequant(oxq_handle* h, const uint8_t* packed_dev, const float* scales_dev, int64_t n, int64_t group_size,
+                             int symmetric, float* y_dev);
+/* quantize_block_scaled of the DNN layer (crates/oxicuda-dnn/src/quantize/block_scale.rs:53-140): per block of block_size
+ * elements (a power of two, at least 16; the last block may be short) scale = max(absmax / 6, 1e-12),
+ * out = clamp(int(rint(clamp(x / scale, -6, 6))) + 6, 0, 255) as one byte per element. */
+OXQ_API int32_t oxq_dnn_block_scaled_quant(oxq_handle* h, const void* x_dev, int dtype, int64_t n, int64_t block_size, uint8_t* out_dev,
+                                   float* scales_dev);
 /* Nf4Quantizer::encode / decode (crates/oxicuda-quant/src/scheme/nf4.rs:93-155): per block absmax (floored at
  * 1e-8), x / absmax clamped to [-1, 1], nearest of the 16 NormalFloat4 levels (the lower index on a tie), two
  * codes per byte with the even element in the low nibble.  packed_dev holds n / 2 bytes, absmax_dev n / block

@@ -69,9 +69,11 @@ def lib():
         _lib.orc_f32_to_bf16.argtypes = [C.c_float]
         _lib.orc_nf4_level.restype = C.c_float
         _lib.orc_ref_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_float, C.c_void_p]
+        _lib.orc_spec_rms_norm_blocked.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_float, C.c_void_p]
         _lib.orc_ref_smooth_scales.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_float, C.c_void_p]
         _lib.orc_ref_nearest_nf4.argtypes = [C.c_float]
         _lib.orc_ref_dnn_int8_dequant.argtypes = [C.c_void_p, C.c_size_t, C.c_float, C.c_void_p]
+        _lib.orc_ref_fp4_block_compute_scale.restype = C.c_float
     return _lib
 
 
@@ -316,6 +318,38 @@ def ref_dnn_int8_dequant(q, scale):
     return out
 
 
+def ref_dnn_int4_quant(x, group, symmetric=True):
+    """quantize_to_int4 of the DNN crate: (packed bytes, per-group scales, per-group float zeros or None)."""
+    x = _c(x, np.float32).ravel()
+    ng = (x.size + group - 1) // group
+    packed = np.zeros((x.size + 1) // 2, np.uint8)
+    scales = np.zeros(ng, np.float32)
+    zeros = np.zeros(ng, np.float32)
+    lib().orc_ref_dnn_int4_quant(_p(x), _sz(x.size), _sz(group), C.c_int(1 if symmetric else 0), _p(packed), _p(scales), _p(zeros))
+    return packed, scales, (None if symmetric else zeros)
+
+
+def ref_dnn_int4_dequant(packed, scales, n, group, symmetric=True):
+    out = np.zeros(n, np.float32)
+    lib().orc_ref_dnn_int4_dequant(_p(_c(packed, np.uint8)), _p(_c(scales, np.float32)), _sz(n), _sz(group),
+                                   C.c_int(1 if symmetric else 0), _p(out))
+    return out
+
+
+def ref_dnn_block_scaled_quant(x, block):
+    """quantize_block_scaled of the DNN crate: (biased u8 codes, per-block f32 scales)."""
+    x = _c(x, np.float32).ravel()
+    out = np.zeros(x.size, np.uint8)
+    scales = np.zeros((x.size + block - 1) // block, np.float32)
+    lib().orc_ref_dnn_block_scaled_quant(_p(x), _sz(x.size), _sz(block), _p(out), _p(scales))
+    return out, scales
+
+
+def ref_fp4_block_compute_scale(block) -> float:
+    b = _c(block, np.float32).ravel()
+    return float(lib().orc_ref_fp4_block_compute_scale(_p(b), _sz(b.size)))
+
+
 def ref_smooth_col_absmax(x):
     """compute_act_stats / compute_weight_stats: per-column max |x| of a [rows x cols] matrix."""
     x = _c(x, np.float32)
@@ -433,6 +467,18 @@ def ref_rms_norm(x, weight, eps):
         raise OracleError(4)
     out = np.zeros_like(x)
     lib().orc_ref_rms_norm(_p(x), _p(w), _sz(x.shape[0]), _sz(x.shape[1]), C.c_float(eps), _p(out))
+    return out
+
+
+def spec_rms_norm_blocked(x, weight, eps):
+    """RmsNorm::forward with the sum of squares reduced in the fused device kernel's order (items of 8 dealt to 256
+    threads, fused multiply-adds, butterfly sums); the rest is the reference's arithmetic.  cols % 8 == 0."""
+    x = _c(x, np.float32)
+    w = _c(weight, np.float32)
+    if x.ndim != 2 or x.shape[1] != w.size or x.shape[1] % 8:
+        raise OracleError(4)
+    out = np.zeros_like(x)
+    lib().orc_spec_rms_norm_blocked(_p(x), _p(w), _sz(x.shape[0]), _sz(x.shape[1]), C.c_float(eps), _p(out))
     return out
 
 
@@ -595,6 +641,15 @@ def max_threads() -> int:
     return int(lib().orc_max_threads())
 
 
+def host_cores() -> int:
+    """Cores this process may run on.  Launchers such as torchrun export OMP_NUM_THREADS=1, which caps max_threads();
+    callers that want every core pass this number as an explicit `threads=` argument instead."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 # --------------------------------------------------------------------------- quantized TP MLP (spec)
 
 def _interleave_gate_up(wg, wu):
@@ -608,7 +663,7 @@ def _deinterleave_cols(gu):
     return t[:, :, 0].reshape(m, n2 // 2), t[:, :, 1].reshape(m, n2 // 2)
 
 
-def spec_tp_mlp(x_bf16_bits, w_gate, w_up, w_down, tp, variant="fp8", threads=0, m_chunks=1):
+def spec_tp_mlp(x_bf16_bits, w_gate, w_up, w_down, tp, variant="fp8", threads=0, m_chunks=1, h_bits_per_rank=None, return_h=False):
     """Quantized tensor-parallel SwiGLU MLP with the quantization points of the GPU layer: weights of each
     shard quantised once (fp8: one scale for the fused gate/up shard and one for the down shard; w4a16: uint4
     g128), x quantised per tensor (fp8), h rounded to bf16 and (fp8) quantised per shard, each rank's partial
@@ -616,9 +671,15 @@ def spec_tp_mlp(x_bf16_bits, w_gate, w_up, w_down, tp, variant="fp8", threads=0,
     Matrix products are f32 numpy matmuls of the dequantised operands ("dequantise-then-f32").
     With m_chunks > 1 the rows of x are processed in that many independent chunks (the GPU layer's
     compute / all-reduce pipelining): activation scales are then per chunk.
+    h_bits_per_rank (fp8 variant): the bf16 bit patterns of every rank's h = silu(gate) * up as another implementation
+    produced them.  The down projection then starts from those values instead of the oracle's own h.  This is how a
+    two-GEMM layer is held to the per-GEMM bar of 1e-2: h itself is compared with the oracle's h at that bar, but a bf16
+    ulp of difference in h can move an E4M3 code of h by a whole step (2^-4 relative), so the second GEMM is only
+    comparable with a product over the same codes.  return_h also returns the list of the oracle's own h bit patterns.
     Returns bf16 bit patterns [M x hidden]."""
     del threads
     if m_chunks > 1:
+        assert h_bits_per_rank is None and not return_h
         m = x_bf16_bits.shape[0]
         b = [(i * m) // m_chunks for i in range(m_chunks + 1)]
         return np.concatenate([spec_tp_mlp(x_bf16_bits[b[i]:b[i + 1]], w_gate, w_up, w_down, tp, variant) for i in range(m_chunks)])
@@ -626,6 +687,7 @@ def spec_tp_mlp(x_bf16_bits, w_gate, w_up, w_down, tp, variant="fp8", threads=0,
     inter = w_gate.shape[0]
     sh = inter // tp
     parts = []
+    own_h = []
     if variant == "fp8":
         sx = spec_fp8_scale(spec_absmax(x_bf16_bits))
         dx = spec_fp8_dequant(spec_fp8_quant(x_bf16_bits, float(sx)), 1.0)
@@ -638,6 +700,9 @@ def spec_tp_mlp(x_bf16_bits, w_gate, w_up, w_down, tp, variant="fp8", threads=0,
             gu = (dx @ d_gu.T) * (np.float32(sx) * np.float32(s_gu))
             g, u = _deinterleave_cols(gu)
             h_bits = f32_to_bf16_bits(ref_silu_mul(g, u))
+            own_h.append(h_bits)
+            if h_bits_per_rank is not None:
+                h_bits = np.ascontiguousarray(h_bits_per_rank[r], np.uint16).reshape(h_bits.shape)
             s_h = spec_fp8_scale(spec_absmax(h_bits))
             dh = spec_fp8_dequant(spec_fp8_quant(h_bits, float(s_h)), 1.0)
             s_d = spec_fp8_scale(spec_absmax(wd))
@@ -653,4 +718,5 @@ def spec_tp_mlp(x_bf16_bits, w_gate, w_up, w_down, tp, variant="fp8", threads=0,
             dd = spec_int4g_dequant(c, s, z, wd.shape[0], wd.shape[1], 128)
             part = h @ dd.T
         parts.append(bf16_bits_to_f32(f32_to_bf16_bits(part.astype(np.float32))))
-    return f32_to_bf16_bits(ref_all_reduce_sum(parts))
+    y = f32_to_bf16_bits(ref_all_reduce_sum(parts))
+    return (y, own_h) if return_h else y

@@ -679,6 +679,84 @@ void orc_ref_dnn_int8_dequant(const int8_t* q, size_t n, float scale, float* out
     for (size_t i = 0; i < n; i++) out[i] = (float)q[i] * scale;
 }
 
+/* quantize_to_int4 (crates/oxicuda-dnn/src/quantize/int4_quantize.rs:132-218), the arithmetic of its two generated
+ * kernels.  Scale kernel (:403-545): groups of `group` contiguous elements, the last may be short;
+ *   symmetric   scale = max(absmax, 1e-12) / 7          (INT4_SYM_MAX.abs(), :468)
+ *   asymmetric  scale = max(max - min, 1e-12) / 15, zero = (-min) / scale kept as a float (:518-536); min starts at
+ *               f64::MAX and max at f64::MIN, which are +-inf as f32 immediates; setp.gt / max.f32 skip NaNs.
+ * Pack kernel (:548-701): one byte per two elements, even element in the low nibble;
+ *   symmetric   q = min(trunc(min(max(x / scale, -8), 7) + 8), 15)
+ *   asymmetric  q = min(trunc(min(max(x / scale, 0), 15)), 15)      (the zero point is not read by this kernel)
+ * max.f32 with a NaN operand returns the other operand; cvt.rzi truncates. */
+void orc_ref_dnn_int4_quant(const float* x, size_t n, size_t group, int symmetric, uint8_t* packed, float* scales, float* zeros) {
+    size_t ng = (n + group - 1) / group;
+    for (size_t g = 0; g < ng; g++) {
+        size_t lo = g * group, hi = lo + group < n ? lo + group : n;
+        float amax = 0.0f, mn = INFINITY, mx = -INFINITY;
+        for (size_t i = lo; i < hi; i++) {
+            float v = x[i];
+            amax = fmaxf(amax, fabsf(v));
+            if (mn > v) mn = v;
+            mx = fmaxf(mx, v);
+        }
+        if (symmetric) scales[g] = fmaxf(amax, 1e-12f) / 7.0f;
+        else {
+            float range = mx + mn * -1.0f;
+            scales[g] = fmaxf(range, 1e-12f) / 15.0f;
+            zeros[g] = (mn * -1.0f) / scales[g];
+        }
+    }
+    for (size_t b = 0; b < (n + 1) / 2; b++) {
+        uint32_t nib[2] = {0, 0};
+        for (int j = 0; j < 2; j++) {
+            size_t i = 2 * b + j;
+            if (i >= n) continue;
+            float s = x[i] / scales[i / group];
+            float lo = symmetric ? -8.0f : 0.0f, hi = symmetric ? 7.0f : 15.0f;
+            s = fmaxf(s, lo);
+            if (s > hi) s = hi;
+            if (symmetric) s = s + 8.0f;
+            uint32_t q = (uint32_t)s;                    /* truncation; s is in [0, 15] */
+            nib[j] = q > 15u ? 15u : q;
+        }
+        packed[b] = (uint8_t)(nib[0] | (nib[1] << 4));
+    }
+}
+
+/* dequantize_int4 (int4_quantize.rs:780-826): symmetric (nibble + (-8)) * scale, asymmetric nibble * scale. */
+void orc_ref_dnn_int4_dequant(const uint8_t* packed, const float* scales, size_t n, size_t group, int symmetric, float* out) {
+    for (size_t i = 0; i < n; i++) {
+        float nib = (float)((packed[i / 2] >> ((i & 1) * 4)) & 0x0F);
+        out[i] = symmetric ? (nib + -8.0f) * scales[i / group] : nib * scales[i / group];
+    }
+}
+
+/* quantize_block_scaled (crates/oxicuda-dnn/src/quantize/block_scale.rs:53-140), the arithmetic of its two generated
+ * kernels: scale[b] = max(absmax_b / 6, 1e-12) (:243-249); out[i] = clamp(int(rint(min(max(x / scale, -6), 6))) + 6, 0, 255)
+ * (:300-333; cvt.rni then cvt.rzi, bias FP4_MAX = 6).  The last block may be short. */
+void orc_ref_dnn_block_scaled_quant(const float* x, size_t n, size_t block, uint8_t* out, float* scales) {
+    size_t nb = (n + block - 1) / block;
+    for (size_t b = 0; b < nb; b++) {
+        size_t lo = b * block, hi = lo + block < n ? lo + block : n;
+        float am = 0.0f;
+        for (size_t i = lo; i < hi; i++) am = fmaxf(am, fabsf(x[i]));
+        scales[b] = fmaxf(am / 6.0f, 1e-12f);
+    }
+    for (size_t i = 0; i < n; i++) {
+        float s = x[i] / scales[i / block];
+        s = fminf(fmaxf(s, -6.0f), 6.0f);
+        int q = (int)rintf(s) + 6;
+        out[i] = (uint8_t)(q < 0 ? 0 : (q > 255 ? 255 : q));
+    }
+}
+
+/* Fp4BlockQuantizer::compute_scale (block_scale.rs:420-427): max|x| / 6, or 1 for an all-zero block. */
+float orc_ref_fp4_block_compute_scale(const float* block, size_t n) {
+    float mx = 0.0f;
+    for (size_t i = 0; i < n; i++) mx = fmaxf(mx, fabsf(block[i]));
+    return mx == 0.0f ? 1.0f : mx / 6.0f;
+}
+
 /* SmoothQuantMigrator (crates/oxicuda-quant/src/scheme/smooth_quant.rs).  compute_act_stats / compute_weight_stats
  * (:125-196): per-column maximum of |x| over the rows of a row-major [rows x cols] matrix. */
 int orc_ref_smooth_col_absmax(const float* x, size_t rows, size_t cols, float* stats) {
@@ -855,6 +933,44 @@ void orc_ref_rms_norm(const float* x, const float* weight, size_t rows, size_t d
         float sum = 0.0f;
         for (size_t i = 0; i < dim; i++) sum += row[i] * row[i];
         float mean_sq = sum / (float)dim;
+        float inv_rms = 1.0f / sqrtf(mean_sq + eps);
+        for (size_t i = 0; i < dim; i++) out[t * dim + i] = row[i] * inv_rms * weight[i];
+    }
+}
+
+/* RmsNorm::forward with the sum of squares taken in the order of the fused device kernel instead of left to right:
+ * the row is dealt out in items of 8 consecutive elements, thread t of 256 owns items t, t + 256, t + 512, ... and
+ * chains them with fused multiply-adds; the 32 partial sums of a warp are combined by a butterfly (partner lanes
+ * 16, 8, 4, 2, 1 apart, every lane adding its partner's value), then the 8 warp sums by a butterfly over 4, 2, 1.
+ * Everything after the sum is the reference's arithmetic (crates/oxicuda-lm/src/layer/norm.rs:82-90).  Floating-point
+ * addition is commutative, so the butterfly is the same expression on every lane.  dim is a multiple of 8. */
+void orc_spec_rms_norm_blocked(const float* x, const float* weight, size_t rows, size_t dim, float eps, float* out) {
+    size_t nitems = dim / 8;
+    for (size_t t = 0; t < rows; t++) {
+        const float* row = x + t * dim;
+        float part[256];
+        for (int th = 0; th < 256; th++) {
+            float ss = 0.0f;
+            for (size_t it = (size_t)th; it < nitems; it += 256)
+                for (int e = 0; e < 8; e++) ss = fmaf(row[it * 8 + e], row[it * 8 + e], ss);
+            part[th] = ss;
+        }
+        float wsum[8];
+        for (int w = 0; w < 8; w++) {
+            float v[32], n[32];
+            for (int l = 0; l < 32; l++) v[l] = part[w * 32 + l];
+            for (int o = 16; o > 0; o >>= 1) {
+                for (int l = 0; l < 32; l++) n[l] = v[l] + v[l ^ o];
+                for (int l = 0; l < 32; l++) v[l] = n[l];
+            }
+            wsum[w] = v[0];
+        }
+        for (int o = 4; o > 0; o >>= 1) {
+            float n[8];
+            for (int l = 0; l < 8; l++) n[l] = wsum[l] + wsum[l ^ o];
+            for (int l = 0; l < 8; l++) wsum[l] = n[l];
+        }
+        float mean_sq = wsum[0] / (float)dim;
         float inv_rms = 1.0f / sqrtf(mean_sq + eps);
         for (size_t i = 0; i < dim; i++) out[t * dim + i] = row[i] * inv_rms * weight[i];
     }

@@ -29,6 +29,13 @@ SIGNATURES = {
     "oxq_fp8_dequant": (_i32, [_vp, _vp, _i64, _vp, _vp, _int, _int]),
     "oxq_int4g_quant_pack": (_i32, [_vp, _vp, _int, _i64, _i64, _int, _vp, _vp, _vp, _int]),
     "oxq_int4g_dequant": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _int]),
+    "oxq_int4g_quant_pack_f32": (_i32, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp, _int]),
+    "oxq_int4g_dequant_f32": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _int, _vp]),
+    "oxq_fp4_microscale_quant": (_i32, [_vp, _vp, _i64, _i64, _vp, _vp]),
+    "oxq_fp4_microscale_dequant": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp]),
+    "oxq_dnn_int4_quant": (_i32, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp]),
+    "oxq_dnn_int4_dequant": (_i32, [_vp, _vp, _vp, _i64, _i64, _int, _vp]),
+    "oxq_dnn_block_scaled_quant": (_i32, [_vp, _vp, _int, _i64, _i64, _vp, _vp]),
     "oxq_swiglu_interleaved": (_i32, [_vp, _vp, _i64, _i64, _vp]),
     "oxq_sf_mma_bytes": (_sz, [_i64, _i64]),
     "oxq_mxfp8_quant": (_i32, [_vp, _vp, _int, _i64, _i64, _vp, _vp, _vp]),

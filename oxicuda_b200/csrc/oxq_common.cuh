@@ -6,6 +6,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
+#include <atomic>
 #include "../../include/oxq.h"
 
 struct oxq_handle {
@@ -46,6 +47,17 @@ struct oxq_handle {
         }                                                                \
     } while (0)
 
+// Launch settings that belong to a device (a kernel's dynamic shared-memory limit, occupancy figures) are cached per
+// device ordinal, not per process: one process may hold handles on several GPUs, and function attributes set on one
+// device say nothing about another.  A slot holds 0 until its value is known; two host threads that both find 0 both
+// compute the same value and store it, which is harmless.
+constexpr int OXQ_MAX_DEVICES = 64;
+struct OxqPerDevice {
+    std::atomic<int> v[OXQ_MAX_DEVICES];
+    int get(int device) const { return (unsigned)device < (unsigned)OXQ_MAX_DEVICES ? v[device].load(std::memory_order_acquire) : 0; }
+    void set(int device, int value) { if ((unsigned)device < (unsigned)OXQ_MAX_DEVICES) v[device].store(value, std::memory_order_release); }
+};
+
 // Refuses to launch on anything but a compute-capability 10.x device: there is no fallback path.
 int32_t oxq_require_sm100(oxq_handle* h);
 
@@ -65,6 +77,20 @@ static inline cudaError_t oxq_launch(void (*kernel)(P...), dim3 grid, dim3 block
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = (PDL && oxq_pdl_enabled()) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+
+// Cooperative launch: the driver either makes every CTA of the grid resident at once or refuses the launch, which is
+// what a kernel with a grid-wide meeting point needs when other streams may hold part of the GPU.
+template <typename... P, typename... A>
+static inline cudaError_t oxq_launch_cooperative(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeCooperative;
+    attr.val.cooperative = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
 }
 

@@ -238,6 +238,7 @@ struct GvParams {
     const uint16_t* scales;      // f16 [n x k/group]
     const uint32_t* zeros;       // packed, linear group order
     __nv_bfloat16* y;            // [m x n]
+    int scales_vec_ok;           // the scales pointer is 8-byte aligned, so four f16 scales may be read with one load
 };
 
 // PIPE: the warp's K range is longer than one chunk, so a second register buffer holds the next chunk's requests.
@@ -259,7 +260,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 2) w4a16_gemv_kernel(const GvPa
 
     // With group 128, a chunk that starts at a multiple of four groups and whole rows of scales that are 8-byte aligned,
     // the chunk's four scales of a row are one 8-byte load and its zero-points sit in one word.
-    const bool vec_meta = p.group == 128 && (gpr & 7) == 0 && ((s_lo & 3) == 0) && (((s_hi - s_lo) & 3) == 0);
+    const bool vec_meta = p.scales_vec_ok && p.group == 128 && (gpr & 7) == 0 && ((s_lo & 3) == 0) && (((s_hi - s_lo) & 3) == 0);
 
     auto fetch = [&](int s0, uint4 (&wa)[GV_CHUNK], uint4 (&wb)[GV_CHUNK], uint32_t (&sa)[GV_CHUNK], uint32_t (&sb)[GV_CHUNK]) {
 #pragma unroll
@@ -518,9 +519,14 @@ static int32_t w4a16_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const 
 
 extern "C" {
 
+// Layout of the caller's workspace: [sums and counters of the decode kernels: zero between calls][bf16 copy of the
+// dequantised weight (m > 32 only)].  The second part starts behind the largest decode region (64 batch rows), so a
+// prefill call never dirties what a later decode call on the same workspace expects to find zeroed.
+static size_t w4_clean_bytes(int64_t n) { return w4tc_ws_bytes(64, n); }
+
 size_t oxq_gemm_w4a16_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     if (m <= 0 || n <= 0) return 0;
-    if (m > 32) return (((size_t)n * (size_t)k * 2) + 255) & ~(size_t)255;      // bf16 copy of the dequantised weight
+    if (m > 32) return w4_clean_bytes(n) + ((((size_t)n * (size_t)k * 2) + 255) & ~(size_t)255);
     return w4tc_ws_bytes(m, n);                                                  // covers the mma.sync kernel's needs as well
 }
 
@@ -566,18 +572,19 @@ static int32_t w4a16_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const 
         const size_t need = w4tc_ws_bytes(m, n);
         if (!ws || ws_bytes < need || ((uintptr_t)ws & 255u))
             OXQ_FAIL(h, OXQ_ERR_BUFFER_TOO_SMALL, "workspace: expected at least %zu bytes (256-byte aligned), got %zu", need, ws_bytes);
-        // up to 32 rows the workspace is zero on entry by contract; above, it may hold a dequantised weight from a prefill call
+        // up to 32 rows the workspace is zero on entry by contract; a caller that only ever runs more rows never had to clear it
         if (m > 32) OXQ_CUDA(h, cudaMemsetAsync(ws, 0, need, h->stream));
         return oxq_w4tc_launch(h, m, n, k, x, codes, scales, zeros, y, (float*)ws, (int*)((char*)ws + sums));
     }
     if (m > 32) {
         // Prefill shapes are tensor-bound: dequantise the weight once to bf16 in the workspace (which needs
         // no zero fill on this path), then run the bf16 tensor-core GEMM.
-        const size_t need = (((size_t)n * (size_t)k * 2) + 255) & ~(size_t)255;
-        if (!ws || ws_bytes < need || ((uintptr_t)ws & 15u))
-            OXQ_FAIL(h, OXQ_ERR_BUFFER_TOO_SMALL, "workspace: expected at least %zu bytes, got %zu", need, ws_bytes);
-        if (int32_t rc = oxq_int4g_dequant(h, codes, scales, zeros, n, k, group, ws, OXQ_BF16)) return rc;
-        return oxq_gemm_bf16(h, m, n, k, x, k, ws, k, y, n);
+        const size_t need = oxq_gemm_w4a16_workspace_bytes(m, n, k);
+        if (!ws || ws_bytes < need || ((uintptr_t)ws & 255u))
+            OXQ_FAIL(h, OXQ_ERR_BUFFER_TOO_SMALL, "workspace: expected at least %zu bytes (256-byte aligned), got %zu", need, ws_bytes);
+        void* wdq = (char*)ws + w4_clean_bytes(n);           // behind the region the decode kernels keep zeroed
+        if (int32_t rc = oxq_int4g_dequant(h, codes, scales, zeros, n, k, group, wdq, OXQ_BF16)) return rc;
+        return oxq_gemm_bf16(h, m, n, k, x, k, wdq, k, y, n);
     }
     if (group % 128 != 0 || k % 128 != 0) OXQ_FAIL(h, OXQ_ERR_UNSUPPORTED_OPERATION, "decode kernel needs group and k to be multiples of 128");
     if (((uintptr_t)x & 15u) || ((uintptr_t)codes & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "x and codes must be 16-byte aligned");
@@ -589,6 +596,7 @@ static int32_t w4a16_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const 
         GvParams gp;
         gp.m = (int)m; gp.n = (int)n; gp.k = (int)k; gp.group = group;
         gp.x = (const __nv_bfloat16*)x; gp.codes = codes; gp.scales = scales; gp.zeros = zeros; gp.y = (__nv_bfloat16*)y;
+        gp.scales_vec_ok = ((uintptr_t)scales & 7u) == 0;          // the C type promises 2-byte alignment only: unaligned scales take the scalar loads
         OXQ_CUDA(h, oxq_launch(w4a16_gemv_kernel<true>, (unsigned)((n + 15) / 16), GV_WARPS * 32, 0, h->stream, gp));
         return OXQ_OK;
     }

@@ -34,7 +34,6 @@ struct GemmParams {
     int sf_col_tiles;                 // 4-column scale-factor tiles per row tile
     int sfa_row_tiles, sfb_row_tiles;
     int group_m;                      // M-tiles per rasterisation group (L2 reuse of the X panel)
-    int debug_flags;                  // timing experiments only (bit 0: skip the scale-factor copies; results are wrong)
     float alpha, beta;                // plain epilogue: y = alpha * (acc * scales) + beta * y (beta == 0: y is not read)
     int full_tiles, tail_split;       // CTA-pair dense kernel: tiles done whole, and the number of N-parts of each remaining tile
     int32_t* status;
@@ -252,7 +251,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     tc_fence_after();
                     const uint64_t adesc = smem_desc_sw128(sm_a + stage * C::kABytes);
                     const uint64_t bdesc = smem_desc_sw128(sm_b + stage * C::kBBytes);
-                    if (C::kScaled && !(p.debug_flags & 1)) {
+                    if (C::kScaled) {
 #pragma unroll
                         for (int c = 0; c < C::kSfChunks; c++) {
                             tc_cp_32x128b_warpx4(tmem_base + C::kSfaCol + 4 * c, smem_desc_sf(sm_sfa + stage * C::kSfaBytes + c * 512));
@@ -772,16 +771,15 @@ static int32_t launch(oxq_handle* h, const void* x, int64_t ldx_bytes, const voi
     CUtensorMap tm_a, tm_b;
     if (!make_tmap_bytes(&tm_a, x, p.m, p.k_bytes, ldx_bytes, BM) || !make_tmap_bytes(&tm_b, w, p.n, p.k_bytes, ldw_bytes, BN))
         OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned, leading dimensions multiples of 16 bytes)");
-    static bool attr_set = false;
-    if (!attr_set) {
+    static OxqPerDevice attr_set;
+    if (!attr_set.get(h->device)) {
         OXQ_CUDA(h, cudaFuncSetAttribute(gemm_tc_kernel<KIND, BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-        attr_set = true;
+        attr_set.set(h->device, 1);
     }
     const int tiles = ((p.m + BM - 1) / BM) * ((p.n + BN - 1) / BN);
     const int grid = tiles < h->sm_count ? tiles : h->sm_count;
     p.status = h->dev_status;
     p.group_m = group_m_setting();
-    { const char* e = getenv("OXQ_DEBUG_FLAGS"); p.debug_flags = e ? atoi(e) : 0; }
     oxq_launch(gemm_tc_kernel<KIND, BN, EPI>, grid, NUM_THREADS, C::kSmemBytes, h->stream, tm_a, tm_b, p);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
@@ -799,7 +797,8 @@ static int32_t launch2(oxq_handle* h, const void* x, int64_t ldx_bytes, const vo
     CUtensorMap tm_a, tm_b;
     if (!make_tmap_bytes(&tm_a, x, p.m, p.k_bytes, ldx_bytes, BM) || !make_tmap_bytes(&tm_b, w, p.n, p.k_bytes, ldw_bytes, BM))
         OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned, leading dimensions multiples of 16 bytes)");
-    static int max_clusters = 0;
+    static OxqPerDevice cluster_cache;
+    int max_clusters = cluster_cache.get(h->device);
     if (max_clusters == 0) {
         OXQ_CUDA(h, cudaFuncSetAttribute(gemm_tc2_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES));
         cudaLaunchConfig_t cfg = {};
@@ -813,6 +812,7 @@ static int32_t launch2(oxq_handle* h, const void* x, int64_t ldx_bytes, const vo
         int n = 0;
         if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<KIND, EPI>, &cfg) != cudaSuccess || n < 1) n = h->sm_count / 2;
         max_clusters = n < h->sm_count / 2 ? n : h->sm_count / 2;
+        cluster_cache.set(h->device, max_clusters);
     }
     const int tiles = ((p.m + 255) / 256) * ((p.n + 255) / 256);
     // The last wave: r tiles for max_clusters pairs.  Each of them is cut along N into up to four parts (64 accumulator
@@ -866,7 +866,8 @@ static int32_t launch2_scaled(oxq_handle* h, const void* x, int64_t ldx_bytes, c
         !make_tmap_sf(&tm_sfa, p.sfa, (int64_t)p.sfa_row_tiles * p.sf_col_tiles, C::kSfChunks) ||
         !make_tmap_sf(&tm_sfb, p.sfb, (int64_t)p.sfb_row_tiles * p.sf_col_tiles, C::kSfChunks))
         OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned, leading dimensions multiples of 16 bytes)");
-    static int max_clusters = 0;
+    static OxqPerDevice cluster_cache;
+    int max_clusters = cluster_cache.get(h->device);
     if (max_clusters == 0) {
         OXQ_CUDA(h, cudaFuncSetAttribute(gemm_tc2_scaled_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
         cudaLaunchConfig_t cfg = {};
@@ -880,6 +881,7 @@ static int32_t launch2_scaled(oxq_handle* h, const void* x, int64_t ldx_bytes, c
         int n = 0;
         if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_scaled_kernel<KIND>, &cfg) != cudaSuccess || n < 1) n = h->sm_count / 2;
         max_clusters = n < h->sm_count / 2 ? n : h->sm_count / 2;
+        cluster_cache.set(h->device, max_clusters);
     }
     const int tiles = ((p.m + 255) / 256) * ((p.n + C::BN2 - 1) / C::BN2);
     const int clusters = tiles < max_clusters ? tiles : max_clusters;

@@ -389,10 +389,10 @@ static int32_t launch_nb(oxq_handle* h, const CUtensorMap& tm_codes, const void*
     if (!oxq_make_tmap_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x, (uint64_t)p.k, (uint64_t)p.m, (uint64_t)p.k * 2, 64, NB,
                           CU_TENSOR_MAP_SWIZZLE_128B))
         OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "cuTensorMapEncodeTiled failed for the activations (16-byte aligned pointer needed)");
-    static bool attr_set = false;
-    if (!attr_set) {
+    static OxqPerDevice attr_set;
+    if (!attr_set.get(h->device)) {
         OXQ_CUDA(h, cudaFuncSetAttribute(w4a16_tc_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-        attr_set = true;
+        attr_set.set(h->device, 1);
     }
     const int grid = p.total_units < h->sm_count ? p.total_units : h->sm_count;
     oxq_launch(w4a16_tc_kernel<NB>, grid, NUM_THREADS, C::kSmemBytes, h->stream, tm_codes, tm_x, p);

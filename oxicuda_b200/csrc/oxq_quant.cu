@@ -329,11 +329,13 @@ __global__ void __launch_bounds__(256) fp8_quant_kernel(const T* __restrict__ x,
     }
 }
 
-// absmax and quantize in one launch.  All CTAs are resident (the host sizes the grid from the occupancy), so after
-// the first pass they meet at a counter in the handle's cells, read the maximum and run the second pass over the
-// tensor in reverse order: what the first pass read last is still in L2 (a whole activation tensor of tens of MB
-// is).  The wait on the counter is bounded; on expiry the status word is set and the pass goes on with what it has.
-// cells[0] maximum, cells[1] arrivals, cells[2] departures; the last CTA to leave puts all three back to zero.
+// absmax and quantize in one launch.  All CTAs are resident (a cooperative launch with the grid sized from the
+// occupancy: the driver refuses it rather than run part of the grid), so after the first pass they meet at a counter
+// in the handle's cells, read the maximum and run the second pass over the tensor in reverse order: what the first
+// pass read last is still in L2 (a whole activation tensor of tens of MB is).  The wait on the counter is bounded; on
+// expiry the status word is set and stats[0] and stats[1] become NaN, so the partial maximum cannot pass for a result.
+// cells[0] maximum, cells[1] arrivals, cells[2] departures, cells[3] set by a CTA whose wait expired; the last CTA to
+// leave puts all four back to zero.
 template <typename T>
 __global__ void __launch_bounds__(256) fp8_quant_dynamic_fused_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ stats,
                                                                       uint8_t* __restrict__ q, unsigned int* __restrict__ cells,
@@ -377,7 +379,7 @@ __global__ void __launch_bounds__(256) fp8_quant_dynamic_fused_kernel(const T* _
             for (uint32_t it = 0; *arrivals < gridDim.x; ++it) {
                 if ((it & 1023u) == 1023u) {
                     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
-                    if (t1 - t0 > 2000000000ull) { atomicExch(status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                    if (t1 - t0 > 2000000000ull) { atomicExch(status, OXQ_ERR_DEVICE_TIMEOUT); atomicExch(cells + 3, 1u); break; }
                 }
             }
             __threadfence();
@@ -428,7 +430,11 @@ __global__ void __launch_bounds__(256) fp8_quant_dynamic_fused_kernel(const T* _
     // ---- leave the cells as they were found --------------------------------------------------------------------
     __syncthreads();
     if (threadIdx.x == 0 && atomicAdd(cells + 2, 1u) == gridDim.x - 1) {
-        cells[0] = 0u; cells[1] = 0u; cells[2] = 0u;
+        __threadfence();
+        if (*reinterpret_cast<const volatile unsigned int*>(cells + 3) != 0u) {        // some CTA gave up waiting: no valid maximum
+            stats[0] = __uint_as_float(0x7FC00000u); stats[1] = __uint_as_float(0x7FC00000u);
+        }
+        cells[0] = 0u; cells[1] = 0u; cells[2] = 0u; cells[3] = 0u;
         __threadfence();
     }
 }
@@ -947,8 +953,10 @@ int32_t oxq_fp8_quant_dynamic(oxq_handle* h, const void* x, int dtype, int64_t n
     const int64_t bytes = n * (dtype == OXQ_F32 ? 4 : 2);
     if (fused && bytes >= (int64_t)48 << 20 && h->dev_scratch && (dtype == OXQ_F32 || dtype == OXQ_BF16 || dtype == OXQ_F16)) {
         if (int32_t rc = oxq_require_sm100(h)) return rc;
-        static int occ[3] = {0, 0, 0};
+        static OxqPerDevice occ_cache[3];
         const int di = dtype == OXQ_F32 ? 0 : (dtype == OXQ_BF16 ? 1 : 2);
+        int occ[3] = {0, 0, 0};
+        occ[di] = occ_cache[di].get(h->device);
         if (occ[di] == 0) {
             int o = 0;
             cudaError_t e = cudaSuccess;
@@ -956,14 +964,19 @@ int32_t oxq_fp8_quant_dynamic(oxq_handle* h, const void* x, int dtype, int64_t n
             else if (di == 1) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o, fp8_quant_dynamic_fused_kernel<__nv_bfloat16>, 256, 0);
             else e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&o, fp8_quant_dynamic_fused_kernel<__half>, 256, 0);
             occ[di] = (e == cudaSuccess && o > 0) ? o : -1;
+            occ_cache[di].set(h->device, occ[di]);
         }
         if (occ[di] > 0) {
             const int per_sm = occ[di] < 6 ? occ[di] : 6;
             const int grid = grid_for(h, n / (8 * FP8_ILP) + 1, 256, per_sm);          // never more CTAs than fit at once
-            unsigned int* cells = h->dev_scratch + 8;                                   // cells 8-10; 0-1 and 4 have other owners
-            DISPATCH_DTYPE(dtype, oxq_launch(fp8_quant_dynamic_fused_kernel<T>, grid, 256, 0, h->stream, (const T*)x, n, stats_dev, q, cells, h->dev_status));
-            OXQ_LAUNCH_CHECK(h);
-            return OXQ_OK;
+            unsigned int* cells = h->dev_scratch + 8;                                   // cells 8-11; 0-1 and 4 have other owners
+            // Cooperative: other streams of the process may occupy part of the GPU, and a grid that is only partly resident
+            // would wait at the meeting point for CTAs that cannot start.  If the driver cannot place the whole grid the
+            // launch fails here and the two-launch form below runs instead.
+            cudaError_t le = cudaSuccess;
+            DISPATCH_DTYPE(dtype, le = oxq_launch_cooperative(fp8_quant_dynamic_fused_kernel<T>, grid, 256, 0, h->stream, (const T*)x, n, stats_dev, q, cells, h->dev_status));
+            if (le == cudaSuccess) return OXQ_OK;
+            (void)cudaGetLastError();                                                   // clear the refused launch, fall through
         }
     }
     if (int32_t rc = oxq_absmax(h, x, dtype, n, stats_dev)) return rc;

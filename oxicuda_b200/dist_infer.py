@@ -254,6 +254,8 @@ class TpSwiGluMlp:
         self._comm_stream = torch.cuda.Stream() if self.overlap_chunks > 1 else None
         self._symm = None           # (buffer, handle) of the NVLS all-reduce path, created on first use
         import os
+        self.keep_h = False         # tests set this: forward_partial then leaves its h = silu(gate) * up in self.last_h
+        self.last_h = None
         self.use_multimem = tp > 1 and reduce_dtype == torch.bfloat16 and os.environ.get("OXQ_TP_NO_MULTIMEM", "0") != "1"
         self.split_reduce = os.environ.get("OXQ_TP_SPLIT_REDUCE", "1") != "0"
 
@@ -309,6 +311,8 @@ class TpSwiGluMlp:
         main, comm = torch.cuda.current_stream(), self._comm_stream
         xq, sx = ops.fp8_quant_dynamic(x)
         h = ops.gemm_fp8_swiglu(xq, self.w_gu_q, sx[1:], self.s_gu)
+        if self.keep_h:
+            self.last_h = h
         hq, sh = ops.fp8_quant_dynamic(h)
         ops.gemm_fp8(hq, self.w_down_q[:half], sh[1:], self.s_down, out=y[:, :half])
         ev_a = torch.cuda.Event()
@@ -334,6 +338,8 @@ class TpSwiGluMlp:
         if self.variant == "fp8":
             xq, sx = ops.fp8_quant_dynamic(x)
             h = ops.gemm_fp8_swiglu(xq, self.w_gu_q, sx[1:], self.s_gu)
+            if self.keep_h:
+                self.last_h = h
             hq, sh = ops.fp8_quant_dynamic(h)
             return ops.gemm_fp8(hq, self.w_down_q, sh[1:], self.s_down, out=out)
         m = x.shape[0]
@@ -351,7 +357,9 @@ class TpSwiGluMlp:
 
     # -- full layer: partial + all-reduce ----------------------------------------------------------
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        """x: bf16 [M x hidden], replicated on every rank.  Returns the reduced bf16 [M x hidden] on every rank."""
+        """x: bf16 [M x hidden], replicated on every rank.  Returns the reduced bf16 [M x hidden] on every rank: a
+        tensor of its own in eager use; under CUDA-graph capture, on the in-switch paths, a view of the layer's symmetric
+        buffer that the next replay overwrites."""
         import torch.distributed as dist
         if self.tp == 1:
             return self.forward_partial(x)
@@ -363,7 +371,7 @@ class TpSwiGluMlp:
                 if y is None:
                     y = self._forward_multimem(x)
                 if y is not None:
-                    return y
+                    return self._detach_from_symm(y)
             y = self.forward_partial(x)
             return self._all_reduce(y)
         # M-chunk pipelining: the all-reduce of chunk i runs on a side stream while chunk i+1 computes
@@ -385,7 +393,7 @@ class TpSwiGluMlp:
                     self.ops.multimem_all_reduce_bf16(hdl.multicast_ptr + lo * self.hidden * 2, (hi - lo) * self.hidden, self.rank, self.tp)
                     hdl.barrier(channel=2 * i + 1)
             main.wait_stream(self._comm_stream)
-            return y
+            return self._detach_from_symm(y)
         y = torch.empty((m, self.hidden), dtype=torch.bfloat16, device=x.device)
         for i in range(chunks):
             lo, hi = bounds[i], bounds[i + 1]
@@ -397,6 +405,13 @@ class TpSwiGluMlp:
                 dist.all_reduce(y[lo:hi], op=dist.ReduceOp.SUM, group=self.group)
         main.wait_stream(self._comm_stream)
         return y
+
+    def _detach_from_symm(self, y: torch.Tensor) -> torch.Tensor:
+        """The in-switch paths reduce in place in the layer's persistent symmetric buffer, which the next call
+        overwrites.  Eager callers get a copy, so a result kept across two calls (a residual) stays what it was, as
+        with the NCCL path; inside a CUDA-graph capture the view itself is returned (capture() hands it out as the
+        graph's static output, valid until the next replay)."""
+        return y if torch.cuda.is_current_stream_capturing() else y.clone()
 
     def _all_reduce(self, y: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist

@@ -20,6 +20,17 @@ class BlasError(OxqError):
     pass
 
 
+class DnnError(OxqError):
+    """DnnError of the reference (crates/oxicuda-dnn/src/error.rs:13-60).  BufferTooSmall counts BYTES here
+    (`expected` / `actual` attributes), unlike BlasError::BufferTooSmall, which counts elements."""
+
+    def __init__(self, variant: str, message: str = "", status: int = 0, expected: int | None = None, actual: int | None = None):
+        if variant == "BufferTooSmall" and expected is not None:
+            message = f"expected {expected} bytes, got {actual} bytes"
+        super().__init__(variant, message, status)
+        self.expected, self.actual = expected, actual
+
+
 class DistInferError(OxqError):
     """DistInferError of the reference (crates/oxicuda-dist-infer/src/error.rs): TpFeaturesMisaligned,
     TpInputMisaligned, DimensionMismatch, TooFewRanks, ShardShapeMismatch."""

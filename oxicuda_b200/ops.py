@@ -159,6 +159,132 @@ def int4g_dequant(codes, scales, zeros, rows: int, k: int, group: int = 128, dty
     return y
 
 
+def int4g_quant_pack_f32(x: torch.Tensor, group: int = 128, rounding: int = ROUND_HALF_AWAY, check_scales: bool = True):
+    """MinMaxQuantizer per group, asymmetric, in the reference's own parameter types: (codes u32 words [rows x k/8],
+    scales f32 [rows x k/group], zero_points i32 [rows x k/group]).  With check_scales the scales are read back and a
+    non-finite or non-positive one raises QuantError InvalidScale, as calibrate does (minmax.rs:234-236)."""
+    _chk(x, torch.float32)
+    rows, k = (x.shape[0], x.shape[1]) if x.dim() == 2 else (0, 0)
+    gpr = k // group if group > 0 else 0
+    codes = torch.empty((rows, max(k // 8, 0)), dtype=torch.int32, device=x.device)
+    scales = torch.empty((rows, gpr), dtype=torch.float32, device=x.device)
+    zps = torch.empty((rows, gpr), dtype=torch.int32, device=x.device)
+    handle(x.device.index).call("oxq_int4g_quant_pack_f32", _p(x), rows, k, group, _p(codes), _p(scales), _p(zps), rounding)
+    if check_scales and not bool((torch.isfinite(scales) & (scales > 0)).all()):
+        from .errors import QuantError
+        raise QuantError("InvalidScale", "a group's scale is not finite and positive", 3)
+    return codes, scales, zps
+
+
+def int4g_dequant_f32(codes, scales, zps, rows: int, k: int, group: int = 128):
+    y = torch.empty((rows, k), dtype=torch.float32, device=codes.device)
+    handle(codes.device.index).call("oxq_int4g_dequant_f32", _p(codes), _p(scales), _p(zps), rows, k, group, _p(y))
+    return y
+
+
+def fp4_microscale_quant(x: torch.Tensor, block: int = 32):
+    """MicroScalingQuantizer::quantize_fp4 (crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:849-876):
+    (packed bytes [ceil(n / 2)], f32 scales [ceil(n / block)])."""
+    _chk(x, torch.float32)
+    n = x.numel()
+    packed = torch.empty(max((n + 1) // 2, 1), dtype=torch.uint8, device=x.device)
+    scales = torch.empty(max((n + max(block, 1) - 1) // max(block, 1), 1), dtype=torch.float32, device=x.device)
+    handle(x.device.index).call("oxq_fp4_microscale_quant", _p(x), n, block, _p(packed), _p(scales))
+    return packed[: (n + 1) // 2], scales[: (n + block - 1) // block]
+
+
+def fp4_microscale_dequant(packed: torch.Tensor, scales: torch.Tensor, n: int, block: int = 32):
+    y = torch.empty(max(n, 1), dtype=torch.float32, device=packed.device)
+    handle(packed.device.index).call("oxq_fp4_microscale_dequant", _p(packed), _p(scales), n, block, _p(y))
+    return y[:n]
+
+
+class TensorDesc:
+    """TensorDesc<T> of the reference's DNN layer (crates/oxicuda-dnn/src/types.rs:108-118) over a torch tensor:
+    a borrowed device pointer with dims and strides; numel() and the byte size follow the dims."""
+
+    def __init__(self, tensor: torch.Tensor):
+        _chk(tensor, torch.float32, torch.bfloat16, torch.float16)
+        self.tensor = tensor
+        self.ptr = tensor.data_ptr()
+        self.dims = tuple(tensor.shape)
+        self.strides = tuple(tensor.stride())
+
+    def numel(self) -> int:
+        return self.tensor.numel()
+
+    def nbytes(self) -> int:
+        return self.tensor.numel() * self.tensor.element_size()
+
+
+def _dnn_need(buf: torch.Tensor, elems: int, what: str):
+    """DnnError::BufferTooSmall counts bytes (crates/oxicuda-dnn/src/error.rs:33-40)."""
+    if buf.numel() < elems:
+        from .errors import DnnError
+        raise DnnError("BufferTooSmall", what, 11, expected=elems * buf.element_size(), actual=buf.numel() * buf.element_size())
+
+
+class Int4QuantConfig:
+    """Int4QuantConfig of the DNN layer (crates/oxicuda-dnn/src/quantize/int4_quantize.rs:66-104)."""
+
+    def __init__(self, group_size: int, symmetric: bool):
+        if group_size == 0:
+            from .errors import DnnError
+            raise DnnError("InvalidArgument", "INT4 group_size must be non-zero", 15)
+        self.group_size, self.symmetric = int(group_size), bool(symmetric)
+
+    def num_groups(self, n: int) -> int:
+        return -(-n // self.group_size)
+
+    def packed_bytes(self, n: int) -> int:
+        return -(-n // 2)
+
+
+def quantize_to_int4(x: torch.Tensor, output: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor | None, n: int, config: Int4QuantConfig):
+    """quantize_to_int4 (int4_quantize.rs:132-218): fills `output` (ceil(n / 2) bytes), `scales` and, when asymmetric,
+    `zeros` (one float per group).  n == 0 does nothing; undersized buffers raise DnnError BufferTooSmall in bytes."""
+    if n == 0:
+        return
+    _chk(x, torch.float32)
+    _dnn_need(x, n, "input")
+    _dnn_need(output, config.packed_bytes(n), "output")
+    _dnn_need(scales, config.num_groups(n), "scales")
+    if not config.symmetric:
+        if zeros is None:
+            from .errors import DnnError
+            raise DnnError("BufferTooSmall", "zeros", 11, expected=config.num_groups(n) * 4, actual=0)
+        _dnn_need(zeros, config.num_groups(n), "zeros")
+    handle(x.device.index).call("oxq_dnn_int4_quant", _p(x), n, config.group_size, 1 if config.symmetric else 0, _p(output), _p(scales),
+                                _p(zeros if not config.symmetric else None))
+
+
+def dequantize_int4(packed: torch.Tensor, scales: torch.Tensor, output: torch.Tensor, n: int, config: Int4QuantConfig):
+    """dequantize_int4 (int4_quantize.rs:229-300)."""
+    if n == 0:
+        return
+    _dnn_need(packed, config.packed_bytes(n), "input")
+    _dnn_need(scales, config.num_groups(n), "scales")
+    _dnn_need(output, n, "output")
+    handle(packed.device.index).call("oxq_dnn_int4_dequant", _p(packed), _p(scales), n, config.group_size, 1 if config.symmetric else 0, _p(output))
+
+
+def quantize_block_scaled(desc: TensorDesc, output: torch.Tensor, scales: torch.Tensor, block_size: int):
+    """quantize_block_scaled (crates/oxicuda-dnn/src/quantize/block_scale.rs:53-140): one biased byte per element into
+    `output`, one f32 scale per block into `scales`."""
+    from .errors import DnnError
+    n = desc.numel()
+    if n == 0:
+        return
+    if block_size == 0 or (block_size & (block_size - 1)) != 0:
+        raise DnnError("InvalidArgument", f"block_size must be a non-zero power of 2, got {block_size}", 15)
+    if block_size < 16:
+        raise DnnError("InvalidArgument", f"block_size must be >= 16, got {block_size}", 15)
+    _dnn_need(output, n, "output")
+    _dnn_need(scales, -(-n // block_size), "scales")
+    x = desc.tensor
+    handle(x.device.index).call("oxq_dnn_block_scaled_quant", _p(x), _DT[x.dtype], n, block_size, _p(output), _p(scales))
+
+
 # ------------------------------------------------------------------------------------------- block scaled
 
 def sf_mma_bytes(rows: int, sf_cols: int) -> int:

@@ -239,6 +239,61 @@ def test_gemm_w4a16_decode(ops, orc, m, nk):
     _status_clean(ops)
 
 
+@pytest.mark.parametrize("nk", [(14336, 4096), (4096, 14336)])
+def test_gemm_w4a16_decode_llama8b_mlp_weights(ops, orc, nk):
+    """Benchmark configuration 3's two large projection weights at M = 1, 8, 32 (quantised once per weight)."""
+    n, k = nk
+    w = orc.gaussian((n, k), 0.02, 0)
+    c, s, z = ops.int4g_quant_pack(to_dev(w), 128)
+    deq = orc.spec_int4g_dequant(u32(c), u16(s), u32(z), n, k, 128).astype(np.float64)
+    for m in (1, 8, 32):
+        xb = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 1 + m))
+        ws = ops.gemm_w4a16_workspace(m, n, k, "cuda")
+        y = ops.gemm_w4a16(bf16_dev(xb), c, s, z, 128, workspace=ws)
+        torch.cuda.synchronize()
+        ref = (orc.bf16_bits_to_f32(xb).astype(np.float64) @ deq.T).astype(np.float32)
+        _check(_bf16_to_np(y), ref, f"w4a16 m={m} {nk}")
+        assert int(ws.view(torch.int32).abs().max()) == 0
+    _status_clean(ops)
+
+
+def test_gemm_w4a16_one_workspace_for_prefill_and_decode(ops, orc):
+    """One workspace sized for the largest batch, used for a prefill call and then for decode calls: the dequantised weight
+    of the prefill call must not sit where the decode kernels expect zeroed partial sums."""
+    n, k = 1024, 2048
+    w = orc.gaussian((n, k), 0.02, 0)
+    c, s, z = ops.int4g_quant_pack(to_dev(w), 128)
+    deq = orc.spec_int4g_dequant(u32(c), u16(s), u32(z), n, k, 128).astype(np.float64)
+    ws = ops.gemm_w4a16_workspace(128, n, k, "cuda")
+    for m in (128, 16, 4, 48, 128, 32, 1):
+        xb = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 10 + m))
+        y = ops.gemm_w4a16(bf16_dev(xb), c, s, z, 128, workspace=ws)
+        torch.cuda.synchronize()
+        ref = (orc.bf16_bits_to_f32(xb).astype(np.float64) @ deq.T).astype(np.float32)
+        _check(_bf16_to_np(y), ref, f"w4a16 shared workspace m={m}")
+    _status_clean(ops)
+
+
+def test_gemm_w4a16_scales_at_an_odd_offset(ops, orc):
+    """The scales pointer is only promised 2-byte alignment: scales that start 2, 4 or 6 bytes into a buffer take the
+    scalar loads and give the same result."""
+    n, k, m = 256, 4096, 3
+    w = orc.gaussian((n, k), 0.02, 0)
+    c, s, z = ops.int4g_quant_pack(to_dev(w), 128)
+    xb = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 1))
+    want = ops.gemm_w4a16(bf16_dev(xb), c, s, z, 128)
+    for off in (1, 2, 3):
+        buf = torch.zeros(s.numel() + 8, dtype=torch.float16, device="cuda")
+        shifted = buf[off:off + s.numel()]
+        shifted.copy_(s.view(-1))
+        assert shifted.data_ptr() % 8 == (2 * off) % 8
+        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        ops.handle().call("oxq_gemm_w4a16", m, n, k, ops._p(bf16_dev(xb)), ops._p(c), ops._p(shifted), ops._p(z), 128, ops._p(y), ops._p(None), 0)
+        torch.cuda.synchronize()
+        assert torch.equal(y, want)
+    _status_clean(ops)
+
+
 @pytest.mark.parametrize("m", [33, 64, 100, 128])
 @pytest.mark.parametrize("nk", [(4096, 4096), (200, 1024)])
 def test_gemm_w4a16_mid_batch(ops, orc, m, nk):
@@ -363,6 +418,45 @@ def test_gemm_nvfp4(ops, orc, mnk):
     da = orc.spec_nvfp4_dequant(pa.cpu().numpy(), sfa.cpu().numpy(), float(sta[1]), m, k).astype(np.float64)
     db = orc.spec_nvfp4_dequant(pb.cpu().numpy(), sfb.cpu().numpy(), float(stb[1]), n, k).astype(np.float64)
     _check(_bf16_to_np(y), (da @ db.T).astype(np.float32), f"nvfp4 {mnk}")
+
+
+@pytest.mark.parametrize("fmt", ["mxfp8", "nvfp4"])
+def test_gemm_block_scaled_llama8b_prefill_size(ops, orc, fmt):
+    """Benchmark configuration 4 at its real size (M = 4096, N = 14336, K = 4096), operands quantised on the GPU: 64 sampled
+    rows of the output, all columns, against the f64 product of the dequantised codes."""
+    m, n, k = 4096, 14336, 4096
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    a = torch.randn((m, k), generator=gen, device="cuda").to(torch.bfloat16)
+    b = torch.randn((n, k), generator=gen, device="cuda").to(torch.bfloat16)
+    rows = torch.randint(0, m, (64,), generator=torch.Generator().manual_seed(1)).cuda()
+    if fmt == "mxfp8":
+        ca, sfa, sfa_mma = ops.mxfp8_quant(a)
+        cb, sfb, sfb_mma = ops.mxfp8_quant(b)
+        y = ops.gemm_mxfp8(ca, sfa_mma, cb, sfb_mma)
+        torch.cuda.synchronize()
+        da = orc.spec_mxfp8_dequant(ca[rows].cpu().numpy(), sfa[rows].cpu().numpy())
+        db = orc.spec_mxfp8_dequant(cb.cpu().numpy(), sfb.cpu().numpy())
+    else:
+        pa, sfa, sfa_mma, sta = ops.nvfp4_quant(a)
+        pb, sfb, sfb_mma, stb = ops.nvfp4_quant(b)
+        y = ops.gemm_nvfp4(pa, sfa_mma, sta, pb, sfb_mma, stb)
+        torch.cuda.synchronize()
+        da = orc.spec_nvfp4_dequant(pa[rows].cpu().numpy(), sfa[rows].cpu().numpy(), float(sta[1]), 64, k)
+        db = orc.spec_nvfp4_dequant(pb.cpu().numpy(), sfb.cpu().numpy(), float(stb[1]), n, k)
+    _status_clean(ops)
+    ref = np.empty((64, n), np.float32)
+    da64 = da.astype(np.float64)
+    for c0 in range(0, n, 2048):                                  # column blocks keep the f64 copy of the weight small
+        ref[:, c0:c0 + 2048] = (da64 @ db[c0:c0 + 2048].astype(np.float64).T).astype(np.float32)
+    _check(_bf16_to_np(y[rows]), ref, f"{fmt} 4096x14336x4096 sample")
+    # the codes the GEMM consumed are the oracle's codes (bit-exact) on a slice of the activation tensor
+    xs = a[:256].float().cpu().numpy()
+    if fmt == "mxfp8":
+        c_ref, sf_ref = orc.spec_mxfp8_quant(xs)
+        assert np.array_equal(ca[:256].cpu().numpy(), c_ref) and np.array_equal(sfa[:256].cpu().numpy(), sf_ref)
+    else:
+        p_ref, sf_ref = orc.spec_nvfp4_quant(xs, float(sta[1]))
+        assert np.array_equal(pa[:256].cpu().numpy(), p_ref) and np.array_equal(sfa[:256].cpu().numpy(), sf_ref)
 
 
 def test_quantize_then_gemm_back_to_back(ops):

@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-from tests.gpu_util import bf16_dev
+from tests.gpu_util import bf16_bits, bf16_dev
 
 pytestmark = pytest.mark.gpu
 MAX_REL = 1e-2
@@ -29,18 +29,35 @@ def test_tp_mlp_partials_one_gpu(orc, variant, m, tp):
     xb = orc.f32_to_bf16_bits(orc.gaussian((m, hidden), 1.0, 1))
     x = bf16_dev(xb)
     acc = None
+    hs = []
     for r in range(tp):
         layer = TpSwiGluMlp(torch.from_numpy(wg), torch.from_numpy(wu), torch.from_numpy(wd), variant, tp=tp, rank=r)
+        layer.keep_h = True
         part = layer.forward_partial(x).float()
         acc = part if acc is None else acc + part
+        if variant == "fp8":
+            hs.append(bf16_bits(layer.last_h))
     torch.cuda.synchronize()
     from oxicuda_b200 import ops
     assert ops.handle().device_status() == 0
     got = acc.to(torch.bfloat16).float().cpu().numpy()
-    ref = orc.bf16_bits_to_f32(orc.spec_tp_mlp(xb, wg, wu, wd, tp, variant))
-    scale = np.abs(ref).max()
+    _check_against_oracle(orc, got, xb, wg, wu, wd, tp, variant, hs, (variant, m, tp))
+
+
+def _check_against_oracle(orc, got, xb, wg, wu, wd, tp, variant, hs, tag):
+    """Both GEMMs of the layer at the 1e-2 bar.  FP8: h of every rank against the oracle's h, then the layer output against
+    the oracle continued from those very h values (the E4M3 codes of h are a step function of h: see spec_tp_mlp)."""
     assert np.isfinite(got).all()
-    assert np.abs(got - ref).max() <= MAX_REL * scale * (2.0 if variant == "fp8" else 1.0), (variant, m, tp, np.abs(got - ref).max() / scale)
+    if variant == "fp8":
+        ref_own, own_h = orc.spec_tp_mlp(xb, wg, wu, wd, tp, variant, return_h=True)
+        for r in range(tp):
+            h_gpu, h_ref = orc.bf16_bits_to_f32(hs[r]), orc.bf16_bits_to_f32(own_h[r])
+            assert np.abs(h_gpu - h_ref).max() <= MAX_REL * np.abs(h_ref).max(), (tag, "h", r)
+        ref = orc.bf16_bits_to_f32(orc.spec_tp_mlp(xb, wg, wu, wd, tp, variant, h_bits_per_rank=hs))
+    else:
+        ref = orc.bf16_bits_to_f32(orc.spec_tp_mlp(xb, wg, wu, wd, tp, variant))
+    scale = np.abs(ref).max()
+    assert np.abs(got - ref).max() <= MAX_REL * scale, (tag, np.abs(got - ref).max() / scale)
 
 
 def _free_port():
@@ -64,12 +81,32 @@ def _nccl_rank(rank, world, port, variant, q):
     xb = orc.f32_to_bf16_bits(orc.gaussian((m, hidden), 1.0, 1))
     x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
     errs = []
-    for chunks in (1, 2):
-        layer = TpSwiGluMlp(torch.from_numpy(wg), torch.from_numpy(wu), torch.from_numpy(wd), variant, tp=world, rank=rank,
-                            overlap_chunks=chunks)
-        y = layer.forward(x).float().cpu().numpy()
-        ref = orc.bf16_bits_to_f32(orc.spec_tp_mlp(xb, wg, wu, wd, world, variant, m_chunks=chunks))
-        errs.append(float(np.abs(y - ref).max() / np.abs(ref).max()))
+    layer = TpSwiGluMlp(torch.from_numpy(wg), torch.from_numpy(wu), torch.from_numpy(wd), variant, tp=world, rank=rank)
+    layer.keep_h = True
+    y1 = layer.forward(x)
+    y1_host = y1.float().cpu().numpy()
+    hs = None
+    if variant == "fp8":                                    # every rank's h, so that the oracle can continue from the same values
+        mine = layer.last_h.contiguous()
+        allh = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allh, mine)
+        hs = [t.view(torch.int16).cpu().numpy().view(np.uint16) for t in allh]
+        ref_own, own_h = orc.spec_tp_mlp(xb, wg, wu, wd, world, variant, return_h=True)
+        for r in range(world):
+            a, b = orc.bf16_bits_to_f32(hs[r]), orc.bf16_bits_to_f32(own_h[r])
+            errs.append(float(np.abs(a - b).max() / np.abs(b).max()))
+    ref = orc.bf16_bits_to_f32(orc.spec_tp_mlp(xb, wg, wu, wd, world, variant, h_bits_per_rank=hs))
+    errs.append(float(np.abs(y1_host - ref).max() / np.abs(ref).max()))
+    # a second call on other activations must leave the first result as it was (eager results do not alias the layer's buffers)
+    y2 = layer.forward(x * 0.5)
+    torch.cuda.synchronize()
+    errs.append(0.0 if np.array_equal(y1.float().cpu().numpy(), y1_host) and not torch.equal(y1, y2) else 1.0)
+    # M-chunk pipelining: per-chunk activation scales on both sides, no h hand-over (sanity bound only: the E4M3 codes of h
+    # are a step function of h, so this path is not held to the per-GEMM bar)
+    layer2 = TpSwiGluMlp(torch.from_numpy(wg), torch.from_numpy(wu), torch.from_numpy(wd), variant, tp=world, rank=rank, overlap_chunks=2)
+    y = layer2.forward(x).float().cpu().numpy()
+    ref2 = orc.bf16_bits_to_f32(orc.spec_tp_mlp(xb, wg, wu, wd, world, variant, m_chunks=2))
+    errs.append(float(np.abs(y - ref2).max() / np.abs(ref2).max()) / (1.0 if variant == "w4a16" else 3.0))
     q.put((rank, errs))
     dist.barrier()
     dist.destroy_process_group()
@@ -92,7 +129,47 @@ def test_tp_mlp_nccl_two_gpus(variant):
         assert p.exitcode == 0
     for _, errs in res:
         for e in errs:
-            assert e <= 2 * MAX_REL
+            assert e <= MAX_REL, errs
+
+
+@pytest.fixture(scope="module")
+def llama70b_weights(orc):
+    """Gate, up and down weights of the benchmark's layer (hidden 8192, intermediate 28672), N(0, 0.02).  One Gaussian
+    matrix is drawn; the other two are a row rotation and a transposed column rotation of it (drawing 705 M samples three
+    times over would take longer than everything the GPU does in this file)."""
+    hidden, inter = 8192, 28672
+    wg = orc.gaussian((inter, hidden), 0.02, 0)
+    wu = np.roll(wg, 977, axis=0)
+    wd = np.ascontiguousarray(np.roll(wg, 131, axis=1).T)
+    return wg, wu, wd
+
+
+@pytest.mark.parametrize("variant", ["fp8", "w4a16"])
+@pytest.mark.parametrize("m", [1, 64])
+def test_tp_mlp_llama70b_shape_one_gpu(orc, llama70b_weights, variant, m):
+    """The benchmark's layer at its real size (hidden 8192, intermediate 28672), tp = 8 with the ranks emulated one
+    after the other on one GPU: every rank's kernels see exactly the shard shapes of the 8-GPU run."""
+    from oxicuda_b200.dist_infer import TpSwiGluMlp
+    hidden, inter, tp = 8192, 28672, 8
+    wg, wu, wd = llama70b_weights
+    xb = orc.f32_to_bf16_bits(orc.gaussian((m, hidden), 1.0, 1))
+    x = bf16_dev(xb)
+    sh = inter // tp
+    acc, hs = None, []
+    for r in range(tp):
+        layer = TpSwiGluMlp(torch.from_numpy(wg[r * sh:(r + 1) * sh]), torch.from_numpy(wu[r * sh:(r + 1) * sh]),
+                            torch.from_numpy(np.ascontiguousarray(wd[:, r * sh:(r + 1) * sh])), variant, tp=tp, rank=r, already_sharded=True)
+        layer.keep_h = True
+        part = layer.forward_partial(x).float()
+        acc = part if acc is None else acc + part
+        if variant == "fp8":
+            hs.append(bf16_bits(layer.last_h))
+        del layer
+    torch.cuda.synchronize()
+    from oxicuda_b200 import ops
+    assert ops.handle().device_status() == 0
+    got = acc.to(torch.bfloat16).float().cpu().numpy()
+    _check_against_oracle(orc, got, xb, wg, wu, wd, tp, variant, hs, (variant, m, "llama70b"))
 
 
 # ---- single column- / row-parallel linears ---------------------------------------------------------

@@ -353,3 +353,51 @@ def test_gptq_kats(orc):  # crates/oxicuda-quant/src/scheme/gptq.rs:341-520
     x = rng.standard_normal((256, 32)).astype(np.float32)
     q2, _, _ = orc.ref_gptq_quantize_layer(w, 16, 32, (2.0 * x.T @ x / 256.0).astype(np.float32), bits=4)
     assert np.array_equal(q2[:, 0], qi[:, 0]) and not np.array_equal(q2, qi)
+
+
+# --------------------------------------------------------------------------- DNN INT4 / block-scaled (f1)
+
+def test_fp4_block_quantizer_scale_kats(orc):
+    """Fp4BlockQuantizer::compute_scale known answers (crates/oxicuda-dnn/src/quantize/block_scale.rs:511-544, :574-590)."""
+    assert orc.ref_fp4_block_compute_scale(np.zeros(32, np.float32)) == 1.0
+    assert abs(orc.ref_fp4_block_compute_scale(np.full(32, 6.0, np.float32)) - 1.0) < 1e-6
+    assert abs(orc.ref_fp4_block_compute_scale(np.full(32, 12.0, np.float32)) - 2.0) < 1e-6
+    blk = np.zeros(32, np.float32)
+    blk[0], blk[1], blk[2] = -6.0, 3.0, 1.5
+    assert abs(orc.ref_fp4_block_compute_scale(blk) - 1.0) < 1e-6
+
+
+def test_dnn_block_scaled_restatement(orc):
+    """quantize_block_scaled's generated arithmetic (block_scale.rs:243-249, :300-333) on hand-checked values:
+    scale = absmax / 6, codes = rint(x / scale) + 6, ties to even, a short last block, an all-zero block."""
+    x = np.array([6.0, -6.0, 3.0, 2.5, 1.5, 0.5, -0.5, 0.0] + [0.0] * 8 + [0.0] * 16 + [12.0, -3.0], np.float32)
+    q, s = orc.ref_dnn_block_scaled_quant(x, 16)
+    assert s.tolist() == [1.0, np.float32(1e-12), 2.0]
+    assert q[:8].tolist() == [12, 0, 9, 8, 8, 6, 6, 6]               # 2.5 -> 2, 1.5 -> 2, +-0.5 -> 0 (half to even)
+    assert q[16:32].tolist() == [6] * 16
+    assert q[32:].tolist() == [12, 4]                                 # -3 / 2 = -1.5 -> -2
+
+
+def test_dnn_int4_restatement(orc):
+    """quantize_to_int4's generated arithmetic (int4_quantize.rs:440-468, :518-536, :655-690): symmetric scale = absmax / 7
+    with codes trunc(x / scale + 8); asymmetric scale = (max - min) / 15, zero = -min / scale, codes trunc(x / scale) clamped at 0."""
+    x = np.array([7.0, -7.0, 3.5, -3.5, 0.0, 1.0, -8.0, 6.9], np.float32)
+    p, s, z = orc.ref_dnn_int4_quant(x, 8, True)
+    assert s.tolist() == [np.float32(8.0) / np.float32(7.0)] and z is None
+    codes = [int(b) & 15 for b in p for _ in (0,)] + []
+    lo = [int(b) & 15 for b in p]
+    hi = [int(b) >> 4 for b in p]
+    got = [v for pair in zip(lo, hi) for v in pair]
+    want = [int(min(max(np.float32(v) / s[0], -8.0), 7.0) + 8.0) for v in x]
+    assert got == want and got[6] == 1 and got[0] == 14              # -8 / (8/7) = -7 -> 1; 7 / (8/7) = 6.125 -> 14
+    y = orc.ref_dnn_int4_dequant(p, s, 8, 8, True)
+    assert y[4] == 0.0 and y[6] == np.float32(-7.0) * s[0]
+    x = np.arange(16, dtype=np.float32) - 5.0                         # min -5, max 10: scale 1, zero 5; negatives clamp to code 0
+    p, s, z = orc.ref_dnn_int4_quant(x, 16, False)
+    assert s.tolist() == [1.0] and z.tolist() == [5.0]
+    lo = [int(b) & 15 for b in p]
+    hi = [int(b) >> 4 for b in p]
+    got = [v for pair in zip(lo, hi) for v in pair]
+    assert got == [0, 0, 0, 0, 0, 0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10]
+    p, s, z = orc.ref_dnn_int4_quant(np.zeros(5, np.float32), 4, True)   # short last group, all zero: scale floor 1e-12 / 7
+    assert len(p) == 3 and s.tolist() == [np.float32(1e-12) / np.float32(7.0)] * 2

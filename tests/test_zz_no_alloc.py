@@ -5,8 +5,9 @@ framework's memory plan, or in a plugin that must not call cudaMalloc after star
 neither create a handle nor hand over a workspace.  oxq_gemm_w4a16_static serves them from a scratch
 array built into the library.  This test drives it with nothing but a stream and the operand
 pointers, twice in a row (the second call finds the first call's leftovers in the shared array and
-must clear them itself), and compares each result with the regular entry point's on the same inputs,
-with the GEMM tolerance of the other tests (max-relative 1e-2 on bf16 outputs).
+must clear them itself), and compares each result with the regular entry point's on the same inputs
+and with the CPU oracle's product of the dequantised codes, with the GEMM tolerance of the other tests
+(max-relative 1e-2 on bf16 outputs).
 
 This file sorts last on purpose: if it fails under `pytest -x`, every other test has already run.
 """
@@ -30,6 +31,7 @@ def _call_static(lib, x, codes, scales, zeros, y, group=128):
 
 
 def test_static_entry_matches_regular_entry_twice():
+    from oracle import oracle as orc
     from oxicuda_b200 import _ffi, ops
     lib = _ffi.load()
     torch.cuda.set_device(0)
@@ -40,6 +42,11 @@ def test_static_entry_matches_regular_entry_twice():
         x = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
         want = ops.gemm_w4a16(x, codes, scales, zeros, 128).float()
         scale = float(want.abs().max())
+        # the regular entry point's result is itself what the CPU oracle gives for these codes (dequantise, then f64 product)
+        deq = orc.spec_int4g_dequant(codes.cpu().numpy().view(np.uint32), scales.view(torch.int16).cpu().numpy().view(np.uint16),
+                                     zeros.cpu().numpy().view(np.uint32), n, k, 128).astype(np.float64)
+        oracle_y = torch.from_numpy((x.float().cpu().numpy().astype(np.float64) @ deq.T).astype(np.float32)).cuda()
+        assert float((want - oracle_y).abs().max()) <= MAX_REL * float(oracle_y.abs().max())
         for call in range(2):
             y = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
             assert _call_static(lib, x, codes, scales, zeros, y) == 0
@@ -47,6 +54,7 @@ def test_static_entry_matches_regular_entry_twice():
             got = y.float()
             assert bool(torch.isfinite(got).all()), f"call {call}: unwritten or non-finite outputs"
             assert float((got - want).abs().max()) <= MAX_REL * scale, f"call {call} shape {(m, n, k)}"
+            assert float((got - oracle_y).abs().max()) <= MAX_REL * float(oracle_y.abs().max()), f"call {call} against the oracle"
         # a different, smaller problem right after: stale sums from the larger one must not leak in
         y2 = torch.empty((1, n), dtype=torch.bfloat16, device="cuda")
         assert _call_static(lib, x[:1].contiguous(), codes, scales, zeros, y2) == 0

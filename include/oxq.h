@@ -186,6 +186,24 @@ OXQ_API int32_t oxq_gemm_fp8_ex(oxq_handle* h, int64_t m, int64_t n, int64_t k, 
                         const uint8_t* w_dev, int64_t ldw, const float* sx_dev, const float* sw_dev, float beta, void* y_bf16_dev, int64_t ldy);
 OXQ_API int32_t oxq_gemm_bf16_ex(oxq_handle* h, int64_t m, int64_t n, int64_t k, float alpha, const void* x_bf16_dev, int64_t ldx,
                          const void* w_bf16_dev, int64_t ldw, float beta, void* y_bf16_dev, int64_t ldy);
+/* gemm's operand forms (trans_a, trans_b and MatrixDesc.layout, gemm_api.rs:73-82, types.rs:60-90, :443-455).  C = alpha * op(A) * op(B)
+ * + beta * C with op(A) [m x k] and op(B) [k x n]; what matters to the kernel is which index is contiguous in memory:
+ *   a_major  OXQ_OP_K_MAJOR   A is stored [m x lda], k contiguous   (NoTrans + RowMajor, or Trans + ColMajor)
+ *            OXQ_OP_MN_MAJOR  A is stored [k x lda], m contiguous   (Trans + RowMajor, or NoTrans + ColMajor)
+ *   b_major  OXQ_OP_K_MAJOR   B is stored [n x ldb], k contiguous   (Trans + RowMajor, or NoTrans + ColMajor): the weight layout W[N x K]
+ *            OXQ_OP_MN_MAJOR  B is stored [k x ldb], n contiguous   (NoTrans + RowMajor: the reference's default call)
+ * so a reference caller's gemm(NoTrans, NoTrans, ...) on row-major matrices is (K_MAJOR, MN_MAJOR) and needs no transposed copy.
+ * The output is row-major [m x ldy] bf16; a column-major C is the row-major C^T = op(B)^T * op(A)^T, i.e. the same call with the
+ * operands exchanged and their flags flipped (the host mirror does that).  MN-major tiles go through the shared-memory descriptor
+ * and the major bits of the tcgen05 instruction descriptor.  Leading dimensions are multiples of 16 bytes; k is a multiple of
+ * 16 bytes' worth of elements when an operand is K-major.  Errors: InvalidDimension (zero sizes, a leading dimension smaller
+ * than the contiguous extent), InvalidArgument (alignment, unknown flag). */
+enum { OXQ_OP_K_MAJOR = 0, OXQ_OP_MN_MAJOR = 1 };
+OXQ_API int32_t oxq_gemm_fp8_op(oxq_handle* h, int64_t m, int64_t n, int64_t k, float alpha, const uint8_t* a_dev, int64_t lda, int a_major,
+                        const uint8_t* b_dev, int64_t ldb, int b_major, const float* sa_dev, const float* sb_dev, float beta,
+                        void* y_bf16_dev, int64_t ldy);
+OXQ_API int32_t oxq_gemm_bf16_op(oxq_handle* h, int64_t m, int64_t n, int64_t k, float alpha, const void* a_bf16_dev, int64_t lda, int a_major,
+                         const void* b_bf16_dev, int64_t ldb, int b_major, float beta, void* y_bf16_dev, int64_t ldy);
 OXQ_API int32_t oxq_gemm_fp8_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, const uint8_t* x_dev, int64_t ldx,
                             const uint8_t* w_gu_dev, int64_t ldw, const float* sx_dev, const float* sw_dev,
                             void* h_bf16_dev, int64_t ldh);

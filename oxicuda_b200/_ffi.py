@@ -60,6 +60,8 @@ SIGNATURES = {
     "oxq_gemm_fp8": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64]),
     "oxq_gemm_fp8_ex": (_i32, [_vp, _i64, _i64, _i64, C.c_float, _vp, _i64, _vp, _i64, _vp, _vp, C.c_float, _vp, _i64]),
     "oxq_gemm_bf16_ex": (_i32, [_vp, _i64, _i64, _i64, C.c_float, _vp, _i64, _vp, _i64, C.c_float, _vp, _i64]),
+    "oxq_gemm_fp8_op": (_i32, [_vp, _i64, _i64, _i64, C.c_float, _vp, _i64, _int, _vp, _i64, _int, _vp, _vp, C.c_float, _vp, _i64]),
+    "oxq_gemm_bf16_op": (_i32, [_vp, _i64, _i64, _i64, C.c_float, _vp, _i64, _int, _vp, _i64, _int, C.c_float, _vp, _i64]),
     "oxq_gemm_fp8_swiglu": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64]),
     "oxq_gemm_bf16": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64]),
     "oxq_gemm_bf16_swiglu": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64]),

@@ -36,6 +36,8 @@ struct GemmParams {
     int group_m;                      // M-tiles per rasterisation group (L2 reuse of the X panel)
     float alpha, beta;                // plain epilogue: y = alpha * (acc * scales) + beta * y (beta == 0: y is not read)
     int full_tiles, tail_split;       // CTA-pair dense kernel: tiles done whole, and the number of N-parts of each remaining tile
+    int a_mn, b_mn;                   // CTA-pair dense kernel: operand stored MN-major (X as [K x M], W as [K x N]) instead of K-major
+    int esize;                        // bytes per operand element (1 or 2)
     int32_t* status;
 };
 
@@ -440,8 +442,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     // the full barrier of the pair lives in CTA 0 and expects the bytes of both CTAs
                     if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * T2_STAGE_BYTES);
                     const uint32_t full0 = mapa_shared(bar_full + 8 * stage, 0);
-                    tma_load_2d_cg2(sm_a + stage * BM * BKB, &tm_a, kb * BKB, m0, full0);
-                    tma_load_2d_cg2(sm_b + stage * BM * BKB, &tm_b, kb * BKB, n0, full0);
+                    // K-major operand: one box of 128 rows x 128 bytes of K.  MN-major operand ([K x M] / [K x N] in memory):
+                    // `esize` boxes of (128 / esize) K rows x 128 bytes of M / N, one swizzle atom each, side by side.
+                    if (!p.a_mn) tma_load_2d_cg2(sm_a + stage * BM * BKB, &tm_a, kb * BKB, m0, full0);
+                    else for (int j = 0; j < p.esize; j++)
+                        tma_load_2d_cg2(sm_a + stage * BM * BKB + j * (BM * BKB / p.esize), &tm_a, m0 * p.esize + j * 128, kb * (BKB / p.esize), full0);
+                    if (!p.b_mn) tma_load_2d_cg2(sm_b + stage * BM * BKB, &tm_b, kb * BKB, n0, full0);
+                    else for (int j = 0; j < p.esize; j++)
+                        tma_load_2d_cg2(sm_b + stage * BM * BKB + j * (BM * BKB / p.esize), &tm_b, n0 * p.esize + j * 128, kb * (BKB / p.esize), full0);
                     if (++stage == S) { stage = 0; phase ^= 1; }
                 }
             }
@@ -454,18 +462,23 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
             for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
-                const uint32_t idesc = idesc_dense(cf, af, af, BM2, (uint32_t)work_item(w, p.full_tiles, p.tail_split).n_cols);
+                const uint32_t idesc = idesc_dense(cf, af, af, BM2, (uint32_t)work_item(w, p.full_tiles, p.tail_split).n_cols) |
+                                       idesc_majors((uint32_t)p.a_mn, (uint32_t)p.b_mn);
                 if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN2;
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(bar_full + 8 * stage, phase)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                     tc_fence_after();
-                    const uint64_t adesc = smem_desc_sw128(sm_a + stage * BM * BKB);
-                    const uint64_t bdesc = smem_desc_sw128(sm_b + stage * BM * BKB);
+                    // each MMA consumes 32 bytes of K: 32 bytes further along a K-major row, or 32 / esize rows of 128 bytes
+                    // (whole 1024-byte row groups) further down an MN-major tile
+                    const uint32_t atom = (uint32_t)(BM * BKB / p.esize), kstep_mn = (uint32_t)(4096 / p.esize) >> 4;
+                    const uint64_t adesc = p.a_mn ? smem_desc_mn_sw128(sm_a + stage * BM * BKB, atom) : smem_desc_sw128(sm_a + stage * BM * BKB);
+                    const uint64_t bdesc = p.b_mn ? smem_desc_mn_sw128(sm_b + stage * BM * BKB, atom) : smem_desc_sw128(sm_b + stage * BM * BKB);
+                    const uint32_t ka = p.a_mn ? kstep_mn : 2u, kbs = p.b_mn ? kstep_mn : 2u;
 #pragma unroll
                     for (int k = 0; k < BKB / 32; k++) {
-                        const uint64_t a = adesc + (uint64_t)(k * 2), b = bdesc + (uint64_t)(k * 2);
+                        const uint64_t a = adesc + (uint64_t)(k * ka), b = bdesc + (uint64_t)(k * kbs);
                         const uint32_t accum = (kb | k) != 0;
                         if (KIND == KIND_F8) mma_f8f6f4_cg2(d_tmem, a, b, idesc, accum);
                         else if (KIND == KIND_BF16) mma_f16_cg2(d_tmem, a, b, idesc, accum);
@@ -795,7 +808,15 @@ static bool use_2cta_setting() {
 template <int KIND, int EPI = EPI_SCALE>
 static int32_t launch2(oxq_handle* h, const void* x, int64_t ldx_bytes, const void* w, int64_t ldw_bytes, GemmParams p) {
     CUtensorMap tm_a, tm_b;
-    if (!make_tmap_bytes(&tm_a, x, p.m, p.k_bytes, ldx_bytes, BM) || !make_tmap_bytes(&tm_b, w, p.n, p.k_bytes, ldw_bytes, BM))
+    if (p.esize != 2) p.esize = 1;
+    // K-major: byte matrix [rows x K bytes], boxes of 128 rows x 128 bytes.  MN-major: byte matrix [K x rows * esize],
+    // boxes of (128 / esize) K rows x 128 bytes.
+    const int64_t k_elems = p.k_bytes / p.esize;
+    const bool ok_a = p.a_mn ? make_tmap_bytes(&tm_a, x, k_elems, (int64_t)p.m * p.esize, ldx_bytes, BKB / p.esize)
+                             : make_tmap_bytes(&tm_a, x, p.m, p.k_bytes, ldx_bytes, BM);
+    const bool ok_b = p.b_mn ? make_tmap_bytes(&tm_b, w, k_elems, (int64_t)p.n * p.esize, ldw_bytes, BKB / p.esize)
+                             : make_tmap_bytes(&tm_b, w, p.n, p.k_bytes, ldw_bytes, BM);
+    if (!ok_a || !ok_b)
         OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned, leading dimensions multiples of 16 bytes)");
     static OxqPerDevice cluster_cache;
     int max_clusters = cluster_cache.get(h->device);
@@ -946,6 +967,44 @@ int32_t oxq_gemm_fp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8
 int32_t oxq_gemm_fp8_ex(oxq_handle* h, int64_t m, int64_t n, int64_t k, float alpha, const uint8_t* x, int64_t ldx, const uint8_t* w, int64_t ldw,
                         const float* sx, const float* sw, float beta, void* y, int64_t ldy) {
     return gemm_fp8_impl(h, m, n, k, x, ldx, w, ldw, sx, sw, alpha, beta, y, ldy);
+}
+
+static int32_t gemm_bf16_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, int64_t ldx, const void* w, int64_t ldw,
+                              float alpha, float beta, void* y, int64_t ldy);
+
+// gemm's operand forms: each operand K-major or MN-major in memory; the CTA-pair kernel takes either through the shared-memory
+// descriptor and the instruction descriptor's major bits, whatever m (a single 128-row tile of X simply leaves the second CTA's rows empty)
+static int32_t gemm_op_impl(oxq_handle* h, bool fp8, int64_t m, int64_t n, int64_t k, float alpha, const void* a, int64_t lda, int a_major,
+                            const void* b, int64_t ldb, int b_major, const float* sa, const float* sb, float beta, void* y, int64_t ldy) {
+    OXQ_CHECK_HANDLE(h);
+    if (int32_t rc = check_gemm_args(h, m, n, k, a, b, y, ldy)) return rc;
+    if (fp8 && (!sa || !sb)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
+    if ((a_major != OXQ_OP_K_MAJOR && a_major != OXQ_OP_MN_MAJOR) || (b_major != OXQ_OP_K_MAJOR && b_major != OXQ_OP_MN_MAJOR))
+        OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "operand layout must be OXQ_OP_K_MAJOR or OXQ_OP_MN_MAJOR");
+    const int64_t es = fp8 ? 1 : 2, al = 16 / es;
+    const int64_t need_a = a_major == OXQ_OP_K_MAJOR ? k : m, need_b = b_major == OXQ_OP_K_MAJOR ? k : n;
+    if (lda < need_a || ldb < need_b) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "leading dimension smaller than the contiguous extent (lda %lld < %lld or ldb %lld < %lld)",
+                                               (long long)lda, (long long)need_a, (long long)ldb, (long long)need_b);
+    if ((lda % al) || (ldb % al)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "leading dimensions must be multiples of %lld elements (16 bytes)", (long long)al);
+    if ((a_major == OXQ_OP_K_MAJOR || b_major == OXQ_OP_K_MAJOR) && (k % al)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k must be a multiple of %lld for a K-major operand", (long long)al);
+    if (a_major == OXQ_OP_K_MAJOR && b_major == OXQ_OP_K_MAJOR)
+        return fp8 ? gemm_fp8_impl(h, m, n, k, (const uint8_t*)a, lda, (const uint8_t*)b, ldb, sa, sb, alpha, beta, y, ldy)
+                   : gemm_bf16_impl(h, m, n, k, a, lda, b, ldb, alpha, beta, y, ldy);
+    GemmParams p{};
+    p.alpha = alpha; p.beta = beta;
+    p.m = (int)m; p.n = (int)n; p.k_bytes = (int)(k * es); p.y = y; p.ldy = ldy; p.s0 = sa; p.s1 = sb;
+    p.a_mn = a_major == OXQ_OP_MN_MAJOR; p.b_mn = b_major == OXQ_OP_MN_MAJOR; p.esize = (int)es;
+    return fp8 ? launch2<KIND_F8>(h, a, lda * es, b, ldb * es, p) : launch2<KIND_BF16>(h, a, lda * es, b, ldb * es, p);
+}
+
+int32_t oxq_gemm_fp8_op(oxq_handle* h, int64_t m, int64_t n, int64_t k, float alpha, const uint8_t* a, int64_t lda, int a_major,
+                        const uint8_t* b, int64_t ldb, int b_major, const float* sa, const float* sb, float beta, void* y, int64_t ldy) {
+    return gemm_op_impl(h, true, m, n, k, alpha, a, lda, a_major, b, ldb, b_major, sa, sb, beta, y, ldy);
+}
+
+int32_t oxq_gemm_bf16_op(oxq_handle* h, int64_t m, int64_t n, int64_t k, float alpha, const void* a, int64_t lda, int a_major,
+                         const void* b, int64_t ldb, int b_major, float beta, void* y, int64_t ldy) {
+    return gemm_op_impl(h, false, m, n, k, alpha, a, lda, a_major, b, ldb, b_major, nullptr, nullptr, beta, y, ldy);
 }
 
 int32_t oxq_gemm_fp8_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, const uint8_t* x, int64_t ldx, const uint8_t* w_gu, int64_t ldw,

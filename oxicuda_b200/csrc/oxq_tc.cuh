@@ -213,6 +213,14 @@ __device__ __forceinline__ void mma_mxf4nvf4_x4_cg2(uint32_t d_tmem, uint64_t ad
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
     return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
+// The same for an MN-major operand tile (the M or N index is the contiguous one in memory, as in B[K x N] row-major):
+// the tile is stored as rows of 128 bytes, one row per K index, 128-byte swizzle (what a TMA load of a [K rows x 128
+// bytes] box writes), 8-row groups 1024 bytes apart (stride byte offset); a tile wider than 128 bytes of M / N is a
+// sequence of such atoms `lbo_bytes` apart (leading byte offset).
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
 // Un-swizzled descriptor for a scale-factor chunk: four 8-row x 16-byte core matrices 128 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sf(uint32_t smem_addr) {
     return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | (1ull << 46);
@@ -224,6 +232,8 @@ __device__ __forceinline__ uint64_t smem_desc_sf(uint32_t smem_addr) {
 __host__ __device__ constexpr uint32_t idesc_dense(uint32_t c_fmt, uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n) {
     return (c_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
+// major-ness bits of the dense kinds: set for an operand whose tile is MN-major in shared memory
+__host__ __device__ constexpr uint32_t idesc_majors(uint32_t a_mn, uint32_t b_mn) { return (a_mn << 15) | (b_mn << 16); }
 // Block-scaled kinds (mxf8f6f4, mxf4nvf4): B scale-factor id at [4,6), A/B format as above,
 // scale format at 23 (0 = UE4M3, 1 = UE8M0), M >> 4 at [24,29), A scale-factor id at [29,31).
 __host__ __device__ constexpr uint32_t idesc_block_scaled(uint32_t a_fmt, uint32_t b_fmt, uint32_t sf_fmt, uint32_t m, uint32_t n) {

@@ -62,20 +62,136 @@ inline void gemm_fp8(const BlasHandle& h, float alpha, const MatrixDesc<E4M3>& a
                             reinterpret_cast<const uint8_t*>(b_nk.ptr), b_nk.ld, scale_a_dev, scale_b_dev, beta, c_bf16.ptr, c_bf16.ld));
 }
 
-// Int4GemmConfig (precision/int_ops.rs:215-355): validate() keeps the reference's rules.
-struct Int4GemmConfig {
-    uint32_t m, n, k, group_size;
-    void validate() const {
-        if (m == 0 || n == 0 || k == 0) throw BlasError(OXQ_ERR_INVALID_DIMENSION, "INT4 GEMM dimensions must be non-zero");
-        if (k % 8 != 0) throw BlasError(OXQ_ERR_INVALID_ARGUMENT, "K must be a multiple of 8 for INT4 packing");
-        if (!(group_size == 32 || group_size == 64 || group_size == 128 || group_size == 256))
-            throw BlasError(OXQ_ERR_INVALID_ARGUMENT, "invalid group size");
+// ---- gemm<T> with the reference's operand forms --------------------------------------------------------------------
+// gemm(handle, trans_a, trans_b, alpha, a, b, beta, c) of gemm_api.rs:73-138: op(A) is [m x k], op(B) is [k x n], every
+// matrix row- or column-major.  Validation order and error variants follow gemm_api.rs:84-137: zero dimensions ->
+// InvalidDimension, inner dimensions that disagree -> DimensionMismatch, C of another shape -> DimensionMismatch.  The
+// library's kernels take either index of an operand as the contiguous one, so no combination is refused and nothing is
+// copied; a column-major C is computed as the row-major C^T = op(B)^T * op(A)^T.  Per-tensor scales (device floats) are
+// the E4M3 operands' dequantisation factors; C is bf16.
+namespace detail {
+// true when the operand's row index (of op(X)) is the contiguous one in memory
+inline bool rows_contiguous(Transpose t, Layout l) { return (t == Transpose::Trans) == (l == Layout::RowMajor); }
+inline uint32_t op_rows(Transpose t, uint32_t rows, uint32_t cols) { return t == Transpose::NoTrans ? rows : cols; }
+inline uint32_t op_cols(Transpose t, uint32_t rows, uint32_t cols) { return t == Transpose::NoTrans ? cols : rows; }
+}  // namespace detail
+
+inline void gemm(const BlasHandle& h, Transpose trans_a, Transpose trans_b, float alpha, const MatrixDesc<E4M3>& a, const float* scale_a_dev,
+                 const MatrixDesc<E4M3>& b, const float* scale_b_dev, float beta, MatrixDescMut<uint16_t>& c_bf16) {
+    const uint32_t m = detail::op_rows(trans_a, a.rows, a.cols), k = detail::op_cols(trans_a, a.rows, a.cols);
+    const uint32_t kb = detail::op_rows(trans_b, b.rows, b.cols), n = detail::op_cols(trans_b, b.rows, b.cols);
+    if (m == 0 || n == 0 || k == 0) throw BlasError(OXQ_ERR_INVALID_DIMENSION, "GEMM dimensions must be non-zero");
+    if (k != kb) throw BlasError(OXQ_ERR_DIMENSION_MISMATCH, "inner dimensions of op(A) and op(B) do not match");
+    if (c_bf16.rows != m || c_bf16.cols != n) throw BlasError(OXQ_ERR_DIMENSION_MISMATCH, "C shape does not match the GEMM result");
+    // op(A) [m x k]: MN-major when m is the contiguous index; op(B) [k x n]: K-major when k (its row index) is contiguous
+    const int a_major = detail::rows_contiguous(trans_a, a.layout) ? OXQ_OP_MN_MAJOR : OXQ_OP_K_MAJOR;
+    const int b_major = detail::rows_contiguous(trans_b, b.layout) ? OXQ_OP_K_MAJOR : OXQ_OP_MN_MAJOR;
+    const uint8_t* ap = reinterpret_cast<const uint8_t*>(a.ptr);
+    const uint8_t* bp = reinterpret_cast<const uint8_t*>(b.ptr);
+    if (c_bf16.layout == Layout::RowMajor) {
+        h.check(oxq_gemm_fp8_op(h.raw(), m, n, k, alpha, ap, a.ld, a_major, bp, b.ld, b_major, scale_a_dev, scale_b_dev, beta, c_bf16.ptr, c_bf16.ld));
+    } else {
+        // C^T [n x m] row-major = op(B)^T [n x k] * op(A)^T [k x m]: B takes A's place with the meaning of its flag kept
+        // (K-major stays "k contiguous"), and likewise A
+        h.check(oxq_gemm_fp8_op(h.raw(), n, m, k, alpha, bp, b.ld, b_major, ap, a.ld, a_major, scale_b_dev, scale_a_dev, beta, c_bf16.ptr, c_bf16.ld));
+    }
+}
+
+// ---- low-precision GEMM configurations ----------------------------------------------------------------------------
+// SmVersion of the reference's PTX layer (crates/oxicuda-ptx/src/arch.rs:20-37), ordered.
+enum class SmVersion { Sm75 = 75, Sm80 = 80, Sm86 = 86, Sm89 = 89, Sm90 = 90, Sm90a = 91, Sm100 = 100, Sm120 = 120 };
+enum class AccType { I32, F32 };
+
+// Int8GemmConfig (precision/int_ops.rs:79-125).
+struct Int8GemmConfig {
+    uint32_t m, n, k;
+    Layout layout_a = Layout::RowMajor, layout_b = Layout::RowMajor;
+    AccType accumulator = AccType::I32;
+    static constexpr uint32_t ELEMENT_BYTES = 1;
+    static bool is_available(SmVersion sm) { return sm >= SmVersion::Sm75; }
+    void validate(SmVersion sm) const {
+        if (m == 0 || n == 0 || k == 0) throw BlasError(OXQ_ERR_INVALID_DIMENSION, "INT8 GEMM dimensions must be non-zero");
+        if (k % 4 != 0) throw BlasError(OXQ_ERR_INVALID_DIMENSION, "INT8 GEMM K dimension must be a multiple of 4 for dp4a, got k=" + std::to_string(k));
+        if (!is_available(sm)) throw BlasError(OXQ_ERR_UNSUPPORTED_OPERATION, "INT8 dp4a requires Turing+ (sm_75)");
     }
 };
+
+// Int4GemmConfig (precision/int_ops.rs:215-281).
+struct Int4GemmConfig {
+    uint32_t m, n, k;
+    Layout layout_a = Layout::RowMajor, layout_b = Layout::RowMajor;
+    uint32_t group_size = 128;
+    static constexpr uint32_t PACKED_ELEMENT_BYTES = 4, VALUES_PER_U32 = 8;
+    static bool is_available(SmVersion sm) { return sm >= SmVersion::Sm75; }
+    void validate(SmVersion sm) const {
+        if (m == 0 || n == 0 || k == 0) throw BlasError(OXQ_ERR_INVALID_DIMENSION, "INT4 GEMM dimensions must be non-zero");
+        if (k % 8 != 0) throw BlasError(OXQ_ERR_INVALID_DIMENSION, "INT4 GEMM K dimension must be a multiple of 8 for packing, got k=" + std::to_string(k));
+        if (group_size == 0 || (group_size & (group_size - 1)) != 0)
+            throw BlasError(OXQ_ERR_INVALID_ARGUMENT, "INT4 group_size must be a positive power of 2, got " + std::to_string(group_size));
+        if (k % group_size != 0) throw BlasError(OXQ_ERR_INVALID_ARGUMENT, "INT4 group_size must divide K evenly");
+        if (!is_available(sm)) throw BlasError(OXQ_ERR_UNSUPPORTED_OPERATION, "INT4 GEMM requires Turing+ (sm_75)");
+    }
+};
+
+// MicroScalingConfig (precision/fp4_fp6_ops.rs:190-225).
+enum class ScalingFormat { E8M0, Fp16, Fp32 };
+enum class ScalingGranularity { PerTensor, PerChannel, PerBlock };
+struct MicroScalingConfig {
+    uint32_t block_size = 32;
+    ScalingFormat scaling_format = ScalingFormat::Fp32;
+    ScalingGranularity scaling_granularity = ScalingGranularity::PerBlock;
+    void validate() const {
+        if (!(block_size == 32 || block_size == 64 || block_size == 128))
+            throw BlasError(OXQ_ERR_INVALID_ARGUMENT, "MicroScaling block_size must be one of [32, 64, 128], got " + std::to_string(block_size));
+    }
+    uint32_t num_scales(uint32_t num_elements) const {
+        switch (scaling_granularity) {
+            case ScalingGranularity::PerTensor: return 1;
+            case ScalingGranularity::PerChannel: return num_elements;
+            default: return (num_elements + block_size - 1) / block_size;
+        }
+    }
+};
+
+// Fp4GemmConfig (precision/fp4_fp6_ops.rs:337-395).
+enum class Fp4Format { E2M1, Int4 };
+enum class SubByteAccumulator { F16, F32 };
+struct Fp4GemmConfig {
+    uint32_t m, n, k;
+    Fp4Format format = Fp4Format::E2M1;
+    SubByteAccumulator accumulator = SubByteAccumulator::F32;
+    MicroScalingConfig micro_scaling;
+    SmVersion sm_version = SmVersion::Sm100;
+    static constexpr SmVersion MIN_SM = SmVersion::Sm100;
+    void validate() const {
+        if (m == 0 || n == 0 || k == 0) throw BlasError(OXQ_ERR_INVALID_DIMENSION, "FP4 GEMM dimensions must be non-zero");
+        if (sm_version < MIN_SM) throw BlasError(OXQ_ERR_UNSUPPORTED_OPERATION, "FP4 Tensor Cores require Blackwell+ (sm_100)");
+        if (k % 2 != 0) throw BlasError(OXQ_ERR_INVALID_DIMENSION, "FP4 GEMM K dimension must be even for packing, got k=" + std::to_string(k));
+        micro_scaling.validate();
+    }
+    std::string kernel_name() const {
+        return std::string("fp4_") + (format == Fp4Format::E2M1 ? "e2m1" : "int4") + "_gemm_" + std::to_string(m) + "x" + std::to_string(n) + "x" +
+               std::to_string(k) + "_" + (accumulator == SubByteAccumulator::F32 ? "f32" : "f16");
+    }
+};
+
+// The GEMMs those configurations describe, over the library's kernels.  The quantised operand is the weight W[N x K]
+// (the reference's generators quantise "A"; the roles are exchanged, C^T = W * X^T).
+inline void gemm_w8a8(const BlasHandle& h, const Int8GemmConfig& cfg, const int8_t* x, const int8_t* w, const float* sx_rows, const float* sw_rows,
+                      void* y_bf16) {
+    cfg.validate(SmVersion::Sm100);
+    h.check(oxq_gemm_w8a8(h.raw(), cfg.m, cfg.n, cfg.k, x, cfg.k, w, cfg.k, sx_rows, sw_rows, y_bf16, cfg.n));
+}
 inline void gemm_w4a16(const BlasHandle& h, const Int4GemmConfig& cfg, const void* x_bf16, const uint32_t* codes, const uint16_t* scales_f16,
                        const uint32_t* zeros, void* y_bf16, void* workspace, size_t workspace_bytes) {
-    cfg.validate();
+    cfg.validate(SmVersion::Sm100);
     h.check(oxq_gemm_w4a16(h.raw(), cfg.m, cfg.n, cfg.k, x_bf16, codes, scales_f16, zeros, (int)cfg.group_size, y_bf16, workspace, workspace_bytes));
+}
+// NVFP4 operands (E2M1 codes, UE4M3 scale per 16, f32 tensor scale) as produced by oxq_nvfp4_quant
+inline void gemm_nvfp4(const BlasHandle& h, const Fp4GemmConfig& cfg, const uint8_t* x, const uint8_t* sfx_mma, const float* gx, const uint8_t* w,
+                       const uint8_t* sfw_mma, const float* gw, void* y_bf16) {
+    cfg.validate();
+    h.check(oxq_gemm_nvfp4(h.raw(), cfg.m, cfg.n, cfg.k, x, sfx_mma, gx, w, sfw_mma, gw, y_bf16, cfg.n));
 }
 
 }  // namespace oxicuda_blas

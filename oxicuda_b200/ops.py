@@ -605,6 +605,23 @@ def gemm_bf16_ex(alpha: float, x, w, beta: float, y: torch.Tensor):
     return y
 
 
+OP_K_MAJOR, OP_MN_MAJOR = 0, 1
+
+
+def gemm_fp8_op(m: int, n: int, k: int, alpha: float, a, a_major: int, b, b_major: int, sa, sb, beta: float, y: torch.Tensor):
+    """gemm's operand forms (crates/oxicuda-blas/src/level3/gemm_api.rs:73-82) for E4M3 operands: a is [m x k] (K-major) or
+    [k x m] (MN-major) in memory, b is [n x k] (K-major) or [k x n] (MN-major); y [m x n] bf16 is updated in place."""
+    handle(a.device.index).call("oxq_gemm_fp8_op", m, n, k, C.c_float(alpha), _p(a), a.stride(0), a_major, _p(b), b.stride(0), b_major,
+                                _p(sa), _p(sb), C.c_float(beta), _p(y), y.stride(0))
+    return y
+
+
+def gemm_bf16_op(m: int, n: int, k: int, alpha: float, a, a_major: int, b, b_major: int, beta: float, y: torch.Tensor):
+    handle(a.device.index).call("oxq_gemm_bf16_op", m, n, k, C.c_float(alpha), _p(a), a.stride(0), a_major, _p(b), b.stride(0), b_major,
+                                C.c_float(beta), _p(y), y.stride(0))
+    return y
+
+
 def gemm_fp8_swiglu(x_q, w_gu_q, sx, sw, out: torch.Tensor | None = None):
     """H = bf16(silu(g) * u); w_gu_q holds gate/up rows interleaved in blocks of 128 (see interleave_gate_up)."""
     m, k = x_q.shape

@@ -218,6 +218,66 @@ def test_gemm_alpha_beta(ops, orc, mnk, ab):
     _check(_bf16_to_np(y), ref.astype(np.float32), f"fp8 alpha/beta {mnk} {ab}")
 
 
+def _mn_major(t):
+    """[rows x k] -> the transposed matrix [k x rows] with its leading dimension padded to 16 bytes (a view of the padded buffer)."""
+    rows, k = t.shape
+    al = 16 // t.element_size()
+    ld = (rows + al - 1) // al * al
+    buf = torch.zeros((k, ld), dtype=t.dtype, device=t.device)
+    buf[:, :rows] = t.t()
+    return buf[:, :rows]
+
+
+@pytest.mark.parametrize("mnk", [(256, 512, 256), (300, 520, 384), (1024, 1024, 1024), (64, 264, 2048), (2048, 2304, 512), (129, 136, 48)])
+@pytest.mark.parametrize("majors", [(0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("kind", ["fp8", "bf16"])
+def test_gemm_operand_forms(ops, orc, mnk, majors, kind):
+    """gemm's trans_a / trans_b / layout forms: A stored [M x K] or [K x M], B stored [N x K] or [K x N] (the reference's default
+    NoTrans, NoTrans call on row-major matrices is A K-major, B MN-major), against the same oracle as the K-major form, with
+    alpha and beta."""
+    m, n, k = mnk
+    a_mn, b_mn = majors
+    ab = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 0))
+    bb = orc.f32_to_bf16_bits(orc.gaussian((n, k), 1.0, 1))
+    y0b = orc.f32_to_bf16_bits(orc.gaussian((m, n), 3.0, 2))
+    a, b = bf16_dev(ab), bf16_dev(bb)
+    y = bf16_dev(y0b).clone()
+    alpha, beta = 0.5, 1.0
+    if kind == "fp8":
+        qa, sa = ops.fp8_quant_dynamic(a)
+        qb, sb = ops.fp8_quant_dynamic(b)
+        am = _mn_major(qa) if a_mn else qa                      # [K x M] when MN-major
+        bm = _mn_major(qb) if b_mn else qb                      # [K x N] when MN-major
+        ops.gemm_fp8_op(m, n, k, alpha, am, a_mn, bm, b_mn, sa[1:], sb[1:], beta, y)
+        acc = orc.e4m3_to_f32(qa.cpu().numpy()).astype(np.float64) @ orc.e4m3_to_f32(qb.cpu().numpy()).astype(np.float64).T
+        acc *= float(sa[1]) * float(sb[1])
+    else:
+        am = _mn_major(a) if a_mn else a
+        bm = _mn_major(b) if b_mn else b
+        ops.gemm_bf16_op(m, n, k, alpha, am, a_mn, bm, b_mn, beta, y)
+        acc = orc.bf16_bits_to_f32(ab).astype(np.float64) @ orc.bf16_bits_to_f32(bb).astype(np.float64).T
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    ref = alpha * acc + beta * orc.bf16_bits_to_f32(y0b)
+    _check(_bf16_to_np(y), ref.astype(np.float32), f"{kind} operand forms {mnk} {majors}")
+
+
+def test_gemm_operand_forms_errors(ops):
+    from oxicuda_b200.errors import BlasError
+    a = torch.zeros((64, 128), dtype=torch.uint8, device="cuda")
+    y = torch.zeros((64, 64), dtype=torch.bfloat16, device="cuda")
+    one = torch.ones(1, device="cuda")
+    with pytest.raises(BlasError) as e:                      # unknown layout flag
+        ops.gemm_fp8_op(64, 64, 128, 1.0, a, 2, a, 0, one, one, 0.0, y)
+    assert e.value.variant == "InvalidArgument"
+    with pytest.raises(BlasError) as e:                      # B said to be [K x N] with N = 256 but only 128 elements per row
+        ops.gemm_fp8_op(64, 256, 64, 1.0, a[:, :64].contiguous(), 0, a, 1, one, one, 0.0, torch.zeros((64, 256), dtype=torch.bfloat16, device="cuda"))
+    assert e.value.variant == "InvalidDimension"
+    with pytest.raises(BlasError) as e:                      # zero dimension (gemm_api.rs:88-92)
+        ops.gemm_fp8_op(0, 64, 128, 1.0, a, 0, a, 0, one, one, 0.0, y)
+    assert e.value.variant == "InvalidDimension"
+
+
 # ------------------------------------------------------------------------------------------- W4A16
 
 @pytest.mark.parametrize("m", [1, 8, 32, 5, 17, 9, 16])

@@ -21,6 +21,20 @@ def _build(tmp_path):
     return exe
 
 
+def test_host_config_types(tmp_path):
+    """The configuration types' validate() rules (the reference's own tests restated in tests/cpp/host_config_test.cpp): host only."""
+    from oxicuda_b200 import _build
+    _build.build()
+    exe = str(tmp_path / "host_config_test")
+    libdir = os.path.join(ROOT, "oxicuda_b200", "lib")
+    cmd = ["/usr/bin/g++", "-std=c++17", "-O1", "-I/usr/local/cuda/include", os.path.join(ROOT, "tests", "cpp", "host_config_test.cpp"),
+           "-o", exe, "-L" + libdir, "-loxq_b200", "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath," + libdir]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=60)
+    assert run.returncode == 0, f"check {run.returncode} failed: {run.stdout} {run.stderr}"
+
+
 def test_host_mirror_compiles_and_links(tmp_path):
     exe = _build(tmp_path)
     assert os.path.exists(exe)

@@ -22,7 +22,7 @@
  *
  * Status codes: 0 = OK; 1..9 mirror QuantError (crates/oxicuda-quant/src/error.rs:10-58);
  * 10..19 mirror BlasError (crates/oxicuda-blas/src/error.rs:16-59); 100 = a bounded device-side
- * wait expired; 1000 + n = cudaError_t n.
+ * wait expired; 1000 + n = cudaError_t n; 2000 + n = ncclResult_t n.
  */
 #ifndef OXQ_H_
 #define OXQ_H_
@@ -61,7 +61,8 @@ enum {
     OXQ_ERR_INVALID_ARGUMENT = 15,
     /* device side */
     OXQ_ERR_DEVICE_TIMEOUT = 100,
-    OXQ_ERR_CUDA_BASE = 1000
+    OXQ_ERR_CUDA_BASE = 1000,
+    OXQ_ERR_NCCL_BASE = 2000           /* 2000 + n = ncclResult_t n */
 };
 
 /* element types of floating-point tensors handed to the quantizers */
@@ -341,6 +342,47 @@ OXQ_API int32_t oxq_multimem_all_reduce_bf16(oxq_handle* h, void* multicast_ptr,
 /* The same over a column block of a row-major bf16 matrix ([rows x cols] at multicast_ptr, leading dimension ld elements):
  * rank r reduces rows [r * rows / world, (r + 1) * rows / world).  cols and ld multiples of 8, rows a multiple of world. */
 OXQ_API int32_t oxq_multimem_all_reduce_bf16_2d(oxq_handle* h, void* multicast_ptr, int64_t rows, int64_t cols, int64_t ld, int rank, int world);
+
+/* ---- tensor-parallel layer behind the C ABI --------------------------------------------------------------------------
+ * ColumnLinear / RowLinear / SwiGluFfn of the reference (crates/oxicuda-dist-infer/src/tensor_parallel/column_parallel.rs:103-204,
+ * row_parallel.rs:97-223, crates/oxicuda-lm/src/layer/ffn.rs:202-254) hold f32 weights and add the ranks' partial sums on the
+ * host.  Here every rank is one process with one GPU, holds its shard quantised, and the partial sums meet in one NCCL
+ * all-reduce over NVLink.
+ *   oxq_comm_unique_id  rank 0 makes the 128-byte identifier (ncclGetUniqueId) and hands it to the other ranks out of band
+ *   oxq_comm_init       every rank joins with the same identifier (ncclCommInitRank on the handle's device); one communicator
+ *                       per handle; the handle's stream carries the collectives
+ *   oxq_comm_destroy    leaves the communicator (oxq_handle_destroy does it as well)
+ * NCCL is bound at run time: the libnccl.so.2 the process already holds, else the one named by OXQ_NCCL_LIB, else the
+ * loader's.  Without one, these calls return UnsupportedOperation; a handle without a communicator is a world of one rank. */
+OXQ_API int32_t oxq_comm_unique_id(void* id_out_128);
+OXQ_API int32_t oxq_comm_init(oxq_handle* h, const void* id_128, int nranks, int rank);
+OXQ_API int32_t oxq_comm_destroy(oxq_handle* h);
+OXQ_API int32_t oxq_comm_info(const oxq_handle* h, int* nranks_out, int* rank_out, int* nccl_version_out);
+/* RowLinear::all_reduce (row_parallel.rs:199-223) and ColumnLinear::all_gather (column_parallel.rs:181-204) on device buffers,
+ * asynchronous on the handle's stream.  The gather is rank-major: rank r's numel_local elements land at [r * numel_local, ...). */
+OXQ_API int32_t oxq_all_reduce_bf16(oxq_handle* h, void* y_bf16_dev, int64_t numel);
+OXQ_API int32_t oxq_all_gather_bf16(oxq_handle* h, const void* local_bf16_dev, int64_t numel_local, void* gathered_bf16_dev);
+/* One rank's shard of the SwiGLU MLP.  inter_local = intermediate / nranks rows of the gate and of the up weight (interleaved in
+ * blocks of 128 rows: [gate 0..127][up 0..127][gate 128..255]..., so w_gu is [2 * inter_local x hidden]) and the matching
+ * inter_local input columns of the down weight ([hidden x inter_local]).
+ *   OXQ_TP_FP8    w_gu / w_down are E4M3 bytes, w_gu_scales / w_down_scales one f32 each; the zeros are unused.  x is quantised
+ *                 per tensor, h per shard (no maximum crosses ranks), both on the fly.
+ *   OXQ_TP_W4A16  w_gu / w_down are uint4 codes (8 per u32, group 128 along K), the scales f16 per group, the zeros packed
+ *                 nibbles: the tensors of oxq_int4g_quant_pack.
+ * y_bf16 [m x hidden] receives the rank's partial and, with reduce != 0, the sum over the ranks (in place, bf16, one
+ * all-reduce).  The workspace (oxq_mlp_swiglu_tp_workspace_bytes, 256-byte aligned) holds the intermediates; for
+ * OXQ_TP_W4A16 it must be zero-filled once before its first use (the W4A16 decode kernels keep their partial sums there and
+ * leave them zero).  Nothing is allocated and nothing synchronises. */
+enum { OXQ_TP_FP8 = 0, OXQ_TP_W4A16 = 1 };
+typedef struct oxq_tp_mlp_weights {
+    int32_t variant;
+    int64_t hidden, inter_local;
+    const void* w_gu; const void* w_gu_scales; const void* w_gu_zeros;
+    const void* w_down; const void* w_down_scales; const void* w_down_zeros;
+} oxq_tp_mlp_weights;
+OXQ_API int32_t oxq_mlp_swiglu_tp_workspace_bytes(int variant, int64_t m, int64_t hidden, int64_t inter_local, size_t* bytes_out);
+OXQ_API int32_t oxq_mlp_swiglu_tp(oxq_handle* h, const oxq_tp_mlp_weights* w, int64_t m, const void* x_bf16_dev, void* y_bf16_dev,
+                          void* workspace_dev, size_t workspace_bytes, int reduce);
 
 /* ---- GPTQ weight preparation -------------------------------------------------------------------------------------
  * GptqQuantizer::quantize_layer (crates/oxicuda-quant/src/scheme/gptq.rs:133-257): dampen the Hessian by

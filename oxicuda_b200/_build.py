@@ -62,7 +62,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             if res.returncode:
                 raise RuntimeError("nvcc failed for " + cmd[-3])
     if force or jobs or _stale(LIB_PATH, objs):
-        cmd = [nvcc, "-shared", "-o", LIB_PATH] + objs + ["-cudart", "static", "-Xlinker", "--no-undefined"]
+        cmd = [nvcc, "-shared", "-o", LIB_PATH] + objs + ["-cudart", "static", "-ldl", "-Xlinker", "--no-undefined"]
         res = subprocess.run(cmd, capture_output=True, text=True, env=env)
         if res.returncode:
             print(res.stdout + res.stderr)

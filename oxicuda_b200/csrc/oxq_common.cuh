@@ -16,6 +16,8 @@ struct oxq_handle {
     int cc_major, cc_minor;
     int32_t* dev_status;      // one word in device memory, written by bounded waits that expire
     uint32_t* dev_scratch;    // 16 words after the status word: reduction cells that kernels leave zeroed (absmax)
+    void* comm;               // ncclComm_t of oxq_comm_init (tensor-parallel entry points), or null
+    int nranks, rank;
     char last_error[256];
 };
 

@@ -27,6 +27,11 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ uint32_t sub_bf16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
 __device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
     uint4 u;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(p));
@@ -218,9 +223,8 @@ __global__ void __launch_bounds__(W4_THREADS) w4a16_decode_kernel(const W4Params
 // nothing is shared: lane (g, t) streams rows g and g + 8 (16 bytes = 32 codes per load, chunks of four spans
 // of 128 K, the next chunk requested before the current one is multiplied), reads the matching 8 activations of
 // batch row g straight from global memory (they stay in L1) and permutes them in registers into the K order of
-// the unpacked codes.  The MMAs multiply 128 + code; a second chain of MMAs with an all-ones row operand gives
-// every lane the sum of the activations of the span, which takes the 128 and the zero-point back out:
-//   sum_k (c_k - z) x_k = sum_k (128 + c_k) x_k - (128 + z) sum_k x_k
+// the unpacked codes.  0x4300 | nibble is the bf16 value 128 + code; a packed subtraction of 128 + z leaves the exact
+// integer code - z in both halves, so the MMAs multiply the dequantised integers and only the group's scale is left.
 constexpr int GV_WARPS = 8;
 constexpr int GV_CHUNK = 4;            // spans per register buffer (the vector scale loads assume 4)
 
@@ -311,8 +315,13 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 2) w4a16_gemv_kernel(const GvPa
         for (int j = 0; j < GV_CHUNK; j++) {
             const int s = s0 + j;
             if (s < s_hi) {
-                float part[4] = {0.0f, 0.0f, 0.0f, 0.0f}, xs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 const uint32_t wwa[4] = {cur_a[j].x, cur_a[j].y, cur_a[j].z, cur_a[j].w}, wwb[4] = {cur_b[j].x, cur_b[j].y, cur_b[j].z, cur_b[j].w};
+                // bf16x2 (128 + z): one packed subtraction per code pair takes the 128 and the zero-point out, exactly (all
+                // values are small integers).  The legacy tensor path is the scarce unit of this kernel on sm_100 -- an
+                // m16n8k16 occupies it for 8 cycles per SM -- so the sums of the activations are not formed by extra MMAs.
+                const uint32_t za = cur_sa[j] >> 16, zb = cur_sb[j] >> 16;
+                const uint32_t zz_a = 0x43004300u | za | (za << 16), zz_b = 0x43004300u | zb | (zb << 16);
                 // the span's 32 activations of batch row g (L1-resident), requested here and not earlier: hoisting the
                 // requests of all spans to the top would cost 64 registers
                 const uint4* xp = reinterpret_cast<const uint4*>(xr + (size_t)s * 128);
@@ -331,22 +340,18 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 2) w4a16_gemv_kernel(const GvPa
                     uint32_t ra[4], rb4[4];
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
-                        ra[q] = ((wwa[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u;           // bf16x2 (128 + c, 128 + c')
-                        rb4[q] = ((wwb[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u;
+                        ra[q] = sub_bf16x2(((wwa[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u, zz_a);   // bf16x2 (c - z, c' - z)
+                        rb4[q] = sub_bf16x2(((wwb[i] >> (4 * q)) & 0x000F000Fu) | 0x43004300u, zz_b);
                     }
                     mma_bf16_16816(part, ra[0], rb4[0], ra[1], rb4[1], b0, b1);
                     mma_bf16_16816(part, ra[2], rb4[2], ra[3], rb4[3], b2, b3);
-                    constexpr uint32_t ONES = 0x3F803F80u;                                    // bf16x2 (1, 1)
-                    mma_bf16_16816(xs, ONES, ONES, ONES, ONES, b0, b1);
-                    mma_bf16_16816(xs, ONES, ONES, ONES, ONES, b2, b3);
                 }
                 const float sa = __half2float(__ushort_as_half((unsigned short)(cur_sa[j] & 0xFFFFu)));
                 const float sb = __half2float(__ushort_as_half((unsigned short)(cur_sb[j] & 0xFFFFu)));
-                const float za = 128.0f + (float)(cur_sa[j] >> 16), zb = 128.0f + (float)(cur_sb[j] >> 16);
-                total[0] += sa * fmaf(-za, xs[0], part[0]);
-                total[1] += sa * fmaf(-za, xs[1], part[1]);
-                total[2] += sb * fmaf(-zb, xs[2], part[2]);
-                total[3] += sb * fmaf(-zb, xs[3], part[3]);
+                total[0] = fmaf(sa, part[0], total[0]);
+                total[1] = fmaf(sa, part[1], total[1]);
+                total[2] = fmaf(sb, part[2], total[2]);
+                total[3] = fmaf(sb, part[3], total[3]);
             }
         }
         if (PIPE) {
@@ -681,7 +686,7 @@ int32_t oxq_gemm_w4a16_static(void* cuda_stream, int64_t m, int64_t n, int64_t k
     if (e != cudaSuccess) return OXQ_ERR_CUDA_BASE + (int32_t)e;
     oxq_handle tmp;
     tmp.device = dev; tmp.stream = (cudaStream_t)cuda_stream; tmp.sm_count = d.sm_count;
-    tmp.cc_major = d.cc_major; tmp.cc_minor = d.cc_minor; tmp.dev_status = nullptr; tmp.dev_scratch = nullptr; tmp.last_error[0] = 0;
+    tmp.cc_major = d.cc_major; tmp.cc_minor = d.cc_minor; tmp.dev_status = nullptr; tmp.dev_scratch = nullptr; tmp.comm = nullptr; tmp.nranks = 1; tmp.rank = 0; tmp.last_error[0] = 0;
     return w4a16_impl(&tmp, m, n, k, x, codes, scales, zeros, group, y, d.scratch, sums + counters, 0);
 }
 

@@ -24,7 +24,7 @@ const char* oxq_status_name(int32_t s) {
         case OXQ_ERR_LAUNCH_FAILED: return "LaunchFailed";
         case OXQ_ERR_INVALID_ARGUMENT: return "InvalidArgument";
         case OXQ_ERR_DEVICE_TIMEOUT: return "DeviceTimeout";
-        default: return s >= OXQ_ERR_CUDA_BASE ? "Cuda" : "Unknown";
+        default: return s >= OXQ_ERR_NCCL_BASE ? "Nccl" : (s >= OXQ_ERR_CUDA_BASE ? "Cuda" : "Unknown");
     }
 }
 
@@ -48,6 +48,7 @@ int32_t oxq_handle_create(int device, void* cuda_stream, oxq_handle** out) {
     h->cc_major = prop.major;
     h->cc_minor = prop.minor;
     h->last_error[0] = 0;
+    h->comm = nullptr; h->nranks = 1; h->rank = 0;
     h->dev_status = nullptr;
     // The only allocation the library ever makes: 128 bytes per handle (status word + self-cleaning reduction cells).
     h->dev_scratch = nullptr;
@@ -61,6 +62,7 @@ int32_t oxq_handle_create(int device, void* cuda_stream, oxq_handle** out) {
 
 int32_t oxq_handle_destroy(oxq_handle* h) {
     if (!h) return OXQ_ERR_INVALID_ARGUMENT;
+    if (h->comm) oxq_comm_destroy(h);
     if (h->dev_status) cudaFree(h->dev_status);
     delete h;
     return OXQ_OK;

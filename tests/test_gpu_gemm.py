@@ -341,7 +341,8 @@ def test_gemm_w4a16_scales_at_an_odd_offset(ops, orc):
     w = orc.gaussian((n, k), 0.02, 0)
     c, s, z = ops.int4g_quant_pack(to_dev(w), 128)
     xb = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 1))
-    want = ops.gemm_w4a16(bf16_dev(xb), c, s, z, 128)
+    want = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")              # the same kernel (no workspace), aligned scales
+    ops.handle().call("oxq_gemm_w4a16", m, n, k, ops._p(bf16_dev(xb)), ops._p(c), ops._p(s), ops._p(z), 128, ops._p(want), ops._p(None), 0)
     for off in (1, 2, 3):
         buf = torch.zeros(s.numel() + 8, dtype=torch.float16, device="cuda")
         shifted = buf[off:off + s.numel()]

@@ -278,3 +278,64 @@ def test_column_then_row_linear_nccl_two_gpus():
         assert p.exitcode == 0
     for _, eh, ey in res:
         assert eh <= 1e-2 and ey <= 2e-2
+
+
+# ---- the layer through the C ABI alone -------------------------------------------------------------------------------
+
+def _nccl_lib_dir():
+    import importlib.util
+    spec = importlib.util.find_spec("nvidia.nccl")
+    if spec is None or not spec.submodule_search_locations:
+        return None
+    d = os.path.join(list(spec.submodule_search_locations)[0], "lib")
+    return d if os.path.exists(os.path.join(d, "libnccl.so.2")) else None
+
+
+@pytest.mark.parametrize("m", [4, 300])
+def test_tp_mlp_c_abi_two_ranks(tmp_path, orc, m):
+    """oxq_comm_init + oxq_mlp_swiglu_tp from a C++ program, one process per rank and GPU, no Python in the ranks: each rank's
+    partial equals, bit for bit, what the Python layer computes for the same shard (whose parity with the oracle the tests
+    above establish), both ranks hold the same reduced result, and it is the bf16 sum of the two partials."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import subprocess
+    from oxicuda_b200 import _build
+    from oxicuda_b200.dist_infer import TpSwiGluMlp, interleave_gate_up
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    libdir = os.path.join(root, "oxicuda_b200", "lib")
+    exe = str(tmp_path / "tp_mlp_test")
+    cmd = ["/usr/bin/g++", "-std=c++17", "-O1", "-I/usr/local/cuda/include", os.path.join(root, "tests", "cpp", "tp_mlp_test.cpp"),
+           "-o", exe, "-L" + libdir, "-loxq_b200", "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath," + libdir]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    hidden, inter, tp = 512, 2048, 2
+    il = inter // tp
+    wg, wu, wd = _weights(orc, hidden, inter)
+    xb = orc.f32_to_bf16_bits(orc.gaussian((m, hidden), 1.0, 1))
+    xb.tofile(str(tmp_path / "x.bin"))
+    x = bf16_dev(xb)
+    want_parts = []
+    for r in range(tp):
+        g, u = torch.from_numpy(wg[r * il:(r + 1) * il]), torch.from_numpy(wu[r * il:(r + 1) * il])
+        d = torch.from_numpy(np.ascontiguousarray(wd[:, r * il:(r + 1) * il]))
+        bf16_bits(interleave_gate_up(g, u).to(torch.bfloat16)).tofile(str(tmp_path / f"rank{r}_wgu.bin"))
+        bf16_bits(d.to(torch.bfloat16)).tofile(str(tmp_path / f"rank{r}_wd.bin"))
+        layer = TpSwiGluMlp(g.to(torch.bfloat16), u.to(torch.bfloat16), d.to(torch.bfloat16), "fp8", tp=tp, rank=r, already_sharded=True)
+        want_parts.append(bf16_bits(layer.forward_partial(x)))
+    env = dict(os.environ)
+    nccl_dir = _nccl_lib_dir()
+    if nccl_dir:
+        env["OXQ_NCCL_LIB"] = os.path.join(nccl_dir, "libnccl.so.2")
+    env["NCCL_NVLS_ENABLE"] = "0"
+    run = subprocess.run([exe, str(tmp_path), str(tp), str(m), str(hidden), str(il)], capture_output=True, text=True, timeout=600, env=env)
+    assert run.returncode == 0, f"rc={run.returncode} {run.stdout[-2000:]} {run.stderr[-2000:]}"
+    parts = [np.fromfile(str(tmp_path / f"rank{r}_partial.bin"), np.uint16).reshape(m, hidden) for r in range(tp)]
+    ys = [np.fromfile(str(tmp_path / f"rank{r}_y.bin"), np.uint16).reshape(m, hidden) for r in range(tp)]
+    for r in range(tp):
+        assert np.array_equal(parts[r], want_parts[r]), f"rank {r}: partial differs from the Python layer's"
+    assert np.array_equal(ys[0], ys[1])
+    total = orc.bf16_bits_to_f32(parts[0]) + orc.bf16_bits_to_f32(parts[1])                  # one addition: the bf16 rounding of the f32 sum
+    assert np.array_equal(ys[0], orc.f32_to_bf16_bits(total))
+    for r in range(tp):                                                                       # rank-major gather of the first 1024 elements
+        gth = np.fromfile(str(tmp_path / f"rank{r}_gather.bin"), np.uint16)
+        assert np.array_equal(gth, np.concatenate([parts[q].ravel()[:1024] for q in range(tp)]))

@@ -239,19 +239,21 @@ def time_region(torch, fn, steps, dist_on):
     return ms
 
 
-def timed_median(torch, fn, steps, dist_on, repeats=7, gap_s=0.05):
-    """`repeats` timed regions of exactly `steps` calls each, an idle gap before every region; returns (median ms per
-    step, stats).  One region of a few milliseconds is at the mercy of a single clock change, so it is repeated; the
-    gaps keep every region what the roofline denominator is: a burst on a GPU that was not already at its power cap
-    (back to back, 300 ms of FP8 GEMMs settle some 25 % lower, at the sustained clock -- `sustained_rate` measures that)."""
+def timed_median(torch, fn, steps, dist_on, repeats=7, gap_s=0.05, warm=5):
+    """`repeats` timed regions of exactly `steps` calls each; before every region an idle gap and then `warm` untimed
+    calls, so that each region is what a single run of this script times: warm-up launches followed at once by the timed
+    ones, on a GPU that is neither idling at low clocks nor already at its power cap (back to back, 300 ms of FP8 GEMMs
+    settle some 25 % lower, at the sustained clock -- `sustained_rate` measures that).  Returns (median ms per step, stats)."""
     regions = []
     for _ in range(repeats):
         time.sleep(gap_s)
+        for _ in range(warm):
+            fn()
         regions.append(time_region(torch, fn, steps, dist_on))
     per = sorted(r / steps for r in regions)
     med = statistics.median(per)
     return med, {"repeats": len(per), "median": med, "min": per[0], "max": per[-1], "spread": (per[-1] - per[0]) / med if med > 0 else 0.0,
-                 "protocol": f"{len(per)} regions of {steps} launches, {int(gap_s * 1e3)} ms idle before each"}
+                 "protocol": f"{len(per)} regions of {steps} launches, each after {int(gap_s * 1e3)} ms idle and {warm} untimed launches"}
 
 
 def sustained_rate(torch, fn, steps, total_ms=400.0):

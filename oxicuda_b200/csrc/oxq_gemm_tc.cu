@@ -386,9 +386,12 @@ constexpr int T2_STAGES = 7;
 constexpr int T2_STAGE_BYTES = 2 * BM * BKB;                      // 16 KB of X + 16 KB of W per CTA
 constexpr int T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + 2048;
 
-template <int KIND, int EPI>
+// GENERIC = false is the K-major / K-major kernel; GENERIC = true reads the operands' major-ness from the parameters (the
+// operand forms of gemm).  Two instantiations, so that the common form carries none of the other's address arithmetic.
+template <int KIND, int EPI, bool GENERIC = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
+    const bool a_mn = GENERIC && p.a_mn, b_mn = GENERIC && p.b_mn;
     constexpr int S = T2_STAGES;
     constexpr int BN2 = 256, BM2 = 256;
     extern __shared__ uint8_t smem_raw[];
@@ -430,6 +433,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
+            const int es_shift = p.esize == 2 ? 1 : 0;
             for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
                 const WorkItem wi = work_item(w, p.full_tiles, p.tail_split);
                 int tm, tn;
@@ -443,13 +447,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * T2_STAGE_BYTES);
                     const uint32_t full0 = mapa_shared(bar_full + 8 * stage, 0);
                     // K-major operand: one box of 128 rows x 128 bytes of K.  MN-major operand ([K x M] / [K x N] in memory):
-                    // `esize` boxes of (128 / esize) K rows x 128 bytes of M / N, one swizzle atom each, side by side.
-                    if (!p.a_mn) tma_load_2d_cg2(sm_a + stage * BM * BKB, &tm_a, kb * BKB, m0, full0);
+                    // `esize` boxes of (128 / esize) K rows x 128 bytes of M / N, one swizzle atom each, side by side
+                    // (esize is 1 or 2: the shifts below are the divisions by it).
+                    if (!a_mn) tma_load_2d_cg2(sm_a + stage * BM * BKB, &tm_a, kb * BKB, m0, full0);
                     else for (int j = 0; j < p.esize; j++)
-                        tma_load_2d_cg2(sm_a + stage * BM * BKB + j * (BM * BKB / p.esize), &tm_a, m0 * p.esize + j * 128, kb * (BKB / p.esize), full0);
-                    if (!p.b_mn) tma_load_2d_cg2(sm_b + stage * BM * BKB, &tm_b, kb * BKB, n0, full0);
+                        tma_load_2d_cg2(sm_a + stage * BM * BKB + j * ((BM * BKB) >> es_shift), &tm_a, (m0 << es_shift) + j * 128, kb * (BKB >> es_shift), full0);
+                    if (!b_mn) tma_load_2d_cg2(sm_b + stage * BM * BKB, &tm_b, kb * BKB, n0, full0);
                     else for (int j = 0; j < p.esize; j++)
-                        tma_load_2d_cg2(sm_b + stage * BM * BKB + j * (BM * BKB / p.esize), &tm_b, n0 * p.esize + j * 128, kb * (BKB / p.esize), full0);
+                        tma_load_2d_cg2(sm_b + stage * BM * BKB + j * ((BM * BKB) >> es_shift), &tm_b, (n0 << es_shift) + j * 128, kb * (BKB >> es_shift), full0);
                     if (++stage == S) { stage = 0; phase ^= 1; }
                 }
             }
@@ -461,21 +466,26 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             int stage = 0; uint32_t phase = 0;
             int acc = 0; uint32_t acc_phase = 0;
             bool ok = true;
+            // Per MMA (32 bytes of K) the start address moves 32 bytes along a K-major row, or 32 / esize rows of 128 bytes
+            // (whole 1024-byte row groups) down an MN-major tile; an MN-major tile wider than 128 bytes is `esize` atoms apart
+            // by the leading byte offset.  All of it is fixed per launch and kept out of the issue loop.
+            const uint32_t es_shift = p.esize == 2 ? 1u : 0u;
+            const uint32_t atom = (uint32_t)(BM * BKB) >> es_shift;
+            const uint32_t ka = a_mn ? ((4096u >> es_shift) >> 4) : 2u, kbs = b_mn ? ((4096u >> es_shift) >> 4) : 2u;
+            const uint64_t a_fixed = a_mn ? (smem_desc_mn_sw128(0, atom)) : smem_desc_sw128(0);
+            const uint64_t b_fixed = b_mn ? (smem_desc_mn_sw128(0, atom)) : smem_desc_sw128(0);
+            const uint32_t majors = idesc_majors((uint32_t)a_mn, (uint32_t)b_mn);
             for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
-                const uint32_t idesc = idesc_dense(cf, af, af, BM2, (uint32_t)work_item(w, p.full_tiles, p.tail_split).n_cols) |
-                                       idesc_majors((uint32_t)p.a_mn, (uint32_t)p.b_mn);
+                const uint32_t idesc = idesc_dense(cf, af, af, BM2, (uint32_t)work_item(w, p.full_tiles, p.tail_split).n_cols) | majors;
                 if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN2;
                 for (int kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(bar_full + 8 * stage, phase)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                     tc_fence_after();
-                    // each MMA consumes 32 bytes of K: 32 bytes further along a K-major row, or 32 / esize rows of 128 bytes
-                    // (whole 1024-byte row groups) further down an MN-major tile
-                    const uint32_t atom = (uint32_t)(BM * BKB / p.esize), kstep_mn = (uint32_t)(4096 / p.esize) >> 4;
-                    const uint64_t adesc = p.a_mn ? smem_desc_mn_sw128(sm_a + stage * BM * BKB, atom) : smem_desc_sw128(sm_a + stage * BM * BKB);
-                    const uint64_t bdesc = p.b_mn ? smem_desc_mn_sw128(sm_b + stage * BM * BKB, atom) : smem_desc_sw128(sm_b + stage * BM * BKB);
-                    const uint32_t ka = p.a_mn ? kstep_mn : 2u, kbs = p.b_mn ? kstep_mn : 2u;
+                    // descriptor = the launch's fixed fields + the stage's start address (bits [0, 14), in units of 16 bytes)
+                    const uint64_t adesc = a_fixed | (uint64_t)(((sm_a + stage * BM * BKB) & 0x3FFFFu) >> 4);
+                    const uint64_t bdesc = b_fixed | (uint64_t)(((sm_b + stage * BM * BKB) & 0x3FFFFu) >> 4);
 #pragma unroll
                     for (int k = 0; k < BKB / 32; k++) {
                         const uint64_t a = adesc + (uint64_t)(k * ka), b = bdesc + (uint64_t)(k * kbs);
@@ -561,25 +571,35 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
 // columns 0 and 256 (192 wide), A scales at 448, B scales at 464.  Scale factors travel as TMA tiles of
 // 512-byte chunks (a [chunks x 128] u32 view of the tiled scale array) so that, like the operands, they can
 // count their bytes on CTA 0's barrier.
-template <int KIND>
+// Two tile shapes.  256 x 192: two accumulators of 192 columns (the epilogue of a tile runs under the main loop of the next),
+// scale factors behind them.  256 x 256: every operand byte in shared memory feeds twice as many MMA columns per byte of W as
+// it costs to bring in (the shared-memory traffic per MMA cycle is what limits the 4-bit kind), but tensor memory then holds
+// one accumulator only (256 + 48 scale columns), so the main loop of the next tile waits for the epilogue; the epilogue is
+// spread over eight warps (two per lane quarter, 128 columns each) to keep that wait short.
+template <int KIND, int BN2_>
 struct Cfg2S {
     static constexpr int kSfChunks = KIND == KIND_MXF8 ? 1 : 4;
     static constexpr int kSfBytes = kSfChunks * 512;
-    static constexpr int BN2 = 192;
+    static constexpr int BN2 = BN2_;
+    static constexpr int kAcc = BN2 == 256 ? 1 : 2;                                // accumulator buffers
+    static constexpr int kEpiWarps = BN2 == 256 ? 8 : 4;
+    static constexpr int kThreads = 32 * (2 + kEpiWarps);
     static constexpr int kABytes = BM * BKB, kBBytes = (BN2 / 2) * BKB;
     static constexpr int kStageBytes = kABytes + kBBytes + 3 * kSfBytes;           // A, B half, SFA, 2 x SFB
     static constexpr int kStages = (SMEM_BUDGET - 2048) / kStageBytes > 8 ? 8 : (SMEM_BUDGET - 2048) / kStageBytes;
     static constexpr int kSmemBytes = kStages * kStageBytes + 2048;
-    static constexpr int kSfaCol = 448, kSfbCol = 464;
+    static constexpr int kSfaCol = BN2 == 256 ? 256 : 448, kSfbCol = kSfaCol + 16;
+    static_assert(BN2 == 192 || BN2 == 256, "tile widths of the CTA-pair block-scaled kernel");
 };
 
-template <int KIND>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+template <int KIND, int BN2_>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Cfg2S<KIND, BN2_>::kThreads, 1)
 gemm_tc2_scaled_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                        const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {
-    using C = Cfg2S<KIND>;
+    using C = Cfg2S<KIND, BN2_>;
     constexpr int S = C::kStages;
     constexpr int BN2 = C::BN2, BM2 = 256;
+    constexpr int ACC = C::kAcc, EW = C::kEpiWarps;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sm_a = base;
@@ -601,7 +621,7 @@ gemm_tc2_scaled_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 8); }
+        for (int a = 0; a < 2; a++) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 2 * EW); }
         fence_barrier_init();
         prefetch_tmap(&tm_a); prefetch_tmap(&tm_b); prefetch_tmap(&tm_sfa); prefetch_tmap(&tm_sfb);
     }
@@ -675,11 +695,13 @@ gemm_tc2_scaled_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
                 }
                 if (!ok) break;
                 tc_commit_cg2_mc(bar_tfull + 8 * acc, 3);
-                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+                if (++acc == ACC) { acc = 0; acc_phase ^= 1; }
             }
         }
     } else {
         const int quarter = warp & 3;
+        // with eight epilogue warps, warps 2-5 take the first half of the tile's columns and warps 6-9 the second
+        const int col_lo = EW == 8 ? ((warp - 2) >> 2) * (BN2 / 2) : 0, col_hi = EW == 8 ? col_lo + BN2 / 2 : BN2;
         int acc = 0; uint32_t acc_phase = 0;
         float tensor_scale = 1.0f;
         if (KIND == KIND_NVF4) tensor_scale = __ldg(p.s0) * __ldg(p.s1);
@@ -696,7 +718,7 @@ gemm_tc2_scaled_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
             const int row = m0 + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * 256;
 #pragma unroll 1
-            for (int c = 0; c < BN2 / 32; c++) {
+            for (int c = col_lo / 32; c < col_hi / 32; c++) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(t_row + c * 32, r);
                 tmem_ld_wait();
@@ -705,7 +727,7 @@ gemm_tc2_scaled_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * acc, 0));
-            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            if (++acc == ACC) { acc = 0; acc_phase ^= 1; }
         }
     }
 
@@ -805,7 +827,7 @@ static bool use_2cta_setting() {
     return v != 0;
 }
 
-template <int KIND, int EPI = EPI_SCALE>
+template <int KIND, int EPI = EPI_SCALE, bool GENERIC = false>
 static int32_t launch2(oxq_handle* h, const void* x, int64_t ldx_bytes, const void* w, int64_t ldw_bytes, GemmParams p) {
     CUtensorMap tm_a, tm_b;
     if (p.esize != 2) p.esize = 1;
@@ -821,7 +843,7 @@ static int32_t launch2(oxq_handle* h, const void* x, int64_t ldx_bytes, const vo
     static OxqPerDevice cluster_cache;
     int max_clusters = cluster_cache.get(h->device);
     if (max_clusters == 0) {
-        OXQ_CUDA(h, cudaFuncSetAttribute(gemm_tc2_kernel<KIND, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES));
+        OXQ_CUDA(h, cudaFuncSetAttribute(gemm_tc2_kernel<KIND, EPI, GENERIC>, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES));
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(h->sm_count & ~1, 1, 1);
         cfg.blockDim = dim3(NUM_THREADS, 1, 1);
@@ -831,7 +853,7 @@ static int32_t launch2(oxq_handle* h, const void* x, int64_t ldx_bytes, const vo
         attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
         cfg.attrs = &attr; cfg.numAttrs = 1;
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<KIND, EPI>, &cfg) != cudaSuccess || n < 1) n = h->sm_count / 2;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<KIND, EPI, GENERIC>, &cfg) != cudaSuccess || n < 1) n = h->sm_count / 2;
         max_clusters = n < h->sm_count / 2 ? n : h->sm_count / 2;
         cluster_cache.set(h->device, max_clusters);
     }
@@ -852,7 +874,7 @@ static int32_t launch2(oxq_handle* h, const void* x, int64_t ldx_bytes, const vo
     p.full_tiles = full; p.tail_split = split;
     p.status = h->dev_status;
     p.group_m = group_m_setting() / 2 > 0 ? group_m_setting() / 2 : 1;     // same panel height in rows as the 1-CTA walk
-    oxq_launch(gemm_tc2_kernel<KIND, EPI>, 2 * clusters, NUM_THREADS, T2_SMEM_BYTES, h->stream, tm_a, tm_b, p);
+    oxq_launch(gemm_tc2_kernel<KIND, EPI, GENERIC>, 2 * clusters, NUM_THREADS, T2_SMEM_BYTES, h->stream, tm_a, tm_b, p);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }
@@ -879,9 +901,9 @@ static bool make_tmap_sf(CUtensorMap* tm, const void* ptr, int64_t total_chunks,
               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int KIND>
+template <int KIND, int BN2_>
 static int32_t launch2_scaled(oxq_handle* h, const void* x, int64_t ldx_bytes, const void* w, int64_t ldw_bytes, GemmParams p) {
-    using C = Cfg2S<KIND>;
+    using C = Cfg2S<KIND, BN2_>;
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
     if (!make_tmap_bytes(&tm_a, x, p.m, p.k_bytes, ldx_bytes, BM) || !make_tmap_bytes(&tm_b, w, p.n, p.k_bytes, ldw_bytes, C::BN2 / 2) ||
         !make_tmap_sf(&tm_sfa, p.sfa, (int64_t)p.sfa_row_tiles * p.sf_col_tiles, C::kSfChunks) ||
@@ -890,17 +912,17 @@ static int32_t launch2_scaled(oxq_handle* h, const void* x, int64_t ldx_bytes, c
     static OxqPerDevice cluster_cache;
     int max_clusters = cluster_cache.get(h->device);
     if (max_clusters == 0) {
-        OXQ_CUDA(h, cudaFuncSetAttribute(gemm_tc2_scaled_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+        OXQ_CUDA(h, cudaFuncSetAttribute(gemm_tc2_scaled_kernel<KIND, BN2_>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(h->sm_count & ~1, 1, 1);
-        cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+        cfg.blockDim = dim3(C::kThreads, 1, 1);
         cfg.dynamicSmemBytes = C::kSmemBytes;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
         attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
         cfg.attrs = &attr; cfg.numAttrs = 1;
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_scaled_kernel<KIND>, &cfg) != cudaSuccess || n < 1) n = h->sm_count / 2;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_scaled_kernel<KIND, BN2_>, &cfg) != cudaSuccess || n < 1) n = h->sm_count / 2;
         max_clusters = n < h->sm_count / 2 ? n : h->sm_count / 2;
         cluster_cache.set(h->device, max_clusters);
     }
@@ -908,9 +930,16 @@ static int32_t launch2_scaled(oxq_handle* h, const void* x, int64_t ldx_bytes, c
     const int clusters = tiles < max_clusters ? tiles : max_clusters;
     p.status = h->dev_status;
     p.group_m = group_m_setting() / 2 > 0 ? group_m_setting() / 2 : 1;
-    oxq_launch(gemm_tc2_scaled_kernel<KIND>, 2 * clusters, NUM_THREADS, C::kSmemBytes, h->stream, tm_a, tm_b, tm_sfa, tm_sfb, p);
+    oxq_launch(gemm_tc2_scaled_kernel<KIND, BN2_>, 2 * clusters, C::kThreads, C::kSmemBytes, h->stream, tm_a, tm_b, tm_sfa, tm_sfb, p);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
+}
+
+// tile width of the CTA-pair block-scaled kernel: OXQ_GEMM_SCALED_TILE = 192 or 256
+static int scaled_tile_setting() {
+    static int v = 0;
+    if (v == 0) { const char* e = getenv("OXQ_GEMM_SCALED_TILE"); v = (e && atoi(e) == 256) ? 256 : 192; }
+    return v;
 }
 
 static int32_t check_gemm_args(oxq_handle* h, int64_t m, int64_t n, int64_t k, const void* x, const void* w, const void* y, int64_t ldy) {
@@ -994,7 +1023,7 @@ static int32_t gemm_op_impl(oxq_handle* h, bool fp8, int64_t m, int64_t n, int64
     p.alpha = alpha; p.beta = beta;
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)(k * es); p.y = y; p.ldy = ldy; p.s0 = sa; p.s1 = sb;
     p.a_mn = a_major == OXQ_OP_MN_MAJOR; p.b_mn = b_major == OXQ_OP_MN_MAJOR; p.esize = (int)es;
-    return fp8 ? launch2<KIND_F8>(h, a, lda * es, b, ldb * es, p) : launch2<KIND_BF16>(h, a, lda * es, b, ldb * es, p);
+    return fp8 ? launch2<KIND_F8, EPI_SCALE, true>(h, a, lda * es, b, ldb * es, p) : launch2<KIND_BF16, EPI_SCALE, true>(h, a, lda * es, b, ldb * es, p);
 }
 
 int32_t oxq_gemm_fp8_op(oxq_handle* h, int64_t m, int64_t n, int64_t k, float alpha, const uint8_t* a, int64_t lda, int a_major,
@@ -1086,7 +1115,7 @@ int32_t oxq_gemm_mxfp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uin
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y; p.ldy = ldy;
     p.sfa = sfx; p.sfb = sfw; p.sf_col_tiles = (int)(k / 32 + 3) / 4;
     p.sfa_row_tiles = (int)((m + 127) / 128); p.sfb_row_tiles = (int)((n + 127) / 128);
-    if (use_2cta_setting() && m > 128) return launch2_scaled<KIND_MXF8>(h, x, k, w, k, p);
+    if (use_2cta_setting() && m > 128) return scaled_tile_setting() == 256 ? launch2_scaled<KIND_MXF8, 256>(h, x, k, w, k, p) : launch2_scaled<KIND_MXF8, 192>(h, x, k, w, k, p);
     return launch<KIND_MXF8, 192>(h, x, k, w, k, p);
 }
 
@@ -1105,7 +1134,8 @@ int32_t oxq_gemm_nvfp4(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uin
     // operand traffic, are the limit), so it is opt-in: OXQ_GEMM_NVFP4_2CTA=1.
     static int nv2 = -1;
     if (nv2 < 0) { const char* e = getenv("OXQ_GEMM_NVFP4_2CTA"); nv2 = e ? (atoi(e) != 0) : 0; }
-    if (nv2 && use_2cta_setting() && m > 128) return launch2_scaled<KIND_NVF4>(h, x, k / 2, w, k / 2, p);
+    if (nv2 && use_2cta_setting() && m > 128)
+        return scaled_tile_setting() == 256 ? launch2_scaled<KIND_NVF4, 256>(h, x, k / 2, w, k / 2, p) : launch2_scaled<KIND_NVF4, 192>(h, x, k / 2, w, k / 2, p);
     return launch<KIND_NVF4, 192>(h, x, k / 2, w, k / 2, p);
 }
 

@@ -196,8 +196,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     pdl_wait();                                                  // only now wait for the kernel that produced the operands
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer (one lane)
-        if (lane == 0) {
+        // ------------------------------------------------------------------ TMA producer (whole warp, one elected lane issues)
+        {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -205,7 +205,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
                 const int m0 = tm * BM, n0 = tn * BN;
                 for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                    if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1)) { ok = false; if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                     const uint32_t full = bar_full + 8 * stage;
                     uint32_t bytes = C::kABytes + C::kBBytes;
                     if (C::kScaled) {
@@ -213,6 +213,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         const int rt0 = n0 >> 7;
                         bytes += (rt0 < p.sfb_row_tiles ? C::kSfaBytes : 0) + (rt0 + 1 < p.sfb_row_tiles ? C::kSfaBytes : 0);
                     }
+                    if (elect_one()) {
                     mbar_arrive_expect_tx(full, bytes);
                     tma_load_2d(sm_a + stage * C::kABytes, &tm_a, kb * BKB, m0, full);
                     tma_load_2d(sm_b + stage * C::kBBytes, &tm_b, kb * BKB, n0, full);
@@ -226,13 +227,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         if (rt0 + 1 < p.sfb_row_tiles)
                             bulk_load(sm_sfb + stage * C::kSfbBytes + C::kSfaBytes, p.sfb + (size_t)(rt0 + 1) * row_stride + col_off, C::kSfaBytes, full);
                     }
+                    }
+                    __syncwarp();
                     if (++stage == S) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer (one lane)
-        if (lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer (whole warp, one elected lane issues)
+        {
             constexpr uint32_t idesc =
                 KIND == KIND_F8 ? idesc_dense(1, 0, 0, BM, BN) :
                 KIND == KIND_BF16 ? idesc_dense(1, 1, 1, BM, BN) :
@@ -245,14 +248,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 int tm, tn;
                 tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
                 const int n0 = tn * BN;
-                if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                if (!mbar_wait_warp(bar_tempty + 8 * acc, acc_phase ^ 1)) { ok = false; if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * C::kAccStride;
                 for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(bar_full + 8 * stage, phase)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                    if (!mbar_wait_warp(bar_full + 8 * stage, phase)) { ok = false; if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                     tc_fence_after();
                     const uint64_t adesc = smem_desc_sw128(sm_a + stage * C::kABytes);
                     const uint64_t bdesc = smem_desc_sw128(sm_b + stage * C::kBBytes);
+                    if (elect_one()) {
                     if (C::kScaled) {
 #pragma unroll
                         for (int c = 0; c < C::kSfChunks; c++) {
@@ -286,10 +290,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         }
                     }
                     tc_commit(bar_empty + 8 * stage);            // frees the stage once these MMAs have read it
+                    }
+                    __syncwarp();
                     if (++stage == S) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                tc_commit(bar_tfull + 8 * acc);                  // accumulator complete
+                if (elect_one()) tc_commit(bar_tfull + 8 * acc);  // accumulator complete
+                __syncwarp();
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
         }
@@ -429,8 +436,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     pdl_wait();
 
     if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer (one lane, both CTAs)
-        if (lane == 0) {
+        // ------------------------------------------------------------------ TMA producer (whole warp, one elected lane issues; both CTAs)
+        {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             const int es_shift = p.esize == 2 ? 1 : 0;
@@ -442,10 +449,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 // past the part; the MMA uses the first n_cols / 2 rows)
                 const int m0 = tm * BM2 + (int)cta_rank * BM, n0 = tn * BN2 + (int)cta_rank * BM + wi.part * (wi.n_cols >> 1);
                 for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                    if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1)) { ok = false; if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                    const uint32_t full0 = mapa_shared(bar_full + 8 * stage, 0);
+                    if (elect_one()) {
                     // the full barrier of the pair lives in CTA 0 and expects the bytes of both CTAs
                     if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * T2_STAGE_BYTES);
-                    const uint32_t full0 = mapa_shared(bar_full + 8 * stage, 0);
                     // K-major operand: one box of 128 rows x 128 bytes of K.  MN-major operand ([K x M] / [K x N] in memory):
                     // `esize` boxes of (128 / esize) K rows x 128 bytes of M / N, one swizzle atom each, side by side
                     // (esize is 1 or 2: the shifts below are the divisions by it).
@@ -455,13 +463,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                     if (!b_mn) tma_load_2d_cg2(sm_b + stage * BM * BKB, &tm_b, kb * BKB, n0, full0);
                     else for (int j = 0; j < p.esize; j++)
                         tma_load_2d_cg2(sm_b + stage * BM * BKB + j * ((BM * BKB) >> es_shift), &tm_b, (n0 << es_shift) + j * 128, kb * (BKB >> es_shift), full0);
+                    }
+                    __syncwarp();
                     if (++stage == S) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer (one lane of CTA 0)
-        if (lane == 0 && cta_rank == 0) {
+        // ------------------------------------------------------------------ MMA issuer (warp 1 of CTA 0, one elected lane issues)
+        if (cta_rank == 0) {
             constexpr uint32_t cf = KIND == KIND_I8 ? 2 : 1, af = KIND == KIND_F8 ? 0 : 1;
             int stage = 0; uint32_t phase = 0;
             int acc = 0; uint32_t acc_phase = 0;
@@ -477,15 +487,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             const uint32_t majors = idesc_majors((uint32_t)a_mn, (uint32_t)b_mn);
             for (int w = cluster_id; w < num_work && ok; w += num_clusters) {
                 const uint32_t idesc = idesc_dense(cf, af, af, BM2, (uint32_t)work_item(w, p.full_tiles, p.tail_split).n_cols) | majors;
-                if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                if (!mbar_wait_warp(bar_tempty + 8 * acc, acc_phase ^ 1)) { ok = false; if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN2;
                 for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(bar_full + 8 * stage, phase)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                    if (!mbar_wait_warp(bar_full + 8 * stage, phase)) { ok = false; if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                     tc_fence_after();
                     // descriptor = the launch's fixed fields + the stage's start address (bits [0, 14), in units of 16 bytes)
                     const uint64_t adesc = a_fixed | (uint64_t)(((sm_a + stage * BM * BKB) & 0x3FFFFu) >> 4);
                     const uint64_t bdesc = b_fixed | (uint64_t)(((sm_b + stage * BM * BKB) & 0x3FFFFu) >> 4);
+                    if (elect_one()) {
 #pragma unroll
                     for (int k = 0; k < BKB / 32; k++) {
                         const uint64_t a = adesc + (uint64_t)(k * ka), b = bdesc + (uint64_t)(k * kbs);
@@ -495,10 +506,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                         else mma_i8_cg2(d_tmem, a, b, idesc, accum);
                     }
                     tc_commit_cg2_mc(bar_empty + 8 * stage, 3);          // frees the stage in both CTAs
+                    }
+                    __syncwarp();
                     if (++stage == S) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                tc_commit_cg2_mc(bar_tfull + 8 * acc, 3);                // accumulator complete, both CTAs
+                if (elect_one()) tc_commit_cg2_mc(bar_tfull + 8 * acc, 3);   // accumulator complete, both CTAs
+                __syncwarp();
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
         }
@@ -635,7 +649,7 @@ gemm_tc2_scaled_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
     pdl_wait();
 
     if (warp == 0) {
-        if (lane == 0) {
+        {                                                         // whole warp; one elected lane issues
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
@@ -644,21 +658,24 @@ gemm_tc2_scaled_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
                 const int m0 = tm * BM2 + (int)cta_rank * BM, n0 = tn * BN2;
                 const int sfa_row = (m0 >> 7) * p.sf_col_tiles, sfb_row = (n0 >> 7) * p.sf_col_tiles;
                 for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
-                    if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * C::kStageBytes);
+                    if (!mbar_wait_warp(bar_empty + 8 * stage, phase ^ 1)) { ok = false; if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                     const uint32_t full0 = mapa_shared(bar_full + 8 * stage, 0);
+                    if (elect_one()) {
+                    if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * C::kStageBytes);
                     tma_load_2d_cg2(sm_a + stage * C::kABytes, &tm_a, kb * BKB, m0, full0);
                     tma_load_2d_cg2(sm_b + stage * C::kBBytes, &tm_b, kb * BKB, n0 + (int)cta_rank * (BN2 / 2), full0);
                     // scale chunks: rows of the [chunk x 128 u32] view; rows past the end read as zero
                     tma_load_2d_cg2(sm_sfa + stage * C::kSfBytes, &tm_sfa, 0, sfa_row + kb * C::kSfChunks, full0);
                     tma_load_2d_cg2(sm_sfb + stage * 2 * C::kSfBytes, &tm_sfb, 0, sfb_row + kb * C::kSfChunks, full0);
                     tma_load_2d_cg2(sm_sfb + stage * 2 * C::kSfBytes + C::kSfBytes, &tm_sfb, 0, sfb_row + p.sf_col_tiles + kb * C::kSfChunks, full0);
+                    }
+                    __syncwarp();
                     if (++stage == S) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && cta_rank == 0) {
+        if (cta_rank == 0) {                                      // whole warp; one elected lane issues
             constexpr uint32_t idesc = KIND == KIND_MXF8 ? idesc_block_scaled(0, 0, 1, BM2, BN2) : idesc_block_scaled(1, 1, 0, BM2, BN2);
             int stage = 0; uint32_t phase = 0;
             int acc = 0; uint32_t acc_phase = 0;
@@ -667,14 +684,15 @@ gemm_tc2_scaled_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
                 int tm, tn;
                 tile_coords(tile, tiles_m, tiles_n, p.group_m, tm, tn);
                 const uint32_t sfb_shift = (uint32_t)((tn * BN2) & 127) >> 5;       // 0 or 2: odd tiles start 64 rows into a scale tile
-                if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                if (!mbar_wait_warp(bar_tempty + 8 * acc, acc_phase ^ 1)) { ok = false; if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * 256;
                 for (int kb = 0; kb < num_kb; kb++) {
-                    if (!mbar_wait(bar_full + 8 * stage, phase)) { ok = false; atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+                    if (!mbar_wait_warp(bar_full + 8 * stage, phase)) { ok = false; if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
                     tc_fence_after();
                     const uint64_t adesc = smem_desc_sw128(sm_a + stage * C::kABytes);
                     const uint64_t bdesc = smem_desc_sw128(sm_b + stage * C::kBBytes);
+                    if (elect_one()) {
 #pragma unroll
                     for (int c = 0; c < C::kSfChunks; c++) {
                         tc_cp_32x128b_warpx4_cg2(tmem_base + C::kSfaCol + 4 * c, smem_desc_sf(sm_sfa + stage * C::kSfBytes + c * 512));
@@ -691,10 +709,13 @@ gemm_tc2_scaled_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_co
                             mma_mxf4nvf4_x4_cg2(d_tmem, a, b, idesc, accum, tmem_base + C::kSfaCol + 4 * k, tmem_base + C::kSfbCol + 8 * k + sfb_shift);
                     }
                     tc_commit_cg2_mc(bar_empty + 8 * stage, 3);
+                    }
+                    __syncwarp();
                     if (++stage == S) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                tc_commit_cg2_mc(bar_tfull + 8 * acc, 3);
+                if (elect_one()) tc_commit_cg2_mc(bar_tfull + 8 * acc, 3);
+                __syncwarp();
                 if (++acc == ACC) { acc = 0; acc_phase ^= 1; }
             }
         }
@@ -1130,10 +1151,9 @@ int32_t oxq_gemm_nvfp4(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uin
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)(k / 2); p.y = y; p.ldy = ldy; p.s0 = gx; p.s1 = gw;
     p.sfa = sfx; p.sfb = sfw; p.sf_col_tiles = (int)(k / 16 + 3) / 4;
     p.sfa_row_tiles = (int)((m + 127) / 128); p.sfb_row_tiles = (int)((n + 127) / 128);
-    // Measured on B200 the CTA-pair kernel is not faster for NVFP4 (the scale-factor copies into tensor memory, not
-    // operand traffic, are the limit), so it is opt-in: OXQ_GEMM_NVFP4_2CTA=1.
+    // The CTA-pair kernel is the default for prefill shapes (OXQ_GEMM_NVFP4_2CTA=0 keeps the single-CTA one for A/B runs).
     static int nv2 = -1;
-    if (nv2 < 0) { const char* e = getenv("OXQ_GEMM_NVFP4_2CTA"); nv2 = e ? (atoi(e) != 0) : 0; }
+    if (nv2 < 0) { const char* e = getenv("OXQ_GEMM_NVFP4_2CTA"); nv2 = e ? (atoi(e) != 0) : 1; }
     if (nv2 && use_2cta_setting() && m > 128)
         return scaled_tile_setting() == 256 ? launch2_scaled<KIND_NVF4, 256>(h, x, k / 2, w, k / 2, p) : launch2_scaled<KIND_NVF4, 192>(h, x, k / 2, w, k / 2, p);
     return launch<KIND_NVF4, 192>(h, x, k / 2, w, k / 2, p);

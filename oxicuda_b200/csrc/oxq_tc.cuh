@@ -51,6 +51,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     return false;
 }
 
+// One lane of a converged warp (the same one on every call from a given warp state).  The issuing loops of the GEMM
+// kernels run with the whole warp so that their control flow and the descriptors they build are warp-uniform -- values
+// the compiler can keep in uniform registers, which is where tcgen05 instructions take their operands from -- and only
+// the tcgen05 instruction itself is guarded by the election.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+// Whole-warp bounded wait: every lane polls, the warp agrees on the outcome.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity) {
+    const bool ok = mbar_wait(bar, parity);
+    return __all_sync(0xffffffffu, ok);
+}
+
 // ---- TMA ----------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");

@@ -376,6 +376,25 @@ def extras(torch, ops, tab):
             if m == 16:
                 del tab.short[f"w4_m{m}_{n}x{k}"]                      # the compact table keeps M = 1, 8, 32
         del ring
+    # config 4 at decode batch sizes: the block-scaled GEMMs as weight streams (weights cycled through a ring > 4x L2)
+    for (n, k) in ((14336, 4096), (4096, 14336)):
+        w = torch.randn((n, k), generator=g, device="cuda").to(torch.bfloat16)
+        b8, b4 = n * k + n * k // 32, n * k // 2 + n * k // 16
+        cb, _, fb = ops.mxfp8_quant(w)
+        pb, _, fb4, stb = ops.nvfp4_quant(w)
+        del w
+        ring8 = [(cb.clone(), fb.clone()) for _ in range(int(4 * L2_BYTES // b8) + 1)]
+        ring4 = [(pb.clone(), fb4.clone()) for _ in range(int(4 * L2_BYTES // b4) + 1)]
+        for m in (1, 8, 32):
+            x = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+            y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+            ca, _, fa = ops.mxfp8_quant(x)
+            pa, _, fa4, sta = ops.nvfp4_quant(x)
+            ms = ring_time(torch, lambda r: ops.gemm_mxfp8(ca, fa, r[0], r[1], out=y), ring8)
+            tab.hbm(f"gemm_mxfp8_m{m}_{n}x{k}", f"mxfp8_m{m}_{n}x{k}", b8 + m * k * 33 // 32 + m * n * 2, ms)
+            ms = ring_time(torch, lambda r: ops.gemm_nvfp4(pa, fa4, sta, r[0], r[1], stb, out=y), ring4)
+            tab.hbm(f"gemm_nvfp4_m{m}_{n}x{k}", f"nvfp4_m{m}_{n}x{k}", b4 + m * k * 9 // 16 + m * n * 2, ms)
+        del ring8, ring4
     # the offline W4 quantize + pack kernel on the largest weight
     ringw = [torch.randn((14336, 4096), generator=g, device="cuda") * 0.02 for _ in range(3)]
     tab.hbm("int4g_quant_pack_f32_14336x4096", "q_int4g", 14336 * 4096 * 4 + 14336 * 4096 // 2 + 458752 * 2 + 458752 // 2,
@@ -950,6 +969,27 @@ def run_case(args):
             r = ws[it[0] % 2]
             ops.gemm_fp8(xq, r[0], sx[1:], r[1][1:], out=y)
         work, unit = float(n * k + m * k + 2 * m * n), "GB/s"
+    elif args.case in ("gemm_mxfp8_decode", "gemm_nvfp4_decode"):
+        n, k, m = 57344 * sz // 8192, 8192, args.m                        # two weights of n x 8192 in rotation
+        mx = args.case == "gemm_mxfp8_decode"
+        ws = []
+        for _ in range(2):
+            wb = torch.randn((n, k), generator=g, device="cuda", dtype=torch.bfloat16)
+            ws.append(ops.mxfp8_quant(wb) if mx else ops.nvfp4_quant(wb))
+            del wb
+        xb = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+        xq = ops.mxfp8_quant(xb) if mx else ops.nvfp4_quant(xb)
+        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        it = [0]
+
+        def fn():
+            it[0] += 1
+            r = ws[it[0] % 2]
+            if mx:
+                ops.gemm_mxfp8(xq[0], xq[2], r[0], r[2], out=y)
+            else:
+                ops.gemm_nvfp4(xq[0], xq[2], xq[3], r[0], r[2], r[3], out=y)
+        work, unit = float((n * k * 33 // 32 if mx else n * k * 9 // 16) + m * k + 2 * m * n), "GB/s"
     elif args.case in ("rmsnorm_int8", "rmsnorm_fp8", "silu_gate_fp8"):
         ring = [torch.randn((sz, sz), generator=g, device="cuda").to(torch.bfloat16) for _ in range(3)]
         wn = torch.ones(sz, device="cuda")
@@ -1004,7 +1044,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--peaks", default=None, help="JSON file with hbm_gbs / bf16_tflops / bf16_tflops_sustained (default: the pool's measured peaks beside this script)")
-    ap.add_argument("--case", default=None, help="single-kernel mode, e.g. gemm_fp8, gemm_mxfp8, gemm_nvfp4, fp8_quant, gemm_w4a16, gemm_fp8_decode, nf4_quant, gemm_nf4")
+    ap.add_argument("--case", default=None, help="single-kernel mode, e.g. gemm_fp8, gemm_mxfp8, gemm_nvfp4, fp8_quant, gemm_w4a16, gemm_fp8_decode, gemm_mxfp8_decode, gemm_nvfp4_decode, nf4_quant, gemm_nf4")
     ap.add_argument("--size", type=int, default=8192)
     ap.add_argument("--m", type=int, default=8)
     args = ap.parse_args()

@@ -15,7 +15,6 @@
 namespace oxq {
 namespace tc {
 
-enum { KIND_F8 = 0, KIND_I8 = 1, KIND_MXF8 = 2, KIND_NVF4 = 3, KIND_BF16 = 4 };
 // Epilogues: EPI_SCALE stores acc * scale; EPI_SWIGLU treats each 256-column tile as 128 gate columns
 // followed by the 128 matching up columns and stores silu(gate) * up (SwiGluFfn::forward,
 // crates/oxicuda-lm/src/layer/ffn.rs:235-254, fused into the gate/up projection).
@@ -1125,12 +1124,22 @@ int32_t oxq_gemm_w8a8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const int8
     return launch_dense<KIND_I8>(h, x, ldx, w, ldw, p);
 }
 
+// Block-scaled GEMMs with at most this many batch rows take the weight-streaming kernel (OXQ_SCALED_DECODE_MAX_M, 0..64; 0 = never).
+// Every CTA of that kernel reads the batch again, m / 128 of the weight bytes on top of the weight stream: from about 32 rows
+// on the 128-row kernels are as fast.
+static int scaled_decode_max_m() {
+    static const int v = [] { const char* e = getenv("OXQ_SCALED_DECODE_MAX_M"); const int x = e ? atoi(e) : 32; return x < 0 ? 0 : (x > 64 ? 64 : x); }();
+    return v;
+}
+
 int32_t oxq_gemm_mxfp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x, const uint8_t* sfx, const uint8_t* w,
                        const uint8_t* sfw, void* y, int64_t ldy) {
     OXQ_CHECK_HANDLE(h);
     if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
     if (!sfx || !sfw || ((uintptr_t)sfx & 15u) || ((uintptr_t)sfw & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned scale-factor pointer");
     if (k & 127) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k must be a multiple of 128 for the MXFP8 GEMM");
+    if (m <= scaled_decode_max_m())
+        return oxq_scaled_decode_launch(h, KIND_MXF8, (int)m, (int)n, (int)k, x, sfx, w, sfw, nullptr, nullptr, y, ldy);
     GemmParams p{};
     p.alpha = 1.0f; p.beta = 0.0f;
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y; p.ldy = ldy;
@@ -1146,6 +1155,8 @@ int32_t oxq_gemm_nvfp4(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uin
     if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
     if (!sfx || !sfw || !gx || !gw || ((uintptr_t)sfx & 15u) || ((uintptr_t)sfw & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned scale pointer");
     if (k & 255) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k must be a multiple of 256 for the NVFP4 GEMM");
+    if (m <= scaled_decode_max_m())
+        return oxq_scaled_decode_launch(h, KIND_NVF4, (int)m, (int)n, (int)(k / 2), x, sfx, w, sfw, gx, gw, y, ldy);
     GemmParams p{};
     p.alpha = 1.0f; p.beta = 0.0f;
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)(k / 2); p.y = y; p.ldy = ldy; p.s0 = gx; p.s1 = gw;

@@ -481,6 +481,35 @@ def test_gemm_nvfp4(ops, orc, mnk):
     _check(_bf16_to_np(y), (da @ db.T).astype(np.float32), f"nvfp4 {mnk}")
 
 
+# Decode shapes: one to 64 batch rows, every batch tile width (16 / 32 / 64), K splits from 1 to 8 CTAs, a ragged last
+# weight tile, and the two weight shapes of the Llama-3-8B MLP.
+@pytest.mark.parametrize("fmt", ["mxfp8", "nvfp4"])
+@pytest.mark.parametrize("mnk", [(1, 128, 256), (3, 200, 512), (8, 1000, 1024), (16, 4096, 4096), (17, 384, 2048), (32, 14336, 4096),
+                                 (33, 256, 8192), (64, 520, 1024), (5, 4096, 14336), (1, 14336, 4096)])
+def test_gemm_block_scaled_decode(ops, orc, fmt, mnk):
+    m, n, k = mnk
+    a = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 10))
+    b = orc.f32_to_bf16_bits(orc.gaussian((n, k), 1.0, 11))
+    if fmt == "mxfp8":
+        ca, sfa, sfa_mma = ops.mxfp8_quant(bf16_dev(a))
+        cb, sfb, sfb_mma = ops.mxfp8_quant(bf16_dev(b))
+        y = ops.gemm_mxfp8(ca, sfa_mma, cb, sfb_mma)
+        y2 = ops.gemm_mxfp8(ca, sfa_mma, cb, sfb_mma)
+        da = orc.spec_mxfp8_dequant(ca.cpu().numpy(), sfa.cpu().numpy()).astype(np.float64)
+        db = orc.spec_mxfp8_dequant(cb.cpu().numpy(), sfb.cpu().numpy()).astype(np.float64)
+    else:
+        pa, sfa, sfa_mma, sta = ops.nvfp4_quant(bf16_dev(a))
+        pb, sfb, sfb_mma, stb = ops.nvfp4_quant(bf16_dev(b))
+        y = ops.gemm_nvfp4(pa, sfa_mma, sta, pb, sfb_mma, stb)
+        y2 = ops.gemm_nvfp4(pa, sfa_mma, sta, pb, sfb_mma, stb)
+        da = orc.spec_nvfp4_dequant(pa.cpu().numpy(), sfa.cpu().numpy(), float(sta[1]), m, k).astype(np.float64)
+        db = orc.spec_nvfp4_dequant(pb.cpu().numpy(), sfb.cpu().numpy(), float(stb[1]), n, k).astype(np.float64)
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    assert torch.equal(y, y2), "the K split must not depend on scheduling"
+    _check(_bf16_to_np(y), (da @ db.T).astype(np.float32), f"{fmt} decode {mnk}")
+
+
 @pytest.mark.parametrize("fmt", ["mxfp8", "nvfp4"])
 def test_gemm_block_scaled_llama8b_prefill_size(ops, orc, fmt):
     """Benchmark configuration 4 at its real size (M = 4096, N = 14336, K = 4096), operands quantised on the GPU: 64 sampled

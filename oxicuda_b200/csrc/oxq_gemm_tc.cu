@@ -38,6 +38,11 @@ struct GemmParams {
     int a_mn, b_mn;                   // CTA-pair dense kernel: operand stored MN-major (X as [K x M], W as [K x N]) instead of K-major
     int esize;                        // bytes per operand element (1 or 2)
     int32_t* status;
+    // fused all-reduce form of the CTA-pair kernel: y is this rank's replica of a symmetric buffer
+    void* ar_mc_y;                    // the same buffer through the multicast mapping
+    uint32_t* ar_flags;               // this rank's replica of the flag words: [items] arrivals, then one word of finished units
+    uint32_t* ar_mc_flags;            // the flag words through the multicast mapping
+    int ar_world, ar_rank;
 };
 
 template <int KIND, int BN>
@@ -394,8 +399,48 @@ constexpr int T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + 2048;
 
 // GENERIC = false is the K-major / K-major kernel; GENERIC = true reads the operands' major-ness from the parameters (the
 // operand forms of gemm).  Two instantiations, so that the common form carries none of the other's address arithmetic.
-template <int KIND, int EPI, bool GENERIC = false>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+// ---- all-reduce fused into the CTA-pair kernel (AR = true) ----------------------------------------------------------
+// Every rank of a tensor-parallel group runs this kernel on its K-shard and writes its partial tiles into its replica of
+// a symmetric buffer.  When an epilogue warp has stored its 32 rows of a tile it adds one to the tile's arrival word on
+// every rank (multimem.red through the NVSwitch).  Tile w belongs to rank w % world: four more warps per CTA, the
+// reducers, take the owned tiles in strips of 16 rows, wait until every epilogue warp of every rank has arrived
+// (8 * world), pull the sum of all replicas with multimem.ld_reduce (the switch adds in f32) and push it to every
+// replica with multimem.st, then add one to the word of finished units on every rank.  CTA 0 leaves only when every
+// unit of every rank is finished, so the kernel that follows in the stream finds the complete sum in its replica; it
+// then clears this call's flag words (calls alternate between two sets of words, so a peer that is already a call
+// ahead never meets a word that is still to be cleared).  The transfer of a tile overlaps the MMAs of the tiles after
+// it; nothing waits on the reducers except the end of the kernel, and every wait is bounded.
+__device__ __forceinline__ void mm_red_add_u32(uint32_t* mc_addr, uint32_t v) {
+    asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* addr) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ bool wait_word_at_least(const uint32_t* addr, uint32_t target) {
+    if (ld_acquire_sys_u32(addr) >= target) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 0; it < 0x40000000u; ++it) {
+        if (ld_acquire_sys_u32(addr) >= target) return true;
+        if ((it & 63u) == 63u && globaltimer_ns() - t0 > kWaitLimitNs) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ uint4 mm_ld_reduce_bf16x8(const void* mc_addr) {
+    uint4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_addr) : "memory");
+    return r;
+}
+__device__ __forceinline__ void mm_st_bf16x8(void* mc_addr, const uint4& r) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc_addr), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w) : "memory");
+}
+constexpr int AR_THREADS = NUM_THREADS + 128;                      // + four reducer warps
+
+template <int KIND, int EPI, bool GENERIC = false, bool AR = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(AR ? AR_THREADS : NUM_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
     const bool a_mn = GENERIC && p.a_mn, b_mn = GENERIC && p.b_mn;
     constexpr int S = T2_STAGES;
@@ -515,7 +560,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
                 if (++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
         }
-    } else {
+    } else if (!AR || warp < 6) {
         // ------------------------------------------------------------------ epilogue (4 warps, both CTAs)
         const int quarter = warp & 3;
         int acc = 0; uint32_t acc_phase = 0;
@@ -561,6 +606,56 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_tempty + 8 * acc, 0));
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            if (AR) {
+                // this warp's 32 rows of the tile are stored: one arrival on every rank (lane 0's release, after the warp
+                // has met, covers the stores of all its lanes)
+                if (lane == 0) { __threadfence_system(); mm_red_add_u32(p.ar_mc_flags + w, 1u); }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ reducers (AR only: 4 warps, both CTAs)
+        // A unit is a strip of 16 rows x 256 columns of an owned tile; the reducer warps of the whole grid take the
+        // units in order, each warp on its own (no CTA-wide meeting point anywhere in this role).
+        const int world = p.ar_world;
+        const int owned = num_work > p.ar_rank ? (num_work - p.ar_rank + world - 1) / world : 0;   // items w = rank, rank + world, ...
+        const int units = owned * 16;
+        const uint32_t arrive_target = 8u * (uint32_t)world;            // 2 CTAs x 4 epilogue warps per rank
+        char* mc_y = reinterpret_cast<char*>(p.ar_mc_y);
+        bool ok = true;
+        for (int u = (int)blockIdx.x * 4 + (warp - 6); u < units && ok; u += (int)gridDim.x * 4) {
+            const int w = (u >> 4) * world + p.ar_rank, strip = u & 15;
+            int tm, tn;
+            tile_coords(w, tiles_m, tiles_n, p.group_m, tm, tn);
+            if (lane == 0) ok = wait_word_at_least(p.ar_flags + w, arrive_target);
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+            if (!ok) { if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
+            // 16 rows x 256 columns of bf16 = 16 x 32 vectors of 16 bytes; four vectors in flight per lane
+            const int row0 = tm * BM2 + strip * 16, col0 = tn * BN2;
+#pragma unroll 1
+            for (int v0 = lane; v0 < 16 * 32; v0 += 32 * 4) {
+                uint4 val[4];
+                char* at[4];
+                bool in[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int v = v0 + j * 32, r = row0 + (v >> 5), c = col0 + ((v & 31) << 3);
+                    in[j] = r < p.m && c < p.n;
+                    at[j] = mc_y + ((size_t)r * p.ldy + c) * 2;
+                    if (in[j]) val[j] = mm_ld_reduce_bf16x8(at[j]);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (in[j]) mm_st_bf16x8(at[j], val[j]);
+            }
+            __syncwarp();
+            if (lane == 0) { __threadfence_system(); mm_red_add_u32(p.ar_mc_flags + num_work, 1u); }
+        }
+        if (blockIdx.x == 0 && warp == 6) {
+            // the last to leave: every unit of every rank is finished (16 per item), then this call's words are cleared
+            if (lane == 0 && ok && !wait_word_at_least(p.ar_flags + num_work, 16u * (uint32_t)num_work)) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT);
+            __syncwarp();
+            for (int i = lane; i <= num_work; i += 32) p.ar_flags[i] = 0u;
+            __threadfence_system();
         }
     }
 
@@ -899,6 +994,43 @@ static int32_t launch2(oxq_handle* h, const void* x, int64_t ldx_bytes, const vo
     return OXQ_OK;
 }
 
+// The CTA-pair FP8 kernel with the all-reduce fused in (whole 256 x 256 tiles only: no split of the last wave).
+static int32_t launch2_ar(oxq_handle* h, const void* x, int64_t ldx_bytes, const void* w, int64_t ldw_bytes, GemmParams p) {
+    CUtensorMap tm_a, tm_b;
+    p.esize = 1; p.a_mn = 0; p.b_mn = 0;
+    if (!make_tmap_bytes(&tm_a, x, p.m, p.k_bytes, ldx_bytes, BM) || !make_tmap_bytes(&tm_b, w, p.n, p.k_bytes, ldw_bytes, BM))
+        OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned, leading dimensions multiples of 16 bytes)");
+    auto kernel = gemm_tc2_kernel<KIND_F8, EPI_SCALE, false, true>;
+    static OxqPerDevice cluster_cache;
+    int max_clusters = cluster_cache.get(h->device);
+    if (max_clusters == 0) {
+        OXQ_CUDA(h, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(h->sm_count & ~1, 1, 1);
+        cfg.blockDim = dim3(AR_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = T2_SMEM_BYTES;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr; cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n < 1)
+            OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "the fused all-reduce kernel does not fit this device");
+        max_clusters = n < h->sm_count / 2 ? n : h->sm_count / 2;
+        cluster_cache.set(h->device, max_clusters);
+    }
+    const int tiles = ((p.m + 255) / 256) * ((p.n + 255) / 256);
+    const int clusters = tiles < max_clusters ? tiles : max_clusters;
+    p.full_tiles = tiles; p.tail_split = 1;
+    p.status = h->dev_status;
+    p.group_m = group_m_setting() / 2 > 0 ? group_m_setting() / 2 : 1;
+    // Every CTA of the grid has to be resident (the reducers of one rank serve the epilogues of all ranks): the grid is
+    // at most one cluster per SM pair, and the launch is plain stream order, without an early start under the kernel before.
+    oxq_launch<false>(kernel, 2 * clusters, AR_THREADS, T2_SMEM_BYTES, h->stream, tm_a, tm_b, p);
+    OXQ_LAUNCH_CHECK(h);
+    return OXQ_OK;
+}
+
 // Dense kinds: 256 x 256 tiles on CTA pairs when there are at least two 128-row tiles of X, else 128 x 256.
 template <int KIND, int EPI = EPI_SCALE>
 static int32_t launch_dense(oxq_handle* h, const void* x, int64_t ldx_bytes, const void* w, int64_t ldw_bytes, const GemmParams& p) {
@@ -1054,6 +1186,30 @@ int32_t oxq_gemm_fp8_op(oxq_handle* h, int64_t m, int64_t n, int64_t k, float al
 int32_t oxq_gemm_bf16_op(oxq_handle* h, int64_t m, int64_t n, int64_t k, float alpha, const void* a, int64_t lda, int a_major,
                          const void* b, int64_t ldb, int b_major, float beta, void* y, int64_t ldy) {
     return gemm_op_impl(h, false, m, n, k, alpha, a, lda, a_major, b, ldb, b_major, nullptr, nullptr, beta, y, ldy);
+}
+
+int32_t oxq_gemm_fp8_all_reduce(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x, int64_t ldx, const uint8_t* w, int64_t ldw,
+                                const float* sx, const float* sw, void* y_local, void* y_multicast, int64_t ldy, uint32_t* flags_local,
+                                uint32_t* flags_multicast, int64_t flag_words, int rank, int world, int64_t call_index) {
+    OXQ_CHECK_HANDLE(h);
+    if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y_local, ldy)) return rc;
+    if (!sx || !sw) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
+    if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
+    if (world < 2 || world > 64 || rank < 0 || rank >= world) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "rank %d outside a world of %d (2..64)", rank, world);
+    if (!y_multicast || ((uintptr_t)y_multicast & 15u) || !flags_local || !flags_multicast || ((uintptr_t)flags_local & 3u) || ((uintptr_t)flags_multicast & 3u))
+        OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned multicast / flag pointer");
+    if (n & 7) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "n must be a multiple of 8 (16-byte vectors through the switch)");
+    if (call_index < 0) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "negative call index");
+    const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256);
+    if (flag_words < 2 * (tiles + 1)) OXQ_FAIL(h, OXQ_ERR_BUFFER_TOO_SMALL, "flag words: expected at least %lld, got %lld", (long long)(2 * (tiles + 1)), (long long)flag_words);
+    GemmParams p{};
+    p.alpha = 1.0f; p.beta = 0.0f;
+    p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y_local; p.ldy = ldy; p.s0 = sx; p.s1 = sw;
+    // calls alternate between the two halves of the flag words
+    const int64_t set = (call_index & 1) * (flag_words / 2);
+    p.ar_mc_y = y_multicast; p.ar_flags = flags_local + set; p.ar_mc_flags = flags_multicast + set;
+    p.ar_world = world; p.ar_rank = rank;
+    return launch2_ar(h, x, ldx, w, ldw, p);
 }
 
 int32_t oxq_gemm_fp8_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, const uint8_t* x, int64_t ldx, const uint8_t* w_gu, int64_t ldw,

@@ -33,7 +33,8 @@ constexpr int RAW_BYTES = ROWS * 128;      // 16 KB
 constexpr int A_COLS = 128;                // tensor-memory columns of one unpacked unit (two groups of 128 bf16 per lane)
 constexpr int A_SLOTS = 2;                 // units of unpacked weights in tensor memory
 constexpr int U_SLOTS = 4;                 // units of activations in shared memory == units of accumulators in tensor memory
-constexpr int NUM_WARPS = 15;              // 0: codes TMA, 1: X TMA, 2: MMA + tensor-memory owner, 3-6: epilogue, 7-14: unpack
+constexpr int UNPACK_WARPS = 16;           // four per group quarter: a thread unpacks 64 codes of one weight row per unit
+constexpr int NUM_WARPS = 7 + UNPACK_WARPS; // 0: codes TMA, 1: X TMA, 2: MMA + tensor-memory owner, 3-6: epilogue, 7-: unpack
 constexpr int NUM_THREADS = NUM_WARPS * 32;
 constexpr int SMEM_BUDGET = 227 * 1024;
 constexpr int PASS_ROWS = 32;              // batch rows per launch; the workspace keeps 32 f32 per weight row and pass
@@ -111,9 +112,9 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     const int num_units = unit1 - unit0;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < RS; s++) { mbar_init(bar_raw_full + 8 * s, 1); mbar_init(bar_raw_empty + 8 * s, 8); }
+        for (int s = 0; s < RS; s++) { mbar_init(bar_raw_full + 8 * s, 1); mbar_init(bar_raw_empty + 8 * s, UNPACK_WARPS); }
         for (int s = 0; s < U_SLOTS; s++) { mbar_init(bar_x_full + 8 * s, 1); mbar_init(bar_done + 8 * s, 1); mbar_init(bar_acc_empty + 8 * s, 4); }
-        for (int s = 0; s < A_SLOTS; s++) mbar_init(bar_a_full + 8 * s, 8);
+        for (int s = 0; s < A_SLOTS; s++) mbar_init(bar_a_full + 8 * s, UNPACK_WARPS);
         fence_barrier_init();
         prefetch_tmap(&tm_codes);
         prefetch_tmap(&tm_x);
@@ -133,42 +134,45 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     // activation producer (slot free again, four units later) and the unpack warps (tensor-memory slot of the
     // weights free again, two units later) -- a single tcgen05.commit per unit on the issuing thread.
     if (warp == 0) {
-        // ------------------------------------------------------------------ codes producer (one lane)
-        if (lane == 0) {
-            for (int lu = 0; lu < num_units; lu++) {
-                const int unit = unit0 + lu, rb = unit / p.upr, uk = unit - rb * p.upr;
-                const int rs = lu % RS;
-                if (!mbar_wait(bar_raw_empty + 8 * rs, ((lu / RS) & 1) ^ 1)) { fail(p); break; }
+        // ------------------------------------------------------------------ codes producer (whole warp, one elected lane issues)
+        for (int lu = 0; lu < num_units; lu++) {
+            const int unit = unit0 + lu, rb = unit / p.upr, uk = unit - rb * p.upr;
+            const int rs = lu % RS;
+            if (!mbar_wait_warp(bar_raw_empty + 8 * rs, ((lu / RS) & 1) ^ 1)) { if (lane == 0) fail(p); break; }
+            if (elect_one()) {
                 mbar_arrive_expect_tx(bar_raw_full + 8 * rs, RAW_BYTES);
                 tma_load_2d(sm_raw + rs * RAW_BYTES, &tm_codes, uk * 128, rb * ROWS, bar_raw_full + 8 * rs);
             }
+            __syncwarp();
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ activation producer (one lane)
-        if (lane == 0) {
-            pdl_wait();
-            for (int lu = 0; lu < num_units; lu++) {
-                const int unit = unit0 + lu, rb = unit / p.upr, uk = unit - rb * p.upr;
-                const int k0 = uk * UNIT_K;
-                const int us = lu % U_SLOTS;
-                if (!mbar_wait(bar_done + 8 * us, ((lu / U_SLOTS) & 1) ^ 1)) { fail(p); break; }
-                const uint32_t xdst = sm_x + us * C::kXBytes;
+        // ------------------------------------------------------------------ activation producer (whole warp, one elected lane issues)
+        pdl_wait();
+        for (int lu = 0; lu < num_units; lu++) {
+            const int unit = unit0 + lu, rb = unit / p.upr, uk = unit - rb * p.upr;
+            const int k0 = uk * UNIT_K;
+            const int us = lu % U_SLOTS;
+            if (!mbar_wait_warp(bar_done + 8 * us, ((lu / U_SLOTS) & 1) ^ 1)) { if (lane == 0) fail(p); break; }
+            const uint32_t xdst = sm_x + us * C::kXBytes;
+            if (elect_one()) {
                 mbar_arrive_expect_tx(bar_x_full + 8 * us, C::kXBytes);
 #pragma unroll
                 for (int s = 0; s < 4; s++) tma_load_2d(xdst + s * (NB * 128), &tm_x, k0 + 64 * s, 0, bar_x_full + 8 * us);
             }
+            __syncwarp();
         }
     } else if (warp == 2) {
-        // ------------------------------------------------------------------ MMA issuer (one lane)
-        if (lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer (whole warp, one elected lane issues)
+        {
             constexpr uint32_t idesc = idesc_dense(1, 1, 1, ROWS, NB);
             for (int lu = 0; lu < num_units; lu++) {
                 const int us = lu % U_SLOTS, as = lu % A_SLOTS;
-                if (!mbar_wait(bar_acc_empty + 8 * us, ((lu / U_SLOTS) & 1) ^ 1)) { fail(p); break; }
-                if (!mbar_wait(bar_x_full + 8 * us, (lu / U_SLOTS) & 1)) { fail(p); break; }
-                if (!mbar_wait(bar_a_full + 8 * as, (lu / A_SLOTS) & 1)) { fail(p); break; }    // weights unpacked into tensor memory
+                if (!mbar_wait_warp(bar_acc_empty + 8 * us, ((lu / U_SLOTS) & 1) ^ 1)) { if (lane == 0) fail(p); break; }
+                if (!mbar_wait_warp(bar_x_full + 8 * us, (lu / U_SLOTS) & 1)) { if (lane == 0) fail(p); break; }
+                if (!mbar_wait_warp(bar_a_full + 8 * as, (lu / A_SLOTS) & 1)) { if (lane == 0) fail(p); break; }    // weights unpacked into tensor memory
                 tc_fence_after();
                 const uint32_t x0 = sm_x + us * C::kXBytes;
+                if (elect_one()) {
 #pragma unroll
                 for (int h = 0; h < 2; h++) {                 // the unit's two groups, one accumulator each
                     const uint32_t d_tmem = tmem_base + (us * 2 + h) * NB;
@@ -182,6 +186,8 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
                     }
                 }
                 tc_commit(bar_done + 8 * us);
+                }
+                __syncwarp();
             }
         }
     } else if (warp < 7) {
@@ -300,11 +306,12 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
         if (ok && cur_rb >= 0) flush(cur_rb, seg_groups);
         if (ok) finish_pending();
     } else {
-        // ------------------------------------------------------------------ unpack (8 warps)
-        // Warps 7-10 take the first group of every unit, warps 11-14 the second; a warp serves the tensor-memory
-        // lane quarter it may access (warp index mod 4) and a thread owns one weight row of its group: 64 bytes of
-        // codes in, 64 columns of bf16 pairs out.
-        const int half = (warp - 7) >> 2, quarter = warp & 3;
+        // ------------------------------------------------------------------ unpack (16 warps)
+        // Warps 7-14 take the first group of every unit, warps 15-22 the second, four warps per half group; a warp
+        // serves the tensor-memory lane quarter it may access (warp index mod 4) and a thread owns half a group of one
+        // weight row: 32 bytes of codes in, 32 columns of bf16 pairs out.
+        constexpr int JJ = 32 / UNPACK_WARPS;                    // 16-byte pieces of a row's group per thread
+        const int part = (warp - 7) >> 2, half = part / (UNPACK_WARPS / 8), sub = part % (UNPACK_WARPS / 8), quarter = warp & 3;
         const int r = quarter * 32 + lane;                       // row inside the block == tensor-memory lane
         const uint32_t rsw = (uint32_t)(r & 7);
         uint32_t zw_cur = 0, zw_next = 0;
@@ -331,10 +338,10 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
             bool ok = mbar_wait(bar_raw_full + 8 * rs, (lu / RS) & 1);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { if (lane == 0) fail(p); break; }
-            uint4 raw[4];
+            uint4 raw[JJ];
             const uint32_t raw_row = sm_raw + rs * RAW_BYTES + r * 128;
 #pragma unroll
-            for (int jj = 0; jj < 4; jj++) raw[jj] = lds128(raw_row + ((((uint32_t)(half * 4 + jj)) ^ rsw) << 4));
+            for (int jj = 0; jj < JJ; jj++) raw[jj] = lds128(raw_row + ((((uint32_t)(half * 4 + sub * JJ + jj)) ^ rsw) << 4));
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_raw_empty + 8 * rs);   // the codes are in registers
 
@@ -349,7 +356,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
             const uint32_t a_lane = tmem_base + ((uint32_t)(quarter * 32) << 16) + C::kACol0 + as * A_COLS + half * 64;
             {
 #pragma unroll
-                for (int jj = 0; jj < 4; jj++) {
+                for (int jj = 0; jj < JJ; jj++) {
                     // 32 consecutive K of this row -> 16 columns, K pairs in their natural order
                     const uint32_t wv[4] = {raw[jj].x, raw[jj].y, raw[jj].z, raw[jj].w};
                     uint32_t o[16];
@@ -361,7 +368,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
                         o[4 * i + 2] = unpack_pair(__byte_perm(w, w4, 0x6622), zz);
                         o[4 * i + 3] = unpack_pair(__byte_perm(w, w4, 0x7733), zz);
                     }
-                    tmem_st_32x32b_x16(a_lane + 16 * jj, o);
+                    tmem_st_32x32b_x16(a_lane + 16 * (sub * JJ + jj), o);
                 }
                 tmem_st_wait();
             }

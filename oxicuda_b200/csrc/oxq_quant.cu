@@ -28,14 +28,33 @@ __device__ __forceinline__ uint32_t quant_i8(float x, const InvDiv& scale, int r
     return code & 0xFFu;
 }
 
+// Fast form for a scale derived from the row's own maximum and inside the exact-division range: finite inputs give
+// quotients within +-127 (+ rounding), so no clamp; a NaN gives code 0.  ROUND is a compile-time constant here.
+// Half away from zero is trunc(v + copysign(pred(0.5), v)): the sum rounds to the next integer exactly when the
+// fraction of |v| is at least one half.
+template <int ROUND>
+__device__ __forceinline__ uint32_t quant_i8_fast(float x, const InvDiv& d) {
+    const float q0 = x * d.y;
+    float v = fmaf(fmaf(-d.s, q0, x), d.y, q0);
+    v = v != v ? 0.0f : v;
+    if (ROUND == OXQ_ROUND_HALF_AWAY) {
+        const float half = __uint_as_float((__float_as_uint(v) & 0x80000000u) | 0x3EFFFFFFu);
+        return (uint32_t)__float2int_rz(v + half);
+    }
+    return __float_as_uint(v + 12582912.0f);                // RNE(v) in the low mantissa byte
+}
+__device__ __forceinline__ uint32_t pack4_low(uint32_t a, uint32_t b, uint32_t c, uint32_t e) {
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, e, 0x0040), 0x5410);
+}
+
 // One CTA per row at a time (grid-stride over rows).  Each thread keeps up to NV float4 of the row in
 // registers, so a row of up to 256*4*NV floats is read from HBM exactly once (longer rows are read a second
 // time for the quantize pass), and the next row of the CTA is already being fetched while the current one is
 // reduced, quantised and stored.
-template <int NV>
+template <int NV, int ROUND>
 __global__ void __launch_bounds__(256) int8_quant_rows_kernel(const float* __restrict__ x, int64_t rows, int64_t cols,
-                                                              int8_t* __restrict__ q, float* __restrict__ scales,
-                                                              int rounding) {
+                                                              int8_t* __restrict__ q, float* __restrict__ scales) {
+    constexpr int rounding = ROUND;
     pdl_trigger();
     pdl_wait();
     __shared__ float s_red[2][8];
@@ -81,13 +100,23 @@ __global__ void __launch_bounds__(256) int8_quant_rows_kernel(const float* __res
         if (tid == 0) scales[row] = scale_f;
         const InvDiv scale = make_invdiv(scale_f);
         uint32_t* qr = reinterpret_cast<uint32_t*>(q + row * cols);
+        if (scale.fast) {                                    // the whole CTA takes the same side
 #pragma unroll
-        for (int i = 0; i < NV; i++) {
-            const int64_t idx = tid + (int64_t)i * 256;
-            if (idx < nvec) {
-                uint32_t p = quant_i8(cur[i].x, scale, rounding) | (quant_i8(cur[i].y, scale, rounding) << 8) |
-                             (quant_i8(cur[i].z, scale, rounding) << 16) | (quant_i8(cur[i].w, scale, rounding) << 24);
-                __stcs(qr + idx, p);
+            for (int i = 0; i < NV; i++) {
+                const int64_t idx = tid + (int64_t)i * 256;
+                if (idx < nvec)
+                    __stcs(qr + idx, pack4_low(quant_i8_fast<ROUND>(cur[i].x, scale), quant_i8_fast<ROUND>(cur[i].y, scale),
+                                               quant_i8_fast<ROUND>(cur[i].z, scale), quant_i8_fast<ROUND>(cur[i].w, scale)));
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < NV; i++) {
+                const int64_t idx = tid + (int64_t)i * 256;
+                if (idx < nvec) {
+                    uint32_t p = quant_i8(cur[i].x, scale, rounding) | (quant_i8(cur[i].y, scale, rounding) << 8) |
+                                 (quant_i8(cur[i].z, scale, rounding) << 16) | (quant_i8(cur[i].w, scale, rounding) << 24);
+                    __stcs(qr + idx, p);
+                }
             }
         }
         for (int64_t idx = tid + (int64_t)NV * 256; idx < nvec; idx += 256) {
@@ -884,8 +913,14 @@ int32_t oxq_int8_quant_rows(oxq_handle* h, const float* x, int64_t rows, int64_t
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     const int grid = (int)(rows < (int64_t)h->sm_count * 6 ? rows : (int64_t)h->sm_count * 6);
     if ((cols & 3) == 0 && aligned16(x) && (((uintptr_t)q & 3u) == 0)) {
-        if (cols <= 4096) oxq_launch(int8_quant_rows_kernel<4>, grid, 256, 0, h->stream, x, rows, cols, q, scales, rounding);
-        else oxq_launch(int8_quant_rows_kernel<8>, grid, 256, 0, h->stream, x, rows, cols, q, scales, rounding);
+        const bool away = rounding == OXQ_ROUND_HALF_AWAY;
+        if (cols <= 4096) {
+            if (away) oxq_launch(int8_quant_rows_kernel<4, OXQ_ROUND_HALF_AWAY>, grid, 256, 0, h->stream, x, rows, cols, q, scales);
+            else oxq_launch(int8_quant_rows_kernel<4, OXQ_ROUND_HALF_EVEN>, grid, 256, 0, h->stream, x, rows, cols, q, scales);
+        } else {
+            if (away) oxq_launch(int8_quant_rows_kernel<8, OXQ_ROUND_HALF_AWAY>, grid, 256, 0, h->stream, x, rows, cols, q, scales);
+            else oxq_launch(int8_quant_rows_kernel<8, OXQ_ROUND_HALF_EVEN>, grid, 256, 0, h->stream, x, rows, cols, q, scales);
+        }
     } else {
         oxq_launch(int8_quant_rows_scalar_kernel, grid, 256, 0, h->stream, x, rows, cols, q, scales, rounding);
     }

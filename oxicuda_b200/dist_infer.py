@@ -258,6 +258,10 @@ class TpSwiGluMlp:
         self.last_h = None
         self.use_multimem = tp > 1 and reduce_dtype == torch.bfloat16 and os.environ.get("OXQ_TP_NO_MULTIMEM", "0") != "1"
         self.split_reduce = os.environ.get("OXQ_TP_SPLIT_REDUCE", "1") != "0"
+        # OXQ_TP_FUSED_REDUCE=1: the down projection and the all-reduce as one kernel (oxq_gemm_fp8_all_reduce)
+        self.fused_reduce = self.use_multimem and os.environ.get("OXQ_TP_FUSED_REDUCE", "0") == "1"
+        self._flags = None
+        self._fused_calls = 0
 
     # -- NVLS path: symmetric output buffer mapped through the NVSwitch multicast object ----------
     def _symm_buffer(self, m: int):
@@ -279,6 +283,48 @@ class TpSwiGluMlp:
             self.use_multimem = False       # NCCL all-reduce instead
             self._symm = None
         return self._symm
+
+    def _fused_flags(self):
+        """Symmetric flag words of the fused GEMM + all-reduce kernel (zeroed once; every call leaves them zero)."""
+        if self._flags is None:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm_mem
+            words = symm_mem.empty((2 * 4096,), dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()))
+            words.zero_()
+            fh = symm_mem.rendezvous(words, self.group if self.group is not None else dist.group.WORLD)
+            if not fh.multicast_ptr:
+                raise RuntimeError("no multicast support")
+            torch.cuda.synchronize()
+            fh.barrier(channel=0)                      # every replica is zero before anyone's first arrival can land
+            torch.cuda.synchronize()
+            self._flags = (words, fh)
+        return self._flags
+
+    def _forward_fused(self, x: torch.Tensor):
+        """FP8 variant: the down projection and the all-reduce are one kernel per rank (tiles are summed in the NVSwitch
+        while later tiles are still being multiplied); no barrier kernels, no side stream."""
+        m = x.shape[0]
+        sym = self._symm_buffer(m)
+        tiles = ((m + 255) // 256) * ((self.hidden + 255) // 256)
+        if sym is None or self.variant != "fp8" or self.hidden % 8 != 0 or tiles + 1 > 4096 or m <= 128:
+            return None
+        try:
+            words, fh = self._fused_flags()
+        except Exception:
+            self.fused_reduce = False
+            return None
+        buf, hdl = sym
+        y = buf[:m]
+        ops = self.ops
+        xq, sx = ops.fp8_quant_dynamic(x)
+        h = ops.gemm_fp8_swiglu(xq, self.w_gu_q, sx[1:], self.s_gu)
+        if self.keep_h:
+            self.last_h = h
+        hq, sh = ops.fp8_quant_dynamic(h)
+        ops.gemm_fp8_all_reduce(hq, self.w_down_q, sh[1:], self.s_down, y, hdl.multicast_ptr, words, fh.multicast_ptr, self.rank, self.tp,
+                                self._fused_calls)
+        self._fused_calls += 1
+        return y
 
     def _forward_multimem(self, x: torch.Tensor):
         """down-projection partial straight into the symmetric buffer, barrier, in-switch reduce + broadcast, barrier."""
@@ -367,7 +413,9 @@ class TpSwiGluMlp:
         chunks = min(self.overlap_chunks, max(1, m // 256))
         if chunks <= 1:
             if self.use_multimem:
-                y = self._forward_multimem_split(x) if (self.split_reduce and m >= 512) else None
+                y = self._forward_fused(x) if self.fused_reduce else None
+                if y is None:
+                    y = self._forward_multimem_split(x) if (self.split_reduce and m >= 512) else None
                 if y is None:
                     y = self._forward_multimem(x)
                 if y is not None:

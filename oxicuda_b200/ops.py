@@ -727,6 +727,19 @@ def multimem_all_reduce_bf16(multicast_ptr: int, numel: int, rank: int, world: i
     handle(device_index).call("oxq_multimem_all_reduce_bf16", C.c_void_p(multicast_ptr), numel, rank, world)
 
 
+def gemm_fp8_all_reduce(x_q, w_q, sx, sw, y_local: torch.Tensor, y_multicast_ptr: int, flags_local: torch.Tensor, flags_multicast_ptr: int,
+                        rank: int, world: int, call_index: int):
+    """FP8 GEMM of this rank's K-shard with the all-reduce over the ranks fused in (RowLinear::forward_partial + all_reduce):
+    y_local is this rank's [m x n] view of a symmetric bf16 buffer, flags_local its int32 flag words (zero before the first
+    call); the *_multicast_ptr arguments are the multicast addresses of the same two buffers."""
+    m, k = x_q.shape
+    n = w_q.shape[0]
+    handle(x_q.device.index).call("oxq_gemm_fp8_all_reduce", m, n, k, _p(x_q), x_q.stride(0), _p(w_q), w_q.stride(0), _p(sx), _p(sw), _p(y_local),
+                                  C.c_void_p(y_multicast_ptr), y_local.stride(0), _p(flags_local), C.c_void_p(flags_multicast_ptr),
+                                  flags_local.numel(), rank, world, call_index)
+    return y_local
+
+
 def multimem_all_reduce_bf16_2d(multicast_ptr: int, rows: int, cols: int, ld: int, rank: int, world: int, device_index: int | None = None):
     """In-place all-reduce of a [rows x cols] column block (leading dimension ld) of a symmetric bf16 matrix."""
     handle(device_index).call("oxq_multimem_all_reduce_bf16_2d", C.c_void_p(multicast_ptr), rows, cols, ld, rank, world)

@@ -132,6 +132,65 @@ def test_tp_mlp_nccl_two_gpus(variant):
             assert e <= MAX_REL, errs
 
 
+def _fused_rank(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["OXQ_TP_FUSED_REDUCE"] = "1"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from oracle import oracle as orc
+    from oxicuda_b200 import ops
+    from oxicuda_b200.dist_infer import TpSwiGluMlp
+    errs = []
+    for (hidden, inter, ms) in ((512, 2048, (520, 300, 520, 1024)), (2048, 4096, (2048, 2048, 2048))):
+        wg, wu, wd = _weights(orc, hidden, inter)
+        layer = TpSwiGluMlp(torch.from_numpy(wg), torch.from_numpy(wu), torch.from_numpy(wd), "fp8", tp=world, rank=rank)
+        if not layer.fused_reduce:                           # no multicast mapping on this fabric: nothing to test
+            q.put((rank, None))
+            dist.barrier()
+            dist.destroy_process_group()
+            return
+        plain = TpSwiGluMlp(torch.from_numpy(wg), torch.from_numpy(wu), torch.from_numpy(wd), "fp8", tp=world, rank=rank)
+        plain.fused_reduce = False
+        plain.split_reduce = False
+        for i, m in enumerate(ms):
+            xb = orc.f32_to_bf16_bits(orc.gaussian((m, hidden), 1.0, 20 + i))
+            x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+            y = layer.forward(x)
+            want = plain.forward(x)                          # GEMM, barrier, in-switch reduce, barrier: the same bf16 partials, the same sum
+            torch.cuda.synchronize()
+            assert layer._fused_calls == i + 1
+            errs.append(float((y.float() - want.float()).abs().max() / want.float().abs().max()))
+        errs.append(float(ops.handle(torch.cuda.current_device()).device_status()))
+    q.put((rank, errs))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tp_mlp_fused_reduce_two_gpus():
+    """The down projection with the all-reduce fused in (tiles summed in the switch under the MMAs of later tiles) against
+    the unfused in-switch path: several calls (both sets of flag words, changing tile counts), two layer sizes."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_fused_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for _, errs in res:
+        if errs is None:
+            pytest.skip("no multicast mapping")
+        for e in errs:
+            assert e <= 1e-6, errs                           # the same partials through the same reduction: identical results
+
+
 @pytest.fixture(scope="module")
 def llama70b_weights(orc):
     """Gate, up and down weights of the benchmark's layer (hidden 8192, intermediate 28672), N(0, 0.02).  One Gaussian

@@ -43,6 +43,7 @@ struct GemmParams {
     uint32_t* ar_flags;               // this rank's replica of the flag words: [items] arrivals, then one word of finished units
     uint32_t* ar_mc_flags;            // the flag words through the multicast mapping
     int ar_world, ar_rank;
+    int ar_sleep_ns;                  // pause between two looks at a flag word (0: none)
 };
 
 template <int KIND, int BN>
@@ -402,8 +403,8 @@ constexpr int T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + 2048;
 // ---- all-reduce fused into the CTA-pair kernel (AR = true) ----------------------------------------------------------
 // Every rank of a tensor-parallel group runs this kernel on its K-shard and writes its partial tiles into its replica of
 // a symmetric buffer.  When an epilogue warp has stored its 32 rows of a tile it adds one to the tile's arrival word on
-// every rank (multimem.red through the NVSwitch).  Tile w belongs to rank w % world: four more warps per CTA, the
-// reducers, take the owned tiles in strips of 16 rows, wait until every epilogue warp of every rank has arrived
+// every rank (multimem.red through the NVSwitch).  Tile w belongs to rank w % world: sixteen more warps per CTA, the
+// reducers, take the owned tiles in strips of 8 rows, wait until every epilogue warp of every rank has arrived
 // (8 * world), pull the sum of all replicas with multimem.ld_reduce (the switch adds in f32) and push it to every
 // replica with multimem.st, then add one to the word of finished units on every rank.  CTA 0 leaves only when every
 // unit of every rank is finished, so the kernel that follows in the stream finds the complete sum in its replica; it
@@ -413,19 +414,21 @@ constexpr int T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + 2048;
 __device__ __forceinline__ void mm_red_add_u32(uint32_t* mc_addr, uint32_t v) {
     asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_addr), "r"(v) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* addr) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
-    return v;
-}
-__device__ __forceinline__ bool wait_word_at_least(const uint32_t* addr, uint32_t target) {
-    if (ld_acquire_sys_u32(addr) >= target) return true;
-    const uint64_t t0 = globaltimer_ns();
-    for (uint32_t it = 0; it < 0x40000000u; ++it) {
-        if (ld_acquire_sys_u32(addr) >= target) return true;
-        if ((it & 63u) == 63u && globaltimer_ns() - t0 > kWaitLimitNs) return false;
+// Polls with plain system-scope loads and a short sleep between them (hundreds of warps wait at the same time next to
+// the MMA pipeline: they must not crowd the L2); one acquire fence once the word has arrived.
+__device__ __forceinline__ bool wait_word_at_least(const uint32_t* addr, uint32_t target, int sleep_ns) {
+    auto peek = [&]() { uint32_t v; asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory"); return v; };
+    bool ok = peek() >= target;
+    if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        for (uint32_t it = 0; it < 0x40000000u; ++it) {
+            if (sleep_ns > 0) __nanosleep(sleep_ns);
+            if (peek() >= target) { ok = true; break; }
+            if ((it & 63u) == 63u && globaltimer_ns() - t0 > kWaitLimitNs) break;
+        }
     }
-    return false;
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    return ok;
 }
 __device__ __forceinline__ uint4 mm_ld_reduce_bf16x8(const void* mc_addr) {
     uint4 r;
@@ -437,7 +440,8 @@ __device__ __forceinline__ void mm_st_bf16x8(void* mc_addr, const uint4& r) {
     asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
                  ::"l"(mc_addr), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w) : "memory");
 }
-constexpr int AR_THREADS = NUM_THREADS + 128;                      // + four reducer warps
+constexpr int AR_WARPS = 16;                                       // reducer warps per CTA
+constexpr int AR_THREADS = NUM_THREADS + 32 * AR_WARPS;
 
 template <int KIND, int EPI, bool GENERIC = false, bool AR = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(AR ? AR_THREADS : NUM_THREADS, 1)
@@ -609,50 +613,42 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             if (AR) {
                 // this warp's 32 rows of the tile are stored: one arrival on every rank (lane 0's release, after the warp
                 // has met, covers the stores of all its lanes)
-                if (lane == 0) { __threadfence_system(); mm_red_add_u32(p.ar_mc_flags + w, 1u); }
+                if (lane == 0) mm_red_add_u32(p.ar_mc_flags + w, 1u);
             }
         }
     } else {
-        // ------------------------------------------------------------------ reducers (AR only: 4 warps, both CTAs)
-        // A unit is a strip of 16 rows x 256 columns of an owned tile; the reducer warps of the whole grid take the
+        // ------------------------------------------------------------------ reducers (AR only: 16 warps, both CTAs)
+        // A unit is a strip of 8 rows x 256 columns of an owned tile; the reducer warps of the whole grid take the
         // units in order, each warp on its own (no CTA-wide meeting point anywhere in this role).
         const int world = p.ar_world;
         const int owned = num_work > p.ar_rank ? (num_work - p.ar_rank + world - 1) / world : 0;   // items w = rank, rank + world, ...
-        const int units = owned * 16;
+        const int units = owned * 32;
         const uint32_t arrive_target = 8u * (uint32_t)world;            // 2 CTAs x 4 epilogue warps per rank
         char* mc_y = reinterpret_cast<char*>(p.ar_mc_y);
         bool ok = true;
-        for (int u = (int)blockIdx.x * 4 + (warp - 6); u < units && ok; u += (int)gridDim.x * 4) {
-            const int w = (u >> 4) * world + p.ar_rank, strip = u & 15;
+        for (int u = (int)blockIdx.x * AR_WARPS + (warp - 6); u < units && ok; u += (int)gridDim.x * AR_WARPS) {
+            const int w = (u >> 5) * world + p.ar_rank, strip = u & 31;
             int tm, tn;
             tile_coords(w, tiles_m, tiles_n, p.group_m, tm, tn);
-            if (lane == 0) ok = wait_word_at_least(p.ar_flags + w, arrive_target);
+            if (lane == 0) ok = wait_word_at_least(p.ar_flags + w, arrive_target, p.ar_sleep_ns);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) { if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
-            // 16 rows x 256 columns of bf16 = 16 x 32 vectors of 16 bytes; four vectors in flight per lane
-            const int row0 = tm * BM2 + strip * 16, col0 = tn * BN2;
-#pragma unroll 1
-            for (int v0 = lane; v0 < 16 * 32; v0 += 32 * 4) {
-                uint4 val[4];
-                char* at[4];
-                bool in[4];
+            // 8 rows x 256 columns of bf16 = 8 x 32 vectors of 16 bytes: eight vectors in flight per lane, one round trip
+            const int row0 = tm * BM2 + strip * 8, col0 = tn * BN2 + (lane << 3);
+            uint4 val[8];
+            const bool col_in = col0 < p.n;
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const int v = v0 + j * 32, r = row0 + (v >> 5), c = col0 + ((v & 31) << 3);
-                    in[j] = r < p.m && c < p.n;
-                    at[j] = mc_y + ((size_t)r * p.ldy + c) * 2;
-                    if (in[j]) val[j] = mm_ld_reduce_bf16x8(at[j]);
-                }
+            for (int j = 0; j < 8; j++)
+                if (col_in && row0 + j < p.m) val[j] = mm_ld_reduce_bf16x8(mc_y + ((size_t)(row0 + j) * p.ldy + col0) * 2);
 #pragma unroll
-                for (int j = 0; j < 4; j++)
-                    if (in[j]) mm_st_bf16x8(at[j], val[j]);
-            }
+            for (int j = 0; j < 8; j++)
+                if (col_in && row0 + j < p.m) mm_st_bf16x8(mc_y + ((size_t)(row0 + j) * p.ldy + col0) * 2, val[j]);
             __syncwarp();
-            if (lane == 0) { __threadfence_system(); mm_red_add_u32(p.ar_mc_flags + num_work, 1u); }
+            if (lane == 0) mm_red_add_u32(p.ar_mc_flags + num_work, 1u);
         }
         if (blockIdx.x == 0 && warp == 6) {
-            // the last to leave: every unit of every rank is finished (16 per item), then this call's words are cleared
-            if (lane == 0 && ok && !wait_word_at_least(p.ar_flags + num_work, 16u * (uint32_t)num_work)) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT);
+            // the last to leave: every unit of every rank is finished (32 per item), then this call's words are cleared
+            if (lane == 0 && ok && !wait_word_at_least(p.ar_flags + num_work, 32u * (uint32_t)num_work, p.ar_sleep_ns)) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT);
             __syncwarp();
             for (int i = lane; i <= num_work; i += 32) p.ar_flags[i] = 0u;
             __threadfence_system();
@@ -1209,6 +1205,9 @@ int32_t oxq_gemm_fp8_all_reduce(oxq_handle* h, int64_t m, int64_t n, int64_t k, 
     const int64_t set = (call_index & 1) * (flag_words / 2);
     p.ar_mc_y = y_multicast; p.ar_flags = flags_local + set; p.ar_mc_flags = flags_multicast + set;
     p.ar_world = world; p.ar_rank = rank;
+    // pause between two looks at a flag word: 232 us for the tensor-parallel down projection on two GPUs at 1000 ns against 241 at 0
+    static const int sleep_ns = [] { const char* e = getenv("OXQ_AR_SLEEP_NS"); const int v = e ? atoi(e) : 1000; return v < 0 ? 0 : v; }();
+    p.ar_sleep_ns = sleep_ns;
     return launch2_ar(h, x, ldx, w, ldw, p);
 }
 

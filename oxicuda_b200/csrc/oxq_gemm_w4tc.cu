@@ -33,7 +33,7 @@ constexpr int RAW_BYTES = ROWS * 128;      // 16 KB
 constexpr int A_COLS = 128;                // tensor-memory columns of one unpacked unit (two groups of 128 bf16 per lane)
 constexpr int A_SLOTS = 2;                 // units of unpacked weights in tensor memory
 constexpr int U_SLOTS = 4;                 // units of activations in shared memory == units of accumulators in tensor memory
-constexpr int UNPACK_WARPS = 16;           // four per group quarter: a thread unpacks 64 codes of one weight row per unit
+constexpr int UNPACK_WARPS = 8;            // 8 or 16 (measured alike): with 8 a thread unpacks one group (128 codes) of a weight row per unit
 constexpr int NUM_WARPS = 7 + UNPACK_WARPS; // 0: codes TMA, 1: X TMA, 2: MMA + tensor-memory owner, 3-6: epilogue, 7-: unpack
 constexpr int NUM_THREADS = NUM_WARPS * 32;
 constexpr int SMEM_BUDGET = 227 * 1024;
@@ -306,10 +306,10 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
         if (ok && cur_rb >= 0) flush(cur_rb, seg_groups);
         if (ok) finish_pending();
     } else {
-        // ------------------------------------------------------------------ unpack (16 warps)
-        // Warps 7-14 take the first group of every unit, warps 15-22 the second, four warps per half group; a warp
-        // serves the tensor-memory lane quarter it may access (warp index mod 4) and a thread owns half a group of one
-        // weight row: 32 bytes of codes in, 32 columns of bf16 pairs out.
+        // ------------------------------------------------------------------ unpack (UNPACK_WARPS warps)
+        // The first half of the unpack warps takes the first group of every unit, the second half the second; a warp
+        // serves the tensor-memory lane quarter it may access (warp index mod 4) and a thread owns a group of one weight
+        // row, or half of it with 16 warps: 64 (32) bytes of codes in, 64 (32) columns of bf16 pairs out.
         constexpr int JJ = 32 / UNPACK_WARPS;                    // 16-byte pieces of a row's group per thread
         const int part = (warp - 7) >> 2, half = part / (UNPACK_WARPS / 8), sub = part % (UNPACK_WARPS / 8), quarter = warp & 3;
         const int r = quarter * 32 + lane;                       // row inside the block == tensor-memory lane

@@ -595,6 +595,35 @@ def tp_phases(torch, ops, layer, x, steps=10):
     }
 
 
+def tp_attention_projections(torch, world, rank, peaks):
+    """Configuration 3's attention projections under tensor parallelism, FP8: QKV (6144 x 4096) column-parallel with the
+    all-gather of ColumnLinear::all_gather, O (4096 x 4096) row-parallel with the all-reduce of RowLinear::all_reduce.
+    The first 4096 gathered columns stand in for the attention output.  Returns per-batch times and the largest deviation
+    from the same two products computed in f32 from the bf16 weights (two FP8 GEMMs deep: a sanity figure, the parity
+    tests of the two layers hold the 1e-2 bar per GEMM)."""
+    from oxicuda_b200.dist_infer import ColumnLinear, RowLinear
+    g = torch.Generator(device="cuda").manual_seed(11)
+    wqkv = (torch.randn((6144, 4096), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    wo = (torch.randn((4096, 4096), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    col = ColumnLinear.from_full_weight(4096, 6144, wqkv, None, world, rank, "fp8")
+    row = RowLinear.from_full_weight(4096, 4096, wo, None, world, rank, "fp8")
+    out = {}
+    for m in (2048, 32):
+        x = torch.randn((m, 4096), generator=g, device="cuda").to(torch.bfloat16)
+
+        def step():
+            qkv = col.forward(x)                                  # local GEMM, all-gather -> [m x 6144]
+            return row.forward(qkv[:, :4096])                     # slice, local GEMM, all-reduce -> [m x 4096]
+        for _ in range(3):
+            y = step()
+        ms = time_region(torch, step, 20, True) / 20
+        ref = ((x.float() @ wqkv.float().T)[:, :4096].to(torch.bfloat16).float() @ wo.float().T)
+        err = float((y.float() - ref).abs().max() / ref.abs().max())
+        flop = 2.0 * m * 4096 * (6144 + 4096)
+        out[f"m{m}"] = {"ms": round(ms, 4), "TFLOP/s_all_ranks": round(flop / (ms * 1e-3) / 1e12, 1), "max_rel_vs_f32": round(err, 4)}
+    return out
+
+
 def run_tp_mlp(args, torch, world, rank, local_rank, peaks):
     """N > 1: the tensor-parallel FP8 SwiGLU MLP (hidden 8192, intermediate 28672, M = 2048), weights sharded over
     the ranks, partial sums combined in the NVSwitch (or by one NCCL all-reduce).  Strong scaling: the layer is fixed."""
@@ -649,6 +678,7 @@ def run_tp_mlp(args, torch, world, rank, local_rank, peaks):
             layer.forward(xs)
         t = time_region(torch, lambda: layer.forward(xs), 20, True) / 20
         small[f"m{mm}"] = {"ms": round(t, 4), "weight_GB/s_all_ranks": round(world * layer.weight_bytes_local() / (t * 1e-3) / 1e9, 1)}
+    attn = tp_attention_projections(torch, world, rank, peaks) if variant == "fp8" else None
     # End to end: pinned host activations in, reduced result out, every step, the host traffic sharded over the ranks:
     # every rank copies its 1/N of the rows of X in over its own PCIe link, the ranks all-gather X over NVLink, and every
     # rank copies its own 1/N of the rows of the result out.  Consecutive steps are double-buffered over three streams.
@@ -731,6 +761,8 @@ def run_tp_mlp(args, torch, world, rank, local_rank, peaks):
                     "overlap": "every rank copies 1/N of the rows of X in and 1/N of the rows of the result out over its own PCIe link; X is all-gathered over NVLink; steps double-buffered over three streams"},
             "gpu_launches": args.steps * kernels_per_step * stats["repeats"], "clocks": clocks, "extras": {"decode_points": small},
         }
+        if attn is not None:
+            line["extras"]["qkv_o_projections_fp8"] = attn
         if parity is not None:
             line["parity"] = parity
         if phases is not None:

@@ -220,27 +220,22 @@ scaled_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
     }
 }
 
-// OXQ_DEC_KSPLIT = 1..8 fixes the K split (tuning runs); 0 or unset: chosen per shape.
+// OXQ_DEC_KSPLIT = 1, 2, 4 or 8 fixes the K split (tuning runs); 0 or unset: chosen per shape.
 static int ksplit_override() {
-    static const int v = [] { const char* e = getenv("OXQ_DEC_KSPLIT"); const int x = e ? atoi(e) : 0; return (x >= 1 && x <= 8) ? x : 0; }();
+    static const int v = [] { const char* e = getenv("OXQ_DEC_KSPLIT"); const int x = e ? atoi(e) : 0; return (x == 1 || x == 2 || x == 4 || x == 8) ? x : 0; }();
     return v;
 }
 
-// K split that finishes first under a simple model: an SM streams for the CTAs it is given one after the other (two
-// resident CTAs share its bandwidth), so the time is that of the SM with the most CTAs, ceil(CTAs / SMs) of them, each
-// costing its K blocks plus a fixed set-up of about one and a half blocks' worth of time.
+// Clusters cost scheduling freedom (their CTAs have to start together inside one GPC; sizes that are not powers of two
+// pack badly), so K is split only when the row tiles alone leave much of the machine idle: the smallest power of two
+// that gives at least 0.7 CTAs per SM.  Measured at 8 batch rows, MXFP8, K splits 1 / 2 / 4 / 8: 14336 x 4096 (112
+// tiles) 12.5 / 13.5 / 16.8 / 22.8 us, 57344 x 8192 (448 tiles) 75 / 83 / 87 / 104 us, 4096 x 14336 (32 tiles) 28.2 /
+// 17.9 / 13.8 / 13.8 us, 6144 x 4096 (48 tiles) 10.4 / 8.9 / 8.1 / 11.6 us.
 static int choose_ksplit(int tiles, int num_kb, int sm_count) {
     if (const int o = ksplit_override()) return o <= num_kb ? o : 1;
-    int best = 1; double best_cost = 1e30;
-    for (int ks = 1; ks <= 8; ks++) {
-        const int per = (num_kb + ks - 1) / ks;
-        if (ks > 1 && per < 2) break;
-        const int64_t ctas = (int64_t)tiles * ks;
-        const int64_t most = (ctas + sm_count - 1) / sm_count;
-        const double cost = (double)most * (per + 1.5) + (ks > 1 ? 0.5 : 0.0);
-        if (cost < best_cost - 1e-9) { best_cost = cost; best = ks; }
-    }
-    return best;
+    int ks = 1;
+    while (ks < 8 && (int64_t)tiles * ks * 10 < (int64_t)sm_count * 7 && num_kb / (ks * 2) >= 2) ks *= 2;
+    return ks;
 }
 
 template <int KIND, int BN>

@@ -966,6 +966,19 @@ def run_case(args):
         fn = lambda: ops.fp8_quant(x, one, out=q)  # noqa: E731
         work, unit = 3.0 * sz * sz, "GB/s"
         m = n = k = sz
+    elif args.case in ("mxfp8_quant", "nvfp4_quant"):
+        rows_, k = 14336 * sz // 8192, 4096                              # --size 8192: the 14336 x 4096 weight of configuration 4
+        x = torch.randn((rows_, k), generator=g, device="cuda").to(torch.bfloat16)
+        fn = (lambda: ops.mxfp8_quant(x)) if args.case == "mxfp8_quant" else (lambda: ops.nvfp4_quant(x))  # noqa: E731
+        nel = rows_ * k
+        work, unit = float(nel * 2 + nel + 2 * nel // 32) if args.case == "mxfp8_quant" else float(2 * nel * 2 + nel // 2 + 2 * nel // 16), "GB/s"
+        m, n = rows_, k
+    elif args.case == "int4g_quant":
+        n, k = 14336 * sz // 8192, 4096
+        x = torch.randn((n, k), generator=g, device="cuda") * 0.02
+        fn = lambda: ops.int4g_quant_pack(x, 128)  # noqa: E731
+        work, unit = float(n * k * 4 + n * k // 2 + n * k // 128 * 2 + n * k // 256), "GB/s"
+        m = n
     elif args.case == "int8_quant_rows":
         x = torch.randn((sz, sz), generator=g, device="cuda") * 0.02
         fn = lambda: ops.int8_quant_rows(x)  # noqa: E731
@@ -1076,7 +1089,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--peaks", default=None, help="JSON file with hbm_gbs / bf16_tflops / bf16_tflops_sustained (default: the pool's measured peaks beside this script)")
-    ap.add_argument("--case", default=None, help="single-kernel mode, e.g. gemm_fp8, gemm_mxfp8, gemm_nvfp4, fp8_quant, gemm_w4a16, gemm_fp8_decode, gemm_mxfp8_decode, gemm_nvfp4_decode, nf4_quant, gemm_nf4")
+    ap.add_argument("--case", default=None, help="single-kernel mode, e.g. gemm_fp8, gemm_mxfp8, gemm_nvfp4, fp8_quant, mxfp8_quant, nvfp4_quant, int4g_quant, int8_quant_rows, gemm_w4a16, gemm_fp8_decode, gemm_mxfp8_decode, gemm_nvfp4_decode, nf4_quant, gemm_nf4")
     ap.add_argument("--size", type=int, default=8192)
     ap.add_argument("--m", type=int, default=8)
     args = ap.parse_args()

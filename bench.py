@@ -49,7 +49,7 @@ M = N = K = 8192
 FLOP = 2.0 * M * N * K
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline GEMM kernel, from an ncu capture of
 # `bench.py --case gemm_fp8` (algorithmic operand + output bytes: 268435456)
-NCU_DRAM_BYTES_PER_LAUNCH = 364_810_240
+NCU_DRAM_BYTES_PER_LAUNCH = 344_340_736
 L2_BYTES = 126 * 1024 * 1024
 PEAKS_FILE = os.path.join(ROOT, "MEASURED_PEAKS.json")
 MAX_REL = 1e-2
@@ -92,7 +92,7 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
             out = ""
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
@@ -102,13 +102,20 @@ class ClockSampler:
                 mx.append(float(f[2]))
             except ValueError:
                 continue
+            try:
+                pw.append(float(f[3]))
+            except ValueError:
+                pw.append(0.0)
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        top = sorted(sm)[len(sm) // 2:]                   # samples under load = upper half
-        return {"sm_mhz": statistics.median(top), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        # the timed regions alternate with idle gaps: the samples under load are those near the highest power draw seen
+        top_w = max(pw)
+        load = [c for c, w in zip(sm, pw) if w >= 0.6 * top_w] or sm
+        return {"sm_mhz": statistics.median(load), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
+                "samples_under_load": len(load), "power_w_max": top_w}
 
 
 HIDDEN, INTER = 8192, 28672          # Llama-3-70B MLP shape
@@ -817,10 +824,10 @@ def run_ours(args):
     sampler = ClockSampler(local_rank)
     sampler.start()
     ms_per_step, stats = timed_median(torch, step, args.steps, False)
-    clocks = sampler.stop()
     value = FLOP / (ms_per_step * 1e-3) / 1e12
     sus_ms = sustained_rate(torch, step, args.steps)
     sus_value = FLOP / (sus_ms * 1e-3) / 1e12
+    clocks = sampler.stop()                               # samples of the timed regions and of the sustained loop after them
 
     # ---- end to end through host buffers ------------------------------------------------------
     # Every step copies both bf16 operands from pinned host memory, quantises them, multiplies and copies the bf16

@@ -1113,6 +1113,17 @@ static bool fp8_gemv_setting() {
     return on;
 }
 
+// FP8 / W8A8 GEMMs with dense_decode_min_m() < m <= dense_decode_max_m() batch rows take the tensor-core weight-streaming
+// kernel (OXQ_DENSE_DECODE_MAX_M, 0..64, 0 = never; OXQ_DENSE_DECODE_MIN_M: batches up to this size stay on the GEMV).
+static int dense_decode_max_m() {
+    static const int v = [] { const char* e = getenv("OXQ_DENSE_DECODE_MAX_M"); const int x = e ? atoi(e) : 32; return x < 0 ? 0 : (x > 64 ? 64 : x); }();
+    return v;
+}
+static int dense_decode_min_m() {
+    static const int v = [] { const char* e = getenv("OXQ_DENSE_DECODE_MIN_M"); const int x = e ? atoi(e) : 0; return x < 0 ? 0 : x; }();
+    return v;
+}
+
 // largest batch served by the GEMV (OXQ_FP8_GEMV_MAX_M, 0..8, default 8)
 static int fp8_gemv_max_m() {
     static const int v = [] { const char* e = getenv("OXQ_FP8_GEMV_MAX_M"); const int x = e ? atoi(e) : 8; return x < 0 ? 0 : (x > 8 ? 8 : x); }();
@@ -1125,7 +1136,9 @@ static int32_t gemm_fp8_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, con
     if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
     if (!sx || !sw) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
     if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
-    if (m <= fp8_gemv_max_m() && beta == 0.0f && fp8_gemv_setting()) {             // decode shapes: the weight stream is the whole cost
+    if (m <= dense_decode_max_m() && m > dense_decode_min_m() && beta == 0.0f)     // decode shapes: the weight stream is the whole cost
+        return oxq_scaled_decode_launch(h, KIND_F8, (int)m, (int)n, (int)k, x, ldx, nullptr, w, ldw, nullptr, sx, sw, alpha, y, ldy);
+    if (m <= fp8_gemv_max_m() && beta == 0.0f && fp8_gemv_setting()) {
         if (int32_t rc = oxq_require_sm100(h)) return rc;
         OXQ_CUDA(h, oxq_fp8_gemv_launch(h, (int)m, (int)n, (int)k, x, ldx, w, ldw, sx, sw, alpha, y, ldy, false));
         return OXQ_OK;
@@ -1268,6 +1281,9 @@ int32_t oxq_gemm_w8a8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const int8
     if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
     if (!sx_rows || !sw_rows) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
     if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
+    if (m <= dense_decode_max_m() && m > dense_decode_min_m())
+        return oxq_scaled_decode_launch(h, KIND_I8, (int)m, (int)n, (int)k, (const uint8_t*)x, ldx, nullptr, (const uint8_t*)w, ldw, nullptr, sx_rows,
+                                        sw_rows, 1.0f, y, ldy);
     if (m <= fp8_gemv_max_m() && fp8_gemv_setting()) {             // decode shapes: mma.sync s8 on the raw bytes, exact s32 sums
         OXQ_CUDA(h, oxq_fp8_gemv_launch(h, (int)m, (int)n, (int)k, (const uint8_t*)x, ldx, (const uint8_t*)w, ldw, sx_rows, sw_rows, 1.0f, y, ldy,
                                         false, true));
@@ -1294,7 +1310,7 @@ int32_t oxq_gemm_mxfp8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uin
     if (!sfx || !sfw || ((uintptr_t)sfx & 15u) || ((uintptr_t)sfw & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned scale-factor pointer");
     if (k & 127) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k must be a multiple of 128 for the MXFP8 GEMM");
     if (m <= scaled_decode_max_m())
-        return oxq_scaled_decode_launch(h, KIND_MXF8, (int)m, (int)n, (int)k, x, sfx, w, sfw, nullptr, nullptr, y, ldy);
+        return oxq_scaled_decode_launch(h, KIND_MXF8, (int)m, (int)n, (int)k, x, k, sfx, w, k, sfw, nullptr, nullptr, 1.0f, y, ldy);
     GemmParams p{};
     p.alpha = 1.0f; p.beta = 0.0f;
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y; p.ldy = ldy;
@@ -1311,7 +1327,7 @@ int32_t oxq_gemm_nvfp4(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uin
     if (!sfx || !sfw || !gx || !gw || ((uintptr_t)sfx & 15u) || ((uintptr_t)sfw & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned scale pointer");
     if (k & 255) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k must be a multiple of 256 for the NVFP4 GEMM");
     if (m <= scaled_decode_max_m())
-        return oxq_scaled_decode_launch(h, KIND_NVF4, (int)m, (int)n, (int)(k / 2), x, sfx, w, sfw, gx, gw, y, ldy);
+        return oxq_scaled_decode_launch(h, KIND_NVF4, (int)m, (int)n, (int)(k / 2), x, k / 2, sfx, w, k / 2, sfw, gx, gw, 1.0f, y, ldy);
     GemmParams p{};
     p.alpha = 1.0f; p.beta = 0.0f;
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)(k / 2); p.y = y; p.ldy = ldy; p.s0 = gx; p.s1 = gw;

@@ -1,6 +1,7 @@
 // Decode shapes (1 to 64 batch rows) of the block-scaled GEMMs, Fp4GemmConfig's memory-bound regime
 // (crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:337-395; the reference's kernel unpacks FP4 in registers,
-// generate_fp4_gemm_ptx :1237-1362 and the dequantisation at :1481-1579).
+// generate_fp4_gemm_ptx :1237-1362 and the dequantisation at :1481-1579), and of the FP8 and W8A8 GEMMs (no scale
+// factors to move: the per-tensor or per-row scales are applied when the accumulator is drained).
 //
 // Here the operands swap sides: the weight W[N x K] is the 128-row A operand of tcgen05.mma and the batch X[M x K] its
 // narrow N side (16, 32 or 64 columns), D[128 weight rows x batch] = W_tile . X^T.  Every byte of the weight stream
@@ -28,16 +29,18 @@ constexpr int SMEM_PER_CTA = 112 * 1024;    // two CTAs per SM
 struct DecParams {
     int m, n, k_bytes;
     int ksplit;                       // CTAs of a cluster that share the K range of one tile
-    const uint8_t* sfw; const uint8_t* sfx;   // tiled scale factors of W and X
+    const uint8_t* sfw; const uint8_t* sfx;   // tiled scale factors of W and X (block-scaled kinds)
     int sf_col_tiles;                 // 4-column scale-factor tiles per 128-row tile
-    const float* gx; const float* gw; // NVFP4: per-tensor scales
+    const float* gx; const float* gw; // NVFP4 / FP8: per-tensor scales; W8A8: per-row scales of X [m] and of W [n]
+    float alpha;
     __nv_bfloat16* y; int64_t ldy;
     int32_t* status;
 };
 
 template <int KIND, int BN>
 struct Cfg {
-    static constexpr int kSfChunks = KIND == KIND_MXF8 ? 1 : 4;          // 512-byte scale-factor chunks per stage and operand
+    static constexpr bool kScaled = KIND == KIND_MXF8 || KIND == KIND_NVF4;
+    static constexpr int kSfChunks = KIND == KIND_MXF8 ? 1 : (KIND == KIND_NVF4 ? 4 : 0);   // 512-byte scale-factor chunks per stage and operand
     static constexpr int kSfBytes = kSfChunks * 512;
     static constexpr int kABytes = BM * BKB;
     static constexpr int kBBytes = BN * BKB;
@@ -108,15 +111,18 @@ scaled_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
                 mbar_arrive_expect_tx(full, C::kStageBytes);
                 tma_load_2d(sm_a + stage * C::kABytes, &tm_w, kb * BKB, n0, full);
                 tma_load_2d(sm_b + stage * C::kBBytes, &tm_x, kb * BKB, 0, full);
-                bulk_load(sm_sfa + stage * C::kSfBytes, sfw_tile + (size_t)kb * C::kSfBytes, C::kSfBytes, full);
-                bulk_load(sm_sfb + stage * C::kSfBytes, p.sfx + (size_t)kb * C::kSfBytes, C::kSfBytes, full);
+                if (C::kScaled) {
+                    bulk_load(sm_sfa + stage * C::kSfBytes, sfw_tile + (size_t)kb * C::kSfBytes, C::kSfBytes, full);
+                    bulk_load(sm_sfb + stage * C::kSfBytes, p.sfx + (size_t)kb * C::kSfBytes, C::kSfBytes, full);
+                }
             }
             __syncwarp();
             if (++stage == S) { stage = 0; phase ^= 1; }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (whole warp, one elected lane issues)
-        constexpr uint32_t idesc = KIND == KIND_MXF8 ? idesc_block_scaled(0, 0, 1, BM, BN) : idesc_block_scaled(1, 1, 0, BM, BN);
+        constexpr uint32_t idesc = KIND == KIND_F8 ? idesc_dense(1, 0, 0, BM, BN) : KIND == KIND_I8 ? idesc_dense(2, 1, 1, BM, BN) :
+                                   KIND == KIND_MXF8 ? idesc_block_scaled(0, 0, 1, BM, BN) : idesc_block_scaled(1, 1, 0, BM, BN);
         int stage = 0; uint32_t phase = 0;
         bool ok = true;
         for (int it = 0; it < kb_hi - kb_lo; it++) {
@@ -134,7 +140,9 @@ scaled_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
                 for (int k = 0; k < BKB / 32; k++) {
                     const uint64_t a = adesc + (uint64_t)(k * 2), b = bdesc + (uint64_t)(k * 2);
                     const uint32_t accum = (it | k) != 0;
-                    if (KIND == KIND_MXF8)                        // one scale per row and MMA: byte k of the chunk's 32-bit words
+                    if (KIND == KIND_F8) mma_f8f6f4(tmem_base, a, b, idesc, accum);
+                    else if (KIND == KIND_I8) mma_i8(tmem_base, a, b, idesc, accum);
+                    else if (KIND == KIND_MXF8)                   // one scale per row and MMA: byte k of the chunk's 32-bit words
                         mma_mxf8f6f4(tmem_base, a, b, idesc_with_sf_ids(idesc, k, k), accum, tmem_base + C::kSfaCol, tmem_base + C::kSfbCol);
                     else                                          // four scales per row and MMA: chunk k, all four bytes
                         mma_mxf4nvf4_x4(tmem_base, a, b, idesc, accum, tmem_base + C::kSfaCol + 4 * k, tmem_base + C::kSfbCol + 4 * k);
@@ -170,12 +178,21 @@ scaled_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
                 for (int j = 0; j < 16; j++) acc[c * 16 + j] = __uint_as_float(r[j]);
             }
         }
+        // accumulator (or sum of the cluster's accumulators) of batch row j -> bf16 output.  W8A8 sums are exact integers and
+        // take the same scale expression as the 128-row kernel, (float)acc * (sx[m] * alpha * sw[n]).
+        const float scale = (KIND == KIND_NVF4 || KIND == KIND_F8) ? __ldg(p.gx) * __ldg(p.gw) * p.alpha : p.alpha;
+        const float sw_row = (KIND == KIND_I8 && n0 + i < p.n) ? __ldg(p.gw + n0 + i) : 0.0f;
+        auto emit = [&](int j, uint32_t bits) {
+            float v;
+            if (KIND == KIND_I8) v = (float)(int)bits * ((__ldg(p.gx + j) * p.alpha) * sw_row);
+            else v = __uint_as_float(bits) * scale;
+            p.y[(size_t)j * p.ldy + n0 + i] = __float2bfloat16_rn(v);
+        };
         if (p.ksplit == 1) {
-            const float scale = KIND == KIND_NVF4 ? __ldg(p.gx) * __ldg(p.gw) : 1.0f;
             if (n0 + i < p.n) {
 #pragma unroll
                 for (int j = 0; j < BN; j++)
-                    if (j < p.m) p.y[(size_t)j * p.ldy + n0 + i] = __float2bfloat16_rn(acc[j] * scale);
+                    if (j < p.m) emit(j, __float_as_uint(acc[j]));
             }
         }
         tc_fence_before();
@@ -196,11 +213,18 @@ scaled_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
                 }
             }
             cluster_sync_all();
-            const float scale = KIND == KIND_NVF4 ? __ldg(p.gx) * __ldg(p.gw) : 1.0f;
             for (int slot = 0, j = (int)crank; j < p.m; slot++, j += p.ksplit) {
-                float v = 0.0f;
-                for (int c = 0; c < p.ksplit; c++) v += part[(c * per + slot) * BM + i];
-                if (n0 + i < p.n) p.y[(size_t)j * p.ldy + n0 + i] = __float2bfloat16_rn(v * scale);
+                uint32_t bits;
+                if (KIND == KIND_I8) {
+                    int v = 0;
+                    for (int c = 0; c < p.ksplit; c++) v += (int)__float_as_uint(part[(c * per + slot) * BM + i]);
+                    bits = (uint32_t)v;
+                } else {
+                    float v = 0.0f;
+                    for (int c = 0; c < p.ksplit; c++) v += part[(c * per + slot) * BM + i];
+                    bits = __float_as_uint(v);
+                }
+                if (n0 + i < p.n) emit(j, bits);
             }
         }
     }
@@ -270,27 +294,33 @@ static int32_t launch(oxq_handle* h, const CUtensorMap& tm_w, const CUtensorMap&
 }  // namespace tcdec
 }  // namespace oxq
 
-int32_t oxq_scaled_decode_launch(oxq_handle* h, int kind, int m, int n, int k_bytes, const uint8_t* x, const uint8_t* sfx, const uint8_t* w,
-                                 const uint8_t* sfw, const float* gx, const float* gw, void* y, int64_t ldy) {
+int32_t oxq_scaled_decode_launch(oxq_handle* h, int kind, int m, int n, int k_bytes, const uint8_t* x, int64_t ldx_bytes, const uint8_t* sfx,
+                                 const uint8_t* w, int64_t ldw_bytes, const uint8_t* sfw, const float* gx, const float* gw, float alpha, void* y,
+                                 int64_t ldy) {
     using namespace oxq::tcdec;
+    using namespace oxq::tc;
     const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
     CUtensorMap tm_w, tm_x;
-    if (!oxq_make_tmap_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, (uint64_t)k_bytes, (uint64_t)n, (uint64_t)k_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !oxq_make_tmap_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, x, (uint64_t)k_bytes, (uint64_t)m, (uint64_t)k_bytes, BKB, (uint32_t)bn, CU_TENSOR_MAP_SWIZZLE_128B))
+    if (!oxq_make_tmap_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, (uint64_t)k_bytes, (uint64_t)n, (uint64_t)ldw_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !oxq_make_tmap_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, x, (uint64_t)k_bytes, (uint64_t)m, (uint64_t)ldx_bytes, BKB, (uint32_t)bn, CU_TENSOR_MAP_SWIZZLE_128B))
         OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "cuTensorMapEncodeTiled failed (pointers must be 16-byte aligned, leading dimensions multiples of 16 bytes)");
     DecParams p;
     p.m = m; p.n = n; p.k_bytes = k_bytes;
     const int num_kb = (k_bytes + BKB - 1) / BKB;
     p.ksplit = choose_ksplit((n + BM - 1) / BM, num_kb, h->sm_count);
     p.sfw = sfw; p.sfx = sfx;
-    p.sf_col_tiles = kind == oxq::tc::KIND_MXF8 ? (k_bytes / 32 + 3) / 4 : (k_bytes / 8 + 3) / 4;
-    p.gx = gx; p.gw = gw; p.y = (__nv_bfloat16*)y; p.ldy = ldy; p.status = h->dev_status;
-    if (kind == oxq::tc::KIND_MXF8) {
-        if (bn == 16) return launch<oxq::tc::KIND_MXF8, 16>(h, tm_w, tm_x, p);
-        if (bn == 32) return launch<oxq::tc::KIND_MXF8, 32>(h, tm_w, tm_x, p);
-        return launch<oxq::tc::KIND_MXF8, 64>(h, tm_w, tm_x, p);
-    }
-    if (bn == 16) return launch<oxq::tc::KIND_NVF4, 16>(h, tm_w, tm_x, p);
-    if (bn == 32) return launch<oxq::tc::KIND_NVF4, 32>(h, tm_w, tm_x, p);
-    return launch<oxq::tc::KIND_NVF4, 64>(h, tm_w, tm_x, p);
+    p.sf_col_tiles = kind == KIND_MXF8 ? (k_bytes / 32 + 3) / 4 : (k_bytes / 8 + 3) / 4;
+    p.gx = gx; p.gw = gw; p.alpha = alpha; p.y = (__nv_bfloat16*)y; p.ldy = ldy; p.status = h->dev_status;
+#define OXQ_DEC_DISPATCH(K)                                                     \
+    do {                                                                        \
+        if (bn == 16) return launch<K, 16>(h, tm_w, tm_x, p);                   \
+        if (bn == 32) return launch<K, 32>(h, tm_w, tm_x, p);                   \
+        return launch<K, 64>(h, tm_w, tm_x, p);                                 \
+    } while (0)
+    if (kind == KIND_MXF8) OXQ_DEC_DISPATCH(KIND_MXF8);
+    if (kind == KIND_NVF4) OXQ_DEC_DISPATCH(KIND_NVF4);
+    if (kind == KIND_F8) OXQ_DEC_DISPATCH(KIND_F8);
+    if (kind == KIND_I8) OXQ_DEC_DISPATCH(KIND_I8);
+#undef OXQ_DEC_DISPATCH
+    OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "operand kind %d has no decode kernel", kind);
 }

@@ -419,7 +419,7 @@ def extras(torch, ops, tab):
     fp8w = [ops.fp8_quant_dynamic(wbig[0]) for _ in range(2)]
     i8w = [ops.int8_quant_rows(wbig[0].float()) for _ in range(2)]
     del wbig
-    for mrows in (1, 8):
+    for mrows in (1, 8, 32):
         xd = torch.randn((mrows, 8192), generator=g, device="cuda").to(torch.bfloat16)
         xq8, sx8 = ops.fp8_quant_dynamic(xd)
         tab.hbm(f"gemm_fp8_m{mrows}_57344x8192", f"fp8_m{mrows}_57344x8192", 57344 * 8192 + mrows * 8192 + 2 * mrows * 57344,

@@ -1231,6 +1231,8 @@ int32_t oxq_gemm_fp8_swiglu(oxq_handle* h, int64_t m, int64_t n2, int64_t k, con
     if (int32_t rc = check_gemm_args(h, m, n2 / 2, k, x, w_gu, hout, ldh)) return rc;
     if (!sx || !sw) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
     if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
+    if (m <= dense_decode_max_m() && m <= 32 && m > dense_decode_min_m())
+        return oxq_scaled_decode_launch(h, KIND_F8, (int)m, (int)n2, (int)k, x, ldx, nullptr, w_gu, ldw, nullptr, sx, sw, 1.0f, hout, ldh, true);
     if (m <= fp8_gemv_max_m() && fp8_gemv_setting()) {
         if (int32_t rc = oxq_require_sm100(h)) return rc;
         OXQ_CUDA(h, oxq_fp8_gemv_launch(h, (int)m, (int)n2, (int)k, x, ldx, w_gu, ldw, sx, sw, 1.0f, hout, ldh, true));

@@ -37,12 +37,16 @@ struct DecParams {
     int32_t* status;
 };
 
-template <int KIND, int BN>
+// SWIGLU (FP8 only): the weight holds blocks of 128 gate rows followed by the 128 matching up rows; a CTA takes one such
+// pair of tiles into two accumulators, so a thread's lane holds gate and up of the same output column and stores
+// silu(gate) * up (SwiGluFfn::forward, crates/oxicuda-lm/src/layer/ffn.rs:235-254).
+template <int KIND, int BN, bool SWIGLU = false>
 struct Cfg {
     static constexpr bool kScaled = KIND == KIND_MXF8 || KIND == KIND_NVF4;
     static constexpr int kSfChunks = KIND == KIND_MXF8 ? 1 : (KIND == KIND_NVF4 ? 4 : 0);   // 512-byte scale-factor chunks per stage and operand
     static constexpr int kSfBytes = kSfChunks * 512;
-    static constexpr int kABytes = BM * BKB;
+    static constexpr int kATiles = SWIGLU ? 2 : 1;
+    static constexpr int kABytes = kATiles * BM * BKB;
     static constexpr int kBBytes = BN * BKB;
     static constexpr int kStageBytes = kABytes + kBBytes + 2 * kSfBytes;
     static constexpr int kStagesFit = (SMEM_PER_CTA - 2048) / kStageBytes;
@@ -52,13 +56,15 @@ struct Cfg {
     static constexpr int kSfaCol = 64, kSfbCol = 64 + 4 * kSfChunks, kCols = 128;
     static_assert(BN == 16 || BN == 32 || BN == 64, "batch tile");
     static_assert(kStages >= 3, "pipeline depth");
-    static_assert((BN + 8) * BM * 4 <= kStages * kABytes, "the partial sums reuse the weight stages");
+    static_assert((BN + 8) * kATiles * BM * 4 <= kStages * kABytes, "the partial sums reuse the weight stages");
+    static_assert(!SWIGLU || (KIND == KIND_F8 && BN <= 32), "SwiGLU form: FP8, up to 32 batch rows");
 };
 
-template <int KIND, int BN>
+template <int KIND, int BN, bool SWIGLU = false>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 scaled_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const DecParams p) {
-    using C = Cfg<KIND, BN>;
+    using C = Cfg<KIND, BN, SWIGLU>;
+    constexpr int AT = C::kATiles;
     constexpr int S = C::kStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -74,7 +80,7 @@ scaled_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t crank = p.ksplit > 1 ? cluster_ctarank() : 0u;
-    const int n0 = (int)blockIdx.x * BM;
+    const int n0 = (int)blockIdx.x * BM * AT;                     // first weight row (SwiGLU: of the gate block; the up block follows)
     const int num_kb = (p.k_bytes + BKB - 1) / BKB;
     const int kb_lo = (int)(((int64_t)crank * num_kb) / p.ksplit), kb_hi = (int)(((int64_t)(crank + 1) * num_kb) / p.ksplit);
 
@@ -110,6 +116,7 @@ scaled_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
             if (elect_one()) {
                 mbar_arrive_expect_tx(full, C::kStageBytes);
                 tma_load_2d(sm_a + stage * C::kABytes, &tm_w, kb * BKB, n0, full);
+                if (SWIGLU) tma_load_2d(sm_a + stage * C::kABytes + BM * BKB, &tm_w, kb * BKB, n0 + BM, full);
                 tma_load_2d(sm_b + stage * C::kBBytes, &tm_x, kb * BKB, 0, full);
                 if (C::kScaled) {
                     bulk_load(sm_sfa + stage * C::kSfBytes, sfw_tile + (size_t)kb * C::kSfBytes, C::kSfBytes, full);
@@ -140,7 +147,10 @@ scaled_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
                 for (int k = 0; k < BKB / 32; k++) {
                     const uint64_t a = adesc + (uint64_t)(k * 2), b = bdesc + (uint64_t)(k * 2);
                     const uint32_t accum = (it | k) != 0;
-                    if (KIND == KIND_F8) mma_f8f6f4(tmem_base, a, b, idesc, accum);
+                    if (KIND == KIND_F8) {
+                        mma_f8f6f4(tmem_base, a, b, idesc, accum);
+                        if (SWIGLU) mma_f8f6f4(tmem_base + 64, a + (uint64_t)((BM * BKB) >> 4), b, idesc, accum);   // the up tile, 16 KB further on
+                    }
                     else if (KIND == KIND_I8) mma_i8(tmem_base, a, b, idesc, accum);
                     else if (KIND == KIND_MXF8)                   // one scale per row and MMA: byte k of the chunk's 32-bit words
                         mma_mxf8f6f4(tmem_base, a, b, idesc_with_sf_ids(idesc, k, k), accum, tmem_base + C::kSfaCol, tmem_base + C::kSfbCol);
@@ -158,9 +168,9 @@ scaled_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
         // ------------------------------------------------------------------ epilogue (4 warps): accumulator -> registers
         const int quarter = warp & 3;
         const int i = quarter * 32 + lane;                       // row of the tile
-        float acc[BN];
+        float acc[AT * BN];                                      // SwiGLU: gate sums, then up sums
 #pragma unroll
-        for (int j = 0; j < BN; j++) acc[j] = 0.0f;
+        for (int j = 0; j < AT * BN; j++) acc[j] = 0.0f;
         if (done) {
             bool ok = mbar_wait(bar_tfull, 0);
             ok = __all_sync(0xffffffffu, ok);
@@ -170,19 +180,27 @@ scaled_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll
-            for (int c = 0; c < BN / 16; c++) {
-                uint32_t r[16];
-                tmem_ld_32x32b_x16(t_row + c * 16, r);
-                tmem_ld_wait();
+            for (int a = 0; a < AT; a++) {
 #pragma unroll
-                for (int j = 0; j < 16; j++) acc[c * 16 + j] = __uint_as_float(r[j]);
+                for (int c = 0; c < BN / 16; c++) {
+                    uint32_t r[16];
+                    tmem_ld_32x32b_x16(t_row + a * 64 + c * 16, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; j++) acc[a * BN + c * 16 + j] = __uint_as_float(r[j]);
+                }
             }
         }
         // accumulator (or sum of the cluster's accumulators) of batch row j -> bf16 output.  W8A8 sums are exact integers and
         // take the same scale expression as the 128-row kernel, (float)acc * (sx[m] * alpha * sw[n]).
         const float scale = (KIND == KIND_NVF4 || KIND == KIND_F8) ? __ldg(p.gx) * __ldg(p.gw) * p.alpha : p.alpha;
         const float sw_row = (KIND == KIND_I8 && n0 + i < p.n) ? __ldg(p.gw + n0 + i) : 0.0f;
-        auto emit = [&](int j, uint32_t bits) {
+        auto emit = [&](int j, uint32_t bits, uint32_t up_bits) {
+            if (SWIGLU) {
+                const float gt = __uint_as_float(bits) * scale, up = __uint_as_float(up_bits) * scale;
+                p.y[(size_t)j * p.ldy + (n0 >> 1) + i] = __float2bfloat16_rn(__fdividef(gt, 1.0f + __expf(-gt)) * up);
+                return;
+            }
             float v;
             if (KIND == KIND_I8) v = (float)(int)bits * ((__ldg(p.gx + j) * p.alpha) * sw_row);
             else v = __uint_as_float(bits) * scale;
@@ -192,7 +210,7 @@ scaled_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
             if (n0 + i < p.n) {
 #pragma unroll
                 for (int j = 0; j < BN; j++)
-                    if (j < p.m) emit(j, __float_as_uint(acc[j]));
+                    if (j < p.m) emit(j, __float_as_uint(acc[j]), SWIGLU ? __float_as_uint(acc[(AT - 1) * BN + j]) : 0u);
             }
         }
         tc_fence_before();
@@ -207,24 +225,30 @@ scaled_decode_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_cons
             for (int j = 0; j < BN; j++) {
                 if (j < p.m) {
                     const int owner = j % p.ksplit, slot = j / p.ksplit;
-                    const uint32_t local = sm_a + (uint32_t)((((int)crank * per + slot) * BM + i) * 4);
-                    const uint32_t ra = mapa_shared(local, (uint32_t)owner);
-                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(acc[j]) : "memory");
+#pragma unroll
+                    for (int a = 0; a < AT; a++) {
+                        const uint32_t local = sm_a + (uint32_t)(((((int)crank * per + slot) * AT + a) * BM + i) * 4);
+                        const uint32_t ra = mapa_shared(local, (uint32_t)owner);
+                        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(acc[a * BN + j]) : "memory");
+                    }
                 }
             }
             cluster_sync_all();
             for (int slot = 0, j = (int)crank; j < p.m; slot++, j += p.ksplit) {
-                uint32_t bits;
+                uint32_t bits, up_bits = 0u;
                 if (KIND == KIND_I8) {
                     int v = 0;
                     for (int c = 0; c < p.ksplit; c++) v += (int)__float_as_uint(part[(c * per + slot) * BM + i]);
                     bits = (uint32_t)v;
                 } else {
-                    float v = 0.0f;
-                    for (int c = 0; c < p.ksplit; c++) v += part[(c * per + slot) * BM + i];
-                    bits = __float_as_uint(v);
+                    float v = 0.0f, u = 0.0f;
+                    for (int c = 0; c < p.ksplit; c++) {
+                        v += part[((c * per + slot) * AT) * BM + i];
+                        if (SWIGLU) u += part[((c * per + slot) * AT + 1) * BM + i];
+                    }
+                    bits = __float_as_uint(v); up_bits = __float_as_uint(u);
                 }
-                if (n0 + i < p.n) emit(j, bits);
+                if (n0 + i < p.n) emit(j, bits, up_bits);
             }
         }
     }
@@ -262,15 +286,15 @@ static int choose_ksplit(int tiles, int num_kb, int sm_count) {
     return ks;
 }
 
-template <int KIND, int BN>
+template <int KIND, int BN, bool SWIGLU = false>
 static int32_t launch(oxq_handle* h, const CUtensorMap& tm_w, const CUtensorMap& tm_x, DecParams p) {
-    using C = Cfg<KIND, BN>;
+    using C = Cfg<KIND, BN, SWIGLU>;
     static OxqPerDevice attr_set;
     if (!attr_set.get(h->device)) {
-        OXQ_CUDA(h, cudaFuncSetAttribute(scaled_decode_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+        OXQ_CUDA(h, cudaFuncSetAttribute(scaled_decode_kernel<KIND, BN, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
         attr_set.set(h->device, 1);
     }
-    const int tiles = (p.n + BM - 1) / BM;
+    const int tiles = (p.n + BM * C::kATiles - 1) / (BM * C::kATiles);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)tiles, (unsigned)p.ksplit, 1); cfg.blockDim = dim3(NUM_THREADS, 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes; cfg.stream = h->stream;
@@ -287,7 +311,7 @@ static int32_t launch(oxq_handle* h, const CUtensorMap& tm_w, const CUtensorMap&
         na++;
     }
     cfg.attrs = attrs; cfg.numAttrs = na;
-    OXQ_CUDA(h, cudaLaunchKernelEx(&cfg, scaled_decode_kernel<KIND, BN>, tm_w, tm_x, p));
+    OXQ_CUDA(h, cudaLaunchKernelEx(&cfg, scaled_decode_kernel<KIND, BN, SWIGLU>, tm_w, tm_x, p));
     return OXQ_OK;
 }
 
@@ -296,10 +320,11 @@ static int32_t launch(oxq_handle* h, const CUtensorMap& tm_w, const CUtensorMap&
 
 int32_t oxq_scaled_decode_launch(oxq_handle* h, int kind, int m, int n, int k_bytes, const uint8_t* x, int64_t ldx_bytes, const uint8_t* sfx,
                                  const uint8_t* w, int64_t ldw_bytes, const uint8_t* sfw, const float* gx, const float* gw, float alpha, void* y,
-                                 int64_t ldy) {
+                                 int64_t ldy, bool swiglu) {
     using namespace oxq::tcdec;
     using namespace oxq::tc;
     const int bn = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+    if (swiglu && (kind != KIND_F8 || m > 32 || (n & 255))) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "SwiGLU decode form: FP8, up to 32 batch rows, 256-row blocks");
     CUtensorMap tm_w, tm_x;
     if (!oxq_make_tmap_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, w, (uint64_t)k_bytes, (uint64_t)n, (uint64_t)ldw_bytes, BKB, BM, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !oxq_make_tmap_2d(&tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, x, (uint64_t)k_bytes, (uint64_t)m, (uint64_t)ldx_bytes, BKB, (uint32_t)bn, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -307,7 +332,7 @@ int32_t oxq_scaled_decode_launch(oxq_handle* h, int kind, int m, int n, int k_by
     DecParams p;
     p.m = m; p.n = n; p.k_bytes = k_bytes;
     const int num_kb = (k_bytes + BKB - 1) / BKB;
-    p.ksplit = choose_ksplit((n + BM - 1) / BM, num_kb, h->sm_count);
+    p.ksplit = choose_ksplit(swiglu ? n / (2 * BM) : (n + BM - 1) / BM, num_kb, h->sm_count);
     p.sfw = sfw; p.sfx = sfx;
     p.sf_col_tiles = kind == KIND_MXF8 ? (k_bytes / 32 + 3) / 4 : (k_bytes / 8 + 3) / 4;
     p.gx = gx; p.gw = gw; p.alpha = alpha; p.y = (__nv_bfloat16*)y; p.ldy = ldy; p.status = h->dev_status;
@@ -317,6 +342,10 @@ int32_t oxq_scaled_decode_launch(oxq_handle* h, int kind, int m, int n, int k_by
         if (bn == 32) return launch<K, 32>(h, tm_w, tm_x, p);                   \
         return launch<K, 64>(h, tm_w, tm_x, p);                                 \
     } while (0)
+    if (swiglu) {
+        if (bn == 16) return launch<KIND_F8, 16, true>(h, tm_w, tm_x, p);
+        return launch<KIND_F8, 32, true>(h, tm_w, tm_x, p);
+    }
     if (kind == KIND_MXF8) OXQ_DEC_DISPATCH(KIND_MXF8);
     if (kind == KIND_NVF4) OXQ_DEC_DISPATCH(KIND_NVF4);
     if (kind == KIND_F8) OXQ_DEC_DISPATCH(KIND_F8);

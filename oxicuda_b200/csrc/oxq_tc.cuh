@@ -309,11 +309,12 @@ __device__ __forceinline__ void mma_mxf4nvf4_x4(uint32_t d_tmem, uint64_t adesc,
 // Decode shapes (m <= 64): the weight is the 128-row operand of the MMA and the batch its narrow N side, so the tensor
 // core unpacks the weight stream at memory speed.  Defined in oxq_gemm_tcdec.cu; the caller has validated the arguments.
 // kind: KIND_MXF8 / KIND_NVF4 (sfx, sfw: tiled scale factors; gx, gw: NVFP4 tensor scales), KIND_F8 (gx, gw: tensor
-// scales) or KIND_I8 (gx: per-row scales of X, gw: per-row scales of W).  k_bytes: bytes of K per operand row.
+// scales) or KIND_I8 (gx: per-row scales of X, gw: per-row scales of W).  k_bytes: bytes of K per operand row.  swiglu
+// (KIND_F8, m <= 32): w is the gate/up-interleaved weight of n rows, y the [m x n/2] product silu(gate) * up.
 struct oxq_handle;
 int32_t oxq_scaled_decode_launch(oxq_handle* h, int kind, int m, int n, int k_bytes, const uint8_t* x, int64_t ldx_bytes, const uint8_t* sfx,
                                  const uint8_t* w, int64_t ldw_bytes, const uint8_t* sfw, const float* gx, const float* gw, float alpha, void* y,
-                                 int64_t ldy);
+                                 int64_t ldy, bool swiglu = false);
 
 // Host: tensor map of a row-major 2-D array (inner extent and box in elements of `dtype`, leading dimension in bytes;
 // out-of-range parts of a box read as zero).  Defined in oxq_gemm_tc.cu.

@@ -88,9 +88,11 @@ def test_gemm_fp8_decode_shapes(ops, orc, mnk):
 
 
 @pytest.mark.parametrize("mnk", [(1, 512, 256), (8, 1024, 4096), (5, 256, 1040), (12, 512, 2048), (33, 1024, 1024), (64, 7168, 8192),
-                                 (4, 512, 8192), (2, 256, 28672), (8, 7168, 8192)])   # the last three: K split over clusters of 2 / 4 CTAs
+                                 (4, 512, 8192), (2, 256, 28672), (8, 7168, 8192),    # the last three: K split over clusters of CTAs
+                                 (16, 2048, 4096), (17, 512, 2048), (32, 7168, 8192), (32, 57344 // 8, 1024)])
 def test_gemm_fp8_swiglu_decode_shapes(ops, orc, mnk):
-    """The SwiGLU form of the GEMV: gate and up rows of one output column meet in one lane."""
+    """The SwiGLU form at decode batch sizes: gate and up rows of one output column meet in one lane (up to 32 rows: the
+    weight-streaming tensor-core kernel with a gate and an up accumulator per CTA)."""
     m, n2, k = mnk
     inter = n2 // 2
     x = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 0))

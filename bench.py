@@ -683,8 +683,22 @@ def run_tp_mlp(args, torch, world, rank, local_rank, peaks):
         xs = torch.randn((mm, HIDDEN), generator=g, device="cuda").to(torch.bfloat16)
         for _ in range(3):
             layer.forward(xs)
-        t = time_region(torch, lambda: layer.forward(xs), 20, True) / 20
-        small[f"m{mm}"] = {"ms": round(t, 4), "weight_GB/s_all_ranks": round(world * layer.weight_bytes_local() / (t * 1e-3) / 1e9, 1)}
+        fn_small, mode = (lambda: layer.forward(xs)), "eager"
+        if graphed:                                   # a decode step is a dozen launches of microseconds each: replay them from a graph
+            try:
+                xs_g, _, gr_small = layer.capture(mm)
+                xs_g.copy_(xs)
+                fn_small, mode = gr_small.replay, "cuda_graph"
+            except Exception:
+                torch.cuda.synchronize()
+        ok_all = torch.tensor([1 if mode == "cuda_graph" else 0], device="cuda")
+        dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
+        if int(ok_all.item()) == 0:
+            fn_small, mode = (lambda: layer.forward(xs)), "eager"
+        for _ in range(3):
+            fn_small()
+        t = time_region(torch, fn_small, 20, True) / 20
+        small[f"m{mm}"] = {"ms": round(t, 4), "weight_GB/s_all_ranks": round(world * layer.weight_bytes_local() / (t * 1e-3) / 1e9, 1), "launch": mode}
     attn = tp_attention_projections(torch, world, rank, peaks) if variant == "fp8" else None
     # End to end: pinned host activations in, reduced result out, every step, the host traffic sharded over the ranks:
     # every rank copies its 1/N of the rows of X in over its own PCIe link, the ranks all-gather X over NVLink, and every

@@ -258,6 +258,7 @@ class TpSwiGluMlp:
         self.last_h = None
         self.use_multimem = tp > 1 and reduce_dtype == torch.bfloat16 and os.environ.get("OXQ_TP_NO_MULTIMEM", "0") != "1"
         self.split_reduce = os.environ.get("OXQ_TP_SPLIT_REDUCE", "1") != "0"
+        self.split_blocks = max(2, int(os.environ.get("OXQ_TP_SPLIT_BLOCKS", "2")))    # column blocks of the down projection
         # OXQ_TP_FUSED_REDUCE=1: the down projection and the all-reduce as one kernel (oxq_gemm_fp8_all_reduce)
         self.fused_reduce = self.use_multimem and os.environ.get("OXQ_TP_FUSED_REDUCE", "0") == "1"
         self._flags = None
@@ -341,13 +342,14 @@ class TpSwiGluMlp:
         return y
 
     def _forward_multimem_split(self, x: torch.Tensor):
-        """FP8 variant: the down-projection runs as two column blocks and the in-switch reduce of the first block
-        (on a side stream) overlaps the GEMM of the second.  Three barriers: before the first reduce, between the two
-        (all of block one is written everywhere, and every rank's block two is ready), after the second."""
+        """FP8 variant: the down-projection runs as `split_blocks` column blocks and the in-switch reduce of block i (on a
+        side stream) overlaps the GEMM of block i + 1.  One cross-rank barrier before each reduce (block i is written on
+        every rank; it also tells that reduce i - 1 has finished everywhere) and one after the last."""
         m = x.shape[0]
         sym = self._symm_buffer(m)
-        half = self.hidden // 2
-        if sym is None or self.variant != "fp8" or m % self.tp != 0 or half % 256 != 0:
+        nb = self.split_blocks
+        blk = self.hidden // nb
+        if sym is None or self.variant != "fp8" or m % self.tp != 0 or self.hidden % nb != 0 or blk % 256 != 0:
             return None
         buf, hdl = sym
         y = buf[:m]
@@ -360,21 +362,17 @@ class TpSwiGluMlp:
         if self.keep_h:
             self.last_h = h
         hq, sh = ops.fp8_quant_dynamic(h)
-        ops.gemm_fp8(hq, self.w_down_q[:half], sh[1:], self.s_down, out=y[:, :half])
-        ev_a = torch.cuda.Event()
-        ev_a.record(main)
-        with torch.cuda.stream(comm):
-            comm.wait_event(ev_a)
-            hdl.barrier(channel=0)
-            ops.multimem_all_reduce_bf16_2d(hdl.multicast_ptr, m, half, self.hidden, self.rank, self.tp)
-        ops.gemm_fp8(hq, self.w_down_q[half:], sh[1:], self.s_down, out=y[:, half:])
-        ev_b = torch.cuda.Event()
-        ev_b.record(main)
-        with torch.cuda.stream(comm):
-            comm.wait_event(ev_b)
-            hdl.barrier(channel=1)
-            ops.multimem_all_reduce_bf16_2d(hdl.multicast_ptr + half * 2, m, half, self.hidden, self.rank, self.tp)
-            hdl.barrier(channel=2)
+        for i in range(nb):
+            lo = i * blk
+            ops.gemm_fp8(hq, self.w_down_q[lo:lo + blk], sh[1:], self.s_down, out=y[:, lo:lo + blk])
+            ev = torch.cuda.Event()
+            ev.record(main)
+            with torch.cuda.stream(comm):
+                comm.wait_event(ev)
+                hdl.barrier(channel=i)
+                ops.multimem_all_reduce_bf16_2d(hdl.multicast_ptr + lo * 2, m, blk, self.hidden, self.rank, self.tp)
+                if i == nb - 1:
+                    hdl.barrier(channel=nb)
         main.wait_stream(comm)
         return y
 

@@ -32,20 +32,23 @@ constexpr int UNIT_K = 256;                // K per raw tile (128 bytes of codes
 constexpr int RAW_BYTES = ROWS * 128;      // 16 KB
 constexpr int A_COLS = 128;                // tensor-memory columns of one unpacked unit (two groups of 128 bf16 per lane)
 constexpr int A_SLOTS = 2;                 // units of unpacked weights in tensor memory
-constexpr int U_SLOTS = 4;                 // units of activations in shared memory == units of accumulators in tensor memory
+constexpr int U_SLOTS_MAX = 4;             // units of activations in shared memory == units of accumulators in tensor memory (2 for 64 batch rows)
 constexpr int UNPACK_WARPS = 8;            // 8 or 16 (measured alike): with 8 a thread unpacks one group (128 codes) of a weight row per unit
 constexpr int NUM_WARPS = 7 + UNPACK_WARPS; // 0: codes TMA, 1: X TMA, 2: MMA + tensor-memory owner, 3-6: epilogue, 7-: unpack
 constexpr int NUM_THREADS = NUM_WARPS * 32;
 constexpr int SMEM_BUDGET = 227 * 1024;
-constexpr int PASS_ROWS = 32;              // batch rows per launch; the workspace keeps 32 f32 per weight row and pass
+constexpr int PASS_ROWS = 32;              // batch rows per pass of the 16- and 32-row forms; the workspace keeps 32 f32 per weight row and pass
+                                           // (the 64-row form is one pass with 64 f32 per weight row: the same bytes as two passes)
 
 template <int NB>
 struct Cfg {
+    static constexpr int kUSlots = NB == 64 ? 2 : U_SLOTS_MAX;
+    static constexpr int kPassRows = NB == 64 ? 64 : PASS_ROWS;
     static constexpr int kXBytes = NB * 512;                              // one unit of X: four sub-tiles of NB rows x 128 bytes
-    static constexpr int kRawStages = (SMEM_BUDGET - 3072 - U_SLOTS * kXBytes) / RAW_BYTES;
-    static constexpr int kSmemBytes = U_SLOTS * kXBytes + kRawStages * RAW_BYTES + 3072;
+    static constexpr int kRawStages = (SMEM_BUDGET - 3072 - kUSlots * kXBytes) / RAW_BYTES;
+    static constexpr int kSmemBytes = kUSlots * kXBytes + kRawStages * RAW_BYTES + 3072;
     // tensor memory: accumulators first (two per unit slot, one per group), then the unpacked units
-    static constexpr int kACol0 = U_SLOTS * 2 * NB;
+    static constexpr int kACol0 = kUSlots * 2 * NB;
     static constexpr int kTmemCols = 512;
     static_assert(kACol0 + A_SLOTS * A_COLS <= 512, "tensor memory overflow");
     static_assert(kRawStages >= 4, "raw ring too shallow");
@@ -92,6 +95,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_constant__ CUtensorMap tm_x, const Params p) {
     using C = Cfg<NB>;
     constexpr int RS = C::kRawStages;
+    constexpr int U_SLOTS = C::kUSlots;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t sm_x = base;                                   // activation tiles, one unit each
@@ -215,7 +219,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
             if (!last) return;
             __threadfence();
             if (row < p.n) {
-                float4* w = reinterpret_cast<float4*>(p.ws + (size_t)row * PASS_ROWS);
+                float4* w = reinterpret_cast<float4*>(p.ws + (size_t)row * C::kPassRows);
                 float4 v[NB / 4];
 #pragma unroll
                 for (int q = 0; q < NB / 4; q++) v[q] = __ldcg(w + q);
@@ -244,7 +248,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
             }
             finish_pending();
             if (row < p.n) {
-                float* w = p.ws + (size_t)row * PASS_ROWS;
+                float* w = p.ws + (size_t)row * C::kPassRows;
 #pragma unroll
                 for (int q = 0; q < NB / 4; q++)
                     if (4 * q < p.m) red_add_v4(w + 4 * q, total[4 * q], total[4 * q + 1], total[4 * q + 2], total[4 * q + 3]);
@@ -426,6 +430,14 @@ int32_t oxq_w4tc_launch(oxq_handle* h, int64_t m, int64_t n, int64_t k, const vo
                           CU_TENSOR_MAP_SWIZZLE_128B))
         OXQ_FAIL(h, OXQ_ERR_LAUNCH_FAILED, "cuTensorMapEncodeTiled failed for the codes (16-byte aligned pointer needed)");
     const int row_blocks = (int)((n + ROWS - 1) / ROWS);
+    if (m > PASS_ROWS && m <= 64) {                            // one pass with 64 batch columns: the weights are unpacked once
+        Params p;
+        p.m = (int)m; p.n = (int)n; p.k = (int)k; p.gpr = (int)(k / 128); p.upr = (int)(k / UNIT_K);
+        p.total_units = row_blocks * p.upr;
+        p.scales = scales; p.zeros = zeros; p.y = (__nv_bfloat16*)y; p.ws = ws_sums; p.counters = ws_counters;
+        p.status = h->dev_status;
+        return launch_nb<64>(h, tm_codes, (const __nv_bfloat16*)x, p);
+    }
     for (int64_t m0 = 0; m0 < m; m0 += PASS_ROWS) {
         Params p;
         p.m = (int)(m - m0 < PASS_ROWS ? m - m0 : PASS_ROWS); p.n = (int)n; p.k = (int)k; p.gpr = (int)(k / 128); p.upr = (int)(k / UNIT_K);

@@ -357,11 +357,11 @@ def test_gemm_w4a16_scales_at_an_odd_offset(ops, orc):
     _status_clean(ops)
 
 
-@pytest.mark.parametrize("m", [33, 64, 100, 128])
-@pytest.mark.parametrize("nk", [(4096, 4096), (200, 1024)])
+@pytest.mark.parametrize("m", [33, 48, 64, 100, 128])
+@pytest.mark.parametrize("nk", [(4096, 4096), (200, 1024), (14336, 4096)])
 def test_gemm_w4a16_mid_batch(ops, orc, m, nk):
-    """Batches of 33..128 rows run as passes of 32 over the fused tensor-core kernel; a workspace that held
-    something else before (here: ones) must not leak into the result."""
+    """Batches of 33..64 rows run as one pass of the fused tensor-core kernel with 64 batch columns, larger ones through
+    the dequantised weight; a workspace that held something else before (here: ones) must not leak into the result."""
     n, k = nk
     w = orc.gaussian((n, k), 0.02, 0)
     xb = orc.f32_to_bf16_bits(orc.gaussian((m, k), 1.0, 1))

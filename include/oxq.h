@@ -168,8 +168,9 @@ OXQ_API int32_t oxq_swiglu_interleaved(oxq_handle* h, const void* gu_bf16_dev, i
  *      crates/oxicuda-blas/src/precision/{int_ops,fp8_ops,fp4_fp6_ops}.rs.
  *      Zero dimensions are errors (gemm_api.rs:88-92).  Outputs are bf16 unless noted.
  *      Kernel choice is internal: large M runs tcgen05 kernels with TMA-fed operands and accumulators in tensor
- *      memory; oxq_gemm_fp8, oxq_gemm_fp8_swiglu and oxq_gemm_w8a8 with m <= 8, and the decode entry points
- *      (oxq_gemm_w4a16 with m <= 8, oxq_gemm_w8a32, oxq_gemm_nf4), run weight-streaming kernels.  Operands may be
+ *      memory; oxq_gemm_fp8, oxq_gemm_fp8_swiglu, oxq_gemm_w8a8, oxq_gemm_mxfp8 and oxq_gemm_nvfp4 with m <= 32 run a
+ *      weight-streaming tensor-core kernel (the weight is the 128-row operand of the MMA, the batch its narrow side),
+ *      the decode entry points (oxq_gemm_w4a16 with m <= 8, oxq_gemm_w8a32, oxq_gemm_nf4) mma.sync streams.  Operands may be
  *      produced by the call just before on the same stream (a quantizer followed directly by the GEMM): no kernel
  *      reads an operand before its producer has finished. ---------------- */
 /* FP8 E4M3: Y = bf16((X . W^T) * (*sx_dev * *sw_dev)), f32 accumulate.  K % 16 == 0, ldy % 8 == 0. */
@@ -226,7 +227,8 @@ OXQ_API int32_t oxq_gemm_w8a32(oxq_handle* h, int64_t m, int64_t n, int64_t k, c
  *   m <= 8           HBM-bound mma.sync kernel, one CTA per 16 weight rows over the whole K (no workspace traffic);
  *   9 <= m <= 64     (group 128, k % 1024 == 0) tensor-core kernel with the dequantisation fused in: codes are
  *                    unpacked straight into tensor memory as the row operand of tcgen05.mma, per-group scales are
- *                    applied to the group's accumulator, partial K ranges are combined in the workspace;
+ *                    applied to the group's accumulator, partial K ranges are combined in the workspace; one pass
+ *                    over the weight for up to 16, 32 or 64 batch rows;
  *                    other shapes with m <= 32 use a split-K mma.sync kernel (partial sums in the workspace);
  *   otherwise        the weight is dequantised to bf16 in the workspace and the bf16 tensor-core GEMM runs
  *                    (n % 8 == 0).

@@ -1119,6 +1119,14 @@ static int dense_decode_max_m() {
     static const int v = [] { const char* e = getenv("OXQ_DENSE_DECODE_MAX_M"); const int x = e ? atoi(e) : 32; return x < 0 ? 0 : (x > 64 ? 64 : x); }();
     return v;
 }
+// 33..64 batch rows: the streaming kernel only where the row tiles alone fill the machine (no K split: with 64 batch columns
+// the cluster's exchange of partial sums costs more than the 128-row kernel): 57344 x 8192 at 64 rows 82 us against 116,
+// 14336 x 4096 16 against 19, but 4096 x 4096 14 against 10.
+static bool dense_decode_takes(const oxq_handle* h, int64_t m, int64_t n) {
+    static const int cap = [] { const char* e = getenv("OXQ_DENSE_DECODE_MAX_M"); return e ? atoi(e) : -1; }();
+    if (cap >= 0) return m <= (cap > 64 ? 64 : cap);
+    return m <= 32 || (m <= 64 && ((n + 127) / 128) * 10 >= (int64_t)h->sm_count * 7);
+}
 static int dense_decode_min_m() {
     static const int v = [] { const char* e = getenv("OXQ_DENSE_DECODE_MIN_M"); const int x = e ? atoi(e) : 0; return x < 0 ? 0 : x; }();
     return v;
@@ -1136,7 +1144,7 @@ static int32_t gemm_fp8_impl(oxq_handle* h, int64_t m, int64_t n, int64_t k, con
     if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
     if (!sx || !sw) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
     if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
-    if (m <= dense_decode_max_m() && m > dense_decode_min_m() && beta == 0.0f)     // decode shapes: the weight stream is the whole cost
+    if (dense_decode_takes(h, m, n) && m > dense_decode_min_m() && beta == 0.0f)   // decode shapes: the weight stream is the whole cost
         return oxq_scaled_decode_launch(h, KIND_F8, (int)m, (int)n, (int)k, x, ldx, nullptr, w, ldw, nullptr, sx, sw, alpha, y, ldy);
     if (m <= fp8_gemv_max_m() && beta == 0.0f && fp8_gemv_setting()) {
         if (int32_t rc = oxq_require_sm100(h)) return rc;
@@ -1283,7 +1291,7 @@ int32_t oxq_gemm_w8a8(oxq_handle* h, int64_t m, int64_t n, int64_t k, const int8
     if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y, ldy)) return rc;
     if (!sx_rows || !sw_rows) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
     if ((k & 15) || ldx < k || ldw < k || (ldx & 15) || (ldw & 15)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "k, ldx and ldw must be multiples of 16 and ld >= k");
-    if (m <= dense_decode_max_m() && m > dense_decode_min_m())
+    if (dense_decode_takes(h, m, n) && m > dense_decode_min_m())
         return oxq_scaled_decode_launch(h, KIND_I8, (int)m, (int)n, (int)k, (const uint8_t*)x, ldx, nullptr, (const uint8_t*)w, ldw, nullptr, sx_rows,
                                         sw_rows, 1.0f, y, ldy);
     if (m <= fp8_gemv_max_m() && fp8_gemv_setting()) {             // decode shapes: mma.sync s8 on the raw bytes, exact s32 sums

@@ -715,18 +715,27 @@ def run_tp_mlp(args, torch, world, rank, local_rank, peaks):
     main = torch.cuda.current_stream()
     step_no = [0]
 
+    x_in = [torch.empty((per, HIDDEN), dtype=torch.bfloat16, device="cuda") for _ in range(2)]   # this rank's rows, as they arrive
+
     def e2e_step():
         i = step_no[0] & 1
         step_no[0] += 1
         with torch.cuda.stream(s_in):
             s_in.wait_event(ev_free[i])
-            x_d[i][lo:lo + per].copy_(x_h, non_blocking=True)
+            x_in[i].copy_(x_h, non_blocking=True)
             ev_in[i].record(s_in)
         main.wait_event(ev_in[i])
         main.wait_event(ev_out[i])
-        dist.all_gather_into_tensor(x_d[i], x_d[i][lo:lo + per])
-        y = layer.forward(x_d[i])
-        ev_free[i].record(main)
+        if graphed:
+            # the whole layer replayed from its CUDA graph: X is gathered straight into the graph's input buffer
+            dist.all_gather_into_tensor(xs_, x_in[i])
+            ev_free[i].record(main)
+            gr_.replay()
+            y = ys_
+        else:
+            dist.all_gather_into_tensor(x_d[i], x_in[i])
+            ev_free[i].record(main)
+            y = layer.forward(x_d[i])
         y_d[i].copy_(y[lo:lo + per])
         ev_done[i].record(main)
         with torch.cuda.stream(s_out):

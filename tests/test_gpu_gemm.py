@@ -87,6 +87,38 @@ def test_gemm_fp8_decode_shapes(ops, orc, mnk):
     assert torch.equal(y2.float(), y.float() * -2.0)                       # alpha is a power of two: exact
 
 
+@pytest.mark.parametrize("m", [3, 20, 48])
+def test_gemm_decode_strided_operands(ops, orc, m):
+    """Decode batch sizes with leading dimensions larger than K and an output wider than N: FP8 and W8A8 through the
+    weight-streaming kernel (48 rows with 104 row tiles: its 64-column form)."""
+    n, k = 13312, 512
+    xa = ops.fp8_quant_dynamic(bf16_dev(orc.f32_to_bf16_bits(orc.gaussian((m, 2 * k), 1.0, 3))))
+    wb = ops.fp8_quant_dynamic(bf16_dev(orc.f32_to_bf16_bits(orc.gaussian((n, 2 * k), 1.0, 4))))
+    qx, qw = xa[0][:, k:], wb[0][:, :k]                      # leading dimension 2k
+    ybuf = torch.full((m, n + 64), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_fp8(qx, qw, xa[1][1:], wb[1][1:], out=ybuf[:, :n])
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    s = float(xa[1][1]) * float(wb[1][1])
+    ref = (orc.e4m3_to_f32(qx.cpu().numpy()).astype(np.float64) @ orc.e4m3_to_f32(qw.cpu().numpy()).astype(np.float64).T) * s
+    _check(_bf16_to_np(ybuf[:, :n].contiguous()), ref.astype(np.float32), f"fp8 strided decode m={m}")
+    assert torch.all(ybuf[:, n:] == 7.0)                     # nothing written past N
+    # W8A8: exact integer sums
+    xi = torch.randint(-127, 128, (m, 2 * k), dtype=torch.int8, device="cuda")
+    wi = torch.randint(-127, 128, (n, 2 * k), dtype=torch.int8, device="cuda")
+    sx = torch.rand(m, device="cuda") * 0.01 + 0.001
+    sw = torch.rand(n, device="cuda") * 0.01 + 0.001
+    yi = torch.full((m, n + 64), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_w8a8(xi[:, :k], wi[:, k:], sx, sw, out=yi[:, :n])
+    torch.cuda.synchronize()
+    _status_clean(ops)
+    acc = xi[:, :k].double().cpu().numpy() @ wi[:, k:].double().cpu().numpy().T
+    want = (acc.astype(np.float32) * (sx.cpu().numpy()[:, None] * sw.cpu().numpy()[None, :])).astype(np.float32)
+    got = _bf16_to_np(yi[:, :n].contiguous())
+    assert np.array_equal(got, orc.bf16_bits_to_f32(orc.f32_to_bf16_bits(want))), "w8a8 strided decode: exact sums, one bf16 rounding"
+    assert torch.all(yi[:, n:] == 7.0)
+
+
 @pytest.mark.parametrize("mnk", [(1, 512, 256), (8, 1024, 4096), (5, 256, 1040), (12, 512, 2048), (33, 1024, 1024), (64, 7168, 8192),
                                  (4, 512, 8192), (2, 256, 28672), (8, 7168, 8192),    # the last three: K split over clusters of CTAs
                                  (16, 2048, 4096), (17, 512, 2048), (32, 7168, 8192), (32, 57344 // 8, 1024)])

@@ -468,6 +468,50 @@ __global__ void __launch_bounds__(256) fp8_quant_dynamic_fused_kernel(const T* _
     }
 }
 
+// Small tensors (a decode step's activations): one CTA does both passes, the second from L1 / L2, so the dynamic
+// quantizer is one launch of a few microseconds instead of two.  Same arithmetic as the two-launch form.
+constexpr int64_t FP8_SMALL_MAX = 131072;
+template <typename T>
+__global__ void __launch_bounds__(1024) fp8_quant_dynamic_small_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ stats,
+                                                                       uint8_t* __restrict__ q) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int V = Vec16<T>::N;
+    constexpr int L = 8 / V;
+    __shared__ float s_red[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t nvec = n / V;
+    const uint4* xv = reinterpret_cast<const uint4*>(x);
+    AbsMaxAcc<T> acc;
+    for (int64_t i = tid; i < nvec; i += 1024) acc.add(__ldg(xv + i));
+    float m = acc.result();
+    for (int64_t t = nvec * V + tid; t < n; t += 1024) m = fmaxf(m, fabsf(Elem<T>::to_f32(x[t])));
+    m = warp_max(m);
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
+    m = s_red[0];
+#pragma unroll
+    for (int w = 1; w < 32; w++) m = fmaxf(m, s_red[w]);
+    const float scale_f = m > 0.0f ? __fdiv_rn(m, 448.0f) : 1.0f;
+    if (tid == 0) { stats[0] = m; stats[1] = scale_f; }
+    const InvDiv scale = make_invdiv(scale_f);
+    const int64_t nitems = n / 8;
+    for (int64_t it = tid; it < nitems; it += 1024) {
+        float f[8];
+#pragma unroll
+        for (int l = 0; l < L; l++) {
+            const Vec16<T> in = ld16(x + it * 8 + l * V);
+#pragma unroll
+            for (int e = 0; e < V; e++) f[l * V + e] = div_exact_bounded_signed(Elem<T>::to_f32(in.v[e]), scale);
+        }
+        const uint32_t w0 = (uint32_t)cvt_e4m3x2(f[0], f[1]) | ((uint32_t)cvt_e4m3x2(f[2], f[3]) << 16);
+        const uint32_t w1 = (uint32_t)cvt_e4m3x2(f[4], f[5]) | ((uint32_t)cvt_e4m3x2(f[6], f[7]) << 16);
+        *reinterpret_cast<uint2*>(q + it * 8) = make_uint2(w0, w1);
+    }
+    for (int64_t t = nitems * 8 + tid; t < n; t += 1024)
+        q[t] = (uint8_t)(cvt_e4m3x2(div_exact(Elem<T>::to_f32(x[t]), scale), 0.0f) & 0xFF);
+}
+
 template <typename T, int MODE>
 __global__ void __launch_bounds__(256) fp8_dequant_kernel(const uint8_t* __restrict__ q, int64_t n, const float* __restrict__ scale_ptr,
                                                           T* __restrict__ y) {
@@ -980,6 +1024,12 @@ int32_t oxq_fp8_quant_dynamic(oxq_handle* h, const void* x, int dtype, int64_t n
     OXQ_CHECK_HANDLE(h);
     if (n <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "fp8 encode: empty input");
     if (!x || !q || !stats_dev || !aligned16(x) || !aligned16(q)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (n <= FP8_SMALL_MAX && (dtype == OXQ_F32 || dtype == OXQ_BF16 || dtype == OXQ_F16)) {       // one CTA, one launch
+        if (int32_t rc = oxq_require_sm100(h)) return rc;
+        DISPATCH_DTYPE(dtype, oxq_launch(fp8_quant_dynamic_small_kernel<T>, 1, 1024, 0, h->stream, (const T*)x, n, stats_dev, q));
+        OXQ_LAUNCH_CHECK(h);
+        return OXQ_OK;
+    }
     // one launch with a grid-wide meeting point between the two passes (OXQ_FP8_FUSED_DYNAMIC=0: two launches)
     static int fused = -1;
     if (fused < 0) { const char* e = getenv("OXQ_FP8_FUSED_DYNAMIC"); fused = e ? (atoi(e) != 0) : 1; }

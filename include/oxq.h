@@ -344,6 +344,13 @@ OXQ_API int32_t oxq_multimem_all_reduce_bf16(oxq_handle* h, void* multicast_ptr,
 /* The same over a column block of a row-major bf16 matrix ([rows x cols] at multicast_ptr, leading dimension ld elements):
  * rank r reduces rows [r * rows / world, (r + 1) * rows / world).  cols and ld multiples of 8, rows a multiple of world. */
 OXQ_API int32_t oxq_multimem_all_reduce_bf16_2d(oxq_handle* h, void* multicast_ptr, int64_t rows, int64_t cols, int64_t ld, int rank, int world);
+/* The same with the cross-rank synchronisation inside the kernel: no barrier before or after it.  The call is stream-ordered
+ * behind the kernel that wrote this rank's partial; when it has finished on a rank, that rank's replica holds the complete
+ * sums.  flags_*: this rank's replica and the multicast address of four 32-bit words of symmetric memory (16-byte aligned,
+ * zero before the first call, never written by the host afterwards); call_number = 1, 2, 3, ... counts the calls that used
+ * these words (the same on every rank).  Waits on other ranks are bounded (OXQ_ERR_DEVICE_TIMEOUT in the status word). */
+OXQ_API int32_t oxq_multimem_all_reduce_bf16_2d_sync(oxq_handle* h, void* multicast_ptr, int64_t rows, int64_t cols, int64_t ld, int rank, int world,
+                                             uint32_t* flags_local_dev, uint32_t* flags_multicast_dev, int64_t call_number);
 /* ---- RowLinear::forward_partial + RowLinear::all_reduce in one kernel (crates/oxicuda-dist-infer/src/tensor_parallel/
  *      row_parallel.rs:67-90, :199-223): Y = sum over ranks of (X_r . W_r^T) * sx_r * sw_r, every rank's K-shard an FP8 GEMM as in
  *      oxq_gemm_fp8.  y_local_dev is this rank's replica of a symmetric bf16 buffer [m x ldy] and y_multicast_dev the same

@@ -303,6 +303,38 @@ __device__ __forceinline__ void mma_mxf4nvf4_x4(uint32_t d_tmem, uint64_t adesc,
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
 }
 
+// ---- NVSwitch multicast (multimem) and cross-GPU flag words ------------------------------------------------------------
+// add on the word's replica on every GPU of the multicast group; the release covers what this thread has observed before
+__device__ __forceinline__ void mm_red_add_u32(uint32_t* mc_addr, uint32_t v) {
+    asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_addr), "r"(v) : "memory");
+}
+// Polls with plain system-scope loads and a short sleep between them (hundreds of warps wait at the same time next to
+// the MMA pipeline: they must not crowd the L2); one acquire fence once the word has arrived.
+__device__ __forceinline__ bool wait_word_at_least(const uint32_t* addr, uint32_t target, int sleep_ns) {
+    auto peek = [&]() { uint32_t v; asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory"); return v; };
+    bool ok = peek() >= target;
+    if (!ok) {
+        const uint64_t t0 = globaltimer_ns();
+        for (uint32_t it = 0; it < 0x40000000u; ++it) {
+            if (sleep_ns > 0) __nanosleep(sleep_ns);
+            if (peek() >= target) { ok = true; break; }
+            if ((it & 63u) == 63u && globaltimer_ns() - t0 > kWaitLimitNs) break;
+        }
+    }
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    return ok;
+}
+__device__ __forceinline__ uint4 mm_ld_reduce_bf16x8(const void* mc_addr) {
+    uint4 r;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc_addr) : "memory");
+    return r;
+}
+__device__ __forceinline__ void mm_st_bf16x8(void* mc_addr, const uint4& r) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc_addr), "r"(r.x), "r"(r.y), "r"(r.z), "r"(r.w) : "memory");
+}
+
 }  // namespace tc
 }  // namespace oxq
 

@@ -263,6 +263,10 @@ class TpSwiGluMlp:
         self.fused_reduce = self.use_multimem and os.environ.get("OXQ_TP_FUSED_REDUCE", "0") == "1"
         self._flags = None
         self._fused_calls = 0
+        # OXQ_TP_SYNC_REDUCE=0: cross-rank barrier kernels around the in-switch reduce instead of flag words inside it
+        self.sync_reduce = self.use_multimem and os.environ.get("OXQ_TP_SYNC_REDUCE", "1") != "0"
+        self._sflags = None
+        self._sync_calls = 0
 
     # -- NVLS path: symmetric output buffer mapped through the NVSwitch multicast object ----------
     def _symm_buffer(self, m: int):
@@ -284,6 +288,41 @@ class TpSwiGluMlp:
             self.use_multimem = False       # NCCL all-reduce instead
             self._symm = None
         return self._symm
+
+    def _sync_flags(self):
+        """Four symmetric flag words of the self-synchronising reduce kernel (zeroed once, then only touched by the kernels)."""
+        if self._sflags is None:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm_mem
+            words = symm_mem.empty((4,), dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()))
+            words.zero_()
+            fh = symm_mem.rendezvous(words, self.group if self.group is not None else dist.group.WORLD)
+            if not fh.multicast_ptr:
+                raise RuntimeError("no multicast support")
+            torch.cuda.synchronize()
+            fh.barrier(channel=0)                      # every replica is zero before anyone's first signal can land
+            torch.cuda.synchronize()
+            self._sflags = (words, fh)
+        return self._sflags
+
+    def _reduce_block(self, hdl, ptr_offset_bytes: int, m: int, cols: int, first: bool, last: bool, channel: int):
+        """In-switch all-reduce of a column block of the symmetric output: either the kernel that synchronises the ranks
+        itself, or the plain kernel between cross-rank barriers."""
+        ops = self.ops
+        if self.sync_reduce:
+            try:
+                words, fh = self._sync_flags()
+            except Exception:
+                self.sync_reduce = False
+            else:
+                self._sync_calls += 1
+                ops.multimem_all_reduce_bf16_2d_sync(hdl.multicast_ptr + ptr_offset_bytes, m, cols, self.hidden, self.rank, self.tp, words,
+                                                     fh.multicast_ptr, self._sync_calls)
+                return
+        hdl.barrier(channel=channel)
+        ops.multimem_all_reduce_bf16_2d(hdl.multicast_ptr + ptr_offset_bytes, m, cols, self.hidden, self.rank, self.tp)
+        if last:
+            hdl.barrier(channel=channel + 1)
 
     def _fused_flags(self):
         """Symmetric flag words of the fused GEMM + all-reduce kernel (zeroed once; every call leaves them zero)."""
@@ -336,6 +375,9 @@ class TpSwiGluMlp:
         buf, hdl = sym
         y = buf[:m]
         self.forward_partial(x, out=y)
+        if self.sync_reduce and m % self.tp == 0:
+            self._reduce_block(hdl, 0, m, self.hidden, True, True, 0)      # falls back to barriers by itself
+            return y
         hdl.barrier(channel=0)
         self.ops.multimem_all_reduce_bf16(hdl.multicast_ptr, m * self.hidden, self.rank, self.tp)
         hdl.barrier(channel=1)
@@ -369,10 +411,7 @@ class TpSwiGluMlp:
             ev.record(main)
             with torch.cuda.stream(comm):
                 comm.wait_event(ev)
-                hdl.barrier(channel=i)
-                ops.multimem_all_reduce_bf16_2d(hdl.multicast_ptr + lo * 2, m, blk, self.hidden, self.rank, self.tp)
-                if i == nb - 1:
-                    hdl.barrier(channel=nb)
+                self._reduce_block(hdl, lo * 2, m, blk, i == 0, i == nb - 1, i)
         main.wait_stream(comm)
         return y
 

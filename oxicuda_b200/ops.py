@@ -727,6 +727,13 @@ def multimem_all_reduce_bf16(multicast_ptr: int, numel: int, rank: int, world: i
     handle(device_index).call("oxq_multimem_all_reduce_bf16", C.c_void_p(multicast_ptr), numel, rank, world)
 
 
+def multimem_all_reduce_bf16_2d_sync(multicast_ptr: int, rows: int, cols: int, ld: int, rank: int, world: int, flags_local: torch.Tensor,
+                                     flags_multicast_ptr: int, call_number: int, device_index: int | None = None):
+    """In-place all-reduce of a column block of a symmetric bf16 matrix with the cross-rank synchronisation inside the kernel."""
+    handle(device_index).call("oxq_multimem_all_reduce_bf16_2d_sync", C.c_void_p(multicast_ptr), rows, cols, ld, rank, world, _p(flags_local),
+                              C.c_void_p(flags_multicast_ptr), call_number)
+
+
 def gemm_fp8_all_reduce(x_q, w_q, sx, sw, y_local: torch.Tensor, y_multicast_ptr: int, flags_local: torch.Tensor, flags_multicast_ptr: int,
                         rank: int, world: int, call_index: int):
     """FP8 GEMM of this rank's K-shard with the all-reduce over the ranks fused in (RowLinear::forward_partial + all_reduce):

@@ -263,8 +263,11 @@ class TpSwiGluMlp:
         self.fused_reduce = self.use_multimem and os.environ.get("OXQ_TP_FUSED_REDUCE", "0") == "1"
         self._flags = None
         self._fused_calls = 0
-        # OXQ_TP_SYNC_REDUCE=0: cross-rank barrier kernels around the in-switch reduce instead of flag words inside it
-        self.sync_reduce = self.use_multimem and os.environ.get("OXQ_TP_SYNC_REDUCE", "1") != "0"
+        # The in-switch reduce either synchronises the ranks itself (flag words through the switch) or runs between cross-rank
+        # barrier kernels.  Measured per step at M = 2048: 2 GPUs 0.623 / 0.591 ms, 4 GPUs 0.354 / 0.359, 8 GPUs 0.220 / 0.257:
+        # the first form from four ranks on.  OXQ_TP_SYNC_REDUCE=0 / 1 forces one of them.
+        sr = os.environ.get("OXQ_TP_SYNC_REDUCE", "")
+        self.sync_reduce = self.use_multimem and (sr == "1" or (sr != "0" and tp >= 4))
         self._sflags = None
         self._sync_calls = 0
 
@@ -305,10 +308,11 @@ class TpSwiGluMlp:
             self._sflags = (words, fh)
         return self._sflags
 
-    def _reduce_block(self, hdl, ptr_offset_bytes: int, m: int, cols: int, first: bool, last: bool, channel: int):
+    def _reduce_block(self, hdl, ptr_offset_bytes: int, m: int, cols: int, first: bool, last: bool, channel: int, ld: int | None = None):
         """In-switch all-reduce of a column block of the symmetric output: either the kernel that synchronises the ranks
         itself, or the plain kernel between cross-rank barriers."""
         ops = self.ops
+        ld = self.hidden if ld is None else ld
         if self.sync_reduce:
             try:
                 words, fh = self._sync_flags()
@@ -316,11 +320,11 @@ class TpSwiGluMlp:
                 self.sync_reduce = False
             else:
                 self._sync_calls += 1
-                ops.multimem_all_reduce_bf16_2d_sync(hdl.multicast_ptr + ptr_offset_bytes, m, cols, self.hidden, self.rank, self.tp, words,
+                ops.multimem_all_reduce_bf16_2d_sync(hdl.multicast_ptr + ptr_offset_bytes, m, cols, ld, self.rank, self.tp, words,
                                                      fh.multicast_ptr, self._sync_calls)
                 return
         hdl.barrier(channel=channel)
-        ops.multimem_all_reduce_bf16_2d(hdl.multicast_ptr + ptr_offset_bytes, m, cols, self.hidden, self.rank, self.tp)
+        ops.multimem_all_reduce_bf16_2d(hdl.multicast_ptr + ptr_offset_bytes, m, cols, ld, self.rank, self.tp)
         if last:
             hdl.barrier(channel=channel + 1)
 
@@ -375,9 +379,15 @@ class TpSwiGluMlp:
         buf, hdl = sym
         y = buf[:m]
         self.forward_partial(x, out=y)
-        if self.sync_reduce and m % self.tp == 0:
-            self._reduce_block(hdl, 0, m, self.hidden, True, True, 0)      # falls back to barriers by itself
-            return y
+        if self.sync_reduce:
+            if m % self.tp == 0:
+                self._reduce_block(hdl, 0, m, self.hidden, True, True, 0)      # falls back to barriers by itself
+                return y
+            sub = self.hidden // self.tp
+            if self.hidden % self.tp == 0 and sub % 8 == 0:
+                # fewer rows than ranks (a decode step): the contiguous [m x hidden] block seen as [m * tp x hidden / tp]
+                self._reduce_block(hdl, 0, m * self.tp, sub, True, True, 0, ld=sub)
+                return y
         hdl.barrier(channel=0)
         self.ops.multimem_all_reduce_bf16(hdl.multicast_ptr, m * self.hidden, self.rank, self.tp)
         hdl.barrier(channel=1)

@@ -168,6 +168,63 @@ def _fused_rank(rank, world, port, q):
     dist.destroy_process_group()
 
 
+def _sync_rank(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from oracle import oracle as orc
+    from oxicuda_b200 import ops
+    from oxicuda_b200.dist_infer import TpSwiGluMlp
+    hidden, inter = 1024, 2048
+    wg, wu, wd = _weights(orc, hidden, inter)
+    layer = TpSwiGluMlp(torch.from_numpy(wg), torch.from_numpy(wu), torch.from_numpy(wd), "fp8", tp=world, rank=rank)
+    plain = TpSwiGluMlp(torch.from_numpy(wg), torch.from_numpy(wu), torch.from_numpy(wd), "fp8", tp=world, rank=rank)
+    if not layer.use_multimem:
+        q.put((rank, None))
+        dist.barrier()
+        dist.destroy_process_group()
+        return
+    layer.sync_reduce, plain.sync_reduce = True, False
+    errs = []
+    for i, m in enumerate((1024, 1, 520, 7, 64, 1024)):       # split path, fewer rows than ranks, one block, odd rows
+        xb = orc.f32_to_bf16_bits(orc.gaussian((m, hidden), 1.0, 40 + i))
+        x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+        y = layer.forward(x)
+        want = plain.forward(x)
+        torch.cuda.synchronize()
+        errs.append(float((y.float() - want.float()).abs().max() / want.float().abs().max()))
+    assert layer._sync_calls >= 6
+    errs.append(float(ops.handle(torch.cuda.current_device()).device_status()))
+    q.put((rank, errs))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tp_mlp_sync_reduce_two_gpus():
+    """The in-switch reduce that synchronises the ranks through flag words inside the kernel against the same reduce between
+    cross-rank barrier kernels: identical sums, over the split path, single blocks and batches smaller than the group."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_sync_rank, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for _, errs in res:
+        if errs is None:
+            pytest.skip("no multicast mapping")
+        for e in errs:
+            assert e <= 1e-6, errs
+
+
 def test_tp_mlp_fused_reduce_two_gpus():
     """The down projection with the all-reduce fused in (tiles summed in the switch under the MMAs of later tiles) against
     the unfused in-switch path: several calls (both sets of flag words, changing tile counts), two layer sizes."""

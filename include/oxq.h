@@ -347,24 +347,26 @@ OXQ_API int32_t oxq_multimem_all_reduce_bf16_2d(oxq_handle* h, void* multicast_p
 /* The same with the cross-rank synchronisation inside the kernel: no barrier before or after it.  The call is stream-ordered
  * behind the kernel that wrote this rank's partial; when it has finished on a rank, that rank's replica holds the complete
  * sums.  flags_*: this rank's replica and the multicast address of four 32-bit words of symmetric memory (16-byte aligned,
- * zero before the first call, never written by the host afterwards); call_number = 1, 2, 3, ... counts the calls that used
- * these words (the same on every rank).  Waits on other ranks are bounded (OXQ_ERR_DEVICE_TIMEOUT in the status word). */
+ * zero before the first call, never written by the host afterwards: the calls are counted on the device, so a CUDA graph
+ * that holds such a call may be replayed).  Every rank makes the same sequence of calls on these words.  Waits on other
+ * ranks are bounded (OXQ_ERR_DEVICE_TIMEOUT in the status word). */
 OXQ_API int32_t oxq_multimem_all_reduce_bf16_2d_sync(oxq_handle* h, void* multicast_ptr, int64_t rows, int64_t cols, int64_t ld, int rank, int world,
-                                             uint32_t* flags_local_dev, uint32_t* flags_multicast_dev, int64_t call_number);
+                                             uint32_t* flags_local_dev, uint32_t* flags_multicast_dev);
 /* ---- RowLinear::forward_partial + RowLinear::all_reduce in one kernel (crates/oxicuda-dist-infer/src/tensor_parallel/
  *      row_parallel.rs:67-90, :199-223): Y = sum over ranks of (X_r . W_r^T) * sx_r * sw_r, every rank's K-shard an FP8 GEMM as in
  *      oxq_gemm_fp8.  y_local_dev is this rank's replica of a symmetric bf16 buffer [m x ldy] and y_multicast_dev the same
  *      buffer through the NVSwitch multicast mapping; flags_* are this rank's replica and the multicast address of
- *      flag_words >= 2 * (ceil(m / 256) * ceil(n / 256) + 1) 32-bit words of symmetric memory, zero before the first call
- *      and left zero by every call.  Every rank of the group makes the same sequence of calls (same shapes, call_index
- *      0, 1, 2, ... : calls alternate between the two halves of the flag words).  Tiles are reduced in the switch while
+ *      flag_words >= 2 * (ceil(m / 256) * ceil(n / 256) + 1) + 1 32-bit words of symmetric memory, zero before the first
+ *      call and never written by the host afterwards (the last word counts the calls on the device, so a replayed CUDA
+ *      graph behaves like a sequence of host calls; calls alternate between two sets of words).  Every rank of the group
+ *      makes the same sequence of calls with the same shapes.  Tiles are reduced in the switch while
  *      later tiles are still being multiplied; when the call's kernel has finished on a rank, that rank's replica holds the
  *      complete sum (no barrier needed after it; the buffer may be rewritten by the next call).  Waits on other ranks are
  *      bounded (OXQ_ERR_DEVICE_TIMEOUT in the status word).  n % 8 == 0, 2 <= world <= 64. */
 OXQ_API int32_t oxq_gemm_fp8_all_reduce(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x_dev, int64_t ldx,
                                 const uint8_t* w_dev, int64_t ldw, const float* sx_dev, const float* sw_dev, void* y_local_dev,
                                 void* y_multicast_dev, int64_t ldy, uint32_t* flags_local_dev, uint32_t* flags_multicast_dev,
-                                int64_t flag_words, int rank, int world, int64_t call_index);
+                                int64_t flag_words, int rank, int world);
 
 /* ---- tensor-parallel layer behind the C ABI --------------------------------------------------------------------------
  * ColumnLinear / RowLinear / SwiGluFfn of the reference (crates/oxicuda-dist-infer/src/tensor_parallel/column_parallel.rs:103-204,

@@ -74,8 +74,8 @@ SIGNATURES = {
     "oxq_gemm_w4a16_static": (_i32, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _vp, _int, _vp]),
     "oxq_multimem_all_reduce_bf16": (_i32, [_vp, _vp, _i64, _int, _int]),
     "oxq_multimem_all_reduce_bf16_2d": (_i32, [_vp, _vp, _i64, _i64, _i64, _int, _int]),
-    "oxq_multimem_all_reduce_bf16_2d_sync": (_i32, [_vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _vp, _i64]),
-    "oxq_gemm_fp8_all_reduce": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _int, _int, _i64]),
+    "oxq_multimem_all_reduce_bf16_2d_sync": (_i32, [_vp, _vp, _i64, _i64, _i64, _int, _int, _vp, _vp]),
+    "oxq_gemm_fp8_all_reduce": (_i32, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _int, _int]),
     "oxq_comm_unique_id": (_i32, [_vp]),
     "oxq_comm_init": (_i32, [_vp, _vp, _int, _int]),
     "oxq_comm_destroy": (_i32, [_vp]),

@@ -56,14 +56,17 @@ __global__ void __launch_bounds__(512) multimem_all_reduce_bf16_2d_kernel(uint4*
 // all ranks have signalled, reduces its share, and the last CTA to finish signals "this rank's slice is broadcast" on
 // every rank and leaves only when all ranks have said so -- the kernel that follows in the stream finds the complete sums.
 // flags (symmetric memory, zero before the first call): [0] arrivals, [1] finished ranks, both running totals that are
-// never cleared (target = world * call number); [2] this rank's CTAs that are done, cleared by the last one.
+// never cleared; [2] this rank's CTAs that are done, cleared by the last one; [3] this rank's finished calls.  The
+// target of a call is world * (finished calls + 1): counted on the device, so the same launch replayed from a CUDA graph
+// waits for its own generation of signals.  [3] changes only when every CTA of the grid is done, so all CTAs read one value.
 __global__ void __launch_bounds__(512) multimem_all_reduce_bf16_2d_sync_kernel(uint4* mc, int64_t row_lo, int64_t row_hi, int64_t vec_cols,
-                                                                               int64_t ld_vecs, uint32_t* flags, uint32_t* mc_flags, uint32_t target,
+                                                                               int64_t ld_vecs, uint32_t* flags, uint32_t* mc_flags, uint32_t world,
                                                                                int32_t* status) {
     using namespace oxq::tc;
     pdl_trigger();
     pdl_wait();
     __shared__ int s_ok;
+    const uint32_t target = world * (*reinterpret_cast<const volatile uint32_t*>(flags + 3) + 1u);
     if (threadIdx.x == 0) {
         if (blockIdx.x == 0) mm_red_add_u32(mc_flags, 1u);
         s_ok = wait_word_at_least(flags, target, 200) ? 1 : 0;
@@ -90,6 +93,8 @@ __global__ void __launch_bounds__(512) multimem_all_reduce_bf16_2d_sync_kernel(u
             flags[2] = 0u;
             mm_red_add_u32(mc_flags + 1, 1u);
             if (!wait_word_at_least(flags + 1, target, 200)) atomicExch(status, OXQ_ERR_DEVICE_TIMEOUT);
+            *reinterpret_cast<volatile uint32_t*>(flags + 3) = target / world;      // this call is finished
+            __threadfence();
         }
     }
 }
@@ -97,7 +102,7 @@ __global__ void __launch_bounds__(512) multimem_all_reduce_bf16_2d_sync_kernel(u
 }  // namespace oxq
 
 extern "C" int32_t oxq_multimem_all_reduce_bf16_2d_sync(oxq_handle* h, void* multicast_ptr, int64_t rows, int64_t cols, int64_t ld, int rank, int world,
-                                                        uint32_t* flags_local, uint32_t* flags_multicast, int64_t call_number) {
+                                                        uint32_t* flags_local, uint32_t* flags_multicast) {
     OXQ_CHECK_HANDLE(h);
     if (rows <= 0 || cols <= 0) OXQ_FAIL(h, OXQ_ERR_EMPTY_INPUT, "all_reduce: empty input");
     if (world < 1 || world > 1024 || rank < 0 || rank >= world) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "rank %d outside world of %d", rank, world);
@@ -105,14 +110,13 @@ extern "C" int32_t oxq_multimem_all_reduce_bf16_2d_sync(oxq_handle* h, void* mul
         OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned multicast / flag pointer");
     if ((cols & 7) || (ld & 7) || ld < cols || rows % world != 0)
         OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "cols and ld must be multiples of 8 elements, ld >= cols, rows a multiple of world");
-    if (call_number < 1 || call_number * world > 0xFFFFFFF0ll) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "call number %lld out of range", (long long)call_number);
     if (int32_t rc = oxq_require_sm100(h)) return rc;
     const int64_t per = rows / world, total = per * (cols / 8);
     int64_t blocks = (total + 512 * 4 - 1) / (512 * 4);
     if (blocks > h->sm_count) blocks = h->sm_count;              // one CTA per SM at most: every CTA of the grid is resident
     if (blocks < 1) blocks = 1;
     oxq_launch(oxq::multimem_all_reduce_bf16_2d_sync_kernel, (int)blocks, 512, 0, h->stream, (uint4*)multicast_ptr, per * rank, per * (rank + 1), cols / 8,
-               ld / 8, flags_local, flags_multicast, (uint32_t)(call_number * world), h->dev_status);
+               ld / 8, flags_local, flags_multicast, (uint32_t)world, h->dev_status);
     OXQ_LAUNCH_CHECK(h);
     return OXQ_OK;
 }

@@ -40,8 +40,11 @@ struct GemmParams {
     int32_t* status;
     // fused all-reduce form of the CTA-pair kernel: y is this rank's replica of a symmetric buffer
     void* ar_mc_y;                    // the same buffer through the multicast mapping
-    uint32_t* ar_flags;               // this rank's replica of the flag words: [items] arrivals, then one word of finished units
+    uint32_t* ar_flags;               // this rank's replica of the flag words: two sets of ([items] arrivals, one word of finished units)
     uint32_t* ar_mc_flags;            // the flag words through the multicast mapping
+    uint32_t* ar_calls;               // this rank's count of finished calls on these flag words (device memory: the parity picks the set,
+                                      // so a replayed CUDA graph alternates like a sequence of host calls does)
+    int ar_set_stride;                // words from one set to the other
     int ar_world, ar_rank;
     int ar_sleep_ns;                  // pause between two looks at a flag word (0: none)
 };
@@ -453,6 +456,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot_ptr;
     pdl_trigger();
     pdl_wait();
+    // fused all-reduce: the set of flag words of this call.  The count of finished calls changes only when CTA 0 has seen every
+    // unit of every rank finished, i.e. after every CTA of this grid has done its part, so all CTAs read the same value.
+    uint32_t* ar_flags = nullptr; uint32_t* ar_mc_flags = nullptr;
+    if (AR) {
+        const uint32_t set = *reinterpret_cast<const volatile uint32_t*>(p.ar_calls) & 1u;
+        ar_flags = p.ar_flags + set * p.ar_set_stride;
+        ar_mc_flags = p.ar_mc_flags + set * p.ar_set_stride;
+    }
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (whole warp, one elected lane issues; both CTAs)
@@ -584,7 +595,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             if (AR) {
                 // this warp's 32 rows of the tile are stored: one arrival on every rank (lane 0's release, after the warp
                 // has met, covers the stores of all its lanes)
-                if (lane == 0) mm_red_add_u32(p.ar_mc_flags + w, 1u);
+                if (lane == 0) mm_red_add_u32(ar_mc_flags + w, 1u);
             }
         }
     } else {
@@ -601,7 +612,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             const int w = (u >> 5) * world + p.ar_rank, strip = u & 31;
             int tm, tn;
             tile_coords(w, tiles_m, tiles_n, p.group_m, tm, tn);
-            if (lane == 0) ok = wait_word_at_least(p.ar_flags + w, arrive_target, p.ar_sleep_ns);
+            if (lane == 0) ok = wait_word_at_least(ar_flags + w, arrive_target, p.ar_sleep_ns);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) { if (lane == 0) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT); break; }
             // 8 rows x 256 columns of bf16 = 8 x 32 vectors of 16 bytes: eight vectors in flight per lane, one round trip
@@ -615,14 +626,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
             for (int j = 0; j < 8; j++)
                 if (col_in && row0 + j < p.m) mm_st_bf16x8(mc_y + ((size_t)(row0 + j) * p.ldy + col0) * 2, val[j]);
             __syncwarp();
-            if (lane == 0) mm_red_add_u32(p.ar_mc_flags + num_work, 1u);
+            if (lane == 0) mm_red_add_u32(ar_mc_flags + num_work, 1u);
         }
         if (blockIdx.x == 0 && warp == 6) {
             // the last to leave: every unit of every rank is finished (32 per item), then this call's words are cleared
-            if (lane == 0 && ok && !wait_word_at_least(p.ar_flags + num_work, 32u * (uint32_t)num_work, p.ar_sleep_ns)) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT);
+            if (lane == 0 && ok && !wait_word_at_least(ar_flags + num_work, 32u * (uint32_t)num_work, p.ar_sleep_ns)) atomicExch(p.status, OXQ_ERR_DEVICE_TIMEOUT);
             __syncwarp();
-            for (int i = lane; i <= num_work; i += 32) p.ar_flags[i] = 0u;
+            for (int i = lane; i <= num_work; i += 32) ar_flags[i] = 0u;
             __threadfence_system();
+            __syncwarp();
+            if (lane == 0) *reinterpret_cast<volatile uint32_t*>(p.ar_calls) = *reinterpret_cast<const volatile uint32_t*>(p.ar_calls) + 1u;
         }
     }
 
@@ -1178,7 +1191,7 @@ int32_t oxq_gemm_bf16_op(oxq_handle* h, int64_t m, int64_t n, int64_t k, float a
 
 int32_t oxq_gemm_fp8_all_reduce(oxq_handle* h, int64_t m, int64_t n, int64_t k, const uint8_t* x, int64_t ldx, const uint8_t* w, int64_t ldw,
                                 const float* sx, const float* sw, void* y_local, void* y_multicast, int64_t ldy, uint32_t* flags_local,
-                                uint32_t* flags_multicast, int64_t flag_words, int rank, int world, int64_t call_index) {
+                                uint32_t* flags_multicast, int64_t flag_words, int rank, int world) {
     OXQ_CHECK_HANDLE(h);
     if (int32_t rc = check_gemm_args(h, m, n, k, x, w, y_local, ldy)) return rc;
     if (!sx || !sw) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null scale pointer");
@@ -1187,15 +1200,14 @@ int32_t oxq_gemm_fp8_all_reduce(oxq_handle* h, int64_t m, int64_t n, int64_t k, 
     if (!y_multicast || ((uintptr_t)y_multicast & 15u) || !flags_local || !flags_multicast || ((uintptr_t)flags_local & 3u) || ((uintptr_t)flags_multicast & 3u))
         OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned multicast / flag pointer");
     if (n & 7) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "n must be a multiple of 8 (16-byte vectors through the switch)");
-    if (call_index < 0) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "negative call index");
     const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256);
-    if (flag_words < 2 * (tiles + 1)) OXQ_FAIL(h, OXQ_ERR_BUFFER_TOO_SMALL, "flag words: expected at least %lld, got %lld", (long long)(2 * (tiles + 1)), (long long)flag_words);
+    if (flag_words < 2 * (tiles + 1) + 1) OXQ_FAIL(h, OXQ_ERR_BUFFER_TOO_SMALL, "flag words: expected at least %lld, got %lld", (long long)(2 * (tiles + 1) + 1), (long long)flag_words);
     GemmParams p{};
     p.alpha = 1.0f; p.beta = 0.0f;
     p.m = (int)m; p.n = (int)n; p.k_bytes = (int)k; p.y = y_local; p.ldy = ldy; p.s0 = sx; p.s1 = sw;
-    // calls alternate between the two halves of the flag words
-    const int64_t set = (call_index & 1) * (flag_words / 2);
-    p.ar_mc_y = y_multicast; p.ar_flags = flags_local + set; p.ar_mc_flags = flags_multicast + set;
+    // the last word counts this rank's finished calls; its parity picks one of the two sets of flag words in front of it
+    p.ar_mc_y = y_multicast; p.ar_flags = flags_local; p.ar_mc_flags = flags_multicast;
+    p.ar_set_stride = (int)((flag_words - 1) / 2); p.ar_calls = flags_local + (flag_words - 1);
     p.ar_world = world; p.ar_rank = rank;
     // pause between two looks at a flag word: 232 us for the tensor-parallel down projection on two GPUs at 1000 ns against 241 at 0
     static const int sleep_ns = [] { const char* e = getenv("OXQ_AR_SLEEP_NS"); const int v = e ? atoi(e) : 1000; return v < 0 ? 0 : v; }();

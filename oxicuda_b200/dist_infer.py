@@ -320,8 +320,7 @@ class TpSwiGluMlp:
                 self.sync_reduce = False
             else:
                 self._sync_calls += 1
-                ops.multimem_all_reduce_bf16_2d_sync(hdl.multicast_ptr + ptr_offset_bytes, m, cols, ld, self.rank, self.tp, words,
-                                                     fh.multicast_ptr, self._sync_calls)
+                ops.multimem_all_reduce_bf16_2d_sync(hdl.multicast_ptr + ptr_offset_bytes, m, cols, ld, self.rank, self.tp, words, fh.multicast_ptr)
                 return
         hdl.barrier(channel=channel)
         ops.multimem_all_reduce_bf16_2d(hdl.multicast_ptr + ptr_offset_bytes, m, cols, ld, self.rank, self.tp)
@@ -333,7 +332,7 @@ class TpSwiGluMlp:
         if self._flags is None:
             import torch.distributed as dist
             import torch.distributed._symmetric_memory as symm_mem
-            words = symm_mem.empty((2 * 4096,), dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()))
+            words = symm_mem.empty((2 * 4096 + 1,), dtype=torch.int32, device=torch.device("cuda", torch.cuda.current_device()))
             words.zero_()
             fh = symm_mem.rendezvous(words, self.group if self.group is not None else dist.group.WORLD)
             if not fh.multicast_ptr:
@@ -365,8 +364,7 @@ class TpSwiGluMlp:
         if self.keep_h:
             self.last_h = h
         hq, sh = ops.fp8_quant_dynamic(h)
-        ops.gemm_fp8_all_reduce(hq, self.w_down_q, sh[1:], self.s_down, y, hdl.multicast_ptr, words, fh.multicast_ptr, self.rank, self.tp,
-                                self._fused_calls)
+        ops.gemm_fp8_all_reduce(hq, self.w_down_q, sh[1:], self.s_down, y, hdl.multicast_ptr, words, fh.multicast_ptr, self.rank, self.tp)
         self._fused_calls += 1
         return y
 

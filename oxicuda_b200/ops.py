@@ -728,14 +728,14 @@ def multimem_all_reduce_bf16(multicast_ptr: int, numel: int, rank: int, world: i
 
 
 def multimem_all_reduce_bf16_2d_sync(multicast_ptr: int, rows: int, cols: int, ld: int, rank: int, world: int, flags_local: torch.Tensor,
-                                     flags_multicast_ptr: int, call_number: int, device_index: int | None = None):
+                                     flags_multicast_ptr: int, device_index: int | None = None):
     """In-place all-reduce of a column block of a symmetric bf16 matrix with the cross-rank synchronisation inside the kernel."""
     handle(device_index).call("oxq_multimem_all_reduce_bf16_2d_sync", C.c_void_p(multicast_ptr), rows, cols, ld, rank, world, _p(flags_local),
-                              C.c_void_p(flags_multicast_ptr), call_number)
+                              C.c_void_p(flags_multicast_ptr))
 
 
 def gemm_fp8_all_reduce(x_q, w_q, sx, sw, y_local: torch.Tensor, y_multicast_ptr: int, flags_local: torch.Tensor, flags_multicast_ptr: int,
-                        rank: int, world: int, call_index: int):
+                        rank: int, world: int):
     """FP8 GEMM of this rank's K-shard with the all-reduce over the ranks fused in (RowLinear::forward_partial + all_reduce):
     y_local is this rank's [m x n] view of a symmetric bf16 buffer, flags_local its int32 flag words (zero before the first
     call); the *_multicast_ptr arguments are the multicast addresses of the same two buffers."""
@@ -743,7 +743,7 @@ def gemm_fp8_all_reduce(x_q, w_q, sx, sw, y_local: torch.Tensor, y_multicast_ptr
     n = w_q.shape[0]
     handle(x_q.device.index).call("oxq_gemm_fp8_all_reduce", m, n, k, _p(x_q), x_q.stride(0), _p(w_q), w_q.stride(0), _p(sx), _p(sw), _p(y_local),
                                   C.c_void_p(y_multicast_ptr), y_local.stride(0), _p(flags_local), C.c_void_p(flags_multicast_ptr),
-                                  flags_local.numel(), rank, world, call_index)
+                                  flags_local.numel(), rank, world)
     return y_local
 
 

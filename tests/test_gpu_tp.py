@@ -162,6 +162,17 @@ def _fused_rank(rank, world, port, q):
             torch.cuda.synchronize()
             assert layer._fused_calls == i + 1
             errs.append(float((y.float() - want.float()).abs().max() / want.float().abs().max()))
+        m = ms[-1]
+        xs, ys, gr = layer.capture(m)                        # replays alternate between the two sets of flag words like host calls do
+        for i in range(5):
+            xb = orc.f32_to_bf16_bits(orc.gaussian((m, hidden), 1.0, 80 + i))
+            x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+            xs.copy_(x)
+            gr.replay()
+            got = ys.clone()
+            want = plain.forward(x)
+            torch.cuda.synchronize()
+            errs.append(float((got.float() - want.float()).abs().max() / want.float().abs().max()))
         errs.append(float(ops.handle(torch.cuda.current_device()).device_status()))
     q.put((rank, errs))
     dist.barrier()
@@ -196,6 +207,18 @@ def _sync_rank(rank, world, port, q):
         torch.cuda.synchronize()
         errs.append(float((y.float() - want.float()).abs().max() / want.float().abs().max()))
     assert layer._sync_calls >= 6
+    # the same launches replayed from a CUDA graph: every replay has to wait for its own generation of signals
+    for m in (1024, 64):
+        xs, ys, gr = layer.capture(m)
+        for i in range(5):
+            xb = orc.f32_to_bf16_bits(orc.gaussian((m, hidden), 1.0, 60 + i))
+            x = torch.from_numpy(xb.view(np.int16)).cuda().view(torch.bfloat16)
+            xs.copy_(x)
+            gr.replay()
+            got = ys.clone()
+            want = plain.forward(x)
+            torch.cuda.synchronize()
+            errs.append(float((got.float() - want.float()).abs().max() / want.float().abs().max()))
     errs.append(float(ops.handle(torch.cuda.current_device()).device_status()))
     q.put((rank, errs))
     dist.barrier()

@@ -263,11 +263,10 @@ class TpSwiGluMlp:
         self.fused_reduce = self.use_multimem and os.environ.get("OXQ_TP_FUSED_REDUCE", "0") == "1"
         self._flags = None
         self._fused_calls = 0
-        # The in-switch reduce either synchronises the ranks itself (flag words through the switch) or runs between cross-rank
-        # barrier kernels.  Measured per step at M = 2048: 2 GPUs 0.623 / 0.591 ms, 4 GPUs 0.354 / 0.359, 8 GPUs 0.220 / 0.257:
-        # the first form from four ranks on.  OXQ_TP_SYNC_REDUCE=0 / 1 forces one of them.
-        sr = os.environ.get("OXQ_TP_SYNC_REDUCE", "")
-        self.sync_reduce = self.use_multimem and (sr == "1" or (sr != "0" and tp >= 4))
+        # The in-switch reduce runs between cross-rank barrier kernels, or (OXQ_TP_SYNC_REDUCE=1) synchronises the ranks itself
+        # through flag words in the switch.  Measured per step at M = 2048: 2 GPUs 0.591 / 0.623 ms, 8 GPUs 0.257 / 0.272 ms:
+        # the barrier form is the default.
+        self.sync_reduce = self.use_multimem and os.environ.get("OXQ_TP_SYNC_REDUCE", "0") == "1"
         self._sflags = None
         self._sync_calls = 0
 

@@ -319,6 +319,23 @@ def test_rms_norm_kats(orc):  # crates/oxicuda-lm/src/layer/norm.rs:186-227
     assert e.value.name == "DimensionMismatch"
 
 
+def test_swiglu_ffn_kats(orc):  # crates/oxicuda-lm/src/layer/ffn.rs:279-315, :359-389
+    one = np.ones(1, np.float32)
+    silu = lambda v: float(orc.ref_silu_mul(np.full(1, v, np.float32), one)[0])
+    assert abs(silu(0.0)) < 1e-6 and abs(silu(10.0) - 10.0) < 1e-3 and silu(1.0) > 0.0 and silu(-1.0) < 0.0
+    eye, eye2 = np.eye(4, dtype=np.float32), np.eye(2, dtype=np.float32)
+    assert np.allclose(orc.ref_linear_f32(np.array([[3.0, 4.0]], np.float32), eye2), [[3.0, 4.0]], atol=1e-6)   # linear_vec_identity
+    y = orc.ref_linear_f32(np.array([[1.0, 2.0]], np.float32), eye2, bias=np.array([10.0, 20.0], np.float32))
+    assert np.allclose(y, [[11.0, 22.0]], atol=1e-6)                                                 # linear_vec_with_bias
+    zeros8 = np.zeros((8, 4), np.float32)
+    out = orc.ref_swiglu_mlp(np.ones((1, 4), np.float32), zeros8, zeros8, np.zeros((4, 8), np.float32))
+    assert out.shape == (1, 4) and np.all(np.abs(out) < 1e-6)                                        # zero weights -> zero output
+    out = orc.ref_swiglu_mlp(np.full((1, 4), 2.0, np.float32), eye, eye, eye)                        # gate = up = down = I
+    assert np.allclose(out, 2.0 / (1.0 + math.exp(-2.0)) * 2.0, atol=1e-5)
+    out = orc.ref_swiglu_mlp(np.zeros((3, 4), np.float32), zeros8, zeros8, np.zeros((4, 8), np.float32))
+    assert out.shape == (3, 4)                                                                       # three tokens at once
+
+
 def test_gptq_kats(orc):  # crates/oxicuda-quant/src/scheme/gptq.rs:341-520
     l = orc.ref_cholesky_lower(np.array([[4.0, 2.0], [2.0, 3.0]], np.float32))          # L = [[2, 0], [1, sqrt 2]]
     assert np.allclose(l, [[2.0, 0.0], [1.0, np.sqrt(2.0)]], atol=1e-6) and np.allclose(l @ l.T, [[4.0, 2.0], [2.0, 3.0]], atol=1e-5)

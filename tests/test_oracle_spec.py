@@ -90,6 +90,27 @@ def test_spec_fp8_per_tensor(orc):
     assert np.array_equal(orc.spec_fp8_dequant(q, sc), orc.e4m3_to_f32(q) * sc)
 
 
+def test_spec_fp8_reference_properties(orc):  # crates/oxicuda-dnn/src/quantize/fp8_quantize.rs:494-655
+    """The properties the reference asserts of its absmax-scaled FP8 arithmetic (clamp at 448, tiny values to zero,
+    scale = absmax / 448, round trip within a step, odd symmetry) hold for the spec oracle as well."""
+    f = lambda v, sc=1.0: orc.spec_fp8_dequant(orc.spec_fp8_quant(np.asarray(v, np.float32), np.float32(sc)), np.float32(sc))
+    assert abs(f([1000.0])[0] - 448.0) < 1.0 and abs(f([-1000.0])[0] + 448.0) < 1.0                  # :494-509
+    assert abs(f([1e-10])[0]) < 1.0 / 8.0                                                             # :529-538
+    vals = np.array([10.0, -50.0, 30.0, -20.0, 5.0], np.float32)                                      # :555-575
+    am = orc.spec_absmax(vals)
+    sc = orc.spec_fp8_scale(am)
+    assert abs(am - 50.0) < 1e-6 and abs(float(sc) - 50.0 / 448.0) < 1e-6
+    assert abs(f([am], sc)[0] - am) < float(sc) * 0.5
+    orig = np.array([1.0, -2.0, 0.5, -0.25, 4.0, -3.75], np.float32)                                  # :579-598
+    sc = max(np.float32(4.0) / np.float32(448.0), np.float32(1e-12))
+    back = f(orig, sc)
+    # the reference's model has a fixed step of scale / 8; real E4M3 has a relative step of 2^-3 per binade, so the
+    # bound that holds for it is half a step of the value's own binade: |x| / 16
+    assert np.all(np.abs(back - orig) <= np.abs(orig) / 16.0 + 1e-6)
+    for x in (0.5, 1.0, 2.0, 5.0, 10.0, 100.0):                                                       # :622-633
+        assert abs(f([x])[0] + f([-x])[0]) < 1e-5
+
+
 def test_spec_int4g(orc):
     x = orc.gaussian((8, 512), 0.02, 3)
     codes, sc, zp = orc.spec_int4g_quant(x, 128, orc.ROUND_HALF_AWAY)

@@ -8,6 +8,8 @@
 #include <cstdint>
 #include <stdexcept>
 #include <string>
+#include <utility>
+#include <vector>
 #include "../../include/oxq.h"
 
 namespace oxicuda_blas {
@@ -173,6 +175,62 @@ struct Fp4GemmConfig {
         return std::string("fp4_") + (format == Fp4Format::E2M1 ? "e2m1" : "int4") + "_gemm_" + std::to_string(m) + "x" + std::to_string(n) + "x" +
                std::to_string(k) + "_" + (accumulator == SubByteAccumulator::F32 ? "f32" : "f16");
     }
+};
+
+// PackedFp4 (precision/fp4_fp6_ops.rs:452-480): two 4-bit codes in a byte, the first in the low nibble.
+struct PackedFp4 {
+    uint8_t bits;
+    std::pair<uint8_t, uint8_t> unpack() const { return {uint8_t(bits & 0xF), uint8_t(bits >> 4)}; }
+};
+
+// MicroScalingQuantizer (precision/fp4_fp6_ops.rs:736-898), the FP4 half: one f32 scale max|x| / 6 per block (1 for an
+// all-zero block; the last block may be short), codes from the floor-type E2M1 encoder on x / scale; an odd length is
+// padded with one zero code.  Host slices are staged through device buffers on
+// device 0's default stream.  The device path covers Fp4Format::E2M1.
+class MicroScalingQuantizer {
+public:
+    explicit MicroScalingQuantizer(const MicroScalingConfig& config) : config(config) {}
+    MicroScalingConfig config;
+    std::pair<std::vector<PackedFp4>, std::vector<float>> quantize_fp4(const std::vector<float>& values, Fp4Format format) const {
+        config.validate();
+        if (format != Fp4Format::E2M1) throw BlasError(OXQ_ERR_UNSUPPORTED_OPERATION, "the device path covers Fp4Format::E2M1");
+        const size_t n = values.size(), bs = config.block_size;
+        std::pair<std::vector<PackedFp4>, std::vector<float>> out{std::vector<PackedFp4>((n + 1) / 2), std::vector<float>((n + bs - 1) / bs)};
+        if (n == 0) return out;
+        BlasHandle h;
+        Buf x(n * sizeof(float)), packed(out.first.size()), scales(out.second.size() * sizeof(float));
+        cuda(cudaMemcpy(x.p, values.data(), n * sizeof(float), cudaMemcpyHostToDevice));
+        h.check(oxq_fp4_microscale_quant(h.raw(), (const float*)x.p, (int64_t)n, (int64_t)bs, (uint8_t*)packed.p, (float*)scales.p));
+        cuda(cudaDeviceSynchronize());
+        cuda(cudaMemcpy(out.first.data(), packed.p, out.first.size(), cudaMemcpyDeviceToHost));
+        cuda(cudaMemcpy(out.second.data(), scales.p, out.second.size() * sizeof(float), cudaMemcpyDeviceToHost));
+        return out;
+    }
+    std::vector<float> dequantize_fp4(const std::vector<PackedFp4>& packed, const std::vector<float>& scales, Fp4Format format, size_t original_len) const {
+        if (format != Fp4Format::E2M1) throw BlasError(OXQ_ERR_UNSUPPORTED_OPERATION, "the device path covers Fp4Format::E2M1");
+        const size_t bs = config.block_size;
+        const size_t n = original_len < packed.size() * 2 ? original_len : packed.size() * 2;   // .take(original_len) of what was packed
+        std::vector<float> out(n);
+        if (n == 0) return out;
+        BlasHandle h;
+        std::vector<float> sc((n + bs - 1) / bs, 1.0f);                    // a missing scale counts as 1 (scales.get(..).unwrap_or(1.0))
+        for (size_t i = 0; i < sc.size() && i < scales.size(); i++) sc[i] = scales[i];
+        Buf p((n + 1) / 2), s(sc.size() * sizeof(float)), y(n * sizeof(float));
+        cuda(cudaMemcpy(p.p, packed.data(), (n + 1) / 2, cudaMemcpyHostToDevice));
+        cuda(cudaMemcpy(s.p, sc.data(), sc.size() * sizeof(float), cudaMemcpyHostToDevice));
+        h.check(oxq_fp4_microscale_dequant(h.raw(), (const uint8_t*)p.p, (const float*)s.p, (int64_t)n, (int64_t)bs, (float*)y.p));
+        cuda(cudaDeviceSynchronize());
+        cuda(cudaMemcpy(out.data(), y.p, n * sizeof(float), cudaMemcpyDeviceToHost));
+        return out;
+    }
+private:
+    static void cuda(cudaError_t e) { if (e != cudaSuccess) throw BlasError(OXQ_ERR_LAUNCH_FAILED, cudaGetErrorString(e)); }
+    struct Buf {
+        void* p = nullptr;
+        explicit Buf(size_t bytes) { if (bytes) cuda(cudaMalloc(&p, bytes)); }
+        ~Buf() { if (p) cudaFree(p); }
+        Buf(const Buf&) = delete; Buf& operator=(const Buf&) = delete;
+    };
 };
 
 // The GEMMs those configurations describe, over the library's kernels.  The quantised operand is the weight W[N x K]

@@ -237,6 +237,81 @@ struct BlockQuantizedInt8 {
     }
 };
 
+// SmoothQuantMigrator (crates/oxicuda-quant/src/scheme/smooth_quant.rs:54-293).  Activations are [n_tokens x n_channels],
+// weights [n_out x n_channels], both row-major f32 host slices staged through device buffers; the checks and their order
+// are the reference's.
+struct SmoothQuantConfig { float alpha = 0.5f; };
+class SmoothQuantMigrator {
+public:
+    explicit SmoothQuantMigrator(float alpha) { config.alpha = alpha; }
+    SmoothQuantConfig config;
+    // s[j] = max(|act_max[j]|, 1e-8)^alpha / max(|weight_max[j]|, 1e-8)^(1 - alpha)        (smooth_quant.rs:84-113)
+    std::vector<float> compute_migration_scales(const std::vector<float>& act_max, const std::vector<float>& weight_max) const {
+        if (act_max.empty()) throw QuantError("EmptyInput", "SmoothQuantMigrator::compute_migration_scales");
+        if (act_max.size() != weight_max.size())
+            throw QuantError("DimensionMismatch", "dimension mismatch: expected " + std::to_string(act_max.size()) + ", got " + std::to_string(weight_max.size()));
+        detail::Handle h;
+        detail::DevBuf<float> a(act_max.size()), w(weight_max.size()), s(act_max.size());
+        a.upload(act_max.data()); w.upload(weight_max.data());
+        detail::check(oxq_smooth_scales(h.h, a.p, w.p, (int64_t)act_max.size(), config.alpha, s.p), h.h);
+        detail::cuda(cudaDeviceSynchronize());
+        std::vector<float> out(act_max.size());
+        s.download(out.data());
+        return out;
+    }
+    // per-channel max |x| over the rows                                                    (smooth_quant.rs:125-196)
+    static std::vector<float> compute_act_stats(const std::vector<float>& acts, size_t n_tokens, size_t n_channels) {
+        return col_absmax(acts, n_tokens, n_channels, "compute_act_stats: empty activations");
+    }
+    static std::vector<float> compute_weight_stats(const std::vector<float>& weights, size_t n_out, size_t n_channels) {
+        return col_absmax(weights, n_out, n_channels, "compute_weight_stats: empty weights");
+    }
+    // acts[t, j] /= max(scales[j], 1e-12), in place                                        (smooth_quant.rs:198-222)
+    static void smooth_activations(std::vector<float>& acts, const std::vector<float>& scales, size_t n_tokens, size_t n_channels) {
+        apply(acts, scales, n_tokens, n_channels, 1);
+    }
+    // weights[r, j] *= scales[j], in place                                                 (smooth_quant.rs:231-254)
+    static void smooth_weights(std::vector<float>& weights, const std::vector<float>& scales, size_t n_out, size_t n_channels) {
+        apply(weights, scales, n_out, n_channels, 0);
+    }
+    // statistics, scales and both in-place updates; returns the scales                     (smooth_quant.rs:274-293)
+    std::vector<float> smooth_layer(std::vector<float>& acts, std::vector<float>& weights, size_t n_tokens, size_t n_channels, size_t n_out) const {
+        const std::vector<float> act_stats = compute_act_stats(acts, n_tokens, n_channels);
+        const std::vector<float> weight_stats = compute_weight_stats(weights, n_out, n_channels);
+        const std::vector<float> scales = compute_migration_scales(act_stats, weight_stats);
+        smooth_activations(acts, scales, n_tokens, n_channels);
+        smooth_weights(weights, scales, n_out, n_channels);
+        return scales;
+    }
+private:
+    static std::vector<float> col_absmax(const std::vector<float>& x, size_t rows, size_t cols, const char* empty_msg) {
+        if (x.empty()) throw QuantError("EmptyInput", empty_msg);
+        if (x.size() != rows * cols)
+            throw QuantError("DimensionMismatch", "dimension mismatch: expected " + std::to_string(rows * cols) + ", got " + std::to_string(x.size()));
+        detail::Handle h;
+        detail::DevBuf<float> d(x.size()), st(cols);
+        d.upload(x.data());
+        detail::check(oxq_smooth_col_absmax(h.h, d.p, (int64_t)rows, (int64_t)cols, st.p), h.h);
+        detail::cuda(cudaDeviceSynchronize());
+        std::vector<float> out(cols);
+        st.download(out.data());
+        return out;
+    }
+    static void apply(std::vector<float>& x, const std::vector<float>& scales, size_t rows, size_t cols, int divide) {
+        if (x.size() != rows * cols)
+            throw QuantError("DimensionMismatch", "dimension mismatch: expected " + std::to_string(rows * cols) + ", got " + std::to_string(x.size()));
+        if (scales.size() != cols)
+            throw QuantError("DimensionMismatch", "dimension mismatch: expected " + std::to_string(cols) + ", got " + std::to_string(scales.size()));
+        if (x.empty()) return;                                            // the reference's loops run zero times
+        detail::Handle h;
+        detail::DevBuf<float> d(x.size()), s(cols);
+        d.upload(x.data()); s.upload(scales.data());
+        detail::check(oxq_smooth_apply(h.h, d.p, (int64_t)rows, (int64_t)cols, s.p, divide), h.h);
+        detail::cuda(cudaDeviceSynchronize());
+        d.download(x.data());
+    }
+};
+
 // GptqConfig / GptqOutput / GptqQuantizer (crates/oxicuda-quant/src/scheme/gptq.rs:30-257): the whole layer is
 // quantized on the device by oxq_gptq_quantize_layer; results equal the reference's CPU loop bit for bit.
 struct GptqConfig {

@@ -95,6 +95,68 @@ int main(int argc, char** argv) {
             std::vector<float> aw = {-0.6f, 0.4f, -0.2f, 0.8f, 0.6f, -0.4f, 0.2f, -0.8f};
             if (!(GptqQuantizer(asym).quantize_layer(aw, 2, 4, eye(4)).reconstruction_mse(aw) < 0.05f)) return 19;
         }
+        // SmoothQuantMigrator: the reference's own tests (smooth_quant.rs:311-440)
+        {
+            auto near = [](float a, float b, float eps) { return std::fabs(a - b) <= eps; };
+            std::vector<float> sc = SmoothQuantMigrator(0.5f).compute_migration_scales({4.0f, 1.0f, 9.0f}, {1.0f, 4.0f, 1.0f});
+            if (!near(sc[0], 2.0f, 1e-5f) || !near(sc[1], 0.5f, 1e-5f) || !near(sc[2], 3.0f, 1e-5f)) return 20;
+            sc = SmoothQuantMigrator(1.0f).compute_migration_scales({2.0f, 5.0f}, {3.0f, 7.0f});
+            if (!near(sc[0], 2.0f, 1e-5f) || !near(sc[1], 5.0f, 1e-5f)) return 21;
+            sc = SmoothQuantMigrator(0.0f).compute_migration_scales({4.0f, 1.0f}, {2.0f, 5.0f});
+            if (!near(sc[0], 0.5f, 1e-5f) || !near(sc[1], 0.2f, 1e-5f)) return 22;
+            std::vector<float> st = SmoothQuantMigrator::compute_act_stats({1.0f, -5.0f, 2.0f, -3.0f, 4.0f, 1.0f}, 2, 3);
+            if (st[0] != 3.0f || st[1] != 5.0f || st[2] != 2.0f) return 23;
+            st = SmoothQuantMigrator::compute_weight_stats({0.5f, -2.0f, 1.0f, -1.5f, 0.3f, 3.0f}, 2, 3);
+            if (st[0] != 1.5f || st[1] != 2.0f || st[2] != 3.0f) return 24;
+            int serr = 0;
+            try { SmoothQuantMigrator(0.5f).compute_migration_scales(std::vector<float>(3, 1.0f), std::vector<float>(4, 1.0f)); }
+            catch (const QuantError& e) { serr += e.variant == "DimensionMismatch"; }
+            try { SmoothQuantMigrator(0.5f).compute_migration_scales({}, {}); } catch (const QuantError& e) { serr += e.variant == "EmptyInput"; }
+            try { SmoothQuantMigrator::compute_act_stats(std::vector<float>(5, 1.0f), 2, 3); } catch (const QuantError& e) { serr += e.variant == "DimensionMismatch"; }
+            if (serr != 3) return 25;
+            // smoothing_preserves_layer_output: Y = X W^T is unchanged by the migration
+            const size_t n_tok = 3, n_ch = 4, n_out = 2;
+            std::vector<float> acts(n_tok * n_ch), w(n_out * n_ch);
+            for (size_t i = 0; i < acts.size(); i++) acts[i] = (float)i * 0.3f - 1.0f;
+            for (size_t i = 0; i < w.size(); i++) w[i] = (float)i * 0.2f - 0.5f;
+            auto matmul_nt = [&](const std::vector<float>& x, const std::vector<float>& ww) {
+                std::vector<float> y(n_tok * n_out, 0.0f);
+                for (size_t t = 0; t < n_tok; t++)
+                    for (size_t o = 0; o < n_out; o++)
+                        for (size_t j = 0; j < n_ch; j++) y[t * n_out + o] += x[t * n_ch + j] * ww[o * n_ch + j];
+                return y;
+            };
+            const std::vector<float> y0 = matmul_nt(acts, w);
+            SmoothQuantMigrator(0.5f).smooth_layer(acts, w, n_tok, n_ch, n_out);
+            const std::vector<float> y1 = matmul_nt(acts, w);
+            for (size_t i = 0; i < y0.size(); i++) if (!near(y0[i], y1[i], 1e-4f)) return 26;
+            // smoothing_reduces_act_channel_range_imbalance
+            std::vector<float> a2 = {100.0f, 1.0f, -100.0f, 1.0f, 100.0f, -1.0f, -100.0f, -1.0f}, w2 = {0.5f, 0.5f, -0.5f, 0.5f};
+            sc = SmoothQuantMigrator(0.5f).smooth_layer(a2, w2, 4, 2, 2);
+            float m0 = 0.0f, m1 = 0.0f;
+            for (int t = 0; t < 4; t++) { m0 = std::fmax(m0, std::fabs(a2[t * 2])); m1 = std::fmax(m1, std::fabs(a2[t * 2 + 1])); }
+            if (!(sc[0] > 1.0f) || !(m0 / std::fmax(m1, 1e-8f) < 100.0f)) return 27;
+        }
+        // MicroScalingQuantizer, FP4 half (fp4_fp6_ops.rs:763-897): scale = block max / 6, 1 for an all-zero block, odd lengths padded
+        {
+            using namespace oxicuda_blas;
+            MicroScalingQuantizer mq{MicroScalingConfig()};
+            std::vector<float> v(64);
+            for (int i = 0; i < 64; i++) v[i] = (float)i * 0.25f - 4.0f;
+            auto enc = mq.quantize_fp4(v, Fp4Format::E2M1);
+            if (enc.first.size() != 32 || enc.second.size() != 2 || enc.second[0] != 4.0f / 6.0f || enc.second[1] != 11.75f / 6.0f) return 28;
+            if (enc.first[0].unpack().first != 0xF) return 29;                 // -4 / (4/6) = -6: sign bit + the top code
+            std::vector<float> rec = mq.dequantize_fp4(enc.first, enc.second, Fp4Format::E2M1, 64);
+            if (rec.size() != 64 || rec[0] != -4.0f) return 30;
+            for (int i = 0; i < 64; i++) if (std::fabs(rec[i] - v[i]) > 11.75f * 0.35f) return 31;
+            auto z = mq.quantize_fp4(std::vector<float>(33, 0.0f), Fp4Format::E2M1);
+            if (z.first.size() != 17 || z.second.size() != 2 || z.second[0] != 1.0f || z.second[1] != 1.0f) return 32;
+            if (mq.dequantize_fp4(z.first, z.second, Fp4Format::E2M1, 33).size() != 33) return 33;
+            int merr = 0;
+            MicroScalingConfig bad; bad.block_size = 16;
+            try { MicroScalingQuantizer(bad).quantize_fp4(v, Fp4Format::E2M1); } catch (const BlasError& e) { merr += e.variant == "InvalidArgument"; }
+            if (merr != 1) return 34;
+        }
         FILE* f = fopen(argv[1], "wb");
         if (!f) return 9;
         fwrite(big.data(), sizeof(float), big.size(), f);

@@ -9,12 +9,12 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _build(tmp_path):
+def _build(tmp_path, name="host_mirror_test"):
     from oxicuda_b200 import _build
     _build.build()
-    exe = str(tmp_path / "host_mirror_test")
+    exe = str(tmp_path / name)
     libdir = os.path.join(ROOT, "oxicuda_b200", "lib")
-    cmd = ["/usr/bin/g++", "-std=c++17", "-O1", "-I/usr/local/cuda/include", os.path.join(ROOT, "tests", "cpp", "host_mirror_test.cpp"),
+    cmd = ["/usr/bin/g++", "-std=c++17", "-O1", "-I/usr/local/cuda/include", os.path.join(ROOT, "tests", "cpp", name + ".cpp"),
            "-o", exe, "-L" + libdir, "-loxq_b200", "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath," + libdir]
     res = subprocess.run(cmd, capture_output=True, text=True)
     assert res.returncode == 0, res.stderr
@@ -38,6 +38,7 @@ def test_host_config_types(tmp_path):
 def test_host_mirror_compiles_and_links(tmp_path):
     exe = _build(tmp_path)
     assert os.path.exists(exe)
+    assert os.path.exists(_build(tmp_path, "host_dnn_test"))
 
 
 @pytest.mark.gpu
@@ -60,3 +61,42 @@ def test_host_mirror_runs_and_matches_oracle(tmp_path, orc):
     t = np.array([0.0, 1.0, -1.0, 0.5, 0.0, 2.0, -2.0, 1.5], np.float32).reshape(2, 4)
     qt, st = orc.spec_int8_quant_rows(t, orc.ROUND_HALF_AWAY)
     assert np.array_equal(deq, orc.spec_int8_dequant_rows(qt, st).ravel())
+
+
+@pytest.mark.gpu
+def test_host_dnn_mirror_runs_and_matches_oracle(tmp_path, orc):
+    """oxicuda_dnn.hpp: known answers and buffer checks inside the driver; its 4100-element results against the oracle bit for bit."""
+    exe = _build(tmp_path, "host_dnn_test")
+    out = str(tmp_path / "dnn.bin")
+    res = subprocess.run([exe, out], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, f"rc={res.returncode} {res.stderr}"
+    raw = np.fromfile(out, dtype=np.uint8)
+    n, ng, nb = 4100, (4100 + 127) // 128, (4100 + 31) // 32
+    pos = 0
+
+    def take(count, dtype):
+        nonlocal pos
+        size = count * np.dtype(dtype).itemsize
+        v = raw[pos:pos + size].view(dtype)
+        pos += size
+        return v
+
+    x = take(n, np.float32)
+    q8, s8 = take(n, np.int8), take(1, np.float32)
+    qf, sf = take(n, np.uint8), take(1, np.float32)
+    p4s, s4s = take(n // 2, np.uint8), take(ng, np.float32)
+    p4a, s4a, z4a, y4a = take(n // 2, np.uint8), take(ng, np.float32), take(ng, np.float32), take(n, np.float32)
+    ob, sb = take(n, np.uint8), take(nb, np.float32)
+    assert pos == raw.size
+    q_ref, s_ref = orc.ref_dnn_int8_quant(x)
+    assert np.array_equal(s8.view(np.uint32), s_ref.view(np.uint32)) and np.array_equal(q8, q_ref)
+    sc = orc.spec_fp8_scale(orc.spec_absmax(x))
+    assert sf[0] == sc and np.array_equal(qf, orc.spec_fp8_quant(x, sc))
+    p_ref, sc_ref, _ = orc.ref_dnn_int4_quant(x, 128, True)
+    assert np.array_equal(p4s, p_ref) and np.array_equal(s4s.view(np.uint32), sc_ref.view(np.uint32))
+    p_ref, sc_ref, z_ref = orc.ref_dnn_int4_quant(x, 128, False)
+    assert np.array_equal(p4a, p_ref) and np.array_equal(s4a.view(np.uint32), sc_ref.view(np.uint32))
+    assert np.array_equal(z4a.view(np.uint32), z_ref.view(np.uint32))
+    assert np.array_equal(y4a.view(np.uint32), orc.ref_dnn_int4_dequant(p_ref, sc_ref, n, 128, False).view(np.uint32))
+    o_ref, sb_ref = orc.ref_dnn_block_scaled_quant(x, 32)
+    assert np.array_equal(ob, o_ref) and np.array_equal(sb.view(np.uint32), sb_ref.view(np.uint32))

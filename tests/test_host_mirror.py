@@ -41,6 +41,14 @@ def test_host_mirror_compiles_and_links(tmp_path):
     assert os.path.exists(_build(tmp_path, "host_dnn_test"))
 
 
+def test_host_dist_infer_types(tmp_path):
+    """Rank coordinates, handle accessors and the layers' argument errors (the reference's tests of handle.rs:246-360 and the
+    error cases of column_parallel.rs / row_parallel.rs restated in tests/cpp/host_dist_infer_test.cpp): host only."""
+    exe = _build(tmp_path, "host_dist_infer_test")
+    run = subprocess.run([exe, "host"], capture_output=True, text=True, timeout=60)
+    assert run.returncode == 0, f"check {run.returncode} failed: {run.stdout} {run.stderr}"
+
+
 @pytest.mark.gpu
 def test_host_mirror_runs_and_matches_oracle(tmp_path, orc):
     exe = _build(tmp_path)
@@ -100,3 +108,26 @@ def test_host_dnn_mirror_runs_and_matches_oracle(tmp_path, orc):
     assert np.array_equal(y4a.view(np.uint32), orc.ref_dnn_int4_dequant(p_ref, sc_ref, n, 128, False).view(np.uint32))
     o_ref, sb_ref = orc.ref_dnn_block_scaled_quant(x, 32)
     assert np.array_equal(ob, o_ref) and np.array_equal(sb.view(np.uint32), sb_ref.view(np.uint32))
+
+
+@pytest.mark.gpu
+def test_host_dist_infer_mirror_runs_and_matches_oracle(tmp_path, orc):
+    """oxicuda_dist_infer.hpp: the reference's ColumnLinear / RowLinear cases inside the driver (exact small integers); its
+    256 -> 512 -> 256 pair at tp = 4 against the f32 oracle on the bf16-rounded operands."""
+    exe = _build(tmp_path, "host_dist_infer_test")
+    out = str(tmp_path / "dist.bin")
+    res = subprocess.run([exe, out], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, f"rc={res.returncode} {res.stderr}"
+    raw = np.fromfile(out, dtype=np.float32)
+    tp, in_f, mid, batch = 4, 256, 512, 5
+    sizes = [batch * in_f, mid * in_f, mid, in_f * mid, in_f, batch * mid, batch * in_f]
+    assert raw.size == sum(sizes)
+    x, w1, b1, w2, b2, h, y = np.split(raw, np.cumsum(sizes)[:-1])
+    rb = lambda a: orc.bf16_bits_to_f32(orc.f32_to_bf16_bits(a))  # noqa: E731
+    x, w1, w2 = rb(x).reshape(batch, in_f), rb(w1).reshape(mid, in_f), rb(w2).reshape(in_f, mid)
+    h_ref = orc.ref_linear_f32(x, w1, b1)
+    h = h.reshape(batch, mid)
+    assert np.abs(h - h_ref).max() <= 2.0 ** -6 * np.abs(h_ref).max()          # two bf16 roundings (product, then product + bias): one ulp of the largest value
+    # the row layer continues from the gathered h the driver produced: tp partial sums, each rounded to bf16
+    y_ref = orc.ref_linear_f32(rb(h), w2, b2)
+    assert np.abs(y.reshape(batch, in_f) - y_ref).max() <= 2.0 ** -6 * np.abs(y_ref).max()

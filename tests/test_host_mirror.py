@@ -35,6 +35,14 @@ def test_host_config_types(tmp_path):
     assert run.returncode == 0, f"check {run.returncode} failed: {run.stdout} {run.stderr}"
 
 
+def test_host_lm_types(tmp_path):
+    """WeightTensor, silu and SwiGluFfn's argument errors (crates/oxicuda-lm/src/layer/ffn.rs:279-296, :391-395; weights.rs:31-76)
+    restated in tests/cpp/host_lm_test.cpp: host only."""
+    exe = _build(tmp_path, "host_lm_test")
+    run = subprocess.run([exe, "host"], capture_output=True, text=True, timeout=60)
+    assert run.returncode == 0, f"check {run.returncode} failed: {run.stdout} {run.stderr}"
+
+
 def test_host_mirror_compiles_and_links(tmp_path):
     exe = _build(tmp_path)
     assert os.path.exists(exe)
@@ -131,3 +139,26 @@ def test_host_dist_infer_mirror_runs_and_matches_oracle(tmp_path, orc):
     # the row layer continues from the gathered h the driver produced: tp partial sums, each rounded to bf16
     y_ref = orc.ref_linear_f32(rb(h), w2, b2)
     assert np.abs(y.reshape(batch, in_f) - y_ref).max() <= 2.0 ** -6 * np.abs(y_ref).max()
+
+
+@pytest.mark.gpu
+def test_host_lm_mirror_runs_and_matches_oracle(tmp_path, orc):
+    """oxicuda_lm.hpp: the reference's SwiGluFfn cases inside the driver; its 256 / 200 layer on five tokens against the f32
+    oracle (SwiGluFfn::forward restated) and against the same arithmetic with h rounded to bf16 as the device holds it."""
+    exe = _build(tmp_path, "host_lm_test")
+    out = str(tmp_path / "lm.bin")
+    res = subprocess.run([exe, out], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, f"rc={res.returncode} {res.stderr}"
+    raw = np.fromfile(out, dtype=np.float32)
+    hidden, inter, tokens = 256, 200, 5
+    sizes = [tokens * hidden, inter * hidden, inter * hidden, hidden * inter, tokens * hidden]
+    assert raw.size == sum(sizes)
+    x, wg, wu, wd, y = np.split(raw, np.cumsum(sizes)[:-1])
+    rb = lambda a: orc.bf16_bits_to_f32(orc.f32_to_bf16_bits(a))  # noqa: E731
+    x, wg, wu, wd = rb(x).reshape(tokens, hidden), rb(wg).reshape(inter, hidden), rb(wu).reshape(inter, hidden), rb(wd).reshape(hidden, inter)
+    y = y.reshape(tokens, hidden)
+    y_ref = orc.ref_swiglu_mlp(x, wg, wu, wd)
+    scale = np.abs(y_ref).max()
+    assert np.isfinite(y).all() and np.abs(y - y_ref).max() <= 2.0 ** -5 * scale     # h and y each rounded to bf16
+    h = rb(orc.ref_silu_mul(orc.ref_linear_f32(x, wg), orc.ref_linear_f32(x, wu)))
+    assert np.abs(y - rb(orc.ref_linear_f32(h, wd))).max() <= 2.0 ** -6 * scale       # same roundings: what is left is summation order

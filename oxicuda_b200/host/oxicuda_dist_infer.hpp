@@ -2,6 +2,7 @@
 //   ParallelismConfig, RankCoordinates, DistInferHandle   crates/oxicuda-dist-infer/src/handle.rs:40-240
 //   ColumnLinear (from_full_weight, local_forward, all_gather)               tensor_parallel/column_parallel.rs:103-204
 //   RowLinear (from_full_weight, slice_input, local_forward, all_reduce)     tensor_parallel/row_parallel.rs:97-223
+//   TpSwiGluMlp: SwiGluFfn (crates/oxicuda-lm/src/layer/ffn.rs:202-254) over weights cut the same way, FP8, one fused call
 // Same names, argument meaning, check order and error variants as the reference.  The reference computes the shard's
 // product with f32 loops on the CPU; here the shard lives on the GPU as bf16 and the product is one tensor-core GEMM
 // (oxq_gemm_bf16, f32 accumulation, bf16 result) followed by the bias add (oxq_bias_add_bf16).  Host slices are
@@ -244,6 +245,120 @@ public:
 private:
     explicit RowLinear(const DistInferHandle& h) : handle(h) {}
     std::shared_ptr<detail::DeviceShard> shard_;
+};
+
+// One rank's shard of a tensor-parallel SwiGLU MLP with FP8 (E4M3) weights: SwiGluFfn (crates/oxicuda-lm/src/layer/ffn.rs:202-254)
+// with w_gate / w_up cut by rows as ColumnLinear::from_full_weight cuts them and w_down by columns as RowLinear::from_full_weight
+// does, so that the sum of the ranks' outputs is the layer's output.  The shard is quantised once on the device (one scale for
+// the gate/up tensor, interleaved in blocks of 128 rows, one for the down tensor); a forward is one call of oxq_mlp_swiglu_tp:
+// x quantised per tensor, gate/up GEMM with silu(gate) * up in the epilogue, h quantised per shard, down GEMM and, when asked
+// and a communicator exists, the all-reduce.  Sizes: hidden a multiple of 16, inter / tp a multiple of 128.
+class TpSwiGluMlp {
+public:
+    DistInferHandle handle;
+    size_t hidden = 0, inter = 0, inter_local = 0;
+    TpSwiGluMlp(const DistInferHandle& handle, size_t hidden, size_t inter, const std::vector<float>& w_gate, const std::vector<float>& w_up,
+                const std::vector<float>& w_down)
+        : handle(handle), hidden(hidden), inter(inter) {
+        const size_t tp = handle.config.tp;
+        if (inter % tp != 0) throw DistInferError("TpFeaturesMisaligned", "features " + std::to_string(inter) + " not divisible by degree " + std::to_string(tp), inter, tp);
+        inter_local = inter / tp;
+        for (const std::vector<float>* w : {&w_gate, &w_up, &w_down})
+            if (w->size() != inter * hidden)
+                throw DistInferError("DimensionMismatch", "expected " + std::to_string(inter * hidden) + ", got " + std::to_string(w->size()), inter * hidden, w->size());
+        if (inter_local == 0 || inter_local % 128 != 0 || hidden == 0 || hidden % 16 != 0)
+            throw DistInferError("ShardShapeMismatch", "the shard needs hidden % 16 == 0 and inter / tp % 128 == 0", inter_local, hidden);
+        detail::cuda(cudaSetDevice(handle.device));
+        const int32_t rc = oxq_handle_create(handle.device, nullptr, &h_);
+        if (rc) throw DistInferError(oxq_status_name(rc), "oxq_handle_create");
+        try {
+            const size_t r0 = handle.tp_rank() * inter_local, n_gu = 2 * inter_local * hidden, n_d = hidden * inter_local;
+            std::vector<float> gu(n_gu), dn(n_d);
+            for (size_t r = 0; r < inter_local; r++) {
+                const size_t blk = r / 128, in_blk = r % 128;
+                std::memcpy(&gu[((2 * blk) * 128 + in_blk) * hidden], &w_gate[(r0 + r) * hidden], hidden * sizeof(float));
+                std::memcpy(&gu[((2 * blk + 1) * 128 + in_blk) * hidden], &w_up[(r0 + r) * hidden], hidden * sizeof(float));
+            }
+            for (size_t o = 0; o < hidden; o++) std::memcpy(&dn[o * inter_local], &w_down[o * inter + r0], inter_local * sizeof(float));
+            detail::cuda(cudaMalloc(&w_gu_, n_gu));
+            detail::cuda(cudaMalloc(&w_down_, n_d));
+            detail::cuda(cudaMalloc((void**)&stats_, 4 * sizeof(float)));
+            void* stage = nullptr;
+            detail::cuda(cudaMalloc(&stage, (n_gu > n_d ? n_gu : n_d) * sizeof(float)));
+            int32_t q = OXQ_OK;
+            if (cudaMemcpy(stage, gu.data(), n_gu * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) q = OXQ_ERR_LAUNCH_FAILED;
+            if (!q) q = oxq_fp8_quant_dynamic(h_, stage, OXQ_F32, (int64_t)n_gu, (uint8_t*)w_gu_, stats_);
+            if (!q && cudaDeviceSynchronize() != cudaSuccess) q = OXQ_ERR_LAUNCH_FAILED;
+            if (!q && cudaMemcpy(stage, dn.data(), n_d * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) q = OXQ_ERR_LAUNCH_FAILED;
+            if (!q) q = oxq_fp8_quant_dynamic(h_, stage, OXQ_F32, (int64_t)n_d, (uint8_t*)w_down_, stats_ + 2);
+            if (!q && cudaDeviceSynchronize() != cudaSuccess) q = OXQ_ERR_LAUNCH_FAILED;
+            cudaFree(stage);
+            check(q);
+        } catch (...) { release(); throw; }
+    }
+    ~TpSwiGluMlp() { release(); }
+    TpSwiGluMlp(const TpSwiGluMlp&) = delete; TpSwiGluMlp& operator=(const TpSwiGluMlp&) = delete;
+    oxq_handle* library_handle() const { return h_; }
+    // joins the tensor-parallel group: `id_128` is the identifier rank 0 got from oxq_comm_unique_id
+    void init_comm(const void* id_128) { check(oxq_comm_init(h_, id_128, (int)handle.config.tp, (int)handle.tp_rank())); }
+    oxq_tp_mlp_weights weights() const {
+        oxq_tp_mlp_weights w{};
+        w.variant = OXQ_TP_FP8; w.hidden = (int64_t)hidden; w.inter_local = (int64_t)inter_local;
+        w.w_gu = w_gu_; w.w_gu_scales = stats_ + 1; w.w_down = w_down_; w.w_down_scales = stats_ + 3;
+        return w;
+    }
+    // x bf16 [m x hidden] -> y bf16 [m x hidden]: this rank's partial, or the sum over the ranks when `reduce` is set and a
+    // communicator exists.  Asynchronous on the library handle's stream; the workspace is kept and grows with m.
+    void forward_device(const void* x_bf16_dev, size_t m, void* y_bf16_dev, bool reduce) {
+        size_t need = 0;
+        check(oxq_mlp_swiglu_tp_workspace_bytes(OXQ_TP_FP8, (int64_t)m, (int64_t)hidden, (int64_t)inter_local, &need));
+        if (need > ws_bytes_) {
+            detail::cuda(cudaDeviceSynchronize());
+            if (ws_) cudaFree(ws_);
+            ws_ = nullptr; ws_bytes_ = 0;
+            detail::cuda(cudaMalloc(&ws_, need));
+            ws_bytes_ = need;
+        }
+        const oxq_tp_mlp_weights w = weights();
+        check(oxq_mlp_swiglu_tp(h_, &w, (int64_t)m, x_bf16_dev, y_bf16_dev, ws_, ws_bytes_, reduce ? 1 : 0));
+    }
+    // host slices: x f32 [batch x hidden] (rounded to bf16) -> f32 [batch x hidden]
+    std::vector<float> forward_partial(const std::vector<float>& x, size_t batch) { return forward_host(x, batch, false); }
+    std::vector<float> forward(const std::vector<float>& x, size_t batch) { return forward_host(x, batch, true); }
+private:
+    void check(int32_t rc) const { if (rc) throw DistInferError(oxq_status_name(rc), oxq_last_error_string(h_)); }
+    void release() {
+        if (w_gu_) cudaFree(w_gu_);
+        if (w_down_) cudaFree(w_down_);
+        if (stats_) cudaFree(stats_);
+        if (ws_) cudaFree(ws_);
+        if (h_) oxq_handle_destroy(h_);
+        w_gu_ = w_down_ = ws_ = nullptr; stats_ = nullptr; h_ = nullptr;
+    }
+    std::vector<float> forward_host(const std::vector<float>& x, size_t batch, bool reduce) {
+        if (x.size() != batch * hidden)
+            throw DistInferError("DimensionMismatch", "expected " + std::to_string(batch * hidden) + ", got " + std::to_string(x.size()), batch * hidden, x.size());
+        if (batch == 0) return {};
+        std::vector<uint16_t> xb(x.size()), yb(x.size());
+        for (size_t i = 0; i < x.size(); i++) xb[i] = detail::f32_to_bf16(x[i]);
+        void *xd = nullptr, *yd = nullptr;
+        detail::cuda(cudaMalloc(&xd, xb.size() * 2));
+        if (cudaMalloc(&yd, yb.size() * 2) != cudaSuccess) { cudaFree(xd); throw DistInferError("Cuda", "cudaMalloc"); }
+        try {
+            detail::cuda(cudaMemcpy(xd, xb.data(), xb.size() * 2, cudaMemcpyHostToDevice));
+            forward_device(xd, batch, yd, reduce);
+            detail::cuda(cudaDeviceSynchronize());
+            detail::cuda(cudaMemcpy(yb.data(), yd, yb.size() * 2, cudaMemcpyDeviceToHost));
+        } catch (...) { cudaFree(xd); cudaFree(yd); throw; }
+        cudaFree(xd); cudaFree(yd);
+        std::vector<float> out(x.size());
+        for (size_t i = 0; i < out.size(); i++) out[i] = detail::bf16_to_f32(yb[i]);
+        return out;
+    }
+    oxq_handle* h_ = nullptr;
+    void *w_gu_ = nullptr, *w_down_ = nullptr, *ws_ = nullptr;
+    float* stats_ = nullptr;
+    size_t ws_bytes_ = 0;
 };
 
 }  // namespace oxicuda_dist_infer

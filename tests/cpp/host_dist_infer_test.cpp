@@ -2,7 +2,9 @@
 //   host_dist_infer_test host        the reference's handle / coordinate / error tests: no device needed
 //   host_dist_infer_test <out.bin>   the reference's layer tests on the GPU (every rank's shard built in this process, as
 //                                    the reference's own tests do), then a 256 -> 512 -> 256 column / row pair at tp = 4 whose
-//                                    results are written to the file for the Python side to compare with the oracle
+//                                    results are written to the file for the Python side to compare with the oracle, then
+//                                    the FP8 tensor-parallel SwiGLU MLP at tp = 2 (fused entry against its four steps, h and
+//                                    the partials into the same file)
 // Exit code 0 on success, else the number of the failed check.
 #include <cstdio>
 #include <cstring>
@@ -116,6 +118,56 @@ static int device_checks(const char* out_path) {
     FILE* f = fopen(out_path, "wb");
     if (!f) return 9;
     for (const V* v : {&x, &w1, &b1, &w2, &b2, &h, &y}) fwrite(v->data(), sizeof(float), v->size(), f);
+    // TpSwiGluMlp (FP8) at tp = 2, both ranks' shards in this process: hidden 512, intermediate 2048, five tokens.  Each rank's
+    // partial from the fused entry must equal, bit for bit, the same four steps issued one by one (which also yields h for the
+    // oracle); the file gets x (as bf16 values), the weights, and per rank h and the partial.
+    {
+        const size_t hid = 512, inter = 2048, m = 5, mtp = 2, il = inter / mtp;
+        const V wg = pattern(inter * hid, 21, 0.08f), wu = pattern(inter * hid, 23, 0.08f), wd = pattern(hid * inter, 29, 0.08f);
+        V xs = pattern(m * hid, 31, 1.0f);
+        std::vector<uint16_t> xb(xs.size());
+        for (size_t i = 0; i < xs.size(); i++) { xb[i] = detail::f32_to_bf16(xs[i]); xs[i] = detail::bf16_to_f32(xb[i]); }
+        int errs = 0;
+        try { TpSwiGluMlp(make_handle(3, 0), hid, inter, wg, wu, wd); } catch (const DistInferError& e) { errs += e.variant == "TpFeaturesMisaligned"; }
+        try { TpSwiGluMlp(make_handle(2, 0), hid, inter, wg, V(7, 0.0f), wd); } catch (const DistInferError& e) { errs += e.variant == "DimensionMismatch"; }
+        try { TpSwiGluMlp(make_handle(32, 0), hid, inter, wg, wu, wd); } catch (const DistInferError& e) { errs += e.variant == "ShardShapeMismatch"; }
+        if (errs != 3) { fclose(f); return 14; }
+        fwrite(xs.data(), sizeof(float), xs.size(), f);
+        for (const V* v : {&wg, &wu, &wd}) fwrite(v->data(), sizeof(float), v->size(), f);
+        std::vector<V> partials;
+        for (size_t r = 0; r < mtp; r++) {
+            TpSwiGluMlp mlp(make_handle(mtp, r), hid, inter, wg, wu, wd);
+            const V part = mlp.forward_partial(xs, m);
+            if (mlp.forward(xs, m) != part) { fclose(f); return 15; }        // no communicator: a world of one, the sum is the partial
+            // the same steps one by one on the layer's own handle and weights
+            oxq_handle* lh = mlp.library_handle();
+            const oxq_tp_mlp_weights w = mlp.weights();
+            void *xd, *xq, *hb, *hq, *yd; float* st;
+            detail::cuda(cudaMalloc(&xd, m * hid * 2)); detail::cuda(cudaMalloc(&xq, m * hid)); detail::cuda(cudaMalloc(&hb, m * il * 2));
+            detail::cuda(cudaMalloc(&hq, m * il)); detail::cuda(cudaMalloc(&yd, m * hid * 2)); detail::cuda(cudaMalloc((void**)&st, 4 * sizeof(float)));
+            detail::cuda(cudaMemcpy(xd, xb.data(), xb.size() * 2, cudaMemcpyHostToDevice));
+            int32_t rc = oxq_fp8_quant_dynamic(lh, xd, OXQ_BF16, (int64_t)(m * hid), (uint8_t*)xq, st);
+            if (!rc) rc = oxq_gemm_fp8_swiglu(lh, (int64_t)m, (int64_t)(2 * il), (int64_t)hid, (const uint8_t*)xq, (int64_t)hid, (const uint8_t*)w.w_gu, (int64_t)hid, st + 1,
+                                              (const float*)w.w_gu_scales, hb, (int64_t)il);
+            if (!rc) rc = oxq_fp8_quant_dynamic(lh, hb, OXQ_BF16, (int64_t)(m * il), (uint8_t*)hq, st + 2);
+            if (!rc) rc = oxq_gemm_fp8(lh, (int64_t)m, (int64_t)hid, (int64_t)il, (const uint8_t*)hq, (int64_t)il, (const uint8_t*)w.w_down, (int64_t)il, st + 3,
+                                       (const float*)w.w_down_scales, yd, (int64_t)hid);
+            if (rc) { fprintf(stderr, "staged step failed: %d %s\n", rc, oxq_last_error_string(lh)); fclose(f); return 16; }
+            detail::cuda(cudaDeviceSynchronize());
+            std::vector<uint16_t> hh(m * il), yy(m * hid);
+            detail::cuda(cudaMemcpy(hh.data(), hb, hh.size() * 2, cudaMemcpyDeviceToHost));
+            detail::cuda(cudaMemcpy(yy.data(), yd, yy.size() * 2, cudaMemcpyDeviceToHost));
+            cudaFree(xd); cudaFree(xq); cudaFree(hb); cudaFree(hq); cudaFree(yd); cudaFree(st);
+            for (size_t i = 0; i < yy.size(); i++) if (detail::bf16_to_f32(yy[i]) != part[i]) { fclose(f); return 17; }
+            V hf(hh.size());
+            for (size_t i = 0; i < hh.size(); i++) hf[i] = detail::bf16_to_f32(hh[i]);
+            fwrite(hf.data(), sizeof(float), hf.size(), f);
+            fwrite(part.data(), sizeof(float), part.size(), f);
+            partials.push_back(part);
+        }
+        const V ysum = RowLinear::all_reduce(partials);
+        fwrite(ysum.data(), sizeof(float), ysum.size(), f);
+    }
     fclose(f);
     return 0;
 }

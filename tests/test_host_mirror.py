@@ -129,7 +129,7 @@ def test_host_dist_infer_mirror_runs_and_matches_oracle(tmp_path, orc):
     raw = np.fromfile(out, dtype=np.float32)
     tp, in_f, mid, batch = 4, 256, 512, 5
     sizes = [batch * in_f, mid * in_f, mid, in_f * mid, in_f, batch * mid, batch * in_f]
-    assert raw.size == sum(sizes)
+    raw, mlp_raw = raw[:sum(sizes)], raw[sum(sizes):]
     x, w1, b1, w2, b2, h, y = np.split(raw, np.cumsum(sizes)[:-1])
     rb = lambda a: orc.bf16_bits_to_f32(orc.f32_to_bf16_bits(a))  # noqa: E731
     x, w1, w2 = rb(x).reshape(batch, in_f), rb(w1).reshape(mid, in_f), rb(w2).reshape(in_f, mid)
@@ -139,6 +139,25 @@ def test_host_dist_infer_mirror_runs_and_matches_oracle(tmp_path, orc):
     # the row layer continues from the gathered h the driver produced: tp partial sums, each rounded to bf16
     y_ref = orc.ref_linear_f32(rb(h), w2, b2)
     assert np.abs(y.reshape(batch, in_f) - y_ref).max() <= 2.0 ** -6 * np.abs(y_ref).max()
+    # TpSwiGluMlp (FP8), tp = 2: inside the driver the fused entry equals its four steps bit for bit; here h and the summed
+    # partials against the oracle at the tensor-parallel bar of 1e-2 (the oracle's down projection continues from the device's h)
+    hid, inter, m, mtp = 512, 2048, 5, 2
+    il = inter // mtp
+    sizes = [m * hid, inter * hid, inter * hid, hid * inter] + [m * il, m * hid] * mtp + [m * hid]
+    assert mlp_raw.size == sum(sizes)
+    parts = np.split(mlp_raw, np.cumsum(sizes)[:-1])
+    xs, wg, wu, wd = parts[0].reshape(m, hid), parts[1].reshape(inter, hid), parts[2].reshape(inter, hid), parts[3].reshape(hid, inter)
+    h_dev = [parts[4 + 2 * r].reshape(m, il) for r in range(mtp)]
+    partials = [parts[5 + 2 * r].reshape(m, hid) for r in range(mtp)]
+    ysum = parts[-1].reshape(m, hid)
+    assert np.array_equal(ysum, partials[0] + partials[1])
+    y_bits, own_h = orc.spec_tp_mlp(orc.f32_to_bf16_bits(xs), wg, wu, wd, mtp, variant="fp8",
+                                    h_bits_per_rank=[orc.f32_to_bf16_bits(v) for v in h_dev], return_h=True)
+    for r in range(mtp):
+        h_ref = orc.bf16_bits_to_f32(own_h[r]).reshape(m, il)
+        assert np.abs(h_dev[r] - h_ref).max() <= 1e-2 * np.abs(h_ref).max()
+    y_ref = orc.bf16_bits_to_f32(y_bits).reshape(m, hid)
+    assert np.abs(ysum - y_ref).max() <= 1e-2 * np.abs(y_ref).max()
 
 
 @pytest.mark.gpu

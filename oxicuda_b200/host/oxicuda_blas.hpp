@@ -251,5 +251,17 @@ inline void gemm_nvfp4(const BlasHandle& h, const Fp4GemmConfig& cfg, const uint
     cfg.validate();
     h.check(oxq_gemm_nvfp4(h.raw(), cfg.m, cfg.n, cfg.k, x, sfx_mma, gx, w, sfw_mma, gw, y_bf16, cfg.n));
 }
+// MXFP8 operands (E4M3 codes, one E8M0 scale per 32 elements along K) as produced by oxq_mxfp8_quant; the micro-scaling
+// configuration is the one the format fixes (block 32, E8M0 scales)
+inline void gemm_mxfp8(const BlasHandle& h, uint32_t m, uint32_t n, uint32_t k, const uint8_t* x, const uint8_t* sfx_mma, const uint8_t* w, const uint8_t* sfw_mma,
+                       void* y_bf16) {
+    if (m == 0 || n == 0 || k == 0) throw BlasError(OXQ_ERR_INVALID_DIMENSION, "MXFP8 GEMM dimensions must be non-zero");
+    h.check(oxq_gemm_mxfp8(h.raw(), m, n, k, x, sfx_mma, w, sfw_mma, y_bf16, n));
+}
+// W8A32 decode GEMM (Int8GemmConfig with f32 activations): Y_f32 = X_f32 . (W_i8 * sw_rows)^T
+inline void gemm_w8a32(const BlasHandle& h, const Int8GemmConfig& cfg, const float* x, const int8_t* w, const float* sw_rows, float* y_f32) {
+    cfg.validate(SmVersion::Sm100);
+    h.check(oxq_gemm_w8a32(h.raw(), cfg.m, cfg.n, cfg.k, x, w, sw_rows, y_f32));
+}
 
 }  // namespace oxicuda_blas

@@ -3,6 +3,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <stdexcept>
 #include <vector>
 #include "../../oxicuda_b200/host/oxicuda_blas.hpp"
 #include "../../oxicuda_b200/host/oxicuda_quant.hpp"
@@ -156,6 +157,89 @@ int main(int argc, char** argv) {
             MicroScalingConfig bad; bad.block_size = 16;
             try { MicroScalingQuantizer(bad).quantize_fp4(v, Fp4Format::E2M1); } catch (const BlasError& e) { merr += e.variant == "InvalidArgument"; }
             if (merr != 1) return 34;
+        }
+        // blas mirror: the block-scaled and W8A32 GEMM wrappers against host products of the dequantised operands
+        {
+            using namespace oxicuda_blas;
+            auto pattern = [](size_t n, uint32_t salt, float amp) {
+                std::vector<float> v(n);
+                for (size_t i = 0; i < n; i++) v[i] = amp * (float)((int)((((uint32_t)i + salt) * 2654435761u) >> 20 & 1023) - 512) / 512.0f;
+                return v;
+            };
+            struct Dev {
+                void* p = nullptr;
+                explicit Dev(size_t bytes) { if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess) throw std::runtime_error("cudaMalloc"); }
+                ~Dev() { cudaFree(p); }
+                Dev(const Dev&) = delete; Dev& operator=(const Dev&) = delete;
+            };
+            auto bf16_to_f32 = [](uint16_t b) { uint32_t u = (uint32_t)b << 16; float f; memcpy(&f, &u, 4); return f; };
+            // |y - ref| <= tol * max |ref| over [m x n]; ref accumulated in double from the dequantised operands
+            auto close = [&](const std::vector<float>& y, const std::vector<float>& a, const std::vector<float>& b, size_t m, size_t n, size_t k, double tol) {
+                std::vector<double> ref(m * n);
+                double mx = 0.0;
+                for (size_t i = 0; i < m; i++)
+                    for (size_t j = 0; j < n; j++) {
+                        double acc = 0.0;
+                        for (size_t c = 0; c < k; c++) acc += (double)a[i * k + c] * (double)b[j * k + c];
+                        ref[i * n + j] = acc; mx = std::fmax(mx, std::fabs(acc));
+                    }
+                for (size_t i = 0; i < m * n; i++) if (!(std::fabs((double)y[i] - ref[i]) <= tol * mx)) return false;
+                return mx > 0.0;
+            };
+            const size_t shapes[2][3] = {{128, 384, 256}, {3, 200, 512}};         // a prefill tile and a decode shape
+            for (const auto& sh : shapes) {
+                const size_t m = sh[0], n = sh[1], k = sh[2];
+                const std::vector<float> xa = pattern(m * k, 41, 1.0f), wb = pattern(n * k, 43, 1.0f);
+                Dev xd(m * k * 4), wd(n * k * 4), yd(m * n * 2), xdq(m * k * 4), wdq(n * k * 4);
+                cudaMemcpy(xd.p, xa.data(), m * k * 4, cudaMemcpyHostToDevice);
+                cudaMemcpy(wd.p, wb.data(), n * k * 4, cudaMemcpyHostToDevice);
+                std::vector<float> xq(m * k), wq(n * k), y(m * n);
+                std::vector<uint16_t> yb(m * n);
+                {   // MXFP8: E4M3 codes, E8M0 scale per 32
+                    Dev xc(m * k), wc(n * k), xs(m * k / 32), ws(n * k / 32), xsm(oxq_sf_mma_bytes((int64_t)m, (int64_t)(k / 32))), wsm(oxq_sf_mma_bytes((int64_t)n, (int64_t)(k / 32)));
+                    bh.check(oxq_mxfp8_quant(bh.raw(), xd.p, OXQ_F32, (int64_t)m, (int64_t)k, (uint8_t*)xc.p, (uint8_t*)xs.p, (uint8_t*)xsm.p));
+                    bh.check(oxq_mxfp8_quant(bh.raw(), wd.p, OXQ_F32, (int64_t)n, (int64_t)k, (uint8_t*)wc.p, (uint8_t*)ws.p, (uint8_t*)wsm.p));
+                    gemm_mxfp8(bh, (uint32_t)m, (uint32_t)n, (uint32_t)k, (const uint8_t*)xc.p, (const uint8_t*)xsm.p, (const uint8_t*)wc.p, (const uint8_t*)wsm.p, yd.p);
+                    bh.check(oxq_mxfp8_dequant(bh.raw(), (const uint8_t*)xc.p, (const uint8_t*)xs.p, (int64_t)m, (int64_t)k, xdq.p, OXQ_F32));
+                    bh.check(oxq_mxfp8_dequant(bh.raw(), (const uint8_t*)wc.p, (const uint8_t*)ws.p, (int64_t)n, (int64_t)k, wdq.p, OXQ_F32));
+                    if (cudaDeviceSynchronize() != cudaSuccess) return 35;
+                    cudaMemcpy(xq.data(), xdq.p, m * k * 4, cudaMemcpyDeviceToHost); cudaMemcpy(wq.data(), wdq.p, n * k * 4, cudaMemcpyDeviceToHost);
+                    cudaMemcpy(yb.data(), yd.p, m * n * 2, cudaMemcpyDeviceToHost);
+                    for (size_t i = 0; i < m * n; i++) y[i] = bf16_to_f32(yb[i]);
+                    if (!close(y, xq, wq, m, n, k, 1.0 / 128.0)) return 36;
+                }
+                {   // NVFP4: E2M1 codes, UE4M3 scale per 16, f32 tensor scale
+                    Fp4GemmConfig cfg{(uint32_t)m, (uint32_t)n, (uint32_t)k};
+                    Dev xc(m * k / 2), wc(n * k / 2), xs(m * k / 16), ws(n * k / 16), xsm(oxq_sf_mma_bytes((int64_t)m, (int64_t)(k / 16))), wsm(oxq_sf_mma_bytes((int64_t)n, (int64_t)(k / 16))), stx(8), stw(8);
+                    bh.check(oxq_absmax(bh.raw(), xd.p, OXQ_F32, (int64_t)(m * k), (float*)stx.p));
+                    bh.check(oxq_absmax(bh.raw(), wd.p, OXQ_F32, (int64_t)(n * k), (float*)stw.p));
+                    bh.check(oxq_nvfp4_quant(bh.raw(), xd.p, OXQ_F32, (int64_t)m, (int64_t)k, (float*)stx.p, (uint8_t*)xc.p, (uint8_t*)xs.p, (uint8_t*)xsm.p));
+                    bh.check(oxq_nvfp4_quant(bh.raw(), wd.p, OXQ_F32, (int64_t)n, (int64_t)k, (float*)stw.p, (uint8_t*)wc.p, (uint8_t*)ws.p, (uint8_t*)wsm.p));
+                    gemm_nvfp4(bh, cfg, (const uint8_t*)xc.p, (const uint8_t*)xsm.p, (const float*)stx.p + 1, (const uint8_t*)wc.p, (const uint8_t*)wsm.p, (const float*)stw.p + 1, yd.p);
+                    bh.check(oxq_nvfp4_dequant(bh.raw(), (const uint8_t*)xc.p, (const uint8_t*)xs.p, (const float*)stx.p, (int64_t)m, (int64_t)k, xdq.p, OXQ_F32));
+                    bh.check(oxq_nvfp4_dequant(bh.raw(), (const uint8_t*)wc.p, (const uint8_t*)ws.p, (const float*)stw.p, (int64_t)n, (int64_t)k, wdq.p, OXQ_F32));
+                    if (cudaDeviceSynchronize() != cudaSuccess) return 37;
+                    cudaMemcpy(xq.data(), xdq.p, m * k * 4, cudaMemcpyDeviceToHost); cudaMemcpy(wq.data(), wdq.p, n * k * 4, cudaMemcpyDeviceToHost);
+                    cudaMemcpy(yb.data(), yd.p, m * n * 2, cudaMemcpyDeviceToHost);
+                    for (size_t i = 0; i < m * n; i++) y[i] = bf16_to_f32(yb[i]);
+                    if (!close(y, xq, wq, m, n, k, 1.0 / 128.0)) return 38;
+                }
+            }
+            {   // W8A32 (benchmark configuration 1): per-row INT8 weights, f32 activations and result
+                const size_t m = 13, n = 100, k = 1040;
+                Int8GemmConfig cfg{(uint32_t)m, (uint32_t)n, (uint32_t)k};
+                const std::vector<float> xa = pattern(m * k, 47, 1.0f), wb = pattern(n * k, 53, 0.05f);
+                Dev xd(m * k * 4), wd(n * k * 4), wq8(n * k), sw(n * 4), yd(m * n * 4), wdq(n * k * 4);
+                cudaMemcpy(xd.p, xa.data(), m * k * 4, cudaMemcpyHostToDevice);
+                cudaMemcpy(wd.p, wb.data(), n * k * 4, cudaMemcpyHostToDevice);
+                bh.check(oxq_int8_quant_rows(bh.raw(), (const float*)wd.p, (int64_t)n, (int64_t)k, (int8_t*)wq8.p, (float*)sw.p, OXQ_ROUND_HALF_EVEN));
+                gemm_w8a32(bh, cfg, (const float*)xd.p, (const int8_t*)wq8.p, (const float*)sw.p, (float*)yd.p);
+                bh.check(oxq_int8_dequant_rows(bh.raw(), (const int8_t*)wq8.p, (const float*)sw.p, (int64_t)n, (int64_t)k, (float*)wdq.p));
+                if (cudaDeviceSynchronize() != cudaSuccess) return 39;
+                std::vector<float> wq(n * k), y(m * n);
+                cudaMemcpy(wq.data(), wdq.p, n * k * 4, cudaMemcpyDeviceToHost); cudaMemcpy(y.data(), yd.p, m * n * 4, cudaMemcpyDeviceToHost);
+                if (!close(y, xa, wq, m, n, k, 1e-4)) return 40;
+            }
         }
         FILE* f = fopen(argv[1], "wb");
         if (!f) return 9;

@@ -30,6 +30,29 @@ def test_header_symbols_all_exported(lib):
     assert sorted(_ffi.SIGNATURES) == declared          # the ctypes table covers the whole header
 
 
+def test_every_entry_cites_the_reference_interface_it_replaces():
+    """Each section of the header opens with a comment that names the reference source (a .rs path with line numbers) its
+    entries stand behind; the handle utilities (version, status words, error strings) are the library's own."""
+    text = open(os.path.join(ROOT, "include", "oxq.h")).read()
+    own = {"oxq_version", "oxq_status_name", "oxq_last_error_string", "oxq_device_status"}
+    section_cites, seen = False, 0
+    for m in re.finditer(r"/\*.*?\*/|OXQ_API[^;]*;", text, re.S):
+        tok = m.group(0)
+        if tok.startswith("/*"):
+            if tok.startswith("/* ----"):
+                section_cites = False                     # a new section has to cite again
+            if re.search(r"\w+\.rs:\d+", tok):
+                section_cites = True
+            continue
+        decl = re.search(r"\b(oxq_\w+)\s*\(", tok)
+        if decl is None:                                  # the macro's own definition
+            continue
+        name = decl.group(1)
+        seen += 1
+        assert section_cites or name in own, f"{name}: no reference file:line in its comment or its section's"
+    assert seen == len(_declared_symbols())
+
+
 def test_status_names(lib):
     assert lib.oxq_status_name(0) == b"Ok"
     assert lib.oxq_status_name(1) == b"EmptyInput"

@@ -90,19 +90,27 @@ struct DeviceShard {
         cuda(cudaSetDevice(device));
         const int32_t rc = oxq_handle_create(device, nullptr, &h);
         if (rc) throw DistInferError(oxq_status_name(rc), "oxq_handle_create");
-        std::vector<uint16_t> wb(n_pad * k_pad, 0);
-        for (size_t r = 0; r < n; r++)
-            for (size_t c = 0; c < k; c++) wb[r * k_pad + c] = f32_to_bf16(weight[r * src_ld + c]);
-        cuda(cudaMalloc(&w, wb.size() * 2));
-        cuda(cudaMemcpy(w, wb.data(), wb.size() * 2, cudaMemcpyHostToDevice));
-        if (bias_or_null) {
-            std::vector<float> bb(n_pad, 0.0f);
-            for (size_t i = 0; i < n; i++) bb[i] = bias_or_null[i];
-            cuda(cudaMalloc((void**)&bias, n_pad * sizeof(float)));
-            cuda(cudaMemcpy(bias, bb.data(), n_pad * sizeof(float), cudaMemcpyHostToDevice));
-        }
+        try {
+            std::vector<uint16_t> wb(n_pad * k_pad, 0);
+            for (size_t r = 0; r < n; r++)
+                for (size_t c = 0; c < k; c++) wb[r * k_pad + c] = f32_to_bf16(weight[r * src_ld + c]);
+            cuda(cudaMalloc(&w, wb.size() * 2));
+            cuda(cudaMemcpy(w, wb.data(), wb.size() * 2, cudaMemcpyHostToDevice));
+            if (bias_or_null) {
+                std::vector<float> bb(n_pad, 0.0f);
+                for (size_t i = 0; i < n; i++) bb[i] = bias_or_null[i];
+                cuda(cudaMalloc((void**)&bias, n_pad * sizeof(float)));
+                cuda(cudaMemcpy(bias, bb.data(), n_pad * sizeof(float), cudaMemcpyHostToDevice));
+            }
+        } catch (...) { release(); throw; }                               // a constructor that throws runs no destructor
     }
-    ~DeviceShard() { if (w) cudaFree(w); if (bias) cudaFree(bias); if (h) oxq_handle_destroy(h); }
+    ~DeviceShard() { release(); }
+    void release() {
+        if (w) cudaFree(w);
+        if (bias) cudaFree(bias);
+        if (h) oxq_handle_destroy(h);
+        w = nullptr; bias = nullptr; h = nullptr;
+    }
     DeviceShard(const DeviceShard&) = delete; DeviceShard& operator=(const DeviceShard&) = delete;
     void check(int32_t rc) const { if (rc) throw DistInferError(oxq_status_name(rc), oxq_last_error_string(h)); }
     // y[batch x n_pad] (bf16, ld = n_pad) = x[batch x k_pad] (bf16, ld = k_pad) . W^T (+ bias); asynchronous on the handle's stream

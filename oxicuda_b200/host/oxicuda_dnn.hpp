@@ -58,7 +58,7 @@ public:
     size_t len() const { return n_; }
     bool is_empty() const { return n_ == 0; }
     T* as_device_ptr() const { return p_; }
-    std::vector<T> to_vec() const {                                      // synchronous copy back (copy_to_host)
+    std::vector<T> to_vec() const {                                      // copy back on the default stream: synchronise a non-blocking stream first
         std::vector<T> out(n_);
         if (n_) detail::cuda(cudaMemcpy(out.data(), p_, n_ * sizeof(T), cudaMemcpyDeviceToHost));
         return out;

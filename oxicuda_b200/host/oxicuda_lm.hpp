@@ -82,19 +82,21 @@ public:
         detail::cuda(cudaSetDevice(device));
         const int32_t rc = oxq_handle_create(device, nullptr, &h_);
         if (rc) throw LmError(oxq_status_name(rc), "oxq_handle_create");
-        w_gu_.reset(new detail::DevMem(2 * inter_pad * hidden_pad * 2));
-        w_down_.reset(new detail::DevMem(out_pad * inter_pad * 2));
-        std::vector<uint16_t> gu(2 * inter_pad * hidden_pad, 0), dn(out_pad * inter_pad, 0);
-        for (size_t r = 0; r < inter; r++) {
-            const size_t blk = r / 128, in_blk = r % 128;
-            uint16_t* g = &gu[((2 * blk) * 128 + in_blk) * hidden_pad];
-            uint16_t* u = &gu[((2 * blk + 1) * 128 + in_blk) * hidden_pad];
-            for (size_t c = 0; c < hidden; c++) { g[c] = detail::f32_to_bf16(w_gate[r * hidden + c]); u[c] = detail::f32_to_bf16(w_up[r * hidden + c]); }
-        }
-        for (size_t r = 0; r < hidden; r++)
-            for (size_t c = 0; c < inter; c++) dn[r * inter_pad + c] = detail::f32_to_bf16(w_down[r * inter + c]);
-        detail::cuda(cudaMemcpy(w_gu_->p, gu.data(), gu.size() * 2, cudaMemcpyHostToDevice));
-        detail::cuda(cudaMemcpy(w_down_->p, dn.data(), dn.size() * 2, cudaMemcpyHostToDevice));
+        try {
+            w_gu_.reset(new detail::DevMem(2 * inter_pad * hidden_pad * 2));
+            w_down_.reset(new detail::DevMem(out_pad * inter_pad * 2));
+            std::vector<uint16_t> gu(2 * inter_pad * hidden_pad, 0), dn(out_pad * inter_pad, 0);
+            for (size_t r = 0; r < inter; r++) {
+                const size_t blk = r / 128, in_blk = r % 128;
+                uint16_t* g = &gu[((2 * blk) * 128 + in_blk) * hidden_pad];
+                uint16_t* u = &gu[((2 * blk + 1) * 128 + in_blk) * hidden_pad];
+                for (size_t c = 0; c < hidden; c++) { g[c] = detail::f32_to_bf16(w_gate[r * hidden + c]); u[c] = detail::f32_to_bf16(w_up[r * hidden + c]); }
+            }
+            for (size_t r = 0; r < hidden; r++)
+                for (size_t c = 0; c < inter; c++) dn[r * inter_pad + c] = detail::f32_to_bf16(w_down[r * inter + c]);
+            detail::cuda(cudaMemcpy(w_gu_->p, gu.data(), gu.size() * 2, cudaMemcpyHostToDevice));
+            detail::cuda(cudaMemcpy(w_down_->p, dn.data(), dn.size() * 2, cudaMemcpyHostToDevice));
+        } catch (...) { oxq_handle_destroy(h_); h_ = nullptr; throw; }    // a constructor that throws runs no destructor
     }
     ~DeviceSwiGluFfn() { if (h_) oxq_handle_destroy(h_); }
     DeviceSwiGluFfn(const DeviceSwiGluFfn&) = delete; DeviceSwiGluFfn& operator=(const DeviceSwiGluFfn&) = delete;

@@ -284,6 +284,17 @@ OXQ_API int32_t oxq_dnn_int4_dequant(oxq_handle* h, const uint8_t* packed_dev, c
  * out = clamp(int(rint(clamp(x / scale, -6, 6))) + 6, 0, 255) as one byte per element. */
 OXQ_API int32_t oxq_dnn_block_scaled_quant(oxq_handle* h, const void* x_dev, int dtype, int64_t n, int64_t block_size, uint8_t* out_dev,
                                    float* scales_dev);
+/* The fused dequantise + GEMV of the DNN layer's weight-only plan (dnn_fused_dequant_gemv_f32 of
+ * WeightQuantPlan::generate_fused_dequant_gemv_ptx, crates/oxicuda-dnn/src/quantize/gptq_awq.rs:867-994):
+ *   y[row] = sum over col of (code[row, col] * scale[row, col / group_size]) * x[col],   f32 throughout,
+ * codes unsigned, `bits` wide, packed LSB-first in u32 words (element `sub` of a word at bit sub * bits, :936-945),
+ * packed_w_dev [rows x cols * bits / 32] words, scales_dev [rows x cols / group_size] f32, no zero-point (the reference's
+ * kernel takes a zero pointer and does not read it).  One pass over the packed weight.  The reference adds the products
+ * of a row one after the other; here they are summed by lanes and shuffles, so results agree to f32 summation error.
+ * bits in {2, 4, 8}; cols a multiple of four packed words (128 / bits columns) and of group_size; group_size a multiple of
+ * 32 / bits; packed_w_dev and x_dev 16-byte aligned. */
+OXQ_API int32_t oxq_dnn_fused_dequant_gemv(oxq_handle* h, const uint32_t* packed_w_dev, const float* scales_dev, const float* x_dev, float* y_dev,
+                                   int64_t rows, int64_t cols, int64_t group_size, int bits);
 /* Nf4Quantizer::encode / decode (crates/oxicuda-quant/src/scheme/nf4.rs:93-155): per block absmax (floored at
  * 1e-8), x / absmax clamped to [-1, 1], nearest of the 16 NormalFloat4 levels (the lower index on a tie), two
  * codes per byte with the even element in the low nibble.  packed_dev holds n / 2 bytes, absmax_dev n / block

@@ -336,6 +336,16 @@ def ref_dnn_int4_dequant(packed, scales, n, group, symmetric=True):
     return out
 
 
+def ref_dnn_fused_dequant_gemv(packed_w, scales, x, rows, cols, group_size, bits=4):
+    """dnn_fused_dequant_gemv_f32 of the DNN crate (gptq_awq.rs:867-994): y[row] in the reference's sequential f32 order."""
+    packed_w = _c(packed_w, np.uint32).ravel()
+    scales = _c(scales, np.float32).ravel()
+    x = _c(x, np.float32).ravel()
+    y = np.zeros(rows, np.float32)
+    lib().orc_ref_dnn_fused_dequant_gemv(_p(packed_w), _p(scales), _p(x), _p(y), _sz(rows), _sz(cols), _sz(group_size), C.c_int(bits))
+    return y
+
+
 def ref_dnn_block_scaled_quant(x, block):
     """quantize_block_scaled of the DNN crate: (biased u8 codes, per-block f32 scales)."""
     x = _c(x, np.float32).ravel()

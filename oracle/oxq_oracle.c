@@ -345,6 +345,28 @@ void orc_unpack_uint4(const uint32_t* in, size_t words, uint8_t* out) {
         for (int j = 0; j < 8; j++) out[w * 8 + j] = (uint8_t)((in[w] >> (j * 4)) & 0x0F);
 }
 
+/* dnn_fused_dequant_gemv_f32 (crates/oxicuda-dnn/src/quantize/gptq_awq.rs:867-994): one sequential pass over a row,
+ * codes of `bits` bits packed LSB-first in u32 words (element `sub` of a word at bit sub * bits, :936-945), an f32 scale
+ * per group of group_size columns, no zero-point:
+ *   acc = fma(rn(float(code) * scale[row, col / group_size]), x[col], acc)     (cvt.rn.f32.u32, mul.rn.f32, fma.rn.f32) */
+void orc_ref_dnn_fused_dequant_gemv(const uint32_t* packed_w, const float* scales, const float* x, float* y, size_t rows, size_t cols,
+                                    size_t group_size, int bits) {
+    const size_t epu32 = (size_t)(32 / bits), packed_cols = cols / epu32, gpr = cols / group_size;
+    const uint32_t mask = (1u << bits) - 1u;
+    for (size_t row = 0; row < rows; row++) {
+        float acc = 0.0f;
+        for (size_t pw = 0; pw < packed_cols; pw++) {
+            const uint32_t word = packed_w[row * packed_cols + pw];
+            for (size_t sub = 0; sub < epu32; sub++) {
+                const size_t col = pw * epu32 + sub;
+                const float dq = (float)((word >> (sub * (size_t)bits)) & mask) * scales[row * gpr + col / group_size];
+                acc = fmaf(dq, x[col], acc);
+            }
+        }
+        y[row] = acc;
+    }
+}
+
 /* ------------------------------------------------------------------------- */
 /* A.4  E2M1 + micro-scaling (crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs) */
 /* ------------------------------------------------------------------------- */

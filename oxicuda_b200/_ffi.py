@@ -36,6 +36,7 @@ SIGNATURES = {
     "oxq_dnn_int4_quant": (_i32, [_vp, _vp, _i64, _i64, _int, _vp, _vp, _vp]),
     "oxq_dnn_int4_dequant": (_i32, [_vp, _vp, _vp, _i64, _i64, _int, _vp]),
     "oxq_dnn_block_scaled_quant": (_i32, [_vp, _vp, _int, _i64, _i64, _vp, _vp]),
+    "oxq_dnn_fused_dequant_gemv": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int]),
     "oxq_swiglu_interleaved": (_i32, [_vp, _vp, _i64, _i64, _vp]),
     "oxq_sf_mma_bytes": (_sz, [_i64, _i64]),
     "oxq_mxfp8_quant": (_i32, [_vp, _vp, _int, _i64, _i64, _vp, _vp, _vp]),

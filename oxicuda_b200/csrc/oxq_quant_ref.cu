@@ -9,6 +9,9 @@
 //   * quantize_to_int4 / dequantize_int4 of the DNN layer (crates/oxicuda-dnn/src/quantize/int4_quantize.rs:132-218,
 //     scale kernel :403-545, pack kernel :548-701, unpack :780-826);
 //   * quantize_block_scaled of the DNN layer (crates/oxicuda-dnn/src/quantize/block_scale.rs:53-140, kernels :145-345).
+//   * the fused dequantise + GEMV of the DNN layer's weight-only plan (crates/oxicuda-dnn/src/quantize/gptq_awq.rs:867-994):
+//     unsigned codes packed LSB-first in u32 words, f32 scales per group, f32 vector in and out (a stream over the
+//     packed weight; its sums are ordered for the GPU, so it is compared within a tolerance, not bit for bit).
 //
 // Every division is the IEEE one the reference performs (f32 `/`, div.rn.f32) and sums are never contracted into
 // FMAs, so codes, scales and zero-points are bit-exact against the CPU restatement of those lines.
@@ -253,6 +256,71 @@ __global__ void __launch_bounds__(256) dnn_block_quant_kernel(const T* __restric
     }
 }
 
+// ---- fused dequantise + GEMV: y[row] = sum_col (code[row, col] * scale[row, col / group]) * x[col] -------------------------
+// dnn_fused_dequant_gemv_f32 (gptq_awq.rs:867-994) gives one thread a whole row.  Here a warp takes FGV_ROWS consecutive rows
+// and walks them together: a lane loads 16 bytes of codes of each row per step (the warp 512 contiguous bytes per row) and
+// the matching 4 * 32 / BITS elements of x once for all its rows, so x comes from L1 once per FGV_ROWS rows of weights and the
+// packed weight is read from HBM exactly once.  Codes become floats by or-ing them into the mantissa of 2^23.  The per-word
+// sum is scaled once (a word never straddles a group: group % (32 / BITS) == 0), lanes are summed by shuffles.
+constexpr int FGV_ROWS = 4;
+constexpr int FGV_WARPS = 4;
+template <int BITS>
+__global__ void __launch_bounds__(FGV_WARPS * 32) fused_dequant_gemv_kernel(const uint32_t* __restrict__ w, const float* __restrict__ scales,
+                                                                            const float* __restrict__ x, float* __restrict__ y, int rows, int words,
+                                                                            int group_words, int gpr) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int EPW = 32 / BITS;                                    // elements per packed word
+    constexpr uint32_t MASK = (1u << BITS) - 1u;
+    const int lane = threadIdx.x & 31;
+    const int row0 = (blockIdx.x * FGV_WARPS + (threadIdx.x >> 5)) * FGV_ROWS;
+    if (row0 >= rows) return;
+    float acc[FGV_ROWS];
+    const uint32_t* wr[FGV_ROWS];
+    const float* sr[FGV_ROWS];
+#pragma unroll
+    for (int r = 0; r < FGV_ROWS; r++) {
+        const int row = min(row0 + r, rows - 1);                      // rows past the end repeat the last one and are not stored
+        acc[r] = 0.0f;
+        wr[r] = w + (size_t)row * words;
+        sr[r] = scales + (size_t)row * gpr;
+    }
+    for (int i = lane * 4; i < words; i += 128) {                     // words % 4 == 0: every lane's four words exist together
+        uint4 v[FGV_ROWS];
+#pragma unroll
+        for (int r = 0; r < FGV_ROWS; r++) v[r] = __ldcs(reinterpret_cast<const uint4*>(wr[r] + i));
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            float xv[EPW];
+            const float4* xp = reinterpret_cast<const float4*>(x + (size_t)(i + q) * EPW);
+#pragma unroll
+            for (int e = 0; e < EPW / 4; e++) {
+                const float4 t = __ldg(xp + e);
+                xv[4 * e] = t.x; xv[4 * e + 1] = t.y; xv[4 * e + 2] = t.z; xv[4 * e + 3] = t.w;
+            }
+            const int g = (i + q) / group_words;
+#pragma unroll
+            for (int r = 0; r < FGV_ROWS; r++) {
+                const uint32_t word = q == 0 ? v[r].x : q == 1 ? v[r].y : q == 2 ? v[r].z : v[r].w;
+                float part = 0.0f;
+#pragma unroll
+                for (int e = 0; e < EPW; e++) {
+                    const float c = __uint_as_float(((word >> (e * BITS)) & MASK) | 0x4B000000u) - 8388608.0f;
+                    part = fmaf(c, xv[e], part);
+                }
+                acc[r] = fmaf(part, __ldg(sr[r] + g), acc[r]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < FGV_ROWS; r++) {
+        float a = acc[r];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (lane == 0 && row0 + r < rows) y[row0 + r] = a;
+    }
+}
+
 static inline int grid_for(oxq_handle* h, int64_t threads_wanted, int ctas_per_sm) {
     int64_t need = (threads_wanted + 255) / 256;
     const int64_t cap = (int64_t)h->sm_count * ctas_per_sm;
@@ -362,6 +430,28 @@ int32_t oxq_dnn_block_scaled_quant(oxq_handle* h, const void* x, int dtype, int6
             break;
         default: OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "unknown dtype %d", dtype);
     }
+    return OXQ_OK;
+}
+
+int32_t oxq_dnn_fused_dequant_gemv(oxq_handle* h, const uint32_t* packed_w, const float* scales, const float* x, float* y, int64_t rows, int64_t cols,
+                                   int64_t group_size, int bits) {
+    OXQ_CHECK_HANDLE(h);
+    if (rows <= 0 || cols <= 0) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "fused dequant GEMV: rows and cols must be non-zero");
+    if (rows > INT32_MAX || cols > INT32_MAX) OXQ_FAIL(h, OXQ_ERR_INVALID_DIMENSION, "fused dequant GEMV: dimensions exceed 2^31-1");
+    if (!(bits == 2 || bits == 4 || bits == 8)) OXQ_FAIL(h, OXQ_ERR_UNSUPPORTED_OPERATION, "fused dequant GEMV covers 2, 4 and 8 bits, got %d", bits);
+    const int64_t epw = 32 / bits;
+    if (group_size <= 0 || cols % group_size != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "cols %lld is not divisible by group size %lld", (long long)cols, (long long)group_size);
+    if (group_size % epw != 0) OXQ_FAIL(h, OXQ_ERR_GROUP_SIZE_MISMATCH, "group size %lld is not a multiple of the %lld codes of a packed word", (long long)group_size, (long long)epw);
+    if (cols % (4 * epw) != 0) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "cols must be a multiple of %lld (four packed words)", (long long)(4 * epw));
+    if (!packed_w || !scales || !x || !y || ((uintptr_t)packed_w & 15u) || ((uintptr_t)x & 15u)) OXQ_FAIL(h, OXQ_ERR_INVALID_ARGUMENT, "null or misaligned pointer");
+    if (int32_t rc = oxq_require_sm100(h)) return rc;
+    const int words = (int)(cols / epw), group_words = (int)(group_size / epw), gpr = (int)(cols / group_size);
+    const unsigned grid = (unsigned)((rows + FGV_WARPS * FGV_ROWS - 1) / (FGV_WARPS * FGV_ROWS));
+    cudaError_t le;
+    if (bits == 4) le = oxq_launch(fused_dequant_gemv_kernel<4>, grid, FGV_WARPS * 32, 0, h->stream, packed_w, scales, x, y, (int)rows, words, group_words, gpr);
+    else if (bits == 8) le = oxq_launch(fused_dequant_gemv_kernel<8>, grid, FGV_WARPS * 32, 0, h->stream, packed_w, scales, x, y, (int)rows, words, group_words, gpr);
+    else le = oxq_launch(fused_dequant_gemv_kernel<2>, grid, FGV_WARPS * 32, 0, h->stream, packed_w, scales, x, y, (int)rows, words, group_words, gpr);
+    OXQ_CUDA(h, le);
     return OXQ_OK;
 }
 

@@ -285,6 +285,17 @@ def quantize_block_scaled(desc: TensorDesc, output: torch.Tensor, scales: torch.
     handle(x.device.index).call("oxq_dnn_block_scaled_quant", _p(x), _DT[x.dtype], n, block_size, _p(output), _p(scales))
 
 
+def fused_dequant_gemv(packed_w: torch.Tensor, scales: torch.Tensor, x: torch.Tensor, cols: int, group_size: int, bits: int = 4):
+    """dnn_fused_dequant_gemv_f32 (crates/oxicuda-dnn/src/quantize/gptq_awq.rs:867-994): y[row] = sum_col (code * scale) * x[col] with
+    unsigned codes packed LSB-first in u32 words [rows x cols * bits / 32], f32 scales [rows x cols / group_size], f32 x and y."""
+    _chk(x, torch.float32)
+    _chk(scales, torch.float32)
+    rows = packed_w.shape[0]
+    y = torch.empty(rows, dtype=torch.float32, device=x.device)
+    handle(x.device.index).call("oxq_dnn_fused_dequant_gemv", _p(packed_w), _p(scales), _p(x), _p(y), rows, cols, group_size, bits)
+    return y
+
+
 # ------------------------------------------------------------------------------------------- block scaled
 
 def sf_mma_bytes(rows: int, sf_cols: int) -> int:

@@ -47,6 +47,7 @@ def test_host_mirror_compiles_and_links(tmp_path):
     exe = _build(tmp_path)
     assert os.path.exists(exe)
     assert os.path.exists(_build(tmp_path, "host_dnn_test"))
+    assert os.path.exists(_build(tmp_path, "fused_gemv_test"))
 
 
 def test_host_dist_infer_types(tmp_path):
@@ -181,3 +182,31 @@ def test_host_lm_mirror_runs_and_matches_oracle(tmp_path, orc):
     assert np.isfinite(y).all() and np.abs(y - y_ref).max() <= 2.0 ** -5 * scale     # h and y each rounded to bf16
     h = rb(orc.ref_silu_mul(orc.ref_linear_f32(x, wg), orc.ref_linear_f32(x, wu)))
     assert np.abs(y - rb(orc.ref_linear_f32(h, wd))).max() <= 2.0 ** -6 * scale       # same roundings: what is left is summation order
+
+
+@pytest.mark.gpu
+def test_fused_dequant_gemv_c_abi_matches_oracle(tmp_path, orc):
+    """oxq_dnn_fused_dequant_gemv through the C ABI (tests/cpp/fused_gemv_test.cpp: argument errors, four shapes, 2 / 4 / 8 bits)
+    against the oracle's sequential restatement of dnn_fused_dequant_gemv_f32.  The device sums a row in another order, so
+    the bar is f32 summation error: 2e-6 of the sum of the products' magnitudes (measured: 1.5e-7)."""
+    exe = _build(tmp_path, "fused_gemv_test")
+    out = str(tmp_path / "gemv.bin")
+    res = subprocess.run([exe, out], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, f"rc={res.returncode} {res.stderr}"
+    raw = np.fromfile(out, dtype=np.uint8)
+    pos, seen = 0, []
+    while pos < raw.size:
+        rows, cols, group, bits = (int(v) for v in raw[pos:pos + 32].view(np.int64))
+        pos += 32
+        words, ngroups = rows * cols * bits // 32, rows * cols // group
+        w = raw[pos:pos + 4 * words].view(np.uint32); pos += 4 * words
+        s = raw[pos:pos + 4 * ngroups].view(np.float32); pos += 4 * ngroups
+        x = raw[pos:pos + 4 * cols].view(np.float32); pos += 4 * cols
+        y = raw[pos:pos + 4 * rows].view(np.float32); pos += 4 * rows
+        y_ref = orc.ref_dnn_fused_dequant_gemv(w, s, x, rows, cols, group, bits)
+        epw = 32 // bits
+        codes = ((w.reshape(rows, -1, 1) >> (np.arange(epw, dtype=np.uint32) * bits)) & ((1 << bits) - 1)).reshape(rows, cols).astype(np.float32)
+        mag = (codes * np.repeat(s.reshape(rows, -1), group, axis=1) * np.abs(x)[None, :]).sum(axis=1, dtype=np.float64)
+        assert np.isfinite(y).all() and np.all(np.abs(y.astype(np.float64) - y_ref) <= 2e-6 * mag + 1e-12), (rows, cols, group, bits)
+        seen.append((rows, cols, group, bits))
+    assert seen == [(100, 256, 64, 4), (14336, 4096, 128, 4), (67, 512, 128, 8), (33, 1024, 64, 2)]

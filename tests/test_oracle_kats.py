@@ -336,6 +336,20 @@ def test_swiglu_ffn_kats(orc):  # crates/oxicuda-lm/src/layer/ffn.rs:279-315, :3
     assert out.shape == (3, 4)                                                                       # three tokens at once
 
 
+def test_fused_dequant_gemv_definition(orc):  # crates/oxicuda-dnn/src/quantize/gptq_awq.rs:867-994 (the arithmetic its kernel states)
+    # 4 bits: element `sub` of a word at bit 4 * sub; one group of 8 with scale 0.5; x = 1 -> 0.5 * (0 + 1 + ... + 7)
+    y = orc.ref_dnn_fused_dequant_gemv(np.array([0x76543210], np.uint32), np.array([0.5], np.float32), np.ones(8, np.float32), 1, 8, 8, 4)
+    assert y.tolist() == [14.0]
+    # two rows, two groups of 8 per row, codes unsigned (0xF is 15, not -1), x picks single columns
+    w = np.array([0x0000000F, 0xF0000000, 0x00000001, 0x10000000], np.uint32)
+    s = np.array([2.0, 3.0, 0.25, 0.5], np.float32)
+    x = np.zeros(16, np.float32); x[0] = 1.0; x[15] = 10.0
+    assert orc.ref_dnn_fused_dequant_gemv(w, s, x, 2, 16, 8, 4).tolist() == [15 * 2.0 + 15 * 3.0 * 10.0, 0.25 + 0.5 * 10.0]
+    # 8 bits: four codes per word; 2 bits: sixteen
+    assert orc.ref_dnn_fused_dequant_gemv(np.array([0xFF000102], np.uint32), np.array([1.0], np.float32), np.array([1, 10, 100, 1000], np.float32), 1, 4, 4, 8).tolist() == [2 + 10 + 255000.0]
+    assert orc.ref_dnn_fused_dequant_gemv(np.array([0xE4E4E4E4], np.uint32), np.array([1.0], np.float32), np.ones(16, np.float32), 1, 16, 16, 2).tolist() == [24.0]
+
+
 def test_gptq_kats(orc):  # crates/oxicuda-quant/src/scheme/gptq.rs:341-520
     l = orc.ref_cholesky_lower(np.array([[4.0, 2.0], [2.0, 3.0]], np.float32))          # L = [[2, 0], [1, sqrt 2]]
     assert np.allclose(l, [[2.0, 0.0], [1.0, np.sqrt(2.0)]], atol=1e-6) and np.allclose(l @ l.T, [[4.0, 2.0], [2.0, 3.0]], atol=1e-5)

@@ -205,8 +205,11 @@ def test_fused_dequant_gemv_c_abi_matches_oracle(tmp_path, orc):
         y = raw[pos:pos + 4 * rows].view(np.float32); pos += 4 * rows
         y_ref = orc.ref_dnn_fused_dequant_gemv(w, s, x, rows, cols, group, bits)
         epw = 32 // bits
-        codes = ((w.reshape(rows, -1, 1) >> (np.arange(epw, dtype=np.uint32) * bits)) & ((1 << bits) - 1)).reshape(rows, cols).astype(np.float32)
-        mag = (codes * np.repeat(s.reshape(rows, -1), group, axis=1) * np.abs(x)[None, :]).sum(axis=1, dtype=np.float64)
+        mag = np.zeros(rows, np.float64)
+        for r0 in range(0, rows, 1024):                                  # in blocks of rows: the large case would need a gigabyte at once
+            wb = w.reshape(rows, -1)[r0:r0 + 1024]
+            codes = ((wb[:, :, None] >> (np.arange(epw, dtype=np.uint32) * bits)) & ((1 << bits) - 1)).reshape(wb.shape[0], cols).astype(np.float32)
+            mag[r0:r0 + 1024] = (codes * np.repeat(s.reshape(rows, -1)[r0:r0 + 1024], group, axis=1) * np.abs(x)[None, :]).sum(axis=1, dtype=np.float64)
         assert np.isfinite(y).all() and np.all(np.abs(y.astype(np.float64) - y_ref) <= 2e-6 * mag + 1e-12), (rows, cols, group, bits)
         seen.append((rows, cols, group, bits))
     assert seen == [(100, 256, 64, 4), (14336, 4096, 128, 4), (67, 512, 128, 8), (33, 1024, 64, 2)]

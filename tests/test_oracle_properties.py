@@ -106,6 +106,26 @@ def test_mxfp8_block_scale_rule(orc, x):
 
 
 @settings(**SETTINGS)
+@given(x=_matrix(2, 64))
+def test_nvfp4_error_is_within_half_the_widest_step(orc, x):
+    """NVFP4 (E2M1 codes, a UE4M3 scale per 16, one f32 tensor scale g): with s the decoded block scale times g, every element is
+    reconstructed within s (half of E2M1's widest step, 2), including the few at the top of a block that clip at 6 s when the
+    block scale rounded down; the scale itself is within E4M3's rounding (2^-4 relative) of max / 6."""
+    g = float(orc.spec_nvfp4_global_scale(float(np.abs(x).max())))
+    packed, sf = orc.spec_nvfp4_quant(x, g)
+    back = orc.spec_nvfp4_dequant(packed, sf, g, 2, 64)
+    s = np.repeat(orc.e4m3_to_f32(sf).astype(np.float64) * g, 16, axis=1)
+    # where the block scale is a subnormal E4M3 number its grid is uniform (step 2^-9): the scale may be short of max / 6 by half
+    # a step, down to zero for a block 2^-10 g and less in size, and the elements above 6 s clip
+    slack = np.where(np.repeat(orc.e4m3_to_f32(sf), 16, axis=1) >= 2.0 ** -6, 0.0, 6.0 * g * 2.0 ** -10)
+    assert np.all(np.abs(back - x) <= (s + slack) * (1 + 1e-6) + 1e-30)
+    assert np.all(np.abs(back) <= 6.0 * s * (1 + 1e-6))
+    blk = np.abs(x).reshape(2, 4, 16).max(axis=2).astype(np.float64)
+    normal = orc.e4m3_to_f32(sf) >= 2.0 ** -6
+    assert np.all(np.abs(s[:, ::16] * 6.0 - blk)[normal] <= blk[normal] * 2.0 ** -4 * (1 + 1e-6))
+
+
+@settings(**SETTINGS)
 @given(x=hnp.arrays(np.float32, 128, elements=st.floats(min_value=-100, max_value=100, allow_nan=False, width=32)))
 def test_nf4_codes_are_nearest_levels(orc, x):
     """Nf4Quantizer (nf4.rs:93-155): each code is a nearest level of x / absmax; decode(encode(x)) re-encodes to the same codes."""

@@ -149,3 +149,29 @@ def test_reference_linear_is_linear_to_rounding(orc, a, b, w):
     ya, yb, yab = orc.ref_linear_f32(a, w), orc.ref_linear_f32(b, w), orc.ref_linear_f32(a + b, w)
     mag = (np.abs(a) + np.abs(b)) @ np.abs(w).T
     assert np.all(np.abs(yab - (ya + yb)) <= 1e-5 * mag + 1e-30)
+
+
+@settings(**SETTINGS)
+@given(w=hnp.arrays(np.float32, (6, 8), elements=st.floats(min_value=-4, max_value=4, allow_nan=False, width=32)),
+       bits=st.sampled_from([3, 4, 8]), symmetric=st.booleans(), diag=st.floats(min_value=0.5, max_value=8.0))
+def test_gptq_with_a_diagonal_hessian_is_round_to_nearest_per_column(orc, w, bits, symmetric, diag):
+    """GptqQuantizer::quantize_layer (gptq.rs:133-257): a diagonal Hessian has a diagonal inverse, so no column's error reaches a later
+    column and the codes are plain per-column round-to-nearest with the column's own parameters (col_quant_params, :242-276)."""
+    h = np.eye(8, dtype=np.float32) * np.float32(diag)
+    q, sc, zp = orc.ref_gptq_quantize_layer(w, 6, 8, h, bits=bits, symmetric=symmetric, percdamp=0.01)
+    if symmetric:
+        q_min, q_max = -(1 << (bits - 1)), (1 << (bits - 1)) - 1
+        am = np.maximum(np.abs(w).max(axis=0), np.float32(1e-8))
+        scale = (am / np.float32(q_max)).astype(np.float32)
+        zero = np.zeros(8, np.int32)
+    else:
+        q_min, q_max = 0, (1 << bits) - 1
+        lo, hi = w.min(axis=0), w.max(axis=0)
+        scale = (np.maximum(hi - lo, np.float32(1e-8)) / np.float32(q_max)).astype(np.float32)
+        t = (-lo / scale).astype(np.float32)
+        zero = np.clip(np.sign(t) * np.floor(np.abs(t) + np.float32(0.5)), q_min, q_max).astype(np.int32)
+    assert np.array_equal(sc.view(np.uint32), scale.view(np.uint32)) and np.array_equal(zp, zero)
+    t = (w / scale[None, :]).astype(np.float32) + zero[None, :].astype(np.float32)
+    want = np.clip(np.sign(t) * np.floor(np.abs(t) + np.float32(0.5)), q_min, q_max).astype(np.int32)
+    assert np.array_equal(q, want)
+    assert np.all(np.abs(orc.gptq_dequantize(q, sc, zp) - w)[(want > q_min) & (want < q_max)] <= scale[None, :].repeat(6, axis=0)[(want > q_min) & (want < q_max)] * 0.5 * (1 + 1e-5) + 1e-7)

@@ -123,3 +123,13 @@ def test_nf4_thresholds_match_the_reference_comparison():
             v = np.nextafter(v, np.float32(2.0), dtype=np.float32)
     for v in (-2.0, -1.0, 0.0, 1.0, 2.0, float("nan")):
         assert int((np.float32(v) > thr).sum()) == near(v)
+
+
+def test_package_exports_exist():
+    """Everything the package lists in __all__ can be imported (ops and dist_infer load on first use)."""
+    import importlib
+    pkg = importlib.import_module("oxicuda_b200")
+    for name in pkg.__all__:
+        assert getattr(pkg, name).__name__ == "oxicuda_b200." + name
+    with pytest.raises(AttributeError):
+        pkg.no_such_module

@@ -133,3 +133,19 @@ def test_package_exports_exist():
         assert getattr(pkg, name).__name__ == "oxicuda_b200." + name
     with pytest.raises(AttributeError):
         pkg.no_such_module
+
+
+def test_integration_stubs_match_the_header():
+    """Every `pub fn oxq_*` line of the binding shown in INTEGRATION.md names a declared entry and has its number of arguments."""
+    hdr = open(os.path.join(ROOT, "include", "oxq.h")).read()
+    decl = {}
+    for m in re.finditer(r"OXQ_API\s+[\w\s\*]+?\b(oxq_\w+)\s*\(([^;]*)\);", hdr, re.S):
+        args = [a.strip() for a in re.sub(r"\s+", " ", m.group(2)).split(",")]
+        decl[m.group(1)] = 0 if args == ["void"] else len(args)
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    stubs = re.findall(r"pub fn (oxq_\w+)\(([^;]*)\)\s*->", text, re.S)
+    assert len(stubs) >= 20
+    for name, args in stubs:
+        assert name in decl, f"{name} is not declared in oxq.h"
+        n = len([a for a in re.sub(r"\s+", " ", args).split(",") if a.strip()])
+        assert n == decl[name], f"{name}: {n} arguments in INTEGRATION.md, {decl[name]} in oxq.h"

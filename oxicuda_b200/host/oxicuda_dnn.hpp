@@ -3,7 +3,7 @@
 //   quantize_to_int8 / dequantize_from_int8       crates/oxicuda-dnn/src/quantize/int8_quantize.rs:33-157
 //   quantize_to_fp8 / dequantize_from_fp8         crates/oxicuda-dnn/src/quantize/fp8_quantize.rs:47-170
 //   Int4QuantConfig, quantize_to_int4, dequantize_int4   crates/oxicuda-dnn/src/quantize/int4_quantize.rs:60-300
-//   quantize_block_scaled                         crates/oxicuda-dnn/src/quantize/block_scale.rs:53-140
+//   quantize_block_scaled, Fp4BlockQuantizer      crates/oxicuda-dnn/src/quantize/block_scale.rs:53-140, :346-395
 //   TensorDesc / TensorDescMut (matrix, from_raw, numel)   crates/oxicuda-dnn/src/types.rs:108-400
 //   DnnError                                      crates/oxicuda-dnn/src/error.rs:13-60
 // The order of the checks is the reference's.  BufferTooSmall carries byte counts, as error.rs documents the variant
@@ -218,5 +218,22 @@ inline void quantize_block_scaled(const DnnHandle& handle, const TensorDesc<T>& 
     handle.check(oxq_dnn_block_scaled_quant(handle.raw(), input.ptr, GpuFloat<T>::DTYPE, (int64_t)n, (int64_t)block_size, output.as_device_ptr(),
                                             scales.as_device_ptr()));
 }
+
+// Fp4BlockQuantizer (crates/oxicuda-dnn/src/quantize/block_scale.rs:346-395): the host-side helper for blocks of 32 E2M1 codes.
+struct Fp4BlockQuantizer {
+    static constexpr float MAX_VALUE = 6.0f;
+    static constexpr size_t REQUIRED_BLOCK_SIZE = 32;
+    size_t block_size;
+    explicit Fp4BlockQuantizer(size_t block_size) : block_size(block_size) {
+        if (block_size != REQUIRED_BLOCK_SIZE) throw DnnError("InvalidArgument", "NVFP4/OCP MXFP4 block size must be 32, got " + std::to_string(block_size));
+    }
+    // max |x| / 6, or 1 for an all-zero block; NaN elements are skipped as f32::max skips them
+    float compute_scale(const std::vector<float>& block) const {
+        float max_abs = 0.0f;
+        for (float v : block) { const float a = v < 0.0f ? -v : v; if (a > max_abs) max_abs = a; }
+        return max_abs == 0.0f ? 1.0f : max_abs / MAX_VALUE;
+    }
+    size_t num_scales(size_t n) const { return (n + block_size - 1) / block_size; }
+};
 
 }  // namespace oxicuda_dnn

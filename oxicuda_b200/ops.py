@@ -268,6 +268,29 @@ def dequantize_int4(packed: torch.Tensor, scales: torch.Tensor, output: torch.Te
     handle(packed.device.index).call("oxq_dnn_int4_dequant", _p(packed), _p(scales), n, config.group_size, 1 if config.symmetric else 0, _p(output))
 
 
+class Fp4BlockQuantizer:
+    """Fp4BlockQuantizer of the DNN layer (crates/oxicuda-dnn/src/quantize/block_scale.rs:346-395): the host-side helper for blocks of
+    32 E2M1 codes; compute_scale is max |x| / 6 in f32, or 1 for an all-zero block."""
+
+    MAX_VALUE = 6.0
+    REQUIRED_BLOCK_SIZE = 32
+
+    def __init__(self, block_size: int):
+        if block_size != self.REQUIRED_BLOCK_SIZE:
+            from .errors import DnnError
+            raise DnnError("InvalidArgument", f"NVFP4/OCP MXFP4 block size must be {self.REQUIRED_BLOCK_SIZE}, got {block_size}", 15)
+        self.block_size = int(block_size)
+
+    def compute_scale(self, block) -> float:
+        import numpy as np
+        b = np.asarray(block, dtype=np.float32)
+        max_abs = np.float32(np.nanmax(np.abs(b))) if b.size and not np.isnan(b).all() else np.float32(0.0)   # f32::max skips NaN
+        return 1.0 if max_abs == 0.0 else float(max_abs / np.float32(self.MAX_VALUE))
+
+    def num_scales(self, n: int) -> int:
+        return -(-n // self.block_size)
+
+
 def quantize_block_scaled(desc: TensorDesc, output: torch.Tensor, scales: torch.Tensor, block_size: int):
     """quantize_block_scaled (crates/oxicuda-dnn/src/quantize/block_scale.rs:53-140): one biased byte per element into
     `output`, one f32 scale per block into `scales`."""

@@ -1,8 +1,10 @@
 // Drives the C++ mirror of the oxicuda-dnn quantize API (oxicuda_b200/host/oxicuda_dnn.hpp) on a GPU: known answers and
 // the reference's buffer checks are verified here; the results on a 4100-element pattern are written to a file that the
-// Python test compares with the oracle bit for bit.  Usage: host_dnn_test <out.bin>; exit code 0 on success.
+// Python test compares with the oracle bit for bit.  Usage: host_dnn_test <out.bin> (on a GPU) or host_dnn_test host (the
+// configuration types and Fp4BlockQuantizer only, no device); exit code 0 on success.
 #include <cmath>
 #include <cstdio>
+#include <string>
 #include <vector>
 #include "../../oxicuda_b200/host/oxicuda_dnn.hpp"
 
@@ -10,9 +12,35 @@ using namespace oxicuda_dnn;
 
 template <typename T> static void put(FILE* f, const std::vector<T>& v) { fwrite(v.data(), sizeof(T), v.size(), f); }
 
+// host-only checks: Int4QuantConfig (int4_quantize.rs:971-996) and Fp4BlockQuantizer (block_scale.rs:475-610)
+static int host_checks() {
+    Int4QuantConfig cfg(128, true);
+    if (cfg.num_groups(256) != 2 || cfg.num_groups(257) != 3 || cfg.packed_bytes(256) != 128 || cfg.packed_bytes(257) != 129) return 40;
+    int errs = 0;
+    try { Int4QuantConfig(0, true); } catch (const DnnError& e) { errs += e.variant == "InvalidArgument"; }
+    try { Fp4BlockQuantizer(16); } catch (const DnnError& e) { errs += e.variant == "InvalidArgument"; }
+    try { Fp4BlockQuantizer(64); } catch (const DnnError& e) { errs += e.variant == "InvalidArgument"; }
+    if (errs != 3) return 41;
+    if (Fp4BlockQuantizer::MAX_VALUE != 6.0f || Fp4BlockQuantizer::REQUIRED_BLOCK_SIZE != 32) return 42;
+    Fp4BlockQuantizer q(32);
+    if (q.block_size != 32 || q.num_scales(32) != 1 || q.num_scales(96) != 3 || q.num_scales(33) != 2 || q.num_scales(0) != 0) return 43;
+    if (q.compute_scale(std::vector<float>(32, 0.0f)) != 1.0f || std::fabs(q.compute_scale(std::vector<float>(32, 6.0f)) - 1.0f) > 1e-6f ||
+        std::fabs(q.compute_scale(std::vector<float>(32, 12.0f)) - 2.0f) > 1e-6f) return 44;
+    std::vector<float> block(32, 0.0f);
+    block[0] = -6.0f; block[1] = 3.0f; block[2] = 1.5f;
+    if (std::fabs(q.compute_scale(block) - 1.0f) > 1e-6f) return 45;
+    try { TensorDesc<float>::from_raw(nullptr, {}, {}); } catch (const DnnError& e) { errs += e.variant == "InvalidDimension"; }
+    try { TensorDesc<float>::from_raw(nullptr, {2, 4}, {4}); } catch (const DnnError& e) { errs += e.variant == "InvalidDimension"; }
+    if (errs != 5) return 46;
+    if (TensorDesc<float>::from_raw(nullptr, {2, 3, 4}, {12, 4, 1}).numel() != 24) return 47;
+    return 0;
+}
+
 int main(int argc, char** argv) {
     if (argc < 2) return 2;
     try {
+        if (int rc = host_checks()) return rc;
+        if (std::string(argv[1]) == "host") return 0;
         DnnHandle handle;
         // ---- per-tensor INT8: scale = absmax / 127, codes, round trip (int8_quantize.rs:26-29)
         {

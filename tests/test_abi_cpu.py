@@ -149,3 +149,19 @@ def test_integration_stubs_match_the_header():
         assert name in decl, f"{name} is not declared in oxq.h"
         n = len([a for a in re.sub(r"\s+", " ", args).split(",") if a.strip()])
         assert n == decl[name], f"{name}: {n} arguments in INTEGRATION.md, {decl[name]} in oxq.h"
+
+
+def test_fp4_block_quantizer_host_helper(orc):  # crates/oxicuda-dnn/src/quantize/block_scale.rs:475-610
+    from oxicuda_b200 import ops
+    from oxicuda_b200.errors import DnnError
+    assert ops.Fp4BlockQuantizer.MAX_VALUE == 6.0 and ops.Fp4BlockQuantizer.REQUIRED_BLOCK_SIZE == 32
+    for bad in (16, 64):
+        with pytest.raises(DnnError) as e:
+            ops.Fp4BlockQuantizer(bad)
+        assert e.value.variant == "InvalidArgument"
+    q = ops.Fp4BlockQuantizer(32)
+    assert q.block_size == 32 and [q.num_scales(n) for n in (32, 96, 33, 0)] == [1, 3, 2, 0]
+    assert q.compute_scale([0.0] * 32) == 1.0 and abs(q.compute_scale([6.0] * 32) - 1.0) < 1e-6 and abs(q.compute_scale([12.0] * 32) - 2.0) < 1e-6
+    assert abs(q.compute_scale([-6.0, 3.0, 1.5] + [0.0] * 29) - 1.0) < 1e-6
+    block = orc.gaussian((1, 32), 3.0, 5).ravel()
+    assert q.compute_scale(block) == orc.ref_fp4_block_compute_scale(block)            # the oracle's restatement of the same lines

@@ -35,6 +35,14 @@ def test_host_config_types(tmp_path):
     assert run.returncode == 0, f"check {run.returncode} failed: {run.stdout} {run.stderr}"
 
 
+def test_host_dnn_types(tmp_path):
+    """Int4QuantConfig, TensorDesc::from_raw and Fp4BlockQuantizer (the reference's tests of int4_quantize.rs:971-996 and
+    block_scale.rs:475-610 restated in tests/cpp/host_dnn_test.cpp): host only."""
+    exe = _build(tmp_path, "host_dnn_test")
+    run = subprocess.run([exe, "host"], capture_output=True, text=True, timeout=60)
+    assert run.returncode == 0, f"check {run.returncode} failed: {run.stdout} {run.stderr}"
+
+
 def test_host_lm_types(tmp_path):
     """WeightTensor, silu and SwiGluFfn's argument errors (crates/oxicuda-lm/src/layer/ffn.rs:279-296, :391-395; weights.rs:31-76)
     restated in tests/cpp/host_lm_test.cpp: host only."""

@@ -1,6 +1,7 @@
 """Checks the oracle's format conversions against independent implementations (numpy float16,
-torch float8_e4m3fn / bfloat16 on CPU, brute-force nearest-grid search) and the spec quantizers
-against plain numpy restatements of their stated formulas."""
+torch float8_e4m3fn / bfloat16 on CPU, brute-force nearest-grid search, ml_dtypes' float4_e2m1fn /
+float8_e4m3fn / float8_e8m0fnu) and the spec quantizers against plain numpy restatements of their
+stated formulas (the block-scaled ones rebuilt from ml_dtypes casts, code for code)."""
 import numpy as np
 import pytest
 import torch
@@ -191,3 +192,71 @@ def test_linear_order_and_threads(orc):
     for i in range(333):
         acc = np.float32(acc + np.float32(x[2, i] * w[5, i]))
     assert y1[2, 5] == acc
+
+
+# ---- against ml_dtypes (Google's reference implementation of the narrow float types): element conversions, then the two
+#      block-scaled quantizers rebuilt from its casts and compared code for code -------------------------------------------
+
+def test_element_conversions_match_ml_dtypes(orc):
+    ml = pytest.importorskip("ml_dtypes")
+    x = _all_interesting_f32()
+    inside = x[np.abs(x) <= 448.0]                                       # beyond 448 ml_dtypes gives NaN, the quantizers saturate
+    assert np.array_equal(orc.e4m3_rne_sat(inside), inside.astype(ml.float8_e4m3fn).view(np.uint8))
+    assert np.array_equal(orc.e4m3_to_f32(np.arange(256, dtype=np.uint8)), np.arange(256, dtype=np.uint8).view(ml.float8_e4m3fn).astype(np.float32),
+                          equal_nan=True)
+    small = np.concatenate([x[np.abs(x) <= 8.0], np.arange(-64, 65, dtype=np.float32) * np.float32(0.125), np.array([6.0, 7.0, 100.0, -1e9], np.float32)])
+    assert np.array_equal(orc.e2m1_rne_sat(small) & 0xF, small.astype(ml.float4_e2m1fn).view(np.uint8) & 0xF)        # saturating, ties to even
+    assert np.array_equal(orc.e2m1_to_f32(np.arange(16, dtype=np.uint8)), np.arange(16, dtype=np.uint8).view(ml.float4_e2m1fn).astype(np.float32))
+    # E8M0: byte b is 2^(b - 127) (0xFF is NaN and never written by the quantizer)
+    b = np.arange(255, dtype=np.uint8)
+    x8 = orc.gaussian((1, 32), 1.0, 3)
+    for byte in (1, 60, 127, 128, 200, 246):                                     # 246: a block maximum in the last f32 binade
+        scaled = (x8 * np.exp2(np.float32(byte - 127 + 8) - np.floor(np.log2(np.abs(x8).max())))).astype(np.float32)
+        _, sf = orc.spec_mxfp8_quant(scaled)
+        assert sf[0, 0] == byte and float(b[byte:byte + 1].view(ml.float8_e8m0fnu).astype(np.float32)[0]) == 2.0 ** (byte - 127)
+
+
+def _mxfp8_with_ml_dtypes(ml, x):
+    rows, k = x.shape
+    blocks = x.reshape(rows, k // 32, 32)
+    amax = np.abs(blocks).max(axis=2)
+    with np.errstate(divide="ignore"):
+        e = np.floor(np.log2(amax.astype(np.float64))).astype(np.int64) - 8   # shared exponent of OCP MX v1.0: floor(log2 max) - emax
+    byte = np.where(amax > 0, np.clip(e + 127, 0, 254), 0).astype(np.uint8)
+    scale = byte.view(ml.float8_e8m0fnu).astype(np.float32)
+    scaled = np.clip(blocks / scale[:, :, None], -448.0, 448.0).astype(np.float32)      # saturating conversion
+    codes = scaled.astype(ml.float8_e4m3fn).view(np.uint8)
+    return codes.reshape(rows, k), byte
+
+
+def test_mxfp8_quantizer_matches_a_restatement_over_ml_dtypes(orc):
+    ml = pytest.importorskip("ml_dtypes")
+    x = orc.gaussian((32, 256), 1.0, 5)
+    x[1, 32:64] *= np.float32(1e-12)
+    x[2, 64:96] *= np.float32(1e12)
+    x[3] = np.abs(x[3]) * np.float32(0.999) + np.float32(1e-3)           # no zeros in the row: every element is a normal code
+    codes, sf = orc.spec_mxfp8_quant(x)
+    want_codes, want_sf = _mxfp8_with_ml_dtypes(ml, x)
+    assert np.array_equal(sf, want_sf)
+    assert np.array_equal(codes & 0x7F, want_codes & 0x7F) and np.array_equal((codes >> 7)[(codes & 0x7F) != 0], (want_codes >> 7)[(codes & 0x7F) != 0])
+
+
+def test_nvfp4_quantizer_matches_a_restatement_over_ml_dtypes(orc):
+    ml = pytest.importorskip("ml_dtypes")
+    x = orc.gaussian((16, 256), 1.0, 7)
+    x[1, 16:32] *= np.float32(1e-3)
+    g = np.float32(orc.spec_nvfp4_global_scale(float(np.abs(x).max())))
+    assert g == np.float32(np.abs(x).max()) / (np.float32(448.0) * np.float32(6.0))
+    packed, sf = orc.spec_nvfp4_quant(x, float(g))
+    blocks = x.reshape(16, 16, 16)
+    amax = np.abs(blocks).max(axis=2)
+    want_sf = np.minimum(amax / (np.float32(6.0) * g), np.float32(448.0)).astype(np.float32).astype(ml.float8_e4m3fn)
+    assert np.array_equal(sf, want_sf.view(np.uint8))
+    d = g * want_sf.astype(np.float32)
+    live = d > 0
+    q = np.zeros(blocks.shape, np.uint8)
+    q[live] = (blocks[live] / d[live][:, None]).astype(np.float32).astype(ml.float4_e2m1fn).view(np.uint8) & 0xF
+    nib = np.stack([packed & 0xF, packed >> 4], axis=2).reshape(16, 16, 16)
+    assert np.array_equal(nib[live] & 0x7, q[live] & 0x7)                                                     # magnitudes code for code
+    nz = live[:, :, None] & ((nib & 0x7) != 0)
+    assert np.array_equal((nib >> 3)[nz], (q >> 3)[nz])                                                       # signs wherever the code is not a zero

@@ -260,3 +260,25 @@ def test_nvfp4_quantizer_matches_a_restatement_over_ml_dtypes(orc):
     assert np.array_equal(nib[live] & 0x7, q[live] & 0x7)                                                     # magnitudes code for code
     nz = live[:, :, None] & ((nib & 0x7) != 0)
     assert np.array_equal((nib >> 3)[nz], (q >> 3)[nz])                                                       # signs wherever the code is not a zero
+
+
+def test_nvfp4_packing_matches_compressed_tensors(orc):
+    """The byte layout of packed E2M1 codes (which nibble holds the even element, how the 16 codes are numbered) is the one
+    NVFP4 checkpoints use: compressed_tensors packs the oracle's decoded values into the oracle's own bytes and unpacks the
+    oracle's bytes into the same values; its tensor scale is the reciprocal of the oracle's g = max / (448 * 6)."""
+    helpers = pytest.importorskip("compressed_tensors.compressors.nvfp4.helpers")
+    from compressed_tensors.quantization.utils.helpers import generate_gparam
+    x = orc.gaussian((8, 128), 1.0, 9)
+    x[0, :16] = 0.0
+    g = float(orc.spec_nvfp4_global_scale(float(np.abs(x).max())))
+    packed, _ = orc.spec_nvfp4_quant(x, g)
+    nib = np.stack([packed & 0xF, packed >> 4], axis=2).reshape(8, 128)
+    vals = orc.e2m1_to_f32(nib)
+    repacked = helpers.pack_fp4_to_uint8(torch.from_numpy(vals)).numpy()
+    same = (nib & 0x7) != 0                                              # a zero may be packed with either sign
+    same_bytes = same.reshape(8, 64, 2).all(axis=2)
+    assert np.array_equal(repacked[same_bytes], packed[same_bytes]) and np.array_equal(repacked & 0x77, packed & 0x77)
+    unpacked = helpers.unpack_fp4_from_uint8(torch.from_numpy(packed), 8, 128, dtype=torch.float32).numpy()
+    assert np.array_equal(unpacked, vals)
+    gs = generate_gparam(torch.tensor([float(x.min())]), torch.tensor([float(x.max())]))
+    assert abs(float(gs) * g - 1.0) < 1e-6

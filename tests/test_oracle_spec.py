@@ -282,3 +282,18 @@ def test_nvfp4_packing_matches_compressed_tensors(orc):
     assert np.array_equal(unpacked, vals)
     gs = generate_gparam(torch.tensor([float(x.min())]), torch.tensor([float(x.max())]))
     assert abs(float(gs) * g - 1.0) < 1e-6
+
+
+def test_tiled_scale_factor_layout_is_the_128x4_interleave():
+    """The tiled order the GEMMs read scale factors in (tests/gpu_util.py: sf_to_mma_layout, the checker of the quantizers' second
+    output) is the block-scaled layout CUTLASS, cuBLASLt and the NVFP4 serving stacks use: rows padded to 128 and columns to 4,
+    viewed as [row tile][4][32][column tile][4] and permuted to [row tile][column tile][32][4][4]."""
+    from tests.gpu_util import sf_to_mma_layout
+    rng = np.random.default_rng(0)
+    for rows, cols in ((128, 4), (256, 8), (300, 10), (1, 1), (129, 5)):
+        sf = rng.integers(1, 255, size=(rows, cols), dtype=np.uint8)
+        mp, kp = -(-rows // 128) * 128, -(-cols // 4) * 4
+        padded = np.zeros((mp, kp), np.uint8)
+        padded[:rows, :cols] = sf
+        want = padded.reshape(mp // 128, 4, 32, kp // 4, 4).transpose(0, 3, 2, 1, 4).ravel()
+        assert np.array_equal(sf_to_mma_layout(sf), want)
